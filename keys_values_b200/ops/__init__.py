@@ -1,0 +1,233 @@
+"""Hot ops of the framework.
+
+Every op has exactly one GPU implementation, a hand-written sm_100a kernel in
+``keys_values_b200/csrc`` reached through :mod:`keys_values_b200.ops.cuda`, and a
+plain PyTorch restatement in :mod:`keys_values_b200.ops.reference` that serves
+CPU tensors and is the oracle in the tests. A CUDA tensor never falls back to
+the PyTorch restatement silently: if the native library cannot be loaded on a
+machine with a GPU, the first call raises.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from keys_values_b200.ops import reference as ref
+
+
+def _cuda():
+    from keys_values_b200.ops import cuda as _c
+
+    return _c
+
+
+def native_launches() -> int:
+    """Number of native kernel launches issued by this process so far."""
+    from keys_values_b200.ops import cuda as _c
+
+    return _c.launch_count()
+
+
+# ----------------------------------------------------------------- RMSNorm
+class _RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, eps, add_unit_offset):
+        y, rstd = _cuda().rmsnorm_fwd(x, weight, eps, add_unit_offset)
+        ctx.save_for_backward(x, weight, rstd)
+        ctx.add_unit_offset = add_unit_offset
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, weight, rstd = ctx.saved_tensors
+        need_w = weight is not None and ctx.needs_input_grad[1]
+        dx, dw = _cuda().rmsnorm_bwd(gy.contiguous(), x, weight, rstd, ctx.add_unit_offset, need_w)
+        return dx, dw, None, None
+
+
+def rmsnorm(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float, add_unit_offset: bool = False) -> torch.Tensor:
+    if x.is_cuda:
+        return _RMSNormFn.apply(x.contiguous(), weight, eps, add_unit_offset)
+    return ref.rmsnorm(x, weight, eps, add_unit_offset)
+
+
+# ------------------------------------------------------- QK-norm + RoPE + split
+class _QKNormRopeFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, q_weight, k_weight, H, G, D, eps, rope_n_elem, add_unit_offset):
+        q, k, v, rstd = _cuda().qknorm_rope_fwd(qkv, cos, sin, q_weight, k_weight, H, G, D, eps, rope_n_elem, add_unit_offset)
+        ctx.save_for_backward(qkv, cos, sin, q_weight, k_weight, rstd)
+        ctx.meta = (H, G, D, eps, rope_n_elem, add_unit_offset)
+        return q, k, v
+
+    @staticmethod
+    def backward(ctx, gq, gk, gv):
+        qkv, cos, sin, q_weight, k_weight, rstd = ctx.saved_tensors
+        H, G, D, eps, rope_n_elem, add_unit_offset = ctx.meta
+        need_w = q_weight is not None and (ctx.needs_input_grad[3] or ctx.needs_input_grad[4])
+        dqkv, dqw, dkw = _cuda().qknorm_rope_bwd(
+            gq.contiguous(), gk.contiguous(), gv.contiguous(), qkv, cos, sin, q_weight, k_weight, rstd,
+            H, G, D, rope_n_elem, add_unit_offset, need_w,
+        )
+        return dqkv, None, None, dqw, dkw, None, None, None, None, None, None
+
+
+def qknorm_rope(
+    qkv: torch.Tensor,
+    n_head: int,
+    n_query_groups: int,
+    head_size: int,
+    cos: Optional[torch.Tensor],
+    sin: Optional[torch.Tensor],
+    q_weight: Optional[torch.Tensor],
+    k_weight: Optional[torch.Tensor],
+    eps: float,
+    rope_n_elem: int,
+    add_unit_offset: bool = False,
+) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Fused split of ``qkv (B,T,(H+2G)D)`` + per-head RMSNorm of q/k + RoPE, giving
+    ``q (B,H,T,D)``, ``k, v (B,G,T,D)`` contiguous."""
+    if qkv.is_cuda and _cuda().qknorm_rope_supported(qkv, head_size, rope_n_elem):
+        return _QKNormRopeFn.apply(
+            qkv.contiguous(), cos, sin, q_weight, k_weight, n_head, n_query_groups, head_size, eps, rope_n_elem, add_unit_offset
+        )
+    return ref.qknorm_rope(qkv, n_head, n_query_groups, head_size, cos, sin, q_weight, k_weight, eps, rope_n_elem, add_unit_offset)
+
+
+# ------------------------------------------------------------------- SwiGLU
+class _SwiGLUFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a, b):
+        ctx.save_for_backward(a, b)
+        return _cuda().swiglu_fwd(a, b)
+
+    @staticmethod
+    def backward(ctx, gy):
+        a, b = ctx.saved_tensors
+        return _cuda().swiglu_bwd(gy.contiguous(), a, b)
+
+
+def swiglu(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    if a.is_cuda:
+        return _SwiGLUFn.apply(a.contiguous(), b.contiguous())
+    return ref.swiglu(a, b)
+
+
+# ------------------------------------------------------------------ attention
+def sdpa_fwd(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    scale: float,
+    input_pos: int,
+    token_pos: Optional[torch.Tensor] = None,
+    return_weights: bool = False,
+    sliding_window: Optional[int] = None,
+    softcap: Optional[float] = None,
+):
+    """Returns ``(out (B,q,H·D), weights (B,G,kv) fp32 | None, lse (B,H,q) fp32)``."""
+    if query.is_cuda and _cuda().sdpa_supported(query, key, sliding_window, softcap):
+        return _cuda().sdpa_fwd(query, key, value, scale, input_pos, token_pos, return_weights)
+    return ref.sdpa(query, key, value, scale, input_pos, token_pos, return_weights, sliding_window, softcap, return_lse=True)
+
+
+def sdpa_bwd(
+    grad_out: torch.Tensor,
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    out: torch.Tensor,
+    lse: torch.Tensor,
+    scale: float,
+    input_pos: int,
+    token_pos: Optional[torch.Tensor] = None,
+    sliding_window: Optional[int] = None,
+    softcap: Optional[float] = None,
+):
+    """Returns fp32 ``dq (B,H,q,D)``, ``dk, dv (B,G,kv,D)``."""
+    if query.is_cuda and _cuda().sdpa_supported(query, key, sliding_window, softcap):
+        return _cuda().sdpa_bwd(grad_out, query, key, value, out, lse, scale, input_pos, token_pos)
+    return ref.sdpa_backward(grad_out, query, key, value, scale, input_pos, token_pos, sliding_window, softcap)
+
+
+class SDPAFunction(torch.autograd.Function):
+    """Differentiable SDPA (no cache) on top of :func:`sdpa_fwd` / :func:`sdpa_bwd`
+    (role of ``keys_values/attention/sdpa_op.py:254-371``)."""
+
+    @staticmethod
+    def forward(ctx, query, key, value, scale, input_pos, token_pos, sliding_window, softcap):
+        out, _, lse = sdpa_fwd(query, key, value, scale, input_pos, token_pos, False, sliding_window, softcap)
+        ctx.save_for_backward(query, key, value, out, lse, token_pos)
+        ctx.meta = (scale, input_pos, sliding_window, softcap)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        query, key, value, out, lse, token_pos = ctx.saved_tensors
+        scale, input_pos, sliding_window, softcap = ctx.meta
+        dq, dk, dv = sdpa_bwd(grad_out.contiguous(), query, key, value, out, lse, scale, input_pos, token_pos, sliding_window, softcap)
+        return dq.to(query.dtype), dk.to(key.dtype), dv.to(value.dtype), None, None, None, None, None
+
+
+def sdpa(query, key, value, scale, input_pos, token_pos=None, return_weights=False, sliding_window=None, softcap=None):
+    """SDPA returning ``(out, weights)``; differentiable when weights are not requested."""
+    if return_weights or not torch.is_grad_enabled() or not (query.requires_grad or key.requires_grad or value.requires_grad):
+        out, w, _ = sdpa_fwd(query, key, value, scale, input_pos, token_pos, return_weights, sliding_window, softcap)
+        return out, w
+    return SDPAFunction.apply(query, key, value, scale, input_pos, token_pos, sliding_window, softcap), None
+
+
+# ---------------------------------------------------------------- quantization
+def quantize_rows(x: torch.Tensor, bits: int):
+    if x.is_cuda:
+        return _cuda().quantize_rows(x, bits)
+    return ref.quantize_rows(x, bits)
+
+
+def dequantize_rows(q: torch.Tensor, scale: torch.Tensor, zp: torch.Tensor, bits: int, dtype: torch.dtype, out: Optional[torch.Tensor] = None):
+    if q.is_cuda:
+        return _cuda().dequantize_rows(q, scale, zp, bits, dtype, out)
+    res = ref.dequantize_rows(q, scale, zp, bits, dtype)
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
+
+
+# ------------------------------------------------------------ cache primitives
+def cache_write(k_buf, v_buf, token_pos, slots, key, value, input_pos: int) -> None:
+    if k_buf.is_cuda:
+        return _cuda().cache_write(k_buf, v_buf, token_pos, slots, key, value, input_pos)
+    return ref.cache_write(k_buf, v_buf, token_pos, slots, key, value, input_pos)
+
+
+def cache_write_quant(k_buf, v_buf, token_pos, slots, key, value, input_pos: int, qk, sk, zk, qv, sv, zv, bits: int) -> None:
+    """:func:`cache_write` into the full-precision scratch ``k_buf/v_buf`` (skipped if
+    ``None``) fused with quantize-on-write of the same rows into the quantized
+    storage ``q* (B,G,C,D|D/2) uint8``, ``s* (B,G,C) fp32``, ``z* (B,G,C) int32``."""
+    if key.is_cuda:
+        return _cuda().cache_write_quant(k_buf, v_buf, token_pos, slots, key, value, input_pos, qk, sk, zk, qv, sv, zv, bits)
+    B = key.shape[0]
+    idx = slots.to(torch.int64)
+    if k_buf is not None:
+        ref.cache_write(k_buf, v_buf, token_pos, slots, key, value, input_pos)
+    else:
+        n = key.shape[2]
+        pos = (input_pos + torch.arange(n, device=key.device, dtype=token_pos.dtype)).view(1, 1, n).expand(B, key.shape[1], n)
+        token_pos[:B].scatter_(2, idx, pos)
+    for x, q, s, z in ((key, qk, sk, zk), (value, qv, sv, zv)):
+        xq, xs, xz = ref.quantize_rows(x, bits)
+        q[:B].scatter_(2, idx.unsqueeze(-1).expand(-1, -1, -1, xq.shape[-1]), xq)
+        s[:B].scatter_(2, idx, xs)
+        z[:B].scatter_(2, idx, xz)
+
+
+def h2o_update(scores, weights, k_select: int, n_evictable: int, normalize=False, token_pos=None, input_pos=0, prefill_length=0):
+    if scores.is_cuda:
+        return _cuda().h2o_update(scores, weights, k_select, n_evictable, normalize, token_pos, input_pos, prefill_length)
+    return ref.h2o_update(scores, weights, k_select, n_evictable, normalize, token_pos, input_pos, prefill_length)
+
+
+def cross_entropy_sum(logits: torch.Tensor, targets: torch.Tensor, ignore_index: int = -100) -> torch.Tensor:
+    return ref.cross_entropy_sum(logits, targets, ignore_index)
