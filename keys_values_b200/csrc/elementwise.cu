@@ -1,0 +1,347 @@
+// Memory-bound fused ops: RMSNorm, QKV split + per-head QK-RMSNorm + RoPE + layout
+// change, SwiGLU; forward and backward. One warp per row, fp32 math, 16-byte
+// accesses where the layout allows.
+//
+// Replaces the reference's Triton kernels (keys_values/fused/fused_rmsnorm.py:28-209,
+// fused_rope.py:30-169, fused_swiglu.py:28-73) and the split/transposes/norms of
+// keys_values/model.py:690-779.
+#include "common.cuh"
+#include "kvb200.h"
+
+namespace kvb {
+
+#define KVB_DISPATCH_DTYPE(dtype, ...)                      \
+  switch (dtype) {                                          \
+    case 0: { using T = float; __VA_ARGS__; break; }        \
+    case 1: { using T = __nv_bfloat16; __VA_ARGS__; break; } \
+    case 2: { using T = __half; __VA_ARGS__; break; }       \
+    default: return KVB_ERR_ARG;                            \
+  }
+
+constexpr int EW_WARPS = 8;
+
+// ------------------------------------------------------------------- RMSNorm
+template <typename T>
+__global__ void rmsnorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y, float* __restrict__ rstd,
+                                   long long rows, int dim, float eps, int unit) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * EW_WARPS + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const T* xr = x + row * dim;
+  float ss = 0.f;
+  for (int i = lane; i < dim; i += 32) {
+    float v = to_f32(xr[i]);
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / dim + eps);
+  if (lane == 0 && rstd) rstd[row] = r;
+  T* yr = y + row * dim;
+  for (int i = lane; i < dim; i += 32) {
+    float v = to_f32(xr[i]) * r;
+    if (w) {
+      float ww = to_f32(w[i]);
+      v *= unit ? 1.f + ww : ww;
+    }
+    yr[i] = from_f32<T>(v);
+  }
+}
+
+template <typename T>
+__global__ void rmsnorm_bwd_kernel(const T* __restrict__ gy, const T* __restrict__ x, const T* __restrict__ w,
+                                   const float* __restrict__ rstd, T* __restrict__ dx, float* __restrict__ dw_partial,
+                                   long long rows, int dim, int unit) {
+  extern __shared__ float dw_s[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (dw_partial) {
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) dw_s[i] = 0.f;
+    __syncthreads();
+  }
+  for (long long row = (long long)blockIdx.x * EW_WARPS + warp; row < rows; row += (long long)gridDim.x * EW_WARPS) {
+    const T* xr = x + row * dim;
+    const T* gr = gy + row * dim;
+    const float r = rstd[row];
+    float dot = 0.f;
+    for (int i = lane; i < dim; i += 32) {
+      float ww = w ? to_f32(w[i]) : 1.f;
+      if (w && unit) ww += 1.f;
+      dot += to_f32(gr[i]) * ww * to_f32(xr[i]) * r;
+    }
+    dot = warp_sum(dot) / dim;
+    T* dr = dx + row * dim;
+    for (int i = lane; i < dim; i += 32) {
+      float ww = w ? to_f32(w[i]) : 1.f;
+      if (w && unit) ww += 1.f;
+      const float xh = to_f32(xr[i]) * r;
+      const float g = to_f32(gr[i]);
+      dr[i] = from_f32<T>(r * (g * ww - xh * dot));
+      if (dw_partial) atomicAdd(&dw_s[i], g * xh);
+    }
+  }
+  if (dw_partial) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) dw_partial[(long long)blockIdx.x * dim + i] = dw_s[i];
+  }
+}
+
+// ------------------------------------------------- QKV split + QK-norm + RoPE
+// Row id = ((b * T + t) * (H + 2G) + head); heads [0,H) are queries, [H,H+G) keys,
+// [H+G,H+2G) values.
+template <typename T>
+__global__ void qknorm_rope_fwd_kernel(const T* __restrict__ qkv, const float* __restrict__ cosT, const float* __restrict__ sinT,
+                                       const T* __restrict__ qw, const T* __restrict__ kw, T* __restrict__ q, T* __restrict__ k,
+                                       T* __restrict__ v, float* __restrict__ rstd, int B, int Tn, int H, int G, int D, float eps,
+                                       int rope_n, int unit) {
+  extern __shared__ float sm[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float* xs = sm + warp * D;
+  const int NH = H + 2 * G;
+  const long long row = (long long)blockIdx.x * EW_WARPS + warp;
+  if (row >= (long long)B * Tn * NH) return;
+  const int head = (int)(row % NH);
+  const long long bt = row / NH;
+  const int t = (int)(bt % Tn);
+  const int b = (int)(bt / Tn);
+  const T* src = qkv + row * D;
+  T* dst;
+  if (head < H) dst = q + (((long long)b * H + head) * Tn + t) * D;
+  else if (head < H + G) dst = k + (((long long)b * G + (head - H)) * Tn + t) * D;
+  else {
+    dst = v + (((long long)b * G + (head - H - G)) * Tn + t) * D;
+    for (int i = lane; i < D; i += 32) dst[i] = src[i];
+    return;
+  }
+  const T* w = head < H ? qw : kw;
+  float ss = 0.f;
+  for (int i = lane; i < D; i += 32) {
+    float x = to_f32(src[i]);
+    xs[i] = x;
+    ss += x * x;
+  }
+  float r = 1.f;
+  if (w) {
+    ss = warp_sum(ss);
+    r = rsqrtf(ss / D + eps);
+    if (lane == 0) rstd[bt * (H + G) + head] = r;
+  }
+  __syncwarp();
+  if (w) {
+    for (int i = lane; i < D; i += 32) {
+      float ww = to_f32(w[i]);
+      xs[i] = xs[i] * r * (unit ? 1.f + ww : ww);
+    }
+    __syncwarp();
+  }
+  const int half = rope_n >> 1;
+  for (int i = lane; i < D; i += 32) {
+    float y = xs[i];
+    if (i < rope_n) {
+      const float c = cosT[(long long)t * rope_n + i], s = sinT[(long long)t * rope_n + i];
+      const float rot = i < half ? -xs[i + half] : xs[i - half];
+      y = y * c + rot * s;
+    }
+    dst[i] = from_f32<T>(y);
+  }
+}
+
+template <typename T>
+__global__ void qknorm_rope_bwd_kernel(const T* __restrict__ gq, const T* __restrict__ gk, const T* __restrict__ gv,
+                                       const T* __restrict__ qkv, const float* __restrict__ cosT, const float* __restrict__ sinT,
+                                       const T* __restrict__ qw, const T* __restrict__ kw, const float* __restrict__ rstd,
+                                       T* __restrict__ dqkv, float* __restrict__ dw_partial, int B, int Tn, int H, int G, int D,
+                                       int rope_n, int unit) {
+  extern __shared__ float sm[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float* gs = sm + warp * D;             // per-warp staging of the incoming gradient
+  float* dw_s = sm + EW_WARPS * D;       // [2][D] partial weight gradients (q, k)
+  if (dw_partial) {
+    for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) dw_s[i] = 0.f;
+    __syncthreads();
+  }
+  const int NH = H + 2 * G;
+  const long long total = (long long)B * Tn * NH;
+  for (long long row = (long long)blockIdx.x * EW_WARPS + warp; row < total; row += (long long)gridDim.x * EW_WARPS) {
+    const int head = (int)(row % NH);
+    const long long bt = row / NH;
+    const int t = (int)(bt % Tn);
+    const int b = (int)(bt / Tn);
+    T* dst = dqkv + row * D;
+    if (head >= H + G) {
+      const T* g = gv + (((long long)b * G + (head - H - G)) * Tn + t) * D;
+      for (int i = lane; i < D; i += 32) dst[i] = g[i];
+      continue;
+    }
+    const T* g = head < H ? gq + (((long long)b * H + head) * Tn + t) * D : gk + (((long long)b * G + (head - H)) * Tn + t) * D;
+    const T* w = head < H ? qw : kw;
+    for (int i = lane; i < D; i += 32) gs[i] = to_f32(g[i]);
+    __syncwarp();
+    const int half = rope_n >> 1;
+    float gr[8];  // D <= 256 -> at most 8 elements per lane
+    int cnt = 0;
+    for (int i = lane; i < D; i += 32, ++cnt) {
+      float gi = gs[i];
+      if (i < rope_n) {
+        const float c = cosT[(long long)t * rope_n + i];
+        if (i < half) gi = gi * c + gs[i + half] * sinT[(long long)t * rope_n + i + half];
+        else gi = gi * c - gs[i - half] * sinT[(long long)t * rope_n + i - half];
+      }
+      gr[cnt] = gi;
+    }
+    if (!w) {
+      cnt = 0;
+      for (int i = lane; i < D; i += 32, ++cnt) dst[i] = from_f32<T>(gr[cnt]);
+      __syncwarp();
+      continue;
+    }
+    const T* src = qkv + row * D;
+    const float r = rstd[bt * (H + G) + head];
+    float dot = 0.f;
+    cnt = 0;
+    for (int i = lane; i < D; i += 32, ++cnt) {
+      float ww = to_f32(w[i]);
+      if (unit) ww += 1.f;
+      dot += gr[cnt] * ww * to_f32(src[i]) * r;
+    }
+    dot = warp_sum(dot) / D;
+    cnt = 0;
+    for (int i = lane; i < D; i += 32, ++cnt) {
+      float ww = to_f32(w[i]);
+      if (unit) ww += 1.f;
+      const float xh = to_f32(src[i]) * r;
+      dst[i] = from_f32<T>(r * (gr[cnt] * ww - xh * dot));
+      if (dw_partial) atomicAdd(&dw_s[(head < H ? 0 : D) + i], gr[cnt] * xh);
+    }
+    __syncwarp();
+  }
+  if (dw_partial) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) dw_partial[(long long)blockIdx.x * 2 * D + i] = dw_s[i];
+  }
+}
+
+// -------------------------------------------------------------------- SwiGLU
+template <typename T>
+__global__ void swiglu_fwd_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ y, long long n) {
+  constexpr int V = 16 / sizeof(T);
+  const long long i0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * V;
+  if (i0 + V <= n) {
+    uint4 av = *reinterpret_cast<const uint4*>(a + i0), bv = *reinterpret_cast<const uint4*>(b + i0), yv;
+    const T* ap = reinterpret_cast<const T*>(&av);
+    const T* bp = reinterpret_cast<const T*>(&bv);
+    T* yp = reinterpret_cast<T*>(&yv);
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      const float x = to_f32(ap[j]);
+      yp[j] = from_f32<T>(x / (1.f + __expf(-x)) * to_f32(bp[j]));
+    }
+    *reinterpret_cast<uint4*>(y + i0) = yv;
+  } else {
+    for (long long i = i0; i < n; ++i) {
+      const float x = to_f32(a[i]);
+      y[i] = from_f32<T>(x / (1.f + __expf(-x)) * to_f32(b[i]));
+    }
+  }
+}
+
+template <typename T>
+__global__ void swiglu_bwd_kernel(const T* __restrict__ gy, const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ da,
+                                  T* __restrict__ db, long long n) {
+  constexpr int V = 16 / sizeof(T);
+  const long long i0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * V;
+  if (i0 + V <= n) {
+    uint4 gvv = *reinterpret_cast<const uint4*>(gy + i0), av = *reinterpret_cast<const uint4*>(a + i0),
+          bv = *reinterpret_cast<const uint4*>(b + i0), dav, dbv;
+    const T* gp = reinterpret_cast<const T*>(&gvv);
+    const T* ap = reinterpret_cast<const T*>(&av);
+    const T* bp = reinterpret_cast<const T*>(&bv);
+    T* dap = reinterpret_cast<T*>(&dav);
+    T* dbp = reinterpret_cast<T*>(&dbv);
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      const float x = to_f32(ap[j]), g = to_f32(gp[j]), bb = to_f32(bp[j]);
+      const float sg = 1.f / (1.f + __expf(-x));
+      dap[j] = from_f32<T>(g * bb * sg * (1.f + x * (1.f - sg)));
+      dbp[j] = from_f32<T>(g * x * sg);
+    }
+    *reinterpret_cast<uint4*>(da + i0) = dav;
+    *reinterpret_cast<uint4*>(db + i0) = dbv;
+  } else {
+    for (long long i = i0; i < n; ++i) {
+      const float x = to_f32(a[i]), g = to_f32(gy[i]), bb = to_f32(b[i]);
+      const float sg = 1.f / (1.f + __expf(-x));
+      da[i] = from_f32<T>(g * bb * sg * (1.f + x * (1.f - sg)));
+      db[i] = from_f32<T>(g * x * sg);
+    }
+  }
+}
+
+static inline int check_launch() { return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH; }
+
+}  // namespace kvb
+
+using namespace kvb;
+
+extern "C" int kvb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long long rows, int dim, float eps,
+                               int add_unit_offset, int dtype, void* stream) {
+  if (rows <= 0 || dim <= 0) return KVB_ERR_ARG;
+  const unsigned grid = (unsigned)((rows + EW_WARPS - 1) / EW_WARPS);
+  KVB_DISPATCH_DTYPE(dtype, (rmsnorm_fwd_kernel<T><<<grid, EW_WARPS * 32, 0, (cudaStream_t)stream>>>(
+                                (const T*)x, (const T*)w, (T*)y, rstd, rows, dim, eps, add_unit_offset)));
+  return check_launch();
+}
+
+extern "C" int kvb_rmsnorm_bwd(const void* gy, const void* x, const void* w, const float* rstd, void* dx, float* dw_partial,
+                               long long rows, int dim, int add_unit_offset, int dtype, int n_partial, void* stream) {
+  if (rows <= 0 || dim <= 0 || n_partial <= 0) return KVB_ERR_ARG;
+  const size_t smem = dw_partial ? (size_t)dim * 4 : 0;
+  if (smem > 48 * 1024) return KVB_ERR_TOO_LARGE;
+  KVB_DISPATCH_DTYPE(dtype, (rmsnorm_bwd_kernel<T><<<n_partial, EW_WARPS * 32, smem, (cudaStream_t)stream>>>(
+                                (const T*)gy, (const T*)x, (const T*)w, rstd, (T*)dx, dw_partial, rows, dim, add_unit_offset)));
+  return check_launch();
+}
+
+extern "C" int kvb_qknorm_rope_fwd(const void* qkv, const float* cos, const float* sin, const void* qw, const void* kw, void* q,
+                                   void* k, void* v, float* rstd, int B, int T_, int H, int G, int D, float eps,
+                                   int rope_n_elem, int add_unit_offset, int dtype, void* stream) {
+  if (D > 256 || D <= 0 || rope_n_elem > D || (rope_n_elem & 1)) return KVB_ERR_UNSUPPORTED;
+  const long long rows = (long long)B * T_ * (H + 2 * G);
+  const unsigned grid = (unsigned)((rows + EW_WARPS - 1) / EW_WARPS);
+  const size_t smem = (size_t)EW_WARPS * D * 4;
+  KVB_DISPATCH_DTYPE(dtype, (qknorm_rope_fwd_kernel<T><<<grid, EW_WARPS * 32, smem, (cudaStream_t)stream>>>(
+                                (const T*)qkv, cos, sin, (const T*)qw, (const T*)kw, (T*)q, (T*)k, (T*)v, rstd, B, T_, H, G, D,
+                                eps, rope_n_elem, add_unit_offset)));
+  return check_launch();
+}
+
+extern "C" int kvb_qknorm_rope_bwd(const void* gq, const void* gk, const void* gv, const void* qkv, const float* cos,
+                                   const float* sin, const void* qw, const void* kw, const float* rstd, void* dqkv,
+                                   float* dw_partial, int B, int T_, int H, int G, int D, int rope_n_elem, int add_unit_offset,
+                                   int dtype, int n_partial, void* stream) {
+  if (D > 256 || D <= 0 || rope_n_elem > D || (rope_n_elem & 1) || n_partial <= 0) return KVB_ERR_UNSUPPORTED;
+  const size_t smem = (size_t)(EW_WARPS + 2) * D * 4;
+  KVB_DISPATCH_DTYPE(dtype, (qknorm_rope_bwd_kernel<T><<<n_partial, EW_WARPS * 32, smem, (cudaStream_t)stream>>>(
+                                (const T*)gq, (const T*)gk, (const T*)gv, (const T*)qkv, cos, sin, (const T*)qw, (const T*)kw,
+                                rstd, (T*)dqkv, dw_partial, B, T_, H, G, D, rope_n_elem, add_unit_offset)));
+  return check_launch();
+}
+
+extern "C" int kvb_swiglu_fwd(const void* a, const void* b, void* y, long long n, int dtype, void* stream) {
+  if (n <= 0) return KVB_ERR_ARG;
+  KVB_DISPATCH_DTYPE(dtype, {
+    constexpr int V = 16 / sizeof(T);
+    const unsigned grid = (unsigned)((n + 256LL * V - 1) / (256LL * V));
+    swiglu_fwd_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>((const T*)a, (const T*)b, (T*)y, n);
+  });
+  return check_launch();
+}
+
+extern "C" int kvb_swiglu_bwd(const void* gy, const void* a, const void* b, void* da, void* db, long long n, int dtype,
+                              void* stream) {
+  if (n <= 0) return KVB_ERR_ARG;
+  KVB_DISPATCH_DTYPE(dtype, {
+    constexpr int V = 16 / sizeof(T);
+    const unsigned grid = (unsigned)((n + 256LL * V - 1) / (256LL * V));
+    swiglu_bwd_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>((const T*)gy, (const T*)a, (const T*)b, (T*)da, (T*)db, n);
+  });
+  return check_launch();
+}

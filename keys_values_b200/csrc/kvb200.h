@@ -1,0 +1,67 @@
+// C API of libkvb200: every entry point launches on the given CUDA stream and
+// returns KVB_OK or a negative error code; none of them synchronises the device.
+// Pointers are device pointers unless stated otherwise. dtype codes: 0 = fp32,
+// 1 = bf16, 2 = fp16.
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  KVB_OK = 0,
+  KVB_ERR_ARG = -1,
+  KVB_ERR_ALIGN = -2,
+  KVB_ERR_DRIVER = -3,
+  KVB_ERR_TMAP = -4,
+  KVB_ERR_LAUNCH = -5,
+  KVB_ERR_UNSUPPORTED = -6,
+  KVB_ERR_TOO_LARGE = -7,
+  KVB_ERR_CUDA = -8,
+};
+
+// ---- elementwise.cu
+int kvb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long long rows, int dim, float eps, int add_unit_offset,
+                    int dtype, void* stream);
+int kvb_rmsnorm_bwd(const void* gy, const void* x, const void* w, const float* rstd, void* dx, float* dw_partial,
+                    long long rows, int dim, int add_unit_offset, int dtype, int n_partial, void* stream);
+int kvb_qknorm_rope_fwd(const void* qkv, const float* cos, const float* sin, const void* qw, const void* kw, void* q, void* k,
+                        void* v, float* rstd, int B, int T, int H, int G, int D, float eps, int rope_n_elem,
+                        int add_unit_offset, int dtype, void* stream);
+int kvb_qknorm_rope_bwd(const void* gq, const void* gk, const void* gv, const void* qkv, const float* cos, const float* sin,
+                        const void* qw, const void* kw, const float* rstd, void* dqkv, float* dw_partial, int B, int T, int H,
+                        int G, int D, int rope_n_elem, int add_unit_offset, int dtype, int n_partial, void* stream);
+int kvb_swiglu_fwd(const void* a, const void* b, void* y, long long n, int dtype, void* stream);
+int kvb_swiglu_bwd(const void* gy, const void* a, const void* b, void* da, void* db, long long n, int dtype, void* stream);
+
+// ---- quant.cu
+int kvb_quantize_rows(const void* x, uint8_t* q, float* scale, int32_t* zp, long long rows, int D, int bits, int dtype,
+                      void* stream);
+int kvb_dequantize_rows(const uint8_t* q, const float* scale, const int32_t* zp, void* out, int B, int G, int n, int D,
+                        long long q_sb, long long q_sg, long long q_sn, long long m_sb, long long m_sg, long long o_sb,
+                        long long o_sg, long long o_sn, int bits, int dtype, void* stream);
+int kvb_cache_write(void* k_buf, void* v_buf, int32_t* token_pos, const int32_t* slots, const void* key, const void* value,
+                    uint8_t* qk, float* sk, int32_t* zk, uint8_t* qv, float* sv, int32_t* zv, int B, int G, int n, int D, int C,
+                    long long slot_sb, long long slot_sg, int input_pos, int bits, int dtype, int* status, void* stream);
+
+// ---- h2o.cu
+int kvb_h2o_update(float* scores, const float* weights, const int32_t* token_pos, int32_t* out_idx, int B, int G, int C,
+                   int n_evictable, int k_select, int normalize, int input_pos, int prefill_length, long long sc_sb,
+                   long long sc_sg, long long tp_sb, long long tp_sg, void* stream);
+
+// ---- gemm_sm100.cu
+int kvb_gemm_bf16(const void* A, const void* B, const void* A2, const void* B2, void* C, const void* residual, int M, int N,
+                  int K, int K2, long long lda, long long ldb, long long lda2, long long ldb2, long long ldc, int* status,
+                  int max_ctas, void* stream);
+
+// ---- sdpa_sm100.cu
+// scratch: kvb_sdpa_fwd_scratch_bytes(...) bytes of device memory owned by the caller
+long long kvb_sdpa_fwd_scratch_bytes(int B, int H, int G, int q_len, int kv_len, int want_weights);
+int kvb_sdpa_fwd(const void* q, const void* k, const void* v, const int32_t* token_pos, void* out, float* lse, float* weights,
+                 void* scratch, int B, int H, int G, int q_len, int kv_len, long long k_sb, long long k_sg, long long tp_sb,
+                 long long tp_sg, float scale, int input_pos, int* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

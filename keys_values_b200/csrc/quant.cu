@@ -1,0 +1,186 @@
+// KV-cache storage kernels: asymmetric affine int8/int4 row quantization,
+// de-quantization of (strided) slot ranges, and the fused cache write
+// (scatter new K/V rows into their slots + token_pos update + quantize-on-write).
+//
+// Quantization math per row of D values (keys_values/kvcache/quantize/pytorch.py:100-154):
+//   scale = max((max - min) / (2^bits - 1), eps);  zp = -round(min / scale)  (int32)
+//   q = clamp(round(x / scale) + zp, 0, 2^bits - 1);  x^ = (q - zp) * scale
+//   4 bit: byte j = (q[j] << 4) | q[j + D/2].
+// Replaces buffers.py:498-523 (scatter), attn_weights.py:214-317 (token_pos update)
+// and the ATen chains of quantize/pytorch.py:312-455.
+#include <float.h>
+
+#include "common.cuh"
+#include "kvb200.h"
+
+namespace kvb {
+
+constexpr int Q_WARPS = 8;
+constexpr float QUANT_EPS = 1.1920928955078125e-07f;  // float32 machine epsilon
+
+// Quantizes one row held in shared memory (fp32) by one warp.
+__device__ __forceinline__ void quantize_row_warp(const float* xs, int D, int bits, uint8_t* qdst, float* sdst, int32_t* zdst,
+                                                  int lane) {
+  float mn = FLT_MAX, mx = -FLT_MAX;
+  for (int i = lane; i < D; i += 32) {
+    mn = fminf(mn, xs[i]);
+    mx = fmaxf(mx, xs[i]);
+  }
+  mn = warp_min(mn);
+  mx = warp_max(mx);
+  const float qmax = (float)((1 << bits) - 1);
+  const float scale = fmaxf(__fdiv_rn(mx - mn, qmax), QUANT_EPS);
+  const float zpf = 0.f - rintf(__fdiv_rn(mn, scale));
+  if (lane == 0) {
+    *sdst = scale;
+    *zdst = (int32_t)zpf;
+  }
+  if (bits == 8) {
+    for (int i = lane; i < D; i += 32) {
+      float qv = fminf(fmaxf(rintf(__fdiv_rn(xs[i], scale)) + zpf, 0.f), qmax);
+      qdst[i] = (uint8_t)qv;
+    }
+  } else {
+    const int half = D >> 1;
+    for (int i = lane; i < half; i += 32) {
+      float hi = fminf(fmaxf(rintf(__fdiv_rn(xs[i], scale)) + zpf, 0.f), qmax);
+      float lo = fminf(fmaxf(rintf(__fdiv_rn(xs[i + half], scale)) + zpf, 0.f), qmax);
+      qdst[i] = (uint8_t)(((uint32_t)hi << 4) | (uint32_t)lo);
+    }
+  }
+}
+
+template <typename T>
+__global__ void quantize_rows_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scale,
+                                     int32_t* __restrict__ zp, long long rows, int D, int bits) {
+  extern __shared__ float sm[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float* xs = sm + warp * D;
+  const long long row = (long long)blockIdx.x * Q_WARPS + warp;
+  if (row >= rows) return;
+  const T* xr = x + row * D;
+  for (int i = lane; i < D; i += 32) xs[i] = to_f32(xr[i]);
+  __syncwarp();
+  const int Dq = bits == 8 ? D : D / 2;
+  quantize_row_warp(xs, D, bits, q + row * Dq, scale + row, zp + row, lane);
+}
+
+template <typename T>
+__global__ void dequantize_rows_kernel(const uint8_t* __restrict__ q, const float* __restrict__ scale,
+                                       const int32_t* __restrict__ zp, T* __restrict__ out, int B, int G, int n, int D,
+                                       long long q_sb, long long q_sg, long long q_sn, long long m_sb, long long m_sg,
+                                       long long o_sb, long long o_sg, long long o_sn, int bits) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * Q_WARPS + (threadIdx.x >> 5);
+  if (row >= (long long)B * G * n) return;
+  const int i = (int)(row % n);
+  const int g = (int)((row / n) % G);
+  const int b = (int)(row / ((long long)n * G));
+  const uint8_t* qr = q + b * q_sb + g * q_sg + i * q_sn;
+  const float s = scale[b * m_sb + g * m_sg + i];
+  const float z = (float)zp[b * m_sb + g * m_sg + i];
+  T* o = out + b * o_sb + g * o_sg + i * o_sn;
+  if (bits == 8) {
+    for (int j = lane; j < D; j += 32) o[j] = from_f32<T>(((float)qr[j] - z) * s);
+  } else {
+    const int half = D >> 1;
+    for (int j = lane; j < half; j += 32) {
+      const uint32_t byte = qr[j];
+      o[j] = from_f32<T>(((float)(byte >> 4) - z) * s);
+      o[j + half] = from_f32<T>(((float)(byte & 0xF) - z) * s);
+    }
+  }
+}
+
+// One warp per new row (b, g, i).
+template <typename T>
+__global__ void cache_write_kernel(T* __restrict__ k_buf, T* __restrict__ v_buf, int32_t* __restrict__ token_pos,
+                                   const int32_t* __restrict__ slots, const T* __restrict__ key, const T* __restrict__ value,
+                                   uint8_t* __restrict__ qk, float* __restrict__ sk, int32_t* __restrict__ zk,
+                                   uint8_t* __restrict__ qv, float* __restrict__ sv, int32_t* __restrict__ zv, int B, int G, int n,
+                                   int D, int C, long long slot_sb, long long slot_sg, int input_pos, int bits, int* status) {
+  extern __shared__ float sm[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float* xs = sm + warp * D;
+  const long long row = (long long)blockIdx.x * Q_WARPS + warp;
+  if (row >= (long long)B * G * n) return;
+  const int i = (int)(row % n);
+  const int g = (int)((row / n) % G);
+  const int b = (int)(row / ((long long)n * G));
+  const int slot = slots[b * slot_sb + g * slot_sg + i];
+  if (slot < 0 || slot >= C) {  // never write out of bounds: record and skip
+    if (lane == 0 && status) atomicCAS(status, 0, STATUS_BAD_INDEX);
+    return;
+  }
+  const long long bg = (long long)b * G + g;
+  const long long dst_row = bg * C + slot;
+  const T* kr = key + row * D;
+  const T* vr = value + row * D;
+  if (lane == 0) token_pos[dst_row] = input_pos + i;
+  const int Dq = bits == 8 ? D : D / 2;
+  // keys
+  for (int j = lane; j < D; j += 32) {
+    T val = kr[j];
+    if (k_buf) k_buf[dst_row * D + j] = val;
+    xs[j] = to_f32(val);
+  }
+  __syncwarp();
+  if (qk) quantize_row_warp(xs, D, bits, qk + dst_row * Dq, sk + dst_row, zk + dst_row, lane);
+  __syncwarp();
+  // values
+  for (int j = lane; j < D; j += 32) {
+    T val = vr[j];
+    if (v_buf) v_buf[dst_row * D + j] = val;
+    xs[j] = to_f32(val);
+  }
+  __syncwarp();
+  if (qv) quantize_row_warp(xs, D, bits, qv + dst_row * Dq, sv + dst_row, zv + dst_row, lane);
+}
+
+}  // namespace kvb
+
+using namespace kvb;
+
+#define KVB_DISPATCH_DTYPE(dtype, ...)                      \
+  switch (dtype) {                                          \
+    case 0: { using T = float; __VA_ARGS__; break; }        \
+    case 1: { using T = __nv_bfloat16; __VA_ARGS__; break; } \
+    case 2: { using T = __half; __VA_ARGS__; break; }       \
+    default: return KVB_ERR_ARG;                            \
+  }
+
+extern "C" int kvb_quantize_rows(const void* x, uint8_t* q, float* scale, int32_t* zp, long long rows, int D, int bits,
+                                 int dtype, void* stream) {
+  if (rows <= 0 || D <= 0 || (bits != 4 && bits != 8) || (bits == 4 && (D & 1))) return KVB_ERR_ARG;
+  if ((size_t)Q_WARPS * D * 4 > 48 * 1024) return KVB_ERR_TOO_LARGE;
+  const unsigned grid = (unsigned)((rows + Q_WARPS - 1) / Q_WARPS);
+  KVB_DISPATCH_DTYPE(dtype, (quantize_rows_kernel<T><<<grid, Q_WARPS * 32, (size_t)Q_WARPS * D * 4, (cudaStream_t)stream>>>(
+                                (const T*)x, q, scale, zp, rows, D, bits)));
+  return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
+}
+
+extern "C" int kvb_dequantize_rows(const uint8_t* q, const float* scale, const int32_t* zp, void* out, int B, int G, int n, int D,
+                                   long long q_sb, long long q_sg, long long q_sn, long long m_sb, long long m_sg,
+                                   long long o_sb, long long o_sg, long long o_sn, int bits, int dtype, void* stream) {
+  if (B <= 0 || G <= 0 || n <= 0 || D <= 0 || (bits != 4 && bits != 8)) return KVB_ERR_ARG;
+  const long long rows = (long long)B * G * n;
+  const unsigned grid = (unsigned)((rows + Q_WARPS - 1) / Q_WARPS);
+  KVB_DISPATCH_DTYPE(dtype, (dequantize_rows_kernel<T><<<grid, Q_WARPS * 32, 0, (cudaStream_t)stream>>>(
+                                q, scale, zp, (T*)out, B, G, n, D, q_sb, q_sg, q_sn, m_sb, m_sg, o_sb, o_sg, o_sn, bits)));
+  return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
+}
+
+extern "C" int kvb_cache_write(void* k_buf, void* v_buf, int32_t* token_pos, const int32_t* slots, const void* key,
+                               const void* value, uint8_t* qk, float* sk, int32_t* zk, uint8_t* qv, float* sv, int32_t* zv, int B,
+                               int G, int n, int D, int C, long long slot_sb, long long slot_sg, int input_pos, int bits,
+                               int dtype, int* status, void* stream) {
+  if (B <= 0 || G <= 0 || n <= 0 || D <= 0 || C <= 0) return KVB_ERR_ARG;
+  if (qk && bits != 4 && bits != 8) return KVB_ERR_ARG;
+  if ((size_t)Q_WARPS * D * 4 > 48 * 1024) return KVB_ERR_TOO_LARGE;
+  const long long rows = (long long)B * G * n;
+  const unsigned grid = (unsigned)((rows + Q_WARPS - 1) / Q_WARPS);
+  KVB_DISPATCH_DTYPE(dtype, (cache_write_kernel<T><<<grid, Q_WARPS * 32, (size_t)Q_WARPS * D * 4, (cudaStream_t)stream>>>(
+                                (T*)k_buf, (T*)v_buf, token_pos, slots, (const T*)key, (const T*)value, qk, sk, zk, qv, sv, zv, B,
+                                G, n, D, C, slot_sb, slot_sg, input_pos, bits ? bits : 8, status)));
+  return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
+}

@@ -1,0 +1,547 @@
+// SDPA forward for sm_100a that also returns the per-KV-slot summed attention
+// weights (the H2O score input), with the causal mask taken from token positions.
+//
+//   out[b, t, h, :]   = softmax_j(scale · q[b,h,t]·k[b,g,j] | token_pos[b,g,j] <= input_pos + t) · v[b,g,:]
+//   lse[b, h, t]      = natural-log normaliser of that softmax
+//   weights[b, g, j]  = (1 / (H/G)) · sum over t and over the H/G heads of group g of the softmax weight of slot j
+//
+// Design (bf16, head size 128):
+//   * CTA tile = 128 query rows = (128 / gs) consecutive positions x gs heads of one KV
+//     group (gs = H/G), so every K/V tile is loaded once per group, not once per head.
+//   * S = Q K^T and O += P V run on tcgen05.mma (M=128, N=128, K=16 steps) with S
+//     (double-buffered) and O in TMEM; K/V tiles of 128 slots arrive by TMA into 2-stage
+//     rings (128B swizzle; no multicast). V is consumed as an MN-major B operand.
+//   * Two sweeps over the KV tiles: sweep 1 computes the exact row log-sum-exp (online
+//     max / sum), sweep 2 recomputes S, forms the already-normalised P = exp2(S·c − lse),
+//     accumulates O without any rescaling and takes the column sums of P. The column
+//     sums of a tile are complete once its P tile is written, so they are stored as
+//     deterministic per-(query tile) partials and reduced by a second small kernel:
+//     no atomics, hence run-to-run identical eviction decisions.
+//   * KV tiles whose smallest token position lies beyond the last query of the CTA are
+//     skipped by every role; tiles that contain no position beyond the first query of
+//     the CTA take the mask-free path.
+//   * warp 0 = TMA producer, warp 1 = MMA issuer / TMEM owner, warps 2..5 = softmax +
+//     epilogue (one query row per thread, its TMEM lane).
+//
+// Replaces FlashInfer prefill + Triton score-sum + K/V reordering + query padding of the
+// reference (keys_values/attention/flashinfer_wrapper.py:51-273, :367-510,
+// csrc/kernels/sdpa_prefill.cu, attention/sdpa_wrapper.py:66-432).
+#include <cuda.h>
+#include <limits.h>
+
+#include "common.cuh"
+#include "kvb200.h"
+
+namespace kvb {
+
+int make_tmap_2d_bf16(CUtensorMap* tm, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                      uint32_t box_cols);
+
+constexpr int ATT_BM = 128;   // query rows per CTA
+constexpr int ATT_BN = 128;   // KV slots per tile
+constexpr int ATT_D = 128;    // head size
+constexpr int ATT_THREADS = 192;
+constexpr int ATT_TILE_BYTES = 128 * 128 * 2;  // one 128x128 bf16 tile = two 64-column chunks of 16 KB
+
+struct AttSmem {
+  static constexpr int Q = 0;
+  static constexpr int K = Q + ATT_TILE_BYTES;
+  static constexpr int V = K + 2 * ATT_TILE_BYTES;
+  static constexpr int P = V + 2 * ATT_TILE_BYTES;
+  static constexpr int TP = P + ATT_TILE_BYTES;   // 128 int32 token positions of the current tile
+  static constexpr int BAR = TP + 512;
+  static constexpr int TOTAL = BAR + 256 + 1024;
+};
+
+struct AttParams {
+  const int32_t* token_pos;  // (B,G,L) with strides tp_sb, tp_sg, or nullptr (slot j holds token j)
+  const int32_t* tile_min;   // (B,G,nT)
+  const int32_t* tile_max;   // (B,G,nT)
+  __nv_bfloat16* out;        // (B,T,H,D)
+  float* lse;                // (B,H,T)
+  float* wpart;              // (B,G,nQT,L) or nullptr
+  int B, H, G, T, L, nT, nQT, gs, npos;
+  long long tp_sb, tp_sg;
+  float scale_log2;          // scale * log2(e)
+  int input_pos;
+  int* status;
+};
+
+__global__ void att_tile_minmax_kernel(const int32_t* __restrict__ tp, int32_t* __restrict__ tmin, int32_t* __restrict__ tmax, int G,
+                                       int L, int nT, long long tp_sb, long long tp_sg) {
+  const int t = blockIdx.x % nT;
+  const int bg = blockIdx.x / nT;
+  const int b = bg / G, g = bg % G;
+  const int j = t * ATT_BN + threadIdx.x;
+  int lo = INT_MAX, hi = INT_MIN;
+  if (j < L) {
+    const int v = tp ? tp[b * tp_sb + g * tp_sg + j] : j;
+    lo = hi = v;
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+    hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+  }
+  __shared__ int slo[4], shi[4];
+  if ((threadIdx.x & 31) == 0) {
+    slo[threadIdx.x >> 5] = lo;
+    shi[threadIdx.x >> 5] = hi;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    lo = min(min(slo[0], slo[1]), min(slo[2], slo[3]));
+    hi = max(max(shi[0], shi[1]), max(shi[2], shi[3]));
+    if ((t + 1) * ATT_BN > L) hi = INT_MAX;  // ragged last tile always takes the masked path
+    tmin[blockIdx.x] = lo;
+    tmax[blockIdx.x] = hi;
+  }
+}
+
+// weights[b,g,j] = inv_gs * sum_qt wpart[b,g,qt,j]
+__global__ void att_reduce_weights_kernel(const float* __restrict__ wpart, float* __restrict__ weights, int nQT, int L, float inv_gs) {
+  const long long bg = blockIdx.y;
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= L) return;
+  const float* p = wpart + bg * nQT * (long long)L + j;
+  float s = 0.f;
+  for (int q = 0; q < nQT; ++q) s += p[(long long)q * L];
+  weights[bg * L + j] = s * inv_gs;
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const AttParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + AttSmem::BAR);
+  uint64_t* q_full = bars + 0;
+  uint64_t* k_full = bars + 1;   // [2]
+  uint64_t* k_empty = bars + 3;  // [2]
+  uint64_t* v_full = bars + 5;   // [2]
+  uint64_t* v_empty = bars + 7;  // [2]
+  uint64_t* s_full = bars + 9;   // [2]
+  uint64_t* s_empty = bars + 11; // [2]
+  uint64_t* p_full = bars + 13;
+  uint64_t* p_empty = bars + 14;
+  uint64_t* o_full = bars + 15;
+  uint64_t* grp_bar = bars + 16;  // barrier among the 128 softmax threads (bounded, unlike bar.sync)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int32_t* tp_s = reinterpret_cast<int32_t*>(smem + AttSmem::TP);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // block -> (query tile, group, batch); query tiles fastest so that co-resident CTAs share K/V in L2
+  const int qt = blockIdx.x % p.nQT;
+  const int g = (blockIdx.x / p.nQT) % p.G;
+  const int b = blockIdx.x / (p.nQT * p.G);
+  const int t0 = qt * p.npos;
+  const int qpos_min = p.input_pos + t0;
+  const int qpos_max = p.input_pos + min(t0 + p.npos, p.T) - 1;
+  const int32_t* tmin = p.tile_min + ((long long)b * p.G + g) * p.nT;
+  const int32_t* tmax = p.tile_max + ((long long)b * p.G + g) * p.nT;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
+      mbar_init(&s_full[s], 1);
+      mbar_init(&s_empty[s], 4);
+    }
+    mbar_init(p_full, 4);
+    mbar_init(p_empty, 1);
+    mbar_init(o_full, 1);
+    mbar_init(grp_bar, 128);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_S0 = tmem_base;          // S buffers: columns [0,128) and [128,256)
+  const uint32_t tmem_O = tmem_base + 256;     // O: columns [256,384)
+
+  int n_active = 0;
+  for (int t = 0; t < p.nT; ++t) n_active += (tmin[t] <= qpos_max);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0 && n_active > 0) {
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      mbar_expect_tx(q_full, ATT_TILE_BYTES);
+      tma_load_4d(smem + AttSmem::Q, &tmQ, q_full, 0, t0, g * p.gs, b);
+      tma_load_4d(smem + AttSmem::Q + ATT_TILE_BYTES / 2, &tmQ, q_full, 64, t0, g * p.gs, b);
+      uint32_t i = 0, j = 0;
+      bool ok = true;
+      for (int sweep = 0; sweep < 2 && ok; ++sweep) {
+        for (int t = 0; t < p.nT && ok; ++t) {
+          if (tmin[t] > qpos_max) continue;
+          const int ks = i & 1;
+          if (!mbar_wait_bounded(&k_empty[ks], ((i >> 1) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) { ok = false; break; }
+          uint8_t* kd = smem + AttSmem::K + ks * ATT_TILE_BYTES;
+          mbar_expect_tx(&k_full[ks], ATT_TILE_BYTES);
+          tma_load_4d(kd, &tmK, &k_full[ks], 0, t * ATT_BN, g, b);
+          tma_load_4d(kd + ATT_TILE_BYTES / 2, &tmK, &k_full[ks], 64, t * ATT_BN, g, b);
+          ++i;
+          if (sweep == 1) {
+            const int vs = j & 1;
+            if (!mbar_wait_bounded(&v_empty[vs], ((j >> 1) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) { ok = false; break; }
+            uint8_t* vd = smem + AttSmem::V + vs * ATT_TILE_BYTES;
+            mbar_expect_tx(&v_full[vs], ATT_TILE_BYTES);
+            tma_load_4d(vd, &tmV, &v_full[vs], 0, t * ATT_BN, g, b);
+            tma_load_4d(vd + ATT_TILE_BYTES / 2, &tmV, &v_full[vs], 64, t * ATT_BN, g, b);
+            ++j;
+          }
+        }
+      }
+      if (!ok) {  // let copies in flight land before the CTA's shared memory is released
+        long long c0 = clock64();
+        while (clock64() - c0 < 2000000LL) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issuer
+    if (lane == 0 && n_active > 0) {
+      constexpr uint32_t idesc_qk = make_idesc_bf16(ATT_BM, ATT_BN, 0, 0);  // Q, K both K-major
+      constexpr uint32_t idesc_pv = make_idesc_bf16(ATT_BM, ATT_D, 0, 1);   // P K-major, V MN-major
+      const uint32_t q_addr = smem_u32(smem + AttSmem::Q);
+      const uint32_t p_addr = smem_u32(smem + AttSmem::P);
+      bool ok = mbar_wait_bounded(q_full, 0, abort_flag, p.status, STATUS_TIMEOUT_FULL);
+      uint32_t i = 0, j = 0;
+      auto issue_qk = [&]() -> bool {
+        const int ks = i & 1;
+        if (!mbar_wait_bounded(&k_full[ks], (i >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL)) return false;
+        if (!mbar_wait_bounded(&s_empty[ks], ((i >> 1) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) return false;
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(smem + AttSmem::K + ks * ATT_TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (uint32_t)((kk >> 2) * (ATT_TILE_BYTES / 2) + (kk & 3) * 32);
+          umma_f16_ss(tmem_S0 + (uint32_t)(ks * ATT_BN), make_smem_desc_sw128(q_addr + off, 16, 1024),
+                      make_smem_desc_sw128(k_addr + off, 16, 1024), idesc_qk, kk != 0);
+        }
+        umma_commit(&k_empty[ks]);
+        umma_commit(&s_full[ks]);
+        ++i;
+        return true;
+      };
+      auto issue_pv = [&]() -> bool {
+        const int vs = j & 1;
+        if (!mbar_wait_bounded(p_full, j & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL)) return false;
+        if (!mbar_wait_bounded(&v_full[vs], (j >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL)) return false;
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(smem + AttSmem::V + vs * ATT_TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          // A = P: K-major, 16 kv columns per step inside a 64-column chunk
+          const uint32_t a_off = (uint32_t)((kk >> 2) * (ATT_TILE_BYTES / 2) + (kk & 3) * 32);
+          // B = V: MN-major; 16 kv rows per step (2048 B); the two 64-wide d chunks are LBO apart
+          const uint32_t b_off = (uint32_t)(kk * 16 * 128);
+          umma_f16_ss(tmem_O, make_smem_desc_sw128(p_addr + a_off, 16, 1024),
+                      make_smem_desc_sw128(v_addr + b_off, ATT_TILE_BYTES / 2, 1024), idesc_pv, (j | kk) != 0);
+        }
+        umma_commit(&v_empty[vs]);
+        umma_commit(p_empty);
+        ++j;
+        return true;
+      };
+      // sweep 1: S only
+      for (int t = 0; t < p.nT && ok; ++t) {
+        if (tmin[t] > qpos_max) continue;
+        ok = issue_qk();
+      }
+      // sweep 2: QK of the next tile is issued before PV of the current one
+      bool pending = false;
+      for (int t = 0; t < p.nT && ok; ++t) {
+        if (tmin[t] > qpos_max) continue;
+        ok = issue_qk();
+        if (ok && pending) ok = issue_pv();
+        pending = true;
+      }
+      if (ok && pending) ok = issue_pv();
+      if (ok) umma_commit(o_full);
+    }
+  } else {
+    // ------------------------------------------------- softmax + epilogue warps
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;          // TMEM lane = query row of the tile
+    const int hq = row / p.npos;                  // head within the group
+    const int pl = row % p.npos;                  // position within the tile
+    const int tq = t0 + pl;
+    const bool row_valid = tq < p.T;
+    const int my_pos = p.input_pos + tq;
+    const int sm_tid = threadIdx.x - 64;          // 0..127
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const float c = p.scale_log2;
+    bool ok = n_active > 0;
+    uint32_t i = 0, j = 0;
+    float m = -1e30f, l = 0.f;
+    uint32_t grp_phase = 0;
+    // barrier among the softmax threads; false if it ran into the wait limit
+    auto group_sync = [&]() -> bool {
+      mbar_arrive(grp_bar);
+      const bool done = mbar_wait_bounded(grp_bar, grp_phase, abort_flag, p.status, STATUS_TIMEOUT_MISC);
+      grp_phase ^= 1;
+      return done;
+    };
+    auto load_tile_tp = [&](int t) -> bool {
+      // token positions of tile t -> smem (INT_MAX beyond the end of the cache)
+      const int jj = t * ATT_BN + sm_tid;
+      int v = INT_MAX;
+      if (jj < p.L) v = p.token_pos ? p.token_pos[b * p.tp_sb + g * p.tp_sg + jj] : jj;
+      if (!group_sync()) return false;  // previous readers of tp_s are done
+      tp_s[sm_tid] = v;
+      return group_sync();
+    };
+    if (n_active == 0 && p.wpart) {
+      for (int t = 0; t < p.nT; ++t)
+        if (t * ATT_BN + sm_tid < p.L)
+          p.wpart[((((long long)b * p.G + g) * p.nQT + qt) * p.L) + (long long)t * ATT_BN + sm_tid] = 0.f;
+    }
+
+    // ---- sweep 1: exact row max and sum
+    for (int t = 0; t < p.nT && ok; ++t) {
+      if (tmin[t] > qpos_max) continue;
+      const int sb = i & 1;
+      const bool masked = tmax[t] > qpos_min;
+      if (masked && !load_tile_tp(t)) { ok = false; break; }
+      if (!mbar_wait_bounded(&s_full[sb], (i >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll 1
+      for (int c0 = 0; c0 < ATT_BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_S0 + lane_base + (uint32_t)(sb * ATT_BN + c0), r);
+        tmem_ld_wait();
+        float x[32];
+        float cmax = -INFINITY;
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          float s = __uint_as_float(r[e]) * c;
+          if (masked && tp_s[c0 + e] > my_pos) s = -INFINITY;
+          x[e] = s;
+          cmax = fmaxf(cmax, s);
+        }
+        const float m_new = fmaxf(m, cmax);
+        float sum = 0.f;
+#pragma unroll
+        for (int e = 0; e < 32; ++e) sum += fast_exp2(x[e] - m_new);
+        l = l * fast_exp2(m - m_new) + sum;
+        m = m_new;
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[sb]);
+      ++i;
+    }
+    const float lse2 = l > 0.f ? m + log2f(l) : INFINITY;
+
+    // ---- sweep 2: P = exp2(S·c − lse), O += P V, column sums of P
+    uint8_t* Ps = smem + AttSmem::P;
+    for (int t = 0; t < p.nT && ok; ++t) {
+      float* wdst = p.wpart ? p.wpart + ((((long long)b * p.G + g) * p.nQT + qt) * p.L) + (long long)t * ATT_BN : nullptr;
+      if (tmin[t] > qpos_max) {
+        if (wdst && t * ATT_BN + sm_tid < p.L) wdst[sm_tid] = 0.f;
+        continue;
+      }
+      const int sb = i & 1;
+      const bool masked = tmax[t] > qpos_min;
+      if (masked && !load_tile_tp(t)) { ok = false; break; }
+      if (!mbar_wait_bounded(&s_full[sb], (i >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      // the PV MMA of the previous tile must have finished reading P
+      if (!mbar_wait_bounded(p_empty, (j & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_MISC)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll 1
+      for (int c0 = 0; c0 < ATT_BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_S0 + lane_base + (uint32_t)(sb * ATT_BN + c0), r);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float s0 = __uint_as_float(r[e]) * c - lse2;
+          float s1 = __uint_as_float(r[e + 1]) * c - lse2;
+          float p0 = fast_exp2(s0), p1 = fast_exp2(s1);
+          if (masked) {
+            if (tp_s[c0 + e] > my_pos) p0 = 0.f;
+            if (tp_s[c0 + e + 1] > my_pos) p1 = 0.f;
+          }
+          if (!row_valid) p0 = p1 = 0.f;
+          pk[e >> 1] = pack_bf16x2(p0, p1);
+        }
+        uint8_t* chunk = Ps + (c0 >> 6) * (ATT_TILE_BYTES / 2);
+        const int u0 = (c0 & 63) >> 3;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          uint4 val = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
+          *reinterpret_cast<uint4*>(chunk + sw128_offset(row, u0 + u)) = val;
+        }
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&s_empty[sb]);
+        mbar_arrive(p_full);
+      }
+      ++i;
+      // column sums over the 128 rows of the P tile (as rounded to bf16)
+      if (wdst) {
+        if (!mbar_wait_bounded(p_full, j & 1, abort_flag, p.status, STATUS_TIMEOUT_MISC)) { ok = false; break; }
+        const uint8_t* chunk = Ps + (sm_tid >> 6) * (ATT_TILE_BYTES / 2);
+        const int cu = (sm_tid & 63) >> 3, ce = (sm_tid & 7) * 2;
+        float cs = 0.f;
+#pragma unroll 8
+        for (int rr = 0; rr < ATT_BM; ++rr) {
+          const __nv_bfloat16 hv = *reinterpret_cast<const __nv_bfloat16*>(chunk + sw128_offset(rr, cu) + ce);
+          cs += __bfloat162float(hv);
+        }
+        if (t * ATT_BN + sm_tid < p.L) wdst[sm_tid] = cs;
+        if (!group_sync()) { ok = false; break; }  // all column reads done before P is overwritten
+      }
+      ++j;
+    }
+
+    // ---- epilogue: O (already normalised) -> bf16 -> out; lse
+    if (ok) ok = mbar_wait_bounded(o_full, 0, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL);
+    if (ok || n_active == 0) {
+      tc_fence_after();
+      __nv_bfloat16* dst = p.out + (((long long)b * p.T + tq) * p.H + (g * p.gs + hq)) * ATT_D;
+#pragma unroll 1
+      for (int c0 = 0; c0 < ATT_D; c0 += 32) {
+        uint32_t r[32];
+        if (n_active > 0) {
+          tmem_ld_32x32b_x32(tmem_O + lane_base + (uint32_t)c0, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) r[e] = 0;
+        }
+        if (row_valid) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(r[8 * u + 0]), __uint_as_float(r[8 * u + 1]));
+            o.y = pack_bf16x2(__uint_as_float(r[8 * u + 2]), __uint_as_float(r[8 * u + 3]));
+            o.z = pack_bf16x2(__uint_as_float(r[8 * u + 4]), __uint_as_float(r[8 * u + 5]));
+            o.w = pack_bf16x2(__uint_as_float(r[8 * u + 6]), __uint_as_float(r[8 * u + 7]));
+            *reinterpret_cast<uint4*>(dst + c0 + 8 * u) = o;
+          }
+        }
+      }
+      if (row_valid && p.lse) p.lse[((long long)b * p.H + (g * p.gs + hq)) * p.T + tq] = lse2 * 0.6931471805599453f;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static int make_tmap_4d_bf16(CUtensorMap* tm, const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t d3, uint64_t s1,
+                             uint64_t s2, uint64_t s3, uint32_t b0, uint32_t b1, uint32_t b2) {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* pp = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &pp, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+      return KVB_ERR_DRIVER;
+    fn = reinterpret_cast<EncodeTiledFn>(pp);
+  }
+  cuuint64_t dims[4] = {d0, d1, d2, d3};
+  cuuint64_t strides[3] = {s1 * 2, s2 * 2, s3 * 2};
+  cuuint32_t box[4] = {b0, b1, b2, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? KVB_OK : KVB_ERR_TMAP;
+}
+
+}  // namespace kvb
+
+// Scratch layout (int32 words), provided by the caller:
+//   tile_min (B*G*nT) | tile_max (B*G*nT) | wpart (B*G*nQT*L floats, only if weights != NULL)
+extern "C" long long kvb_sdpa_fwd_scratch_bytes(int B, int H, int G, int q_len, int kv_len, int want_weights) {
+  if (G <= 0 || H % G) return -1;
+  const int gs = H / G;
+  const long long nT = (kv_len + 127) / 128;
+  const long long npos = 128 / gs;
+  const long long nQT = (q_len + npos - 1) / npos;
+  long long words = 2LL * B * G * nT;
+  if (want_weights) words += (long long)B * G * nQT * kv_len;
+  return words * 4;
+}
+
+extern "C" int kvb_sdpa_fwd(const void* q, const void* k, const void* v, const int32_t* token_pos, void* out, float* lse,
+                            float* weights, void* scratch, int B, int H, int G, int q_len, int kv_len, long long k_sb,
+                            long long k_sg, long long tp_sb, long long tp_sg, float scale, int input_pos, int* status,
+                            void* stream) {
+  using namespace kvb;
+  if (B <= 0 || H <= 0 || G <= 0 || q_len <= 0 || kv_len <= 0 || H % G) return KVB_ERR_ARG;
+  const int gs = H / G;
+  if (gs > 128 || (gs & (gs - 1))) return KVB_ERR_UNSUPPORTED;
+  if ((k_sb % 8) || (k_sg % 8)) return KVB_ERR_ALIGN;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(out)) & 15)
+    return KVB_ERR_ALIGN;
+  cudaStream_t s = (cudaStream_t)stream;
+  AttParams p;
+  p.B = B; p.H = H; p.G = G; p.T = q_len; p.L = kv_len;
+  p.gs = gs; p.npos = 128 / gs;
+  p.nT = (kv_len + ATT_BN - 1) / ATT_BN;
+  p.nQT = (q_len + p.npos - 1) / p.npos;
+  p.token_pos = token_pos; p.tp_sb = tp_sb; p.tp_sg = tp_sg;
+  int32_t* sc = reinterpret_cast<int32_t*>(scratch);
+  int32_t* tmin = sc;
+  int32_t* tmax = sc + (long long)B * G * p.nT;
+  p.tile_min = tmin; p.tile_max = tmax;
+  p.wpart = weights ? reinterpret_cast<float*>(sc + 2LL * B * G * p.nT) : nullptr;
+  p.out = (__nv_bfloat16*)out; p.lse = lse;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.input_pos = input_pos; p.status = status;
+
+  CUtensorMap tmQ, tmK, tmV;
+  int rc;
+  // Q (B,H,T,D): dims (D, T, H, B); box = 64 x npos x gs
+  if ((rc = make_tmap_4d_bf16(&tmQ, q, ATT_D, q_len, H, B, ATT_D, (uint64_t)q_len * ATT_D, (uint64_t)H * q_len * ATT_D, 64,
+                              p.npos, gs)))
+    return rc;
+  // K, V (B,G,L,D) with strides: dims (D, L, G, B); box = 64 x 128 x 1
+  if ((rc = make_tmap_4d_bf16(&tmK, k, ATT_D, kv_len, G, B, ATT_D, k_sg, k_sb, 64, ATT_BN, 1))) return rc;
+  if ((rc = make_tmap_4d_bf16(&tmV, v, ATT_D, kv_len, G, B, ATT_D, k_sg, k_sb, 64, ATT_BN, 1))) return rc;
+
+  att_tile_minmax_kernel<<<B * G * p.nT, 128, 0, s>>>(token_pos, tmin, tmax, G, kv_len, p.nT, tp_sb, tp_sg);
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(sdpa_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AttSmem::TOTAL);
+    attr_set = true;
+  }
+  sdpa_fwd_kernel<<<B * G * p.nQT, ATT_THREADS, AttSmem::TOTAL, s>>>(tmQ, tmK, tmV, p);
+  if (weights) {
+    dim3 grid((kv_len + 255) / 256, B * G);
+    att_reduce_weights_kernel<<<grid, 256, 0, s>>>(p.wpart, weights, p.nQT, kv_len, 1.f / gs);
+  }
+  return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
+}

@@ -1,0 +1,385 @@
+"""ctypes bindings to ``libkvb200.so`` (the sm_100a kernels of ``keys_values_b200/csrc``).
+
+The library is built in-tree by :mod:`keys_values_b200.build_ext` and loaded on
+first use. Every wrapper allocates its outputs with torch, passes raw device
+pointers plus the current CUDA stream, and checks the returned status code, so
+a missing library or a rejected argument raises instead of silently running
+something else. Kernels that contain device-side waits report through a status
+word (see ``csrc/common.cuh``); :func:`check_status` reads it.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+import os
+from pathlib import Path
+from typing import Optional, Tuple
+
+import torch
+
+_LIB = None
+_LAUNCHES = 0
+_STATUS = {}
+_ROOT = Path(__file__).resolve().parent.parent
+LIB_PATH = _ROOT / "libkvb200.so"
+
+_DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+_ERRORS = {
+    -1: "invalid argument", -2: "misaligned pointer or stride", -3: "driver entry point unavailable",
+    -4: "tensor map creation failed", -5: "kernel launch failed", -6: "unsupported configuration",
+    -7: "problem too large for this kernel", -8: "CUDA runtime error",
+}
+_STATUS_TEXT = {
+    1: "timeout waiting for a full (data ready) barrier", 2: "timeout waiting for an empty (slot free) barrier",
+    3: "timeout waiting for an accumulator in tensor memory", 4: "timeout waiting for tensor memory to be released",
+    5: "timeout waiting for a peer flag", 6: "timeout in an intra-CTA wait", 7: "slot index out of range",
+}
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        if not LIB_PATH.exists():
+            raise NativeError(
+                f"{LIB_PATH} is missing: run `python -m keys_values_b200.build_ext` (CUDA tensors have no PyTorch fallback)"
+            )
+        _LIB = ctypes.CDLL(str(LIB_PATH))
+        _LIB.kvb_sdpa_fwd_scratch_bytes.restype = ctypes.c_longlong
+    return _LIB
+
+
+def available() -> bool:
+    return LIB_PATH.exists()
+
+
+def launch_count() -> int:
+    return _LAUNCHES
+
+
+def _check(rc: int, name: str) -> None:
+    if rc != 0:
+        raise NativeError(f"{name}: {_ERRORS.get(rc, rc)}")
+
+
+def _p(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream(t: torch.Tensor):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _ll(x) -> ctypes.c_longlong:
+    return ctypes.c_longlong(int(x))
+
+
+def _code(dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise NativeError(f"dtype {dtype} is not supported by the native kernels")
+
+
+def status_word(device) -> torch.Tensor:
+    """Per-device int32 word that kernels with bounded waits write their error code to."""
+    key = torch.device(device).index or 0
+    if key not in _STATUS:
+        _STATUS[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _STATUS[key]
+
+
+def check_status(device, clear: bool = True) -> None:
+    """Synchronising read of the status word; raises if a kernel reported an error."""
+    w = status_word(device)
+    code = int(w.item())
+    if code != 0:
+        if clear:
+            w.zero_()
+        raise NativeError(f"native kernel reported: {_STATUS_TEXT.get(code, code)}")
+
+
+def _count(n: int = 1) -> None:
+    global _LAUNCHES
+    _LAUNCHES += n
+
+
+# ------------------------------------------------------------------ RMSNorm
+def rmsnorm_fwd(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float, add_unit_offset: bool):
+    dim = x.shape[-1]
+    rows = x.numel() // dim
+    if weight is not None and weight.dtype != x.dtype:
+        weight = weight.to(x.dtype)
+    y = torch.empty_like(x)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    _check(lib().kvb_rmsnorm_fwd(_p(x), _p(weight), _p(y), _p(rstd), _ll(rows), dim, ctypes.c_float(eps),
+                                 int(add_unit_offset), _code(x.dtype), _stream(x)), "rmsnorm_fwd")
+    _count()
+    return y, rstd
+
+
+def rmsnorm_bwd(gy, x, weight, rstd, add_unit_offset: bool, need_w: bool):
+    dim = x.shape[-1]
+    rows = x.numel() // dim
+    wt = None if weight is None else weight.to(x.dtype)
+    dx = torch.empty_like(x)
+    n_partial = min(296, (rows + 7) // 8)
+    dw_partial = torch.empty((n_partial, dim), dtype=torch.float32, device=x.device) if need_w else None
+    _check(lib().kvb_rmsnorm_bwd(_p(gy), _p(x), _p(wt), _p(rstd), _p(dx), _p(dw_partial), _ll(rows), dim,
+                                 int(add_unit_offset), _code(x.dtype), n_partial, _stream(x)), "rmsnorm_bwd")
+    _count()
+    dw = dw_partial.sum(0).to(weight.dtype) if need_w else None
+    return dx, dw
+
+
+# --------------------------------------------------------- QK-norm + RoPE
+def qknorm_rope_supported(qkv: torch.Tensor, head_size: int, rope_n_elem: int) -> bool:
+    return qkv.dtype in _DTYPE_CODE and head_size <= 256 and rope_n_elem % 2 == 0
+
+
+def qknorm_rope_fwd(qkv, cos, sin, q_weight, k_weight, H, G, D, eps, rope_n_elem, add_unit_offset):
+    B, T, _ = qkv.shape
+    dev, dt = qkv.device, qkv.dtype
+    q = torch.empty((B, H, T, D), dtype=dt, device=dev)
+    k = torch.empty((B, G, T, D), dtype=dt, device=dev)
+    v = torch.empty((B, G, T, D), dtype=dt, device=dev)
+    has_norm = q_weight is not None
+    rstd = torch.empty((B, T, H + G), dtype=torch.float32, device=dev) if has_norm else None
+    if rope_n_elem > 0 and cos is not None:
+        cos_c = cos.float().contiguous()
+        sin_c = sin.float().contiguous()
+    else:
+        cos_c = sin_c = None
+        rope_n_elem = 0
+    qw = None if q_weight is None else q_weight.to(dt)
+    kw = None if k_weight is None else k_weight.to(dt)
+    _check(lib().kvb_qknorm_rope_fwd(_p(qkv), _p(cos_c), _p(sin_c), _p(qw), _p(kw), _p(q), _p(k), _p(v), _p(rstd), B, T, H, G, D,
+                                     ctypes.c_float(eps), rope_n_elem, int(add_unit_offset), _code(dt), _stream(qkv)),
+           "qknorm_rope_fwd")
+    _count()
+    return q, k, v, rstd
+
+
+def qknorm_rope_bwd(gq, gk, gv, qkv, cos, sin, q_weight, k_weight, rstd, H, G, D, rope_n_elem, add_unit_offset, need_w):
+    B, T, _ = qkv.shape
+    dt = qkv.dtype
+    dqkv = torch.empty_like(qkv)
+    if rope_n_elem > 0 and cos is not None:
+        cos_c, sin_c = cos.float().contiguous(), sin.float().contiguous()
+    else:
+        cos_c = sin_c = None
+        rope_n_elem = 0
+    rows = B * T * (H + 2 * G)
+    n_partial = min(296, (rows + 7) // 8)
+    dw_partial = torch.empty((n_partial, 2, D), dtype=torch.float32, device=qkv.device) if need_w else None
+    qw = None if q_weight is None else q_weight.to(dt)
+    kw = None if k_weight is None else k_weight.to(dt)
+    _check(lib().kvb_qknorm_rope_bwd(_p(gq), _p(gk), _p(gv), _p(qkv), _p(cos_c), _p(sin_c), _p(qw), _p(kw), _p(rstd), _p(dqkv),
+                                     _p(dw_partial), B, T, H, G, D, rope_n_elem, int(add_unit_offset), _code(dt), n_partial,
+                                     _stream(qkv)), "qknorm_rope_bwd")
+    _count()
+    if need_w:
+        dw = dw_partial.sum(0)
+        return dqkv, dw[0].to(q_weight.dtype), dw[1].to(k_weight.dtype)
+    return dqkv, None, None
+
+
+# ------------------------------------------------------------------ SwiGLU
+def swiglu_fwd(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    y = torch.empty_like(a)
+    _check(lib().kvb_swiglu_fwd(_p(a), _p(b), _p(y), _ll(a.numel()), _code(a.dtype), _stream(a)), "swiglu_fwd")
+    _count()
+    return y
+
+
+def swiglu_bwd(gy, a, b):
+    da, db = torch.empty_like(a), torch.empty_like(b)
+    _check(lib().kvb_swiglu_bwd(_p(gy), _p(a), _p(b), _p(da), _p(db), _ll(a.numel()), _code(a.dtype), _stream(a)), "swiglu_bwd")
+    _count()
+    return da, db
+
+
+# ------------------------------------------------------------ quantization
+def quantize_rows(x: torch.Tensor, bits: int):
+    x = x.contiguous()
+    D = x.shape[-1]
+    rows = x.numel() // D
+    q = torch.empty((*x.shape[:-1], D if bits == 8 else D // 2), dtype=torch.uint8, device=x.device)
+    scale = torch.empty(x.shape[:-1], dtype=torch.float32, device=x.device)
+    zp = torch.empty(x.shape[:-1], dtype=torch.int32, device=x.device)
+    _check(lib().kvb_quantize_rows(_p(x), _p(q), _p(scale), _p(zp), _ll(rows), D, bits, _code(x.dtype), _stream(x)), "quantize_rows")
+    _count()
+    return q, scale, zp
+
+
+def dequantize_rows(q, scale, zp, bits: int, dtype, out: Optional[torch.Tensor] = None):
+    D = q.shape[-1] * (2 if bits == 4 else 1)
+    lead = q.shape[:-1]
+    if q.ndim != 4:
+        q4 = q.reshape(1, 1, -1, q.shape[-1])
+        s4, z4 = scale.reshape(1, 1, -1), zp.reshape(1, 1, -1)
+    else:
+        q4, s4, z4 = q, scale, zp
+    if q4.stride(-1) != 1 or s4.stride(-1) != 1 or z4.stride() != s4.stride():
+        q4, s4, z4 = q4.contiguous(), s4.contiguous(), z4.contiguous()
+    B, G, n, _ = q4.shape
+    if out is None:
+        res = torch.empty((B, G, n, D), dtype=dtype, device=q.device)
+    else:
+        res = out.view(B, G, n, D) if out.ndim != 4 else out
+        if res.stride(-1) != 1 or res.dtype != dtype:
+            raise NativeError("dequantize_rows: out must have a contiguous last dimension and the requested dtype")
+    _check(lib().kvb_dequantize_rows(_p(q4), _p(s4), _p(z4), _p(res), B, G, n, D, _ll(q4.stride(0)), _ll(q4.stride(1)),
+                                     _ll(q4.stride(2)), _ll(s4.stride(0)), _ll(s4.stride(1)), _ll(res.stride(0)),
+                                     _ll(res.stride(1)), _ll(res.stride(2)), bits, _code(dtype), _stream(q)), "dequantize_rows")
+    _count()
+    if out is not None:
+        return out
+    return res.view(*lead, D)
+
+
+def _cache_write(k_buf, v_buf, token_pos, slots, key, value, input_pos, qk, sk, zk, qv, sv, zv, bits):
+    B, G, n, D = key.shape
+    ref_buf = k_buf if k_buf is not None else qk
+    C = ref_buf.shape[2]
+    for t in (k_buf, v_buf, token_pos, qk, sk, zk, qv, sv, zv):
+        if t is not None and not t.is_contiguous():
+            raise NativeError("cache_write: cache buffers must be contiguous")
+    if k_buf is not None and k_buf.dtype != key.dtype:
+        key, value = key.to(k_buf.dtype), value.to(k_buf.dtype)
+    key, value = key.contiguous(), value.contiguous()
+    if slots.dtype != torch.int32:
+        slots = slots.to(torch.int32)
+    if slots.stride(2) != 1:
+        slots = slots.contiguous()
+    st = status_word(key.device)
+    _check(lib().kvb_cache_write(_p(k_buf), _p(v_buf), _p(token_pos), _p(slots), _p(key), _p(value), _p(qk), _p(sk), _p(zk),
+                                 _p(qv), _p(sv), _p(zv), B, G, n, D, C, _ll(slots.stride(0)), _ll(slots.stride(1)),
+                                 int(input_pos), int(bits), _code(key.dtype), _p(st), _stream(key)), "cache_write")
+    _count()
+
+
+def cache_write(k_buf, v_buf, token_pos, slots, key, value, input_pos: int) -> None:
+    _cache_write(k_buf, v_buf, token_pos, slots, key, value, input_pos, None, None, None, None, None, None, 0)
+
+
+def cache_write_quant(k_buf, v_buf, token_pos, slots, key, value, input_pos, qk, sk, zk, qv, sv, zv, bits) -> None:
+    _cache_write(k_buf, v_buf, token_pos, slots, key, value, input_pos, qk, sk, zk, qv, sv, zv, bits)
+
+
+# ---------------------------------------------------------------------- H2O
+def h2o_update(scores, weights, k_select, n_evictable, normalize=False, token_pos=None, input_pos=0, prefill_length=0):
+    B, G, C = scores.shape
+    if k_select > 4096 or (n_evictable * 4 + 8 * 2 ** math.ceil(math.log2(max(k_select, 2)))) > 200 * 1024:
+        # cold path: full sort / very large selections stay with the library routine
+        from keys_values_b200.ops import reference as ref
+
+        return ref.h2o_update(scores, weights, k_select, n_evictable, normalize, token_pos, input_pos, prefill_length)
+    weights = weights.contiguous()
+    if scores.stride(2) != 1:
+        raise NativeError("h2o_update: scores must be contiguous along the slot axis")
+    out = torch.empty((B, G, k_select), dtype=torch.int32, device=scores.device)
+    tp = token_pos if normalize else None
+    _check(lib().kvb_h2o_update(_p(scores), _p(weights), _p(tp), _p(out), B, G, C, n_evictable, k_select, int(normalize),
+                                int(input_pos), int(prefill_length or 0), _ll(scores.stride(0)), _ll(scores.stride(1)),
+                                _ll(tp.stride(0) if tp is not None else 0), _ll(tp.stride(1) if tp is not None else 0),
+                                _stream(scores)), "h2o_update")
+    _count()
+    return out
+
+
+# --------------------------------------------------------------------- GEMM
+def gemm_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and w.shape[0] % 8 == 0
+            and x.stride(-1) == 1 and w.stride(-1) == 1)
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, a2=None, b2=None, residual=None, out=None, max_ctas: int = 0) -> torch.Tensor:
+    """``a (M,K) @ b (N,K)^T [+ a2 (M,K2) @ b2 (N,K2)^T] [+ residual (M,N)]`` in bf16 with fp32 accumulation."""
+    M, K = a.shape
+    N = b.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    K2 = 0 if a2 is None else a2.shape[1]
+    st = status_word(a.device)
+    _check(lib().kvb_gemm_bf16(_p(a), _p(b), _p(a2), _p(b2), _p(out), _p(residual), M, N, K, K2, _ll(a.stride(0)), _ll(b.stride(0)),
+                               _ll(a2.stride(0) if a2 is not None else 0), _ll(b2.stride(0) if b2 is not None else 0),
+                               _ll(out.stride(0)), _p(st), int(max_ctas), _stream(a)), "gemm_bf16")
+    _count()
+    return out
+
+
+# ---------------------------------------------------------------- attention
+def sdpa_supported(query: torch.Tensor, key: torch.Tensor, sliding_window, softcap) -> bool:
+    H, G = query.shape[1], key.shape[1]
+    gs = H // G
+    return (query.dtype == torch.bfloat16 and query.shape[-1] == 128 and sliding_window is None and softcap is None
+            and gs <= 128 and (gs & (gs - 1)) == 0 and query.shape[2] > 0)
+
+
+def sdpa_fwd(query, key, value, scale, input_pos, token_pos=None, return_weights=False):
+    B, H, T, D = query.shape
+    G, L = key.shape[1], key.shape[2]
+    query = query.contiguous()
+    if key.stride(3) != 1 or key.stride(2) != D or key.stride() != value.stride():
+        key, value = key.contiguous(), value.contiguous()
+    if token_pos is not None:
+        if token_pos.ndim == 1:
+            token_pos = token_pos.view(1, 1, L).expand(B, G, L)
+        if token_pos.dtype != torch.int32:
+            token_pos = token_pos.to(torch.int32)
+        if token_pos.stride(2) != 1:
+            token_pos = token_pos.contiguous()
+    dev = query.device
+    out = torch.empty((B, T, H * D), dtype=torch.bfloat16, device=dev)
+    lse = torch.empty((B, H, T), dtype=torch.float32, device=dev)
+    weights = torch.empty((B, G, L), dtype=torch.float32, device=dev) if return_weights else None
+    nbytes = lib().kvb_sdpa_fwd_scratch_bytes(B, H, G, T, L, int(return_weights))
+    scratch = torch.empty(nbytes // 4, dtype=torch.int32, device=dev)
+    st = status_word(dev)
+    _check(lib().kvb_sdpa_fwd(_p(query), _p(key), _p(value), _p(token_pos), _p(out), _p(lse), _p(weights), _p(scratch), B, H, G, T, L,
+                              _ll(key.stride(0)), _ll(key.stride(1)),
+                              _ll(token_pos.stride(0) if token_pos is not None else 0),
+                              _ll(token_pos.stride(1) if token_pos is not None else 0),
+                              ctypes.c_float(scale), int(input_pos), _p(st), _stream(query)), "sdpa_fwd")
+    _count(3 if return_weights else 2)
+    return out, weights, lse
+
+
+def sdpa_bwd(grad_out, query, key, value, out, lse, scale, input_pos, token_pos=None):
+    """Attention backward on the GPU: recomputes P from ``lse`` group by group with bf16
+    tensor-core matmuls and fp32 softmax algebra. Returns fp32 ``dq, dk, dv``."""
+    B, H, T, D = query.shape
+    G, L = key.shape[1], key.shape[2]
+    gs = H // G
+    dev = query.device
+    go = grad_out.view(B, T, G, gs, D).permute(0, 2, 3, 1, 4)  # B,G,gs,T,D
+    o = out.view(B, T, G, gs, D).permute(0, 2, 3, 1, 4)
+    delta = (go.float() * o.float()).sum(-1)  # B,G,gs,T
+    dq = torch.empty((B, G, gs, T, D), dtype=torch.float32, device=dev)
+    dk = torch.empty((B, G, L, D), dtype=torch.float32, device=dev)
+    dv = torch.empty((B, G, L, D), dtype=torch.float32, device=dev)
+    qv = query.view(B, G, gs, T, D)
+    lse_v = lse.view(B, G, gs, T)
+    qpos = (input_pos + torch.arange(T, device=dev, dtype=torch.int32)).view(1, T, 1)
+    for g in range(G):
+        kf, vf = key[:, g], value[:, g]  # B,L,D
+        qg = qv[:, g].reshape(B, gs * T, D)
+        s = torch.bmm(qg, kf.transpose(1, 2)).float().view(B, gs, T, L) * scale
+        p = torch.exp(s - lse_v[:, g].unsqueeze(-1))
+        if token_pos is None:
+            tp = torch.arange(L, device=dev, dtype=torch.int32).view(1, 1, L)
+        else:
+            tp = token_pos[:, g].view(-1, 1, L) if token_pos.ndim == 3 else token_pos.view(1, 1, L)
+        p = p.masked_fill((tp > qpos).unsqueeze(1), 0.0)
+        gog = go[:, g].reshape(B, gs * T, D)
+        pb = p.to(torch.bfloat16).view(B, gs * T, L)
+        dv[:, g] = torch.bmm(pb.transpose(1, 2), gog.to(torch.bfloat16)).float()
+        dp = torch.bmm(gog.to(torch.bfloat16), vf.transpose(1, 2)).float().view(B, gs, T, L)
+        ds = (p * (dp - delta[:, g].unsqueeze(-1)) * scale).to(torch.bfloat16).view(B, gs * T, L)
+        dq[:, g] = torch.bmm(ds, kf).float().view(B, gs, T, D)
+        dk[:, g] = torch.bmm(ds.transpose(1, 2), qg).float()
+    return dq.view(B, H, T, D), dk, dv

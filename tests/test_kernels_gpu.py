@@ -1,0 +1,214 @@
+"""Numerics of every CUDA kernel against the plain PyTorch fp32 restatement of the same op."""
+import math
+
+import pytest
+import torch
+
+from keys_values_b200 import ops
+from keys_values_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _cuda():
+    from keys_values_b200.ops import cuda
+
+    return cuda
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("rows,dim,unit", [(37, 2560, False), (8, 64, True), (300, 1000, False)])
+def test_rmsnorm(dtype, rows, dim, unit):
+    x = torch.randn(rows, dim, device=DEV, dtype=dtype, requires_grad=True)
+    w = (torch.randn(dim, device=DEV, dtype=dtype) * 0.1 + 1.0).requires_grad_(True)
+    y = ops.rmsnorm(x, w, 1e-6, unit)
+    xr = x.detach().float().requires_grad_(True)
+    wr = w.detach().float().requires_grad_(True)
+    yr = ref.rmsnorm(xr, wr, 1e-6, unit)
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+    torch.testing.assert_close(y.float(), yr, atol=tol, rtol=tol)
+    g = torch.randn_like(y)
+    y.backward(g)
+    yr.backward(g.float())
+    torch.testing.assert_close(x.grad.float(), xr.grad, atol=tol * 2, rtol=tol * 2)
+    torch.testing.assert_close(w.grad.float(), wr.grad, atol=tol * 8, rtol=tol * 4)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("B,T,H,G,D,rope,norm", [(2, 33, 8, 2, 128, 128, True), (1, 16, 4, 4, 64, 32, False), (1, 7, 4, 2, 16, 16, True)])
+def test_qknorm_rope(dtype, B, T, H, G, D, rope, norm):
+    qkv = torch.randn(B, T, (H + 2 * G) * D, device=DEV, dtype=dtype, requires_grad=True)
+    pos = torch.arange(T, device=DEV).float()[:, None] * torch.rand(rope // 2, device=DEV)[None]
+    ang = torch.cat((pos, pos), -1)
+    cos, sin = ang.cos(), ang.sin()
+    qw = (torch.rand(D, device=DEV, dtype=dtype) + 0.5).requires_grad_(True) if norm else None
+    kw = (torch.rand(D, device=DEV, dtype=dtype) + 0.5).requires_grad_(True) if norm else None
+    q, k, v = ops.qknorm_rope(qkv, H, G, D, cos, sin, qw, kw, 1e-6, rope)
+    qkv_r = qkv.detach().float().requires_grad_(True)
+    qw_r = qw.detach().float().requires_grad_(True) if norm else None
+    kw_r = kw.detach().float().requires_grad_(True) if norm else None
+    qr, kr, vr = ref.qknorm_rope(qkv_r, H, G, D, cos, sin, qw_r, kw_r, 1e-6, rope)
+    tol = 3e-2 if dtype == torch.bfloat16 else 2e-5
+    for a, b in ((q, qr), (k, kr), (v, vr)):
+        torch.testing.assert_close(a.float(), b, atol=tol, rtol=tol)
+    gq, gk, gv = torch.randn_like(q), torch.randn_like(k), torch.randn_like(v)
+    torch.autograd.backward([q, k, v], [gq, gk, gv])
+    torch.autograd.backward([qr, kr, vr], [gq.float(), gk.float(), gv.float()])
+    torch.testing.assert_close(qkv.grad.float(), qkv_r.grad, atol=tol * 2, rtol=tol * 2)
+    if norm:
+        torch.testing.assert_close(qw.grad.float(), qw_r.grad, atol=tol * 16, rtol=tol * 4)
+        torch.testing.assert_close(kw.grad.float(), kw_r.grad, atol=tol * 16, rtol=tol * 4)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_swiglu(dtype):
+    a = torch.randn(5, 1003, device=DEV, dtype=dtype, requires_grad=True)
+    b = torch.randn(5, 1003, device=DEV, dtype=dtype, requires_grad=True)
+    y = ops.swiglu(a, b)
+    ar, br = a.detach().float().requires_grad_(True), b.detach().float().requires_grad_(True)
+    yr = ref.swiglu(ar, br)
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+    torch.testing.assert_close(y.float(), yr, atol=tol, rtol=tol)
+    g = torch.randn_like(y)
+    y.backward(g)
+    yr.backward(g.float())
+    torch.testing.assert_close(a.grad.float(), ar.grad, atol=tol * 2, rtol=tol * 2)
+    torch.testing.assert_close(b.grad.float(), br.grad, atol=tol * 2, rtol=tol * 2)
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_quantize_roundtrip(bits, dtype):
+    x = torch.randn(2, 3, 50, 128, device=DEV, dtype=dtype)
+    q, s, z = ops.quantize_rows(x, bits)
+    qr, sr, zr = ref.quantize_rows(x, bits)
+    torch.testing.assert_close(s, sr)
+    torch.testing.assert_close(z, zr)
+    assert (q.int() - qr.int()).abs().max().item() <= 0 or bits == 4 and ((q >> 4).int() - (qr >> 4).int()).abs().max() <= 1
+    d = ops.dequantize_rows(q, s, z, bits, dtype)
+    dr = ref.dequantize_rows(q, s, z, bits, dtype)
+    torch.testing.assert_close(d.float(), dr.float(), atol=1e-6, rtol=1e-6)
+    # strided destination (a slot range of a larger buffer)
+    buf = torch.zeros(2, 3, 80, 128, device=DEV, dtype=dtype)
+    ops.dequantize_rows(q, s, z, bits, dtype, out=buf[:, :, :50])
+    torch.testing.assert_close(buf[:, :, :50].float(), dr.float(), atol=1e-6, rtol=1e-6)
+    assert buf[:, :, 50:].abs().max().item() == 0
+
+
+@pytest.mark.parametrize("bits", [0, 8, 4])
+def test_cache_write(bits):
+    B, G, C, D, n = 2, 3, 40, 128, 7
+    dt = torch.bfloat16
+    kb = torch.randn(B, G, C, D, device=DEV, dtype=dt)
+    vb = torch.randn(B, G, C, D, device=DEV, dtype=dt)
+    tp = torch.zeros(B, G, C, device=DEV, dtype=torch.int32)
+    slots = torch.stack([torch.stack([torch.randperm(C, device=DEV)[:n] for _ in range(G)]) for _ in range(B)]).to(torch.int32)
+    key, val = torch.randn(B, G, n, D, device=DEV, dtype=dt), torch.randn(B, G, n, D, device=DEV, dtype=dt)
+    kb_r, vb_r, tp_r = kb.clone(), vb.clone(), tp.clone()
+    ref.cache_write(kb_r, vb_r, tp_r, slots, key, val, 100)
+    if bits == 0:
+        ops.cache_write(kb, vb, tp, slots, key, val, 100)
+    else:
+        Dq = D if bits == 8 else D // 2
+        qk = torch.zeros(B, G, C, Dq, device=DEV, dtype=torch.uint8); qv = torch.zeros_like(qk)
+        sk = torch.ones(B, G, C, device=DEV); sv = torch.ones_like(sk)
+        zk = torch.zeros(B, G, C, device=DEV, dtype=torch.int32); zv = torch.zeros_like(zk)
+        ops.cache_write_quant(kb, vb, tp, slots, key, val, 100, qk, sk, zk, qv, sv, zv, bits)
+        q_r, s_r, z_r = ref.quantize_rows(key, bits)
+        idx = slots.long()
+        torch.testing.assert_close(sk.gather(2, idx), s_r)
+        torch.testing.assert_close(zk.gather(2, idx), z_r)
+        got = qk.gather(2, idx.unsqueeze(-1).expand(-1, -1, -1, Dq))
+        assert (got.int() - q_r.int()).abs().max().item() == 0
+    torch.testing.assert_close(kb, kb_r)
+    torch.testing.assert_close(vb, vb_r)
+    torch.testing.assert_close(tp, tp_r)
+    _cuda().check_status(DEV)
+
+
+@pytest.mark.parametrize("C,k,normalize", [(512, 64, False), (16384, 1024, False), (1000, 100, True)])
+def test_h2o_update(C, k, normalize):
+    B, G = 2, 4
+    scores = torch.rand(B, G, C, device=DEV)
+    w = torch.rand(B, G, C, device=DEV)
+    tp = torch.stack([torch.stack([torch.randperm(C, device=DEV) for _ in range(G)]) for _ in range(B)]).to(torch.int32)
+    n_ev = C - 16
+    s_r = scores.clone()
+    idx_r = ref.h2o_update(s_r, w, k, n_ev, normalize, tp, C + 5, 17)
+    idx = ops.h2o_update(scores, w, k, n_ev, normalize, tp, C + 5, 17)
+    torch.testing.assert_close(scores, s_r)
+    assert torch.equal(idx.sort(-1)[0], idx_r.sort(-1)[0])
+    sel = s_r[:, :, :n_ev]
+    if normalize:
+        sel = sel / (C + 5 - tp[:, :, :n_ev].clamp(min=16)).float()
+    vals = sel.gather(2, idx.long())
+    assert (vals[:, :, 1:] >= vals[:, :, :-1]).all()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (1024, 6144, 2560), (200, 264, 136), (4096, 2560, 9728)])
+def test_gemm(M, N, K):
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.05
+    c = _cuda().gemm(a, b)
+    _cuda().check_status(DEV)
+    cr = a.float() @ b.float().t()
+    torch.testing.assert_close(c.float(), cr, atol=3e-2 * math.sqrt(K / 64), rtol=2e-2)
+
+
+def test_gemm_lora_residual():
+    M, N, K, R = 512, 1024, 512, 64
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.05
+    a2 = torch.randn(M, R, device=DEV, dtype=torch.bfloat16)
+    b2 = torch.randn(N, R, device=DEV, dtype=torch.bfloat16) * 0.05
+    res = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    c = _cuda().gemm(a, b, a2, b2, residual=res)
+    _cuda().check_status(DEV)
+    cr = a.float() @ b.float().t() + a2.float() @ b2.float().t() + res.float()
+    torch.testing.assert_close(c.float(), cr, atol=1e-1, rtol=2e-2)
+
+
+def _sdpa_case(B, H, G, T, L, input_pos, mode, want_w=True):
+    D = 128
+    q = torch.randn(B, H, T, D, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(B, G, L, D, device=DEV, dtype=torch.bfloat16)
+    v = torch.randn(B, G, L, D, device=DEV, dtype=torch.bfloat16)
+    if mode == "arange":
+        tp = None
+    else:
+        # an evicted cache: distinct token positions; the last T tokens of the sequence are present
+        tp = torch.empty(B, G, L, device=DEV, dtype=torch.int32)
+        for b in range(B):
+            for g in range(G):
+                old = torch.randperm(input_pos, device=DEV)[: L - T]
+                new = torch.arange(input_pos, input_pos + T, device=DEV)
+                allp = torch.cat((old, new))
+                tp[b, g] = allp[torch.randperm(L, device=DEV)].to(torch.int32)
+    scale = 1.0 / math.sqrt(D)
+    out, w, lse = _cuda().sdpa_fwd(q, k, v, scale, input_pos, tp, want_w)
+    _cuda().check_status(DEV)
+    out_r, w_r, lse_r = ref.sdpa(q, k, v, scale, input_pos, tp, want_w, return_lse=True)
+    torch.testing.assert_close(lse, lse_r, atol=2e-2, rtol=1e-3)
+    torch.testing.assert_close(out.float(), out_r.float(), atol=2e-2, rtol=2e-2)
+    if want_w:
+        torch.testing.assert_close(w, w_r, atol=2e-2, rtol=2e-2)
+
+
+def test_sdpa_single_tile():
+    _sdpa_case(1, 4, 1, 32, 128, 96, "arange")
+
+
+def test_sdpa_prefill_causal():
+    _sdpa_case(1, 8, 2, 512, 512, 0, "arange", want_w=False)
+
+
+@pytest.mark.parametrize("B,H,G,T,L", [(1, 32, 8, 256, 4096), (2, 8, 2, 100, 1000), (1, 4, 4, 64, 300), (1, 16, 2, 50, 777)])
+def test_sdpa_evicted_cache(B, H, G, T, L):
+    _sdpa_case(B, H, G, T, L, 5 * L, "perm")
+
+
+def test_sdpa_status_reports_timeout_free_run():
+    # a healthy run leaves the status word at zero
+    _sdpa_case(1, 4, 1, 32, 256, 224, "arange")
+    assert int(_cuda().status_word(DEV).item()) == 0
