@@ -1,0 +1,221 @@
+"""Headline benchmark: long-context LoRA fine-tuning throughput (tokens/s per box).
+
+Config (the one named in BASELINE.json, config 3): Qwen3-4B architecture, bf16 random
+init, LoRA r=8 alpha=16 on q/k/v/o, one synthetic sequence of 131072 tokens per GPU
+with the loss on the final 1024 tokens, ``h2o-torch-quantized8`` cache of length 16384,
+chunk size 1024, gradient checkpointing through the cache, AdamW; data parallel
+over N GPUs with the gradient all-reduce.
+
+    python bench.py --gpus N --steps K --warmup W          # this framework
+    python bench.py --impl reference --gpus N ...          # the reference library
+
+One step = forward + backward + gradient all-reduce + optimizer step. ``value`` is timed
+on the device (CUDA events, max over ranks) with inputs resident on the device;
+``e2e`` repeats the measurement through the public API with the per-step host→device
+copy of the token ids/targets from pinned memory and the device→host read of the loss
+inside the timed region.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+PUBLISHED_TOKENS_PER_S = 900.0  # derived from the reference's published ≈140 s per 2×64k-token step on 1×A100-40GB
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", type=str, default="b200", choices=["b200", "reference"])
+    ap.add_argument("--model", type=str, default="Qwen3-4B")
+    ap.add_argument("--seq-len", type=int, default=131072)
+    ap.add_argument("--cache-length", type=int, default=16384)
+    ap.add_argument("--chunk-size", type=int, default=1024)
+    ap.add_argument("--num-targets", type=int, default=1024)
+    ap.add_argument("--n-layer", type=int, default=None, help="debug only: fewer layers (marks the result as reduced)")
+    ap.add_argument("--cache-name", type=str, default="h2o-torch-quantized8")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of this rank's GPU while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(
+                    ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits"],
+                    capture_output=True, text=True, timeout=10,
+                ).stdout.strip()
+                if out:
+                    self.samples.append([x.strip() for x in out.split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.5)
+
+    def start(self):
+        self._thread.start()
+
+    def stop(self) -> dict:
+        self._stop.set()
+        self._thread.join(timeout=15)
+        sm, reasons, sm_max = [], set(), None
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            try:
+                sm.append(float(s[0]))
+                sm_max = float(s[1])
+                for n, v in zip(names, s[2:6]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            except Exception:
+                continue
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": sm_max, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def run_b200(args) -> dict:
+    import torch
+    import torch.distributed as dist
+
+    from keys_values_b200 import ops
+    from keys_values_b200.finetune.engine import build_lora_training_setup, training_step
+
+    rank = int(os.environ.get("RANK", 0))
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    setup = build_lora_training_setup(
+        model_name=args.model, device=dev, dtype=torch.bfloat16, cache_name=args.cache_name,
+        cache_length=args.cache_length, chunk_size=args.chunk_size, lora_r=8, lora_alpha=16,
+        lora_targets=("query", "key", "value", "projection"), micro_batch_size=1, n_layer=args.n_layer,
+        world_size=world, rank=rank, yarn_rope=True, seed=1234 + rank,
+    )
+    vocab = setup.config.vocab_size
+    gen = torch.Generator().manual_seed(99 + rank)
+    total = args.warmup + 2 * args.steps
+    host_ids = [torch.randint(0, vocab, (1, args.seq_len), generator=gen).pin_memory() for _ in range(total)]
+    host_tg = [torch.randint(0, vocab, (1, args.num_targets), generator=gen).pin_memory() for _ in range(total)]
+    h2d_bytes = host_ids[0].numel() * host_ids[0].element_size() + host_tg[0].numel() * host_tg[0].element_size()
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    step_i = 0
+    for _ in range(args.warmup):
+        ids, tg = host_ids[step_i].to(dev, non_blocking=True), host_tg[step_i].to(dev, non_blocking=True)
+        training_step(setup, ids, tg)
+        step_i += 1
+    # ---- device-timed region (inputs resident on the device)
+    dev_inputs = [(host_ids[step_i + k].to(dev), host_tg[step_i + k].to(dev)) for k in range(args.steps)]
+    sync()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches0 = ops.native_launches()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for ids, tg in dev_inputs:
+        training_step(setup, ids, tg)
+    e1.record()
+    sync()
+    ms_dev = e0.elapsed_time(e1)
+    launches = ops.native_launches() - launches0
+    step_i += args.steps
+    # ---- end-to-end region: H2D of inputs from pinned memory and D2H of the loss every step
+    sync()
+    t0 = time.perf_counter()
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2.record()
+    losses = []
+    for k in range(args.steps):
+        ids = host_ids[step_i + k].to(dev, non_blocking=True)
+        tg = host_tg[step_i + k].to(dev, non_blocking=True)
+        loss = training_step(setup, ids, tg)
+        losses.append(float(loss.float().cpu()))  # device→host read of the step's result
+    e3.record()
+    sync()
+    ms_e2e = max(e2.elapsed_time(e3), (time.perf_counter() - t0) * 1e3)
+    clocks = sampler.stop()
+    from keys_values_b200.ops import cuda as _cu
+
+    _cu.check_status(dev)
+    if world > 1:
+        t = torch.tensor([ms_dev, ms_e2e], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_dev, ms_e2e = t.tolist()
+    tokens = args.seq_len * world * args.steps
+    value = tokens / (ms_dev / 1e3)
+    e2e = tokens / (ms_e2e / 1e3)
+    reduced = args.n_layer is not None or args.seq_len != 131072 or args.model != "Qwen3-4B"
+    result = {
+        "metric": "long-ctx LoRA train tokens/s/box",
+        "value": value,
+        "unit": "tokens/s",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": ms_dev / args.steps,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None if reduced else value / PUBLISHED_TOKENS_PER_S,
+        "dtype": "bf16",
+        "data": "synthetic uniform-random token ids, random-init weights",
+        "impl": "b200",
+        "config": {
+            "model": f"{args.model}-architecture" + (f" (REDUCED to {args.n_layer} layers)" if args.n_layer else ""),
+            "global_batch": world, "seq_len": args.seq_len, "parallelism": f"dp{world}",
+            "lora": "r=8 alpha=16 on q,k,v,o", "cache": args.cache_name, "cache_length": args.cache_length,
+            "chunk_size": args.chunk_size, "loss_tokens": args.num_targets, "optimizer": "AdamW",
+            "l2": "per-step working set (>30 GB of checkpoints and weights) exceeds the 126 MB L2",
+        },
+        "clocks": clocks,
+        "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4,
+                "ms_per_step": ms_e2e / args.steps},
+        "gpu_launches": launches,
+        "loss": losses[-1] if losses else None,
+        "peak_mem_gb": torch.cuda.max_memory_allocated(dev) / 2**30,
+    }
+    if world > 1:
+        dist.destroy_process_group()
+    return result if rank == 0 else {}
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        from baseline.reference_arm import run_reference
+
+        out = run_reference(args)
+    else:
+        out = run_b200(args)
+    if out:
+        print(json.dumps(out), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,142 @@
+"""Programmatic training setup: model + caches + gradient model + optimizer.
+
+This is the call a user makes to fine-tune with LoRA on long sequences without
+going through the CLI (the CLI in :mod:`keys_values_b200.finetune.longcontext_lora`
+builds on the same functions). Role of ``wrap_gpt_model`` and the inner part of
+``fit`` in ``keys_values/finetune/longcontext_full.py:1055-1198``, ``:1493-1644``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Sequence
+
+import torch
+
+from keys_values_b200.kvcache.factory import KVCacheFactory, split_name
+from keys_values_b200.kvcache.gradient.main import LongContextGradientModel
+from keys_values_b200.models import lora as lora_mod
+from keys_values_b200.models.head_model import CrossEntropyOnLogits, HeadModel
+from keys_values_b200.models.pos_encoding import position_encoding_factory
+
+
+@dataclass
+class TrainingSetup:
+    config: Any
+    gpt_model: torch.nn.Module
+    head_model: HeadModel
+    model: LongContextGradientModel
+    optimizer: torch.optim.Optimizer
+    scheduler: Any = None
+    grad_reducer: Any = None
+    world_size: int = 1
+    rank: int = 0
+    max_norm: Optional[float] = None
+    step: int = 0
+    extras: Dict[str, Any] = field(default_factory=dict)
+
+
+def create_lora_model(
+    model_name: str,
+    device,
+    dtype,
+    lora_r: int = 8,
+    lora_alpha: int = 16,
+    lora_dropout: float = 0.0,
+    lora_targets: Sequence[str] = ("query", "key", "value", "projection"),
+    lora_kind: str = "default",
+    n_layer: Optional[int] = None,
+    yarn_rope: bool = True,
+    seed: int = 0,
+    config_overrides: Optional[Dict[str, Any]] = None,
+):
+    """Random-init LoRA model on ``device`` (weights are loaded separately from a
+    ``lit_model.pth`` with :func:`keys_values_b200.finetune.utils.load_model_checkpoint`)."""
+    flags = {f"lora_{t}": True for t in lora_targets}
+    over = dict(config_overrides or {})
+    if n_layer is not None:
+        over["n_layer"] = n_layer
+    config = lora_mod.Config.from_name(
+        model_name, lora_r=lora_r, lora_alpha=lora_alpha, lora_dropout=lora_dropout, lora_kind=lora_kind, **flags, **over
+    )
+    torch.manual_seed(seed)
+    pos = position_encoding_factory(config, do_yarn=yarn_rope, device=device)
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(dtype)
+    try:
+        with torch.device(device):
+            model = lora_mod.GPT(config, pos_encoding=pos)
+    finally:
+        torch.set_default_dtype(prev)
+    model.apply(model._init_weights)
+    lora_mod.mark_only_lora_as_trainable(model)
+    return config, model
+
+
+def build_lora_training_setup(
+    model_name: str,
+    device,
+    dtype=torch.bfloat16,
+    cache_name: str = "h2o-torch-quantized8",
+    cache_length: int = 16384,
+    chunk_size: int = 1024,
+    layers_per_cell: int = 1,
+    lora_r: int = 8,
+    lora_alpha: int = 16,
+    lora_targets: Sequence[str] = ("query", "key", "value", "projection"),
+    micro_batch_size: int = 1,
+    n_layer: Optional[int] = None,
+    world_size: int = 1,
+    rank: int = 0,
+    yarn_rope: bool = True,
+    seed: int = 0,
+    learning_rate: float = 2e-4,
+    weight_decay: float = 0.0,
+    max_norm: Optional[float] = 1.0,
+    cache_kwargs: Optional[Dict[str, Any]] = None,
+    grad_kwargs: Optional[Dict[str, Any]] = None,
+    head_model: Optional[HeadModel] = None,
+    overlap_allreduce: bool = True,
+) -> TrainingSetup:
+    config, gpt = create_lora_model(
+        model_name, device, dtype, lora_r=lora_r, lora_alpha=lora_alpha, lora_targets=lora_targets,
+        n_layer=n_layer, yarn_rope=yarn_rope, seed=seed,
+    )
+    ck = dict(cache_kwargs or {})
+    cname, _ = split_name(cache_name)
+    if "h2o" in cname and "max_chunk_size" not in ck:
+        ck["max_chunk_size"] = chunk_size
+    caches = KVCacheFactory.create(gpt, cache_name, micro_batch_size, cache_length, device=device, dtype=dtype, cache_kwargs=ck)
+    gpt.assign_kv_caches(caches)
+    head = head_model if head_model is not None else CrossEntropyOnLogits(config)
+    model = LongContextGradientModel(gpt, head, layers_per_cell=layers_per_cell, chunk_size=chunk_size, **(grad_kwargs or {}))
+    model.train()
+    params = [p for p in gpt.parameters() if p.requires_grad] + [p for p in head.parameters() if p.requires_grad]
+    optimizer = torch.optim.AdamW(params, lr=learning_rate, weight_decay=weight_decay, fused=torch.device(device).type == "cuda")
+    setup = TrainingSetup(config, gpt, head, model, optimizer, world_size=world_size, rank=rank, max_norm=max_norm)
+    if world_size > 1:
+        from keys_values_b200.parallel.dp import GradientReducer
+
+        setup.grad_reducer = GradientReducer(params, world_size=world_size, rank=rank, device=device, overlap=overlap_allreduce)
+        if overlap_allreduce:
+            model.row_done_hook = setup.grad_reducer.row_done_hook(gpt)
+    return setup
+
+
+def training_step(setup: TrainingSetup, input_ids: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+    """Forward, backward, gradient all-reduce (mean over ranks), clipping, optimizer
+    step. Returns the (local) loss as a 0-d device tensor."""
+    setup.optimizer.zero_grad(set_to_none=False if setup.grad_reducer is not None else True)
+    if setup.grad_reducer is not None:
+        setup.grad_reducer.begin_step()
+    loss = setup.model(input_ids, targets)
+    loss.backward()
+    if setup.grad_reducer is not None:
+        setup.grad_reducer.finish_step()
+    if setup.max_norm is not None:
+        params = [p for g in setup.optimizer.param_groups for p in g["params"] if p.grad is not None]
+        torch.nn.utils.clip_grad_norm_(params, setup.max_norm)
+    setup.optimizer.step()
+    if setup.scheduler is not None:
+        setup.scheduler.step()
+    setup.step += 1
+    return loss.detach()

