@@ -101,8 +101,12 @@ class MultiHeadSelfAttention:
         input_pos: Optional[int] = None,
         return_attn_weights: bool = False,
         token_positions: Optional[torch.Tensor] = None,
+        return_lse: bool = False,
         **_kwargs,
-    ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    ):
+        """With ``return_lse`` a third value is returned: the log-sum-exp ``(B, H, q)``
+        fp32 of the attention rows (kept by the training forward pass so that the
+        backward pass does not have to recompute the attention outputs)."""
         keys, values = k_and_v.both()
         q_len, kv_len = query.shape[2], keys.shape[2]
         if input_pos is None:
@@ -110,10 +114,7 @@ class MultiHeadSelfAttention:
         if token_positions is None and input_pos != kv_len - q_len:
             # Without token positions the keys are taken to be tokens 0 … kv_len-1
             input_pos = kv_len - q_len
-        out, weights = ops.sdpa(
-            query,
-            keys,
-            values,
+        kwargs = dict(
             scale=self.pos_encoding.sdpa_scale_factor(),
             input_pos=input_pos,
             token_pos=token_positions,
@@ -121,4 +122,6 @@ class MultiHeadSelfAttention:
             sliding_window=self.sliding_window(block_idx),
             softcap=self.config.attention_logit_softcapping,
         )
-        return out, weights
+        if return_lse:
+            return ops.sdpa_fwd(query, keys, values, **kwargs)
+        return ops.sdpa(query, keys, values, **kwargs)

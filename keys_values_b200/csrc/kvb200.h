@@ -62,6 +62,21 @@ int kvb_sdpa_fwd(const void* q, const void* k, const void* v, const int32_t* tok
                  void* scratch, int B, int H, int G, int q_len, int kv_len, long long k_sb, long long k_sg, long long tp_sb,
                  long long tp_sg, float scale, int input_pos, int* status, void* stream);
 
+
+// ---- sdpa_bwd_sm100.cu: dq (B,H,T,D) bf16 is written, dk/dv (B,G,C,D) fp32 are accumulated into
+long long kvb_sdpa_bwd_scratch_bytes(int B, int H, int G, int q_len, int kv_len);
+int kvb_sdpa_bwd(const void* q, const void* k, const void* v, const int32_t* token_pos, const void* out, const void* dout,
+                 const float* lse, void* dq, float* dk, float* dv, void* scratch, int B, int H, int G, int q_len, int kv_len,
+                 long long k_sb, long long k_sg, long long tp_sb, long long tp_sg, long long dk_sb, long long dk_sg, float scale,
+                 int input_pos, int* status, void* stream);
+
+
+// ---- decode.cu: q (B,H,D) bf16; K/V either bf16 (bits = 16) or int8/int4 codes with scale / zero point
+long long kvb_decode_scratch_bytes(int B, int H, int L);
+int kvb_decode_attn(const void* q, const void* kq, const void* vq, const float* ks, const int32_t* kz, const float* vs,
+                    const int32_t* vz, const void* k_new, const void* v_new, const int32_t* new_slot, void* out, float* weights,
+                    void* scratch, int B, int H, int G, int L, int C, int bits, float scale, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

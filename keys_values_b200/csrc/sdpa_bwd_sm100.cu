@@ -1,0 +1,503 @@
+// SDPA backward for sm_100a (bf16, head size 128), mask from token positions.
+//
+// Given dO, the forward's O and log-sum-exp, computes
+//   dQ (B,H,T,D) bf16, and accumulates dK, dV into fp32 cache-shaped buffers (B,G,C,D).
+// Two launches of one kernel template, so that every output tile has exactly one
+// owner CTA (no atomics, deterministic):
+//   MODE_DQ : CTA = 128 query rows (positions x heads of a KV group), streams KV tiles
+//             S = Q K^T, dP = dO V^T  ->  dS = P (dP − δ) scale  ->  dQ += dS K
+//   MODE_DKV: CTA = 128 KV slots, streams query tiles
+//             S^T = K Q^T, dP^T = V dO^T -> P^T, dS^T -> dV += P^T dO, dK += dS^T Q
+// Both are the same pipeline: a fixed "row" tile with two K-major operands (R1, R2),
+// streamed "column" tiles with two operands (C1, C2) that are consumed first as K-major
+// B operands (X = R1 C1^T, Y = R2 C2^T, fp32 in TMEM) and then, from the same shared
+// memory, as MN-major B operands of the accumulating MMAs (acc1 += P C2, acc2 += dS C1).
+// P and dS are produced by the 128 compute threads (one TMEM lane = one row each) and
+// staged in 128B-swizzled shared memory. δ = rowsum(dO ⊙ O) comes from a small kernel.
+//
+// Replaces the blocked fp32 PyTorch backward of the reference
+// (keys_values/attention/sdpa_op.py:31-251) and the library SDPA backward it otherwise uses.
+#include <cuda.h>
+#include <limits.h>
+
+#include "common.cuh"
+#include "kvb200.h"
+
+namespace kvb {
+
+constexpr int BW_TILE_BYTES = 128 * 128 * 2;
+constexpr int BW_THREADS = 192;
+enum { MODE_DQ = 0, MODE_DKV = 1 };
+
+template <int MODE>
+struct BwSmem {
+  static constexpr int STAGES = MODE == MODE_DQ ? 2 : 1;
+  static constexpr int R1 = 0;
+  static constexpr int R2 = R1 + BW_TILE_BYTES;
+  static constexpr int C = R2 + BW_TILE_BYTES;                 // per stage: C1 | C2
+  static constexpr int DS = C + STAGES * 2 * BW_TILE_BYTES;
+  static constexpr int P = DS + BW_TILE_BYTES;                 // only MODE_DKV
+  static constexpr int STATS = P + (MODE == MODE_DKV ? BW_TILE_BYTES : 0);  // 3 x 128 words
+  static constexpr int BAR = STATS + 3 * 512;
+  static constexpr int TOTAL = BAR + 256 + 1024;
+};
+
+struct BwParams {
+  const int32_t* token_pos;
+  const int32_t* tile_min;
+  const int32_t* tile_max;
+  const float* lse;     // (B,H,T) natural log
+  const float* delta;   // (B,H,T)
+  __nv_bfloat16* dq;    // (B,H,T,D)
+  float* dk;            // (B,G,C,D) accumulated
+  float* dv;
+  int B, H, G, T, L, nT, nQT, gs, npos;
+  long long tp_sb, tp_sg, dk_sb, dk_sg;
+  float scale, scale_log2;
+  int input_pos;
+  int* status;
+};
+
+__device__ __forceinline__ float bw_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// delta[b,h,t] = sum_d dO[b,t,h,d] * O[b,t,h,d]
+__global__ void att_delta_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O,
+                                 float* __restrict__ delta, int B, int T, int H) {
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= (long long)B * T * H) return;
+  const int lane = threadIdx.x & 31;
+  const uint2 a = *reinterpret_cast<const uint2*>(dO + row * 128 + lane * 4);
+  const uint2 o = *reinterpret_cast<const uint2*>(O + row * 128 + lane * 4);
+  const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&a);
+  const __nv_bfloat162* op = reinterpret_cast<const __nv_bfloat162*>(&o);
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const float2 x = __bfloat1622float2(ap[i]), y = __bfloat1622float2(op[i]);
+    s += x.x * y.x + x.y * y.y;
+  }
+  s = warp_sum(s);
+  if (lane == 0) {
+    const int h = (int)(row % H);
+    const long long bt = row / H;
+    const int t = (int)(bt % T);
+    const int b = (int)(bt / T);
+    delta[((long long)b * H + h) * T + t] = s;
+  }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(BW_THREADS, 1)
+sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
+                const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const BwParams p) {
+  using S = BwSmem<MODE>;
+  constexpr int ST = S::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::BAR);
+  uint64_t* r_full = bars + 0;
+  uint64_t* c_full = bars + 1;    // [2]
+  uint64_t* c_empty = bars + 3;   // [2]
+  uint64_t* xy_full = bars + 5;
+  uint64_t* pds_full = bars + 6;
+  uint64_t* pds_empty = bars + 7;
+  uint64_t* acc_full = bars + 8;
+  uint64_t* grp_bar = bars + 9;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int32_t* stat_i = reinterpret_cast<int32_t*>(smem + S::STATS);         // MODE_DQ: token_pos of the KV tile
+  float* stat_lse = reinterpret_cast<float*>(smem + S::STATS + 512);     // MODE_DKV: lse2 of the query tile
+  float* stat_dl = reinterpret_cast<float*>(smem + S::STATS + 1024);     // MODE_DKV: delta of the query tile
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_row_tiles = MODE == MODE_DQ ? p.nQT : p.nT;
+  const int rt = blockIdx.x % n_row_tiles;                 // row tile: query tile (DQ) or KV tile (DKV)
+  const int g = (blockIdx.x / n_row_tiles) % p.G;
+  const int b = blockIdx.x / (n_row_tiles * p.G);
+  const int32_t* tmin = p.tile_min + ((long long)b * p.G + g) * p.nT;
+  const int32_t* tmax = p.tile_max + ((long long)b * p.G + g) * p.nT;
+  const int n_col_tiles = MODE == MODE_DQ ? p.nT : p.nQT;
+
+  // (kv tile t, query tile qt) is active iff some slot of t is visible to some query of qt
+  auto qpos_min_of = [&](int qt) { return p.input_pos + qt * p.npos; };
+  auto qpos_max_of = [&](int qt) { return p.input_pos + min((qt + 1) * p.npos, p.T) - 1; };
+  auto active = [&](int ct) -> bool {
+    return MODE == MODE_DQ ? (tmin[ct] <= qpos_max_of(rt)) : (tmin[rt] <= qpos_max_of(ct));
+  };
+  auto masked = [&](int ct) -> bool {
+    return MODE == MODE_DQ ? (tmax[ct] > qpos_min_of(rt)) : (tmax[rt] > qpos_min_of(ct));
+  };
+
+  if (threadIdx.x == 0) {
+    mbar_init(r_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&c_full[s], 1);
+      mbar_init(&c_empty[s], 1);
+    }
+    mbar_init(xy_full, 1);
+    mbar_init(pds_full, 4);
+    mbar_init(pds_empty, 1);
+    mbar_init(acc_full, 1);
+    mbar_init(grp_bar, 128);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_X = tmem_base, tmem_Y = tmem_base + 128, tmem_A1 = tmem_base + 256, tmem_A2 = tmem_base + 384;
+
+  int n_active = 0;
+  for (int ct = 0; ct < n_col_tiles; ++ct) n_active += active(ct) ? 1 : 0;
+
+  auto load_tile = [&](uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int c1, int c2, int c3) {
+    tma_load_4d(dst, tm, bar, 0, c1, c2, c3);
+    tma_load_4d(dst + BW_TILE_BYTES / 2, tm, bar, 64, c1, c2, c3);
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0 && n_active > 0) {
+      mbar_expect_tx(r_full, 2 * BW_TILE_BYTES);
+      if (MODE == MODE_DQ) {
+        load_tile(smem + S::R1, &tmQ, r_full, rt * p.npos, g * p.gs, b);
+        load_tile(smem + S::R2, &tmdO, r_full, rt * p.npos, g * p.gs, b);
+      } else {
+        load_tile(smem + S::R1, &tmK, r_full, rt * 128, g, b);
+        load_tile(smem + S::R2, &tmV, r_full, rt * 128, g, b);
+      }
+      uint32_t s = 0;
+      bool ok = true;
+      for (int ct = 0; ct < n_col_tiles && ok; ++ct) {
+        if (!active(ct)) continue;
+        const int st = s % ST;
+        if (!mbar_wait_bounded(&c_empty[st], ((s / ST) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) { ok = false; break; }
+        uint8_t* c1 = smem + S::C + st * 2 * BW_TILE_BYTES;
+        uint8_t* c2 = c1 + BW_TILE_BYTES;
+        mbar_expect_tx(&c_full[st], 2 * BW_TILE_BYTES);
+        if (MODE == MODE_DQ) {
+          load_tile(c1, &tmK, &c_full[st], ct * 128, g, b);
+          load_tile(c2, &tmV, &c_full[st], ct * 128, g, b);
+        } else {
+          load_tile(c1, &tmQ, &c_full[st], ct * p.npos, g * p.gs, b);
+          load_tile(c2, &tmdO, &c_full[st], ct * p.npos, g * p.gs, b);
+        }
+        ++s;
+      }
+      if (!ok) {
+        long long c0 = clock64();
+        while (clock64() - c0 < 2000000LL) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issuer
+    if (lane == 0 && n_active > 0) {
+      constexpr uint32_t idesc_kk = make_idesc_bf16(128, 128, 0, 0);   // both operands K-major
+      constexpr uint32_t idesc_kmn = make_idesc_bf16(128, 128, 0, 1);  // A K-major, B MN-major
+      const uint32_t r1 = smem_u32(smem + S::R1), r2 = smem_u32(smem + S::R2);
+      const uint32_t ds_addr = smem_u32(smem + S::DS), p_addr = smem_u32(smem + S::P);
+      bool ok = mbar_wait_bounded(r_full, 0, abort_flag, p.status, STATUS_TIMEOUT_FULL);
+      uint32_t s = 0;
+      for (int ct = 0; ct < n_col_tiles && ok; ++ct) {
+        if (!active(ct)) continue;
+        const int st = s % ST;
+        if (!mbar_wait_bounded(&c_full[st], (s / ST) & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t c1 = smem_u32(smem + S::C + st * 2 * BW_TILE_BYTES);
+        const uint32_t c2 = c1 + BW_TILE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (uint32_t)((kk >> 2) * (BW_TILE_BYTES / 2) + (kk & 3) * 32);
+          umma_f16_ss(tmem_X, make_smem_desc_sw128(r1 + off, 16, 1024), make_smem_desc_sw128(c1 + off, 16, 1024), idesc_kk, kk != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (uint32_t)((kk >> 2) * (BW_TILE_BYTES / 2) + (kk & 3) * 32);
+          umma_f16_ss(tmem_Y, make_smem_desc_sw128(r2 + off, 16, 1024), make_smem_desc_sw128(c2 + off, 16, 1024), idesc_kk, kk != 0);
+        }
+        umma_commit(xy_full);
+        if (!mbar_wait_bounded(pds_full, s & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t a_off = (uint32_t)((kk >> 2) * (BW_TILE_BYTES / 2) + (kk & 3) * 32);
+          const uint32_t b_off = (uint32_t)(kk * 16 * 128);
+          if (MODE == MODE_DKV)
+            umma_f16_ss(tmem_A1, make_smem_desc_sw128(p_addr + a_off, 16, 1024),
+                        make_smem_desc_sw128(c2 + b_off, BW_TILE_BYTES / 2, 1024), idesc_kmn, (s | kk) != 0);
+          umma_f16_ss(tmem_A2, make_smem_desc_sw128(ds_addr + a_off, 16, 1024),
+                      make_smem_desc_sw128(c1 + b_off, BW_TILE_BYTES / 2, 1024), idesc_kmn, (s | kk) != 0);
+        }
+        umma_commit(&c_empty[st]);
+        umma_commit(pds_empty);
+        ++s;
+      }
+      if (ok) umma_commit(acc_full);
+    }
+  } else {
+    // ----------------------------------------------- compute + epilogue warps
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const int tid = threadIdx.x - 64;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    bool ok = n_active > 0;
+    uint32_t s = 0, grp_phase = 0;
+    auto group_sync = [&]() -> bool {
+      mbar_arrive(grp_bar);
+      const bool done = mbar_wait_bounded(grp_bar, grp_phase, abort_flag, p.status, STATUS_TIMEOUT_MISC);
+      grp_phase ^= 1;
+      return done;
+    };
+    // per-row constants
+    float row_lse2 = INFINITY, row_delta = 0.f;
+    int row_pos = 0, row_tp = INT_MAX;
+    bool row_valid;
+    int hq = 0, tq = 0;
+    if (MODE == MODE_DQ) {
+      hq = row / p.npos;
+      tq = rt * p.npos + row % p.npos;
+      row_valid = tq < p.T;
+      row_pos = p.input_pos + tq;
+      if (row_valid) {
+        const long long idx = ((long long)b * p.H + g * p.gs + hq) * p.T + tq;
+        row_lse2 = p.lse[idx] * 1.4426950408889634f;
+        row_delta = p.delta[idx];
+      }
+    } else {
+      const int j = rt * 128 + row;
+      row_valid = j < p.L;
+      if (row_valid) row_tp = p.token_pos ? p.token_pos[b * p.tp_sb + g * p.tp_sg + j] : j;
+    }
+    uint8_t* DSs = smem + S::DS;
+    uint8_t* Ps = smem + S::P;
+    for (int ct = 0; ct < n_col_tiles && ok; ++ct) {
+      if (!active(ct)) continue;
+      const bool msk = masked(ct);
+      if (MODE == MODE_DQ) {
+        if (msk) {
+          const int jj = ct * 128 + tid;
+          int v = INT_MAX;
+          if (jj < p.L) v = p.token_pos ? p.token_pos[b * p.tp_sb + g * p.tp_sg + jj] : jj;
+          if (!group_sync()) { ok = false; break; }
+          stat_i[tid] = v;
+          if (!group_sync()) { ok = false; break; }
+        }
+      } else {
+        // statistics of the query tile: column c <-> (head c / npos, position c % npos)
+        const int c_hq = tid / p.npos, c_tq = ct * p.npos + tid % p.npos;
+        float l2 = INFINITY, dl = 0.f;
+        if (c_tq < p.T) {
+          const long long idx = ((long long)b * p.H + g * p.gs + c_hq) * p.T + c_tq;
+          l2 = p.lse[idx] * 1.4426950408889634f;
+          dl = p.delta[idx];
+        }
+        if (!group_sync()) { ok = false; break; }
+        stat_lse[tid] = l2;
+        stat_dl[tid] = dl;
+        if (!group_sync()) { ok = false; break; }
+      }
+      if (!mbar_wait_bounded(xy_full, s & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      if (!mbar_wait_bounded(pds_empty, (s & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_MISC)) { ok = false; break; }
+      tc_fence_after();
+      const int cpos0 = p.input_pos + ct * p.npos;  // MODE_DKV: position of column c is cpos0 + c % npos
+#pragma unroll 1
+      for (int c0 = 0; c0 < 128; c0 += 32) {
+        uint32_t xr[32], yr[32];
+        tmem_ld_32x32b_x32(tmem_X + lane_base + (uint32_t)c0, xr);
+        tmem_ld_32x32b_x32(tmem_Y + lane_base + (uint32_t)c0, yr);
+        tmem_ld_wait();
+        uint32_t pk[16], dk_[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float pv[2], dsv[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int c = c0 + e + u;
+            float l2, dl;
+            bool vis;
+            if (MODE == MODE_DQ) {
+              l2 = row_lse2;
+              dl = row_delta;
+              vis = !msk || stat_i[c] <= row_pos;
+            } else {
+              l2 = stat_lse[c];
+              dl = stat_dl[c];
+              vis = !msk || row_tp <= cpos0 + (c % p.npos);
+            }
+            float pp = bw_exp2(__uint_as_float(xr[e + u]) * p.scale_log2 - l2);
+            if (!vis) pp = 0.f;
+            pv[u] = pp;
+            dsv[u] = pp * (__uint_as_float(yr[e + u]) - dl) * p.scale;
+          }
+          pk[e >> 1] = pack_bf16x2(pv[0], pv[1]);
+          dk_[e >> 1] = pack_bf16x2(dsv[0], dsv[1]);
+        }
+        const int chunk_off = (c0 >> 6) * (BW_TILE_BYTES / 2);
+        const int u0 = (c0 & 63) >> 3;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const uint32_t off = chunk_off + sw128_offset(row, u0 + u);
+          *reinterpret_cast<uint4*>(DSs + off) = make_uint4(dk_[4 * u], dk_[4 * u + 1], dk_[4 * u + 2], dk_[4 * u + 3]);
+          if (MODE == MODE_DKV)
+            *reinterpret_cast<uint4*>(Ps + off) = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
+        }
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pds_full);
+      ++s;
+    }
+    // ---- epilogue
+    if (ok) ok = mbar_wait_bounded(acc_full, 0, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL);
+    if (ok) {
+      tc_fence_after();
+      if (MODE == MODE_DQ) {
+        __nv_bfloat16* dst = p.dq + (((long long)b * p.H + g * p.gs + hq) * p.T + tq) * 128;
+#pragma unroll 1
+        for (int c0 = 0; c0 < 128; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(tmem_A2 + lane_base + (uint32_t)c0, r);
+          tmem_ld_wait();
+          if (row_valid) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(r[8 * u + 0]), __uint_as_float(r[8 * u + 1]));
+              o.y = pack_bf16x2(__uint_as_float(r[8 * u + 2]), __uint_as_float(r[8 * u + 3]));
+              o.z = pack_bf16x2(__uint_as_float(r[8 * u + 4]), __uint_as_float(r[8 * u + 5]));
+              o.w = pack_bf16x2(__uint_as_float(r[8 * u + 6]), __uint_as_float(r[8 * u + 7]));
+              *reinterpret_cast<uint4*>(dst + c0 + 8 * u) = o;
+            }
+          }
+        }
+      } else {
+        const long long off = b * p.dk_sb + g * p.dk_sg + (long long)(rt * 128 + row) * 128;
+#pragma unroll 1
+        for (int c0 = 0; c0 < 128; c0 += 32) {
+          uint32_t r1v[32], r2v[32];
+          tmem_ld_32x32b_x32(tmem_A1 + lane_base + (uint32_t)c0, r1v);
+          tmem_ld_32x32b_x32(tmem_A2 + lane_base + (uint32_t)c0, r2v);
+          tmem_ld_wait();
+          if (row_valid) {
+            float4* dvp = reinterpret_cast<float4*>(p.dv + off + c0);
+            float4* dkp = reinterpret_cast<float4*>(p.dk + off + c0);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              float4 a = dvp[u], c = dkp[u];
+              a.x += __uint_as_float(r1v[4 * u]); a.y += __uint_as_float(r1v[4 * u + 1]);
+              a.z += __uint_as_float(r1v[4 * u + 2]); a.w += __uint_as_float(r1v[4 * u + 3]);
+              c.x += __uint_as_float(r2v[4 * u]); c.y += __uint_as_float(r2v[4 * u + 1]);
+              c.z += __uint_as_float(r2v[4 * u + 2]); c.w += __uint_as_float(r2v[4 * u + 3]);
+              dvp[u] = a;
+              dkp[u] = c;
+            }
+          }
+        }
+      }
+    } else if (n_active == 0 && MODE == MODE_DQ && row_valid) {
+      __nv_bfloat16* dst = p.dq + (((long long)b * p.H + g * p.gs + hq) * p.T + tq) * 128;
+      for (int c = 0; c < 128; c += 8) *reinterpret_cast<uint4*>(dst + c) = make_uint4(0, 0, 0, 0);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static int bw_make_tmap_4d(CUtensorMap* tm, const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t d3, uint64_t s1,
+                           uint64_t s2, uint64_t s3, uint32_t b0, uint32_t b1, uint32_t b2) {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* pp = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &pp, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+      return KVB_ERR_DRIVER;
+    fn = reinterpret_cast<EncodeTiledFn>(pp);
+  }
+  cuuint64_t dims[4] = {d0, d1, d2, d3};
+  cuuint64_t strides[3] = {s1 * 2, s2 * 2, s3 * 2};
+  cuuint32_t box[4] = {b0, b1, b2, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? KVB_OK : KVB_ERR_TMAP;
+}
+
+}  // namespace kvb
+
+extern "C" int kvb_att_tile_minmax(const int32_t* token_pos, int32_t* tmin, int32_t* tmax, int B, int G, int L, long long tp_sb,
+                                   long long tp_sg, void* stream);
+
+// scratch: tile_min | tile_max (B*G*nT int32 each) | delta (B*H*T fp32)
+extern "C" long long kvb_sdpa_bwd_scratch_bytes(int B, int H, int G, int q_len, int kv_len) {
+  const long long nT = (kv_len + 127) / 128;
+  return (2LL * B * G * nT + (long long)B * H * q_len) * 4;
+}
+
+extern "C" int kvb_sdpa_bwd(const void* q, const void* k, const void* v, const int32_t* token_pos, const void* out,
+                            const void* dout, const float* lse, void* dq, float* dk, float* dv, void* scratch, int B, int H,
+                            int G, int q_len, int kv_len, long long k_sb, long long k_sg, long long tp_sb, long long tp_sg,
+                            long long dk_sb, long long dk_sg, float scale, int input_pos, int* status, void* stream) {
+  using namespace kvb;
+  if (B <= 0 || H <= 0 || G <= 0 || q_len <= 0 || kv_len <= 0 || H % G) return KVB_ERR_ARG;
+  const int gs = H / G;
+  if (gs > 128 || (gs & (gs - 1))) return KVB_ERR_UNSUPPORTED;
+  if ((k_sb % 8) || (k_sg % 8) || (dk_sb % 4) || (dk_sg % 4)) return KVB_ERR_ALIGN;
+  cudaStream_t s = (cudaStream_t)stream;
+  BwParams p;
+  p.B = B; p.H = H; p.G = G; p.T = q_len; p.L = kv_len;
+  p.gs = gs; p.npos = 128 / gs;
+  p.nT = (kv_len + 127) / 128;
+  p.nQT = (q_len + p.npos - 1) / p.npos;
+  p.token_pos = token_pos; p.tp_sb = tp_sb; p.tp_sg = tp_sg;
+  p.dk_sb = dk_sb; p.dk_sg = dk_sg;
+  int32_t* sc = reinterpret_cast<int32_t*>(scratch);
+  int32_t* tmin = sc;
+  int32_t* tmax = sc + (long long)B * G * p.nT;
+  float* delta = reinterpret_cast<float*>(sc + 2LL * B * G * p.nT);
+  p.tile_min = tmin; p.tile_max = tmax; p.lse = lse; p.delta = delta;
+  p.dq = (__nv_bfloat16*)dq; p.dk = dk; p.dv = dv;
+  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+  p.input_pos = input_pos; p.status = status;
+
+  CUtensorMap tmQ, tmdO, tmK, tmV;
+  int rc;
+  // Q (B,H,T,D): dims (D,T,H,B)
+  if ((rc = bw_make_tmap_4d(&tmQ, q, 128, q_len, H, B, 128, (uint64_t)q_len * 128, (uint64_t)H * q_len * 128, 64, p.npos, gs))) return rc;
+  // dO (B,T,H,D) viewed with dims (D,T,H,B): T stride H*D, H stride D
+  if ((rc = bw_make_tmap_4d(&tmdO, dout, 128, q_len, H, B, (uint64_t)H * 128, 128, (uint64_t)q_len * H * 128, 64, p.npos, gs))) return rc;
+  if ((rc = bw_make_tmap_4d(&tmK, k, 128, kv_len, G, B, 128, k_sg, k_sb, 64, 128, 1))) return rc;
+  if ((rc = bw_make_tmap_4d(&tmV, v, 128, kv_len, G, B, 128, k_sg, k_sb, 64, 128, 1))) return rc;
+
+  if ((rc = kvb_att_tile_minmax(token_pos, tmin, tmax, B, G, kv_len, tp_sb, tp_sg, stream))) return rc;
+  const long long rows = (long long)B * q_len * H;
+  att_delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, delta, B, q_len, H);
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(sdpa_bwd_kernel<MODE_DQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwSmem<MODE_DQ>::TOTAL);
+    cudaFuncSetAttribute(sdpa_bwd_kernel<MODE_DKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwSmem<MODE_DKV>::TOTAL);
+    attr_set = true;
+  }
+  sdpa_bwd_kernel<MODE_DQ><<<B * G * p.nQT, BW_THREADS, BwSmem<MODE_DQ>::TOTAL, s>>>(tmQ, tmdO, tmK, tmV, p);
+  sdpa_bwd_kernel<MODE_DKV><<<B * G * p.nT, BW_THREADS, BwSmem<MODE_DKV>::TOTAL, s>>>(tmQ, tmdO, tmK, tmV, p);
+  return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
+}

@@ -481,6 +481,14 @@ static int make_tmap_4d_bf16(CUtensorMap* tm, const void* ptr, uint64_t d0, uint
 
 }  // namespace kvb
 
+// Per-tile min/max of the token positions (tiles of 128 slots): (B,G,nT) each.
+extern "C" int kvb_att_tile_minmax(const int32_t* token_pos, int32_t* tmin, int32_t* tmax, int B, int G, int L, long long tp_sb,
+                                   long long tp_sg, void* stream) {
+  const int nT = (L + kvb::ATT_BN - 1) / kvb::ATT_BN;
+  kvb::att_tile_minmax_kernel<<<B * G * nT, 128, 0, (cudaStream_t)stream>>>(token_pos, tmin, tmax, G, L, nT, tp_sb, tp_sg);
+  return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
+}
+
 // Scratch layout (int32 words), provided by the caller:
 //   tile_min (B*G*nT) | tile_max (B*G*nT) | wpart (B*G*nQT*L floats, only if weights != NULL)
 extern "C" long long kvb_sdpa_fwd_scratch_bytes(int B, int H, int G, int q_len, int kv_len, int want_weights) {

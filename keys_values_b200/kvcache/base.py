@@ -191,6 +191,9 @@ class DefaultKVCache(KVCache):
     def __init__(self, config, max_batch_size, cache_length, block_idx, dtype=None, head_size=None, mha: Optional[MultiHeadSelfAttention] = None, **mha_kwargs):
         super().__init__(config, max_batch_size, cache_length, block_idx, dtype, head_size)
         self.mha = mha if mha is not None else MultiHeadSelfAttention(config, **mha_kwargs)
+        # ``recorder(block_idx, input_pos, attn_out, lse)``: set by the training forward
+        # pass to keep attention outputs and normalisers for the backward pass
+        self.attn_recorder = None
 
     def set_seq_length(self, value: int) -> None:
         self.mha.set_seq_length(value)
@@ -207,6 +210,14 @@ class DefaultKVCache(KVCache):
 
     def _update(self, *args, **kwargs) -> None:
         pass
+
+    def _can_decode_direct(self, query: torch.Tensor) -> bool:
+        """True if a single new token can be served by the decode kernel that reads
+        the cache storage directly (quantized storage included)."""
+        return False
+
+    def _decode_direct(self, query, key, value, token_idx, need_weights: bool):
+        raise NotImplementedError
 
     def _check_args(self, query, key, value, token_idx) -> int:
         if query.ndim != 4 or key.ndim != 4 or value.ndim != 4:
@@ -237,16 +248,33 @@ class DefaultKVCache(KVCache):
         if self._input_pos == 0:
             self._batch_size = query.shape[0]
             self._prefill(key, value, token_idx)
-            attn_out, _ = self.mha(query, DefaultKeysAndValues(key, value), block_idx=self.block_idx, input_pos=0)
+            if self.attn_recorder is not None:
+                attn_out, _, lse = self.mha(query, DefaultKeysAndValues(key, value), block_idx=self.block_idx, input_pos=0, return_lse=True)
+                self.attn_recorder(self.block_idx, 0, attn_out, lse)
+            else:
+                attn_out, _ = self.mha(query, DefaultKeysAndValues(key, value), block_idx=self.block_idx, input_pos=0)
             self._input_pos = n
             return attn_out
         input_pos = self._input_pos
-        k_and_v = self._forward(key, value, token_idx)
         need_w = self.needs_attn_weights()
-        attn_out, weights = self.mha(
-            query, k_and_v, block_idx=self.block_idx, input_pos=input_pos,
-            return_attn_weights=need_w, token_positions=self.token_positions(),
-        )
+        if n == 1 and self.attn_recorder is None and self._can_decode_direct(query):
+            attn_out, weights = self._decode_direct(query, key, value, token_idx, need_w)
+            self._input_pos = input_pos + 1
+            if need_w:
+                self._update(weights, 1)
+            return attn_out
+        k_and_v = self._forward(key, value, token_idx)
+        if self.attn_recorder is not None:
+            attn_out, weights, lse = self.mha(
+                query, k_and_v, block_idx=self.block_idx, input_pos=input_pos,
+                return_attn_weights=need_w, token_positions=self.token_positions(), return_lse=True,
+            )
+            self.attn_recorder(self.block_idx, input_pos, attn_out, lse)
+        else:
+            attn_out, weights = self.mha(
+                query, k_and_v, block_idx=self.block_idx, input_pos=input_pos,
+                return_attn_weights=need_w, token_positions=self.token_positions(),
+            )
         self._input_pos = input_pos + n
         if need_w:
             self._update(weights, n)

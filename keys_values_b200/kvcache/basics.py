@@ -65,6 +65,24 @@ class KVCacheWithBuffers(DefaultKVCache):
         self.kv_buffers.reset()
         self._replay_log = None
 
+    # -- single-token decode straight from the storage
+    def _can_decode_direct(self, query: torch.Tensor) -> bool:
+        if not query.is_cuda or self.mha.sliding_window(self.block_idx) is not None:
+            return False
+        if self.config.attention_logit_softcapping is not None or torch.is_grad_enabled() and query.requires_grad:
+            return False
+        from keys_values_b200.ops import cuda as _cu
+
+        return _cu.decode_supported(query, self.n_query_groups) and self.kv_buffers.supports_direct_decode()
+
+    def _decode_direct(self, query, key, value, token_idx, need_weights: bool):
+        self.kv_buffers.decode_mode = True
+        try:
+            self._forward(key, value, token_idx)
+        finally:
+            self.kv_buffers.decode_mode = False
+        return self.kv_buffers.decode_attention(query, self.mha.pos_encoding.sdpa_scale_factor(), need_weights)
+
     def deallocate_buffers(self) -> None:
         self.kv_buffers.deallocate()
 

@@ -49,6 +49,14 @@ class KVCacheBuffers(torch.nn.Module):
         self.cache_length = cache_length
         self.current_length = 0
         self.batch_size: Optional[int] = None
+        # set by the cache around a single-token step that is served by the decode kernel
+        self.decode_mode = False
+
+    def supports_direct_decode(self) -> bool:
+        return False
+
+    def decode_attention(self, query: torch.Tensor, scale: float, need_weights: bool):
+        raise NotImplementedError
 
     @property
     def max_batch_size(self) -> int:
@@ -147,6 +155,14 @@ class DefaultKVCacheBuffers(KVCacheBuffers):
     def get_keys_values(self) -> KeysAndValues:
         B, L = self.batch_size, self.current_length
         return DefaultKeysAndValues(self.k[:B, :, :L], self.v[:B, :, :L])
+
+    def supports_direct_decode(self) -> bool:
+        return self.k is not None and self.k.is_cuda and self.k.dtype == torch.bfloat16 and self.head_size == 128
+
+    def decode_attention(self, query, scale, need_weights):
+        from keys_values_b200.ops import cuda as _cu
+
+        return _cu.decode_attention(query, self.k, self.v, scale, self.current_length, need_weights)
 
     def size_estimate(self):
         p = self.params

@@ -79,6 +79,7 @@ class LongContextGradientModel(LongContextInferenceModel):
         profile_steps: bool = False,
         row_done_hook: Optional[Callable[[int, int], None]] = None,
         average_loss_per_batch: bool = False,
+        save_attention_outputs: Optional[bool] = None,
         **kwargs,
     ):
         super().__init__(
@@ -95,6 +96,11 @@ class LongContextGradientModel(LongContextInferenceModel):
         self.row_done_hook = row_done_hook
         self.average_loss_per_batch = average_loss_per_batch
         self.profile_steps = profile_steps
+        # Keep the attention outputs and normalisers of the forward pass (B·T·H·D values per
+        # layer) so that the backward pass only recomputes the linear parts. None = decide
+        # from the free device memory.
+        self.save_attention_outputs = save_attention_outputs
+        self._attn_saved = None
         self.profile_records: List[Dict[str, Any]] = []
         self._status = "init"
         self._layer_ckpt: Optional[LayerInputCheckpoints] = None
@@ -133,14 +139,32 @@ class LongContextGradientModel(LongContextInferenceModel):
             if cell_idx < n_cells - 1:
                 self._kv_ckpt.put(layer_idx, cell_idx + 1, caches[layer_idx].kv_snapshot())
 
+        self._attn_saved = None
+        if self._decide_save_attention(B, T, dev, dtype):
+            cfg = gpt.config
+            self._attn_saved = [
+                (torch.empty((B, T, cfg.n_head * cfg.head_size), dtype=dtype, device=dev),
+                 torch.empty((B, cfg.n_head, T), dtype=torch.float32, device=dev))
+                for _ in range(cfg.n_layer)
+            ]
+
+            def recorder(block_idx, pos, attn_out, lse):
+                o, l = self._attn_saved[block_idx]
+                n = attn_out.shape[1]
+                o[:, pos : pos + n] = attn_out
+                l[:, :, pos : pos + n] = lse
+
         for c in caches:
             c.switch_replay_logging(True)
+            c.attn_recorder = recorder if self._attn_saved is not None else None
         self.layer_input_hook, self.cell_boundary_hook = layer_hook, boundary_hook
         try:
             with torch.no_grad():
                 loss_rows = self._forward_internal(input_ids, targets, scale_factor)
         finally:
             self.layer_input_hook = self.cell_boundary_hook = None
+            for c in caches:
+                c.attn_recorder = None
         self._replay_logs = [c.get_replay_log() for c in caches]
         for c in caches:
             c.switch_replay_logging(False)
@@ -151,6 +175,19 @@ class LongContextGradientModel(LongContextInferenceModel):
                 torch.cuda.synchronize(dev)
             self.profile_records.append(dict(forward_time=time.perf_counter() - t0))
         return LossValue(loss_rows.mean(), self)
+
+    def _decide_save_attention(self, B: int, T: int, dev, dtype) -> bool:
+        if self.save_attention_outputs is not None:
+            return self.save_attention_outputs
+        if dev.type != "cuda":
+            return False
+        cfg = self.gpt_model.config
+        need = cfg.n_layer * B * T * (cfg.n_head * cfg.head_size * torch.empty((), dtype=dtype).element_size() + cfg.n_head * 4)
+        free, _ = torch.cuda.mem_get_info(dev)
+        free += torch.cuda.memory_reserved(dev) - torch.cuda.memory_allocated(dev)
+        # leave room for the other checkpoints and the per-cell activations
+        other = (len(self._row_boundaries()) + 1) * B * T * cfg.n_embd * 2 + 24 * 2**30
+        return need + other < free
 
     # ------------------------------------------------------------- backward
     def backward(self) -> None:
@@ -201,7 +238,8 @@ class LongContextGradientModel(LongContextInferenceModel):
                 c = caches[l]
                 st = ReplayState(B, c.n_query_groups, c.cache_length, c.head_size, ckpt.dtype, dev)
                 states.append(st)
-                tcaches.append(TrainingReplayCache(st, self._replay_logs[l], c.mha, l, c.n_head))
+                saved = self._attn_saved[l] if self._attn_saved is not None else None
+                tcaches.append(TrainingReplayCache(st, self._replay_logs[l], c.mha, l, c.n_head, saved=saved))
             try:
                 for l, tc in zip(range(first, end), tcaches):
                     blocks[l].attn.kv_cache = tc
@@ -226,6 +264,9 @@ class LongContextGradientModel(LongContextInferenceModel):
                 for l in range(first, end):
                     blocks[l].attn.kv_cache = caches[l]
             del states, tcaches
+            if self._attn_saved is not None:
+                for l in range(first, end):
+                    self._attn_saved[l] = None  # release as soon as the row is done
             if self.row_done_hook is not None:
                 self.row_done_hook(first, end)
         # 3) Input embeddings
@@ -248,6 +289,7 @@ class LongContextGradientModel(LongContextInferenceModel):
                 self.profile_records[-1]["peak_memory_gb"] = torch.cuda.max_memory_allocated(dev) / 2**30
 
     def clear(self) -> None:
+        self._attn_saved = None
         self._layer_ckpt = None
         self._kv_ckpt = None
         self._replay_logs = None

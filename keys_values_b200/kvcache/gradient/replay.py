@@ -81,7 +81,7 @@ class CacheWriteSDPA(torch.autograd.Function):
     """One replay step: write ``key/value`` at ``slots``, attend with ``query``."""
 
     @staticmethod
-    def forward(ctx, query, key, value, token, state: ReplayState, slots, new_length: int, scale: float, sliding_window, softcap):
+    def forward(ctx, query, key, value, token, state: ReplayState, slots, new_length: int, scale: float, sliding_window, softcap, saved=None):
         B, G, n, D = key.shape
         idx = slots.to(torch.int64)
         idx4 = idx.unsqueeze(-1).expand(-1, -1, -1, D)
@@ -94,10 +94,15 @@ class CacheWriteSDPA(torch.autograd.Function):
         state.current_length = new_length
         state.input_pos = input_pos + n
         L = new_length
-        out, _, lse = ops.sdpa_fwd(
-            query, state.k_buf[:, :, :L], state.v_buf[:, :, :L], scale, input_pos,
-            state.token_pos[:, :, :L], False, sliding_window, softcap,
-        )
+        if saved is not None:
+            # attention outputs and normalisers were kept by the forward pass
+            out = saved[0][:, input_pos : input_pos + n]
+            lse = saved[1][:, :, input_pos : input_pos + n]
+        else:
+            out, _, lse = ops.sdpa_fwd(
+                query, state.k_buf[:, :, :L], state.v_buf[:, :, :L], scale, input_pos,
+                state.token_pos[:, :, :L], False, sliding_window, softcap,
+            )
         ctx.save_for_backward(query, out, lse, idx, old_k, old_v, old_tp)
         ctx.state = state
         ctx.meta = (input_pos, old_length, new_length, scale, sliding_window, softcap, key.dtype)
@@ -112,12 +117,10 @@ class CacheWriteSDPA(torch.autograd.Function):
             raise RuntimeError("replay steps are being differentiated out of order")
         D = old_k.shape[-1]
         idx4 = idx.unsqueeze(-1).expand(-1, -1, -1, D)
-        dq, dk, dv = ops.sdpa_bwd(
+        dq, _, _ = ops.sdpa_bwd(
             grad_out.contiguous(), query, state.k_buf[:, :, :L], state.v_buf[:, :, :L], out, lse, scale, input_pos,
-            state.token_pos[:, :, :L], sliding_window, softcap,
+            state.token_pos[:, :, :L], sliding_window, softcap, dk_accum=state.dk_buf, dv_accum=state.dv_buf,
         )
-        state.dk_buf[:, :, :L] += dk
-        state.dv_buf[:, :, :L] += dv
         dk_new = state.dk_buf.gather(2, idx4)
         dv_new = state.dv_buf.gather(2, idx4)
         state.dk_buf.scatter_(2, idx4, 0.0)
@@ -128,14 +131,14 @@ class CacheWriteSDPA(torch.autograd.Function):
         state.token_pos.scatter_(2, idx, old_tp)
         state.current_length = old_length
         state.input_pos = input_pos
-        return dq.to(query.dtype), dk_new.to(kv_dtype), dv_new.to(kv_dtype), grad_token, None, None, None, None, None, None
+        return dq.to(query.dtype), dk_new.to(kv_dtype), dv_new.to(kv_dtype), grad_token, None, None, None, None, None, None, None
 
 
 class TrainingReplayCache(torch.nn.Module):
     """Stands in for the KV cache of one layer while a cell is differentiated.
     Follows the slot decisions of ``replay_log``; no scores are computed."""
 
-    def __init__(self, state: ReplayState, replay_log: KVCacheReplayLog, mha, block_idx: int, n_head: int):
+    def __init__(self, state: ReplayState, replay_log: KVCacheReplayLog, mha, block_idx: int, n_head: int, saved=None):
         if getattr(replay_log, "grace_period", 0):
             raise NotImplementedError("gradient computation with grace_period > 0 is not supported")
         super().__init__()
@@ -149,6 +152,7 @@ class TrainingReplayCache(torch.nn.Module):
         self.cache_length = state.cache_length
         self._chunk_idx = 0
         self.token: Optional[torch.Tensor] = None
+        self.saved = saved  # (attn_out (B,T,H·D), lse (B,H,T)) of the whole sequence, or None
 
     @property
     def input_pos(self) -> int:
@@ -175,6 +179,6 @@ class TrainingReplayCache(torch.nn.Module):
         out, self.token = CacheWriteSDPA.apply(
             query, key, value, self.token, st, slots, new_length,
             self.mha.pos_encoding.sdpa_scale_factor(), self.mha.sliding_window(self.block_idx),
-            self.mha.config.attention_logit_softcapping,
+            self.mha.config.attention_logit_softcapping, self.saved,
         )
         return out

@@ -145,8 +145,36 @@ class QuantizedKVCacheBuffers(KVCacheBuffers):
         self.dequant_buffers.k[:B, :, :n] = key
         self.dequant_buffers.v[:B, :, :n] = value
 
+    def supports_direct_decode(self) -> bool:
+        qk = self.quantizer_k
+        return self._fusable() and qk.buffers_are_allocated and qk.quant_buffer.is_cuda and self.head_size == 128
+
+    def decode_attention(self, query, scale, need_weights):
+        """Attention of one new token straight from the quantized storage; the row
+        written by the preceding :meth:`write` is taken in full precision."""
+        from keys_values_b200.ops import cuda as _cu
+
+        qk, qv = self.quantizer_k, self.quantizer_v
+        slots, key, value = self._last_new
+        new_kv = (key[:, :, 0], value[:, :, 0], slots[:, :, 0])
+        return _cu.decode_attention(
+            query, qk.quant_buffer, qv.quant_buffer, scale, self.current_length, need_weights,
+            quant=(qk.quant_scales, qk.quant_zero_points, qv.quant_scales, qv.quant_zero_points, self.num_bits), new_kv=new_kv,
+        )
+
     def write(self, slots, key, value, token_pos, input_pos) -> None:
         self._touch()
+        if self.decode_mode:
+            # storage only: the full-precision scratch is neither claimed nor filled
+            qk, qv = self.quantizer_k, self.quantizer_v
+            self.dequant_buffers.release(self)
+            ops.cache_write_quant(
+                None, None, token_pos, slots, key, value, input_pos,
+                qk.quant_buffer, qk.quant_scales, qk.quant_zero_points,
+                qv.quant_buffer, qv.quant_scales, qv.quant_zero_points, self.num_bits,
+            )
+            self._last_new = (slots, key, value)
+            return
         self.dequant_buffers.claim(self)
         dq = self.dequant_buffers
         if self._fusable():
@@ -162,6 +190,8 @@ class QuantizedKVCacheBuffers(KVCacheBuffers):
             self.quantizer_v.quantize_slots(slots, value)
 
     def get_keys_values(self) -> KeysAndValues:
+        if self.decode_mode:
+            return None
         self._touch()
         self.dequant_buffers.claim(self)
         B, L = self.batch_size, self.current_length

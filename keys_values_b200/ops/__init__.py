@@ -144,11 +144,21 @@ def sdpa_bwd(
     token_pos: Optional[torch.Tensor] = None,
     sliding_window: Optional[int] = None,
     softcap: Optional[float] = None,
+    dk_accum: Optional[torch.Tensor] = None,
+    dv_accum: Optional[torch.Tensor] = None,
 ):
-    """Returns fp32 ``dq (B,H,q,D)``, ``dk, dv (B,G,kv,D)``."""
+    """Returns ``dq (B,H,q,D)``, ``dk, dv (B,G,kv,D)`` (fp32 for dk/dv). With
+    ``dk_accum/dv_accum`` (fp32, cache shaped) the K/V gradients are added into their
+    first ``kv`` slots instead and ``None`` is returned for them."""
     if query.is_cuda and _cuda().sdpa_supported(query, key, sliding_window, softcap):
-        return _cuda().sdpa_bwd(grad_out, query, key, value, out, lse, scale, input_pos, token_pos)
-    return ref.sdpa_backward(grad_out, query, key, value, scale, input_pos, token_pos, sliding_window, softcap)
+        return _cuda().sdpa_bwd(grad_out, query, key, value, out, lse, scale, input_pos, token_pos, dk_accum, dv_accum)
+    dq, dk, dv = ref.sdpa_backward(grad_out, query, key, value, scale, input_pos, token_pos, sliding_window, softcap)
+    if dk_accum is not None:
+        L = key.shape[2]
+        dk_accum[:, :, :L] += dk
+        dv_accum[:, :, :L] += dv
+        return dq, None, None
+    return dq, dk, dv
 
 
 class SDPAFunction(torch.autograd.Function):
@@ -231,3 +241,12 @@ def h2o_update(scores, weights, k_select: int, n_evictable: int, normalize=False
 
 def cross_entropy_sum(logits: torch.Tensor, targets: torch.Tensor, ignore_index: int = -100) -> torch.Tensor:
     return ref.cross_entropy_sum(logits, targets, ignore_index)
+
+
+def decode_attention(query, key, value, scale, input_pos, token_pos=None, return_weights=False):
+    """One new query token against ``key/value (B,G,L,D)`` (all slots hold tokens at or
+    before the query position). Returns ``(out (B,1,H·D), weights (B,G,L) | None)``."""
+    if query.is_cuda and _cuda().decode_supported(query, key.shape[1]):
+        return _cuda().decode_attention(query, key.contiguous(), value.contiguous(), scale, key.shape[2], return_weights)
+    out, w = ref.sdpa(query, key, value, scale, input_pos, token_pos, return_weights)
+    return out, w

@@ -349,37 +349,88 @@ def sdpa_fwd(query, key, value, scale, input_pos, token_pos=None, return_weights
     return out, weights, lse
 
 
-def sdpa_bwd(grad_out, query, key, value, out, lse, scale, input_pos, token_pos=None):
-    """Attention backward on the GPU: recomputes P from ``lse`` group by group with bf16
-    tensor-core matmuls and fp32 softmax algebra. Returns fp32 ``dq, dk, dv``."""
+def _norm_token_pos(token_pos, B, G, L):
+    if token_pos is None:
+        return None
+    if token_pos.ndim == 1:
+        token_pos = token_pos.view(1, 1, L).expand(B, G, L)
+    if token_pos.dtype != torch.int32:
+        token_pos = token_pos.to(torch.int32)
+    if token_pos.stride(2) != 1:
+        token_pos = token_pos.contiguous()
+    return token_pos
+
+
+def sdpa_bwd(grad_out, query, key, value, out, lse, scale, input_pos, token_pos=None, dk_accum=None, dv_accum=None):
+    """Attention backward (tcgen05 kernels). Returns ``(dq, dk, dv)``: ``dq (B,H,T,D)`` in
+    the dtype of ``query``; ``dk, dv`` fp32. If ``dk_accum/dv_accum`` (fp32, cache shaped,
+    contiguous along the last two axes) are given, the gradients are *added* into their
+    first ``kv_len`` slots and ``None`` is returned for them."""
     B, H, T, D = query.shape
     G, L = key.shape[1], key.shape[2]
-    gs = H // G
     dev = query.device
-    go = grad_out.view(B, T, G, gs, D).permute(0, 2, 3, 1, 4)  # B,G,gs,T,D
-    o = out.view(B, T, G, gs, D).permute(0, 2, 3, 1, 4)
-    delta = (go.float() * o.float()).sum(-1)  # B,G,gs,T
-    dq = torch.empty((B, G, gs, T, D), dtype=torch.float32, device=dev)
-    dk = torch.empty((B, G, L, D), dtype=torch.float32, device=dev)
-    dv = torch.empty((B, G, L, D), dtype=torch.float32, device=dev)
-    qv = query.view(B, G, gs, T, D)
-    lse_v = lse.view(B, G, gs, T)
-    qpos = (input_pos + torch.arange(T, device=dev, dtype=torch.int32)).view(1, T, 1)
-    for g in range(G):
-        kf, vf = key[:, g], value[:, g]  # B,L,D
-        qg = qv[:, g].reshape(B, gs * T, D)
-        s = torch.bmm(qg, kf.transpose(1, 2)).float().view(B, gs, T, L) * scale
-        p = torch.exp(s - lse_v[:, g].unsqueeze(-1))
-        if token_pos is None:
-            tp = torch.arange(L, device=dev, dtype=torch.int32).view(1, 1, L)
-        else:
-            tp = token_pos[:, g].view(-1, 1, L) if token_pos.ndim == 3 else token_pos.view(1, 1, L)
-        p = p.masked_fill((tp > qpos).unsqueeze(1), 0.0)
-        gog = go[:, g].reshape(B, gs * T, D)
-        pb = p.to(torch.bfloat16).view(B, gs * T, L)
-        dv[:, g] = torch.bmm(pb.transpose(1, 2), gog.to(torch.bfloat16)).float()
-        dp = torch.bmm(gog.to(torch.bfloat16), vf.transpose(1, 2)).float().view(B, gs, T, L)
-        ds = (p * (dp - delta[:, g].unsqueeze(-1)) * scale).to(torch.bfloat16).view(B, gs * T, L)
-        dq[:, g] = torch.bmm(ds, kf).float().view(B, gs, T, D)
-        dk[:, g] = torch.bmm(ds.transpose(1, 2), qg).float()
-    return dq.view(B, H, T, D), dk, dv
+    lib().kvb_sdpa_bwd_scratch_bytes.restype = ctypes.c_longlong
+    query = query.contiguous()
+    grad_out = grad_out.contiguous()
+    out = out.contiguous()
+    if key.stride(3) != 1 or key.stride(2) != D or key.stride() != value.stride():
+        key, value = key.contiguous(), value.contiguous()
+    token_pos = _norm_token_pos(token_pos, B, G, L)
+    own = dk_accum is None
+    if own:
+        dk_accum = torch.zeros((B, G, L, D), dtype=torch.float32, device=dev)
+        dv_accum = torch.zeros((B, G, L, D), dtype=torch.float32, device=dev)
+    elif dk_accum.stride(3) != 1 or dk_accum.stride(2) != D or dk_accum.stride() != dv_accum.stride() or dk_accum.dtype != torch.float32:
+        raise NativeError("sdpa_bwd: accumulators must be fp32 with contiguous rows and equal strides")
+    dq = torch.empty((B, H, T, D), dtype=torch.bfloat16, device=dev)
+    nbytes = lib().kvb_sdpa_bwd_scratch_bytes(B, H, G, T, L)
+    scratch = torch.empty(nbytes // 4, dtype=torch.int32, device=dev)
+    st = status_word(dev)
+    _check(lib().kvb_sdpa_bwd(_p(query), _p(key), _p(value), _p(token_pos), _p(out), _p(grad_out), _p(lse.contiguous()), _p(dq),
+                              _p(dk_accum), _p(dv_accum), _p(scratch), B, H, G, T, L, _ll(key.stride(0)), _ll(key.stride(1)),
+                              _ll(token_pos.stride(0) if token_pos is not None else 0),
+                              _ll(token_pos.stride(1) if token_pos is not None else 0),
+                              _ll(dk_accum.stride(0)), _ll(dk_accum.stride(1)), ctypes.c_float(scale), int(input_pos), _p(st),
+                              _stream(query)), "sdpa_bwd")
+    _count(4)
+    if own:
+        return dq, dk_accum, dv_accum
+    return dq, None, None
+
+
+# -------------------------------------------------------------------- decode
+def decode_supported(query: torch.Tensor, n_query_groups: int) -> bool:
+    H = query.shape[1]
+    return (query.is_cuda and query.dtype == torch.bfloat16 and query.shape[-1] == 128 and query.shape[2] == 1
+            and H % n_query_groups == 0 and H // n_query_groups <= 16)
+
+
+def decode_attention(query, key, value, scale, kv_len, return_weights=False, quant=None, new_kv=None):
+    """One-token attention. ``key/value``: bf16 ``(Bmax,G,C,D)`` buffers (``quant is None``) or
+    uint8 code buffers with ``quant = (k_scale, k_zp, v_scale, v_zp, bits)``. ``new_kv =
+    (k_new (B,G,D), v_new (B,G,D), slot (B,G) int32)`` substitutes one row in full precision.
+    Returns ``(out (B,1,H·D), weights (B,G,kv_len) | None)``."""
+    B, H, _, D = query.shape
+    G, C = key.shape[1], key.shape[2]
+    dev = query.device
+    if not key.is_contiguous() or not value.is_contiguous():
+        raise NativeError("decode_attention: cache buffers must be contiguous")
+    lib().kvb_decode_scratch_bytes.restype = ctypes.c_longlong
+    out = torch.empty((B, 1, H * D), dtype=torch.bfloat16, device=dev)
+    weights = torch.empty((B, G, kv_len), dtype=torch.float32, device=dev) if return_weights else None
+    scratch = torch.empty(lib().kvb_decode_scratch_bytes(B, H, kv_len) // 4, dtype=torch.float32, device=dev)
+    if quant is None:
+        ks = kz = vs = vz = None
+        bits = 16
+    else:
+        ks, kz, vs, vz, bits = quant
+    kn = vn = sl = None
+    if new_kv is not None:
+        kn, vn, sl = new_kv
+        kn, vn = kn.contiguous(), vn.contiguous()
+        sl = sl.to(torch.int32).contiguous()
+    _check(lib().kvb_decode_attn(_p(query.contiguous()), _p(key), _p(value), _p(ks), _p(kz), _p(vs), _p(vz), _p(kn), _p(vn), _p(sl),
+                                 _p(out), _p(weights), _p(scratch), B, H, G, int(kv_len), C, int(bits), ctypes.c_float(scale),
+                                 _stream(query)), "decode_attn")
+    _count(3 if return_weights else 2)
+    return out, weights

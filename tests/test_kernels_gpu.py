@@ -221,3 +221,71 @@ def test_sdpa_status_reports_timeout_free_run():
     # a healthy run leaves the status word at zero
     _sdpa_case(1, 4, 1, 32, 256, 224, "arange")
     assert int(_cuda().status_word(DEV).item()) == 0
+
+
+def _rel_err(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("B,H,G,T,L,mode", [(1, 4, 1, 32, 128, "arange"), (1, 8, 2, 256, 256, "prefill"), (2, 8, 2, 100, 1000, "perm"),
+                                             (1, 32, 8, 256, 2048, "perm"), (1, 4, 4, 64, 300, "perm")])
+def test_sdpa_bwd(B, H, G, T, L, mode):
+    if mode == "prefill":
+        mode = "arange"
+    D = 128
+    q = torch.randn(B, H, T, D, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(B, G, L, D, device=DEV, dtype=torch.bfloat16)
+    v = torch.randn(B, G, L, D, device=DEV, dtype=torch.bfloat16)
+    go = torch.randn(B, T, H * D, device=DEV, dtype=torch.bfloat16)
+    if mode == "perm":
+        input_pos = 3 * L
+        tp = torch.empty(B, G, L, device=DEV, dtype=torch.int32)
+        for b in range(B):
+            for g in range(G):
+                allp = torch.cat((torch.randperm(input_pos, device=DEV)[: L - T], torch.arange(input_pos, input_pos + T, device=DEV)))
+                tp[b, g] = allp[torch.randperm(L, device=DEV)].to(torch.int32)
+    else:
+        tp = None
+        input_pos = L - T
+    scale = 1.0 / math.sqrt(D)
+    out, _, lse = _cuda().sdpa_fwd(q, k, v, scale, input_pos, tp, False)
+    # accumulate into a larger cache-shaped buffer that already holds something
+    C = L + 40
+    dk_acc = torch.randn(B, G, C, D, device=DEV)
+    dv_acc = torch.randn(B, G, C, D, device=DEV)
+    dk0, dv0 = dk_acc.clone(), dv_acc.clone()
+    dq, _, _ = _cuda().sdpa_bwd(go, q, k, v, out, lse, scale, input_pos, tp, dk_acc, dv_acc)
+    _cuda().check_status(DEV)
+    dq_r, dk_r, dv_r = ref.sdpa_backward(go, q, k, v, scale, input_pos, tp)
+    assert _rel_err(dq, dq_r) < 3e-2
+    assert _rel_err(dk_acc[:, :, :L] - dk0[:, :, :L], dk_r) < 3e-2
+    assert _rel_err(dv_acc[:, :, :L] - dv0[:, :, :L], dv_r) < 3e-2
+    assert torch.equal(dk_acc[:, :, L:], dk0[:, :, L:]) and torch.equal(dv_acc[:, :, L:], dv0[:, :, L:])
+
+
+@pytest.mark.parametrize("bits", [16, 8, 4])
+@pytest.mark.parametrize("B,H,G,L,C", [(1, 32, 8, 4096, 4096), (2, 8, 2, 1500, 2048), (1, 4, 4, 100, 128)])
+def test_decode_attention(bits, B, H, G, L, C):
+    D = 128
+    scale = 1.0 / math.sqrt(D)
+    q = torch.randn(B, H, 1, D, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(B, G, C, D, device=DEV, dtype=torch.bfloat16)
+    v = torch.randn(B, G, C, D, device=DEV, dtype=torch.bfloat16)
+    if bits == 16:
+        out, w = _cuda().decode_attention(q, k, v, scale, L, True)
+        k_eff, v_eff = k[:, :, :L], v[:, :, :L]
+    else:
+        qk, sk, zk = ref.quantize_rows(k, bits)
+        qv, sv, zv = ref.quantize_rows(v, bits)
+        slot = torch.randint(0, L, (B, G), device=DEV, dtype=torch.int32)
+        k_new = torch.randn(B, G, D, device=DEV, dtype=torch.bfloat16)
+        v_new = torch.randn(B, G, D, device=DEV, dtype=torch.bfloat16)
+        out, w = _cuda().decode_attention(q, qk, qv, scale, L, True, quant=(sk, zk, sv, zv, bits), new_kv=(k_new, v_new, slot))
+        k_eff = ref.dequantize_rows(qk, sk, zk, bits, torch.bfloat16)[:, :, :L].clone()
+        v_eff = ref.dequantize_rows(qv, sv, zv, bits, torch.bfloat16)[:, :, :L].clone()
+        idx = slot.long().view(B, G, 1, 1).expand(B, G, 1, D)
+        k_eff.scatter_(2, idx, k_new.unsqueeze(2))
+        v_eff.scatter_(2, idx, v_new.unsqueeze(2))
+    out_r, w_r = ref.sdpa(q, k_eff, v_eff, scale, L - 1, None, True)
+    torch.testing.assert_close(out.float(), out_r.float(), atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(w, w_r, atol=1e-3, rtol=2e-2)
