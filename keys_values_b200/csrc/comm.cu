@@ -1,0 +1,215 @@
+// Collectives over NVLink peer memory, written as kernels that read the peers'
+// buffers directly (P2P loads/stores through the NVSwitch fabric; no NCCL call, no TMA
+// load from peer memory, no cluster multicast).
+//
+// Symmetric memory: every rank allocates an arena of the same size with cudaMalloc,
+// exports it with cudaIpcGetMemHandle and maps every peer's arena with
+// cudaIpcOpenMemHandle (handle exchange happens in Python over torch.distributed). A
+// small flag area at the end of each arena carries the inter-GPU barriers.
+//
+// kvb_allreduce_mean: in-place two-shot all-reduce of a slice of the arena, fused with
+// the 1/world scale and the dtype cast:
+//   barrier  ->  reduce-scatter: rank r sums shard r of all ranks (fp32, fixed rank order,
+//   so every run gives identical bits) and writes scale·sum into shard r of its own arena
+//   barrier  ->  all-gather: rank r copies shard q from rank q, for all q != r
+//   barrier  (nobody overwrites a slice that a peer may still be reading)
+// Every wait is bounded: on timeout the kernel records STATUS_TIMEOUT_PEER_FLAG and
+// returns.
+//
+// Replaces the flatten -> NCCL all_reduce -> copy-back sequence of
+// keys_values/optimize/grad_accumulate.py:196-245.
+#include <string.h>
+
+#include "common.cuh"
+#include "kvb200.h"
+
+namespace kvb {
+
+constexpr int COMM_MAX_RANKS = 16;
+constexpr int COMM_THREADS = 512;
+
+struct CommPeers {
+  void* base[COMM_MAX_RANKS];       // arena of every rank, mapped into this process
+  uint32_t* flags[COMM_MAX_RANKS];  // flag area of every rank: [COMM_MAX_RANKS] words, one per writer
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Barrier across ranks for a whole grid. `sync` points to two words owned by this rank:
+// sync[0] = release (last epoch completed), sync[1] = number of local CTAs that arrived.
+// Every CTA arrives locally (after making its writes visible system-wide); CTA 0 waits
+// for all of them, exchanges flags with the peers and releases the other CTAs. `epoch`
+// must increase by one for every barrier of the communicator. All CTAs of the grid must
+// be resident at the same time (the launcher keeps the grid far below the SM count).
+__device__ bool cross_gpu_barrier(const CommPeers& peers, int rank, int world, uint32_t epoch, uint32_t* sync, int* status,
+                                  long long limit) {
+  __shared__ int ok_s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    ok_s = 1;
+    __threadfence_system();
+    atomicAdd(sync + 1, 1u);
+  }
+  __syncthreads();
+  if (blockIdx.x == 0) {
+    if (threadIdx.x == 0) {
+      long long t0 = clock64();
+      while (*((volatile uint32_t*)(sync + 1)) < gridDim.x) {
+        if (clock64() - t0 > limit) {
+          if (status) atomicCAS(status, 0, STATUS_TIMEOUT_PEER_FLAG);
+          ok_s = 0;
+          break;
+        }
+      }
+      *((volatile uint32_t*)(sync + 1)) = 0;
+      __threadfence_system();
+    }
+    __syncthreads();
+    if ((int)threadIdx.x < world && ok_s) {
+      const int peer = threadIdx.x;
+      st_release_sys(peers.flags[peer] + rank, epoch);  // tell `peer` that this rank has arrived
+      const uint32_t* mine = peers.flags[rank] + peer;  // wait until `peer` has arrived here
+      long long t0 = clock64();
+      while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
+        if (clock64() - t0 > limit) {
+          if (status) atomicCAS(status, 0, STATUS_TIMEOUT_PEER_FLAG);
+          ok_s = 0;
+          break;
+        }
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      atomicExch(sync, ok_s ? epoch : 0xFFFFFFFFu);
+    }
+  } else {
+    if (threadIdx.x == 0) {
+      long long t0 = clock64();
+      while (true) {
+        const uint32_t v = *((volatile uint32_t*)sync);
+        if (v == 0xFFFFFFFFu) {
+          ok_s = 0;
+          break;
+        }
+        if ((int32_t)(v - epoch) >= 0) break;
+        if (clock64() - t0 > 3 * limit) {
+          if (status) atomicCAS(status, 0, STATUS_TIMEOUT_PEER_FLAG);
+          ok_s = 0;
+          break;
+        }
+      }
+      __threadfence();
+    }
+  }
+  __syncthreads();
+  return ok_s != 0;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(COMM_THREADS)
+allreduce_mean_kernel(CommPeers peers, int rank, int world, long long start, long long count, float scale, uint32_t epoch0,
+                      uint32_t* sync, int* status, long long limit) {
+  constexpr int V = 16 / sizeof(T);
+  if (!cross_gpu_barrier(peers, rank, world, epoch0, sync, status, limit)) return;
+  // shards in units of 16-byte vectors
+  const long long nvec = count / V;
+  const long long per = (nvec + world - 1) / world;
+  const long long v0 = min(per * rank, nvec), v1 = min(v0 + per, nvec);
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = v0 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < v1; i += stride) {
+    float acc[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) acc[j] = 0.f;
+    for (int r = 0; r < world; ++r) {
+      const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(peers.base[r]) + start + i * V));
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int j = 0; j < V; ++j) acc[j] += to_f32(e[j]);
+    }
+    uint4 outv;
+    T* o = reinterpret_cast<T*>(&outv);
+#pragma unroll
+    for (int j = 0; j < V; ++j) o[j] = from_f32<T>(acc[j] * scale);
+    *reinterpret_cast<uint4*>(reinterpret_cast<T*>(peers.base[rank]) + start + i * V) = outv;
+  }
+  if (!cross_gpu_barrier(peers, rank, world, epoch0 + 1, sync, status, limit)) return;
+  for (int q = 1; q < world; ++q) {
+    const int src = (rank + q) % world;
+    const long long s0 = min(per * src, nvec), s1 = min(s0 + per, nvec);
+    for (long long i = s0 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < s1; i += stride) {
+      const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(peers.base[src]) + start + i * V));
+      *reinterpret_cast<uint4*>(reinterpret_cast<T*>(peers.base[rank]) + start + i * V) = raw;
+    }
+  }
+  cross_gpu_barrier(peers, rank, world, epoch0 + 2, sync, status, limit);
+}
+
+}  // namespace kvb
+
+using namespace kvb;
+
+// ---- symmetric memory plumbing -------------------------------------------------------
+extern "C" int kvb_symm_alloc(void** ptr, long long bytes) {
+  if (cudaMalloc(ptr, (size_t)bytes) != cudaSuccess) return KVB_ERR_CUDA;
+  if (cudaMemset(*ptr, 0, (size_t)bytes) != cudaSuccess) return KVB_ERR_CUDA;
+  return KVB_OK;
+}
+extern "C" int kvb_symm_free(void* ptr) { return cudaFree(ptr) == cudaSuccess ? KVB_OK : KVB_ERR_CUDA; }
+extern "C" int kvb_ipc_handle_size() { return (int)sizeof(cudaIpcMemHandle_t); }
+extern "C" int kvb_ipc_get_handle(void* ptr, void* handle_out) {
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, ptr) != cudaSuccess) return KVB_ERR_CUDA;
+  memcpy(handle_out, &h, sizeof(h));
+  return KVB_OK;
+}
+extern "C" int kvb_ipc_open_handle(const void* handle, void** ptr_out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  if (cudaIpcOpenMemHandle(ptr_out, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) return KVB_ERR_CUDA;
+  return KVB_OK;
+}
+extern "C" int kvb_ipc_close_handle(void* ptr) { return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? KVB_OK : KVB_ERR_CUDA; }
+
+// bases/flags: arrays of `world` device pointers valid in this process. dtype: 0 fp32, 1 bf16, 2 fp16.
+// start/count in elements; start*sizeof(T) and the arena base must be 16-byte aligned, count a multiple of 16/sizeof(T).
+extern "C" int kvb_allreduce_mean(void* const* bases, void* const* flags, int rank, int world, long long start, long long count,
+                                  float scale, unsigned epoch0, void* local_sync, int dtype, int n_ctas, int* status,
+                                  double timeout_s, void* stream) {
+  if (world < 1 || world > COMM_MAX_RANKS || rank < 0 || rank >= world || count <= 0) return KVB_ERR_ARG;
+  CommPeers peers;
+  for (int r = 0; r < world; ++r) {
+    peers.base[r] = bases[r];
+    peers.flags[r] = reinterpret_cast<uint32_t*>(flags[r]);
+  }
+  const long long limit = (long long)(timeout_s * 1.9e9);
+  if (n_ctas <= 0) n_ctas = 32;
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (dtype) {
+    case 0:
+      if ((start % 4) || (count % 4)) return KVB_ERR_ALIGN;
+      allreduce_mean_kernel<float><<<n_ctas, COMM_THREADS, 0, s>>>(peers, rank, world, start, count, scale, epoch0,
+                                                                  (uint32_t*)local_sync, status, limit);
+      break;
+    case 1:
+      if ((start % 8) || (count % 8)) return KVB_ERR_ALIGN;
+      allreduce_mean_kernel<__nv_bfloat16><<<n_ctas, COMM_THREADS, 0, s>>>(peers, rank, world, start, count, scale, epoch0,
+                                                                          (uint32_t*)local_sync, status, limit);
+      break;
+    case 2:
+      if ((start % 8) || (count % 8)) return KVB_ERR_ALIGN;
+      allreduce_mean_kernel<__half><<<n_ctas, COMM_THREADS, 0, s>>>(peers, rank, world, start, count, scale, epoch0,
+                                                                   (uint32_t*)local_sync, status, limit);
+      break;
+    default:
+      return KVB_ERR_ARG;
+  }
+  return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
+}

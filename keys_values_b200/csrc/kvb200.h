@@ -77,6 +77,20 @@ int kvb_decode_attn(const void* q, const void* kq, const void* vq, const float* 
                     const int32_t* vz, const void* k_new, const void* v_new, const int32_t* new_slot, void* out, float* weights,
                     void* scratch, int B, int H, int G, int L, int C, int bits, float scale, void* stream);
 
+
+// ---- comm.cu: symmetric memory over CUDA IPC and the fused all-reduce
+int kvb_symm_alloc(void** ptr, long long bytes);
+int kvb_symm_free(void* ptr);
+int kvb_ipc_handle_size(void);
+int kvb_ipc_get_handle(void* ptr, void* handle_out);
+int kvb_ipc_open_handle(const void* handle, void** ptr_out);
+int kvb_ipc_close_handle(void* ptr);
+// In-place mean over ranks of elements [start, start+count) of the symmetric arenas. `epoch0` advances by 3 per call.
+// `local_sync`: two zero-initialised uint32 words in this rank's device memory.
+int kvb_allreduce_mean(void* const* bases, void* const* flags, int rank, int world, long long start, long long count,
+                       float scale, unsigned epoch0, void* local_sync, int dtype, int n_ctas, int* status, double timeout_s,
+                       void* stream);
+
 #ifdef __cplusplus
 }
 #endif

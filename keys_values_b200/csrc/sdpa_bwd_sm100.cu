@@ -26,7 +26,7 @@
 namespace kvb {
 
 constexpr int BW_TILE_BYTES = 128 * 128 * 2;
-constexpr int BW_THREADS = 192;
+constexpr int BW_THREADS = 320;  // TMA warp + MMA warp + 8 compute warps
 enum { MODE_DQ = 0, MODE_DKV = 1 };
 
 template <int MODE>
@@ -139,10 +139,10 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(&c_empty[s], 1);
     }
     mbar_init(xy_full, 1);
-    mbar_init(pds_full, 4);
+    mbar_init(pds_full, 8);
     mbar_init(pds_empty, 1);
     mbar_init(acc_full, 1);
-    mbar_init(grp_bar, 128);
+    mbar_init(grp_bar, 256);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -246,9 +246,12 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else {
     // ----------------------------------------------- compute + epilogue warps
+    // 8 warps: two per TMEM sub-partition; thread (row, half) owns columns [64·half, +64) of its row
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int cbeg = half * 64;
     const int row = quarter * 32 + lane;
-    const int tid = threadIdx.x - 64;
+    const int tid = threadIdx.x - 64;  // 0..255
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     bool ok = n_active > 0;
     uint32_t s = 0, grp_phase = 0;
@@ -287,23 +290,25 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (msk) {
           const int jj = ct * 128 + tid;
           int v = INT_MAX;
-          if (jj < p.L) v = p.token_pos ? p.token_pos[b * p.tp_sb + g * p.tp_sg + jj] : jj;
+          if (tid < 128 && jj < p.L) v = p.token_pos ? p.token_pos[b * p.tp_sb + g * p.tp_sg + jj] : jj;
           if (!group_sync()) { ok = false; break; }
-          stat_i[tid] = v;
+          if (tid < 128) stat_i[tid] = v;
           if (!group_sync()) { ok = false; break; }
         }
       } else {
         // statistics of the query tile: column c <-> (head c / npos, position c % npos)
-        const int c_hq = tid / p.npos, c_tq = ct * p.npos + tid % p.npos;
+        const int c_hq = (tid & 127) / p.npos, c_tq = ct * p.npos + (tid & 127) % p.npos;
         float l2 = INFINITY, dl = 0.f;
-        if (c_tq < p.T) {
+        if (tid < 128 && c_tq < p.T) {
           const long long idx = ((long long)b * p.H + g * p.gs + c_hq) * p.T + c_tq;
           l2 = p.lse[idx] * 1.4426950408889634f;
           dl = p.delta[idx];
         }
         if (!group_sync()) { ok = false; break; }
-        stat_lse[tid] = l2;
-        stat_dl[tid] = dl;
+        if (tid < 128) {
+          stat_lse[tid] = l2;
+          stat_dl[tid] = dl;
+        }
         if (!group_sync()) { ok = false; break; }
       }
       if (!mbar_wait_bounded(xy_full, s & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
@@ -311,7 +316,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_after();
       const int cpos0 = p.input_pos + ct * p.npos;  // MODE_DKV: position of column c is cpos0 + c % npos
 #pragma unroll 1
-      for (int c0 = 0; c0 < 128; c0 += 32) {
+      for (int c0 = cbeg; c0 < cbeg + 64; c0 += 32) {
         uint32_t xr[32], yr[32];
         tmem_ld_32x32b_x32(tmem_X + lane_base + (uint32_t)c0, xr);
         tmem_ld_32x32b_x32(tmem_Y + lane_base + (uint32_t)c0, yr);
@@ -365,7 +370,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (MODE == MODE_DQ) {
         __nv_bfloat16* dst = p.dq + (((long long)b * p.H + g * p.gs + hq) * p.T + tq) * 128;
 #pragma unroll 1
-        for (int c0 = 0; c0 < 128; c0 += 32) {
+        for (int c0 = cbeg; c0 < cbeg + 64; c0 += 32) {
           uint32_t r[32];
           tmem_ld_32x32b_x32(tmem_A2 + lane_base + (uint32_t)c0, r);
           tmem_ld_wait();
@@ -384,7 +389,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       } else {
         const long long off = b * p.dk_sb + g * p.dk_sg + (long long)(rt * 128 + row) * 128;
 #pragma unroll 1
-        for (int c0 = 0; c0 < 128; c0 += 32) {
+        for (int c0 = cbeg; c0 < cbeg + 64; c0 += 32) {
           uint32_t r1v[32], r2v[32];
           tmem_ld_32x32b_x32(tmem_A1 + lane_base + (uint32_t)c0, r1v);
           tmem_ld_32x32b_x32(tmem_A2 + lane_base + (uint32_t)c0, r2v);
@@ -407,7 +412,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
     } else if (n_active == 0 && MODE == MODE_DQ && row_valid) {
       __nv_bfloat16* dst = p.dq + (((long long)b * p.H + g * p.gs + hq) * p.T + tq) * 128;
-      for (int c = 0; c < 128; c += 8) *reinterpret_cast<uint4*>(dst + c) = make_uint4(0, 0, 0, 0);
+      for (int c = cbeg; c < cbeg + 64; c += 8) *reinterpret_cast<uint4*>(dst + c) = make_uint4(0, 0, 0, 0);
     }
   }
   tc_fence_before();

@@ -20,8 +20,10 @@
 //   * KV tiles whose smallest token position lies beyond the last query of the CTA are
 //     skipped by every role; tiles that contain no position beyond the first query of
 //     the CTA take the mask-free path.
-//   * warp 0 = TMA producer, warp 1 = MMA issuer / TMEM owner, warps 2..5 = softmax +
-//     epilogue (one query row per thread, its TMEM lane).
+//   * warp 0 = TMA producer, warp 1 = MMA issuer / TMEM owner, warps 2..9 = softmax +
+//     epilogue: two warps per TMEM sub-partition, each thread owns one query row (its TMEM
+//     lane) and one 64-column half of every tile, so that every SM sub-partition has two
+//     warps to interleave exp2 (MUFU) and ALU work.
 //
 // Replaces FlashInfer prefill + Triton score-sum + K/V reordering + query padding of the
 // reference (keys_values/attention/flashinfer_wrapper.py:51-273, :367-510,
@@ -40,7 +42,7 @@ int make_tmap_2d_bf16(CUtensorMap* tm, const void* ptr, uint64_t rows, uint64_t 
 constexpr int ATT_BM = 128;   // query rows per CTA
 constexpr int ATT_BN = 128;   // KV slots per tile
 constexpr int ATT_D = 128;    // head size
-constexpr int ATT_THREADS = 192;
+constexpr int ATT_THREADS = 320;  // TMA warp + MMA warp + 8 softmax warps
 constexpr int ATT_TILE_BYTES = 128 * 128 * 2;  // one 128x128 bf16 tile = two 64-column chunks of 16 KB
 
 struct AttSmem {
@@ -49,7 +51,8 @@ struct AttSmem {
   static constexpr int V = K + 2 * ATT_TILE_BYTES;
   static constexpr int P = V + 2 * ATT_TILE_BYTES;
   static constexpr int TP = P + ATT_TILE_BYTES;   // 128 int32 token positions of the current tile
-  static constexpr int BAR = TP + 512;
+  static constexpr int ML = TP + 512;             // (max, sum) of both column halves: 2 x 128 x 2 floats
+  static constexpr int BAR = ML + 2048;
   static constexpr int TOTAL = BAR + 256 + 1024;
 };
 
@@ -59,7 +62,7 @@ struct AttParams {
   const int32_t* tile_max;   // (B,G,nT)
   __nv_bfloat16* out;        // (B,T,H,D)
   float* lse;                // (B,H,T)
-  float* wpart;              // (B,G,nQT,L) or nullptr
+  float* wpart;              // (B,G,2*nQT,L) or nullptr
   int B, H, G, T, L, nT, nQT, gs, npos;
   long long tp_sb, tp_sg;
   float scale_log2;          // scale * log2(e)
@@ -134,6 +137,7 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int32_t* tp_s = reinterpret_cast<int32_t*>(smem + AttSmem::TP);
+  float* ml_s = reinterpret_cast<float*>(smem + AttSmem::ML);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // block -> (query tile, group, batch); query tiles fastest so that co-resident CTAs share K/V in L2
@@ -154,12 +158,12 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(&v_full[s], 1);
       mbar_init(&v_empty[s], 1);
       mbar_init(&s_full[s], 1);
-      mbar_init(&s_empty[s], 4);
+      mbar_init(&s_empty[s], 8);
     }
-    mbar_init(p_full, 4);
+    mbar_init(p_full, 8);
     mbar_init(p_empty, 1);
     mbar_init(o_full, 1);
-    mbar_init(grp_bar, 128);
+    mbar_init(grp_bar, 256);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -279,14 +283,18 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else {
     // ------------------------------------------------- softmax + epilogue warps
+    // 8 warps: two per TMEM sub-partition. Thread (row, half) owns columns
+    // [64·half, 64·half + 64) of its row in every S / P / O tile.
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int row = quarter * 32 + lane;          // TMEM lane = query row of the tile
     const int hq = row / p.npos;                  // head within the group
     const int pl = row % p.npos;                  // position within the tile
     const int tq = t0 + pl;
     const bool row_valid = tq < p.T;
     const int my_pos = p.input_pos + tq;
-    const int sm_tid = threadIdx.x - 64;          // 0..127
+    const int sm_tid = threadIdx.x - 64;          // 0..255
+    const int cbeg = half * 64;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     const float c = p.scale_log2;
     bool ok = n_active > 0;
@@ -302,20 +310,24 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     };
     auto load_tile_tp = [&](int t) -> bool {
       // token positions of tile t -> smem (INT_MAX beyond the end of the cache)
-      const int jj = t * ATT_BN + sm_tid;
       int v = INT_MAX;
-      if (jj < p.L) v = p.token_pos ? p.token_pos[b * p.tp_sb + g * p.tp_sg + jj] : jj;
+      if (sm_tid < ATT_BN) {
+        const int jj = t * ATT_BN + sm_tid;
+        if (jj < p.L) v = p.token_pos ? p.token_pos[b * p.tp_sb + g * p.tp_sg + jj] : jj;
+      }
       if (!group_sync()) return false;  // previous readers of tp_s are done
-      tp_s[sm_tid] = v;
+      if (sm_tid < ATT_BN) tp_s[sm_tid] = v;
       return group_sync();
     };
-    if (n_active == 0 && p.wpart) {
+    // column-sum partials: slot (2·qt + row half) of wpart (B,G,2·nQT,L); thread -> (column, row half)
+    const int cs_col = sm_tid & 127, cs_rh = sm_tid >> 7;
+    float* wbase = p.wpart ? p.wpart + ((((long long)b * p.G + g) * (2 * p.nQT) + 2 * qt + cs_rh) * p.L) : nullptr;
+    if (n_active == 0 && wbase) {
       for (int t = 0; t < p.nT; ++t)
-        if (t * ATT_BN + sm_tid < p.L)
-          p.wpart[((((long long)b * p.G + g) * p.nQT + qt) * p.L) + (long long)t * ATT_BN + sm_tid] = 0.f;
+        if (t * ATT_BN + cs_col < p.L) wbase[(long long)t * ATT_BN + cs_col] = 0.f;
     }
 
-    // ---- sweep 1: exact row max and sum
+    // ---- sweep 1: exact row max and sum (each half over its own columns)
     for (int t = 0; t < p.nT && ok; ++t) {
       if (tmin[t] > qpos_max) continue;
       const int sb = i & 1;
@@ -324,7 +336,7 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (!mbar_wait_bounded(&s_full[sb], (i >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
 #pragma unroll 1
-      for (int c0 = 0; c0 < ATT_BN; c0 += 32) {
+      for (int c0 = cbeg; c0 < cbeg + 64; c0 += 32) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(tmem_S0 + lane_base + (uint32_t)(sb * ATT_BN + c0), r);
         tmem_ld_wait();
@@ -332,10 +344,10 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         float cmax = -INFINITY;
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
-          float s = __uint_as_float(r[e]) * c;
-          if (masked && tp_s[c0 + e] > my_pos) s = -INFINITY;
-          x[e] = s;
-          cmax = fmaxf(cmax, s);
+          float sv = __uint_as_float(r[e]) * c;
+          if (masked && tp_s[c0 + e] > my_pos) sv = -INFINITY;
+          x[e] = sv;
+          cmax = fmaxf(cmax, sv);
         }
         const float m_new = fmaxf(m, cmax);
         float sum = 0.f;
@@ -349,14 +361,26 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (lane == 0) mbar_arrive(&s_empty[sb]);
       ++i;
     }
-    const float lse2 = l > 0.f ? m + log2f(l) : INFINITY;
+    // merge the two halves of every row
+    float lse2 = INFINITY;
+    if (ok) {
+      ml_s[(half * ATT_BM + row) * 2] = m;
+      ml_s[(half * ATT_BM + row) * 2 + 1] = l;
+      if (!group_sync()) ok = false;
+      if (ok) {
+        const float m2 = ml_s[((half ^ 1) * ATT_BM + row) * 2], l2 = ml_s[((half ^ 1) * ATT_BM + row) * 2 + 1];
+        const float mm = fmaxf(m, m2);
+        const float ll = l * fast_exp2(m - mm) + l2 * fast_exp2(m2 - mm);
+        lse2 = ll > 0.f ? mm + log2f(ll) : INFINITY;
+      }
+    }
 
     // ---- sweep 2: P = exp2(S·c − lse), O += P V, column sums of P
     uint8_t* Ps = smem + AttSmem::P;
     for (int t = 0; t < p.nT && ok; ++t) {
-      float* wdst = p.wpart ? p.wpart + ((((long long)b * p.G + g) * p.nQT + qt) * p.L) + (long long)t * ATT_BN : nullptr;
+      float* wdst = wbase ? wbase + (long long)t * ATT_BN : nullptr;
       if (tmin[t] > qpos_max) {
-        if (wdst && t * ATT_BN + sm_tid < p.L) wdst[sm_tid] = 0.f;
+        if (wdst && t * ATT_BN + cs_col < p.L) wdst[cs_col] = 0.f;
         continue;
       }
       const int sb = i & 1;
@@ -366,8 +390,9 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // the PV MMA of the previous tile must have finished reading P
       if (!mbar_wait_bounded(p_empty, (j & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_MISC)) { ok = false; break; }
       tc_fence_after();
+      uint8_t* chunk = Ps + half * (ATT_TILE_BYTES / 2);  // this half's 64 columns = one 64-wide swizzled chunk
 #pragma unroll 1
-      for (int c0 = 0; c0 < ATT_BN; c0 += 32) {
+      for (int c0 = cbeg; c0 < cbeg + 64; c0 += 32) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(tmem_S0 + lane_base + (uint32_t)(sb * ATT_BN + c0), r);
         tmem_ld_wait();
@@ -384,7 +409,6 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           if (!row_valid) p0 = p1 = 0.f;
           pk[e >> 1] = pack_bf16x2(p0, p1);
         }
-        uint8_t* chunk = Ps + (c0 >> 6) * (ATT_TILE_BYTES / 2);
         const int u0 = (c0 & 63) >> 3;
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
@@ -400,18 +424,18 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         mbar_arrive(p_full);
       }
       ++i;
-      // column sums over the 128 rows of the P tile (as rounded to bf16)
+      // column sums of the P tile (as rounded to bf16): thread -> (column, half of the rows)
       if (wdst) {
         if (!mbar_wait_bounded(p_full, j & 1, abort_flag, p.status, STATUS_TIMEOUT_MISC)) { ok = false; break; }
-        const uint8_t* chunk = Ps + (sm_tid >> 6) * (ATT_TILE_BYTES / 2);
-        const int cu = (sm_tid & 63) >> 3, ce = (sm_tid & 7) * 2;
+        const uint8_t* cchunk = Ps + (cs_col >> 6) * (ATT_TILE_BYTES / 2);
+        const int cu = (cs_col & 63) >> 3, ce = (cs_col & 7) * 2;
         float cs = 0.f;
 #pragma unroll 8
-        for (int rr = 0; rr < ATT_BM; ++rr) {
-          const __nv_bfloat16 hv = *reinterpret_cast<const __nv_bfloat16*>(chunk + sw128_offset(rr, cu) + ce);
+        for (int rr = cs_rh * 64; rr < cs_rh * 64 + 64; ++rr) {
+          const __nv_bfloat16 hv = *reinterpret_cast<const __nv_bfloat16*>(cchunk + sw128_offset(rr, cu) + ce);
           cs += __bfloat162float(hv);
         }
-        if (t * ATT_BN + sm_tid < p.L) wdst[sm_tid] = cs;
+        if (t * ATT_BN + cs_col < p.L) wdst[cs_col] = cs;
         if (!group_sync()) { ok = false; break; }  // all column reads done before P is overwritten
       }
       ++j;
@@ -423,7 +447,7 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_after();
       __nv_bfloat16* dst = p.out + (((long long)b * p.T + tq) * p.H + (g * p.gs + hq)) * ATT_D;
 #pragma unroll 1
-      for (int c0 = 0; c0 < ATT_D; c0 += 32) {
+      for (int c0 = cbeg; c0 < cbeg + 64; c0 += 32) {
         uint32_t r[32];
         if (n_active > 0) {
           tmem_ld_32x32b_x32(tmem_O + lane_base + (uint32_t)c0, r);
@@ -444,7 +468,7 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           }
         }
       }
-      if (row_valid && p.lse) p.lse[((long long)b * p.H + (g * p.gs + hq)) * p.T + tq] = lse2 * 0.6931471805599453f;
+      if (half == 0 && row_valid && p.lse) p.lse[((long long)b * p.H + (g * p.gs + hq)) * p.T + tq] = lse2 * 0.6931471805599453f;
     }
   }
   tc_fence_before();
@@ -490,7 +514,7 @@ extern "C" int kvb_att_tile_minmax(const int32_t* token_pos, int32_t* tmin, int3
 }
 
 // Scratch layout (int32 words), provided by the caller:
-//   tile_min (B*G*nT) | tile_max (B*G*nT) | wpart (B*G*nQT*L floats, only if weights != NULL)
+//   tile_min (B*G*nT) | tile_max (B*G*nT) | wpart (B*G*2*nQT*L floats, only if weights != NULL)
 extern "C" long long kvb_sdpa_fwd_scratch_bytes(int B, int H, int G, int q_len, int kv_len, int want_weights) {
   if (G <= 0 || H % G) return -1;
   const int gs = H / G;
@@ -498,7 +522,7 @@ extern "C" long long kvb_sdpa_fwd_scratch_bytes(int B, int H, int G, int q_len, 
   const long long npos = 128 / gs;
   const long long nQT = (q_len + npos - 1) / npos;
   long long words = 2LL * B * G * nT;
-  if (want_weights) words += (long long)B * G * nQT * kv_len;
+  if (want_weights) words += 2LL * B * G * nQT * kv_len;
   return words * 4;
 }
 
@@ -549,7 +573,7 @@ extern "C" int kvb_sdpa_fwd(const void* q, const void* k, const void* v, const i
   sdpa_fwd_kernel<<<B * G * p.nQT, ATT_THREADS, AttSmem::TOTAL, s>>>(tmQ, tmK, tmV, p);
   if (weights) {
     dim3 grid((kv_len + 255) / 256, B * G);
-    att_reduce_weights_kernel<<<grid, 256, 0, s>>>(p.wpart, weights, p.nQT, kv_len, 1.f / gs);
+    att_reduce_weights_kernel<<<grid, 256, 0, s>>>(p.wpart, weights, 2 * p.nQT, kv_len, 1.f / gs);
   }
   return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
 }

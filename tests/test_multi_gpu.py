@@ -1,0 +1,51 @@
+"""Multi-rank tests. On a machine with >= 2 GPUs the ranks use NCCL for the plumbing
+and the framework's peer-memory kernels for the data path; without GPUs the
+host-side logic of the data-parallel path runs on 2 gloo ranks."""
+import socket
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+WORKER = str(Path(__file__).resolve().parent / "dist_worker.py")
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _run(case: str, world: int, timeout: int = 300):
+    port = _free_port()
+    procs = [subprocess.Popen([sys.executable, WORKER, case, str(r), str(world), str(port)], stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in range(world)]
+    outs = []
+    try:
+        for p in procs:
+            out, _ = p.communicate(timeout=timeout)
+            outs.append(out)
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+    assert all(p.returncode == 0 for p in procs), "\n".join(outs)
+    assert "OK" in outs[0], outs[0]
+
+
+def test_dp_gradients_match_on_cpu_ranks():
+    _run("dp_train", 2)
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_allreduce_matches_nccl():
+    _run("allreduce", 2)
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_dp_gradients_match_on_gpus():
+    _run("dp_train", 2)
