@@ -1,0 +1,66 @@
+"""Runs ONE small case of one kernel family, for use under ``ncu`` (a few launches, a few
+hundred MB on the device). Inputs are larger than the 126 MB L2 only where stated.
+
+    python -m keys_values_b200.tools.profile_case sdpa_fwd|sdpa_bwd|gemm|decode|allreduce [--iters N]
+"""
+import argparse
+import math
+
+import torch
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("which")
+    ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--q", type=int, default=1024)
+    ap.add_argument("--kv", type=int, default=16384)
+    ap.add_argument("--batch", type=int, default=1)
+    args = ap.parse_args()
+    from keys_values_b200.ops import cuda as cu
+
+    dev = torch.device("cuda")
+    H, G, D = 32, 8, 128
+    scale = 1 / math.sqrt(D)
+    B, T, L = args.batch, args.q, args.kv
+    torch.manual_seed(0)
+    if args.which in ("sdpa_fwd", "sdpa_bwd"):
+        q = torch.randn(B, H, T, D, device=dev, dtype=torch.bfloat16)
+        k = torch.randn(B, G, L, D, device=dev, dtype=torch.bfloat16)
+        v = torch.randn(B, G, L, D, device=dev, dtype=torch.bfloat16)
+        tp = torch.stack([torch.stack([torch.randperm(L, device=dev) for _ in range(G)]) for _ in range(B)]).to(torch.int32) + 4 * L
+        # the last T tokens of the sequence are in the cache
+        tp[:, :, :T] = (torch.arange(T, device=dev) + 6 * L).to(torch.int32)
+        input_pos = 6 * L
+        if args.which == "sdpa_fwd":
+            for _ in range(args.iters):
+                out, w, lse = cu.sdpa_fwd(q, k, v, scale, input_pos, tp, True)
+        else:
+            out, w, lse = cu.sdpa_fwd(q, k, v, scale, input_pos, tp, False)
+            go = torch.randn_like(out)
+            dk = torch.zeros(B, G, L, D, device=dev)
+            dv = torch.zeros_like(dk)
+            for _ in range(args.iters):
+                cu.sdpa_bwd(go, q, k, v, out, lse, scale, input_pos, tp, dk, dv)
+    elif args.which == "gemm":
+        a = torch.randn(12288, 2560, device=dev, dtype=torch.bfloat16)
+        b = torch.randn(6144, 2560, device=dev, dtype=torch.bfloat16)
+        for _ in range(args.iters):
+            cu.gemm(a, b)
+    elif args.which == "decode":
+        q = torch.randn(4, H, 1, D, device=dev, dtype=torch.bfloat16)
+        k = torch.randint(0, 255, (4, G, L, D), device=dev, dtype=torch.uint8)
+        v = torch.randint(0, 255, (4, G, L, D), device=dev, dtype=torch.uint8)
+        s = torch.rand(4, G, L, device=dev) * 0.01
+        z = torch.randint(100, 150, (4, G, L), device=dev, dtype=torch.int32)
+        for _ in range(args.iters):
+            cu.decode_attention(q, k, v, scale, L, True, quant=(s, z, s, z, 8))
+    else:
+        raise SystemExit(f"unknown case {args.which}")
+    torch.cuda.synchronize()
+    cu.check_status(dev)
+    print("done")
+
+
+if __name__ == "__main__":
+    main()
