@@ -15,6 +15,7 @@
 // Replaces the cuBLAS calls behind nn.Linear in the reference
 // (keys_values/model.py:596-610, lora_utils.py:159-172).
 #include <cuda.h>
+#include <string.h>
 
 #include "common.cuh"
 #include "kvb200.h"
@@ -25,6 +26,61 @@ constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;
 constexpr int GEMM_STAGES = 4;
 constexpr int GEMM_THREADS = 192;
+
+// Optional fusion of the GEMM with a collective over NVLink peer memory.
+//   * reduce-scatter epilogue (rs_world > 1): the output rows are partitioned over ranks
+//     (rows_per_rank each, a multiple of 128). A finished tile is not written to C but
+//     stored straight into the *owner rank's* receive buffer, slot [this rank][row][col],
+//     with plain peer stores; then the tile is counted on the owner's flag word. Tiles for
+//     remote owners are produced first, the rank's own rows last, so the transfers hide
+//     behind the remaining MMAs. The owner sums the partials with kvb_reduce_partials.
+//   * gated A operand (a_flags != nullptr): rows of A arrive chunk by chunk (an all-gather
+//     that copies remote shards into LOCAL staging memory); the TMA producer waits for the
+//     chunk's flag before it loads a tile of that chunk. The copy runs in the first
+//     `ag_copy_ctas` CTAs of the same grid, which pull the peers' shards with plain loads.
+// No TMA load ever targets peer memory and nothing uses cluster multicast.
+struct GemmExtra {
+  // reduce-scatter epilogue
+  int rs_world, rs_rank, rows_per_rank;
+  uint32_t rs_tile_inc;                  // value added to the owner's flag per finished tile (1)
+  __nv_bfloat16* rs_dst[16];             // receive buffer of every rank: [world][rows_per_rank][N]
+  uint32_t* rs_flag[16];                 // flag words of every rank: [world] counters, indexed by source rank
+  // gated A / all-gather
+  const uint32_t* a_flags;               // [world] local counters: chunk q is complete when a_flags[q] >= a_target
+  uint32_t a_target;
+  int rows_per_chunk;                    // rows of A per source rank
+  int ag_copy_ctas;                      // CTAs [0, ag_copy_ctas) copy, the rest compute
+  int ag_world, ag_rank;
+  const __nv_bfloat16* ag_src[16];       // shard of every rank (peer pointers), [rows_per_chunk][K] with pitch ag_ld
+  __nv_bfloat16* ag_stage;               // local staging [world*rows_per_chunk][K] with pitch ag_ld (also operand A)
+  uint32_t* ag_flags_w;                  // same memory as a_flags, writable
+  long long ag_ld;
+  uint32_t* ag_ready[16];                // "shard is ready" word of every rank (each rank publishes its own)
+  uint32_t ag_epoch;                     // value of the ready words for this call
+  uint32_t* ag_pulled[16];               // "how many copy CTAs have pulled my shard" counter of every rank
+  uint32_t ag_pulled_target;             // own counter value at which this rank's shard may be overwritten
+  long long wait_limit;
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void red_release_gpu_add(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 
 template <int BN>
 struct GemmSmem {
@@ -40,8 +96,63 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
                  __nv_bfloat16* __restrict__ C, const __nv_bfloat16* __restrict__ residual, int M, int N, int K, int K2,
-                 long long ldc, int* status) {
+                 long long ldc, int* status, const GemmExtra ex) {
   using S = GemmSmem<BN>;
+  // ---- all-gather copy CTAs: pull the peers' shards into local staging, chunk by chunk
+  if (ex.ag_copy_ctas > 0 && (int)blockIdx.x < ex.ag_copy_ctas) {
+    __shared__ int ok_s;
+    if (threadIdx.x == 0) ok_s = 1;
+    __syncthreads();
+    const long long vec_per_row = (long long)K / 8;
+    // everything issued earlier on this stream has completed, so this rank's shard is final: publish it
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+      __threadfence_system();
+      st_release_sys_u32(ex.ag_ready[ex.ag_rank], ex.ag_epoch);
+    }
+    for (int qi = 1; qi < ex.ag_world; ++qi) {
+      const int src = (ex.ag_rank + qi) % ex.ag_world;
+      // the peer publishes "shard ready" by writing the epoch into ITS OWN ready word
+      if (threadIdx.x == 0) {
+        long long t0 = clock64();
+        while ((int32_t)(ld_acquire_sys_u32(ex.ag_ready[src]) - ex.ag_epoch) < 0) {
+          if (clock64() - t0 > ex.wait_limit) {
+            if (status) atomicCAS(status, 0, STATUS_TIMEOUT_PEER_FLAG);
+            ok_s = 0;
+            break;
+          }
+        }
+      }
+      __syncthreads();
+      if (!ok_s) return;
+      const long long total = (long long)ex.rows_per_chunk * vec_per_row;
+      const __nv_bfloat16* sp = ex.ag_src[src];
+      __nv_bfloat16* dp = ex.ag_stage + (long long)src * ex.rows_per_chunk * ex.ag_ld;
+      for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)ex.ag_copy_ctas * blockDim.x) {
+        const long long r = i / vec_per_row, c = i % vec_per_row;
+        const uint4 v = __ldcg(reinterpret_cast<const uint4*>(sp + r * ex.ag_ld + c * 8));
+        *reinterpret_cast<uint4*>(dp + r * ex.ag_ld + c * 8) = v;
+      }
+      __threadfence();
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        red_release_gpu_add(ex.ag_flags_w + src, 1u);        // local: chunk `src` is (partly) staged
+        red_release_sys_add(ex.ag_pulled[src], 1u);          // remote: tell `src` that this CTA is done with its shard
+      }
+    }
+    // do not let this rank overwrite its shard before every peer has pulled it
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+      long long t0 = clock64();
+      while ((int32_t)(ld_acquire_sys_u32(ex.ag_pulled[ex.ag_rank]) - ex.ag_pulled_target) < 0) {
+        if (clock64() - t0 > ex.wait_limit) {
+          if (status) atomicCAS(status, 0, STATUS_TIMEOUT_PEER_FLAG);
+          break;
+        }
+      }
+    }
+    return;
+  }
+  const int cta = (int)blockIdx.x - ex.ag_copy_ctas;
+  const int n_ctas = (int)gridDim.x - ex.ag_copy_ctas;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::BAR_OFFSET);
@@ -59,6 +170,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int kb1 = (K + GEMM_BK - 1) / GEMM_BK;
   const int kb2 = (K2 + GEMM_BK - 1) / GEMM_BK;
   const int num_kb = kb1 + kb2;
+  // tile -> (row offset, column offset). Row blocks are rotated so that the blocks this rank
+  // already holds (all-gather) come first, or the rows this rank owns (reduce-scatter) last.
+  int m_rot = 0;
+  if (ex.a_flags) m_rot = (ex.ag_rank * ex.rows_per_chunk) / GEMM_BM;
+  if (ex.rs_world > 1) m_rot = ((ex.rs_rank + 1) * ex.rows_per_rank / GEMM_BM) % num_m;
+  auto tile_coords = [&](int tile, int& m0, int& n0) {
+    const bool comm = ex.a_flags != nullptr || ex.rs_world > 1;
+    if (comm) {
+      // row-block major: all column tiles of a row block are adjacent in time
+      const int mi = (tile / num_n + m_rot) % num_m;
+      m0 = mi * GEMM_BM;
+      n0 = (tile % num_n) * BN;
+    } else {
+      m0 = (tile % num_m) * GEMM_BM;
+      n0 = (tile / num_m) * BN;
+    }
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < GEMM_STAGES; ++s) {
@@ -90,9 +218,26 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       long long issued = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % num_m) * GEMM_BM;
-        const int n0 = (tile / num_m) * BN;
+      for (int tile = cta; tile < num_tiles && ok; tile += n_ctas) {
+        int m0, n0;
+        tile_coords(tile, m0, n0);
+        if (ex.a_flags) {
+          // rows of A come from an all-gather: wait until the chunk that holds this tile is local
+          const int chunk = m0 / ex.rows_per_chunk;
+          if (chunk != ex.ag_rank) {
+            long long t0 = clock64();
+            while ((int32_t)(ld_acquire_gpu_u32(ex.a_flags + chunk) - ex.a_target) < 0) {
+              if (*abort_flag || clock64() - t0 > ex.wait_limit) {
+                if (status) atomicCAS(status, 0, STATUS_TIMEOUT_PEER_FLAG);
+                *abort_flag = 1;
+                ok = false;
+                break;
+              }
+            }
+            if (!ok) break;
+            asm volatile("fence.proxy.async;" ::: "memory");  // generic-proxy writes -> visible to the TMA reads
+          }
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag, status, STATUS_TIMEOUT_EMPTY)) {
             ok = false;
@@ -132,7 +277,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = cta; tile < num_tiles && ok; tile += n_ctas) {
         if (!mbar_wait_bounded(&tmem_empty[acc], acc_phase ^ 1, abort_flag, status, STATUS_TIMEOUT_TMEM_EMPTY)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
@@ -171,12 +316,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int row_in_tile = quarter * 32 + lane;
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-      const int m0 = (tile % num_m) * GEMM_BM;
-      const int n0 = (tile / num_m) * BN;
+    for (int tile = cta; tile < num_tiles; tile += n_ctas) {
+      int m0, n0;
+      tile_coords(tile, m0, n0);
       if (!mbar_wait_bounded(&tmem_full[acc], acc_phase, abort_flag, status, STATUS_TIMEOUT_TMEM_FULL)) break;
       tc_fence_after();
       const int m = m0 + row_in_tile;
+      // reduce-scatter epilogue: the tile goes to the receive buffer of the rank that owns its rows
+      __nv_bfloat16* out_base = C;
+      long long out_row = m;
+      int dest = -1;
+      if (ex.rs_world > 1) {
+        dest = m0 / ex.rows_per_rank;
+        out_base = ex.rs_dst[dest];
+        out_row = (long long)ex.rs_rank * ex.rows_per_rank + (m - dest * ex.rows_per_rank);
+      }
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -185,7 +339,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tmem_ld_wait();
         const int n = n0 + c0;
         if (m < M && n < N) {
-          __nv_bfloat16* dst = C + (long long)m * ldc + n;
+          __nv_bfloat16* dst = out_base + out_row * ldc + n;
           const __nv_bfloat16* res = residual ? residual + (long long)m * ldc + n : nullptr;
           if (n + 32 <= N) {
 #pragma unroll
@@ -222,6 +376,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if (dest >= 0) {
+        // make this warp's peer stores visible system-wide, then count a quarter tile at the owner
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) red_release_sys_add(ex.rs_flag[dest] + ex.rs_rank, ex.rs_tile_inc);
+      }
       if (++acc == 2) {
         acc = 0;
         acc_phase ^= 1;
@@ -282,7 +442,7 @@ static int sm_count() {
 template <int BN>
 static int launch_gemm(const void* A, const void* B, const void* A2, const void* B2, void* C, const void* residual, int M,
                        int N, int K, int K2, long long lda, long long ldb, long long lda2, long long ldb2, long long ldc,
-                       int* status, int max_ctas, cudaStream_t stream) {
+                       int* status, int max_ctas, cudaStream_t stream, const GemmExtra* extra = nullptr) {
   using S = GemmSmem<BN>;
   CUtensorMap tmA, tmB, tmA2, tmB2;
   int rc;
@@ -301,11 +461,17 @@ static int launch_gemm(const void* A, const void* B, const void* A2, const void*
     attr_set = true;
   }
   const int num_tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN);
+  GemmExtra ex;
+  memset(&ex, 0, sizeof(ex));
+  if (extra) ex = *extra;
   int ctas = sm_count();
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
-  if (num_tiles < ctas) ctas = num_tiles;
+  int compute = ctas - ex.ag_copy_ctas;
+  if (compute < 1) return KVB_ERR_ARG;
+  if (num_tiles < compute) compute = num_tiles;
+  ctas = compute + ex.ag_copy_ctas;
   gemm_bf16_kernel<BN><<<ctas, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, tmA2, tmB2, (__nv_bfloat16*)C,
-                                                               (const __nv_bfloat16*)residual, M, N, K, K2, ldc, status);
+                                                               (const __nv_bfloat16*)residual, M, N, K, K2, ldc, status, ex);
   return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
 }
 
@@ -324,4 +490,130 @@ extern "C" int kvb_gemm_bf16(const void* A, const void* B, const void* A2, const
   if (tiles256 >= 120 || N % 256 == 0 && tiles256 >= 64)
     return kvb::launch_gemm<256>(A, B, A2, B2, C, residual, M, N, K, K2, lda, ldb, lda2, ldb2, ldc, status, max_ctas, s);
   return kvb::launch_gemm<128>(A, B, A2, B2, C, residual, M, N, K, K2, lda, ldb, lda2, ldb2, ldc, status, max_ctas, s);
+}
+
+
+// ------------------------------------------------------------------------------------
+// Fused GEMM + collective entry points (tensor parallelism over NVLink peer memory)
+// ------------------------------------------------------------------------------------
+namespace kvb {
+
+// out[r, :] = sum_src recv[src][r, :] (+ residual[r, :]), after every source has delivered all its tiles
+__global__ void reduce_partials_kernel(const __nv_bfloat16* __restrict__ recv, const uint32_t* __restrict__ flags,
+                                       uint32_t target, int world, const __nv_bfloat16* __restrict__ residual,
+                                       __nv_bfloat16* __restrict__ out, long long rows, int N, long long wait_limit, int* status) {
+  __shared__ int ok_s;
+  if (threadIdx.x == 0) ok_s = 1;
+  __syncthreads();
+  if ((int)threadIdx.x < world) {
+    long long t0 = clock64();
+    while ((int32_t)(ld_acquire_sys_u32(flags + threadIdx.x) - target) < 0) {
+      if (clock64() - t0 > wait_limit) {
+        if (status) atomicCAS(status, 0, STATUS_TIMEOUT_PEER_FLAG);
+        ok_s = 0;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (!ok_s) return;
+  const long long nvec = rows * N / 8;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int s = 0; s < world; ++s) {
+      const uint4 v = __ldcg(reinterpret_cast<const uint4*>(recv + (long long)s * rows * N) + i);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+    if (residual) {
+      const uint4 v = reinterpret_cast<const uint4*>(residual)[i];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    reinterpret_cast<uint4*>(out)[i] = o;
+  }
+}
+
+}  // namespace kvb
+
+// GEMM -> reduce-scatter. A (M,K) and B (N,K) are this rank's shards along K; the rows of the
+// (M,N) product are owned by ranks in blocks of M/world rows. recv_bufs[r]: rank r's receive
+// buffer [world][M/world][N] bf16; flags[r]: rank r's [world] tile counters. After the GEMM the
+// rank reduces what it received into `out` (M/world, N) (+ residual). `flag_target`: value every
+// counter of this rank reaches when all sources have delivered this call (4 x tiles x calls).
+extern "C" int kvb_gemm_reduce_scatter(const void* A, const void* B, void* out, const void* residual, void* const* recv_bufs,
+                                       void* const* flags, int rank, int world, int M, int N, int K, long long lda,
+                                       long long ldb, unsigned flag_target, int* status, double timeout_s, void* stream) {
+  using namespace kvb;
+  if (world < 2 || world > 16 || M % world || (M / world) % GEMM_BM || N % 8 || K % 8) return KVB_ERR_ARG;
+  GemmExtra ex;
+  memset(&ex, 0, sizeof(ex));
+  ex.rs_world = world;
+  ex.rs_rank = rank;
+  ex.rows_per_rank = M / world;
+  ex.rs_tile_inc = 1;
+  for (int r = 0; r < world; ++r) {
+    ex.rs_dst[r] = (__nv_bfloat16*)recv_bufs[r];
+    ex.rs_flag[r] = (uint32_t*)flags[r];
+  }
+  ex.wait_limit = (long long)(timeout_s * 1.9e9);
+  cudaStream_t s = (cudaStream_t)stream;
+  // ldc of the receive buffers is N
+  int rc = launch_gemm<128>(A, B, nullptr, nullptr, recv_bufs[rank], nullptr, M, N, K, 0, lda, ldb, 0, 0, N, status, 0, s, &ex);
+  if (rc) return rc;
+  const long long rows = M / world;
+  reduce_partials_kernel<<<128, 512, 0, s>>>((const __nv_bfloat16*)recv_bufs[rank], (const uint32_t*)flags[rank], flag_target,
+                                             world, (const __nv_bfloat16*)residual, (__nv_bfloat16*)out, rows, N, ex.wait_limit,
+                                             status);
+  return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
+}
+
+// all-gather -> GEMM. stage: local staging (world*rows, K) whose block `rank` already holds this
+// rank's shard; stages[r]: the same buffer of rank r (peer pointer); chunk_flags: [world] local
+// counters; ready[r] / pulled[r]: flag words of rank r. C (world*rows, N) = stage · B^T.
+extern "C" int kvb_allgather_gemm(void* stage, void* const* stages, const void* B, void* C, void* chunk_flags,
+                                  void* const* ready, void* const* pulled, int rank, int world, int rows, int N, int K,
+                                  long long ld_stage, long long ldb, long long ldc, unsigned epoch, unsigned chunk_target,
+                                  unsigned pulled_target, int copy_ctas, int* status, double timeout_s, void* stream) {
+  using namespace kvb;
+  if (world < 2 || world > 16 || rows % GEMM_BM || N % 8 || K % 8 || copy_ctas < 1) return KVB_ERR_ARG;
+  GemmExtra ex;
+  memset(&ex, 0, sizeof(ex));
+  ex.a_flags = (const uint32_t*)chunk_flags;
+  ex.ag_flags_w = (uint32_t*)chunk_flags;
+  ex.a_target = chunk_target;
+  ex.rows_per_chunk = rows;
+  ex.ag_copy_ctas = copy_ctas;
+  ex.ag_world = world;
+  ex.ag_rank = rank;
+  ex.ag_stage = (__nv_bfloat16*)stage;
+  ex.ag_ld = ld_stage;
+  ex.ag_epoch = epoch;
+  ex.ag_pulled_target = pulled_target;
+  for (int r = 0; r < world; ++r) {
+    ex.ag_src[r] = (const __nv_bfloat16*)stages[r] + (long long)r * rows * ld_stage;
+    ex.ag_ready[r] = (uint32_t*)ready[r];
+    ex.ag_pulled[r] = (uint32_t*)pulled[r];
+  }
+  ex.wait_limit = (long long)(timeout_s * 1.9e9);
+  const int M = world * rows;
+  return launch_gemm<128>(stage, B, nullptr, nullptr, C, nullptr, M, N, K, 0, ld_stage, ldb, 0, 0, ldc, status, 0,
+                          (cudaStream_t)stream, &ex);
 }

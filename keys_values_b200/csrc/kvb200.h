@@ -91,6 +91,16 @@ int kvb_allreduce_mean(void* const* bases, void* const* flags, int rank, int wor
                        float scale, unsigned epoch0, void* local_sync, int dtype, int n_ctas, int* status, double timeout_s,
                        void* stream);
 
+
+// ---- gemm_sm100.cu: GEMM fused with a collective over peer memory (tensor parallelism)
+int kvb_gemm_reduce_scatter(const void* A, const void* B, void* out, const void* residual, void* const* recv_bufs,
+                            void* const* flags, int rank, int world, int M, int N, int K, long long lda, long long ldb,
+                            unsigned flag_target, int* status, double timeout_s, void* stream);
+int kvb_allgather_gemm(void* stage, void* const* stages, const void* B, void* C, void* chunk_flags, void* const* ready,
+                       void* const* pulled, int rank, int world, int rows, int N, int K, long long ld_stage, long long ldb,
+                       long long ldc, unsigned epoch, unsigned chunk_target, unsigned pulled_target, int copy_ctas, int* status,
+                       double timeout_s, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
