@@ -104,5 +104,93 @@ def case_dp_train(rank, world, dev):
             torch.testing.assert_close(p.grad.float(), ref[n], atol=tol, rtol=tol, msg=lambda m: f"{n}: {m}")
 
 
+def case_tp_ops(rank, world, dev):
+    """Fused all-gather→GEMM and GEMM→reduce-scatter against NCCL + a library matmul."""
+    from keys_values_b200.ops import cuda as cu
+    from keys_values_b200.parallel.tp import TPContext
+
+    rows, K, N = 256, 512, 768
+    ctx = TPContext(world, rank, dev, max_rows=world * rows, max_features=1024, copy_ctas=4)
+    g = torch.Generator(device=dev).manual_seed(11 + rank)
+    for it in range(3):
+        # all-gather → GEMM
+        shard = torch.randn(rows, K, device=dev, dtype=torch.bfloat16, generator=g)
+        w = torch.randn(N, K, device=dev, dtype=torch.bfloat16, generator=g) * 0.05
+        ctx.stage_view(rows, K).copy_(shard)
+        out = ctx.allgather_gemm(rows, w)
+        full = [torch.empty_like(shard) for _ in range(world)]
+        dist.all_gather(full, shard)
+        ref = torch.cat(full).float() @ w.float().t()
+        torch.cuda.synchronize(dev)
+        cu.check_status(dev)
+        torch.testing.assert_close(out.float(), ref, atol=0.15, rtol=3e-2)
+        # GEMM → reduce-scatter (+ residual)
+        M = world * rows
+        x = torch.randn(M, K, device=dev, dtype=torch.bfloat16, generator=g)
+        w2 = torch.randn(N, K, device=dev, dtype=torch.bfloat16, generator=g) * 0.05
+        res = torch.randn(rows, N, device=dev, dtype=torch.bfloat16, generator=g)
+        out2 = ctx.gemm_reduce_scatter(x, w2, residual=res)
+        part = (x.float() @ w2.float().t()).to(torch.bfloat16).float()
+        dist.all_reduce(part, op=dist.ReduceOp.SUM)
+        ref2 = part[rank * rows : (rank + 1) * rows] + res.float()
+        torch.cuda.synchronize(dev)
+        cu.check_status(dev)
+        torch.testing.assert_close(out2.float(), ref2, atol=0.25, rtol=3e-2)
+    ctx.close()
+
+
+def case_tp_model(rank, world, dev):
+    """Tensor-parallel chunked forward with H2O caches equals the single-GPU forward."""
+    import dataclasses
+
+    from keys_values_b200.kvcache.factory import KVCacheFactory
+    from keys_values_b200.models.model import GPT
+    from keys_values_b200.ops import cuda as cu
+    from keys_values_b200.parallel.tp import TPContext, TPModel
+
+    torch.manual_seed(3)
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    with torch.device(dev):
+        gpt = GPT.from_name("tiny-qwen3")
+    torch.set_default_dtype(prev)
+    gpt.apply(gpt._init_weights)
+    cfg = gpt.config
+    T0, Tc, C = 256, 256, 512
+    ids = torch.randint(0, cfg.vocab_size, (1, T0 + 2 * Tc), device=dev)
+    dist.broadcast(ids, 0)
+    name = "lastrec-default"
+    # single GPU reference
+    gpt.assign_kv_caches(KVCacheFactory.create(gpt, name, 1, C, dtype=torch.bfloat16, device=dev))
+    gpt.max_seq_length = ids.shape[1]
+    with torch.no_grad():
+        gpt.reset()
+        refs = [gpt(ids[:, :T0], skip_lm_head=True)]
+        for s in range(T0, ids.shape[1], Tc):
+            refs.append(gpt(ids[:, s : s + Tc], skip_lm_head=True))
+    # tensor parallel
+    ctx = TPContext(world, rank, dev, max_rows=256, max_features=max(cfg.n_embd, cfg.intermediate_size), copy_ctas=4)
+
+    def make_cache(block_idx, g_local, h_local):
+        lc = dataclasses.replace(cfg, n_head=h_local, n_query_groups=g_local)
+        return KVCacheFactory.create_single(name, lc, 1, C, block_idx, device=dev, dtype=torch.bfloat16, cache_kwargs=dict(mha=gpt.mha))
+
+    tpm = TPModel(gpt, ctx, make_cache)
+    tpm.reset()
+    pos = 0
+    for ref_chunk, n in zip(refs, [T0, Tc, Tc]):
+        chunk_ids = ids[:, pos : pos + n]
+        x = gpt.embed(chunk_ids)[0]
+        rows = n // world
+        out = tpm.forward_hidden(x[rank * rows : (rank + 1) * rows].contiguous(), chunk_ids)
+        torch.cuda.synchronize(dev)
+        cu.check_status(dev)
+        want = ref_chunk[0, rank * rows : (rank + 1) * rows].float()
+        err = (out.float() - want).norm() / want.norm()
+        assert err < 5e-2, f"chunk at {pos}: relative error {err}"
+        pos += n
+    ctx.close()
+
+
 if __name__ == "__main__":
     main()

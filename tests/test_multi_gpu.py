@@ -49,3 +49,15 @@ def test_fused_allreduce_matches_nccl():
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_dp_gradients_match_on_gpus():
     _run("dp_train", 2)
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_tp_gemm_collectives_match_nccl():
+    _run("tp_ops", 2)
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tp_model_matches_single_gpu():
+    _run("tp_model", 2)
