@@ -178,6 +178,9 @@ class LongContextInferenceModel(GPTAndHeadModel):
         self.debug_single_cell_per_row = debug_single_cell_per_row
         self.chunk_sizes: Optional[List[int]] = None
         self.cells: Optional[List[ChunksForCell]] = None
+        # Context width for the position encoding; None = length of the batch being processed
+        # (generation sets it to prompt + new tokens before the prefill)
+        self.fixed_max_seq_length: Optional[int] = None
         self.layer_input_hook: Optional[LayerInputHook] = None
         self.cell_boundary_hook: Optional[CellBoundaryHook] = None
 
@@ -193,7 +196,7 @@ class LongContextInferenceModel(GPTAndHeadModel):
         if targets is not None and (targets.ndim != 2 or targets.shape[0] != input_ids.shape[0] or targets.shape[1] > seq_length):
             raise ValueError(f"targets.shape = {tuple(targets.shape)} not compatible with input_ids.shape = {tuple(input_ids.shape)}")
         # The position encoding (and for YaRN the SDPA scale) follows the batch length
-        gpt.max_seq_length = seq_length
+        gpt.max_seq_length = seq_length if self.fixed_max_seq_length is None else max(seq_length, self.fixed_max_seq_length)
         n_single = 0
         if self.single_tokens_for_targets and targets is not None:
             n_single = min(targets.shape[1], seq_length - 1)
