@@ -1,0 +1,370 @@
+"""Long-context fine-tuning driver (full weights or LoRA).
+
+``setup`` validates the arguments and launches one process per GPU; ``main`` builds model,
+caches, gradient model, optimizer and data; ``fit`` is the training loop: chunked forward,
+cell-wise backward, gradient all-reduce over ranks (overlapped with the backward), gradient
+clipping, optimizer step, logging, periodic validation and checkpoints with resumable
+training state. Parity: ``keys_values/finetune/longcontext_full.py:153-2008``.
+"""
+from __future__ import annotations
+
+import dataclasses
+import math
+import os
+import time
+from pathlib import Path
+from typing import Any, Dict, List, Optional, Union
+
+import torch
+import torch.distributed as dist
+
+from keys_values_b200.config import Config
+from keys_values_b200.data.base import DataModule
+from keys_values_b200.data.dataloader import CycleIterator
+from keys_values_b200.finetune import utils as fu
+from keys_values_b200.finetune.args import EvalArgs, GradientArgs, KVCacheArgs, LoRAArgs, OptimizerArgs, SDPAArgs, TrainArgs
+from keys_values_b200.finetune.batch_transform import BatchTransformFactory
+from keys_values_b200.finetune.resume_state import TrainingStateManager, find_resume_dir, restore_from_training_state
+from keys_values_b200.kvcache.consts import split_name
+from keys_values_b200.kvcache.factory import KVCacheFactory
+from keys_values_b200.kvcache.gradient.main import LongContextGradientModel
+from keys_values_b200.models.head_model import CrossEntropyOnLogits, HeadModelFactory
+from keys_values_b200.models.pos_encoding import position_encoding_factory
+from keys_values_b200.utils import get_default_supported_precision, message_memory_all_devices, num_parameters, str_to_torch_dtype
+
+
+@dataclasses.dataclass
+class TrainingStateVars:
+    iter_num: int = 0
+    step_count: int = 0
+    total_tokens: int = 0
+    train_time: float = 0.0
+    saved_dirs: List[str] = dataclasses.field(default_factory=list)
+
+
+def _dist_info():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+def setup(
+    checkpoint_dir: Union[str, Path],
+    out_dir: Union[str, Path] = Path("out/finetune/long-full"),
+    precision: Optional[str] = None,
+    devices: int = 1,
+    resume: Union[bool, str, Path] = False,
+    data: Optional[DataModule] = None,
+    train: TrainArgs = TrainArgs(),
+    eval: EvalArgs = EvalArgs(),
+    optimizer: OptimizerArgs = OptimizerArgs(),
+    kv_cache: KVCacheArgs = KVCacheArgs(),
+    grad: GradientArgs = GradientArgs(),
+    sdpa: SDPAArgs = SDPAArgs(),
+    lora: Optional[LoRAArgs] = None,
+    head_model: str = CrossEntropyOnLogits.NAME,
+    head_model_kwargs: Optional[Dict[str, Any]] = None,
+    logger_name: str = "csv",
+    seed: int = 1337,
+    yarn_rope: bool = True,
+    model_name: Optional[str] = None,
+    profile_grad_times: int = 0,
+    record_gpu_memory_snapshots: Optional[int] = None,
+) -> None:
+    """Entry point of ``finetune_long_full`` (and, with ``lora`` given, ``finetune_long_lora``).
+    ``checkpoint_dir`` holds ``lit_model.pth`` and ``model_config.yaml``; with ``model_name`` the
+    architecture is taken from the registry and weights are initialised randomly if no
+    ``lit_model.pth`` is present."""
+    from keys_values_b200.parallel.launch import launch
+
+    checkpoint_dir, out_dir = Path(checkpoint_dir), Path(out_dir)
+    if not HeadModelFactory.is_supported(head_model):
+        raise ValueError(f"head_model = {head_model} not supported")
+    split_name(kv_cache.name)  # validates the cache name
+    if devices < 1:
+        raise ValueError("devices must be >= 1")
+    precision = precision or get_default_supported_precision(training=True)
+    hparams = dict(checkpoint_dir=str(checkpoint_dir), out_dir=str(out_dir), precision=precision, devices=devices, train=train, eval=eval,
+                   optimizer=optimizer, kv_cache=kv_cache, grad=grad, sdpa=sdpa, lora=lora, head_model=head_model, seed=seed,
+                   yarn_rope=yarn_rope, model_name=model_name)
+    launch(main, devices, checkpoint_dir=checkpoint_dir, out_dir=out_dir, precision=precision, resume=resume, data=data, train=train,
+           eval=eval, optimizer=optimizer, kv_cache=kv_cache, grad=grad, lora=lora, head_model_name=head_model,
+           head_model_kwargs=head_model_kwargs or {}, logger_name=logger_name, seed=seed, yarn_rope=yarn_rope, model_name=model_name,
+           hparams=hparams, profile_grad_times=profile_grad_times, record_gpu_memory_snapshots=record_gpu_memory_snapshots)
+
+
+def create_gpt_model(checkpoint_dir: Path, model_name: Optional[str], lora: Optional[LoRAArgs], device, dtype, yarn_rope: bool):
+    from keys_values_b200.models import lora as lora_mod
+    from keys_values_b200.models.model import GPT
+
+    kwargs = lora.config_kwargs() if lora is not None else {}
+    cfg_cls = lora_mod.Config if lora is not None else Config
+    if (Path(checkpoint_dir) / "model_config.yaml").is_file():
+        config = cfg_cls.from_file(Path(checkpoint_dir) / "model_config.yaml", **kwargs)
+    elif model_name is not None:
+        config = cfg_cls.from_name(model_name, **kwargs)
+    else:
+        raise FileNotFoundError(f"{checkpoint_dir}/model_config.yaml not found and no model_name given")
+    pos = position_encoding_factory(config, do_yarn=yarn_rope, device=device)
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(dtype)
+    try:
+        with torch.device(device):
+            model = (lora_mod.GPT if lora is not None else GPT)(config, pos_encoding=pos)
+    finally:
+        torch.set_default_dtype(prev)
+    model.apply(model._init_weights)
+    if lora is not None:
+        lora_mod.mark_only_lora_as_trainable(model)
+    return config, model
+
+
+def wrap_gpt_model(gpt_model, head_model, kv_cache: KVCacheArgs, grad: GradientArgs, micro_batch_size: int, device, dtype,
+                   profile_steps: bool = False) -> LongContextGradientModel:
+    """Create the KV caches (optionally with host offload of the quantized storage), assign
+    them to the model, and wrap model + head into the gradient model."""
+    ck = kv_cache.resolved_cache_kwargs()
+    if kv_cache.cpu_offload:
+        caches, offloader = KVCacheFactory.create_cpu_offloading(gpt_model, kv_cache.name, micro_batch_size, kv_cache.cache_length,
+                                                                 device=device, dtype=dtype, cache_kwargs=ck)
+        gpt_model._kv_offloader = offloader
+    else:
+        caches = KVCacheFactory.create(gpt_model, kv_cache.name, micro_batch_size, kv_cache.cache_length, device=device, dtype=dtype,
+                                       cache_kwargs=ck)
+    gpt_model.assign_kv_caches(caches)
+    return LongContextGradientModel(
+        gpt_model, head_model, layers_per_cell=grad.layers_per_cell, chunk_size=kv_cache.chunk_size,
+        randomize_chunk_sizes=kv_cache.randomize_chunk_sizes, chunks_per_cell_multiplier=grad.chunks_per_cell_multiplier,
+        single_tokens_for_targets=grad.single_tokens_for_targets, offload_checkpoints=grad.offload_checkpoints,
+        pin_memory=grad.layercp_pin_memory, layercp_qname=grad.layercp_qname, cachecp_qname=grad.cachecp_qname,
+        save_attention_outputs=grad.save_attention_outputs, profile_steps=profile_steps,
+    )
+
+
+def main(rank: int, local_rank: int, world_size: int, *, checkpoint_dir, out_dir, precision, resume, data, train, eval, optimizer, kv_cache,
+         grad, lora, head_model_name, head_model_kwargs, logger_name, seed, yarn_rope, model_name, hparams, profile_grad_times,
+         record_gpu_memory_snapshots) -> None:
+    cuda = torch.cuda.is_available()
+    device = torch.device("cuda", local_rank) if cuda else torch.device("cpu")
+    if cuda:
+        torch.cuda.set_device(device)
+    dtype = str_to_torch_dtype(precision)
+    torch.manual_seed(seed)
+    out_dir = Path(out_dir)
+    if rank == 0:
+        out_dir.mkdir(parents=True, exist_ok=True)
+    logger = fu.choose_logger(logger_name, out_dir) if rank == 0 else None
+    config, gpt_model = create_gpt_model(checkpoint_dir, model_name, lora, device, dtype, yarn_rope)
+    head_model = HeadModelFactory.create(head_model_name, config, **head_model_kwargs).to(device)
+    resume_dir = find_resume_dir(out_dir, resume)
+    fu.load_model_checkpoint(gpt_model, checkpoint_dir, resume_dir, head_model)
+    model = wrap_gpt_model(gpt_model, head_model, kv_cache, grad, train.micro_batch_size, device, dtype, profile_steps=profile_grad_times > 0)
+    if rank == 0:
+        print(f"trainable parameters: {num_parameters(gpt_model, True):,} of {num_parameters(gpt_model):,}")
+    params = [p for p in gpt_model.parameters() if p.requires_grad] + [p for p in head_model.parameters() if p.requires_grad]
+    opt = optimizer.create(params)
+    # data
+    tokenizer = None
+    if (Path(checkpoint_dir) / "tokenizer.json").is_file() or (Path(checkpoint_dir) / "tokenizer.model").is_file():
+        from keys_values_b200.tokenizer import Tokenizer
+
+        tokenizer = Tokenizer(checkpoint_dir)
+    if data is None:
+        from keys_values_b200.data.module import SyntheticLongContext
+
+        data = SyntheticLongContext(config.vocab_size, seq_lengths=(4 * kv_cache.cache_length,), num_targets=kv_cache.chunk_size)
+    data.connect(tokenizer=tokenizer, batch_size=train.micro_batch_size, max_seq_length=train.max_seq_length, num_devices=world_size, rank=rank)
+    if rank == 0:
+        data.prepare_data()
+    if world_size > 1:
+        dist.barrier()
+    data.setup()
+    train_loader, val_loader = data.train_dataloader(), data.val_dataloader()
+    accum = train.gradient_accumulation_iters(world_size)
+    steps_per_epoch = max(1, len(train_loader) // accum)
+    max_steps = train.max_steps or (train.epochs or 1) * steps_per_epoch
+    warmup = min(max_steps, train.lr_warmup_steps or int((train.lr_warmup_fraction or 0.0) * max_steps))
+    scheduler = fu.get_lr_scheduler(opt, warmup_steps=warmup, max_steps=max_steps, min_lr=train.min_lr)
+    state = TrainingStateVars()
+    if resume_dir is not None:
+        st = restore_from_training_state(resume_dir, opt, scheduler, rank, world_size)
+        state.iter_num, state.step_count = st["iter_num"], st["step_count"]
+        if hasattr(train_loader, "load_state_dict"):
+            train_loader.load_state_dict(st.get("iterator", {}))
+    grad_reducer = None
+    if world_size > 1:
+        from keys_values_b200.parallel.dp import GradientReducer
+
+        grad_reducer = GradientReducer(params, world_size=world_size, rank=rank, device=device)
+        model.row_done_hook = grad_reducer.row_done_hook(gpt_model)
+    pad_id = getattr(tokenizer, "pad_id", None) or 0
+    batch_transform = BatchTransformFactory.from_head_model(head_model_name, pad_id=pad_id)
+    fit(model=model, optimizer=opt, scheduler=scheduler, train_loader=train_loader, val_loader=val_loader, batch_transform=batch_transform,
+        train=train, eval=eval, state=state, max_steps=max_steps, accum=accum, device=device, rank=rank, world_size=world_size,
+        grad_reducer=grad_reducer, logger=logger, out_dir=out_dir, checkpoint_dir=Path(checkpoint_dir), lora=lora is not None,
+        hparams=hparams, profile_grad_times=profile_grad_times, record_gpu_memory_snapshots=record_gpu_memory_snapshots)
+    if rank == 0:
+        final = out_dir / "final"
+        fu.save_model_checkpoint(gpt_model, head_model, final, lora=lora is not None)
+        fu.copy_config_files(Path(checkpoint_dir), final)
+        config.save(final / "model_config.yaml")
+        fu.save_hyperparameters(hparams, final)
+        print(message_memory_all_devices("memory: "))
+
+
+def _all_reduce_mean(x: torch.Tensor, world_size: int) -> torch.Tensor:
+    if world_size > 1:
+        dist.all_reduce(x, op=dist.ReduceOp.SUM)
+        x = x / world_size
+    return x
+
+
+@torch.no_grad()
+def validate(model: LongContextGradientModel, val_loader, batch_transform, device, max_iters: Optional[int]) -> torch.Tensor:
+    model.eval()
+    losses = []
+    for k, batch in enumerate(val_loader):
+        if max_iters is not None and k >= max_iters:
+            break
+        b = batch_transform(batch)
+        loss = model(b["input_ids"].to(device), b["targets"].to(device))
+        losses.append(loss.float().mean())
+    model.train()
+    return torch.stack(losses).mean() if losses else torch.tensor(float("nan"), device=device)
+
+
+def validate_and_all_reduce(model, val_loader, batch_transform, device, eval: EvalArgs, world_size: int) -> Dict[str, float]:
+    t0 = time.perf_counter()
+    val_loss = validate(model, val_loader, batch_transform, device, eval.max_iters)
+    val_loss = _all_reduce_mean(val_loss.to(device), world_size)
+    v = float(val_loss)
+    return {"val_loss": v, "val_ppl": math.exp(v) if v < 50 else float("inf"), "val_time": time.perf_counter() - t0}
+
+
+def save_checkpoint_regular(model: LongContextGradientModel, out_dir: Path, step: int, checkpoint_dir: Path, lora: bool, hparams, rank: int,
+                            state: TrainingStateVars, intermed_save_num: Optional[int]) -> Path:
+    step_dir = out_dir / f"step-{step:06d}"
+    if rank == 0:
+        fu.save_model_checkpoint(model.gpt_model, model.head_model, step_dir, lora=lora)
+        fu.copy_config_files(checkpoint_dir, step_dir)
+        model.gpt_model.config.save(step_dir / "model_config.yaml")
+        fu.save_hyperparameters(hparams, step_dir)
+        state.saved_dirs.append(str(step_dir))
+        if intermed_save_num is not None:
+            import shutil
+
+            while len(state.saved_dirs) > intermed_save_num:
+                shutil.rmtree(state.saved_dirs.pop(0), ignore_errors=True)
+    return step_dir
+
+
+def fit(*, model, optimizer, scheduler, train_loader, val_loader, batch_transform, train: TrainArgs, eval: EvalArgs, state: TrainingStateVars,
+        max_steps: int, accum: int, device, rank: int, world_size: int, grad_reducer, logger, out_dir: Path, checkpoint_dir: Path, lora: bool,
+        hparams, profile_grad_times: int = 0, record_gpu_memory_snapshots: Optional[int] = None) -> None:
+    ts_manager = TrainingStateManager(out_dir, rank, world_size)
+    train_iter = CycleIterator(train_loader)
+    if eval.initial_validation:
+        metrics = validate_and_all_reduce(model, val_loader, batch_transform, device, eval, world_size)
+        if rank == 0:
+            print(f"initial validation: {metrics}")
+            logger.log_dict(metrics, step=state.step_count)
+    recorder = None
+    if record_gpu_memory_snapshots:
+        from keys_values_b200.tools.gpu_memory import RecordGPUMemory
+
+        recorder = RecordGPUMemory(out_dir / "gpu_memory", max_entries=record_gpu_memory_snapshots)
+    if world_size > 1:
+        dist.barrier()
+    params = [p for g in optimizer.param_groups for p in g["params"]]
+    while state.step_count < max_steps:
+        t0 = time.perf_counter()
+        if grad_reducer is not None:
+            grad_reducer.begin_step()
+            grad_reducer.flat.zero_()
+        else:
+            optimizer.zero_grad(set_to_none=True)
+        step_loss = torch.zeros((), device=device)
+        step_tokens = 0
+        if recorder is not None:
+            recorder.start(f"step{state.step_count}")
+        for micro in range(accum):
+            batch = batch_transform(next(train_iter))
+            ids, targets = batch["input_ids"].to(device, non_blocking=True), batch["targets"].to(device, non_blocking=True)
+            # token-weighted averaging over ranks: weight this rank's loss by its share of target tokens
+            n_tok = (targets != -100).sum().float()
+            scale = 1.0 / accum
+            if world_size > 1:
+                mean_tok = _all_reduce_mean(n_tok.clone(), world_size)
+                scale = scale * float(n_tok / mean_tok.clamp(min=1))
+            if grad_reducer is not None and micro < accum - 1:
+                hook, model.row_done_hook = model.row_done_hook, None  # reduce only after the last micro-batch
+            loss = model(ids, targets, scale_factor=scale)
+            loss.backward()
+            if grad_reducer is not None and micro < accum - 1:
+                model.row_done_hook = hook
+            step_loss += loss.detach().float()
+            step_tokens += ids.numel()
+            state.iter_num += 1
+        if grad_reducer is not None:
+            grad_reducer.finish_step()
+        if recorder is not None:
+            recorder.stop()
+        if train.max_norm is not None:
+            torch.nn.utils.clip_grad_norm_([p for p in params if p.grad is not None], train.max_norm)
+        optimizer.step()
+        scheduler.step()
+        state.step_count += 1
+        step_loss = _all_reduce_mean(step_loss, world_size)
+        state.total_tokens += step_tokens * world_size
+        dt = time.perf_counter() - t0
+        state.train_time += dt
+        if rank == 0 and state.step_count % train.log_interval == 0:
+            metrics = {"loss": float(step_loss), "iter": state.iter_num, "step": state.step_count, "epoch": train_iter.epoch,
+                       "iter_time": dt, "tokens": step_tokens * world_size, "total_tokens": state.total_tokens,
+                       "tokens_per_sec": step_tokens * world_size / dt, "learning_rate": scheduler.get_last_lr()[0]}
+            logger.log_dict(metrics, step=state.step_count)
+            print(f"step {state.step_count}/{max_steps} | loss {metrics['loss']:.4f} | {dt:.1f} s | {metrics['tokens_per_sec']:.0f} tok/s")
+        if profile_grad_times and state.step_count >= profile_grad_times:
+            if rank == 0:
+                import csv
+
+                with open(out_dir / "profile_grad_times.csv", "w", newline="") as fp:
+                    recs = model.profile_records
+                    w = csv.DictWriter(fp, fieldnames=sorted({k for r in recs for k in r}))
+                    w.writeheader()
+                    w.writerows(recs)
+            return
+        if eval.interval and state.step_count % eval.interval == 0:
+            metrics = validate_and_all_reduce(model, val_loader, batch_transform, device, eval, world_size)
+            if rank == 0:
+                logger.log_dict(metrics, step=state.step_count)
+                print(f"validation: {metrics}")
+            if world_size > 1:
+                dist.barrier()
+        if train.save_interval and state.step_count % train.save_interval == 0:
+            step_dir = save_checkpoint_regular(model, out_dir, state.step_count, checkpoint_dir, lora, hparams, rank, state, train.intermed_save_num)
+            it_state = train_loader.state_dict() if hasattr(train_loader, "state_dict") else {}
+            ts_manager.save(step_dir, optimizer, scheduler, state.iter_num, state.step_count, None, it_state)
+            if world_size > 1:
+                dist.barrier()
+    if eval.final_validation:
+        metrics = validate_and_all_reduce(model, val_loader, batch_transform, device, eval, world_size)
+        if rank == 0:
+            logger.log_dict(metrics, step=state.step_count)
+            print(f"final validation: {metrics}")
+
+
+def inherit_cli_signature(fn, defaults: Optional[Dict[str, Any]] = None):
+    """Give a thin ``setup(**kwargs)`` variant the parameters of :func:`setup` (with other
+    defaults), so that the command line parser sees the same flags."""
+    import inspect
+
+    sig = inspect.signature(setup)
+    params = []
+    for name, p in sig.parameters.items():
+        if defaults and name in defaults:
+            p = p.replace(default=defaults[name])
+        params.append(p)
+    fn.__signature__ = sig.replace(parameters=params)
+    import typing
+
+    fn.__annotations__ = typing.get_type_hints(setup)
+    return fn

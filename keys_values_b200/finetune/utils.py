@@ -1,0 +1,166 @@
+"""Checkpoint I/O, LR schedule, loggers (``keys_values/finetune/utils.py:91-547``).
+
+Checkpoint format (LitGPT compatible): ``lit_model.pth`` = ``torch.save({"model": state_dict})``
+(a bare state dict is accepted when loading); LoRA runs write ``lit_model.lora.pth`` with the
+LoRA tensors only; heads with weights write ``head_model.pth``. A checkpoint directory also
+holds ``model_config.yaml``, tokenizer files, ``hyperparameters.yaml`` and the prompt style.
+"""
+from __future__ import annotations
+
+import csv
+import math
+import shutil
+import time
+from pathlib import Path
+from typing import Any, Dict, Optional
+
+import torch
+import yaml
+
+LIT_MODEL_FNAME = "lit_model.pth"
+LORA_WEIGHTS_FNAME = "lit_model.lora.pth"
+LORA_WEIGHTS_FNAME_OLD = "lit_model.pth.lora"
+HEAD_MODEL_FNAME = "head_model.pth"
+CONFIG_FILES = ("config.json", "generation_config.json", "model_config.yaml", "tokenizer.json", "tokenizer.model",
+                "tokenizer_config.json", "prompt_style.yaml")
+
+
+def get_lr_scheduler(optimizer, warmup_steps: int, max_steps: int, min_lr: float = 0.0):
+    """Linear warm-up for ``warmup_steps`` then cosine decay to ``min_lr`` at ``max_steps``."""
+    base_lrs = [g["lr"] for g in optimizer.param_groups]
+
+    def factor(step: int, base_lr: float) -> float:
+        if warmup_steps > 0 and step < warmup_steps:
+            return (step + 1) / warmup_steps
+        if max_steps <= warmup_steps:
+            return 1.0
+        progress = min(1.0, (step - warmup_steps) / (max_steps - warmup_steps))
+        cos = 0.5 * (1.0 + math.cos(math.pi * progress))
+        return (min_lr + (base_lr - min_lr) * cos) / base_lr
+
+    return torch.optim.lr_scheduler.LambdaLR(optimizer, [lambda s, b=b: factor(s, b) for b in base_lrs])
+
+
+def lora_state_dict(model: torch.nn.Module) -> Dict[str, torch.Tensor]:
+    from keys_values_b200.models.lora import lora_filter
+
+    return {k: v for k, v in model.state_dict().items() if lora_filter(k, v)}
+
+
+def save_model_checkpoint(gpt_model, head_model, out_dir: Path, lora: bool = False, rank: int = 0) -> None:
+    """Rank 0 writes ``lit_model.lora.pth`` (LoRA tensors only) or ``lit_model.pth``, and
+    ``head_model.pth`` if the head has weights."""
+    if rank != 0:
+        return
+    out_dir = Path(out_dir)
+    out_dir.mkdir(parents=True, exist_ok=True)
+    if lora:
+        torch.save({"model": lora_state_dict(gpt_model)}, out_dir / LORA_WEIGHTS_FNAME)
+    else:
+        torch.save({"model": gpt_model.state_dict()}, out_dir / LIT_MODEL_FNAME)
+    if head_model is not None and any(True for _ in head_model.parameters()):
+        torch.save({"model": head_model.state_dict()}, out_dir / HEAD_MODEL_FNAME)
+
+
+def _load_sd(path: Path) -> Dict[str, torch.Tensor]:
+    sd = torch.load(str(path), map_location="cpu", weights_only=True, mmap=True)
+    return sd.get("model", sd) if isinstance(sd, dict) else sd
+
+
+def load_model_checkpoint(gpt_model, checkpoint_dir: Path, resume_dir: Optional[Path] = None, head_model=None, strict: Optional[bool] = None) -> None:
+    """Base weights from ``checkpoint_dir/lit_model.pth`` (strict unless the model has LoRA
+    parameters), then LoRA / head weights from ``resume_dir`` (or ``checkpoint_dir``)."""
+    checkpoint_dir = Path(checkpoint_dir)
+    has_lora = any("lora_" in n for n, _ in gpt_model.named_parameters())
+    base = checkpoint_dir / LIT_MODEL_FNAME
+    if base.is_file() and base.stat().st_size > 0:
+        gpt_model.load_state_dict(_load_sd(base), strict=(not has_lora) if strict is None else strict)
+    for d in ([Path(resume_dir)] if resume_dir is not None else []) + [checkpoint_dir]:
+        for fname in (LORA_WEIGHTS_FNAME, LORA_WEIGHTS_FNAME_OLD):
+            if has_lora and (d / fname).is_file():
+                gpt_model.load_state_dict(_load_sd(d / fname), strict=False)
+                break
+        if head_model is not None and (d / HEAD_MODEL_FNAME).is_file():
+            head_model.load_state_dict(_load_sd(d / HEAD_MODEL_FNAME))
+        if resume_dir is not None:
+            break
+
+
+def copy_config_files(source_dir: Path, out_dir: Path) -> None:
+    out_dir.mkdir(parents=True, exist_ok=True)
+    for name in CONFIG_FILES:
+        if (Path(source_dir) / name).is_file():
+            shutil.copy(Path(source_dir) / name, out_dir / name)
+
+
+def save_hyperparameters(hparams: Dict[str, Any], out_dir: Path) -> None:
+    def clean(o):
+        if isinstance(o, dict):
+            return {k: clean(v) for k, v in o.items()}
+        if isinstance(o, (list, tuple)):
+            return [clean(v) for v in o]
+        if isinstance(o, (str, int, float, bool)) or o is None:
+            return o
+        if hasattr(o, "__dataclass_fields__"):
+            from dataclasses import asdict
+
+            return clean(asdict(o))
+        return str(o)
+
+    Path(out_dir).mkdir(parents=True, exist_ok=True)
+    with open(Path(out_dir) / "hyperparameters.yaml", "w") as fp:
+        yaml.safe_dump(clean(hparams), fp)
+
+
+def load_generation_config(checkpoint_dir: Path) -> Dict[str, Any]:
+    import json
+
+    p = Path(checkpoint_dir) / "generation_config.json"
+    return json.loads(p.read_text()) if p.is_file() else {}
+
+
+def adapt_requires_grad(model: torch.nn.Module, trainable_prefixes=None) -> None:
+    for n, p in model.named_parameters():
+        p.requires_grad = trainable_prefixes is None or any(n.startswith(pre) for pre in trainable_prefixes)
+
+
+class CSVLogger:
+    """Minimal metrics logger: one CSV row per ``log_dict`` call (default logger)."""
+
+    def __init__(self, out_dir: Path, name: str = "metrics.csv", flush_every: int = 1):
+        self.path = Path(out_dir) / "logs" / name
+        self.path.parent.mkdir(parents=True, exist_ok=True)
+        self.rows, self.keys = [], []
+
+    def log_dict(self, metrics: Dict[str, Any], step: Optional[int] = None) -> None:
+        row = dict(metrics, step=step, time=time.time())
+        self.rows.append(row)
+        new_keys = [k for k in row if k not in self.keys]
+        self.keys += new_keys
+        with self.path.open("w", newline="") as fp:
+            w = csv.DictWriter(fp, fieldnames=self.keys)
+            w.writeheader()
+            w.writerows(self.rows)
+
+
+def choose_logger(logger_name: str, out_dir: Path, name: str = "metrics", **kwargs):
+    """``csv`` (default) or ``tensorboard`` if it is installed; ``wandb``/``mlflow`` need their packages."""
+    if logger_name == "csv":
+        return CSVLogger(out_dir, name + ".csv")
+    if logger_name == "tensorboard":
+        from torch.utils.tensorboard import SummaryWriter
+
+        class _TB:
+            def __init__(self):
+                self.w = SummaryWriter(str(Path(out_dir) / "logs" / "tensorboard"))
+
+            def log_dict(self, metrics, step=None):
+                for k, v in metrics.items():
+                    if isinstance(v, (int, float)):
+                        self.w.add_scalar(k, v, step)
+
+        return _TB()
+    if logger_name in ("wandb", "mlflow"):
+        __import__(logger_name)
+        raise NotImplementedError(f"{logger_name} logger: package found but not wired in this build")
+    raise ValueError(f"`--logger_name={logger_name}` is not a valid option. Choose from 'csv', 'tensorboard', 'wandb', 'mlflow'.")

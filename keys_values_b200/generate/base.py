@@ -38,9 +38,8 @@ def sample(logits: torch.Tensor, temperature: float = 1.0, top_k: Optional[int] 
     if top_k is not None:
         v, i = torch.topk(logits, min(top_k, logits.size(-1)))
         logits = torch.full_like(logits, float("-inf")).scatter_(-1, i, v)
-    if temperature > 0.0 or top_p > 0.0:
-        if temperature > 0.0:
-            logits = logits / temperature
+    if temperature > 0.0 and top_k != 1:
+        logits = logits / temperature
         if top_p < 1.0:
             logits = sample_top_p(logits, top_p)
         probs = torch.nn.functional.softmax(logits.float(), dim=-1)

@@ -1,0 +1,185 @@
+"""Data pipeline, batch transform, CLI fine-tuning end to end (with resume), evaluation grid,
+metrics, RL helpers, tools."""
+import csv
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_similar_length_iterator_partitions_ranks_and_resumes():
+    from keys_values_b200.data.iterators import SimilarSequenceLengthIterator
+
+    lengths = [int(x) for x in torch.randint(10, 1000, (64,))]
+    its = [SimilarSequenceLengthIterator(lengths, 2, num_devices=2, rank=r, seed=3) for r in range(2)]
+    seen = set()
+    for b0, b1 in zip(its[0], its[1]):
+        assert len(b0) == len(b1) == 2 and not (set(b0) & set(b1))
+        group = [lengths[i] for i in b0 + b1]
+        # the global batch consists of neighbours in the length ordering
+        by_len = sorted(lengths, reverse=True)
+        assert any(sorted(group, reverse=True) == by_len[k : k + 4] for k in range(0, 64, 4))
+        seen.update(b0 + b1)
+    assert len(seen) == 64
+    it = SimilarSequenceLengthIterator(lengths, 2, seed=5)
+    first = [next(it) for _ in range(3)]
+    state = it.state_dict()
+    rest = [next(it) for _ in range(3)]
+    it2 = SimilarSequenceLengthIterator(lengths, 2, seed=5)
+    it2.load_state_dict(state)
+    assert [next(it2) for _ in range(3)] == rest
+
+
+def test_sft_batch_transform_left_pads_prompts():
+    from keys_values_b200.finetune.batch_transform import SFTBatchTransform
+
+    ids = torch.tensor([[5, 6, 7, 8, 9, 0, 0], [1, 2, 3, 4, 5, 6, 7]])
+    labels = torch.tensor([[-100, -100, 7, 8, 9, -100, -100], [-100, -100, -100, -100, 5, 6, 7]])
+    out = SFTBatchTransform(pad_id=0)({"input_ids": ids, "labels": labels})
+    # prompts of length 2 and 4 are right-aligned at position 4; targets start there
+    assert out["input_ids"].tolist() == [[0, 0, 5, 6, 7, 8], [1, 2, 3, 4, 5, 6]]
+    assert out["targets"].tolist() == [[7, 8, 9], [5, 6, 7]]
+
+
+def test_metrics_and_parser():
+    from keys_values_b200.evaluation.metrics import exact_match, multiple_choice_letter, ndcg_at_k, rouge_n_f1, sub_exact_match
+    from keys_values_b200.evaluation.response_parser import parse_answer
+
+    assert exact_match("The Eiffel Tower.", ["eiffel tower"]) == 1.0
+    assert sub_exact_match("It is the Eiffel Tower in Paris", ["Eiffel Tower"]) == 1.0
+    assert abs(rouge_n_f1("a b c d", ["a b x d"], 1) - 2 / 3) < 0.1
+    assert multiple_choice_letter("The correct answer is (C).", "C") == 1.0
+    assert ndcg_at_k(["d1", "d2"], {"d1": 1.0, "d2": 0.0}) == 1.0
+    assert parse_answer("blah\nAnswer: Paris\nmore") == "Paris"
+
+
+def test_lr_schedule_and_checkpoint_io(tmp_path):
+    from keys_values_b200.finetune import utils as fu
+    from keys_values_b200.models import lora as lora_mod
+
+    p = torch.nn.Parameter(torch.zeros(1))
+    opt = torch.optim.SGD([p], lr=1.0)
+    sched = fu.get_lr_scheduler(opt, warmup_steps=4, max_steps=12, min_lr=0.1)
+    lrs = []
+    for _ in range(12):
+        lrs.append(opt.param_groups[0]["lr"])
+        opt.step()
+        sched.step()
+    assert lrs[0] == pytest.approx(0.25) and lrs[3] == pytest.approx(1.0) and lrs[-1] < 0.2 and all(a >= b for a, b in zip(lrs[4:], lrs[5:]))
+    cfg = lora_mod.Config.from_name("tiny-gpt", lora_r=2, lora_query=True, lora_value=True)
+    m = lora_mod.GPT(cfg)
+    fu.save_model_checkpoint(m, None, tmp_path / "base", lora=False)
+    fu.save_model_checkpoint(m, None, tmp_path / "ft", lora=True)
+    sd = torch.load(tmp_path / "ft" / "lit_model.lora.pth", weights_only=True)["model"]
+    assert sd and all("lora_" in k for k in sd)
+    m2 = lora_mod.GPT(cfg)
+    fu.load_model_checkpoint(m2, tmp_path / "base", tmp_path / "ft")
+    for (n1, p1), (_, p2) in zip(m.named_parameters(), m2.named_parameters()):
+        assert torch.equal(p1, p2), n1
+    cfg.save(tmp_path / "model_config.yaml")
+    assert lora_mod.Config.from_file(tmp_path / "model_config.yaml").n_embd == cfg.n_embd
+
+
+def _run_cli(args, cwd):
+    env = dict(os.environ, PYTHONPATH=str(ROOT), CUDA_VISIBLE_DEVICES="")
+    return subprocess.run([sys.executable, "-m", "keys_values_b200", *args], cwd=cwd, env=env, capture_output=True, text=True, timeout=600)
+
+
+def test_cli_finetune_lora_then_resume_then_eval(tmp_path):
+    from keys_values_b200.config import Config
+
+    ckpt = tmp_path / "ckpt"
+    ckpt.mkdir()
+    Config.from_name("tiny-gpt").save(ckpt / "model_config.yaml")
+    out = tmp_path / "out"
+    common = [str(ckpt), "--out_dir", str(out), "--precision", "32-true", "--kv_cache.name", "h2o-torch-quantized8", "--kv_cache.cache_length", "64",
+              "--kv_cache.chunk_size", "16", "--lora.r", "4", "--train.global_batch_size", "1", "--train.micro_batch_size", "1",
+              "--train.save_interval", "2", "--train.lr_warmup_steps", "1", "--eval.interval", "2", "--eval.max_iters", "1", "--yarn_rope", "false"]
+    r = _run_cli(["finetune_long_lora", *common, "--train.max_steps", "2"], tmp_path)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert (out / "final" / "lit_model.lora.pth").is_file() and (out / "final" / "hyperparameters.yaml").is_file()
+    assert (out / "step-000002" / "training_state.pth").is_file()
+    rows = list(csv.DictReader(open(out / "logs" / "metrics.csv")))
+    assert any(r_.get("loss") for r_ in rows) and any(r_.get("val_loss") for r_ in rows)
+    r = _run_cli(["finetune_long_lora", *common, "--train.max_steps", "3", "--resume", "auto"], tmp_path)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "step 3/3" in r.stdout and "step 1/3" not in r.stdout
+
+
+def test_evaluation_lock_grid(tmp_path):
+    from keys_values_b200.evaluation.tasks import EvaluationTasks, EvaluationWithTasksHelper
+
+    tasks = EvaluationTasks(["h2o-default"], ["ck/final", "ck/step-000002"])
+    h = EvaluationWithTasksHelper(tmp_path)
+    t = list(tasks)[0]
+    lock = h.get_lock(t, 0)
+    assert lock is not None and h.get_lock(t, 0) is None
+    h.result_path(t, 0).write_text("task,loss\nx,1\n")
+    h.release(lock, True)
+    assert h.get_lock(t, 0) is None and h.pending(t, 3) == [1, 2]
+
+
+def test_logprobs_and_grpo_step():
+    from keys_values_b200.kvcache.factory import KVCacheFactory
+    from keys_values_b200.kvcache.gradient.main import LongContextGradientModel
+    from keys_values_b200.models import lora as lora_mod
+    from keys_values_b200.rl import GRPOLossHeadModel, compute_group_advantages, compute_logprobs, grpo_step
+
+    torch.manual_seed(0)
+    cfg = lora_mod.Config.from_name("tiny-gpt", lora_r=2, lora_query=True, lora_value=True)
+    m = lora_mod.GPT(cfg)
+    m.apply(m._init_weights)
+    lora_mod.mark_only_lora_as_trainable(m)
+    ids, tg = torch.randint(0, 512, (4, 100)), torch.randint(0, 512, (4, 24))
+    m.assign_kv_caches(KVCacheFactory.create(m, "dense-default", 4, 128, dtype=torch.float32))
+    lp = compute_logprobs(m, ids, tg, chunk_size=16)
+    caches = m.get_kv_caches()
+    m.clear_kv_caches()
+    with torch.no_grad():
+        logits = m(ids)[:, -24:]
+    m.assign_kv_caches(caches)
+    want = torch.gather(torch.log_softmax(logits.float(), -1), 2, tg.unsqueeze(-1)).squeeze(-1)
+    torch.testing.assert_close(lp, want, atol=1e-4, rtol=1e-4)
+    adv = compute_group_advantages(torch.tensor([1.0, 0.0, 2.0, 2.0]), 2, scale_rewards=False)
+    assert adv.tolist() == [0.5, -0.5, 0.0, 0.0]
+    head = GRPOLossHeadModel(cfg)
+    gm = LongContextGradientModel(m, head, layers_per_cell=1, chunk_size=16)
+    opt = torch.optim.SGD([p for p in m.parameters() if p.requires_grad], lr=0.1)
+    stats = grpo_step(gm, opt, ids, tg, torch.tensor([1.0, 0.0, 0.5, 2.0]), group_size=2)
+    assert all(map(lambda v: v == v, stats.values()))  # finite
+
+
+def test_tools_and_flat_vectors(tmp_path):
+    from keys_values_b200.models.model import GPT
+    from keys_values_b200.optimize import AccessWeightsGradients, ModelFromFlatVectorsFactory
+    from keys_values_b200.tools.size_log import SizeWeightsGradientsLog, WeightsTracker
+    from keys_values_b200.array_limit import TemporaryArrayLimit
+
+    m = GPT.from_name("tiny-gpt")
+    acc = AccessWeightsGradients(m)
+    flats = acc.get_weights()
+    assert sum(f.numel() for f in flats.values()) == sum(p.numel() for p in m.parameters())
+    m2 = GPT.from_name("tiny-gpt")
+    AccessWeightsGradients(m2).set_weights(flats)
+    assert all(torch.equal(a, b) for a, b in zip(m.parameters(), m2.parameters()))
+    fac = ModelFromFlatVectorsFactory(m, "cpu")
+    clones = fac.create("h0:1")
+    x = torch.randn(1, 4, 64)
+    y = clones[0][1](x, torch.zeros(1, 4, dtype=torch.long), m.mha)
+    y.sum().backward()
+    fac.return_gradients("h0:1", clones)
+    assert m.transformer.h[0].attn.qkv.weight.grad is not None and m.transformer.h[1].attn.qkv.weight.grad is None
+    tr = WeightsTracker(m, predicate=lambda n, p: "wte" in n)
+    assert tr.changed() == []
+    m.transformer.wte.weight.data[0, 0] += 1
+    assert tr.changed() == ["transformer.wte.weight"]
+    log = SizeWeightsGradientsLog(m, tmp_path / "sizes.csv", only_trainable=False)
+    assert log.log(0)["grad_norm"] > 0
+    lim = TemporaryArrayLimit(4.0)
+    assert lim() == 4.0 and lim.reduce() == 3.0 and lim.reduce() == 2.0
