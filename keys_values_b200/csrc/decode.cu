@@ -322,3 +322,49 @@ extern "C" int kvb_decode_attn(const void* q, const void* kq, const void* vq, co
   }
   return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
 }
+
+// ------------------------------------------------------------------------------------
+// Decode attention for callers that must not allocate.
+//
+// Some callers cannot hand this library a scratch buffer because they cannot create one
+// at the point of the call: code running while the CUDA caching allocator is frozen,
+// latency-critical serving loops that pre-plan every byte of device memory at start-up and
+// forbid cudaMalloc afterwards, or host runtimes in other languages that only link the C
+// symbols and have no tensor allocator at all. For them the workspace of the decode kernels
+// (raw scores, per-split partial results, log-sum-exp) lives in a fixed array inside this
+// library's device image. Every GPU that loads the library holds these
+// KVB_DECODE_STATIC_SCRATCH_BYTES until the process exits.
+//
+// Host code must never hand the array's name to a kernel: in host code the name is only a
+// stand-in for the symbol, not a device address. The device address is looked up with
+// cudaGetSymbolAddress, once per device, with that device current, and cached here.
+// ------------------------------------------------------------------------------------
+#define KVB_DECODE_STATIC_SCRATCH_BYTES (8u << 20)
+#define KVB_DECODE_STATIC_MAX_DEVICES 64
+
+static __device__ __align__(256) unsigned char kvb_decode_static_scratch[KVB_DECODE_STATIC_SCRATCH_BYTES];
+static void* kvb_decode_static_scratch_addr[KVB_DECODE_STATIC_MAX_DEVICES] = {nullptr};
+
+extern "C" long long kvb_decode_attn_noalloc_max_bytes(void) { return (long long)KVB_DECODE_STATIC_SCRATCH_BYTES; }
+
+extern "C" int kvb_decode_attn_noalloc(const void* q, const void* kq, const void* vq, const float* ks, const int32_t* kz,
+                                       const float* vs, const int32_t* vz, const void* k_new, const void* v_new,
+                                       const int32_t* new_slot, void* out, float* weights, int B, int H, int G, int L, int C,
+                                       int bits, float scale, void* stream) {
+  if (B <= 0 || H <= 0 || L <= 0) return KVB_ERR_ARG;
+  // workspace needed by this problem size; refuse what does not fit the fixed array
+  const long long need = kvb_decode_scratch_bytes(B, H, L);
+  if (need > (long long)KVB_DECODE_STATIC_SCRATCH_BYTES) return KVB_ERR_TOO_LARGE;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= KVB_DECODE_STATIC_MAX_DEVICES) return KVB_ERR_CUDA;
+  if (kvb_decode_static_scratch_addr[dev] == nullptr) {
+    // first call on this device: resolve the device address of the array (no allocation)
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress((void**)&ptr, kvb_decode_static_scratch) != cudaSuccess || ptr == nullptr) return KVB_ERR_CUDA;
+    kvb_decode_static_scratch_addr[dev] = ptr;
+  }
+  // Every word of the workspace that the kernels read (scores, partial max/sum/output,
+  // log-sum-exp) is written earlier in the same call, so nothing has to be cleared.
+  return kvb_decode_attn(q, kq, vq, ks, kz, vs, vz, k_new, v_new, new_slot, out, weights, kvb_decode_static_scratch_addr[dev], B, H,
+                         G, L, C, bits, scale, stream);
+}
