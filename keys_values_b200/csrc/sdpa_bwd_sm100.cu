@@ -450,7 +450,7 @@ static int bw_make_tmap_4d(CUtensorMap* tm, const void* ptr, uint64_t d0, uint64
 }  // namespace kvb
 
 extern "C" int kvb_att_tile_minmax(const int32_t* token_pos, int32_t* tmin, int32_t* tmax, int B, int G, int L, long long tp_sb,
-                                   long long tp_sg, void* stream);
+                                   long long tp_sg, int tile, void* stream);
 
 // scratch: tile_min | tile_max (B*G*nT int32 each) | delta (B*H*T fp32)
 extern "C" long long kvb_sdpa_bwd_scratch_bytes(int B, int H, int G, int q_len, int kv_len) {
@@ -493,7 +493,7 @@ extern "C" int kvb_sdpa_bwd(const void* q, const void* k, const void* v, const i
   if ((rc = bw_make_tmap_4d(&tmK, k, 128, kv_len, G, B, 128, k_sg, k_sb, 64, 128, 1))) return rc;
   if ((rc = bw_make_tmap_4d(&tmV, v, 128, kv_len, G, B, 128, k_sg, k_sb, 64, 128, 1))) return rc;
 
-  if ((rc = kvb_att_tile_minmax(token_pos, tmin, tmax, B, G, kv_len, tp_sb, tp_sg, stream))) return rc;
+  if ((rc = kvb_att_tile_minmax(token_pos, tmin, tmax, B, G, kv_len, tp_sb, tp_sg, 128, stream))) return rc;
   const long long rows = (long long)B * q_len * H;
   att_delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, delta, B, q_len, H);
   static bool attr_set = false;

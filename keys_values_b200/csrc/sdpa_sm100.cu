@@ -8,9 +8,11 @@
 // Design (bf16, head size 128):
 //   * CTA tile = 128 query rows = (128 / gs) consecutive positions x gs heads of one KV
 //     group (gs = H/G), so every K/V tile is loaded once per group, not once per head.
-//   * S = Q K^T and O += P V run on tcgen05.mma (M=128, N=128, K=16 steps) with S
-//     (double-buffered) and O in TMEM; K/V tiles of 128 slots arrive by TMA into 2-stage
+//   * S = Q K^T (M=128, N=64) and O += P V (M=128, N=128) run on tcgen05.mma with S
+//     (double-buffered) and O in TMEM; K/V tiles of 64 slots arrive by TMA into 2-stage
 //     rings (128B swizzle; no multicast). V is consumed as an MN-major B operand.
+//   * A CTA uses 112.5 KB of shared memory and 256 TMEM columns, so two CTAs share an SM:
+//     while one waits on its MMA -> softmax -> MMA chain the other one issues.
 //   * Two sweeps over the KV tiles: sweep 1 computes the exact row log-sum-exp (online
 //     max / sum), sweep 2 recomputes S, forms the already-normalised P = exp2(S·c − lse),
 //     accumulates O without any rescaling and takes the column sums of P. The column
@@ -20,10 +22,8 @@
 //   * KV tiles whose smallest token position lies beyond the last query of the CTA are
 //     skipped by every role; tiles that contain no position beyond the first query of
 //     the CTA take the mask-free path.
-//   * warp 0 = TMA producer, warp 1 = MMA issuer / TMEM owner, warps 2..9 = softmax +
-//     epilogue: two warps per TMEM sub-partition, each thread owns one query row (its TMEM
-//     lane) and one 64-column half of every tile, so that every SM sub-partition has two
-//     warps to interleave exp2 (MUFU) and ALU work.
+//   * warp 0 = TMA producer, warp 1 = MMA issuer / TMEM owner, warps 2..5 = softmax +
+//     epilogue: each thread owns one query row (its TMEM lane) of every tile.
 //
 // Replaces FlashInfer prefill + Triton score-sum + K/V reordering + query padding of the
 // reference (keys_values/attention/flashinfer_wrapper.py:51-273, :367-510,
@@ -40,20 +40,25 @@ int make_tmap_2d_bf16(CUtensorMap* tm, const void* ptr, uint64_t rows, uint64_t 
                       uint32_t box_cols);
 
 constexpr int ATT_BM = 128;   // query rows per CTA
-constexpr int ATT_BN = 128;   // KV slots per tile
+constexpr int ATT_BN = 64;    // KV slots per tile
 constexpr int ATT_D = 128;    // head size
-constexpr int ATT_THREADS = 320;  // TMA warp + MMA warp + 8 softmax warps
-constexpr int ATT_TILE_BYTES = 128 * 128 * 2;  // one 128x128 bf16 tile = two 64-column chunks of 16 KB
+constexpr int ATT_THREADS = 192;  // TMA warp + MMA warp + 4 softmax warps; two CTAs per SM
+constexpr int ATT_Q_BYTES = ATT_BM * ATT_D * 2;    // 32 KB: two 64-feature chunks of [128 rows x 128 B]
+constexpr int ATT_KV_BYTES = ATT_BN * ATT_D * 2;   // 16 KB: two 64-feature chunks of [64 rows x 128 B]
+constexpr int ATT_P_BYTES = ATT_BM * ATT_BN * 2;   // 16 KB: one 64-column chunk of [128 rows x 128 B]
+constexpr int ATT_TMEM_COLS = 256;                 // S0 | S1 (64 columns each) | O (128 columns)
 
+// Shared memory of one CTA: 112.5 KB, so that two CTAs fit into the 228 KB of an SM (each
+// CTA also costs 1 KB of system reserve). The dynamic shared memory window must be 1024-byte
+// aligned for the 128B-swizzled tiles; the kernel checks this and reports instead of running.
 struct AttSmem {
   static constexpr int Q = 0;
-  static constexpr int K = Q + ATT_TILE_BYTES;
-  static constexpr int V = K + 2 * ATT_TILE_BYTES;
-  static constexpr int P = V + 2 * ATT_TILE_BYTES;
-  static constexpr int TP = P + ATT_TILE_BYTES;   // 128 int32 token positions of the current tile
-  static constexpr int ML = TP + 512;             // (max, sum) of both column halves: 2 x 128 x 2 floats
-  static constexpr int BAR = ML + 2048;
-  static constexpr int TOTAL = BAR + 256 + 1024;
+  static constexpr int K = Q + ATT_Q_BYTES;
+  static constexpr int V = K + 2 * ATT_KV_BYTES;
+  static constexpr int P = V + 2 * ATT_KV_BYTES;
+  static constexpr int TP = P + ATT_P_BYTES;   // 64 int32 token positions of the current tile
+  static constexpr int BAR = TP + 256;
+  static constexpr int TOTAL = BAR + 256;
 };
 
 struct AttParams {
@@ -62,7 +67,7 @@ struct AttParams {
   const int32_t* tile_max;   // (B,G,nT)
   __nv_bfloat16* out;        // (B,T,H,D)
   float* lse;                // (B,H,T)
-  float* wpart;              // (B,G,2*nQT,L) or nullptr
+  float* wpart;              // (B,G,4*nQT,L) or nullptr
   int B, H, G, T, L, nT, nQT, gs, npos;
   long long tp_sb, tp_sg;
   float scale_log2;          // scale * log2(e)
@@ -72,10 +77,12 @@ struct AttParams {
 
 __global__ void att_tile_minmax_kernel(const int32_t* __restrict__ tp, int32_t* __restrict__ tmin, int32_t* __restrict__ tmax, int G,
                                        int L, int nT, long long tp_sb, long long tp_sg) {
+  // one block per tile; blockDim.x = tile size (64 or 128)
+  const int tile = blockDim.x;
   const int t = blockIdx.x % nT;
   const int bg = blockIdx.x / nT;
   const int b = bg / G, g = bg % G;
-  const int j = t * ATT_BN + threadIdx.x;
+  const int j = t * tile + threadIdx.x;
   int lo = INT_MAX, hi = INT_MIN;
   if (j < L) {
     const int v = tp ? tp[b * tp_sb + g * tp_sg + j] : j;
@@ -92,9 +99,11 @@ __global__ void att_tile_minmax_kernel(const int32_t* __restrict__ tp, int32_t* 
   }
   __syncthreads();
   if (threadIdx.x == 0) {
-    lo = min(min(slo[0], slo[1]), min(slo[2], slo[3]));
-    hi = max(max(shi[0], shi[1]), max(shi[2], shi[3]));
-    if ((t + 1) * ATT_BN > L) hi = INT_MAX;  // ragged last tile always takes the masked path
+    for (int w = 1; w < tile / 32; ++w) {
+      lo = min(lo, slo[w]);
+      hi = max(hi, shi[w]);
+    }
+    if ((t + 1) * tile > L) hi = INT_MAX;  // ragged last tile always takes the masked path
     tmin[blockIdx.x] = lo;
     tmax[blockIdx.x] = hi;
   }
@@ -117,11 +126,15 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-__global__ void __launch_bounds__(ATT_THREADS, 1)
+__global__ void __launch_bounds__(ATT_THREADS, 2)
 sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const AttParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if (smem_u32(smem) & 1023u) {  // swizzled tiles need a 1024-byte aligned window: report, do not run
+    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, STATUS_TIMEOUT_MISC);
+    return;
+  }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + AttSmem::BAR);
   uint64_t* q_full = bars + 0;
   uint64_t* k_full = bars + 1;   // [2]
@@ -137,7 +150,6 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int32_t* tp_s = reinterpret_cast<int32_t*>(smem + AttSmem::TP);
-  float* ml_s = reinterpret_cast<float*>(smem + AttSmem::ML);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // block -> (query tile, group, batch); query tiles fastest so that co-resident CTAs share K/V in L2
@@ -158,25 +170,25 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(&v_full[s], 1);
       mbar_init(&v_empty[s], 1);
       mbar_init(&s_full[s], 1);
-      mbar_init(&s_empty[s], 8);
+      mbar_init(&s_empty[s], 4);
     }
-    mbar_init(p_full, 8);
+    mbar_init(p_full, 4);
     mbar_init(p_empty, 1);
     mbar_init(o_full, 1);
-    mbar_init(grp_bar, 256);
+    mbar_init(grp_bar, 128);
     *abort_flag = 0;
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 512);
+    tmem_alloc(tmem_slot, ATT_TMEM_COLS);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_S0 = tmem_base;          // S buffers: columns [0,128) and [128,256)
-  const uint32_t tmem_O = tmem_base + 256;     // O: columns [256,384)
+  const uint32_t tmem_S0 = tmem_base;          // S buffers: columns [0,64) and [64,128)
+  const uint32_t tmem_O = tmem_base + 128;     // O: columns [128,256)
 
   int n_active = 0;
   for (int t = 0; t < p.nT; ++t) n_active += (tmin[t] <= qpos_max);
@@ -187,9 +199,9 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tma_prefetch_desc(&tmQ);
       tma_prefetch_desc(&tmK);
       tma_prefetch_desc(&tmV);
-      mbar_expect_tx(q_full, ATT_TILE_BYTES);
+      mbar_expect_tx(q_full, ATT_Q_BYTES);
       tma_load_4d(smem + AttSmem::Q, &tmQ, q_full, 0, t0, g * p.gs, b);
-      tma_load_4d(smem + AttSmem::Q + ATT_TILE_BYTES / 2, &tmQ, q_full, 64, t0, g * p.gs, b);
+      tma_load_4d(smem + AttSmem::Q + ATT_Q_BYTES / 2, &tmQ, q_full, 64, t0, g * p.gs, b);
       uint32_t i = 0, j = 0;
       bool ok = true;
       for (int sweep = 0; sweep < 2 && ok; ++sweep) {
@@ -197,18 +209,18 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           if (tmin[t] > qpos_max) continue;
           const int ks = i & 1;
           if (!mbar_wait_bounded(&k_empty[ks], ((i >> 1) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) { ok = false; break; }
-          uint8_t* kd = smem + AttSmem::K + ks * ATT_TILE_BYTES;
-          mbar_expect_tx(&k_full[ks], ATT_TILE_BYTES);
+          uint8_t* kd = smem + AttSmem::K + ks * ATT_KV_BYTES;
+          mbar_expect_tx(&k_full[ks], ATT_KV_BYTES);
           tma_load_4d(kd, &tmK, &k_full[ks], 0, t * ATT_BN, g, b);
-          tma_load_4d(kd + ATT_TILE_BYTES / 2, &tmK, &k_full[ks], 64, t * ATT_BN, g, b);
+          tma_load_4d(kd + ATT_KV_BYTES / 2, &tmK, &k_full[ks], 64, t * ATT_BN, g, b);
           ++i;
           if (sweep == 1) {
             const int vs = j & 1;
             if (!mbar_wait_bounded(&v_empty[vs], ((j >> 1) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) { ok = false; break; }
-            uint8_t* vd = smem + AttSmem::V + vs * ATT_TILE_BYTES;
-            mbar_expect_tx(&v_full[vs], ATT_TILE_BYTES);
+            uint8_t* vd = smem + AttSmem::V + vs * ATT_KV_BYTES;
+            mbar_expect_tx(&v_full[vs], ATT_KV_BYTES);
             tma_load_4d(vd, &tmV, &v_full[vs], 0, t * ATT_BN, g, b);
-            tma_load_4d(vd + ATT_TILE_BYTES / 2, &tmV, &v_full[vs], 64, t * ATT_BN, g, b);
+            tma_load_4d(vd + ATT_KV_BYTES / 2, &tmV, &v_full[vs], 64, t * ATT_BN, g, b);
             ++j;
           }
         }
@@ -233,12 +245,14 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!mbar_wait_bounded(&k_full[ks], (i >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL)) return false;
         if (!mbar_wait_bounded(&s_empty[ks], ((i >> 1) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) return false;
         tc_fence_after();
-        const uint32_t k_addr = smem_u32(smem + AttSmem::K + ks * ATT_TILE_BYTES);
+        const uint32_t k_addr = smem_u32(smem + AttSmem::K + ks * ATT_KV_BYTES);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t off = (uint32_t)((kk >> 2) * (ATT_TILE_BYTES / 2) + (kk & 3) * 32);
-          umma_f16_ss(tmem_S0 + (uint32_t)(ks * ATT_BN), make_smem_desc_sw128(q_addr + off, 16, 1024),
-                      make_smem_desc_sw128(k_addr + off, 16, 1024), idesc_qk, kk != 0);
+          // 16 features per step: chunk kk/4 of the operand, 32 bytes per step inside the swizzled row
+          const uint32_t q_off = (uint32_t)((kk >> 2) * (ATT_Q_BYTES / 2) + (kk & 3) * 32);
+          const uint32_t k_off = (uint32_t)((kk >> 2) * (ATT_KV_BYTES / 2) + (kk & 3) * 32);
+          umma_f16_ss(tmem_S0 + (uint32_t)(ks * ATT_BN), make_smem_desc_sw128(q_addr + q_off, 16, 1024),
+                      make_smem_desc_sw128(k_addr + k_off, 16, 1024), idesc_qk, kk != 0);
         }
         umma_commit(&k_empty[ks]);
         umma_commit(&s_full[ks]);
@@ -250,15 +264,15 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!mbar_wait_bounded(p_full, j & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL)) return false;
         if (!mbar_wait_bounded(&v_full[vs], (j >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL)) return false;
         tc_fence_after();
-        const uint32_t v_addr = smem_u32(smem + AttSmem::V + vs * ATT_TILE_BYTES);
+        const uint32_t v_addr = smem_u32(smem + AttSmem::V + vs * ATT_KV_BYTES);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          // A = P: K-major, 16 kv columns per step inside a 64-column chunk
-          const uint32_t a_off = (uint32_t)((kk >> 2) * (ATT_TILE_BYTES / 2) + (kk & 3) * 32);
+        for (int kk = 0; kk < ATT_BN / 16; ++kk) {
+          // A = P: K-major, 16 kv columns (32 B) per step inside the single 64-column chunk
+          const uint32_t a_off = (uint32_t)(kk * 32);
           // B = V: MN-major; 16 kv rows per step (2048 B); the two 64-wide d chunks are LBO apart
           const uint32_t b_off = (uint32_t)(kk * 16 * 128);
           umma_f16_ss(tmem_O, make_smem_desc_sw128(p_addr + a_off, 16, 1024),
-                      make_smem_desc_sw128(v_addr + b_off, ATT_TILE_BYTES / 2, 1024), idesc_pv, (j | kk) != 0);
+                      make_smem_desc_sw128(v_addr + b_off, ATT_KV_BYTES / 2, 1024), idesc_pv, (j | kk) != 0);
         }
         umma_commit(&v_empty[vs]);
         umma_commit(p_empty);
@@ -283,18 +297,16 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else {
     // ------------------------------------------------- softmax + epilogue warps
-    // 8 warps: two per TMEM sub-partition. Thread (row, half) owns columns
-    // [64·half, 64·half + 64) of its row in every S / P / O tile.
+    // 4 warps, one query row (TMEM lane) per thread, 64 columns per KV tile. A second CTA on the
+    // same SM runs its own chain, which is what keeps MUFU / ALU / tensor pipes busy.
     const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;
     const int row = quarter * 32 + lane;          // TMEM lane = query row of the tile
     const int hq = row / p.npos;                  // head within the group
     const int pl = row % p.npos;                  // position within the tile
     const int tq = t0 + pl;
     const bool row_valid = tq < p.T;
     const int my_pos = p.input_pos + tq;
-    const int sm_tid = threadIdx.x - 64;          // 0..255
-    const int cbeg = half * 64;
+    const int sm_tid = threadIdx.x - 64;          // 0..127
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     const float c = p.scale_log2;
     bool ok = n_active > 0;
@@ -319,15 +331,16 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (sm_tid < ATT_BN) tp_s[sm_tid] = v;
       return group_sync();
     };
-    // column-sum partials: slot (2·qt + row half) of wpart (B,G,2·nQT,L); thread -> (column, row half)
-    const int cs_col = sm_tid & 127, cs_rh = sm_tid >> 7;
-    float* wbase = p.wpart ? p.wpart + ((((long long)b * p.G + g) * (2 * p.nQT) + 2 * qt + cs_rh) * p.L) : nullptr;
+    // column-sum partials: slot (4·qt + warp quarter) of wpart (B,G,4·nQT,L). A warp sums the 32
+    // rows that it wrote itself, so the column sums need no barrier among the warps; lane ->
+    // columns (2·lane, 2·lane + 1) of the tile.
+    float* wbase = p.wpart ? p.wpart + ((((long long)b * p.G + g) * (4 * p.nQT) + 4 * qt + quarter) * p.L) : nullptr;
     if (n_active == 0 && wbase) {
-      for (int t = 0; t < p.nT; ++t)
-        if (t * ATT_BN + cs_col < p.L) wbase[(long long)t * ATT_BN + cs_col] = 0.f;
+      for (int jj = lane; jj < p.L; jj += 32) wbase[jj] = 0.f;
     }
+    const uint32_t NEG_INF_BITS = 0xff800000u;
 
-    // ---- sweep 1: exact row max and sum (each half over its own columns)
+    // ---- sweep 1: exact row max and sum
     for (int t = 0; t < p.nT && ok; ++t) {
       if (tmin[t] > qpos_max) continue;
       const int sb = i & 1;
@@ -335,110 +348,111 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (masked && !load_tile_tp(t)) { ok = false; break; }
       if (!mbar_wait_bounded(&s_full[sb], (i >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
-#pragma unroll 1
-      for (int c0 = cbeg; c0 < cbeg + 64; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(tmem_S0 + lane_base + (uint32_t)(sb * ATT_BN + c0), r);
-        tmem_ld_wait();
-        float x[32];
-        float cmax = -INFINITY;
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          float sv = __uint_as_float(r[e]) * c;
-          if (masked && tp_s[c0 + e] > my_pos) sv = -INFINITY;
-          x[e] = sv;
-          cmax = fmaxf(cmax, sv);
-        }
-        const float m_new = fmaxf(m, cmax);
-        float sum = 0.f;
-#pragma unroll
-        for (int e = 0; e < 32; ++e) sum += fast_exp2(x[e] - m_new);
-        l = l * fast_exp2(m - m_new) + sum;
-        m = m_new;
-      }
+      uint32_t r[ATT_BN];
+      tmem_ld_32x32b_x32(tmem_S0 + lane_base + (uint32_t)(sb * ATT_BN), r);
+      tmem_ld_32x32b_x32(tmem_S0 + lane_base + (uint32_t)(sb * ATT_BN + 32), r + 32);
+      tmem_ld_wait();
+      // the tile is in registers: hand the S buffer back before the arithmetic
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[sb]);
       ++i;
-    }
-    // merge the two halves of every row
-    float lse2 = INFINITY;
-    if (ok) {
-      ml_s[(half * ATT_BM + row) * 2] = m;
-      ml_s[(half * ATT_BM + row) * 2 + 1] = l;
-      if (!group_sync()) ok = false;
-      if (ok) {
-        const float m2 = ml_s[((half ^ 1) * ATT_BM + row) * 2], l2 = ml_s[((half ^ 1) * ATT_BM + row) * 2 + 1];
-        const float mm = fmaxf(m, m2);
-        const float ll = l * fast_exp2(m - mm) + l2 * fast_exp2(m2 - mm);
-        lse2 = ll > 0.f ? mm + log2f(ll) : INFINITY;
+      if (masked) {
+#pragma unroll
+        for (int e = 0; e < ATT_BN; ++e)
+          if (tp_s[e] > my_pos) r[e] = NEG_INF_BITS;
       }
+      // max of the raw scores (the scale is positive), four independent chains
+      float a0 = __uint_as_float(r[0]), a1 = __uint_as_float(r[1]), a2 = __uint_as_float(r[2]), a3 = __uint_as_float(r[3]);
+#pragma unroll
+      for (int e = 4; e < ATT_BN; e += 4) {
+        a0 = fmaxf(a0, __uint_as_float(r[e]));
+        a1 = fmaxf(a1, __uint_as_float(r[e + 1]));
+        a2 = fmaxf(a2, __uint_as_float(r[e + 2]));
+        a3 = fmaxf(a3, __uint_as_float(r[e + 3]));
+      }
+      const float m_new = fmaxf(m, fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)) * c);
+      const float neg_m = -m_new;
+      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+      for (int e = 0; e < ATT_BN; e += 4) {
+        s0 += fast_exp2(fmaf(__uint_as_float(r[e]), c, neg_m));
+        s1 += fast_exp2(fmaf(__uint_as_float(r[e + 1]), c, neg_m));
+        s2 += fast_exp2(fmaf(__uint_as_float(r[e + 2]), c, neg_m));
+        s3 += fast_exp2(fmaf(__uint_as_float(r[e + 3]), c, neg_m));
+      }
+      l = l * fast_exp2(m - m_new) + ((s0 + s1) + (s2 + s3));
+      m = m_new;
     }
+    const float lse2 = l > 0.f ? m + log2f(l) : INFINITY;
+    const float neg_lse2 = -lse2;
 
     // ---- sweep 2: P = exp2(S·c − lse), O += P V, column sums of P
     uint8_t* Ps = smem + AttSmem::P;
     for (int t = 0; t < p.nT && ok; ++t) {
       float* wdst = wbase ? wbase + (long long)t * ATT_BN : nullptr;
       if (tmin[t] > qpos_max) {
-        if (wdst && t * ATT_BN + cs_col < p.L) wdst[cs_col] = 0.f;
+        if (wdst) {
+          if (t * ATT_BN + 2 * lane < p.L) wdst[2 * lane] = 0.f;
+          if (t * ATT_BN + 2 * lane + 1 < p.L) wdst[2 * lane + 1] = 0.f;
+        }
         continue;
       }
       const int sb = i & 1;
       const bool masked = tmax[t] > qpos_min;
       if (masked && !load_tile_tp(t)) { ok = false; break; }
       if (!mbar_wait_bounded(&s_full[sb], (i >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t r[ATT_BN];
+      tmem_ld_32x32b_x32(tmem_S0 + lane_base + (uint32_t)(sb * ATT_BN), r);
+      tmem_ld_32x32b_x32(tmem_S0 + lane_base + (uint32_t)(sb * ATT_BN + 32), r + 32);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[sb]);
+      ++i;
+      if (masked) {
+#pragma unroll
+        for (int e = 0; e < ATT_BN; ++e)
+          if (tp_s[e] > my_pos) r[e] = NEG_INF_BITS;
+      }
+      uint32_t pk[ATT_BN / 2];
+#pragma unroll
+      for (int e = 0; e < ATT_BN; e += 2) {
+        float p0 = fast_exp2(fmaf(__uint_as_float(r[e]), c, neg_lse2));
+        float p1 = fast_exp2(fmaf(__uint_as_float(r[e + 1]), c, neg_lse2));
+        if (!row_valid) p0 = p1 = 0.f;
+        pk[e >> 1] = pack_bf16x2(p0, p1);
+      }
       // the PV MMA of the previous tile must have finished reading P
       if (!mbar_wait_bounded(p_empty, (j & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_MISC)) { ok = false; break; }
-      tc_fence_after();
-      uint8_t* chunk = Ps + half * (ATT_TILE_BYTES / 2);  // this half's 64 columns = one 64-wide swizzled chunk
-#pragma unroll 1
-      for (int c0 = cbeg; c0 < cbeg + 64; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(tmem_S0 + lane_base + (uint32_t)(sb * ATT_BN + c0), r);
-        tmem_ld_wait();
-        uint32_t pk[16];
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float s0 = __uint_as_float(r[e]) * c - lse2;
-          float s1 = __uint_as_float(r[e + 1]) * c - lse2;
-          float p0 = fast_exp2(s0), p1 = fast_exp2(s1);
-          if (masked) {
-            if (tp_s[c0 + e] > my_pos) p0 = 0.f;
-            if (tp_s[c0 + e + 1] > my_pos) p1 = 0.f;
-          }
-          if (!row_valid) p0 = p1 = 0.f;
-          pk[e >> 1] = pack_bf16x2(p0, p1);
-        }
-        const int u0 = (c0 & 63) >> 3;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          uint4 val = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
-          *reinterpret_cast<uint4*>(chunk + sw128_offset(row, u0 + u)) = val;
-        }
+      for (int u = 0; u < ATT_BN / 8; ++u) {
+        uint4 val = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
+        *reinterpret_cast<uint4*>(Ps + sw128_offset(row, u)) = val;
       }
-      tc_fence_before();
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&s_empty[sb]);
-        mbar_arrive(p_full);
-      }
-      ++i;
-      // column sums of the P tile (as rounded to bf16): thread -> (column, half of the rows)
-      if (wdst) {
-        if (!mbar_wait_bounded(p_full, j & 1, abort_flag, p.status, STATUS_TIMEOUT_MISC)) { ok = false; break; }
-        const uint8_t* cchunk = Ps + (cs_col >> 6) * (ATT_TILE_BYTES / 2);
-        const int cu = (cs_col & 63) >> 3, ce = (cs_col & 7) * 2;
-        float cs = 0.f;
-#pragma unroll 8
-        for (int rr = cs_rh * 64; rr < cs_rh * 64 + 64; ++rr) {
-          const __nv_bfloat16 hv = *reinterpret_cast<const __nv_bfloat16*>(cchunk + sw128_offset(rr, cu) + ce);
-          cs += __bfloat162float(hv);
-        }
-        if (t * ATT_BN + cs_col < p.L) wdst[cs_col] = cs;
-        if (!group_sync()) { ok = false; break; }  // all column reads done before P is overwritten
-      }
+      if (lane == 0) mbar_arrive(p_full);
       ++j;
+      // column sums over this warp's 32 rows of the P tile (as rounded to bf16)
+      if (wdst) {
+        float c0a = 0.f, c1a = 0.f, c0b = 0.f, c1b = 0.f;
+        const uint32_t coff = (uint32_t)((lane & 3) * 4);
+        const int cu = lane >> 2;
+#pragma unroll 8
+        for (int rr = 0; rr < 32; rr += 2) {
+          const uint32_t w0 = *reinterpret_cast<const uint32_t*>(Ps + sw128_offset(quarter * 32 + rr, cu) + coff);
+          const uint32_t w1 = *reinterpret_cast<const uint32_t*>(Ps + sw128_offset(quarter * 32 + rr + 1, cu) + coff);
+          c0a += __uint_as_float(w0 << 16);
+          c1a += __uint_as_float(w0 & 0xffff0000u);
+          c0b += __uint_as_float(w1 << 16);
+          c1b += __uint_as_float(w1 & 0xffff0000u);
+        }
+        if (t * ATT_BN + 2 * lane < p.L) wdst[2 * lane] = c0a + c0b;
+        if (t * ATT_BN + 2 * lane + 1 < p.L) wdst[2 * lane + 1] = c1a + c1b;
+        __syncwarp();  // all lanes have read the warp's rows before the next tile overwrites them
+      }
     }
 
     // ---- epilogue: O (already normalised) -> bf16 -> out; lse
@@ -447,7 +461,7 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_after();
       __nv_bfloat16* dst = p.out + (((long long)b * p.T + tq) * p.H + (g * p.gs + hq)) * ATT_D;
 #pragma unroll 1
-      for (int c0 = cbeg; c0 < cbeg + 64; c0 += 32) {
+      for (int c0 = 0; c0 < ATT_D; c0 += 32) {
         uint32_t r[32];
         if (n_active > 0) {
           tmem_ld_32x32b_x32(tmem_O + lane_base + (uint32_t)c0, r);
@@ -468,14 +482,14 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           }
         }
       }
-      if (half == 0 && row_valid && p.lse) p.lse[((long long)b * p.H + (g * p.gs + hq)) * p.T + tq] = lse2 * 0.6931471805599453f;
+      if (row_valid && p.lse) p.lse[((long long)b * p.H + (g * p.gs + hq)) * p.T + tq] = lse2 * 0.6931471805599453f;
     }
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    tmem_dealloc(tmem_base, ATT_TMEM_COLS);
   }
 }
 
@@ -505,24 +519,25 @@ static int make_tmap_4d_bf16(CUtensorMap* tm, const void* ptr, uint64_t d0, uint
 
 }  // namespace kvb
 
-// Per-tile min/max of the token positions (tiles of 128 slots): (B,G,nT) each.
+// Per-tile min/max of the token positions for tiles of `tile` slots (64 or 128): (B,G,nT) each.
 extern "C" int kvb_att_tile_minmax(const int32_t* token_pos, int32_t* tmin, int32_t* tmax, int B, int G, int L, long long tp_sb,
-                                   long long tp_sg, void* stream) {
-  const int nT = (L + kvb::ATT_BN - 1) / kvb::ATT_BN;
-  kvb::att_tile_minmax_kernel<<<B * G * nT, 128, 0, (cudaStream_t)stream>>>(token_pos, tmin, tmax, G, L, nT, tp_sb, tp_sg);
+                                   long long tp_sg, int tile, void* stream) {
+  if (tile != 64 && tile != 128) return KVB_ERR_ARG;
+  const int nT = (L + tile - 1) / tile;
+  kvb::att_tile_minmax_kernel<<<B * G * nT, tile, 0, (cudaStream_t)stream>>>(token_pos, tmin, tmax, G, L, nT, tp_sb, tp_sg);
   return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
 }
 
 // Scratch layout (int32 words), provided by the caller:
-//   tile_min (B*G*nT) | tile_max (B*G*nT) | wpart (B*G*2*nQT*L floats, only if weights != NULL)
+//   tile_min (B*G*nT) | tile_max (B*G*nT) | wpart (B*G*4*nQT*L floats, only if weights != NULL)
 extern "C" long long kvb_sdpa_fwd_scratch_bytes(int B, int H, int G, int q_len, int kv_len, int want_weights) {
   if (G <= 0 || H % G) return -1;
   const int gs = H / G;
-  const long long nT = (kv_len + 127) / 128;
+  const long long nT = (kv_len + kvb::ATT_BN - 1) / kvb::ATT_BN;
   const long long npos = 128 / gs;
   const long long nQT = (q_len + npos - 1) / npos;
   long long words = 2LL * B * G * nT;
-  if (want_weights) words += 2LL * B * G * nQT * kv_len;
+  if (want_weights) words += 4LL * B * G * nQT * kv_len;
   return words * 4;
 }
 
@@ -560,11 +575,11 @@ extern "C" int kvb_sdpa_fwd(const void* q, const void* k, const void* v, const i
   if ((rc = make_tmap_4d_bf16(&tmQ, q, ATT_D, q_len, H, B, ATT_D, (uint64_t)q_len * ATT_D, (uint64_t)H * q_len * ATT_D, 64,
                               p.npos, gs)))
     return rc;
-  // K, V (B,G,L,D) with strides: dims (D, L, G, B); box = 64 x 128 x 1
+  // K, V (B,G,L,D) with strides: dims (D, L, G, B); box = 64 x ATT_BN x 1
   if ((rc = make_tmap_4d_bf16(&tmK, k, ATT_D, kv_len, G, B, ATT_D, k_sg, k_sb, 64, ATT_BN, 1))) return rc;
   if ((rc = make_tmap_4d_bf16(&tmV, v, ATT_D, kv_len, G, B, ATT_D, k_sg, k_sb, 64, ATT_BN, 1))) return rc;
 
-  att_tile_minmax_kernel<<<B * G * p.nT, 128, 0, s>>>(token_pos, tmin, tmax, G, kv_len, p.nT, tp_sb, tp_sg);
+  att_tile_minmax_kernel<<<B * G * p.nT, ATT_BN, 0, s>>>(token_pos, tmin, tmax, G, kv_len, p.nT, tp_sb, tp_sg);
   static bool attr_set = false;
   if (!attr_set) {
     cudaFuncSetAttribute(sdpa_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AttSmem::TOTAL);
@@ -573,7 +588,7 @@ extern "C" int kvb_sdpa_fwd(const void* q, const void* k, const void* v, const i
   sdpa_fwd_kernel<<<B * G * p.nQT, ATT_THREADS, AttSmem::TOTAL, s>>>(tmQ, tmK, tmV, p);
   if (weights) {
     dim3 grid((kv_len + 255) / 256, B * G);
-    att_reduce_weights_kernel<<<grid, 256, 0, s>>>(p.wpart, weights, 2 * p.nQT, kv_len, 1.f / gs);
+    att_reduce_weights_kernel<<<grid, 256, 0, s>>>(p.wpart, weights, 4 * p.nQT, kv_len, 1.f / gs);
   }
   return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
 }
