@@ -4,16 +4,20 @@
 //   dQ (B,H,T,D) bf16, and accumulates dK, dV into fp32 cache-shaped buffers (B,G,C,D).
 // Two launches of one kernel template, so that every output tile has exactly one
 // owner CTA (no atomics, deterministic):
-//   MODE_DQ : CTA = 128 query rows (positions x heads of a KV group), streams KV tiles
+//   MODE_DQ : CTA = 128 query rows (positions x heads of a KV group), streams KV slots
 //             S = Q K^T, dP = dO V^T  ->  dS = P (dP − δ) scale  ->  dQ += dS K
-//   MODE_DKV: CTA = 128 KV slots, streams query tiles
+//   MODE_DKV: CTA = 128 KV slots, streams query rows
 //             S^T = K Q^T, dP^T = V dO^T -> P^T, dS^T -> dV += P^T dO, dK += dS^T Q
-// Both are the same pipeline: a fixed "row" tile with two K-major operands (R1, R2),
-// streamed "column" tiles with two operands (C1, C2) that are consumed first as K-major
-// B operands (X = R1 C1^T, Y = R2 C2^T, fp32 in TMEM) and then, from the same shared
-// memory, as MN-major B operands of the accumulating MMAs (acc1 += P C2, acc2 += dS C1).
-// P and dS are produced by the 128 compute threads (one TMEM lane = one row each) and
-// staged in 128B-swizzled shared memory. δ = rowsum(dO ⊙ O) comes from a small kernel.
+// Both are the same pipeline. A fixed "row" tile has two K-major operands (R1, R2) in shared
+// memory. The streamed "column" operands (C1, C2) arrive by TMA in units of 64 columns through a
+// 4-stage ring. For every unit, X = R1 C1^T and Y = R2 C2^T (128 x 64, fp32) are formed in one of
+// two TMEM buffers; the 256 compute threads (TMEM lane = row) turn them into bf16 P and dS, which
+// they write back into the same TMEM columns; the accumulating MMAs then take P / dS as their
+// A operand straight from TMEM and the column operands, from the same shared memory, as
+// MN-major B operands (acc1 += P C2, acc2 += dS C1). P and dS never touch shared memory, whose
+// bandwidth is what bounds this kernel. MMAs of one thread execute in issue order, so the X/Y
+// MMAs of unit u+2, which overwrite the buffer of unit u, are issued after the accumulating
+// MMAs of unit u. δ = rowsum(dO ⊙ O) comes from a small kernel.
 //
 // Replaces the blocked fp32 PyTorch backward of the reference
 // (keys_values/attention/sdpa_op.py:31-251) and the library SDPA backward it otherwise uses.
@@ -25,20 +29,20 @@
 
 namespace kvb {
 
-constexpr int BW_TILE_BYTES = 128 * 128 * 2;
-constexpr int BW_THREADS = 320;  // TMA warp + MMA warp + 8 compute warps
+constexpr int BW_TILE_BYTES = 128 * 128 * 2;   // row operand: two 64-feature chunks of [128 rows x 128 B]
+constexpr int BW_UNIT_BYTES = 64 * 128 * 2;    // column operand of one unit: two chunks of [64 rows x 128 B]
+constexpr int BW_STAGES = 4;                   // ring of column units (C1 | C2 per stage)
+constexpr int BW_THREADS = 320;                // TMA warp + MMA warp + 8 compute warps
 enum { MODE_DQ = 0, MODE_DKV = 1 };
 
-template <int MODE>
 struct BwSmem {
-  static constexpr int STAGES = MODE == MODE_DQ ? 2 : 1;
   static constexpr int R1 = 0;
   static constexpr int R2 = R1 + BW_TILE_BYTES;
-  static constexpr int C = R2 + BW_TILE_BYTES;                 // per stage: C1 | C2
-  static constexpr int DS = C + STAGES * 2 * BW_TILE_BYTES;
-  static constexpr int P = DS + BW_TILE_BYTES;                 // only MODE_DKV
-  static constexpr int STATS = P + (MODE == MODE_DKV ? BW_TILE_BYTES : 0);  // 3 x 128 words
-  static constexpr int BAR = STATS + 3 * 512;
+  static constexpr int C = R2 + BW_TILE_BYTES;                    // per stage: C1 | C2
+  static constexpr int STATS = C + BW_STAGES * 2 * BW_UNIT_BYTES; // tp[128] | nlse[2][128] | ndls[2][128]
+  static constexpr int FLAGS = STATS + 512 + 1024 + 1024;         // one byte per column tile: bit 0 active, bit 1 masked
+  static constexpr int NFLAGS = 4096;
+  static constexpr int BAR = FLAGS + NFLAGS;
   static constexpr int TOTAL = BAR + 256 + 1024;
 };
 
@@ -52,6 +56,7 @@ struct BwParams {
   float* dk;            // (B,G,C,D) accumulated
   float* dv;
   int B, H, G, T, L, nT, nQT, gs, npos;
+  int hgs, hnpos;       // a 64-row half of a query tile covers hgs heads x hnpos positions
   long long tp_sb, tp_sg, dk_sb, dk_sg;
   float scale, scale_log2;
   int input_pos;
@@ -90,28 +95,28 @@ __global__ void att_delta_kernel(const __nv_bfloat16* __restrict__ dO, const __n
   }
 }
 
+// tmR1/tmR2: row operands (boxes of 128 rows); tmC1/tmC2: column operands (boxes of 64 rows).
+//   MODE_DQ : R1 = Q, R2 = dO, C1 = K, C2 = V      MODE_DKV: R1 = K, R2 = V, C1 = Q, C2 = dO
 template <int MODE>
 __global__ void __launch_bounds__(BW_THREADS, 1)
-sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
-                const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const BwParams p) {
-  using S = BwSmem<MODE>;
-  constexpr int ST = S::STAGES;
+sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ CUtensorMap tmR2,
+                const __grid_constant__ CUtensorMap tmC1, const __grid_constant__ CUtensorMap tmC2, const BwParams p) {
+  using S = BwSmem;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::BAR);
   uint64_t* r_full = bars + 0;
-  uint64_t* c_full = bars + 1;    // [2]
-  uint64_t* c_empty = bars + 3;   // [2]
-  uint64_t* xy_full = bars + 5;
-  uint64_t* pds_full = bars + 6;
-  uint64_t* pds_empty = bars + 7;
-  uint64_t* acc_full = bars + 8;
-  uint64_t* grp_bar = bars + 9;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* c_full = bars + 1;     // [4]
+  uint64_t* c_empty = bars + 5;    // [4]
+  uint64_t* xy_full = bars + 9;    // [2]
+  uint64_t* pds_full = bars + 11;  // [2]
+  uint64_t* acc_full = bars + 13;
+  uint64_t* grp_bar = bars + 14;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int32_t* stat_i = reinterpret_cast<int32_t*>(smem + S::STATS);         // MODE_DQ: token_pos of the KV tile
-  float* stat_lse = reinterpret_cast<float*>(smem + S::STATS + 512);     // MODE_DKV: lse2 of the query tile
-  float* stat_dl = reinterpret_cast<float*>(smem + S::STATS + 1024);     // MODE_DKV: delta of the query tile
+  int32_t* stat_i = reinterpret_cast<int32_t*>(smem + S::STATS);       // MODE_DQ: token_pos of the KV tile
+  float* stat_nlse = reinterpret_cast<float*>(smem + S::STATS + 512);  // MODE_DKV: [2][128] −lse·log2(e) of the query tile
+  float* stat_ndls = reinterpret_cast<float*>(smem + S::STATS + 1536); // MODE_DKV: [2][128] −delta·scale of the query tile
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_row_tiles = MODE == MODE_DQ ? p.nQT : p.nT;
@@ -125,22 +130,34 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   // (kv tile t, query tile qt) is active iff some slot of t is visible to some query of qt
   auto qpos_min_of = [&](int qt) { return p.input_pos + qt * p.npos; };
   auto qpos_max_of = [&](int qt) { return p.input_pos + min((qt + 1) * p.npos, p.T) - 1; };
-  auto active = [&](int ct) -> bool {
+  auto active_g = [&](int ct) -> bool {
     return MODE == MODE_DQ ? (tmin[ct] <= qpos_max_of(rt)) : (tmin[rt] <= qpos_max_of(ct));
   };
-  auto masked = [&](int ct) -> bool {
+  auto masked_g = [&](int ct) -> bool {
     return MODE == MODE_DQ ? (tmax[ct] > qpos_min_of(rt)) : (tmax[rt] > qpos_min_of(ct));
+  };
+  // the flags of the column tiles are kept in shared memory so that no role reads global memory
+  // inside its tile loop
+  uint8_t* tflags = smem + S::FLAGS;
+  for (int ct = threadIdx.x; ct < n_col_tiles && ct < S::NFLAGS; ct += BW_THREADS)
+    tflags[ct] = (uint8_t)((active_g(ct) ? 1 : 0) | (masked_g(ct) ? 2 : 0));
+  auto active = [&](int ct) -> bool { return ct < S::NFLAGS ? (tflags[ct] & 1) != 0 : active_g(ct); };
+  auto masked = [&](int ct) -> bool { return ct < S::NFLAGS ? (tflags[ct] & 2) != 0 : masked_g(ct); };
+  auto next_active = [&](int ct) -> int {
+    while (ct < n_col_tiles && !active(ct)) ++ct;
+    return ct;
   };
 
   if (threadIdx.x == 0) {
     mbar_init(r_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < BW_STAGES; ++s) {
       mbar_init(&c_full[s], 1);
       mbar_init(&c_empty[s], 1);
     }
-    mbar_init(xy_full, 1);
-    mbar_init(pds_full, 8);
-    mbar_init(pds_empty, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&xy_full[s], 1);
+      mbar_init(&pds_full[s], 8);
+    }
     mbar_init(acc_full, 1);
     mbar_init(grp_bar, 256);
     *abort_flag = 0;
@@ -154,46 +171,56 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // X buffers: columns [0,64) and [64,128); Y buffers: [128,192) and [192,256); accumulators after
   const uint32_t tmem_X = tmem_base, tmem_Y = tmem_base + 128, tmem_A1 = tmem_base + 256, tmem_A2 = tmem_base + 384;
 
   int n_active = 0;
   for (int ct = 0; ct < n_col_tiles; ++ct) n_active += active(ct) ? 1 : 0;
 
-  auto load_tile = [&](uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int c1, int c2, int c3) {
-    tma_load_4d(dst, tm, bar, 0, c1, c2, c3);
-    tma_load_4d(dst + BW_TILE_BYTES / 2, tm, bar, 64, c1, c2, c3);
-  };
-
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0 && n_active > 0) {
+      tma_prefetch_desc(&tmR1);
+      tma_prefetch_desc(&tmR2);
+      tma_prefetch_desc(&tmC1);
+      tma_prefetch_desc(&tmC2);
       mbar_expect_tx(r_full, 2 * BW_TILE_BYTES);
-      if (MODE == MODE_DQ) {
-        load_tile(smem + S::R1, &tmQ, r_full, rt * p.npos, g * p.gs, b);
-        load_tile(smem + S::R2, &tmdO, r_full, rt * p.npos, g * p.gs, b);
-      } else {
-        load_tile(smem + S::R1, &tmK, r_full, rt * 128, g, b);
-        load_tile(smem + S::R2, &tmV, r_full, rt * 128, g, b);
+      {
+        const int c1 = MODE == MODE_DQ ? rt * p.npos : rt * 128;
+        const int c2 = MODE == MODE_DQ ? g * p.gs : g;
+        tma_load_4d(smem + S::R1, &tmR1, r_full, 0, c1, c2, b);
+        tma_load_4d(smem + S::R1 + BW_TILE_BYTES / 2, &tmR1, r_full, 64, c1, c2, b);
+        tma_load_4d(smem + S::R2, &tmR2, r_full, 0, c1, c2, b);
+        tma_load_4d(smem + S::R2 + BW_TILE_BYTES / 2, &tmR2, r_full, 64, c1, c2, b);
       }
-      uint32_t s = 0;
+      uint32_t u = 0;
       bool ok = true;
       for (int ct = 0; ct < n_col_tiles && ok; ++ct) {
         if (!active(ct)) continue;
-        const int st = s % ST;
-        if (!mbar_wait_bounded(&c_empty[st], ((s / ST) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) { ok = false; break; }
-        uint8_t* c1 = smem + S::C + st * 2 * BW_TILE_BYTES;
-        uint8_t* c2 = c1 + BW_TILE_BYTES;
-        mbar_expect_tx(&c_full[st], 2 * BW_TILE_BYTES);
-        if (MODE == MODE_DQ) {
-          load_tile(c1, &tmK, &c_full[st], ct * 128, g, b);
-          load_tile(c2, &tmV, &c_full[st], ct * 128, g, b);
-        } else {
-          load_tile(c1, &tmQ, &c_full[st], ct * p.npos, g * p.gs, b);
-          load_tile(c2, &tmdO, &c_full[st], ct * p.npos, g * p.gs, b);
+        for (int h = 0; h < 2; ++h, ++u) {
+          const int st = u % BW_STAGES;
+          if (!mbar_wait_bounded(&c_empty[st], ((u / BW_STAGES) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) { ok = false; break; }
+          uint8_t* c1 = smem + S::C + st * 2 * BW_UNIT_BYTES;
+          uint8_t* c2 = c1 + BW_UNIT_BYTES;
+          int x1, x2;  // coordinates 1 and 2 of the 64-row box
+          if (MODE == MODE_DQ) {
+            x1 = ct * 128 + h * 64;
+            x2 = g;
+          } else if (p.gs >= 2) {
+            x1 = ct * p.npos;
+            x2 = g * p.gs + h * p.hgs;
+          } else {
+            x1 = ct * p.npos + h * 64;
+            x2 = g;
+          }
+          mbar_expect_tx(&c_full[st], 2 * BW_UNIT_BYTES);
+          tma_load_4d(c1, &tmC1, &c_full[st], 0, x1, x2, b);
+          tma_load_4d(c1 + BW_UNIT_BYTES / 2, &tmC1, &c_full[st], 64, x1, x2, b);
+          tma_load_4d(c2, &tmC2, &c_full[st], 0, x1, x2, b);
+          tma_load_4d(c2 + BW_UNIT_BYTES / 2, &tmC2, &c_full[st], 64, x1, x2, b);
         }
-        ++s;
       }
-      if (!ok) {
+      if (!ok) {  // let copies in flight land before the CTA's shared memory is released
         long long c0 = clock64();
         while (clock64() - c0 < 2000000LL) {
         }
@@ -202,54 +229,69 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer
     if (lane == 0 && n_active > 0) {
-      constexpr uint32_t idesc_kk = make_idesc_bf16(128, 128, 0, 0);   // both operands K-major
-      constexpr uint32_t idesc_kmn = make_idesc_bf16(128, 128, 0, 1);  // A K-major, B MN-major
+      constexpr uint32_t idesc_xy = make_idesc_bf16(128, 64, 0, 0);     // both operands K-major
+      constexpr uint32_t idesc_acc = make_idesc_bf16(128, 128, 0, 1);   // A from TMEM, B MN-major
       const uint32_t r1 = smem_u32(smem + S::R1), r2 = smem_u32(smem + S::R2);
-      const uint32_t ds_addr = smem_u32(smem + S::DS), p_addr = smem_u32(smem + S::P);
+      const uint32_t cbase = smem_u32(smem + S::C);
+      const uint32_t n_units = 2u * (uint32_t)n_active;
       bool ok = mbar_wait_bounded(r_full, 0, abort_flag, p.status, STATUS_TIMEOUT_FULL);
-      uint32_t s = 0;
-      for (int ct = 0; ct < n_col_tiles && ok; ++ct) {
-        if (!active(ct)) continue;
-        const int st = s % ST;
-        if (!mbar_wait_bounded(&c_full[st], (s / ST) & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL)) { ok = false; break; }
+      auto issue_xy = [&](uint32_t u) -> bool {
+        const uint32_t st = u % BW_STAGES, hb = u & 1;
+        if (!mbar_wait_bounded(&c_full[st], (u / BW_STAGES) & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL)) return false;
         tc_fence_after();
-        const uint32_t c1 = smem_u32(smem + S::C + st * 2 * BW_TILE_BYTES);
-        const uint32_t c2 = c1 + BW_TILE_BYTES;
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t off = (uint32_t)((kk >> 2) * (BW_TILE_BYTES / 2) + (kk & 3) * 32);
-          umma_f16_ss(tmem_X, make_smem_desc_sw128(r1 + off, 16, 1024), make_smem_desc_sw128(c1 + off, 16, 1024), idesc_kk, kk != 0);
-        }
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t off = (uint32_t)((kk >> 2) * (BW_TILE_BYTES / 2) + (kk & 3) * 32);
-          umma_f16_ss(tmem_Y, make_smem_desc_sw128(r2 + off, 16, 1024), make_smem_desc_sw128(c2 + off, 16, 1024), idesc_kk, kk != 0);
-        }
-        umma_commit(xy_full);
-        if (!mbar_wait_bounded(pds_full, s & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL)) { ok = false; break; }
-        tc_fence_after();
+        const uint32_t c1 = cbase + st * 2 * BW_UNIT_BYTES, c2 = c1 + BW_UNIT_BYTES;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t a_off = (uint32_t)((kk >> 2) * (BW_TILE_BYTES / 2) + (kk & 3) * 32);
+          const uint32_t b_off = (uint32_t)((kk >> 2) * (BW_UNIT_BYTES / 2) + (kk & 3) * 32);
+          umma_f16_ss(tmem_X + 64 * hb, make_smem_desc_sw128(r1 + a_off, 16, 1024), make_smem_desc_sw128(c1 + b_off, 16, 1024),
+                      idesc_xy, kk != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t a_off = (uint32_t)((kk >> 2) * (BW_TILE_BYTES / 2) + (kk & 3) * 32);
+          const uint32_t b_off = (uint32_t)((kk >> 2) * (BW_UNIT_BYTES / 2) + (kk & 3) * 32);
+          umma_f16_ss(tmem_Y + 64 * hb, make_smem_desc_sw128(r2 + a_off, 16, 1024), make_smem_desc_sw128(c2 + b_off, 16, 1024),
+                      idesc_xy, kk != 0);
+        }
+        umma_commit(&xy_full[hb]);
+        return true;
+      };
+      auto issue_acc = [&](uint32_t u) -> bool {
+        const uint32_t st = u % BW_STAGES, hb = u & 1;
+        if (!mbar_wait_bounded(&pds_full[hb], (u >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL)) return false;
+        tc_fence_after();
+        const uint32_t c1 = cbase + st * 2 * BW_UNIT_BYTES, c2 = c1 + BW_UNIT_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          // A: 16 columns of the unit per step = 8 TMEM columns; the two compute warps of a lane
+          // quarter keep their 32 columns in separate 32-column halves of the buffer
+          const uint32_t a_col = (uint32_t)(32 * (kk >> 1) + 8 * (kk & 1));
+          // B: MN-major, 16 rows of the unit per step (2048 B); the 64-feature chunks are LBO apart
           const uint32_t b_off = (uint32_t)(kk * 16 * 128);
           if (MODE == MODE_DKV)
-            umma_f16_ss(tmem_A1, make_smem_desc_sw128(p_addr + a_off, 16, 1024),
-                        make_smem_desc_sw128(c2 + b_off, BW_TILE_BYTES / 2, 1024), idesc_kmn, (s | kk) != 0);
-          umma_f16_ss(tmem_A2, make_smem_desc_sw128(ds_addr + a_off, 16, 1024),
-                      make_smem_desc_sw128(c1 + b_off, BW_TILE_BYTES / 2, 1024), idesc_kmn, (s | kk) != 0);
+            umma_f16_ts(tmem_A1, tmem_X + 64 * hb + a_col, make_smem_desc_sw128(c2 + b_off, BW_UNIT_BYTES / 2, 1024), idesc_acc,
+                        (u | kk) != 0);
+          umma_f16_ts(tmem_A2, tmem_Y + 64 * hb + a_col, make_smem_desc_sw128(c1 + b_off, BW_UNIT_BYTES / 2, 1024), idesc_acc,
+                      (u | kk) != 0);
         }
         umma_commit(&c_empty[st]);
-        umma_commit(pds_empty);
-        ++s;
+        return true;
+      };
+      uint32_t ux = 0;
+      while (ok && ux < n_units && ux < 2) ok = issue_xy(ux++);
+      for (uint32_t u = 0; u < n_units && ok; ++u) {
+        ok = issue_acc(u);
+        if (ok && ux < n_units) ok = issue_xy(ux++);
       }
       if (ok) umma_commit(acc_full);
     }
   } else {
     // ----------------------------------------------- compute + epilogue warps
-    // 8 warps: two per TMEM sub-partition; thread (row, half) owns columns [64·half, +64) of its row
+    // 8 warps: two per TMEM lane quarter; thread (row, hh) owns columns [32·hh, +32) of its row in
+    // every 64-column unit, and columns [64·hh, +64) of the accumulators in the epilogue
     const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;
-    const int cbeg = half * 64;
+    const int hh = (warp - 2) >> 2;
     const int row = quarter * 32 + lane;
     const int tid = threadIdx.x - 64;  // 0..255
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
@@ -262,7 +304,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       return done;
     };
     // per-row constants
-    float row_lse2 = INFINITY, row_delta = 0.f;
+    float row_nlse = -INFINITY, row_ndls = 0.f;
     int row_pos = 0, row_tp = INT_MAX;
     bool row_valid;
     int hq = 0, tq = 0;
@@ -273,19 +315,38 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       row_pos = p.input_pos + tq;
       if (row_valid) {
         const long long idx = ((long long)b * p.H + g * p.gs + hq) * p.T + tq;
-        row_lse2 = p.lse[idx] * 1.4426950408889634f;
-        row_delta = p.delta[idx];
+        row_nlse = -p.lse[idx] * 1.4426950408889634f;
+        row_ndls = -p.delta[idx] * p.scale;
       }
     } else {
       const int j = rt * 128 + row;
       row_valid = j < p.L;
       if (row_valid) row_tp = p.token_pos ? p.token_pos[b * p.tp_sb + g * p.tp_sg + j] : j;
     }
-    uint8_t* DSs = smem + S::DS;
-    uint8_t* Ps = smem + S::P;
-    for (int ct = 0; ct < n_col_tiles && ok; ++ct) {
-      if (!active(ct)) continue;
+    // MODE_DKV: statistics of query tile ct, column cc <-> (head cc / npos, position cc % npos);
+    // threads 0..127 fetch −lse·log2(e), threads 128..255 fetch −delta·scale
+    auto fetch_stat = [&](int ct) -> float {
+      const int cc = tid & 127;
+      const int c_hq = cc / p.npos, c_tq = ct * p.npos + cc % p.npos;
+      if (ct >= n_col_tiles || c_tq >= p.T) return tid < 128 ? -INFINITY : 0.f;
+      const long long idx = ((long long)b * p.H + g * p.gs + c_hq) * p.T + c_tq;
+      return tid < 128 ? -p.lse[idx] * 1.4426950408889634f : -p.delta[idx] * p.scale;
+    };
+    auto store_stat = [&](int buf, float v) {
+      if (tid < 128) stat_nlse[buf * 128 + tid] = v;
+      else stat_ndls[buf * 128 + (tid - 128)] = v;
+    };
+    int ct = next_active(0);
+    if (MODE == MODE_DKV && ok) {
+      store_stat(0, fetch_stat(ct));
+      ok = group_sync();
+    }
+    const float2 c2 = make_float2(p.scale_log2, p.scale_log2);
+    const float2 sc2 = make_float2(p.scale, p.scale);
+    while (ct < n_col_tiles && ok) {
       const bool msk = masked(ct);
+      const int ct_next = next_active(ct + 1);
+      float stat_next = 0.f;
       if (MODE == MODE_DQ) {
         if (msk) {
           const int jj = ct * 128 + tid;
@@ -296,72 +357,66 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           if (!group_sync()) { ok = false; break; }
         }
       } else {
-        // statistics of the query tile: column c <-> (head c / npos, position c % npos)
-        const int c_hq = (tid & 127) / p.npos, c_tq = ct * p.npos + (tid & 127) % p.npos;
-        float l2 = INFINITY, dl = 0.f;
-        if (tid < 128 && c_tq < p.T) {
-          const long long idx = ((long long)b * p.H + g * p.gs + c_hq) * p.T + c_tq;
-          l2 = p.lse[idx] * 1.4426950408889634f;
-          dl = p.delta[idx];
-        }
-        if (!group_sync()) { ok = false; break; }
-        if (tid < 128) {
-          stat_lse[tid] = l2;
-          stat_dl[tid] = dl;
-        }
-        if (!group_sync()) { ok = false; break; }
+        stat_next = fetch_stat(ct_next);  // in flight while this tile is processed
       }
-      if (!mbar_wait_bounded(xy_full, s & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
-      if (!mbar_wait_bounded(pds_empty, (s & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_MISC)) { ok = false; break; }
-      tc_fence_after();
-      const int cpos0 = p.input_pos + ct * p.npos;  // MODE_DKV: position of column c is cpos0 + c % npos
-#pragma unroll 1
-      for (int c0 = cbeg; c0 < cbeg + 64; c0 += 32) {
+      const int sbuf = s & 1;
+      const int cpos0 = p.input_pos + ct * p.npos;  // MODE_DKV: position of column cc is cpos0 + cc % npos
+      for (int h = 0; h < 2 && ok; ++h) {
+        if (!mbar_wait_bounded(&xy_full[h], s & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t xaddr = tmem_X + lane_base + (uint32_t)(64 * h + 32 * hh);
+        const uint32_t yaddr = tmem_Y + lane_base + (uint32_t)(64 * h + 32 * hh);
         uint32_t xr[32], yr[32];
-        tmem_ld_32x32b_x32(tmem_X + lane_base + (uint32_t)c0, xr);
-        tmem_ld_32x32b_x32(tmem_Y + lane_base + (uint32_t)c0, yr);
+        tmem_ld_32x32b_x32(xaddr, xr);
+        tmem_ld_32x32b_x32(yaddr, yr);
         tmem_ld_wait();
+        const int cc0 = 64 * h + 32 * hh;  // first column of this thread within the 128-column tile
         uint32_t pk[16], dk_[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
-          float pv[2], dsv[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int c = c0 + e + u;
-            float l2, dl;
-            bool vis;
-            if (MODE == MODE_DQ) {
-              l2 = row_lse2;
-              dl = row_delta;
-              vis = !msk || stat_i[c] <= row_pos;
-            } else {
-              l2 = stat_lse[c];
-              dl = stat_dl[c];
-              vis = !msk || row_tp <= cpos0 + (c % p.npos);
-            }
-            float pp = bw_exp2(__uint_as_float(xr[e + u]) * p.scale_log2 - l2);
-            if (!vis) pp = 0.f;
-            pv[u] = pp;
-            dsv[u] = pp * (__uint_as_float(yr[e + u]) - dl) * p.scale;
+          float2 nl, nd;
+          if (MODE == MODE_DQ) {
+            nl = make_float2(row_nlse, row_nlse);
+            nd = make_float2(row_ndls, row_ndls);
+          } else {
+            nl = *reinterpret_cast<const float2*>(stat_nlse + sbuf * 128 + cc0 + e);
+            nd = *reinterpret_cast<const float2*>(stat_ndls + sbuf * 128 + cc0 + e);
           }
-          pk[e >> 1] = pack_bf16x2(pv[0], pv[1]);
-          dk_[e >> 1] = pack_bf16x2(dsv[0], dsv[1]);
+          const float2 xx = ffma2(make_float2(__uint_as_float(xr[e]), __uint_as_float(xr[e + 1])), c2, nl);
+          float2 pp = make_float2(bw_exp2(xx.x), bw_exp2(xx.y));
+          if (msk) {
+            bool v0, v1;
+            if (MODE == MODE_DQ) {
+              v0 = stat_i[cc0 + e] <= row_pos;
+              v1 = stat_i[cc0 + e + 1] <= row_pos;
+            } else {
+              v0 = row_tp <= cpos0 + ((cc0 + e) % p.npos);
+              v1 = row_tp <= cpos0 + ((cc0 + e + 1) % p.npos);
+            }
+            if (!v0) pp.x = 0.f;
+            if (!v1) pp.y = 0.f;
+          }
+          const float2 tt = ffma2(make_float2(__uint_as_float(yr[e]), __uint_as_float(yr[e + 1])), sc2, nd);
+          const float2 ds = fmul2(pp, tt);
+          pk[e >> 1] = pack_bf16x2(pp.x, pp.y);
+          dk_[e >> 1] = pack_bf16x2(ds.x, ds.y);
         }
-        const int chunk_off = (c0 >> 6) * (BW_TILE_BYTES / 2);
-        const int u0 = (c0 & 63) >> 3;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const uint32_t off = chunk_off + sw128_offset(row, u0 + u);
-          *reinterpret_cast<uint4*>(DSs + off) = make_uint4(dk_[4 * u], dk_[4 * u + 1], dk_[4 * u + 2], dk_[4 * u + 3]);
-          if (MODE == MODE_DKV)
-            *reinterpret_cast<uint4*>(Ps + off) = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
-        }
+        // P and dS go back into the first 16 columns of the 32 that this thread has just read
+        if (MODE == MODE_DKV) tmem_st_32x32b_x16(xaddr, pk);
+        tmem_st_32x32b_x16(yaddr, dk_);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&pds_full[h]);
       }
-      tc_fence_before();
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(pds_full);
+      if (!ok) break;
+      if (MODE == MODE_DKV) {
+        // the other buffer was last read during the previous tile, before that tile's barrier
+        store_stat(sbuf ^ 1, stat_next);
+        if (!group_sync()) { ok = false; break; }
+      }
       ++s;
+      ct = ct_next;
     }
     // ---- epilogue
     if (ok) ok = mbar_wait_bounded(acc_full, 0, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL);
@@ -370,7 +425,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (MODE == MODE_DQ) {
         __nv_bfloat16* dst = p.dq + (((long long)b * p.H + g * p.gs + hq) * p.T + tq) * 128;
 #pragma unroll 1
-        for (int c0 = cbeg; c0 < cbeg + 64; c0 += 32) {
+        for (int c0 = 64 * hh; c0 < 64 * hh + 64; c0 += 32) {
           uint32_t r[32];
           tmem_ld_32x32b_x32(tmem_A2 + lane_base + (uint32_t)c0, r);
           tmem_ld_wait();
@@ -389,7 +444,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       } else {
         const long long off = b * p.dk_sb + g * p.dk_sg + (long long)(rt * 128 + row) * 128;
 #pragma unroll 1
-        for (int c0 = cbeg; c0 < cbeg + 64; c0 += 32) {
+        for (int c0 = 64 * hh; c0 < 64 * hh + 64; c0 += 32) {
           uint32_t r1v[32], r2v[32];
           tmem_ld_32x32b_x32(tmem_A1 + lane_base + (uint32_t)c0, r1v);
           tmem_ld_32x32b_x32(tmem_A2 + lane_base + (uint32_t)c0, r2v);
@@ -412,7 +467,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
     } else if (n_active == 0 && MODE == MODE_DQ && row_valid) {
       __nv_bfloat16* dst = p.dq + (((long long)b * p.H + g * p.gs + hq) * p.T + tq) * 128;
-      for (int c = cbeg; c < cbeg + 64; c += 8) *reinterpret_cast<uint4*>(dst + c) = make_uint4(0, 0, 0, 0);
+      for (int c = 64 * hh; c < 64 * hh + 64; c += 8) *reinterpret_cast<uint4*>(dst + c) = make_uint4(0, 0, 0, 0);
     }
   }
   tc_fence_before();
@@ -471,6 +526,7 @@ extern "C" int kvb_sdpa_bwd(const void* q, const void* k, const void* v, const i
   BwParams p;
   p.B = B; p.H = H; p.G = G; p.T = q_len; p.L = kv_len;
   p.gs = gs; p.npos = 128 / gs;
+  p.hgs = gs >= 2 ? gs / 2 : 1; p.hnpos = 64 / p.hgs;
   p.nT = (kv_len + 127) / 128;
   p.nQT = (q_len + p.npos - 1) / p.npos;
   p.token_pos = token_pos; p.tp_sb = tp_sb; p.tp_sg = tp_sg;
@@ -484,25 +540,31 @@ extern "C" int kvb_sdpa_bwd(const void* q, const void* k, const void* v, const i
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
   p.input_pos = input_pos; p.status = status;
 
-  CUtensorMap tmQ, tmdO, tmK, tmV;
+  // full (128-row) boxes for the row operands, half (64-row) boxes for the streamed units
+  CUtensorMap tmQ, tmdO, tmK, tmV, tmQh, tmdOh, tmKh, tmVh;
   int rc;
+  const uint64_t qT = (uint64_t)q_len, HT = (uint64_t)H * q_len;
   // Q (B,H,T,D): dims (D,T,H,B)
-  if ((rc = bw_make_tmap_4d(&tmQ, q, 128, q_len, H, B, 128, (uint64_t)q_len * 128, (uint64_t)H * q_len * 128, 64, p.npos, gs))) return rc;
+  if ((rc = bw_make_tmap_4d(&tmQ, q, 128, q_len, H, B, 128, qT * 128, HT * 128, 64, p.npos, gs))) return rc;
+  if ((rc = bw_make_tmap_4d(&tmQh, q, 128, q_len, H, B, 128, qT * 128, HT * 128, 64, p.hnpos, p.hgs))) return rc;
   // dO (B,T,H,D) viewed with dims (D,T,H,B): T stride H*D, H stride D
-  if ((rc = bw_make_tmap_4d(&tmdO, dout, 128, q_len, H, B, (uint64_t)H * 128, 128, (uint64_t)q_len * H * 128, 64, p.npos, gs))) return rc;
+  if ((rc = bw_make_tmap_4d(&tmdO, dout, 128, q_len, H, B, (uint64_t)H * 128, 128, HT * 128, 64, p.npos, gs))) return rc;
+  if ((rc = bw_make_tmap_4d(&tmdOh, dout, 128, q_len, H, B, (uint64_t)H * 128, 128, HT * 128, 64, p.hnpos, p.hgs))) return rc;
   if ((rc = bw_make_tmap_4d(&tmK, k, 128, kv_len, G, B, 128, k_sg, k_sb, 64, 128, 1))) return rc;
   if ((rc = bw_make_tmap_4d(&tmV, v, 128, kv_len, G, B, 128, k_sg, k_sb, 64, 128, 1))) return rc;
+  if ((rc = bw_make_tmap_4d(&tmKh, k, 128, kv_len, G, B, 128, k_sg, k_sb, 64, 64, 1))) return rc;
+  if ((rc = bw_make_tmap_4d(&tmVh, v, 128, kv_len, G, B, 128, k_sg, k_sb, 64, 64, 1))) return rc;
 
   if ((rc = kvb_att_tile_minmax(token_pos, tmin, tmax, B, G, kv_len, tp_sb, tp_sg, 128, stream))) return rc;
   const long long rows = (long long)B * q_len * H;
   att_delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, delta, B, q_len, H);
   static bool attr_set = false;
   if (!attr_set) {
-    cudaFuncSetAttribute(sdpa_bwd_kernel<MODE_DQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwSmem<MODE_DQ>::TOTAL);
-    cudaFuncSetAttribute(sdpa_bwd_kernel<MODE_DKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwSmem<MODE_DKV>::TOTAL);
+    cudaFuncSetAttribute(sdpa_bwd_kernel<MODE_DQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwSmem::TOTAL);
+    cudaFuncSetAttribute(sdpa_bwd_kernel<MODE_DKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwSmem::TOTAL);
     attr_set = true;
   }
-  sdpa_bwd_kernel<MODE_DQ><<<B * G * p.nQT, BW_THREADS, BwSmem<MODE_DQ>::TOTAL, s>>>(tmQ, tmdO, tmK, tmV, p);
-  sdpa_bwd_kernel<MODE_DKV><<<B * G * p.nT, BW_THREADS, BwSmem<MODE_DKV>::TOTAL, s>>>(tmQ, tmdO, tmK, tmV, p);
+  sdpa_bwd_kernel<MODE_DQ><<<B * G * p.nQT, BW_THREADS, BwSmem::TOTAL, s>>>(tmQ, tmdO, tmKh, tmVh, p);
+  sdpa_bwd_kernel<MODE_DKV><<<B * G * p.nT, BW_THREADS, BwSmem::TOTAL, s>>>(tmK, tmV, tmQh, tmdOh, p);
   return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
 }

@@ -11,7 +11,7 @@
 //   * S = Q K^T (M=128, N=64) and O += P V (M=128, N=128) run on tcgen05.mma with S
 //     (double-buffered) and O in TMEM; K/V tiles of 64 slots arrive by TMA into 2-stage
 //     rings (128B swizzle; no multicast). V is consumed as an MN-major B operand.
-//   * A CTA uses 112.5 KB of shared memory and 256 TMEM columns, so two CTAs share an SM:
+//   * A CTA uses 112.75 KB of shared memory and 256 TMEM columns, so two CTAs share an SM:
 //     while one waits on its MMA -> softmax -> MMA chain the other one issues.
 //   * Two sweeps over the KV tiles: sweep 1 computes the exact row log-sum-exp (online
 //     max / sum), sweep 2 recomputes S, forms the already-normalised P = exp2(S·c − lse),
@@ -48,7 +48,7 @@ constexpr int ATT_KV_BYTES = ATT_BN * ATT_D * 2;   // 16 KB: two 64-feature chun
 constexpr int ATT_P_BYTES = ATT_BM * ATT_BN * 2;   // 16 KB: one 64-column chunk of [128 rows x 128 B]
 constexpr int ATT_TMEM_COLS = 256;                 // S0 | S1 (64 columns each) | O (128 columns)
 
-// Shared memory of one CTA: 112.5 KB, so that two CTAs fit into the 228 KB of an SM (each
+// Shared memory of one CTA: 112.75 KB, so that two CTAs fit into the 228 KB of an SM (each
 // CTA also costs 1 KB of system reserve). The dynamic shared memory window must be 1024-byte
 // aligned for the 128B-swizzled tiles; the kernel checks this and reports instead of running.
 struct AttSmem {
@@ -57,7 +57,8 @@ struct AttSmem {
   static constexpr int V = K + 2 * ATT_KV_BYTES;
   static constexpr int P = V + 2 * ATT_KV_BYTES;
   static constexpr int TP = P + ATT_P_BYTES;   // 64 int32 token positions of the current tile
-  static constexpr int BAR = TP + 256;
+  static constexpr int TF = TP + 256;          // 2 bits per KV tile (active, masked) for the first 1024 tiles
+  static constexpr int BAR = TF + 256;
   static constexpr int TOTAL = BAR + 256;
 };
 
@@ -73,7 +74,19 @@ struct AttParams {
   float scale_log2;          // scale * log2(e)
   int input_pos;
   int* status;
+  long long* trace;          // optional timeline of CTA 0: per role trace_cap (tag, clock) pairs
+  int trace_cap;
 };
+
+// Timeline event of one role (0 producer, 1 MMA issuer, 2 first softmax warp) of CTA 0.
+#define ATT_TRACE(role, tag)                                              \
+  do {                                                                    \
+    if (p.trace && blockIdx.x == 0 && tr_n < p.trace_cap) {               \
+      p.trace[((role) * p.trace_cap + tr_n) * 2] = (long long)(tag);      \
+      p.trace[((role) * p.trace_cap + tr_n) * 2 + 1] = clock64();         \
+      ++tr_n;                                                             \
+    }                                                                     \
+  } while (0)
 
 __global__ void att_tile_minmax_kernel(const int32_t* __restrict__ tp, int32_t* __restrict__ tmin, int32_t* __restrict__ tmax, int G,
                                        int L, int nT, long long tp_sb, long long tp_sg) {
@@ -162,6 +175,26 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int32_t* tmin = p.tile_min + ((long long)b * p.G + g) * p.nT;
   const int32_t* tmax = p.tile_max + ((long long)b * p.G + g) * p.nT;
 
+  // (active, masked) bits of the KV tiles for this query tile, so that no role reads global
+  // memory inside its tile loop
+  uint32_t* tflags = reinterpret_cast<uint32_t*>(smem + AttSmem::TF);
+  constexpr int TF_TILES = 1024;
+  for (int w = threadIdx.x; w < TF_TILES / 16; w += ATT_THREADS) {
+    uint32_t bits = 0;
+#pragma unroll 4
+    for (int i = 0; i < 16; ++i) {
+      const int t = w * 16 + i;
+      if (t < p.nT) bits |= ((uint32_t)(tmin[t] <= qpos_max) | ((uint32_t)(tmax[t] > qpos_min) << 1)) << (2 * i);
+    }
+    tflags[w] = bits;
+  }
+  auto tile_active = [&](int t) -> bool {
+    return t < TF_TILES ? ((tflags[t >> 4] >> ((t & 15) * 2)) & 1u) != 0 : tmin[t] <= qpos_max;
+  };
+  auto tile_masked = [&](int t) -> bool {
+    return t < TF_TILES ? ((tflags[t >> 4] >> ((t & 15) * 2)) & 2u) != 0 : tmax[t] > qpos_min;
+  };
+
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < 2; ++s) {
@@ -191,7 +224,8 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t tmem_O = tmem_base + 128;     // O: columns [128,256)
 
   int n_active = 0;
-  for (int t = 0; t < p.nT; ++t) n_active += (tmin[t] <= qpos_max);
+  for (int w = 0; w < TF_TILES / 16; ++w) n_active += __popc(tflags[w] & 0x55555555u);
+  for (int t = TF_TILES; t < p.nT; ++t) n_active += (tmin[t] <= qpos_max);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -204,11 +238,13 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tma_load_4d(smem + AttSmem::Q + ATT_Q_BYTES / 2, &tmQ, q_full, 64, t0, g * p.gs, b);
       uint32_t i = 0, j = 0;
       bool ok = true;
+      int tr_n = 0;
       for (int sweep = 0; sweep < 2 && ok; ++sweep) {
         for (int t = 0; t < p.nT && ok; ++t) {
-          if (tmin[t] > qpos_max) continue;
+          if (!tile_active(t)) continue;
           const int ks = i & 1;
           if (!mbar_wait_bounded(&k_empty[ks], ((i >> 1) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) { ok = false; break; }
+          ATT_TRACE(0, 100000 + sweep * 50000 + t);
           uint8_t* kd = smem + AttSmem::K + ks * ATT_KV_BYTES;
           mbar_expect_tx(&k_full[ks], ATT_KV_BYTES);
           tma_load_4d(kd, &tmK, &k_full[ks], 0, t * ATT_BN, g, b);
@@ -240,10 +276,14 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint32_t p_addr = smem_u32(smem + AttSmem::P);
       bool ok = mbar_wait_bounded(q_full, 0, abort_flag, p.status, STATUS_TIMEOUT_FULL);
       uint32_t i = 0, j = 0;
+      int tr_n = 0;
       auto issue_qk = [&]() -> bool {
         const int ks = i & 1;
+        ATT_TRACE(1, 1000000 + i);
         if (!mbar_wait_bounded(&k_full[ks], (i >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL)) return false;
+        ATT_TRACE(1, 1100000 + i);
         if (!mbar_wait_bounded(&s_empty[ks], ((i >> 1) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) return false;
+        ATT_TRACE(1, 1200000 + i);
         tc_fence_after();
         const uint32_t k_addr = smem_u32(smem + AttSmem::K + ks * ATT_KV_BYTES);
 #pragma unroll
@@ -256,13 +296,17 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         umma_commit(&k_empty[ks]);
         umma_commit(&s_full[ks]);
+        ATT_TRACE(1, 1300000 + i);
         ++i;
         return true;
       };
       auto issue_pv = [&]() -> bool {
         const int vs = j & 1;
+        ATT_TRACE(1, 2000000 + j);
         if (!mbar_wait_bounded(p_full, j & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL)) return false;
+        ATT_TRACE(1, 2100000 + j);
         if (!mbar_wait_bounded(&v_full[vs], (j >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL)) return false;
+        ATT_TRACE(1, 2200000 + j);
         tc_fence_after();
         const uint32_t v_addr = smem_u32(smem + AttSmem::V + vs * ATT_KV_BYTES);
 #pragma unroll
@@ -276,18 +320,19 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         umma_commit(&v_empty[vs]);
         umma_commit(p_empty);
+        ATT_TRACE(1, 2300000 + j);
         ++j;
         return true;
       };
       // sweep 1: S only
       for (int t = 0; t < p.nT && ok; ++t) {
-        if (tmin[t] > qpos_max) continue;
+        if (!tile_active(t)) continue;
         ok = issue_qk();
       }
       // sweep 2: QK of the next tile is issued before PV of the current one
       bool pending = false;
       for (int t = 0; t < p.nT && ok; ++t) {
-        if (tmin[t] > qpos_max) continue;
+        if (!tile_active(t)) continue;
         ok = issue_qk();
         if (ok && pending) ok = issue_pv();
         pending = true;
@@ -309,10 +354,12 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int sm_tid = threadIdx.x - 64;          // 0..127
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     const float c = p.scale_log2;
+    const float2 c2 = make_float2(c, c);
     bool ok = n_active > 0;
     uint32_t i = 0, j = 0;
     float m = -1e30f, l = 0.f;
     uint32_t grp_phase = 0;
+    int tr_n = (warp == 2 && lane == 0) ? 0 : (1 << 30);  // only the first softmax warp records
     // barrier among the softmax threads; false if it ran into the wait limit
     auto group_sync = [&]() -> bool {
       mbar_arrive(grp_bar);
@@ -342,16 +389,19 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
     // ---- sweep 1: exact row max and sum
     for (int t = 0; t < p.nT && ok; ++t) {
-      if (tmin[t] > qpos_max) continue;
+      if (!tile_active(t)) continue;
       const int sb = i & 1;
-      const bool masked = tmax[t] > qpos_min;
+      const bool masked = tile_masked(t);
       if (masked && !load_tile_tp(t)) { ok = false; break; }
+      ATT_TRACE(2, 3000000 + i);
       if (!mbar_wait_bounded(&s_full[sb], (i >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      ATT_TRACE(2, 3100000 + i);
       tc_fence_after();
       uint32_t r[ATT_BN];
       tmem_ld_32x32b_x32(tmem_S0 + lane_base + (uint32_t)(sb * ATT_BN), r);
       tmem_ld_32x32b_x32(tmem_S0 + lane_base + (uint32_t)(sb * ATT_BN + 32), r + 32);
       tmem_ld_wait();
+      ATT_TRACE(2, 3200000 + i);
       // the tile is in registers: hand the S buffer back before the arithmetic
       tc_fence_before();
       __syncwarp();
@@ -362,36 +412,44 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int e = 0; e < ATT_BN; ++e)
           if (tp_s[e] > my_pos) r[e] = NEG_INF_BITS;
       }
-      // max of the raw scores (the scale is positive), four independent chains
-      float a0 = __uint_as_float(r[0]), a1 = __uint_as_float(r[1]), a2 = __uint_as_float(r[2]), a3 = __uint_as_float(r[3]);
+      // max of the raw scores (the scale is positive): four independent chains of 3-input max
+      float a0 = -INFINITY, a1 = -INFINITY, a2 = -INFINITY, a3 = -INFINITY;
 #pragma unroll
-      for (int e = 4; e < ATT_BN; e += 4) {
-        a0 = fmaxf(a0, __uint_as_float(r[e]));
-        a1 = fmaxf(a1, __uint_as_float(r[e + 1]));
-        a2 = fmaxf(a2, __uint_as_float(r[e + 2]));
-        a3 = fmaxf(a3, __uint_as_float(r[e + 3]));
+      for (int e = 0; e < ATT_BN; e += 8) {
+        a0 = fmax3(a0, __uint_as_float(r[e]), __uint_as_float(r[e + 1]));
+        a1 = fmax3(a1, __uint_as_float(r[e + 2]), __uint_as_float(r[e + 3]));
+        a2 = fmax3(a2, __uint_as_float(r[e + 4]), __uint_as_float(r[e + 5]));
+        a3 = fmax3(a3, __uint_as_float(r[e + 6]), __uint_as_float(r[e + 7]));
       }
-      const float m_new = fmaxf(m, fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)) * c);
-      const float neg_m = -m_new;
-      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+      const float m_new = fmaxf(m, fmax3(a0, a1, fmaxf(a2, a3)) * c);
+      const float2 neg_m2 = make_float2(-m_new, -m_new);
+      float2 s0 = make_float2(0.f, 0.f), s1 = s0, s2 = s0, s3 = s0;
 #pragma unroll
-      for (int e = 0; e < ATT_BN; e += 4) {
-        s0 += fast_exp2(fmaf(__uint_as_float(r[e]), c, neg_m));
-        s1 += fast_exp2(fmaf(__uint_as_float(r[e + 1]), c, neg_m));
-        s2 += fast_exp2(fmaf(__uint_as_float(r[e + 2]), c, neg_m));
-        s3 += fast_exp2(fmaf(__uint_as_float(r[e + 3]), c, neg_m));
+      for (int e = 0; e < ATT_BN; e += 8) {
+        float2 x0 = ffma2(make_float2(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), c2, neg_m2);
+        float2 x1 = ffma2(make_float2(__uint_as_float(r[e + 2]), __uint_as_float(r[e + 3])), c2, neg_m2);
+        float2 x2 = ffma2(make_float2(__uint_as_float(r[e + 4]), __uint_as_float(r[e + 5])), c2, neg_m2);
+        float2 x3 = ffma2(make_float2(__uint_as_float(r[e + 6]), __uint_as_float(r[e + 7])), c2, neg_m2);
+        s0 = fadd2(s0, make_float2(fast_exp2(x0.x), fast_exp2(x0.y)));
+        s1 = fadd2(s1, make_float2(fast_exp2(x1.x), fast_exp2(x1.y)));
+        s2 = fadd2(s2, make_float2(fast_exp2(x2.x), fast_exp2(x2.y)));
+        s3 = fadd2(s3, make_float2(fast_exp2(x3.x), fast_exp2(x3.y)));
       }
-      l = l * fast_exp2(m - m_new) + ((s0 + s1) + (s2 + s3));
+      s0 = fadd2(fadd2(s0, s1), fadd2(s2, s3));
+      l = l * fast_exp2(m - m_new) + (s0.x + s0.y);
       m = m_new;
+      ATT_TRACE(2, 3300000 + i);
     }
     const float lse2 = l > 0.f ? m + log2f(l) : INFINITY;
-    const float neg_lse2 = -lse2;
+    // rows beyond the end of the query get P = 0 (their Q rows are zero-filled, so S = 0)
+    const float nl = row_valid ? -lse2 : -INFINITY;
+    const float2 neg_lse2 = make_float2(nl, nl);
 
     // ---- sweep 2: P = exp2(S·c − lse), O += P V, column sums of P
     uint8_t* Ps = smem + AttSmem::P;
     for (int t = 0; t < p.nT && ok; ++t) {
       float* wdst = wbase ? wbase + (long long)t * ATT_BN : nullptr;
-      if (tmin[t] > qpos_max) {
+      if (!tile_active(t)) {
         if (wdst) {
           if (t * ATT_BN + 2 * lane < p.L) wdst[2 * lane] = 0.f;
           if (t * ATT_BN + 2 * lane + 1 < p.L) wdst[2 * lane + 1] = 0.f;
@@ -399,14 +457,17 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         continue;
       }
       const int sb = i & 1;
-      const bool masked = tmax[t] > qpos_min;
+      const bool masked = tile_masked(t);
       if (masked && !load_tile_tp(t)) { ok = false; break; }
+      ATT_TRACE(2, 4000000 + i);
       if (!mbar_wait_bounded(&s_full[sb], (i >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      ATT_TRACE(2, 4100000 + i);
       tc_fence_after();
       uint32_t r[ATT_BN];
       tmem_ld_32x32b_x32(tmem_S0 + lane_base + (uint32_t)(sb * ATT_BN), r);
       tmem_ld_32x32b_x32(tmem_S0 + lane_base + (uint32_t)(sb * ATT_BN + 32), r + 32);
       tmem_ld_wait();
+      ATT_TRACE(2, 4200000 + i);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[sb]);
@@ -419,13 +480,13 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       uint32_t pk[ATT_BN / 2];
 #pragma unroll
       for (int e = 0; e < ATT_BN; e += 2) {
-        float p0 = fast_exp2(fmaf(__uint_as_float(r[e]), c, neg_lse2));
-        float p1 = fast_exp2(fmaf(__uint_as_float(r[e + 1]), c, neg_lse2));
-        if (!row_valid) p0 = p1 = 0.f;
-        pk[e >> 1] = pack_bf16x2(p0, p1);
+        const float2 x = ffma2(make_float2(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), c2, neg_lse2);
+        pk[e >> 1] = pack_bf16x2(fast_exp2(x.x), fast_exp2(x.y));
       }
       // the PV MMA of the previous tile must have finished reading P
+      ATT_TRACE(2, 4300000 + i);
       if (!mbar_wait_bounded(p_empty, (j & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_MISC)) { ok = false; break; }
+      ATT_TRACE(2, 4400000 + i);
 #pragma unroll
       for (int u = 0; u < ATT_BN / 8; ++u) {
         uint4 val = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
@@ -434,25 +495,26 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
+      ATT_TRACE(2, 4500000 + i);
       ++j;
       // column sums over this warp's 32 rows of the P tile (as rounded to bf16)
       if (wdst) {
-        float c0a = 0.f, c1a = 0.f, c0b = 0.f, c1b = 0.f;
+        float2 ca = make_float2(0.f, 0.f), cb = ca;
         const uint32_t coff = (uint32_t)((lane & 3) * 4);
         const int cu = lane >> 2;
 #pragma unroll 8
         for (int rr = 0; rr < 32; rr += 2) {
           const uint32_t w0 = *reinterpret_cast<const uint32_t*>(Ps + sw128_offset(quarter * 32 + rr, cu) + coff);
           const uint32_t w1 = *reinterpret_cast<const uint32_t*>(Ps + sw128_offset(quarter * 32 + rr + 1, cu) + coff);
-          c0a += __uint_as_float(w0 << 16);
-          c1a += __uint_as_float(w0 & 0xffff0000u);
-          c0b += __uint_as_float(w1 << 16);
-          c1b += __uint_as_float(w1 & 0xffff0000u);
+          ca = fadd2(ca, make_float2(__uint_as_float(w0 << 16), __uint_as_float(w0 & 0xffff0000u)));
+          cb = fadd2(cb, make_float2(__uint_as_float(w1 << 16), __uint_as_float(w1 & 0xffff0000u)));
         }
-        if (t * ATT_BN + 2 * lane < p.L) wdst[2 * lane] = c0a + c0b;
-        if (t * ATT_BN + 2 * lane + 1 < p.L) wdst[2 * lane + 1] = c1a + c1b;
+        ca = fadd2(ca, cb);
+        if (t * ATT_BN + 2 * lane < p.L) wdst[2 * lane] = ca.x;
+        if (t * ATT_BN + 2 * lane + 1 < p.L) wdst[2 * lane + 1] = ca.y;
         __syncwarp();  // all lanes have read the warp's rows before the next tile overwrites them
       }
+      ATT_TRACE(2, 4600000 + i);
     }
 
     // ---- epilogue: O (already normalised) -> bf16 -> out; lse
@@ -528,6 +590,18 @@ extern "C" int kvb_att_tile_minmax(const int32_t* token_pos, int32_t* tmin, int3
   return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
 }
 
+// Optional timeline trace of the forward kernel (diagnostics): `buf` holds 3 roles x `cap` events
+// x 2 int64 (tag, SM clock) and is filled by CTA 0 of every later kvb_sdpa_fwd launch of this
+// process; buf = NULL switches tracing off. Tags: 1e5 producer, 1e6+ QK issue, 2e6+ PV issue,
+// 3e6+ / 4e6+ softmax of sweep 1 / 2; the digits below 1e5 count tiles.
+static long long* g_att_trace = nullptr;
+static int g_att_trace_cap = 0;
+extern "C" int kvb_sdpa_fwd_set_trace(void* buf, int cap) {
+  g_att_trace = reinterpret_cast<long long*>(buf);
+  g_att_trace_cap = buf ? cap : 0;
+  return KVB_OK;
+}
+
 // Scratch layout (int32 words), provided by the caller:
 //   tile_min (B*G*nT) | tile_max (B*G*nT) | wpart (B*G*4*nQT*L floats, only if weights != NULL)
 extern "C" long long kvb_sdpa_fwd_scratch_bytes(int B, int H, int G, int q_len, int kv_len, int want_weights) {
@@ -568,6 +642,7 @@ extern "C" int kvb_sdpa_fwd(const void* q, const void* k, const void* v, const i
   p.out = (__nv_bfloat16*)out; p.lse = lse;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.input_pos = input_pos; p.status = status;
+  p.trace = g_att_trace; p.trace_cap = g_att_trace_cap;
 
   CUtensorMap tmQ, tmK, tmV;
   int rc;

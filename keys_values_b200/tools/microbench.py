@@ -1,7 +1,7 @@
 """Kernel micro-benchmarks: CUDA-event timing after warm-up, with an L2 flush
 (a write larger than the 126 MB L2) between timed iterations.
 
-    python -m keys_values_b200.tools.microbench sdpa|gemm|elementwise|all [--out file.jsonl]
+    python -m keys_values_b200.tools.microbench sdpa|sdpa_bwd|gemm|elementwise|all [--out file.jsonl]
 
 ``sdpa`` covers the SDPA-with-weights grid: bf16 GQA 32/8 heads, head size 128,
 batch 1 and 4, query length {1, 256, 2048}, KV length {4096, 16384, 32768}.
@@ -73,6 +73,37 @@ def bench_sdpa(out, peaks):
                 t_roof = max(flops / (peaks["bf16_tflops"] * 1e12), bytes_ / (peaks["hbm_gbs"] * 1e9))
                 out({"bench": "sdpa_w", "B": B, "q": q_len, "kv": kv, "us": ms * 1e3, "tflops": flops / ms / 1e9,
                      "frac_of_measured_roofline": t_roof / (ms / 1e3)})
+
+
+def bench_sdpa_bwd(out, peaks):
+    """Backward (dQ launch + dK/dV launch + delta kernel) on the training-chunk shapes: a chunk of
+    ``q`` new tokens against a cache of ``kv`` slots in random slot order."""
+    from keys_values_b200.ops import cuda as cu
+
+    dev = torch.device("cuda")
+    flush = _flush_buf(dev)
+    H, G, D = 32, 8, 128
+    scale = 1 / math.sqrt(D)
+    for B, q_len, kv in ((1, 1024, 16384), (1, 2048, 16384), (4, 1024, 16384), (1, 16384, 16384)):
+        q = torch.randn(B, H, q_len, D, device=dev, dtype=torch.bfloat16)
+        k = torch.randn(B, G, kv, D, device=dev, dtype=torch.bfloat16)
+        v = torch.randn(B, G, kv, D, device=dev, dtype=torch.bfloat16)
+        if q_len < kv:
+            tp = torch.stack([torch.stack([torch.randperm(kv, device=dev) for _ in range(G)]) for _ in range(B)]).to(torch.int32)
+            tp[:, :, :q_len] = (torch.arange(q_len, device=dev) + 2 * kv).to(torch.int32)
+            input_pos = 2 * kv
+        else:
+            tp, input_pos = None, 0
+        o, _, lse = cu.sdpa_fwd(q, k, v, scale, input_pos, tp, False)
+        go = torch.randn_like(o)
+        dk = torch.zeros(B, G, kv, D, device=dev)
+        dv = torch.zeros_like(dk)
+        ms = time_fn(lambda: cu.sdpa_bwd(go, q, k, v, o, lse, scale, input_pos, tp, dk, dv), flush=flush)
+        cu.check_status(dev)
+        vis = kv - q_len / 2
+        flops = 10.0 * B * H * q_len * vis * D  # five GEMMs of useful work
+        out({"bench": "sdpa_bwd", "B": B, "q": q_len, "kv": kv, "us": ms * 1e3, "tflops": flops / ms / 1e9,
+             "frac_of_measured_peak": flops / ms / 1e9 / peaks["bf16_tflops"]})
 
 
 def bench_gemm(out, peaks):
@@ -149,6 +180,8 @@ def main():
         bench_gemm(out, peaks)
     if args.which in ("sdpa", "all"):
         bench_sdpa(out, peaks)
+    if args.which in ("sdpa_bwd", "all"):
+        bench_sdpa_bwd(out, peaks)
     if args.which in ("elementwise", "all"):
         bench_elementwise(out, peaks)
 
