@@ -61,7 +61,19 @@ struct BwParams {
   float scale, scale_log2;
   int input_pos;
   int* status;
+  long long* trace;     // optional timeline of CTA 0: per role trace_cap (tag, clock) pairs
+  int trace_cap;
 };
+
+// Timeline event of one role (1 MMA issuer, 2 first compute warp) of CTA 0.
+#define BW_TRACE(role, tag)                                               \
+  do {                                                                    \
+    if (p.trace && blockIdx.x == 0 && tr_n < p.trace_cap) {               \
+      p.trace[((role) * p.trace_cap + tr_n) * 2] = (long long)(tag);      \
+      p.trace[((role) * p.trace_cap + tr_n) * 2 + 1] = clock64();         \
+      ++tr_n;                                                             \
+    }                                                                     \
+  } while (0)
 
 __device__ __forceinline__ float bw_exp2(float x) {
   float y;
@@ -112,9 +124,9 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
   uint64_t* pds_full = bars + 11;  // [2]
   uint64_t* acc_full = bars + 13;
   uint64_t* grp_bar = bars + 14;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* rows_ready = bars + 15;  // MODE_DQ: the row operands are in TMEM
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int32_t* stat_i = reinterpret_cast<int32_t*>(smem + S::STATS);       // MODE_DQ: token_pos of the KV tile
   float* stat_nlse = reinterpret_cast<float*>(smem + S::STATS + 512);  // MODE_DKV: [2][128] −lse·log2(e) of the query tile
   float* stat_ndls = reinterpret_cast<float*>(smem + S::STATS + 1536); // MODE_DKV: [2][128] −delta·scale of the query tile
 
@@ -160,6 +172,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
     }
     mbar_init(acc_full, 1);
     mbar_init(grp_bar, 256);
+    mbar_init(rows_ready, 8);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -172,7 +185,12 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   // X buffers: columns [0,64) and [64,128); Y buffers: [128,192) and [192,256); accumulators after
-  const uint32_t tmem_X = tmem_base, tmem_Y = tmem_base + 128, tmem_A1 = tmem_base + 256, tmem_A2 = tmem_base + 384;
+  // MODE_DQ has one accumulator only; the free 128 columns hold its row operands Q and dO as bf16
+  // pairs (64 columns each), so that the X / Y MMAs take A from TMEM and read only the streamed
+  // columns from shared memory.
+  const uint32_t tmem_X = tmem_base, tmem_Y = tmem_base + 128, tmem_A1 = tmem_base + 256;
+  const uint32_t tmem_A2 = tmem_base + (MODE == MODE_DQ ? 256 : 384);
+  const uint32_t tmem_R1 = tmem_base + 384, tmem_R2 = tmem_base + 448;  // MODE_DQ only
 
   int n_active = 0;
   for (int ct = 0; ct < n_col_tiles; ++ct) n_active += active(ct) ? 1 : 0;
@@ -235,24 +253,37 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
       const uint32_t cbase = smem_u32(smem + S::C);
       const uint32_t n_units = 2u * (uint32_t)n_active;
       bool ok = mbar_wait_bounded(r_full, 0, abort_flag, p.status, STATUS_TIMEOUT_FULL);
-      auto issue_xy = [&](uint32_t u) -> bool {
+      if (MODE == MODE_DQ && ok) {
+        ok = mbar_wait_bounded(rows_ready, 0, abort_flag, p.status, STATUS_TIMEOUT_FULL);
+        tc_fence_after();
+      }
+      int tr_n = 0;
+      auto wait_c = [&](uint32_t u) -> bool {
+        return mbar_wait_bounded(&c_full[u % BW_STAGES], (u / BW_STAGES) & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL);
+      };
+      auto issue_xy = [&](uint32_t u) -> bool {  // after wait_c(u)
         const uint32_t st = u % BW_STAGES, hb = u & 1;
-        if (!mbar_wait_bounded(&c_full[st], (u / BW_STAGES) & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL)) return false;
         tc_fence_after();
         const uint32_t c1 = cbase + st * 2 * BW_UNIT_BYTES, c2 = c1 + BW_UNIT_BYTES;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t a_off = (uint32_t)((kk >> 2) * (BW_TILE_BYTES / 2) + (kk & 3) * 32);
           const uint32_t b_off = (uint32_t)((kk >> 2) * (BW_UNIT_BYTES / 2) + (kk & 3) * 32);
-          umma_f16_ss(tmem_X + 64 * hb, make_smem_desc_sw128(r1 + a_off, 16, 1024), make_smem_desc_sw128(c1 + b_off, 16, 1024),
-                      idesc_xy, kk != 0);
+          if (MODE == MODE_DQ)
+            umma_f16_ts(tmem_X + 64 * hb, tmem_R1 + 8 * kk, make_smem_desc_sw128(c1 + b_off, 16, 1024), idesc_xy, kk != 0);
+          else
+            umma_f16_ss(tmem_X + 64 * hb, make_smem_desc_sw128(r1 + a_off, 16, 1024), make_smem_desc_sw128(c1 + b_off, 16, 1024),
+                        idesc_xy, kk != 0);
         }
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t a_off = (uint32_t)((kk >> 2) * (BW_TILE_BYTES / 2) + (kk & 3) * 32);
           const uint32_t b_off = (uint32_t)((kk >> 2) * (BW_UNIT_BYTES / 2) + (kk & 3) * 32);
-          umma_f16_ss(tmem_Y + 64 * hb, make_smem_desc_sw128(r2 + a_off, 16, 1024), make_smem_desc_sw128(c2 + b_off, 16, 1024),
-                      idesc_xy, kk != 0);
+          if (MODE == MODE_DQ)
+            umma_f16_ts(tmem_Y + 64 * hb, tmem_R2 + 8 * kk, make_smem_desc_sw128(c2 + b_off, 16, 1024), idesc_xy, kk != 0);
+          else
+            umma_f16_ss(tmem_Y + 64 * hb, make_smem_desc_sw128(r2 + a_off, 16, 1024), make_smem_desc_sw128(c2 + b_off, 16, 1024),
+                        idesc_xy, kk != 0);
         }
         umma_commit(&xy_full[hb]);
         return true;
@@ -260,6 +291,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
       auto issue_acc = [&](uint32_t u) -> bool {
         const uint32_t st = u % BW_STAGES, hb = u & 1;
         if (!mbar_wait_bounded(&pds_full[hb], (u >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL)) return false;
+        BW_TRACE(1, 1200000 + u);
         tc_fence_after();
         const uint32_t c1 = cbase + st * 2 * BW_UNIT_BYTES, c2 = c1 + BW_UNIT_BYTES;
 #pragma unroll
@@ -279,10 +311,20 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
         return true;
       };
       uint32_t ux = 0;
-      while (ok && ux < n_units && ux < 2) ok = issue_xy(ux++);
+      while (ok && ux < n_units && ux < 2) {
+        ok = wait_c(ux);
+        if (ok) ok = issue_xy(ux++);
+      }
       for (uint32_t u = 0; u < n_units && ok; ++u) {
-        ok = issue_acc(u);
+        // the columns of unit ux are awaited while the compute warps still work on unit u, so
+        // that only the wait for P / dS lies between them and the next MMAs
+        BW_TRACE(1, 1000000 + u);
+        if (ux < n_units) ok = wait_c(ux);
+        BW_TRACE(1, 1100000 + u);
+        if (ok) ok = issue_acc(u);
+        BW_TRACE(1, 1300000 + u);
         if (ok && ux < n_units) ok = issue_xy(ux++);
+        BW_TRACE(1, 1400000 + u);
       }
       if (ok) umma_commit(acc_full);
     }
@@ -297,6 +339,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     bool ok = n_active > 0;
     uint32_t s = 0, grp_phase = 0;
+    int tr_n = (warp == 2 && lane == 0) ? 0 : (1 << 30);  // only the first compute warp records
     auto group_sync = [&]() -> bool {
       mbar_arrive(grp_bar);
       const bool done = mbar_wait_bounded(grp_bar, grp_phase, abort_flag, p.status, STATUS_TIMEOUT_MISC);
@@ -336,6 +379,30 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
       if (tid < 128) stat_nlse[buf * 128 + tid] = v;
       else stat_ndls[buf * 128 + (tid - 128)] = v;
     };
+    if (MODE == MODE_DQ && ok) {
+      // row operands: shared memory -> registers -> TMEM. This thread moves features
+      // [64·hh, +64) of its row: one 128-byte swizzled row of chunk hh = 32 columns of bf16 pairs.
+      ok = mbar_wait_bounded(r_full, 0, abort_flag, p.status, STATUS_TIMEOUT_FULL);
+      if (ok) {
+#pragma unroll
+        for (int op = 0; op < 2; ++op) {
+          const uint8_t* src = smem + (op == 0 ? S::R1 : S::R2) + hh * (BW_TILE_BYTES / 2);
+          uint32_t w[32];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const uint4 q4 = *reinterpret_cast<const uint4*>(src + sw128_offset(row, u));
+            w[4 * u] = q4.x; w[4 * u + 1] = q4.y; w[4 * u + 2] = q4.z; w[4 * u + 3] = q4.w;
+          }
+          const uint32_t dst = (op == 0 ? tmem_R1 : tmem_R2) + lane_base + (uint32_t)(32 * hh);
+          tmem_st_32x32b_x16(dst, w);
+          tmem_st_32x32b_x16(dst + 16, w + 16);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(rows_ready);
+      }
+    }
     int ct = next_active(0);
     if (MODE == MODE_DKV && ok) {
       store_stat(0, fetch_stat(ct));
@@ -343,26 +410,25 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
     }
     const float2 c2 = make_float2(p.scale_log2, p.scale_log2);
     const float2 sc2 = make_float2(p.scale, p.scale);
+    const int32_t* tpp = p.token_pos ? p.token_pos + b * p.tp_sb + g * p.tp_sg : nullptr;
     while (ct < n_col_tiles && ok) {
       const bool msk = masked(ct);
       const int ct_next = next_active(ct + 1);
       float stat_next = 0.f;
-      if (MODE == MODE_DQ) {
-        if (msk) {
-          const int jj = ct * 128 + tid;
-          int v = INT_MAX;
-          if (tid < 128 && jj < p.L) v = p.token_pos ? p.token_pos[b * p.tp_sb + g * p.tp_sg + jj] : jj;
-          if (!group_sync()) { ok = false; break; }
-          if (tid < 128) stat_i[tid] = v;
-          if (!group_sync()) { ok = false; break; }
-        }
-      } else {
-        stat_next = fetch_stat(ct_next);  // in flight while this tile is processed
-      }
+      if (MODE == MODE_DKV) stat_next = fetch_stat(ct_next);  // in flight while this tile is processed
       const int sbuf = s & 1;
       const int cpos0 = p.input_pos + ct * p.npos;  // MODE_DKV: position of column cc is cpos0 + cc % npos
       for (int h = 0; h < 2 && ok; ++h) {
+        const int cc0 = 64 * h + 32 * hh;  // first column of this thread within the 128-column tile
+        // MODE_DQ: lane holds the token position of column cc0 + lane (asked for before the wait)
+        int v_tp = INT_MAX;
+        if (MODE == MODE_DQ && msk) {
+          const int jj = ct * 128 + cc0 + lane;
+          if (jj < p.L) v_tp = tpp ? tpp[jj] : jj;
+        }
+        BW_TRACE(2, 2000000 + 2 * s + h);
         if (!mbar_wait_bounded(&xy_full[h], s & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        BW_TRACE(2, 2100000 + 2 * s + h);
         tc_fence_after();
         const uint32_t xaddr = tmem_X + lane_base + (uint32_t)(64 * h + 32 * hh);
         const uint32_t yaddr = tmem_Y + lane_base + (uint32_t)(64 * h + 32 * hh);
@@ -370,7 +436,24 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
         tmem_ld_32x32b_x32(xaddr, xr);
         tmem_ld_32x32b_x32(yaddr, yr);
         tmem_ld_wait();
-        const int cc0 = 64 * h + 32 * hh;  // first column of this thread within the 128-column tile
+        BW_TRACE(2, 2200000 + 2 * s + h);
+        // bit e of `hide`: column cc0 + e is not visible to this thread's row
+        uint32_t hide = 0;
+        if (msk) {
+          if (MODE == MODE_DQ) {
+            // only columns beyond the first query of the CTA need the per-row comparison
+            // (positions broadcast by shuffle)
+            uint32_t nm = __ballot_sync(0xffffffffu, v_tp > qpos_min_of(rt));
+            while (nm) {
+              const int e = __ffs(nm) - 1;
+              nm &= nm - 1;
+              hide |= (uint32_t)(__shfl_sync(0xffffffffu, v_tp, e) > row_pos) << e;
+            }
+          } else if (__any_sync(0xffffffffu, row_tp > cpos0)) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) hide |= (uint32_t)(row_tp > cpos0 + ((cc0 + e) & (p.npos - 1))) << e;
+          }
+        }
         uint32_t pk[16], dk_[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
@@ -384,23 +467,14 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
           }
           const float2 xx = ffma2(make_float2(__uint_as_float(xr[e]), __uint_as_float(xr[e + 1])), c2, nl);
           float2 pp = make_float2(bw_exp2(xx.x), bw_exp2(xx.y));
-          if (msk) {
-            bool v0, v1;
-            if (MODE == MODE_DQ) {
-              v0 = stat_i[cc0 + e] <= row_pos;
-              v1 = stat_i[cc0 + e + 1] <= row_pos;
-            } else {
-              v0 = row_tp <= cpos0 + ((cc0 + e) % p.npos);
-              v1 = row_tp <= cpos0 + ((cc0 + e + 1) % p.npos);
-            }
-            if (!v0) pp.x = 0.f;
-            if (!v1) pp.y = 0.f;
-          }
+          if (hide & (1u << e)) pp.x = 0.f;
+          if (hide & (1u << (e + 1))) pp.y = 0.f;
           const float2 tt = ffma2(make_float2(__uint_as_float(yr[e]), __uint_as_float(yr[e + 1])), sc2, nd);
           const float2 ds = fmul2(pp, tt);
           pk[e >> 1] = pack_bf16x2(pp.x, pp.y);
           dk_[e >> 1] = pack_bf16x2(ds.x, ds.y);
         }
+        BW_TRACE(2, 2300000 + 2 * s + h);
         // P and dS go back into the first 16 columns of the 32 that this thread has just read
         if (MODE == MODE_DKV) tmem_st_32x32b_x16(xaddr, pk);
         tmem_st_32x32b_x16(yaddr, dk_);
@@ -408,6 +482,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&pds_full[h]);
+        BW_TRACE(2, 2400000 + 2 * s + h);
       }
       if (!ok) break;
       if (MODE == MODE_DKV) {
@@ -507,6 +582,19 @@ static int bw_make_tmap_4d(CUtensorMap* tm, const void* ptr, uint64_t d0, uint64
 extern "C" int kvb_att_tile_minmax(const int32_t* token_pos, int32_t* tmin, int32_t* tmax, int B, int G, int L, long long tp_sb,
                                    long long tp_sg, int tile, void* stream);
 
+// Optional timeline trace (diagnostics): `buf` holds 3 roles x `cap` events x 2 int64 (tag, SM clock),
+// filled by CTA 0 of the dQ launch (mode 0) or the dK/dV launch (mode 1) of every later kvb_sdpa_bwd
+// call of this process; buf = NULL switches tracing off. Tags: 1e6+ MMA issuer, 2e6+ compute warp;
+// the digits below 1e5 count 64-column units.
+static long long* g_bw_trace = nullptr;
+static int g_bw_trace_cap = 0, g_bw_trace_mode = 0;
+extern "C" int kvb_sdpa_bwd_set_trace(void* buf, int cap, int mode) {
+  g_bw_trace = reinterpret_cast<long long*>(buf);
+  g_bw_trace_cap = buf ? cap : 0;
+  g_bw_trace_mode = mode;
+  return KVB_OK;
+}
+
 // scratch: tile_min | tile_max (B*G*nT int32 each) | delta (B*H*T fp32)
 extern "C" long long kvb_sdpa_bwd_scratch_bytes(int B, int H, int G, int q_len, int kv_len) {
   const long long nT = (kv_len + 127) / 128;
@@ -564,7 +652,9 @@ extern "C" int kvb_sdpa_bwd(const void* q, const void* k, const void* v, const i
     cudaFuncSetAttribute(sdpa_bwd_kernel<MODE_DKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwSmem::TOTAL);
     attr_set = true;
   }
+  p.trace = g_bw_trace_mode == 0 ? g_bw_trace : nullptr; p.trace_cap = g_bw_trace_cap;
   sdpa_bwd_kernel<MODE_DQ><<<B * G * p.nQT, BW_THREADS, BwSmem::TOTAL, s>>>(tmQ, tmdO, tmKh, tmVh, p);
+  p.trace = g_bw_trace_mode == 1 ? g_bw_trace : nullptr;
   sdpa_bwd_kernel<MODE_DKV><<<B * G * p.nT, BW_THREADS, BwSmem::TOTAL, s>>>(tmK, tmV, tmQh, tmdOh, p);
   return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
 }

@@ -8,10 +8,15 @@
 // Design (bf16, head size 128):
 //   * CTA tile = 128 query rows = (128 / gs) consecutive positions x gs heads of one KV
 //     group (gs = H/G), so every K/V tile is loaded once per group, not once per head.
-//   * S = Q K^T (M=128, N=64) and O += P V (M=128, N=128) run on tcgen05.mma with S
-//     (double-buffered) and O in TMEM; K/V tiles of 64 slots arrive by TMA into 2-stage
-//     rings (128B swizzle; no multicast). V is consumed as an MN-major B operand.
-//   * A CTA uses 112.75 KB of shared memory and 256 TMEM columns, so two CTAs share an SM:
+//   * S = Q K^T (M=128, N=64) and O += P V (M=128, N=128) run on tcgen05.mma. Q is moved once
+//     from shared memory into TMEM and is the A operand of every QK MMA from there, so that
+//     those MMAs read only K from shared memory (operand traffic from shared memory, 128 B per
+//     clock, is what bounds tcgen05 at these tile sizes). S has one TMEM buffer: the softmax
+//     warps pull a tile into registers and hand the buffer back at once, so the next QK runs
+//     during their arithmetic. O stays in TMEM. K tiles of 64 slots arrive by TMA into a
+//     4-stage ring, V tiles into a 2-stage ring (128B swizzle; no multicast). V is consumed as
+//     an MN-major B operand.
+//   * A CTA uses 112.5 KB of shared memory and 256 TMEM columns, so two CTAs share an SM:
 //     while one waits on its MMA -> softmax -> MMA chain the other one issues.
 //   * Two sweeps over the KV tiles: sweep 1 computes the exact row log-sum-exp (online
 //     max / sum), sweep 2 recomputes S, forms the already-normalised P = exp2(S·c − lse),
@@ -21,7 +26,9 @@
 //     no atomics, hence run-to-run identical eviction decisions.
 //   * KV tiles whose smallest token position lies beyond the last query of the CTA are
 //     skipped by every role; tiles that contain no position beyond the first query of
-//     the CTA take the mask-free path.
+//     the CTA take the mask-free path. In a masked tile only the columns whose token lies
+//     beyond the first query need a per-row comparison; their positions travel by warp
+//     shuffle and end up as a 64-bit mask per row, without shared memory or block barriers.
 //   * warp 0 = TMA producer, warp 1 = MMA issuer / TMEM owner, warps 2..5 = softmax +
 //     epilogue: each thread owns one query row (its TMEM lane) of every tile.
 //
@@ -46,21 +53,22 @@ constexpr int ATT_THREADS = 192;  // TMA warp + MMA warp + 4 softmax warps; two 
 constexpr int ATT_Q_BYTES = ATT_BM * ATT_D * 2;    // 32 KB: two 64-feature chunks of [128 rows x 128 B]
 constexpr int ATT_KV_BYTES = ATT_BN * ATT_D * 2;   // 16 KB: two 64-feature chunks of [64 rows x 128 B]
 constexpr int ATT_P_BYTES = ATT_BM * ATT_BN * 2;   // 16 KB: one 64-column chunk of [128 rows x 128 B]
-constexpr int ATT_TMEM_COLS = 256;                 // S0 | S1 (64 columns each) | O (128 columns)
+constexpr int ATT_TMEM_COLS = 256;                 // Q as bf16 pairs (64 columns) | S (64) | O (128)
+constexpr int ATT_KSTAGES = 4;
 
-// Shared memory of one CTA: 112.75 KB, so that two CTAs fit into the 228 KB of an SM (each
+// Shared memory of one CTA: 112.5 KB, so that two CTAs fit into the 228 KB of an SM (each
 // CTA also costs 1 KB of system reserve). The dynamic shared memory window must be 1024-byte
 // aligned for the 128B-swizzled tiles; the kernel checks this and reports instead of running.
 struct AttSmem {
-  static constexpr int Q = 0;
-  static constexpr int K = Q + ATT_Q_BYTES;
-  static constexpr int V = K + 2 * ATT_KV_BYTES;
+  static constexpr int K = 0;                              // ring of ATT_KSTAGES K tiles
+  static constexpr int Q = K + 2 * ATT_KV_BYTES;           // Q lands in K stages 2, 3 and moves on to TMEM
+  static constexpr int V = K + ATT_KSTAGES * ATT_KV_BYTES; // ring of 2 V tiles
   static constexpr int P = V + 2 * ATT_KV_BYTES;
-  static constexpr int TP = P + ATT_P_BYTES;   // 64 int32 token positions of the current tile
-  static constexpr int TF = TP + 256;          // 2 bits per KV tile (active, masked) for the first 1024 tiles
+  static constexpr int TF = P + ATT_P_BYTES;   // 2 bits per KV tile (active, masked) for the first 1024 tiles
   static constexpr int BAR = TF + 256;
   static constexpr int TOTAL = BAR + 256;
 };
+static_assert(ATT_Q_BYTES == 2 * ATT_KV_BYTES, "Q must fit into two K stages");
 
 struct AttParams {
   const int32_t* token_pos;  // (B,G,L) with strides tp_sb, tp_sg, or nullptr (slot j holds token j)
@@ -150,19 +158,18 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + AttSmem::BAR);
   uint64_t* q_full = bars + 0;
-  uint64_t* k_full = bars + 1;   // [2]
-  uint64_t* k_empty = bars + 3;  // [2]
-  uint64_t* v_full = bars + 5;   // [2]
-  uint64_t* v_empty = bars + 7;  // [2]
-  uint64_t* s_full = bars + 9;   // [2]
-  uint64_t* s_empty = bars + 11; // [2]
-  uint64_t* p_full = bars + 13;
-  uint64_t* p_empty = bars + 14;
-  uint64_t* o_full = bars + 15;
-  uint64_t* grp_bar = bars + 16;  // barrier among the 128 softmax threads (bounded, unlike bar.sync)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+  uint64_t* k_full = bars + 1;    // [4]
+  uint64_t* k_empty = bars + 5;   // [4]
+  uint64_t* v_full = bars + 9;    // [2]
+  uint64_t* v_empty = bars + 11;  // [2]
+  uint64_t* s_full = bars + 13;
+  uint64_t* s_empty = bars + 14;
+  uint64_t* p_full = bars + 15;
+  uint64_t* p_empty = bars + 16;
+  uint64_t* o_full = bars + 17;
+  uint64_t* q_ready = bars + 18;  // Q has been moved from shared memory to TMEM
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int32_t* tp_s = reinterpret_cast<int32_t*>(smem + AttSmem::TP);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // block -> (query tile, group, batch); query tiles fastest so that co-resident CTAs share K/V in L2
@@ -188,27 +195,33 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
     tflags[w] = bits;
   }
-  auto tile_active = [&](int t) -> bool {
-    return t < TF_TILES ? ((tflags[t >> 4] >> ((t & 15) * 2)) & 1u) != 0 : tmin[t] <= qpos_max;
-  };
-  auto tile_masked = [&](int t) -> bool {
-    return t < TF_TILES ? ((tflags[t >> 4] >> ((t & 15) * 2)) & 2u) != 0 : tmax[t] > qpos_min;
+  // bit 0: active, bit 1: masked. Shared memory is slow to reach while the tensor core streams its
+  // operands from it, so each role keeps the word of 16 tiles in a register.
+  auto tile_bits = [&](int t, uint32_t& fw, int& fwi) -> uint32_t {
+    if (t >= TF_TILES) return (uint32_t)(tmin[t] <= qpos_max) | ((uint32_t)(tmax[t] > qpos_min) << 1);
+    if ((t >> 4) != fwi) {
+      fwi = t >> 4;
+      fw = tflags[fwi];
+    }
+    return (fw >> ((t & 15) * 2)) & 3u;
   };
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < ATT_KSTAGES; ++s) {
       mbar_init(&k_full[s], 1);
       mbar_init(&k_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
       mbar_init(&v_full[s], 1);
       mbar_init(&v_empty[s], 1);
-      mbar_init(&s_full[s], 1);
-      mbar_init(&s_empty[s], 4);
     }
+    mbar_init(s_full, 1);
+    mbar_init(s_empty, 4);
     mbar_init(p_full, 4);
     mbar_init(p_empty, 1);
     mbar_init(o_full, 1);
-    mbar_init(grp_bar, 128);
+    mbar_init(q_ready, 4);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -220,8 +233,12 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_S0 = tmem_base;          // S buffers: columns [0,64) and [64,128)
-  const uint32_t tmem_O = tmem_base + 128;     // O: columns [128,256)
+  // Q stays in TMEM as the A operand of S = Q K^T, so that each QK MMA reads only K from shared
+  // memory. S has one buffer: the softmax warps pull a tile into registers and hand the buffer
+  // back at once, so that the next QK runs during their arithmetic.
+  const uint32_t tmem_Q = tmem_base;           // columns [0,64): 128 features as bf16 pairs
+  const uint32_t tmem_S = tmem_base + 64;      // columns [64,128)
+  const uint32_t tmem_O = tmem_base + 128;     // columns [128,256)
 
   int n_active = 0;
   for (int w = 0; w < TF_TILES / 16; ++w) n_active += __popc(tflags[w] & 0x55555555u);
@@ -239,11 +256,15 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       uint32_t i = 0, j = 0;
       bool ok = true;
       int tr_n = 0;
+      uint32_t fw = 0;
+      int fwi = -1;
       for (int sweep = 0; sweep < 2 && ok; ++sweep) {
         for (int t = 0; t < p.nT && ok; ++t) {
-          if (!tile_active(t)) continue;
-          const int ks = i & 1;
-          if (!mbar_wait_bounded(&k_empty[ks], ((i >> 1) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) { ok = false; break; }
+          if (!(tile_bits(t, fw, fwi) & 1u)) continue;
+          const int ks = i % ATT_KSTAGES;
+          // stages 2 and 3 first hold Q
+          if (i == 2 && !mbar_wait_bounded(q_ready, 0, abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) { ok = false; break; }
+          if (!mbar_wait_bounded(&k_empty[ks], ((i / ATT_KSTAGES) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) { ok = false; break; }
           ATT_TRACE(0, 100000 + sweep * 50000 + t);
           uint8_t* kd = smem + AttSmem::K + ks * ATT_KV_BYTES;
           mbar_expect_tx(&k_full[ks], ATT_KV_BYTES);
@@ -272,30 +293,28 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (lane == 0 && n_active > 0) {
       constexpr uint32_t idesc_qk = make_idesc_bf16(ATT_BM, ATT_BN, 0, 0);  // Q, K both K-major
       constexpr uint32_t idesc_pv = make_idesc_bf16(ATT_BM, ATT_D, 0, 1);   // P K-major, V MN-major
-      const uint32_t q_addr = smem_u32(smem + AttSmem::Q);
       const uint32_t p_addr = smem_u32(smem + AttSmem::P);
-      bool ok = mbar_wait_bounded(q_full, 0, abort_flag, p.status, STATUS_TIMEOUT_FULL);
+      bool ok = mbar_wait_bounded(q_ready, 0, abort_flag, p.status, STATUS_TIMEOUT_FULL);
+      tc_fence_after();
       uint32_t i = 0, j = 0;
       int tr_n = 0;
       auto issue_qk = [&]() -> bool {
-        const int ks = i & 1;
+        const int ks = i % ATT_KSTAGES;
         ATT_TRACE(1, 1000000 + i);
-        if (!mbar_wait_bounded(&k_full[ks], (i >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL)) return false;
+        if (!mbar_wait_bounded(&k_full[ks], (i / ATT_KSTAGES) & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL)) return false;
         ATT_TRACE(1, 1100000 + i);
-        if (!mbar_wait_bounded(&s_empty[ks], ((i >> 1) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) return false;
+        if (!mbar_wait_bounded(s_empty, (i & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) return false;
         ATT_TRACE(1, 1200000 + i);
         tc_fence_after();
         const uint32_t k_addr = smem_u32(smem + AttSmem::K + ks * ATT_KV_BYTES);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          // 16 features per step: chunk kk/4 of the operand, 32 bytes per step inside the swizzled row
-          const uint32_t q_off = (uint32_t)((kk >> 2) * (ATT_Q_BYTES / 2) + (kk & 3) * 32);
+          // 16 features per step: 8 TMEM columns of Q; chunk kk/4 of K, 32 bytes per step inside the swizzled row
           const uint32_t k_off = (uint32_t)((kk >> 2) * (ATT_KV_BYTES / 2) + (kk & 3) * 32);
-          umma_f16_ss(tmem_S0 + (uint32_t)(ks * ATT_BN), make_smem_desc_sw128(q_addr + q_off, 16, 1024),
-                      make_smem_desc_sw128(k_addr + k_off, 16, 1024), idesc_qk, kk != 0);
+          umma_f16_ts(tmem_S, tmem_Q + 8 * kk, make_smem_desc_sw128(k_addr + k_off, 16, 1024), idesc_qk, kk != 0);
         }
         umma_commit(&k_empty[ks]);
-        umma_commit(&s_full[ks]);
+        umma_commit(s_full);
         ATT_TRACE(1, 1300000 + i);
         ++i;
         return true;
@@ -303,9 +322,10 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       auto issue_pv = [&]() -> bool {
         const int vs = j & 1;
         ATT_TRACE(1, 2000000 + j);
-        if (!mbar_wait_bounded(p_full, j & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL)) return false;
-        ATT_TRACE(1, 2100000 + j);
+        // V first: it does not depend on the softmax, so only the wait for P is on the critical path
         if (!mbar_wait_bounded(&v_full[vs], (j >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL)) return false;
+        ATT_TRACE(1, 2100000 + j);
+        if (!mbar_wait_bounded(p_full, j & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL)) return false;
         ATT_TRACE(1, 2200000 + j);
         tc_fence_after();
         const uint32_t v_addr = smem_u32(smem + AttSmem::V + vs * ATT_KV_BYTES);
@@ -325,14 +345,16 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         return true;
       };
       // sweep 1: S only
+      uint32_t fw = 0;
+      int fwi = -1;
       for (int t = 0; t < p.nT && ok; ++t) {
-        if (!tile_active(t)) continue;
+        if (!(tile_bits(t, fw, fwi) & 1u)) continue;
         ok = issue_qk();
       }
       // sweep 2: QK of the next tile is issued before PV of the current one
       bool pending = false;
       for (int t = 0; t < p.nT && ok; ++t) {
-        if (!tile_active(t)) continue;
+        if (!(tile_bits(t, fw, fwi) & 1u)) continue;
         ok = issue_qk();
         if (ok && pending) ok = issue_pv();
         pending = true;
@@ -351,32 +373,40 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int tq = t0 + pl;
     const bool row_valid = tq < p.T;
     const int my_pos = p.input_pos + tq;
-    const int sm_tid = threadIdx.x - 64;          // 0..127
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     const float c = p.scale_log2;
     const float2 c2 = make_float2(c, c);
     bool ok = n_active > 0;
     uint32_t i = 0, j = 0;
     float m = -1e30f, l = 0.f;
-    uint32_t grp_phase = 0;
     int tr_n = (warp == 2 && lane == 0) ? 0 : (1 << 30);  // only the first softmax warp records
-    // barrier among the softmax threads; false if it ran into the wait limit
-    auto group_sync = [&]() -> bool {
-      mbar_arrive(grp_bar);
-      const bool done = mbar_wait_bounded(grp_bar, grp_phase, abort_flag, p.status, STATUS_TIMEOUT_MISC);
-      grp_phase ^= 1;
-      return done;
+    uint32_t fw = 0;
+    int fwi = -1;
+    // Token positions of a tile: lane holds columns lane and lane + 32 (INT_MAX beyond the cache).
+    // The positions of the next tile are fetched one tile ahead.
+    const int32_t* tpp = p.token_pos ? p.token_pos + b * p.tp_sb + g * p.tp_sg : nullptr;
+    auto fetch_tp = [&](int t, int& v0, int& v1) {
+      const int j0 = t * ATT_BN + lane, j1 = j0 + 32;
+      v0 = j0 < p.L ? (tpp ? tpp[j0] : j0) : INT_MAX;
+      v1 = j1 < p.L ? (tpp ? tpp[j1] : j1) : INT_MAX;
     };
-    auto load_tile_tp = [&](int t) -> bool {
-      // token positions of tile t -> smem (INT_MAX beyond the end of the cache)
-      int v = INT_MAX;
-      if (sm_tid < ATT_BN) {
-        const int jj = t * ATT_BN + sm_tid;
-        if (jj < p.L) v = p.token_pos ? p.token_pos[b * p.tp_sb + g * p.tp_sg + jj] : jj;
+    int pf0 = INT_MAX, pf1 = INT_MAX, pf_t = -1;
+    // Mask bits of this thread's row for a masked tile (bit e of mlo / mhi: column e / 32 + e is
+    // hidden). Only columns whose token lies beyond the first query of the CTA need the per-row
+    // comparison; their positions are broadcast by shuffle, so no shared memory is involved.
+    auto row_mask = [&](int v0, int v1, uint32_t& mlo, uint32_t& mhi) {
+      uint32_t n0 = __ballot_sync(0xffffffffu, v0 > qpos_min), n1 = __ballot_sync(0xffffffffu, v1 > qpos_min);
+      mlo = mhi = 0;
+      while (n0) {
+        const int e = __ffs(n0) - 1;
+        n0 &= n0 - 1;
+        mlo |= (uint32_t)(__shfl_sync(0xffffffffu, v0, e) > my_pos) << e;
       }
-      if (!group_sync()) return false;  // previous readers of tp_s are done
-      if (sm_tid < ATT_BN) tp_s[sm_tid] = v;
-      return group_sync();
+      while (n1) {
+        const int e = __ffs(n1) - 1;
+        n1 &= n1 - 1;
+        mhi |= (uint32_t)(__shfl_sync(0xffffffffu, v1, e) > my_pos) << e;
+      }
     };
     // column-sum partials: slot (4·qt + warp quarter) of wpart (B,G,4·nQT,L). A warp sums the 32
     // rows that it wrote itself, so the column sums need no barrier among the warps; lane ->
@@ -387,30 +417,60 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
     const uint32_t NEG_INF_BITS = 0xff800000u;
 
+    // ---- Q: shared memory -> registers -> TMEM (row = lane; feature pair f/2 = column)
+    if (ok) ok = mbar_wait_bounded(q_full, 0, abort_flag, p.status, STATUS_TIMEOUT_FULL);
+    if (ok) {
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch) {
+        const uint8_t* src = smem + AttSmem::Q + ch * (ATT_Q_BYTES / 2);
+        uint32_t w[32];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const uint4 q4 = *reinterpret_cast<const uint4*>(src + sw128_offset(row, u));
+          w[4 * u] = q4.x; w[4 * u + 1] = q4.y; w[4 * u + 2] = q4.z; w[4 * u + 3] = q4.w;
+        }
+        tmem_st_32x32b_x16(tmem_Q + lane_base + (uint32_t)(32 * ch), w);
+        tmem_st_32x32b_x16(tmem_Q + lane_base + (uint32_t)(32 * ch + 16), w + 16);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(q_ready);
+    }
+
     // ---- sweep 1: exact row max and sum
     for (int t = 0; t < p.nT && ok; ++t) {
-      if (!tile_active(t)) continue;
-      const int sb = i & 1;
-      const bool masked = tile_masked(t);
-      if (masked && !load_tile_tp(t)) { ok = false; break; }
+      const uint32_t tb = tile_bits(t, fw, fwi);
+      if (!(tb & 1u)) continue;
+      const bool masked = (tb & 2u) != 0;
+      int v0 = pf0, v1 = pf1;
+      if (masked && pf_t != t) fetch_tp(t, v0, v1);
+      if (t + 1 < p.nT) {
+        fetch_tp(t + 1, pf0, pf1);
+        pf_t = t + 1;
+      }
       ATT_TRACE(2, 3000000 + i);
-      if (!mbar_wait_bounded(&s_full[sb], (i >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      if (!mbar_wait_bounded(s_full, i & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       ATT_TRACE(2, 3100000 + i);
       tc_fence_after();
       uint32_t r[ATT_BN];
-      tmem_ld_32x32b_x32(tmem_S0 + lane_base + (uint32_t)(sb * ATT_BN), r);
-      tmem_ld_32x32b_x32(tmem_S0 + lane_base + (uint32_t)(sb * ATT_BN + 32), r + 32);
+      tmem_ld_32x32b_x32(tmem_S + lane_base, r);
+      tmem_ld_32x32b_x32(tmem_S + lane_base + 32u, r + 32);
       tmem_ld_wait();
       ATT_TRACE(2, 3200000 + i);
       // the tile is in registers: hand the S buffer back before the arithmetic
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty[sb]);
+      if (lane == 0) mbar_arrive(s_empty);
       ++i;
       if (masked) {
+        uint32_t mlo, mhi;
+        row_mask(v0, v1, mlo, mhi);
 #pragma unroll
-        for (int e = 0; e < ATT_BN; ++e)
-          if (tp_s[e] > my_pos) r[e] = NEG_INF_BITS;
+        for (int e = 0; e < 32; ++e) {
+          if (mlo & (1u << e)) r[e] = NEG_INF_BITS;
+          if (mhi & (1u << e)) r[32 + e] = NEG_INF_BITS;
+        }
       }
       // max of the raw scores (the scale is positive): four independent chains of 3-input max
       float a0 = -INFINITY, a1 = -INFINITY, a2 = -INFINITY, a3 = -INFINITY;
@@ -449,33 +509,42 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     uint8_t* Ps = smem + AttSmem::P;
     for (int t = 0; t < p.nT && ok; ++t) {
       float* wdst = wbase ? wbase + (long long)t * ATT_BN : nullptr;
-      if (!tile_active(t)) {
+      const uint32_t tb = tile_bits(t, fw, fwi);
+      if (!(tb & 1u)) {
         if (wdst) {
           if (t * ATT_BN + 2 * lane < p.L) wdst[2 * lane] = 0.f;
           if (t * ATT_BN + 2 * lane + 1 < p.L) wdst[2 * lane + 1] = 0.f;
         }
         continue;
       }
-      const int sb = i & 1;
-      const bool masked = tile_masked(t);
-      if (masked && !load_tile_tp(t)) { ok = false; break; }
+      const bool masked = (tb & 2u) != 0;
+      int v0 = pf0, v1 = pf1;
+      if (masked && pf_t != t) fetch_tp(t, v0, v1);
+      if (t + 1 < p.nT) {
+        fetch_tp(t + 1, pf0, pf1);
+        pf_t = t + 1;
+      }
       ATT_TRACE(2, 4000000 + i);
-      if (!mbar_wait_bounded(&s_full[sb], (i >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      if (!mbar_wait_bounded(s_full, i & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       ATT_TRACE(2, 4100000 + i);
       tc_fence_after();
       uint32_t r[ATT_BN];
-      tmem_ld_32x32b_x32(tmem_S0 + lane_base + (uint32_t)(sb * ATT_BN), r);
-      tmem_ld_32x32b_x32(tmem_S0 + lane_base + (uint32_t)(sb * ATT_BN + 32), r + 32);
+      tmem_ld_32x32b_x32(tmem_S + lane_base, r);
+      tmem_ld_32x32b_x32(tmem_S + lane_base + 32u, r + 32);
       tmem_ld_wait();
       ATT_TRACE(2, 4200000 + i);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty[sb]);
+      if (lane == 0) mbar_arrive(s_empty);
       ++i;
       if (masked) {
+        uint32_t mlo, mhi;
+        row_mask(v0, v1, mlo, mhi);
 #pragma unroll
-        for (int e = 0; e < ATT_BN; ++e)
-          if (tp_s[e] > my_pos) r[e] = NEG_INF_BITS;
+        for (int e = 0; e < 32; ++e) {
+          if (mlo & (1u << e)) r[e] = NEG_INF_BITS;
+          if (mhi & (1u << e)) r[32 + e] = NEG_INF_BITS;
+        }
       }
       uint32_t pk[ATT_BN / 2];
 #pragma unroll
@@ -502,7 +571,7 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         float2 ca = make_float2(0.f, 0.f), cb = ca;
         const uint32_t coff = (uint32_t)((lane & 3) * 4);
         const int cu = lane >> 2;
-#pragma unroll 8
+#pragma unroll
         for (int rr = 0; rr < 32; rr += 2) {
           const uint32_t w0 = *reinterpret_cast<const uint32_t*>(Ps + sw128_offset(quarter * 32 + rr, cu) + coff);
           const uint32_t w1 = *reinterpret_cast<const uint32_t*>(Ps + sw128_offset(quarter * 32 + rr + 1, cu) + coff);
