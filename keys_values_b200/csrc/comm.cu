@@ -7,12 +7,12 @@
 // cudaIpcOpenMemHandle (handle exchange happens in Python over torch.distributed). A
 // small flag area at the end of each arena carries the inter-GPU barriers.
 //
-// kvb_allreduce_mean: in-place two-shot all-reduce of a slice of the arena, fused with
-// the 1/world scale and the dtype cast:
-//   barrier  ->  reduce-scatter: rank r sums shard r of all ranks (fp32, fixed rank order,
-//   so every run gives identical bits) and writes scale·sum into shard r of its own arena
-//   barrier  ->  all-gather: rank r copies shard q from rank q, for all q != r
-//   barrier  (nobody overwrites a slice that a peer may still be reading)
+// kvb_allreduce_mean: in-place all-reduce of a slice of the arena, fused with the 1/world
+// scale and the dtype cast:
+//   barrier  ->  rank r pulls shard r from all ranks (several 16-byte loads per peer in flight
+//   per thread), sums in fp32 in a fixed rank order, so every run and every rank gives identical
+//   bits, and pushes scale·sum into shard r of every rank's arena (posted stores)
+//   barrier  (nobody reads its arena before every push has landed)
 // Every wait is bounded: on timeout the kernel records STATUS_TIMEOUT_PEER_FLAG and
 // returns.
 //
@@ -113,43 +113,63 @@ __device__ bool cross_gpu_barrier(const CommPeers& peers, int rank, int world, u
   return ok_s != 0;
 }
 
+// Vectors of 16 bytes that one thread keeps in flight per peer. Remote loads take a few
+// microseconds, so the bandwidth of the reduction is (bytes in flight) / latency.
+constexpr int COMM_UNROLL = 4;
+
 template <typename T>
 __global__ void __launch_bounds__(COMM_THREADS)
 allreduce_mean_kernel(CommPeers peers, int rank, int world, long long start, long long count, float scale, uint32_t epoch0,
                       uint32_t* sync, int* status, long long limit) {
   constexpr int V = 16 / sizeof(T);
+  constexpr int U = COMM_UNROLL;
   if (!cross_gpu_barrier(peers, rank, world, epoch0, sync, status, limit)) return;
   // shards in units of 16-byte vectors
   const long long nvec = count / V;
   const long long per = (nvec + world - 1) / world;
   const long long v0 = min(per * rank, nvec), v1 = min(v0 + per, nvec);
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long i = v0 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < v1; i += stride) {
-    float acc[V];
+  const long long step = (long long)gridDim.x * blockDim.x * U;
+  // pull shard `rank` from every rank (U loads per peer in flight), reduce in fp32 in a fixed
+  // rank order, push scale * sum into shard `rank` of every rank
+  for (long long base = v0 + (long long)blockIdx.x * blockDim.x * U; base < v1; base += step) {
+    float acc[U][V];
 #pragma unroll
-    for (int j = 0; j < V; ++j) acc[j] = 0.f;
+    for (int k = 0; k < U; ++k)
+#pragma unroll
+      for (int j = 0; j < V; ++j) acc[k][j] = 0.f;
     for (int r = 0; r < world; ++r) {
-      const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(peers.base[r]) + start + i * V));
-      const T* e = reinterpret_cast<const T*>(&raw);
+      const T* src = reinterpret_cast<const T*>(peers.base[r]) + start;
+      uint4 raw[U];
 #pragma unroll
-      for (int j = 0; j < V; ++j) acc[j] += to_f32(e[j]);
-    }
-    uint4 outv;
-    T* o = reinterpret_cast<T*>(&outv);
+      for (int k = 0; k < U; ++k) {
+        const long long i = base + (long long)k * blockDim.x + threadIdx.x;
+        raw[k] = i < v1 ? __ldcg(reinterpret_cast<const uint4*>(src + i * V)) : make_uint4(0, 0, 0, 0);
+      }
 #pragma unroll
-    for (int j = 0; j < V; ++j) o[j] = from_f32<T>(acc[j] * scale);
-    *reinterpret_cast<uint4*>(reinterpret_cast<T*>(peers.base[rank]) + start + i * V) = outv;
-  }
-  if (!cross_gpu_barrier(peers, rank, world, epoch0 + 1, sync, status, limit)) return;
-  for (int q = 1; q < world; ++q) {
-    const int src = (rank + q) % world;
-    const long long s0 = min(per * src, nvec), s1 = min(s0 + per, nvec);
-    for (long long i = s0 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < s1; i += stride) {
-      const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(peers.base[src]) + start + i * V));
-      *reinterpret_cast<uint4*>(reinterpret_cast<T*>(peers.base[rank]) + start + i * V) = raw;
+      for (int k = 0; k < U; ++k) {
+        const T* e = reinterpret_cast<const T*>(&raw[k]);
+#pragma unroll
+        for (int j = 0; j < V; ++j) acc[k][j] += to_f32(e[j]);
+      }
+    }
+    uint4 outv[U];
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      T* o = reinterpret_cast<T*>(&outv[k]);
+#pragma unroll
+      for (int j = 0; j < V; ++j) o[j] = from_f32<T>(acc[k][j] * scale);
+    }
+    for (int q = 0; q < world; ++q) {
+      T* dst = reinterpret_cast<T*>(peers.base[(rank + q) % world]) + start;
+#pragma unroll
+      for (int k = 0; k < U; ++k) {
+        const long long i = base + (long long)k * blockDim.x + threadIdx.x;
+        if (i < v1) *reinterpret_cast<uint4*>(dst + i * V) = outv[k];
+      }
     }
   }
-  cross_gpu_barrier(peers, rank, world, epoch0 + 2, sync, status, limit);
+  // nobody returns before every rank's pushes have landed
+  cross_gpu_barrier(peers, rank, world, epoch0 + 1, sync, status, limit);
 }
 
 }  // namespace kvb
@@ -190,7 +210,13 @@ extern "C" int kvb_allreduce_mean(void* const* bases, void* const* flags, int ra
     peers.flags[r] = reinterpret_cast<uint32_t*>(flags[r]);
   }
   const long long limit = (long long)(timeout_s * 1.9e9);
-  if (n_ctas <= 0) n_ctas = 32;
+  if (n_ctas <= 0) {
+    // enough CTAs to cover the shard once, between 4 and one per SM (all must be co-resident)
+    const long long esz = dtype == 0 ? 4 : 2;
+    const long long vec_per_rank = (count * esz / 16 + world - 1) / world;
+    const long long want = (vec_per_rank + (long long)COMM_THREADS * COMM_UNROLL - 1) / ((long long)COMM_THREADS * COMM_UNROLL);
+    n_ctas = (int)(want < 4 ? 4 : (want > 148 ? 148 : want));
+  }
   cudaStream_t s = (cudaStream_t)stream;
   switch (dtype) {
     case 0:

@@ -87,7 +87,9 @@ struct GemmSmem {
   static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
   static constexpr int B_BYTES = BN * GEMM_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int BAR_OFFSET = GEMM_STAGES * STAGE_BYTES;
+  static constexpr int EPI_OFFSET = GEMM_STAGES * STAGE_BYTES;   // per epilogue warp: 32 rows x 128 B staging
+  static constexpr int EPI_BYTES = 4 * 32 * 128;
+  static constexpr int BAR_OFFSET = EPI_OFFSET + EPI_BYTES;
   static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // barriers + alignment slack
 };
 
@@ -127,10 +129,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const long long total = (long long)ex.rows_per_chunk * vec_per_row;
       const __nv_bfloat16* sp = ex.ag_src[src];
       __nv_bfloat16* dp = ex.ag_stage + (long long)src * ex.rows_per_chunk * ex.ag_ld;
-      for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)ex.ag_copy_ctas * blockDim.x) {
-        const long long r = i / vec_per_row, c = i % vec_per_row;
-        const uint4 v = __ldcg(reinterpret_cast<const uint4*>(sp + r * ex.ag_ld + c * 8));
-        *reinterpret_cast<uint4*>(dp + r * ex.ag_ld + c * 8) = v;
+      // remote loads take microseconds: keep 16 of them in flight per thread
+      constexpr int CU = 16;
+      const long long cstride = (long long)ex.ag_copy_ctas * blockDim.x;
+      const bool contig = ex.ag_ld == (long long)K;  // rows back to back: element offset = 8 i
+      const unsigned vpr = (unsigned)vec_per_row;
+      auto elem_off = [&](long long i) -> long long {
+        if (contig) return i * 8;
+        const unsigned r = (unsigned)i / vpr, c = (unsigned)i % vpr;  // a shard has far fewer than 2^32 vectors
+        return (long long)r * ex.ag_ld + (long long)c * 8;
+      };
+      for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < total; i0 += cstride * CU) {
+        uint4 v[CU];
+#pragma unroll
+        for (int k = 0; k < CU; ++k) {
+          const long long i = i0 + k * cstride;
+          if (i < total) v[k] = __ldcg(reinterpret_cast<const uint4*>(sp + elem_off(i)));
+        }
+#pragma unroll
+        for (int k = 0; k < CU; ++k) {
+          const long long i = i0 + k * cstride;
+          if (i < total) *reinterpret_cast<uint4*>(dp + elem_off(i)) = v[k];
+        }
       }
       __threadfence();
       __syncthreads();
@@ -332,44 +352,60 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         out_row = (long long)ex.rs_rank * ex.rows_per_rank + (m - dest * ex.rows_per_rank);
       }
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+      // 64 columns at a time: thread = row converts its 128 bytes, the warp exchanges them through
+      // shared memory (16-byte units XOR-swizzled by row, conflict-free both ways) and stores 4 rows
+      // x 128 contiguous bytes per instruction. Peer memory in particular wants long contiguous
+      // writes: a row-per-thread store pattern crosses NVLink in 16-byte pieces.
+      uint8_t* stg = smem + S::EPI_OFFSET + quarter * (32 * 128);
+      const int m_warp0 = m0 + quarter * 32;  // first row of this warp
+      const long long out_row0 = out_row - lane;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(taddr + (uint32_t)c0, r);
-        tmem_ld_wait();
+      for (int c0 = 0; c0 < BN; c0 += 64) {
         const int n = n0 + c0;
-        if (m < M && n < N) {
-          __nv_bfloat16* dst = out_base + out_row * ldc + n;
-          const __nv_bfloat16* res = residual ? residual + (long long)m * ldc + n : nullptr;
-          if (n + 32 <= N) {
+        if (n >= N) break;  // warp-uniform
+        uint32_t r[64];
+        tmem_ld_32x32b_x32(taddr + (uint32_t)c0, r);
+        tmem_ld_32x32b_x32(taddr + (uint32_t)(c0 + 32), r + 32);
+        tmem_ld_wait();
+        if (n + 64 <= N) {
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              float f[8];
+          for (int v = 0; v < 8; ++v) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(r[8 * v]), __uint_as_float(r[8 * v + 1]));
+            o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+            o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+            o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+            *reinterpret_cast<uint4*>(stg + lane * 128 + ((v ^ (lane & 7)) << 4)) = o;
+          }
+          __syncwarp();
+          const int u = lane & 7;
 #pragma unroll
-              for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[v * 8 + i]);
-              if (res) {
-                uint4 rv = *reinterpret_cast<const uint4*>(res + v * 8);
+          for (int j = 0; j < 8; ++j) {
+            const int rr = 4 * j + (lane >> 3);  // row of the warp's 32
+            uint4 o = *reinterpret_cast<const uint4*>(stg + rr * 128 + ((u ^ (rr & 7)) << 4));
+            if (m_warp0 + rr < M) {
+              if (residual) {
+                const uint4 rv = *reinterpret_cast<const uint4*>(residual + (long long)(m_warp0 + rr) * ldc + n + u * 8);
                 const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv);
+                __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                  float2 t = __bfloat1622float2(rp[i]);
-                  f[2 * i] += t.x;
-                  f[2 * i + 1] += t.y;
+                  const float2 a = __bfloat1622float2(op[i]), t = __bfloat1622float2(rp[i]);
+                  op[i] = __floats2bfloat162_rn(a.x + t.x, a.y + t.y);
                 }
               }
-              uint4 o;
-              o.x = pack_bf16x2(f[0], f[1]);
-              o.y = pack_bf16x2(f[2], f[3]);
-              o.z = pack_bf16x2(f[4], f[5]);
-              o.w = pack_bf16x2(f[6], f[7]);
-              *reinterpret_cast<uint4*>(dst + v * 8) = o;
+              *reinterpret_cast<uint4*>(out_base + (out_row0 + rr) * ldc + n + u * 8) = o;
             }
-          } else {
-            for (int i = 0; i < 32 && n + i < N; ++i) {
-              float f = __uint_as_float(r[i]);
-              if (res) f += __bfloat162float(res[i]);
-              dst[i] = __float2bfloat16_rn(f);
-            }
+          }
+          __syncwarp();
+        } else if (m < M) {
+          // ragged right edge: element by element
+          __nv_bfloat16* dst = out_base + out_row * ldc + n;
+          const __nv_bfloat16* res = residual ? residual + (long long)m * ldc + n : nullptr;
+          for (int i = 0; i < 64 && n + i < N; ++i) {
+            float f = __uint_as_float(r[i]);
+            if (res) f += __bfloat162float(res[i]);
+            dst[i] = __float2bfloat16_rn(f);
           }
         }
       }
@@ -557,7 +593,7 @@ __global__ void reduce_partials_kernel(const __nv_bfloat16* __restrict__ recv, c
 // (M,N) product are owned by ranks in blocks of M/world rows. recv_bufs[r]: rank r's receive
 // buffer [world][M/world][N] bf16; flags[r]: rank r's [world] tile counters. After the GEMM the
 // rank reduces what it received into `out` (M/world, N) (+ residual). `flag_target`: value every
-// counter of this rank reaches when all sources have delivered this call (4 x tiles x calls).
+// counter of this rank reaches when all sources have delivered this call (4 x tiles of 128 x 256 x calls).
 extern "C" int kvb_gemm_reduce_scatter(const void* A, const void* B, void* out, const void* residual, void* const* recv_bufs,
                                        void* const* flags, int rank, int world, int M, int N, int K, long long lda,
                                        long long ldb, unsigned flag_target, int* status, double timeout_s, void* stream) {
@@ -576,7 +612,9 @@ extern "C" int kvb_gemm_reduce_scatter(const void* A, const void* B, void* out, 
   ex.wait_limit = (long long)(timeout_s * 1.9e9);
   cudaStream_t s = (cudaStream_t)stream;
   // ldc of the receive buffers is N
-  int rc = launch_gemm<128>(A, B, nullptr, nullptr, recv_bufs[rank], nullptr, M, N, K, 0, lda, ldb, 0, 0, N, status, 0, s, &ex);
+  // 128 x 256 tiles: a 128 x 128 tile reads as many operand bytes from shared memory per MMA cycle as
+  // the tensor core can take, which leaves nothing for the TMA writes of the next stage
+  int rc = launch_gemm<256>(A, B, nullptr, nullptr, recv_bufs[rank], nullptr, M, N, K, 0, lda, ldb, 0, 0, N, status, 0, s, &ex);
   if (rc) return rc;
   const long long rows = M / world;
   reduce_partials_kernel<<<128, 512, 0, s>>>((const __nv_bfloat16*)recv_bufs[rank], (const uint32_t*)flags[rank], flag_target,
@@ -614,6 +652,6 @@ extern "C" int kvb_allgather_gemm(void* stage, void* const* stages, const void* 
   }
   ex.wait_limit = (long long)(timeout_s * 1.9e9);
   const int M = world * rows;
-  return launch_gemm<128>(stage, B, nullptr, nullptr, C, nullptr, M, N, K, 0, ld_stage, ldb, 0, 0, ldc, status, 0,
+  return launch_gemm<256>(stage, B, nullptr, nullptr, C, nullptr, M, N, K, 0, ld_stage, ldb, 0, 0, ldc, status, 0,
                           (cudaStream_t)stream, &ex);
 }

@@ -34,7 +34,7 @@ class _RawCudaBuffer:
 
 class SymmetricArena:
     def __init__(self, numel: int, dtype: torch.dtype, device, world_size: int, rank: int, group=None,
-                 timeout_s: float = 20.0, n_ctas: int = 32):
+                 timeout_s: float = 20.0, n_ctas: int = 0):
         self.numel, self.dtype = numel, dtype
         self.device = torch.device(device)
         self.world_size, self.rank, self.group = world_size, rank, group

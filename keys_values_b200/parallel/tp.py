@@ -85,11 +85,15 @@ class TPContext:
     FLAG_WORDS = 256
 
     def __init__(self, world: int, rank: int, device, max_rows: int, max_features: int, group=None, timeout_s: float = 20.0,
-                 copy_ctas: int = 16):
+                 copy_ctas: Optional[int] = None):
         if max_rows % (128 * world):
             raise ValueError(f"max_rows must be a multiple of {128 * world}")
         self.world, self.rank, self.group = world, rank, group
         self.device = torch.device(device)
+        # CTAs that pull the peers' shards: the remote fraction (world − 1) / world of the activation must
+        # arrive while the local fraction is being multiplied, so more ranks need more copy CTAs
+        if copy_ctas is None:
+            copy_ctas = min(32, 4 + 4 * world)
         self.timeout_s, self.copy_ctas = timeout_s, copy_ctas
         self.max_rows, self.max_features = max_rows, max_features
         torch.cuda.set_device(self.device)
@@ -151,7 +155,7 @@ class TPContext:
             raise ValueError("gemm_reduce_scatter: M/world must be a multiple of 128 within the context limits")
         par = (self._rs_calls[0] + self._rs_calls[1]) & 1
         self._rs_calls[par] += 1
-        tiles_per_dest = (rows // 128) * ((N + 127) // 128)
+        tiles_per_dest = (rows // 128) * ((N + 255) // 256)  # the kernel works on 128 x 256 tiles
         self._rs_tiles[par] += 4 * tiles_per_dest
         if out is None:
             out = torch.empty((rows, N), dtype=torch.bfloat16, device=self.device)
