@@ -2,10 +2,12 @@
 // KV cache, with de-quantization fused into the tile load and the per-slot summed
 // attention weights (H2O score input) as a second output.
 //
-//   split-KV: grid (B·G, n_splits); every CTA scores SPLIT slots for all H/G heads of
-//   its KV group, keeps the raw scores in a (B,H,L) scratch, accumulates its partial
-//   (max, sum, O); a merge kernel combines the partials; a third kernel turns the raw
-//   scores into weights[b,g,j] = (1/(H/G)) Σ_h exp(s_hj − lse_h).
+//   split-KV: grid (B·G, n_splits, head blocks); every CTA scores 256 slots for (up to 8 of) the
+//   H/G heads of its KV group, keeps the raw scores in a (B,H,L) scratch, accumulates its
+//   partial (max, sum, O); a merge kernel combines the partials; a third kernel turns the raw
+//   scores into weights[b,g,j] = (1/(H/G)) Σ_h exp(s_hj − lse_h). A warp reads four cache rows
+//   at a time as whole 16-byte units (8 lanes per row), several loads in flight per lane: the
+//   kernel is bound by the HBM read of the cache.
 //
 // The quantized storage is read directly: x = (q − zp)·scale is folded into the dot
 // products (q·k = scale·(Σ q_i·code_i − zp·Σ q_i)), so no full-precision copy of the cache
@@ -24,9 +26,10 @@
 namespace kvb {
 
 constexpr int DEC_D = 128;
-constexpr int DEC_SPLIT = 1024;
-constexpr int DEC_THREADS = 256;
+constexpr int DEC_SPLIT = 256;    // slots per CTA
+constexpr int DEC_THREADS = 128;  // 4 warps
 constexpr int DEC_MAX_GS = 16;
+constexpr int DEC_HB = 8;         // heads of a group handled by one CTA (more heads: more CTAs along z)
 
 struct DecParams {
   const __nv_bfloat16* q;       // (B,H,D)
@@ -47,199 +50,228 @@ struct DecParams {
   float scale;
 };
 
+// Feature that element k (0..15) of a lane's row fragment holds; fl = lane & 7.
+//   bf16 : two 16-byte units, fl and fl + 8        -> features 8 fl + k, 64 + 8 fl + (k − 8)
+//   int8 : one 16-byte unit                        -> features 16 fl + k
+//   int4 : 8 bytes, byte i = (feature i, feature i + 64) as (high, low) nibble
+//                                                  -> features 8 fl + k, 64 + 8 fl + (k − 8)
 template <int BITS>
-__device__ __forceinline__ void load_row_f32(const void* base, long long row, float* x) {
-  // x[128] <- codes (or bf16 values) of one row
+__device__ __forceinline__ int dec_feature(int fl, int k) {
+  if (BITS == 8) return 16 * fl + k;
+  return k < 8 ? 8 * fl + k : 64 + 8 * fl + (k - 8);
+}
+
+// Byte `idx` of w as a float without the conversion unit: the byte becomes the low mantissa bits
+// of 2^23 (one PRMT), and 2^23 is subtracted (one FADD).
+__device__ __forceinline__ float dec_u8_to_f32(uint32_t w, int idx) {
+  return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7440u | (uint32_t)idx)) - 8388608.f;
+}
+
+// 16 elements of row `row` for feature lane fl, as floats (codes are not de-quantized here).
+template <int BITS>
+__device__ __forceinline__ void dec_load_frag(const void* base, long long row, int fl, float* x) {
   if (BITS == 16) {
     const uint4* p = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(base) + row * DEC_D);
+    const uint4 a = __ldg(p + fl), c = __ldg(p + fl + 8);
+    const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* hc = reinterpret_cast<const __nv_bfloat162*>(&c);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      uint4 v = p[i];
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float2 f = __bfloat1622float2(h[j]);
-        x[i * 8 + 2 * j] = f.x;
-        x[i * 8 + 2 * j + 1] = f.y;
-      }
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(ha[j]), g = __bfloat1622float2(hc[j]);
+      x[2 * j] = f.x; x[2 * j + 1] = f.y;
+      x[8 + 2 * j] = g.x; x[8 + 2 * j + 1] = g.y;
     }
   } else if (BITS == 8) {
-    const uint4* p = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(base) + row * DEC_D);
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(base) + row * DEC_D) + fl);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      uint4 v = p[i];
-      const uint8_t* c = reinterpret_cast<const uint8_t*>(&v);
-#pragma unroll
-      for (int j = 0; j < 16; ++j) x[i * 16 + j] = (float)c[j];
-    }
+    for (int j = 0; j < 16; ++j) x[j] = dec_u8_to_f32(w[j >> 2], j & 3);
   } else {
-    const uint4* p = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(base) + row * (DEC_D / 2));
+    const uint2 v = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(base) + row * (DEC_D / 2)) + fl);
+    const uint32_t w[2] = {v.x, v.y};
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      uint4 v = p[i];
-      const uint8_t* c = reinterpret_cast<const uint8_t*>(&v);
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        x[i * 16 + j] = (float)(c[j] >> 4);
-        x[64 + i * 16 + j] = (float)(c[j] & 0xF);
-      }
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t byte = (w[j >> 2] >> (8 * (j & 3))) & 0xFFu;
+      x[j] = __uint_as_float(0x4B000000u | (byte >> 4)) - 8388608.f;
+      x[8 + j] = __uint_as_float(0x4B000000u | (byte & 0xFu)) - 8388608.f;
     }
   }
 }
 
-template <int BITS>
+// One CTA = (batch, KV group, split of DEC_SPLIT slots, block of GS heads). A warp handles four
+// slots at a time: 8 lanes per slot, 16 features per lane, so that a row is read as whole
+// 16-byte units, coalesced, several loads in flight per lane. Scores are reduced over the 8
+// lanes by shuffles; p·V accumulates in registers (GS x 16 per lane) and is reduced once.
+template <int BITS, int GS>
 __global__ void __launch_bounds__(DEC_THREADS)
 decode_partial_kernel(const DecParams p) {
-  extern __shared__ float sm[];
-  float* q_s = sm;                                  // [gs][128]
-  float* qsum = q_s + p.gs * DEC_D;                 // [gs]
-  float* sc = qsum + DEC_MAX_GS;                    // [gs][SPLIT] scores, later p·scale
-  float* pz = sc + p.gs * DEC_SPLIT;                // [gs][SPLIT] p·scale·zp
-  float* red = pz + p.gs * DEC_SPLIT;               // [8 warps][gs] reductions / [8][gs][128] at the end
-  const int bg = blockIdx.x, split = blockIdx.y;
+  __shared__ float sc[GS][DEC_SPLIT];           // scores, later p · v_scale
+  __shared__ float red[DEC_THREADS / 32][GS];   // per-warp reductions
+  __shared__ float stat[2][GS];                 // block max, Σ p · v_scale · v_zero_point
+  __shared__ float ored[DEC_THREADS / 32][GS][DEC_D];
+  const int bg = blockIdx.x, split = blockIdx.y, h0 = blockIdx.z * GS;
   const int b = bg / p.G, g = bg % p.G;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int fl = lane & 7, sub = lane >> 3;
   const int j0 = split * DEC_SPLIT, j1 = min(j0 + DEC_SPLIT, p.L);
   const int n = j1 - j0;
   const long long row0 = ((long long)b * p.G + g) * p.C;
-  const int gs = p.gs;
   const int ns = p.new_slot ? p.new_slot[b * p.G + g] : -1;
+  const long long head0 = (long long)b * p.H + g * p.gs + h0;  // first head of this CTA
 
-  for (int i = tid; i < gs * DEC_D; i += DEC_THREADS) q_s[i] = __bfloat162float(p.q[((long long)b * p.H + g * gs) * DEC_D + i]);
-  __syncthreads();
-  if (tid < gs) {
-    float s = 0.f;
-    for (int i = 0; i < DEC_D; ++i) s += q_s[tid * DEC_D + i];
-    qsum[tid] = s;
-  }
-  __syncthreads();
-
-  // ---- pass A: raw scores, one slot per thread
-  float lmax[DEC_MAX_GS];
+  // query fragment of this lane and Σ_i q_i per head (for the zero-point term)
+  float qf[GS][16], qsum[GS];
 #pragma unroll
-  for (int h = 0; h < DEC_MAX_GS; ++h) lmax[h] = -FLT_MAX;
-  for (int jj = tid; jj < n; jj += DEC_THREADS) {
-    const int j = j0 + jj;
-    float x[DEC_D];
+  for (int h = 0; h < GS; ++h) {
+    const __nv_bfloat16* qr = p.q + (head0 + h) * DEC_D;
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      qf[h][k] = __bfloat162float(qr[dec_feature<BITS>(fl, k)]);
+      s += qf[h][k];
+    }
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    s += __shfl_xor_sync(0xffffffffu, s, 4);
+    qsum[h] = s;
+  }
+
+  // ---- pass A: raw scores
+  float lmax[GS];
+#pragma unroll
+  for (int h = 0; h < GS; ++h) lmax[h] = -FLT_MAX;
+#pragma unroll 4
+  for (int jb = warp * 4; jb < n; jb += DEC_THREADS / 8) {  // warp-uniform trip count (shuffles inside)
+    const int jj = jb + sub;
+    const bool valid = jj < n;
+    const int j = j0 + (valid ? jj : 0);
+    // the cache row is loaded unconditionally (no branch between the loads of the unrolled
+    // iterations); the row of the token being decoded is then replaced by its exact values
+    float x[16];
     float kscale = 1.f, kzp = 0.f;
+    dec_load_frag<BITS>(p.kq, row0 + j, fl, x);
+    if (BITS != 16) {
+      kscale = __ldg(p.ks + row0 + j);
+      kzp = (float)__ldg(p.kz + row0 + j);
+    }
     if (j == ns) {
       const __nv_bfloat16* kr = p.k_new + ((long long)b * p.G + g) * DEC_D;
-      for (int i = 0; i < DEC_D; ++i) x[i] = __bfloat162float(kr[i]);
-    } else {
-      load_row_f32<BITS>(p.kq, row0 + j, x);
-      if (BITS != 16) {
-        kscale = p.ks[row0 + j];
-        kzp = (float)p.kz[row0 + j];
-      }
+#pragma unroll
+      for (int k = 0; k < 16; ++k) x[k] = __bfloat162float(kr[dec_feature<BITS>(fl, k)]);
+      kscale = 1.f;
+      kzp = 0.f;
     }
-    for (int h = 0; h < gs; ++h) {
+#pragma unroll
+    for (int h = 0; h < GS; ++h) {
       float acc = 0.f;
 #pragma unroll
-      for (int i = 0; i < DEC_D; ++i) acc = fmaf(q_s[h * DEC_D + i], x[i], acc);
-      const float s = p.scale * kscale * (acc - kzp * qsum[h]);
-      sc[h * DEC_SPLIT + jj] = s;
-      p.logits[((long long)b * p.H + g * gs + h) * p.L + j] = s;
-      lmax[h] = fmaxf(lmax[h], s);
+      for (int k = 0; k < 16; ++k) acc = fmaf(qf[h][k], x[k], acc);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+      const float sv = p.scale * kscale * (acc - kzp * qsum[h]);
+      if (valid) lmax[h] = fmaxf(lmax[h], sv);
+      if (fl == 0 && valid) {
+        sc[h][jj] = sv;
+        p.logits[(head0 + h) * p.L + j] = sv;
+      }
     }
   }
-  // block max per head
-  for (int h = 0; h < gs; ++h) {
-    float m = warp_max(lmax[h]);
-    if (lane == 0) red[warp * DEC_MAX_GS + h] = m;
+#pragma unroll
+  for (int h = 0; h < GS; ++h) {
+    const float m = warp_max(lmax[h]);
+    if (lane == 0) red[warp][h] = m;
   }
   __syncthreads();
-  float cmax[DEC_MAX_GS];
-  for (int h = 0; h < gs; ++h) {
+  if (tid < GS) {
     float m = -FLT_MAX;
-    for (int w = 0; w < DEC_THREADS / 32; ++w) m = fmaxf(m, red[w * DEC_MAX_GS + h]);
-    cmax[h] = m;
+    for (int w = 0; w < DEC_THREADS / 32; ++w) m = fmaxf(m, red[w][tid]);
+    stat[0][tid] = m;
   }
   __syncthreads();
-  // ---- p = exp(s − m); fold the V scale / zero point; block sum per head
-  float lsum[DEC_MAX_GS];
-  for (int h = 0; h < gs; ++h) lsum[h] = 0.f;
+  // ---- p = exp(s − m) with the V scale folded in; block sums of p and of p · v_scale · v_zp
+  float lsum[GS], zsum[GS];
+#pragma unroll
+  for (int h = 0; h < GS; ++h) lsum[h] = zsum[h] = 0.f;
   for (int jj = tid; jj < n; jj += DEC_THREADS) {
     const int j = j0 + jj;
     float vscale = 1.f, vzp = 0.f;
     if (BITS != 16 && j != ns) {
-      vscale = p.vs[row0 + j];
-      vzp = (float)p.vz[row0 + j];
+      vscale = __ldg(p.vs + row0 + j);
+      vzp = (float)__ldg(p.vz + row0 + j);
     }
-    for (int h = 0; h < gs; ++h) {
-      const float pr = __expf(sc[h * DEC_SPLIT + jj] - cmax[h]);
+#pragma unroll
+    for (int h = 0; h < GS; ++h) {
+      const float pr = __expf(sc[h][jj] - stat[0][h]);
       lsum[h] += pr;
-      sc[h * DEC_SPLIT + jj] = pr * vscale;
-      pz[h * DEC_SPLIT + jj] = pr * vscale * vzp;
+      zsum[h] += pr * vscale * vzp;
+      sc[h][jj] = pr * vscale;
     }
   }
-  for (int h = 0; h < gs; ++h) {
-    float s = warp_sum(lsum[h]);
-    if (lane == 0) red[warp * DEC_MAX_GS + h] = s;
-  }
-  __syncthreads();
-  if (tid < gs) {
-    float s = 0.f;
-    for (int w = 0; w < DEC_THREADS / 32; ++w) s += red[w * DEC_MAX_GS + tid];
-    const long long idx = ((long long)b * p.H + g * gs + tid) * p.nS + split;
-    p.part_m[idx] = cmax[tid];
-    p.part_l[idx] = s;
-  }
-  __syncthreads();
-  // ---- pass B: O += p · v ; lane owns 4 features, warps stride over slots
-  float acc[DEC_MAX_GS][4];
+  __syncthreads();  // red is reused
 #pragma unroll
-  for (int h = 0; h < DEC_MAX_GS; ++h) acc[h][0] = acc[h][1] = acc[h][2] = acc[h][3] = 0.f;
-  for (int jj = warp; jj < n; jj += DEC_THREADS / 32) {
+  for (int h = 0; h < GS; ++h) {
+    const float s1 = warp_sum(lsum[h]), s2 = warp_sum(zsum[h]);
+    if (lane == 0) {
+      red[warp][h] = s1;
+      ored[warp][h][0] = s2;
+    }
+  }
+  __syncthreads();
+  if (tid < GS) {
+    float s1 = 0.f, s2 = 0.f;
+    for (int w = 0; w < DEC_THREADS / 32; ++w) {
+      s1 += red[w][tid];
+      s2 += ored[w][tid][0];
+    }
+    const long long idx = (head0 + tid) * p.nS + split;
+    p.part_m[idx] = stat[0][tid];
+    p.part_l[idx] = s1;
+    stat[1][tid] = s2;
+  }
+  __syncthreads();
+  // ---- pass B: O += (p · v_scale) · code ; the zero-point term is subtracted once at the end
+  float acc[GS][16];
+#pragma unroll
+  for (int h = 0; h < GS; ++h)
+#pragma unroll
+    for (int k = 0; k < 16; ++k) acc[h][k] = 0.f;
+#pragma unroll 4
+  for (int jb = warp * 4; jb < n; jb += DEC_THREADS / 8) {
+    const int jj = min(jb + sub, n - 1);
+    const bool valid = jb + sub < n;
     const int j = j0 + jj;
-    float v[4];
+    float x[16];
+    dec_load_frag<BITS>(p.vq, row0 + j, fl, x);
     if (j == ns) {
-      const __nv_bfloat16* vr = p.v_new + ((long long)b * p.G + g) * DEC_D + lane * 4;
+      const __nv_bfloat16* vr = p.v_new + ((long long)b * p.G + g) * DEC_D;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) v[i] = __bfloat162float(vr[i]);
-    } else if (BITS == 16) {
-      const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.vq) + (row0 + j) * DEC_D + lane * 4);
-      const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&raw);
-      float2 a = __bfloat1622float2(hh[0]), c = __bfloat1622float2(hh[1]);
-      v[0] = a.x; v[1] = a.y; v[2] = c.x; v[3] = c.y;
-    } else if (BITS == 8) {
-      const uint32_t raw = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(p.vq) + (row0 + j) * DEC_D + lane * 4);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) v[i] = (float)((raw >> (8 * i)) & 0xFF);
-    } else {
-      // features lane*4 .. lane*4+3: high nibbles of bytes [lane*4, +4) if lane < 16, else low nibbles of bytes [(lane-16)*4, +4)
-      const int bo = (lane & 15) * 4;
-      const uint32_t raw = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(p.vq) + (row0 + j) * (DEC_D / 2) + bo);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint32_t byte = (raw >> (8 * i)) & 0xFF;
-        v[i] = (float)(lane < 16 ? (byte >> 4) : (byte & 0xF));
-      }
+      for (int k = 0; k < 16; ++k) x[k] = __bfloat162float(vr[dec_feature<BITS>(fl, k)]);
     }
 #pragma unroll
-    for (int h = 0; h < DEC_MAX_GS; ++h) {
-      if (h < gs) {
-        const float ps = sc[h * DEC_SPLIT + jj], pzv = pz[h * DEC_SPLIT + jj];
+    for (int h = 0; h < GS; ++h) {
+      const float ps = valid ? sc[h][jj] : 0.f;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) acc[h][i] += ps * v[i] - pzv;
-      }
+      for (int k = 0; k < 16; ++k) acc[h][k] = fmaf(ps, x[k], acc[h][k]);
     }
   }
-  __syncthreads();
-  // cross-warp reduction through shared memory (re-using the score area)
-  float* ored = sc;  // [8][gs][128]
+  // reduce over the four slot lanes of the warp, then over the warps
 #pragma unroll
-  for (int h = 0; h < DEC_MAX_GS; ++h) {
-    if (h < gs) {
+  for (int h = 0; h < GS; ++h)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) ored[(warp * gs + h) * DEC_D + lane * 4 + i] = acc[h][i];
+    for (int k = 0; k < 16; ++k) {
+      float v = acc[h][k];
+      v += __shfl_xor_sync(0xffffffffu, v, 8);
+      v += __shfl_xor_sync(0xffffffffu, v, 16);
+      if (sub == 0) ored[warp][h][dec_feature<BITS>(fl, k)] = v;
     }
-  }
   __syncthreads();
-  for (int i = tid; i < gs * DEC_D; i += DEC_THREADS) {
-    float s = 0.f;
-    for (int w = 0; w < DEC_THREADS / 32; ++w) s += ored[w * gs * DEC_D + i];
+  for (int i = tid; i < GS * DEC_D; i += DEC_THREADS) {
     const int h = i / DEC_D, d = i % DEC_D;
-    p.part_o[(((long long)b * p.H + g * gs + h) * p.nS + split) * DEC_D + d] = s;
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < DEC_THREADS / 32; ++w) s += ored[w][h][d];
+    p.part_o[((head0 + h) * p.nS + split) * DEC_D + d] = s - stat[1][h];
   }
 }
 
@@ -302,19 +334,22 @@ extern "C" int kvb_decode_attn(const void* q, const void* kq, const void* vq, co
   p.part_o = sc; sc += (long long)B * H * p.nS * DEC_D;
   p.lse = sc;
   cudaStream_t s = (cudaStream_t)stream;
-  const size_t smem = (size_t)(gs * DEC_D + DEC_MAX_GS + 2 * gs * DEC_SPLIT + (DEC_THREADS / 32) * DEC_MAX_GS) * 4;
-  dim3 grid(B * G, p.nS);
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaFuncSetAttribute(decode_partial_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-    cudaFuncSetAttribute(decode_partial_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-    cudaFuncSetAttribute(decode_partial_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-    attr_set = true;
+  // heads of a group per CTA: the group size up to DEC_HB; larger groups use more CTAs along z
+  const int hb = gs < DEC_HB ? gs : DEC_HB;
+  if (gs % hb) return KVB_ERR_UNSUPPORTED;
+  dim3 grid(B * G, p.nS, gs / hb);
+#define KVB_DEC_LAUNCH(BITS_)                                                            \
+  switch (hb) {                                                                          \
+    case 1: decode_partial_kernel<BITS_, 1><<<grid, DEC_THREADS, 0, s>>>(p); break;      \
+    case 2: decode_partial_kernel<BITS_, 2><<<grid, DEC_THREADS, 0, s>>>(p); break;      \
+    case 4: decode_partial_kernel<BITS_, 4><<<grid, DEC_THREADS, 0, s>>>(p); break;      \
+    case 8: decode_partial_kernel<BITS_, 8><<<grid, DEC_THREADS, 0, s>>>(p); break;      \
+    default: return KVB_ERR_UNSUPPORTED;                                                 \
   }
-  if (smem > 160 * 1024) return KVB_ERR_TOO_LARGE;
-  if (bits == 16) decode_partial_kernel<16><<<grid, DEC_THREADS, smem, s>>>(p);
-  else if (bits == 8) decode_partial_kernel<8><<<grid, DEC_THREADS, smem, s>>>(p);
-  else decode_partial_kernel<4><<<grid, DEC_THREADS, smem, s>>>(p);
+  if (bits == 16) { KVB_DEC_LAUNCH(16) }
+  else if (bits == 8) { KVB_DEC_LAUNCH(8) }
+  else { KVB_DEC_LAUNCH(4) }
+#undef KVB_DEC_LAUNCH
   decode_merge_kernel<<<B * H, DEC_D, 0, s>>>(p);
   if (weights) {
     dim3 g2((L + 255) / 256, B * G);

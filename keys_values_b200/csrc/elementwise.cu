@@ -219,6 +219,158 @@ __global__ void qknorm_rope_bwd_kernel(const T* __restrict__ gq, const T* __rest
   }
 }
 
+// ---- fast paths: bf16, head size 128, RoPE over the whole head. One warp per token: a lane
+// holds 4 consecutive features of a head (8-byte loads and stores), the rotation partner
+// (feature ± 64) lives in lane ± 16 and is fetched by shuffle, cos / sin of the token are loaded
+// once and reused for all heads, weight gradients accumulate in registers.
+__device__ __forceinline__ void bf16x4_to_f32(const uint2 v, float* x) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+  const float2 a = __bfloat1622float2(h[0]), c = __bfloat1622float2(h[1]);
+  x[0] = a.x; x[1] = a.y; x[2] = c.x; x[3] = c.y;
+}
+__device__ __forceinline__ uint2 f32_to_bf16x4(const float* x) {
+  uint2 v;
+  __nv_bfloat162 a = __floats2bfloat162_rn(x[0], x[1]), c = __floats2bfloat162_rn(x[2], x[3]);
+  v.x = *reinterpret_cast<uint32_t*>(&a);
+  v.y = *reinterpret_cast<uint32_t*>(&c);
+  return v;
+}
+
+__global__ void __launch_bounds__(EW_WARPS * 32)
+qknorm_rope_fwd128_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ cosT, const float* __restrict__ sinT,
+                          const __nv_bfloat16* __restrict__ qw, const __nv_bfloat16* __restrict__ kw,
+                          __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ k, __nv_bfloat16* __restrict__ v,
+                          float* __restrict__ rstd, int B, int Tn, int H, int G, float eps, int unit) {
+  constexpr int D = 128;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long tok = (long long)blockIdx.x * EW_WARPS + warp;
+  if (tok >= (long long)B * Tn) return;
+  const int t = (int)(tok % Tn), b = (int)(tok / Tn);
+  const int NH = H + 2 * G;
+  const float4 c4 = *reinterpret_cast<const float4*>(cosT + (long long)t * D + 4 * lane);
+  const float4 s4 = *reinterpret_cast<const float4*>(sinT + (long long)t * D + 4 * lane);
+  const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+  float wq[4] = {1.f, 1.f, 1.f, 1.f}, wk[4] = {1.f, 1.f, 1.f, 1.f};
+  if (qw) {
+    bf16x4_to_f32(*reinterpret_cast<const uint2*>(qw + 4 * lane), wq);
+    bf16x4_to_f32(*reinterpret_cast<const uint2*>(kw + 4 * lane), wk);
+    if (unit) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { wq[i] += 1.f; wk[i] += 1.f; }
+    }
+  }
+  const __nv_bfloat16* src = qkv + tok * NH * D + 4 * lane;
+  const float sgn = lane < 16 ? -1.f : 1.f;
+#pragma unroll 4
+  for (int head = 0; head < H + G; ++head) {
+    float x[4];
+    bf16x4_to_f32(*reinterpret_cast<const uint2*>(src + (long long)head * D), x);
+    const float* w = head < H ? wq : wk;
+    if (qw) {
+      float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+      ss = warp_sum(ss);
+      const float r = rsqrtf(ss / D + eps);
+      if (lane == 0) rstd[tok * (H + G) + head] = r;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) x[i] = x[i] * r * w[i];
+    }
+    float y[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float partner = __shfl_xor_sync(0xffffffffu, x[i], 16);
+      y[i] = x[i] * cs[i] + sgn * partner * sn[i];
+    }
+    __nv_bfloat16* dst = head < H ? q + (((long long)b * H + head) * Tn + t) * D : k + (((long long)b * G + (head - H)) * Tn + t) * D;
+    *reinterpret_cast<uint2*>(dst + 4 * lane) = f32_to_bf16x4(y);
+  }
+#pragma unroll 4
+  for (int head = 0; head < G; ++head)
+    *reinterpret_cast<uint2*>(v + (((long long)b * G + head) * Tn + t) * D + 4 * lane) =
+        *reinterpret_cast<const uint2*>(src + (long long)(H + G + head) * D);
+}
+
+__global__ void __launch_bounds__(EW_WARPS * 32)
+qknorm_rope_bwd128_kernel(const __nv_bfloat16* __restrict__ gq, const __nv_bfloat16* __restrict__ gk,
+                          const __nv_bfloat16* __restrict__ gv, const __nv_bfloat16* __restrict__ qkv,
+                          const float* __restrict__ cosT, const float* __restrict__ sinT, const __nv_bfloat16* __restrict__ qw,
+                          const __nv_bfloat16* __restrict__ kw, const float* __restrict__ rstd, __nv_bfloat16* __restrict__ dqkv,
+                          float* __restrict__ dw_partial, int B, int Tn, int H, int G, int unit) {
+  constexpr int D = 128;
+  __shared__ float dw_s[EW_WARPS][2][D];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int NH = H + 2 * G;
+  float wq[4] = {1.f, 1.f, 1.f, 1.f}, wk[4] = {1.f, 1.f, 1.f, 1.f};
+  if (qw) {
+    bf16x4_to_f32(*reinterpret_cast<const uint2*>(qw + 4 * lane), wq);
+    bf16x4_to_f32(*reinterpret_cast<const uint2*>(kw + 4 * lane), wk);
+    if (unit) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { wq[i] += 1.f; wk[i] += 1.f; }
+    }
+  }
+  float dwq[4] = {0.f, 0.f, 0.f, 0.f}, dwk[4] = {0.f, 0.f, 0.f, 0.f};
+  // the partner of feature i contributes g·sin taken at ITS index: + for i < 64, − otherwise
+  const float sgn = lane < 16 ? 1.f : -1.f;
+  for (long long tok = (long long)blockIdx.x * EW_WARPS + warp; tok < (long long)B * Tn; tok += (long long)gridDim.x * EW_WARPS) {
+    const int t = (int)(tok % Tn), b = (int)(tok / Tn);
+    const float4 c4 = *reinterpret_cast<const float4*>(cosT + (long long)t * D + 4 * lane);
+    const float4 s4 = *reinterpret_cast<const float4*>(sinT + (long long)t * D + 4 * lane);
+    const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+    const __nv_bfloat16* src = qkv + tok * NH * D + 4 * lane;
+    __nv_bfloat16* dst = dqkv + tok * NH * D + 4 * lane;
+#pragma unroll 2
+    for (int head = 0; head < H + G; ++head) {
+      const __nv_bfloat16* g = head < H ? gq + (((long long)b * H + head) * Tn + t) * D : gk + (((long long)b * G + (head - H)) * Tn + t) * D;
+      float gi[4], gr[4];
+      bf16x4_to_f32(*reinterpret_cast<const uint2*>(g + 4 * lane), gi);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float partner = __shfl_xor_sync(0xffffffffu, gi[i] * sn[i], 16);
+        gr[i] = gi[i] * cs[i] + sgn * partner;
+      }
+      if (!qw) {
+        *reinterpret_cast<uint2*>(dst + (long long)head * D) = f32_to_bf16x4(gr);
+        continue;
+      }
+      float x[4];
+      bf16x4_to_f32(*reinterpret_cast<const uint2*>(src + (long long)head * D), x);
+      const float r = rstd[tok * (H + G) + head];
+      const float* w = head < H ? wq : wk;
+      float dot = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) dot += gr[i] * w[i] * x[i] * r;
+      dot = warp_sum(dot) * (1.f / D);
+      float o[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float xh = x[i] * r;
+        o[i] = r * (gr[i] * w[i] - xh * dot);
+        if (head < H) dwq[i] += gr[i] * xh;
+        else dwk[i] += gr[i] * xh;
+      }
+      *reinterpret_cast<uint2*>(dst + (long long)head * D) = f32_to_bf16x4(o);
+    }
+#pragma unroll 4
+    for (int head = 0; head < G; ++head)
+      *reinterpret_cast<uint2*>(dst + (long long)(H + G + head) * D) =
+          *reinterpret_cast<const uint2*>(gv + (((long long)b * G + head) * Tn + t) * D + 4 * lane);
+  }
+  if (dw_partial) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      dw_s[warp][0][4 * lane + i] = dwq[i];
+      dw_s[warp][1][4 * lane + i] = dwk[i];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) {
+      float sum = 0.f;
+#pragma unroll
+      for (int w = 0; w < EW_WARPS; ++w) sum += dw_s[w][i / D][i % D];
+      dw_partial[(long long)blockIdx.x * 2 * D + i] = sum;
+    }
+  }
+}
+
 // -------------------------------------------------------------------- SwiGLU
 template <typename T>
 __global__ void swiglu_fwd_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ y, long long n) {
@@ -304,6 +456,13 @@ extern "C" int kvb_qknorm_rope_fwd(const void* qkv, const float* cos, const floa
                                    void* k, void* v, float* rstd, int B, int T_, int H, int G, int D, float eps,
                                    int rope_n_elem, int add_unit_offset, int dtype, void* stream) {
   if (D > 256 || D <= 0 || rope_n_elem > D || (rope_n_elem & 1)) return KVB_ERR_UNSUPPORTED;
+  if (dtype == 1 && D == 128 && rope_n_elem == 128 && ((qw == nullptr) == (kw == nullptr))) {
+    const unsigned g128 = (unsigned)(((long long)B * T_ + EW_WARPS - 1) / EW_WARPS);
+    qknorm_rope_fwd128_kernel<<<g128, EW_WARPS * 32, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)qkv, cos, sin, (const __nv_bfloat16*)qw, (const __nv_bfloat16*)kw, (__nv_bfloat16*)q,
+        (__nv_bfloat16*)k, (__nv_bfloat16*)v, rstd, B, T_, H, G, eps, add_unit_offset);
+    return check_launch();
+  }
   const long long rows = (long long)B * T_ * (H + 2 * G);
   const unsigned grid = (unsigned)((rows + EW_WARPS - 1) / EW_WARPS);
   const size_t smem = (size_t)EW_WARPS * D * 4;
@@ -318,6 +477,12 @@ extern "C" int kvb_qknorm_rope_bwd(const void* gq, const void* gk, const void* g
                                    float* dw_partial, int B, int T_, int H, int G, int D, int rope_n_elem, int add_unit_offset,
                                    int dtype, int n_partial, void* stream) {
   if (D > 256 || D <= 0 || rope_n_elem > D || (rope_n_elem & 1) || n_partial <= 0) return KVB_ERR_UNSUPPORTED;
+  if (dtype == 1 && D == 128 && rope_n_elem == 128 && ((qw == nullptr) == (kw == nullptr))) {
+    qknorm_rope_bwd128_kernel<<<n_partial, EW_WARPS * 32, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)gq, (const __nv_bfloat16*)gk, (const __nv_bfloat16*)gv, (const __nv_bfloat16*)qkv, cos, sin,
+        (const __nv_bfloat16*)qw, (const __nv_bfloat16*)kw, rstd, (__nv_bfloat16*)dqkv, dw_partial, B, T_, H, G, add_unit_offset);
+    return check_launch();
+  }
   const size_t smem = (size_t)(EW_WARPS + 2) * D * 4;
   KVB_DISPATCH_DTYPE(dtype, (qknorm_rope_bwd_kernel<T><<<n_partial, EW_WARPS * 32, smem, (cudaStream_t)stream>>>(
                                 (const T*)gq, (const T*)gk, (const T*)gv, (const T*)qkv, cos, sin, (const T*)qw, (const T*)kw,

@@ -55,6 +55,25 @@ def main():
         z = torch.randint(100, 150, (4, G, L), device=dev, dtype=torch.int32)
         for _ in range(args.iters):
             cu.decode_attention(q, k, v, scale, L, True, quant=(s, z, s, z, 8))
+    elif args.which == "allreduce":
+        # one rank: the kernel runs its barrier, pull, reduce and push paths on local memory only
+        import os
+
+        import torch.distributed as dist
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29533")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+        from keys_values_b200.parallel.symm import SymmetricArena
+
+        n = 128 * 2**20
+        arena = SymmetricArena(n, torch.bfloat16, dev, 1, 0)
+        arena.tensor.normal_()
+        for _ in range(args.iters):
+            arena.all_reduce_mean_(0, n)
+        torch.cuda.synchronize()
+        arena.close()
+        dist.destroy_process_group()
     else:
         raise SystemExit(f"unknown case {args.which}")
     torch.cuda.synchronize()
