@@ -61,3 +61,16 @@ def test_fused_tp_gemm_collectives_match_nccl():
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_tp_model_matches_single_gpu():
     _run("tp_model", 2)
+
+
+def _all_gpus() -> int:
+    n = min(torch.cuda.device_count(), 8)
+    return 1 << (n.bit_length() - 1) if n >= 1 else 0  # largest power of two
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 or more GPUs")
+@pytest.mark.parametrize("case", ["allreduce", "tp_ops", "dp_train"])
+def test_collectives_on_all_gpus(case):
+    """The fused collectives and the data-parallel step at the full width of the box."""
+    _run(case, _all_gpus(), timeout=600)
