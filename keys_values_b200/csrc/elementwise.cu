@@ -84,6 +84,159 @@ __global__ void rmsnorm_bwd_kernel(const T* __restrict__ gy, const T* __restrict
   }
 }
 
+// ---- bf16 fast path: one warp per row, the whole row in registers (dim a multiple of 256, at most
+// 8192), 16-byte accesses, optional fused residual add in the forward pass (s = x + res is written
+// out, rounded to bf16, and normalised) and optional fused add of the gradient that reaches s by its
+// other consumer in the backward pass.
+
+template <int NC>
+__global__ void __launch_bounds__(EW_WARPS * 32)
+rmsnorm_fwd_bf16_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                        const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ sum_out,
+                        float* __restrict__ rstd, long long rows, float eps, int unit) {
+  constexpr int dim = NC * 256;
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * EW_WARPS + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const long long base = row * dim + lane * 8;
+  uint4 v[NC];
+#pragma unroll
+  for (int c = 0; c < NC; ++c) v[c] = *reinterpret_cast<const uint4*>(x + base + c * 256);
+  if (res) {
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+      const uint4 rv = *reinterpret_cast<const uint4*>(res + base + c * 256);
+      __nv_bfloat162* a = reinterpret_cast<__nv_bfloat162*>(&v[c]);
+      const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 fa = __bfloat1622float2(a[j]), fb = __bfloat1622float2(b[j]);
+        a[j] = __floats2bfloat162_rn(fa.x + fb.x, fa.y + fb.y);
+      }
+      *reinterpret_cast<uint4*>(sum_out + base + c * 256) = v[c];
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < NC; ++c) {
+    const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&v[c]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(a[j]);
+      ss += f.x * f.x + f.y * f.y;
+    }
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / dim + eps);
+  if (lane == 0 && rstd) rstd[row] = r;
+#pragma unroll
+  for (int c = 0; c < NC; ++c) {
+    uint4 wv = make_uint4(0, 0, 0, 0);
+    if (w) wv = *reinterpret_cast<const uint4*>(w + lane * 8 + c * 256);
+    __nv_bfloat162* a = reinterpret_cast<__nv_bfloat162*>(&v[c]);
+    const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&wv);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 f = __bfloat1622float2(a[j]);
+      f.x *= r;
+      f.y *= r;
+      if (w) {
+        float2 ww = __bfloat1622float2(b[j]);
+        if (unit) { ww.x += 1.f; ww.y += 1.f; }
+        f.x *= ww.x;
+        f.y *= ww.y;
+      }
+      a[j] = __floats2bfloat162_rn(f.x, f.y);
+    }
+    *reinterpret_cast<uint4*>(y + base + c * 256) = v[c];
+  }
+}
+
+// dx = r (g ⊙ w − x^ · mean(g ⊙ w ⊙ x^)) (+ gadd); no weight gradient (frozen norm weights)
+template <int NC>
+__global__ void __launch_bounds__(EW_WARPS * 32)
+rmsnorm_bwd_bf16_kernel(const __nv_bfloat16* __restrict__ gy, const __nv_bfloat16* __restrict__ x,
+                        const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+                        const __nv_bfloat16* __restrict__ gadd, __nv_bfloat16* __restrict__ dx, long long rows, int unit) {
+  constexpr int dim = NC * 256;
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * EW_WARPS + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const long long base = row * dim + lane * 8;
+  const float r = rstd[row];
+  float gw[NC][8], xh[NC][8];
+  float dot = 0.f;
+#pragma unroll
+  for (int c = 0; c < NC; ++c) {
+    const uint4 gv = *reinterpret_cast<const uint4*>(gy + base + c * 256);
+    const uint4 xv = *reinterpret_cast<const uint4*>(x + base + c * 256);
+    uint4 wv = make_uint4(0, 0, 0, 0);
+    if (w) wv = *reinterpret_cast<const uint4*>(w + lane * 8 + c * 256);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+    const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&xv);
+    const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 g = __bfloat1622float2(g2[j]), xx = __bfloat1622float2(x2[j]);
+      float2 ww = make_float2(1.f, 1.f);
+      if (w) {
+        ww = __bfloat1622float2(w2[j]);
+        if (unit) { ww.x += 1.f; ww.y += 1.f; }
+      }
+      gw[c][2 * j] = g.x * ww.x;
+      gw[c][2 * j + 1] = g.y * ww.y;
+      xh[c][2 * j] = xx.x * r;
+      xh[c][2 * j + 1] = xx.y * r;
+      dot += gw[c][2 * j] * xh[c][2 * j] + gw[c][2 * j + 1] * xh[c][2 * j + 1];
+    }
+  }
+  dot = warp_sum(dot) / dim;
+#pragma unroll
+  for (int c = 0; c < NC; ++c) {
+    uint4 av = make_uint4(0, 0, 0, 0);
+    if (gadd) av = *reinterpret_cast<const uint4*>(gadd + base + c * 256);
+    const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av);
+    uint4 ov;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float d0 = r * (gw[c][2 * j] - xh[c][2 * j] * dot), d1 = r * (gw[c][2 * j + 1] - xh[c][2 * j + 1] * dot);
+      if (gadd) {
+        const float2 a = __bfloat1622float2(a2[j]);
+        d0 += a.x;
+        d1 += a.y;
+      }
+      o2[j] = __floats2bfloat162_rn(d0, d1);
+    }
+    *reinterpret_cast<uint4*>(dx + base + c * 256) = ov;
+  }
+}
+
+#define KVB_RMS_DISPATCH(NCV, ...)                                  \
+  switch (NCV) {                                                    \
+    case 4: { constexpr int NC = 4; __VA_ARGS__; break; }           \
+    case 8: { constexpr int NC = 8; __VA_ARGS__; break; }           \
+    case 10: { constexpr int NC = 10; __VA_ARGS__; break; }         \
+    case 12: { constexpr int NC = 12; __VA_ARGS__; break; }         \
+    case 14: { constexpr int NC = 14; __VA_ARGS__; break; }         \
+    case 16: { constexpr int NC = 16; __VA_ARGS__; break; }         \
+    case 20: { constexpr int NC = 20; __VA_ARGS__; break; }         \
+    default: return KVB_ERR_UNSUPPORTED;                            \
+  }
+#define KVB_RMS_DISPATCH_BWD(NCV, ...)                              \
+  switch (NCV) {                                                    \
+    case 4: { constexpr int NC = 4; __VA_ARGS__; break; }           \
+    case 8: { constexpr int NC = 8; __VA_ARGS__; break; }           \
+    case 10: { constexpr int NC = 10; __VA_ARGS__; break; }         \
+    case 12: { constexpr int NC = 12; __VA_ARGS__; break; }         \
+    default: return KVB_ERR_UNSUPPORTED;                            \
+  }
+static bool rms_fast_dim(int dim) {
+  if (dim % 256) return false;
+  const int nc = dim / 256;
+  return nc == 4 || nc == 8 || nc == 10 || nc == 12 || nc == 14 || nc == 16 || nc == 20;
+}
+
 // ------------------------------------------------- QKV split + QK-norm + RoPE
 // Row id = ((b * T + t) * (H + 2G) + head); heads [0,H) are queries, [H,H+G) keys,
 // [H+G,H+2G) values.
@@ -433,9 +586,35 @@ static inline int check_launch() { return cudaGetLastError() == cudaSuccess ? KV
 
 using namespace kvb;
 
+// y = rmsnorm(x + res) · w and sum_out = x + res (res and sum_out may be NULL together). bf16 only,
+// dim in {1024, 2048, 2560, 3072, 3584, 4096, 5120}; other cases: KVB_ERR_UNSUPPORTED.
+extern "C" int kvb_add_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* sum_out, float* rstd,
+                                   long long rows, int dim, float eps, int add_unit_offset, void* stream) {
+  if (rows <= 0 || dim <= 0 || ((res == nullptr) != (sum_out == nullptr))) return KVB_ERR_ARG;
+  if (!rms_fast_dim(dim)) return KVB_ERR_UNSUPPORTED;
+  const unsigned grid = (unsigned)((rows + EW_WARPS - 1) / EW_WARPS);
+  KVB_RMS_DISPATCH(dim / 256, (rmsnorm_fwd_bf16_kernel<NC><<<grid, EW_WARPS * 32, 0, (cudaStream_t)stream>>>(
+                                  (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w, (__nv_bfloat16*)y,
+                                  (__nv_bfloat16*)sum_out, rstd, rows, eps, add_unit_offset)));
+  return check_launch();
+}
+
+// dx = rmsnorm_backward(gy; x, w, rstd) + gadd (gadd may be NULL); bf16, dim in {1024, 2048, 2560, 3072}.
+extern "C" int kvb_rmsnorm_bwd_add(const void* gy, const void* x, const void* w, const float* rstd, const void* gadd, void* dx,
+                                   long long rows, int dim, int add_unit_offset, void* stream) {
+  if (rows <= 0 || dim <= 0) return KVB_ERR_ARG;
+  if (!rms_fast_dim(dim) || dim > 3072) return KVB_ERR_UNSUPPORTED;  // the row lives in registers as fp32
+  const unsigned grid = (unsigned)((rows + EW_WARPS - 1) / EW_WARPS);
+  KVB_RMS_DISPATCH_BWD(dim / 256, (rmsnorm_bwd_bf16_kernel<NC><<<grid, EW_WARPS * 32, 0, (cudaStream_t)stream>>>(
+                                  (const __nv_bfloat16*)gy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd,
+                                  (const __nv_bfloat16*)gadd, (__nv_bfloat16*)dx, rows, add_unit_offset)));
+  return check_launch();
+}
+
 extern "C" int kvb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long long rows, int dim, float eps,
                                int add_unit_offset, int dtype, void* stream) {
   if (rows <= 0 || dim <= 0) return KVB_ERR_ARG;
+  if (dtype == 1 && rms_fast_dim(dim)) return kvb_add_rmsnorm_fwd(x, nullptr, w, y, nullptr, rstd, rows, dim, eps, add_unit_offset, stream);
   const unsigned grid = (unsigned)((rows + EW_WARPS - 1) / EW_WARPS);
   KVB_DISPATCH_DTYPE(dtype, (rmsnorm_fwd_kernel<T><<<grid, EW_WARPS * 32, 0, (cudaStream_t)stream>>>(
                                 (const T*)x, (const T*)w, (T*)y, rstd, rows, dim, eps, add_unit_offset)));
@@ -445,6 +624,7 @@ extern "C" int kvb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rst
 extern "C" int kvb_rmsnorm_bwd(const void* gy, const void* x, const void* w, const float* rstd, void* dx, float* dw_partial,
                                long long rows, int dim, int add_unit_offset, int dtype, int n_partial, void* stream) {
   if (rows <= 0 || dim <= 0 || n_partial <= 0) return KVB_ERR_ARG;
+  if (dtype == 1 && !dw_partial && rms_fast_dim(dim) && dim <= 3072) return kvb_rmsnorm_bwd_add(gy, x, w, rstd, nullptr, dx, rows, dim, add_unit_offset, stream);
   const size_t smem = dw_partial ? (size_t)dim * 4 : 0;
   if (smem > 48 * 1024) return KVB_ERR_TOO_LARGE;
   KVB_DISPATCH_DTYPE(dtype, (rmsnorm_bwd_kernel<T><<<n_partial, EW_WARPS * 32, smem, (cudaStream_t)stream>>>(

@@ -22,6 +22,15 @@ enum {
 };
 
 // ---- elementwise.cu
+// Token cross-entropy (csrc/ce_loss.cu)
+int kvb_ce_loss_fwd(const void* logits, const long long* targets, float* loss, float* lse, long long rows, int V, long long ld,
+                    long long ignore_index, int dtype, void* stream);
+int kvb_ce_loss_bwd(const void* logits, const long long* targets, const float* lse, const float* grad, void* dlogits,
+                    long long rows, int V, long long ld, long long ignore_index, int dtype, void* stream);
+int kvb_add_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* sum_out, float* rstd, long long rows,
+                        int dim, float eps, int add_unit_offset, void* stream);
+int kvb_rmsnorm_bwd_add(const void* gy, const void* x, const void* w, const float* rstd, const void* gadd, void* dx,
+                        long long rows, int dim, int add_unit_offset, void* stream);
 int kvb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long long rows, int dim, float eps, int add_unit_offset,
                     int dtype, void* stream);
 int kvb_rmsnorm_bwd(const void* gy, const void* x, const void* w, const float* rstd, void* dx, float* dw_partial,

@@ -294,16 +294,24 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
         BW_TRACE(1, 1200000 + u);
         tc_fence_after();
         const uint32_t c1 = cbase + st * 2 * BW_UNIT_BYTES, c2 = c1 + BW_UNIT_BYTES;
+        // A: 16 columns of the unit per step = 8 TMEM columns; the two compute warps of a lane
+        // quarter keep their 32 columns in separate 32-column halves of the buffer.
+        // B: MN-major, 16 rows of the unit per step (2048 B); the 64-feature chunks are LBO apart.
+        // All steps of one accumulator are issued back to back: changing the accumulator between
+        // MMAs costs far more than the MMA itself.
+        if (MODE == MODE_DKV) {
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-          // A: 16 columns of the unit per step = 8 TMEM columns; the two compute warps of a lane
-          // quarter keep their 32 columns in separate 32-column halves of the buffer
-          const uint32_t a_col = (uint32_t)(32 * (kk >> 1) + 8 * (kk & 1));
-          // B: MN-major, 16 rows of the unit per step (2048 B); the 64-feature chunks are LBO apart
-          const uint32_t b_off = (uint32_t)(kk * 16 * 128);
-          if (MODE == MODE_DKV)
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint32_t a_col = (uint32_t)(32 * (kk >> 1) + 8 * (kk & 1));
+            const uint32_t b_off = (uint32_t)(kk * 16 * 128);
             umma_f16_ts(tmem_A1, tmem_X + 64 * hb + a_col, make_smem_desc_sw128(c2 + b_off, BW_UNIT_BYTES / 2, 1024), idesc_acc,
                         (u | kk) != 0);
+          }
+        }
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          const uint32_t a_col = (uint32_t)(32 * (kk >> 1) + 8 * (kk & 1));
+          const uint32_t b_off = (uint32_t)(kk * 16 * 128);
           umma_f16_ts(tmem_A2, tmem_Y + 64 * hb + a_col, make_smem_desc_sw128(c1 + b_off, BW_UNIT_BYTES / 2, 1024), idesc_acc,
                       (u | kk) != 0);
         }
@@ -652,9 +660,27 @@ extern "C" int kvb_sdpa_bwd(const void* q, const void* k, const void* v, const i
     cudaFuncSetAttribute(sdpa_bwd_kernel<MODE_DKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwSmem::TOTAL);
     attr_set = true;
   }
-  p.trace = g_bw_trace_mode == 0 ? g_bw_trace : nullptr; p.trace_cap = g_bw_trace_cap;
-  sdpa_bwd_kernel<MODE_DQ><<<B * G * p.nQT, BW_THREADS, BwSmem::TOTAL, s>>>(tmQ, tmdO, tmKh, tmVh, p);
-  p.trace = g_bw_trace_mode == 1 ? g_bw_trace : nullptr;
+  // The two launches are independent (dQ | dK, dV). They run on two streams, forked from and joined
+  // back into the caller's stream, so that the tail of one grid (256 CTAs of the dQ launch fill
+  // 148 SMs 1.73 times) is filled with CTAs of the other.
+  static cudaStream_t side[64] = {nullptr};
+  static cudaEvent_t ev_fork[64] = {nullptr}, ev_join[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return KVB_ERR_CUDA;
+  if (!side[dev]) {
+    if (cudaStreamCreateWithFlags(&side[dev], cudaStreamNonBlocking) != cudaSuccess) return KVB_ERR_CUDA;
+    if (cudaEventCreateWithFlags(&ev_fork[dev], cudaEventDisableTiming) != cudaSuccess) return KVB_ERR_CUDA;
+    if (cudaEventCreateWithFlags(&ev_join[dev], cudaEventDisableTiming) != cudaSuccess) return KVB_ERR_CUDA;
+  }
+  cudaEventRecord(ev_fork[dev], s);
+  cudaStreamWaitEvent(side[dev], ev_fork[dev], 0);
+  BwParams pq = p;
+  pq.trace = g_bw_trace_mode == 0 ? g_bw_trace : nullptr; pq.trace_cap = g_bw_trace_cap;
+  p.trace = g_bw_trace_mode == 1 ? g_bw_trace : nullptr; p.trace_cap = g_bw_trace_cap;
+  // the launch with few long CTAs goes first: the short CTAs of the other one fill its second wave
+  sdpa_bwd_kernel<MODE_DQ><<<B * G * p.nQT, BW_THREADS, BwSmem::TOTAL, side[dev]>>>(tmQ, tmdO, tmKh, tmVh, pq);
   sdpa_bwd_kernel<MODE_DKV><<<B * G * p.nT, BW_THREADS, BwSmem::TOTAL, s>>>(tmK, tmV, tmQh, tmdOh, p);
+  cudaEventRecord(ev_join[dev], side[dev]);
+  cudaStreamWaitEvent(s, ev_join[dev], 0);
   return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
 }

@@ -13,6 +13,8 @@ from typing import List, Optional, Union
 import torch
 import torch.nn.functional as F
 
+from keys_values_b200 import ops
+
 from keys_values_b200.config import Config
 
 IGNORE_INDEX = -100
@@ -65,9 +67,7 @@ class CrossEntropyOnLogits(HeadModel):
             return torch.zeros(model_outputs.shape[0], device=model_outputs.device, dtype=torch.float32)
         diff = self._check_model_outputs_targets(model_outputs, targets, self._vocab_size)
         logits = model_outputs[:, diff:, :]
-        losses = F.cross_entropy(
-            logits.reshape(-1, self._vocab_size).float(), targets.reshape(-1), ignore_index=IGNORE_INDEX, reduction="none"
-        )
+        losses = ops.cross_entropy_rows(logits.reshape(-1, self._vocab_size), targets, IGNORE_INDEX)
         return losses.view(targets.shape).sum(dim=-1)
 
     def num_target_entries(self, targets: torch.Tensor) -> Optional[torch.Tensor]:

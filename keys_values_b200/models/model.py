@@ -39,6 +39,10 @@ class RMSNorm(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return ops.rmsnorm(x, self.weight, self.eps, self.add_unit_offset)
 
+    def forward_add(self, x: torch.Tensor, residual: torch.Tensor):
+        """``(norm(x + residual), x + residual)`` in one pass over the data."""
+        return ops.add_rmsnorm(x, residual, self.weight, self.eps, self.add_unit_offset)
+
     def reset_parameters(self) -> None:
         nn.init.ones_(self.weight)
 
@@ -239,6 +243,8 @@ class Block(nn.Module):
             if not self.config.shared_attention_norm:
                 x_normed = self.norm_2(x)
             x = attn_out + x
+        elif isinstance(self.norm_2, RMSNorm):
+            x_normed, x = self.norm_2.forward_add(attn_out, x)  # residual add fused into the norm
         else:
             x = attn_out + x
             x_normed = self.norm_2(x)

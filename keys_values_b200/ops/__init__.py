@@ -52,6 +52,44 @@ def rmsnorm(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float, add_uni
     return ref.rmsnorm(x, weight, eps, add_unit_offset)
 
 
+class _AddRMSNormFn(torch.autograd.Function):
+    """``s = x + res; y = rmsnorm(s) · w`` in one pass; the backward pass adds the gradient that
+    reaches ``s`` through its other consumer (the residual path) in the same kernel."""
+
+    @staticmethod
+    def forward(ctx, x, res, weight, eps, add_unit_offset):
+        y, s, rstd = _cuda().add_rmsnorm_fwd(x, res, weight, eps, add_unit_offset)
+        ctx.save_for_backward(s, weight, rstd)
+        ctx.add_unit_offset = add_unit_offset
+        return y, s
+
+    @staticmethod
+    def backward(ctx, gy, gs):
+        s, weight, rstd = ctx.saved_tensors
+        need_w = weight is not None and ctx.needs_input_grad[2]
+        if need_w or gy is None:
+            # trainable norm weights: the general kernel, then the add
+            if gy is None:
+                return gs, gs, None, None, None
+            dx, dw = _cuda().rmsnorm_bwd(gy.contiguous(), s, weight, rstd, ctx.add_unit_offset, need_w)
+            if gs is not None:
+                dx = dx + gs
+            return dx, dx, dw, None, None
+        gadd = None if gs is None else gs.contiguous()
+        dx = _cuda().rmsnorm_bwd_add(gy.contiguous(), s, weight, rstd, gadd, ctx.add_unit_offset)
+        return dx, dx, None, None, None
+
+
+def add_rmsnorm(x: torch.Tensor, res: torch.Tensor, weight: Optional[torch.Tensor], eps: float,
+                add_unit_offset: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Returns ``(rmsnorm(x + res), x + res)``. One kernel on a GPU for bf16 rows of a supported
+    width, the two separate ops otherwise."""
+    if x.is_cuda and x.shape == res.shape and _cuda().add_rmsnorm_supported(x):
+        return _AddRMSNormFn.apply(x.contiguous(), res.contiguous(), weight, eps, add_unit_offset)
+    s = x + res
+    return rmsnorm(s, weight, eps, add_unit_offset), s
+
+
 # ------------------------------------------------------- QK-norm + RoPE + split
 class _QKNormRopeFn(torch.autograd.Function):
     @staticmethod
@@ -239,8 +277,32 @@ def h2o_update(scores, weights, k_select: int, n_evictable: int, normalize=False
     return ref.h2o_update(scores, weights, k_select, n_evictable, normalize, token_pos, input_pos, prefill_length)
 
 
+class _CrossEntropyFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, targets, ignore_index):
+        loss, lse = _cuda().ce_loss_fwd(logits, targets, ignore_index)
+        ctx.save_for_backward(logits, targets, lse)
+        ctx.ignore_index = ignore_index
+        return loss
+
+    @staticmethod
+    def backward(ctx, g):
+        logits, targets, lse = ctx.saved_tensors
+        return _cuda().ce_loss_bwd(logits, targets, lse, g.float().contiguous(), ctx.ignore_index), None, None
+
+
+def cross_entropy_rows(logits: torch.Tensor, targets: torch.Tensor, ignore_index: int = -100) -> torch.Tensor:
+    """Token cross-entropy per row of ``logits (N, V)`` (fp32 result, 0 for ignored targets). On a
+    GPU the bf16 / fp32 logits are read in place (no fp32 copy) by the ``ce_loss`` kernels."""
+    if logits.is_cuda and logits.dtype in (torch.bfloat16, torch.float32) and logits.stride(-1) == 1:
+        return _CrossEntropyFn.apply(logits, targets.reshape(-1).to(torch.int64).contiguous(), ignore_index)
+    return torch.nn.functional.cross_entropy(logits.float(), targets.reshape(-1), ignore_index=ignore_index, reduction="none")
+
+
 def cross_entropy_sum(logits: torch.Tensor, targets: torch.Tensor, ignore_index: int = -100) -> torch.Tensor:
-    return ref.cross_entropy_sum(logits, targets, ignore_index)
+    """Sum over positions of the token cross-entropy, per batch row: ``(B,)``."""
+    B = logits.shape[0]
+    return cross_entropy_rows(logits.reshape(-1, logits.shape[-1]), targets, ignore_index).view(B, -1).sum(dim=-1)
 
 
 def decode_attention(query, key, value, scale, input_pos, token_pos=None, return_weights=False):

@@ -121,6 +121,64 @@ def rmsnorm_fwd(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float, add
     return y, rstd
 
 
+# ----------------------------------------------------------- cross-entropy
+def ce_loss_fwd(logits: torch.Tensor, targets: torch.Tensor, ignore_index: int):
+    """``logits (N, V)`` fp32 / bf16 with unit stride along V, ``targets (N,)`` int64. Returns the
+    per-row loss and log-sum-exp, both fp32."""
+    N, V = logits.shape
+    loss = torch.empty(N, dtype=torch.float32, device=logits.device)
+    lse = torch.empty(N, dtype=torch.float32, device=logits.device)
+    _check(lib().kvb_ce_loss_fwd(_p(logits), _p(targets), _p(loss), _p(lse), _ll(N), V, _ll(logits.stride(0)), _ll(ignore_index),
+                                 0 if logits.dtype == torch.float32 else 1, _stream(logits)), "ce_loss_fwd")
+    _count()
+    return loss, lse
+
+
+def ce_loss_bwd(logits: torch.Tensor, targets: torch.Tensor, lse: torch.Tensor, grad: torch.Tensor, ignore_index: int):
+    N, V = logits.shape
+    dlogits = torch.empty((N, V), dtype=logits.dtype, device=logits.device)
+    if logits.stride(0) != V:
+        logits = logits.contiguous()
+    _check(lib().kvb_ce_loss_bwd(_p(logits), _p(targets), _p(lse), _p(grad), _p(dlogits), _ll(N), V, _ll(V), _ll(ignore_index),
+                                 0 if logits.dtype == torch.float32 else 1, _stream(logits)), "ce_loss_bwd")
+    _count()
+    return dlogits
+
+
+_RMS_FAST_DIMS = (1024, 2048, 2560, 3072, 3584, 4096, 5120)
+
+
+def add_rmsnorm_supported(x: torch.Tensor) -> bool:
+    """Fused ``s = x + res; y = rmsnorm(s)`` (and its backward with a fused gradient add): bf16 rows
+    that fit into the registers of a warp."""
+    return x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] in _RMS_FAST_DIMS and x.shape[-1] <= 3072
+
+
+def add_rmsnorm_fwd(x: torch.Tensor, res: torch.Tensor, weight: Optional[torch.Tensor], eps: float, add_unit_offset: bool):
+    dim = x.shape[-1]
+    rows = x.numel() // dim
+    if weight is not None and weight.dtype != x.dtype:
+        weight = weight.to(x.dtype)
+    y, s = torch.empty_like(x), torch.empty_like(x)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    _check(lib().kvb_add_rmsnorm_fwd(_p(x), _p(res), _p(weight), _p(y), _p(s), _p(rstd), _ll(rows), dim, ctypes.c_float(eps),
+                                     int(add_unit_offset), _stream(x)), "add_rmsnorm_fwd")
+    _count()
+    return y, s, rstd
+
+
+def rmsnorm_bwd_add(gy, x, weight, rstd, gadd, add_unit_offset: bool):
+    """``rmsnorm_backward(gy) + gadd`` in one pass (no weight gradient)."""
+    dim = x.shape[-1]
+    rows = x.numel() // dim
+    wt = None if weight is None else weight.to(x.dtype)
+    dx = torch.empty_like(x)
+    _check(lib().kvb_rmsnorm_bwd_add(_p(gy), _p(x), _p(wt), _p(rstd), _p(gadd), _p(dx), _ll(rows), dim, int(add_unit_offset),
+                                     _stream(x)), "rmsnorm_bwd_add")
+    _count()
+    return dx
+
+
 def rmsnorm_bwd(gy, x, weight, rstd, add_unit_offset: bool, need_w: bool):
     dim = x.shape[-1]
     rows = x.numel() // dim

@@ -293,3 +293,56 @@ def test_decode_attention(bits, B, H, G, L, C):
     out_r, w_r = ref.sdpa(q, k_eff, v_eff, scale, L - 1, None, True)
     torch.testing.assert_close(out.float(), out_r.float(), atol=2e-2, rtol=2e-2)
     torch.testing.assert_close(w, w_r, atol=1e-3, rtol=2e-2)
+
+
+@pytest.mark.parametrize("dim", [1024, 2560, 3072])
+def test_add_rmsnorm_fused(dim):
+    """s = x + res; y = rmsnorm(s): one kernel forward, one kernel backward (with the gradient of
+    the residual path added in the same pass), against the fp32 restatement."""
+    from keys_values_b200 import ops
+
+    torch.manual_seed(0)
+    rows = 777
+    x = torch.randn(rows, dim, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    r = torch.randn(rows, dim, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(dim, device=DEV) * 0.1 + 1).to(torch.bfloat16)
+    y, s = ops.add_rmsnorm(x, r, w, 1e-6, False)
+    gy, gs = torch.randn_like(y), torch.randn_like(s)
+    (y.float() * gy.float()).sum().backward(retain_graph=True)
+    gx1 = x.grad.clone()
+    x.grad = None
+    r.grad = None
+    ((y.float() * gy.float()).sum() + (s.float() * gs.float()).sum()).backward()
+    # reference in fp32 from the bf16-rounded sum
+    xf = x.detach().float().requires_grad_(True)
+    rf = r.detach().float().requires_grad_(True)
+    sf = (xf + rf).to(torch.bfloat16).float() + 0 * (xf + rf)  # value of the rounded sum, gradient of the sum
+    yf = ref.rmsnorm(sf, w.float(), 1e-6, False)
+    ((yf * gy.float()).sum() + (sf * gs.float()).sum()).backward()
+    assert torch.equal(s.detach(), (x.detach().float() + r.detach().float()).to(torch.bfloat16))
+    assert _rel_err(y.detach(), yf.detach()) < 1e-2
+    assert _rel_err(x.grad, xf.grad) < 2e-2
+    assert _rel_err(r.grad, rf.grad) < 2e-2
+    assert gx1.isfinite().all()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("V", [1000, 151936, 32003])
+def test_ce_loss_kernels(dtype, V):
+    from keys_values_b200 import ops
+
+    torch.manual_seed(1)
+    N = 37
+    logits = (torch.randn(N, V, device=DEV) * 3).to(dtype).requires_grad_(True)
+    targets = torch.randint(0, V, (N,), device=DEV)
+    targets[3] = -100
+    loss = ops.cross_entropy_rows(logits, targets, -100)
+    g = torch.rand(N, device=DEV)
+    (loss * g).sum().backward()
+    lf = logits.detach().float().requires_grad_(True)
+    ref_loss = torch.nn.functional.cross_entropy(lf, targets, ignore_index=-100, reduction="none")
+    (ref_loss * g).sum().backward()
+    torch.testing.assert_close(loss, ref_loss, atol=2e-3, rtol=1e-4)
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
+    assert _rel_err(logits.grad, lf.grad) < tol
+    assert loss[3] == 0 and logits.grad[3].abs().max() == 0
