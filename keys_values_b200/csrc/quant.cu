@@ -50,6 +50,121 @@ __device__ __forceinline__ void quantize_row_warp(const float* xs, int D, int bi
   }
 }
 
+// ---- fast paths: bf16 rows of 128 values. A lane holds features 4·lane .. 4·lane + 3 (one
+// 8-byte load), the row statistics are warp reductions, the codes leave as one 32-bit store.
+__device__ __forceinline__ void q128_load(const __nv_bfloat16* row, int lane, float* x, uint2& raw) {
+  raw = *reinterpret_cast<const uint2*>(row + 4 * lane);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  const float2 a = __bfloat1622float2(h[0]), c = __bfloat1622float2(h[1]);
+  x[0] = a.x; x[1] = a.y; x[2] = c.x; x[3] = c.y;
+}
+
+// Same arithmetic as quantize_row_warp, for a row held as 4 values per lane.
+__device__ __forceinline__ void quantize_row128(const float* x, int bits, uint8_t* qdst, float* sdst, int32_t* zdst, int lane) {
+  float mn = fminf(fminf(x[0], x[1]), fminf(x[2], x[3])), mx = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
+  mn = warp_min(mn);
+  mx = warp_max(mx);
+  const float qmax = (float)((1 << bits) - 1);
+  const float scale = fmaxf(__fdiv_rn(mx - mn, qmax), QUANT_EPS);
+  const float zpf = 0.f - rintf(__fdiv_rn(mn, scale));
+  if (lane == 0) {
+    *sdst = scale;
+    *zdst = (int32_t)zpf;
+  }
+  uint32_t c[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) c[i] = (uint32_t)fminf(fmaxf(rintf(__fdiv_rn(x[i], scale)) + zpf, 0.f), qmax);
+  if (bits == 8) {
+    *reinterpret_cast<uint32_t*>(qdst + 4 * lane) = c[0] | (c[1] << 8) | (c[2] << 16) | (c[3] << 24);
+  } else {
+    // byte j = (code[j] << 4) | code[j + 64]: the low nibbles come from lane + 16
+    uint32_t packed = c[0] | (c[1] << 8) | (c[2] << 16) | (c[3] << 24);
+    const uint32_t low = __shfl_down_sync(0xffffffffu, packed, 16);
+    if (lane < 16) *reinterpret_cast<uint32_t*>(qdst + 4 * lane) = (packed << 4) | low;
+  }
+}
+
+__global__ void __launch_bounds__(Q_WARPS * 32)
+quantize_rows128_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scale,
+                        int32_t* __restrict__ zp, long long rows, int bits) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int Dq = bits == 8 ? 128 : 64;
+  // two rows per warp, both loads issued before the arithmetic
+  const long long r0 = ((long long)blockIdx.x * Q_WARPS + warp) * 2;
+  if (r0 >= rows) return;
+  const bool two = r0 + 1 < rows;
+  float a[4], b[4];
+  uint2 raw;
+  q128_load(x + r0 * 128, lane, a, raw);
+  if (two) q128_load(x + (r0 + 1) * 128, lane, b, raw);
+  quantize_row128(a, bits, q + r0 * Dq, scale + r0, zp + r0, lane);
+  if (two) quantize_row128(b, bits, q + (r0 + 1) * Dq, scale + r0 + 1, zp + r0 + 1, lane);
+}
+
+__global__ void __launch_bounds__(Q_WARPS * 32)
+dequantize_rows128_kernel(const uint8_t* __restrict__ q, const float* __restrict__ scale, const int32_t* __restrict__ zp,
+                          __nv_bfloat16* __restrict__ out, int B, int G, int n, long long q_sb, long long q_sg, long long q_sn,
+                          long long m_sb, long long m_sg, long long o_sb, long long o_sg, long long o_sn, int bits) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * Q_WARPS + (threadIdx.x >> 5);
+  if (row >= (long long)B * G * n) return;
+  const int i = (int)(row % n);
+  const int g = (int)((row / n) % G);
+  const int b = (int)(row / ((long long)n * G));
+  const uint8_t* qr = q + b * q_sb + g * q_sg + i * q_sn;
+  const float s = scale[b * m_sb + g * m_sg + i];
+  const float z = (float)zp[b * m_sb + g * m_sg + i];
+  uint32_t c[4];
+  if (bits == 8) {
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(qr + 4 * lane);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) c[k] = (w >> (8 * k)) & 0xFFu;
+  } else {
+    // features 4·lane ..: high nibbles of bytes 4·lane .. for lane < 16, low nibbles of bytes 4·(lane − 16) .. otherwise
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(qr + 4 * (lane & 15));
+    const int sh = lane < 16 ? 4 : 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) c[k] = (w >> (8 * k + sh)) & 0xFu;
+  }
+  __nv_bfloat162 lo = __floats2bfloat162_rn(((float)c[0] - z) * s, ((float)c[1] - z) * s);
+  __nv_bfloat162 hi = __floats2bfloat162_rn(((float)c[2] - z) * s, ((float)c[3] - z) * s);
+  uint2 o;
+  o.x = *reinterpret_cast<uint32_t*>(&lo);
+  o.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(out + b * o_sb + g * o_sg + i * o_sn + 4 * lane) = o;
+}
+
+// One warp per new row (b, g, i): scatter K and V into their slot, token position, quantize-on-write.
+__global__ void __launch_bounds__(Q_WARPS * 32)
+cache_write128_kernel(__nv_bfloat16* __restrict__ k_buf, __nv_bfloat16* __restrict__ v_buf, int32_t* __restrict__ token_pos,
+                      const int32_t* __restrict__ slots, const __nv_bfloat16* __restrict__ key,
+                      const __nv_bfloat16* __restrict__ value, uint8_t* __restrict__ qk, float* __restrict__ sk,
+                      int32_t* __restrict__ zk, uint8_t* __restrict__ qv, float* __restrict__ sv, int32_t* __restrict__ zv, int B,
+                      int G, int n, int C, long long slot_sb, long long slot_sg, int input_pos, int bits, int* status) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long row = (long long)blockIdx.x * Q_WARPS + warp;
+  if (row >= (long long)B * G * n) return;
+  const int i = (int)(row % n);
+  const int g = (int)((row / n) % G);
+  const int b = (int)(row / ((long long)n * G));
+  const int slot = slots[b * slot_sb + g * slot_sg + i];
+  if (slot < 0 || slot >= C) {  // never write out of bounds: record and skip
+    if (lane == 0 && status) atomicCAS(status, 0, STATUS_BAD_INDEX);
+    return;
+  }
+  const long long dst_row = ((long long)b * G + g) * C + slot;
+  const int Dq = bits == 8 ? 128 : 64;
+  float kx[4], vx[4];
+  uint2 kraw, vraw;
+  q128_load(key + row * 128, lane, kx, kraw);
+  q128_load(value + row * 128, lane, vx, vraw);
+  if (lane == 0) token_pos[dst_row] = input_pos + i;
+  if (k_buf) *reinterpret_cast<uint2*>(k_buf + dst_row * 128 + 4 * lane) = kraw;
+  if (v_buf) *reinterpret_cast<uint2*>(v_buf + dst_row * 128 + 4 * lane) = vraw;
+  if (qk) quantize_row128(kx, bits, qk + dst_row * Dq, sk + dst_row, zk + dst_row, lane);
+  if (qv) quantize_row128(vx, bits, qv + dst_row * Dq, sv + dst_row, zv + dst_row, lane);
+}
+
 template <typename T>
 __global__ void quantize_rows_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scale,
                                      int32_t* __restrict__ zp, long long rows, int D, int bits) {
@@ -152,6 +267,11 @@ using namespace kvb;
 extern "C" int kvb_quantize_rows(const void* x, uint8_t* q, float* scale, int32_t* zp, long long rows, int D, int bits,
                                  int dtype, void* stream) {
   if (rows <= 0 || D <= 0 || (bits != 4 && bits != 8) || (bits == 4 && (D & 1))) return KVB_ERR_ARG;
+  if (dtype == 1 && D == 128 && !(reinterpret_cast<uintptr_t>(x) & 7) && !(reinterpret_cast<uintptr_t>(q) & 3)) {
+    const unsigned g128 = (unsigned)((rows + 2 * Q_WARPS - 1) / (2 * Q_WARPS));
+    quantize_rows128_kernel<<<g128, Q_WARPS * 32, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, q, scale, zp, rows, bits);
+    return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
+  }
   if ((size_t)Q_WARPS * D * 4 > 48 * 1024) return KVB_ERR_TOO_LARGE;
   const unsigned grid = (unsigned)((rows + Q_WARPS - 1) / Q_WARPS);
   KVB_DISPATCH_DTYPE(dtype, (quantize_rows_kernel<T><<<grid, Q_WARPS * 32, (size_t)Q_WARPS * D * 4, (cudaStream_t)stream>>>(
@@ -165,6 +285,12 @@ extern "C" int kvb_dequantize_rows(const uint8_t* q, const float* scale, const i
   if (B <= 0 || G <= 0 || n <= 0 || D <= 0 || (bits != 4 && bits != 8)) return KVB_ERR_ARG;
   const long long rows = (long long)B * G * n;
   const unsigned grid = (unsigned)((rows + Q_WARPS - 1) / Q_WARPS);
+  if (dtype == 1 && D == 128 && !(reinterpret_cast<uintptr_t>(q) & 3) && !(reinterpret_cast<uintptr_t>(out) & 7) &&
+      !((q_sb | q_sg | q_sn) & 3) && !((o_sb | o_sg | o_sn) & 3)) {
+    dequantize_rows128_kernel<<<grid, Q_WARPS * 32, 0, (cudaStream_t)stream>>>(q, scale, zp, (__nv_bfloat16*)out, B, G, n, q_sb, q_sg,
+                                                                              q_sn, m_sb, m_sg, o_sb, o_sg, o_sn, bits);
+    return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
+  }
   KVB_DISPATCH_DTYPE(dtype, (dequantize_rows_kernel<T><<<grid, Q_WARPS * 32, 0, (cudaStream_t)stream>>>(
                                 q, scale, zp, (T*)out, B, G, n, D, q_sb, q_sg, q_sn, m_sb, m_sg, o_sb, o_sg, o_sn, bits)));
   return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
@@ -179,6 +305,13 @@ extern "C" int kvb_cache_write(void* k_buf, void* v_buf, int32_t* token_pos, con
   if ((size_t)Q_WARPS * D * 4 > 48 * 1024) return KVB_ERR_TOO_LARGE;
   const long long rows = (long long)B * G * n;
   const unsigned grid = (unsigned)((rows + Q_WARPS - 1) / Q_WARPS);
+  auto al = [](const void* p, uintptr_t m) { return (reinterpret_cast<uintptr_t>(p) & m) == 0; };
+  if (dtype == 1 && D == 128 && al(key, 7) && al(value, 7) && al(k_buf, 7) && al(v_buf, 7) && al(qk, 3) && al(qv, 3)) {
+    cache_write128_kernel<<<grid, Q_WARPS * 32, 0, (cudaStream_t)stream>>>(
+        (__nv_bfloat16*)k_buf, (__nv_bfloat16*)v_buf, token_pos, slots, (const __nv_bfloat16*)key, (const __nv_bfloat16*)value, qk,
+        sk, zk, qv, sv, zv, B, G, n, C, slot_sb, slot_sg, input_pos, bits ? bits : 8, status);
+    return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
+  }
   KVB_DISPATCH_DTYPE(dtype, (cache_write_kernel<T><<<grid, Q_WARPS * 32, (size_t)Q_WARPS * D * 4, (cudaStream_t)stream>>>(
                                 (T*)k_buf, (T*)v_buf, token_pos, slots, (const T*)key, (const T*)value, qk, sk, zk, qv, sv, zv, B,
                                 G, n, D, C, slot_sb, slot_sg, input_pos, bits ? bits : 8, status)));
