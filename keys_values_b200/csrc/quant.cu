@@ -84,21 +84,24 @@ __device__ __forceinline__ void quantize_row128(const float* x, int bits, uint8_
   }
 }
 
+constexpr int Q128_ROWS = 8;
+
 __global__ void __launch_bounds__(Q_WARPS * 32)
 quantize_rows128_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scale,
                         int32_t* __restrict__ zp, long long rows, int bits) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int Dq = bits == 8 ? 128 : 64;
-  // two rows per warp, both loads issued before the arithmetic
-  const long long r0 = ((long long)blockIdx.x * Q_WARPS + warp) * 2;
+  // Q128_ROWS rows per warp, all loads issued before the arithmetic (64 bytes in flight per lane)
+  const long long r0 = ((long long)blockIdx.x * Q_WARPS + warp) * Q128_ROWS;
   if (r0 >= rows) return;
-  const bool two = r0 + 1 < rows;
-  float a[4], b[4];
+  float a[Q128_ROWS][4];
   uint2 raw;
-  q128_load(x + r0 * 128, lane, a, raw);
-  if (two) q128_load(x + (r0 + 1) * 128, lane, b, raw);
-  quantize_row128(a, bits, q + r0 * Dq, scale + r0, zp + r0, lane);
-  if (two) quantize_row128(b, bits, q + (r0 + 1) * Dq, scale + r0 + 1, zp + r0 + 1, lane);
+#pragma unroll
+  for (int r = 0; r < Q128_ROWS; ++r)
+    if (r0 + r < rows) q128_load(x + (r0 + r) * 128, lane, a[r], raw);
+#pragma unroll
+  for (int r = 0; r < Q128_ROWS; ++r)
+    if (r0 + r < rows) quantize_row128(a[r], bits, q + (r0 + r) * Dq, scale + r0 + r, zp + r0 + r, lane);
 }
 
 __global__ void __launch_bounds__(Q_WARPS * 32)
@@ -268,7 +271,7 @@ extern "C" int kvb_quantize_rows(const void* x, uint8_t* q, float* scale, int32_
                                  int dtype, void* stream) {
   if (rows <= 0 || D <= 0 || (bits != 4 && bits != 8) || (bits == 4 && (D & 1))) return KVB_ERR_ARG;
   if (dtype == 1 && D == 128 && !(reinterpret_cast<uintptr_t>(x) & 7) && !(reinterpret_cast<uintptr_t>(q) & 3)) {
-    const unsigned g128 = (unsigned)((rows + 2 * Q_WARPS - 1) / (2 * Q_WARPS));
+    const unsigned g128 = (unsigned)((rows + Q128_ROWS * Q_WARPS - 1) / (Q128_ROWS * Q_WARPS));
     quantize_rows128_kernel<<<g128, Q_WARPS * 32, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, q, scale, zp, rows, bits);
     return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
   }
