@@ -17,6 +17,7 @@ from keys_values_b200.kvcache.gradient.main import LongContextGradientModel
 from keys_values_b200.models import lora as lora_mod
 from keys_values_b200.models.head_model import CrossEntropyOnLogits, HeadModel
 from keys_values_b200.models.pos_encoding import position_encoding_factory
+from keys_values_b200.utils.recovery import OOMRetry
 
 
 @dataclass
@@ -122,14 +123,39 @@ def build_lora_training_setup(
     return setup
 
 
+def _free_after_oom(setup: TrainingSetup) -> None:
+    import gc
+
+    setup.model.clear()  # checkpoints, replay logs and saved attention outputs of the failed attempt
+    gc.collect()
+    if torch.cuda.is_available():
+        torch.cuda.empty_cache()
+
+
 def training_step(setup: TrainingSetup, input_ids: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
     """Forward, backward, gradient all-reduce (mean over ranks), clipping, optimizer
     step. Returns the (local) loss as a 0-d device tensor."""
-    setup.optimizer.zero_grad(set_to_none=False if setup.grad_reducer is not None else True)
-    if setup.grad_reducer is not None:
-        setup.grad_reducer.begin_step()
-    loss = setup.model(input_ids, targets)
-    loss.backward()
+    health = setup.extras.get("health")
+    if health is not None:
+        # host rendezvous: no rank launches the collectives of a step that a lost peer will never join
+        health.enter_step(setup.step, grace_s=setup.extras.get("health_grace_s", 60.0))
+
+    def attempt(_limit_gb: float, save_attention: bool):
+        if not save_attention:
+            setup.model.save_attention_outputs = False  # recompute in the backward pass instead
+        setup.optimizer.zero_grad(set_to_none=False if setup.grad_reducer is not None else True)
+        if setup.grad_reducer is not None:
+            setup.grad_reducer.begin_step()
+        out = setup.model(input_ids, targets)
+        out.backward()
+        return out
+
+    if setup.world_size == 1:
+        # out of memory: free, give up the saved attention outputs, retry (single rank only: with
+        # several ranks a retry on one of them would leave the others inside the gradient all-reduce)
+        loss = OOMRetry(limits_gb=(0.0,), free_fn=lambda: _free_after_oom(setup)).run(attempt)
+    else:
+        loss = attempt(0.0, True)
     if setup.grad_reducer is not None:
         setup.grad_reducer.finish_step()
     if setup.max_norm is not None:
