@@ -32,7 +32,7 @@ namespace kvb {
 constexpr int BW_TILE_BYTES = 128 * 128 * 2;   // row operand: two 64-feature chunks of [128 rows x 128 B]
 constexpr int BW_UNIT_BYTES = 64 * 128 * 2;    // column operand of one unit: two chunks of [64 rows x 128 B]
 constexpr int BW_STAGES = 4;                   // ring of column units (C1 | C2 per stage)
-constexpr int BW_THREADS = 320;                // TMA warp + MMA warp + 8 compute warps
+constexpr int BW_THREADS = 352;                // TMA warp + MMA warp (even units) + 8 compute warps + MMA warp (odd units)
 enum { MODE_DQ = 0, MODE_DKV = 1 };
 
 struct BwSmem {
@@ -124,7 +124,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
   uint64_t* pds_full = bars + 11;  // [2]
   uint64_t* acc_full = bars + 13;
   uint64_t* grp_bar = bars + 14;
-  uint64_t* rows_ready = bars + 15;  // MODE_DQ: the row operands are in TMEM
+  uint64_t* rows_ready = bars + 15;  // accumulators zeroed (and, MODE_DQ, the row operands moved to TMEM)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* stat_nlse = reinterpret_cast<float*>(smem + S::STATS + 512);  // MODE_DKV: [2][128] −lse·log2(e) of the query tile
@@ -170,7 +170,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
       mbar_init(&xy_full[s], 1);
       mbar_init(&pds_full[s], 8);
     }
-    mbar_init(acc_full, 1);
+    mbar_init(acc_full, 2);  // one commit per MMA issuer
     mbar_init(grp_bar, 256);
     mbar_init(rows_ready, 8);
     *abort_flag = 0;
@@ -244,20 +244,27 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------- MMA issuer
+  } else if (warp == 1 || warp == 10) {
+    // ------------------------------------------------------------ MMA issuers
+    // Two threads issue: warp 1 the even units, warp 10 the odd ones. A unit's MMAs (its X / Y pair
+    // and, two units later in the same thread, the accumulating MMAs that read P / dS from the same
+    // TMEM buffer) stay in one thread, so their order is the issue order; the accumulators are
+    // shared by both threads, which is why they are zeroed up front and every MMA accumulates.
+    // While one thread sits in its barrier waits (≈ 250 cycles each, even when satisfied) the other
+    // one keeps the tensor pipe fed.
     if (lane == 0 && n_active > 0) {
+      const uint32_t par = warp == 1 ? 0u : 1u;
       constexpr uint32_t idesc_xy = make_idesc_bf16(128, 64, 0, 0);     // both operands K-major
       constexpr uint32_t idesc_acc = make_idesc_bf16(128, 128, 0, 1);   // A from TMEM, B MN-major
       const uint32_t r1 = smem_u32(smem + S::R1), r2 = smem_u32(smem + S::R2);
       const uint32_t cbase = smem_u32(smem + S::C);
       const uint32_t n_units = 2u * (uint32_t)n_active;
       bool ok = mbar_wait_bounded(r_full, 0, abort_flag, p.status, STATUS_TIMEOUT_FULL);
-      if (MODE == MODE_DQ && ok) {
+      if (ok) {
         ok = mbar_wait_bounded(rows_ready, 0, abort_flag, p.status, STATUS_TIMEOUT_FULL);
         tc_fence_after();
       }
-      int tr_n = 0;
+      int tr_n = par == 0 ? 0 : (1 << 30);  // only the first issuer records
       auto wait_c = [&](uint32_t u) -> bool {
         return mbar_wait_bounded(&c_full[u % BW_STAGES], (u / BW_STAGES) & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL);
       };
@@ -304,39 +311,36 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
           for (int kk = 0; kk < 4; ++kk) {
             const uint32_t a_col = (uint32_t)(32 * (kk >> 1) + 8 * (kk & 1));
             const uint32_t b_off = (uint32_t)(kk * 16 * 128);
-            umma_f16_ts(tmem_A1, tmem_X + 64 * hb + a_col, make_smem_desc_sw128(c2 + b_off, BW_UNIT_BYTES / 2, 1024), idesc_acc,
-                        (u | kk) != 0);
+            umma_f16_ts(tmem_A1, tmem_X + 64 * hb + a_col, make_smem_desc_sw128(c2 + b_off, BW_UNIT_BYTES / 2, 1024), idesc_acc, 1);
           }
         }
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
           const uint32_t a_col = (uint32_t)(32 * (kk >> 1) + 8 * (kk & 1));
           const uint32_t b_off = (uint32_t)(kk * 16 * 128);
-          umma_f16_ts(tmem_A2, tmem_Y + 64 * hb + a_col, make_smem_desc_sw128(c1 + b_off, BW_UNIT_BYTES / 2, 1024), idesc_acc,
-                      (u | kk) != 0);
+          umma_f16_ts(tmem_A2, tmem_Y + 64 * hb + a_col, make_smem_desc_sw128(c1 + b_off, BW_UNIT_BYTES / 2, 1024), idesc_acc, 1);
         }
         umma_commit(&c_empty[st]);
         return true;
       };
-      uint32_t ux = 0;
-      while (ok && ux < n_units && ux < 2) {
-        ok = wait_c(ux);
-        if (ok) ok = issue_xy(ux++);
+      if (ok && par < n_units) {
+        ok = wait_c(par);
+        if (ok) ok = issue_xy(par);
       }
-      for (uint32_t u = 0; u < n_units && ok; ++u) {
-        // the columns of unit ux are awaited while the compute warps still work on unit u, so
+      for (uint32_t u = par; u < n_units && ok; u += 2) {
+        // the columns of unit u + 2 are awaited while the compute warps still work on unit u, so
         // that only the wait for P / dS lies between them and the next MMAs
         BW_TRACE(1, 1000000 + u);
-        if (ux < n_units) ok = wait_c(ux);
+        if (u + 2 < n_units) ok = wait_c(u + 2);
         BW_TRACE(1, 1100000 + u);
         if (ok) ok = issue_acc(u);
         BW_TRACE(1, 1300000 + u);
-        if (ok && ux < n_units) ok = issue_xy(ux++);
+        if (ok && u + 2 < n_units) ok = issue_xy(u + 2);
         BW_TRACE(1, 1400000 + u);
       }
       if (ok) umma_commit(acc_full);
     }
-  } else {
+  } else if (warp >= 2) {
     // ----------------------------------------------- compute + epilogue warps
     // 8 warps: two per TMEM lane quarter; thread (row, hh) owns columns [32·hh, +32) of its row in
     // every 64-column unit, and columns [64·hh, +64) of the accumulators in the epilogue
@@ -387,11 +391,20 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
       if (tid < 128) stat_nlse[buf * 128 + tid] = v;
       else stat_ndls[buf * 128 + (tid - 128)] = v;
     };
-    if (MODE == MODE_DQ && ok) {
-      // row operands: shared memory -> registers -> TMEM. This thread moves features
+    if (ok) {
+      // zero this thread's 64 columns of the accumulator(s): both MMA issuers only ever accumulate
+      uint32_t z[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) z[i] = 0;
+#pragma unroll
+      for (int c = 0; c < 64; c += 16) {
+        if (MODE == MODE_DKV) tmem_st_32x32b_x16(tmem_A1 + lane_base + (uint32_t)(64 * hh + c), z);
+        tmem_st_32x32b_x16(tmem_A2 + lane_base + (uint32_t)(64 * hh + c), z);
+      }
+      if (MODE == MODE_DQ) ok = mbar_wait_bounded(r_full, 0, abort_flag, p.status, STATUS_TIMEOUT_FULL);
+      // MODE_DQ row operands: shared memory -> registers -> TMEM. This thread moves features
       // [64·hh, +64) of its row: one 128-byte swizzled row of chunk hh = 32 columns of bf16 pairs.
-      ok = mbar_wait_bounded(r_full, 0, abort_flag, p.status, STATUS_TIMEOUT_FULL);
-      if (ok) {
+      if (MODE == MODE_DQ && ok) {
 #pragma unroll
         for (int op = 0; op < 2; ++op) {
           const uint8_t* src = smem + (op == 0 ? S::R1 : S::R2) + hh * (BW_TILE_BYTES / 2);
@@ -405,11 +418,11 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
           tmem_st_32x32b_x16(dst, w);
           tmem_st_32x32b_x16(dst + 16, w + 16);
         }
-        tmem_st_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(rows_ready);
       }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0 && ok) mbar_arrive(rows_ready);
     }
     int ct = next_active(0);
     if (MODE == MODE_DKV && ok) {
