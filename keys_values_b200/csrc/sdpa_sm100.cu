@@ -29,8 +29,9 @@
 //     the CTA take the mask-free path. In a masked tile only the columns whose token lies
 //     beyond the first query need a per-row comparison; their positions travel by warp
 //     shuffle and end up as a 64-bit mask per row, without shared memory or block barriers.
-//   * warp 0 = TMA producer, warp 1 = MMA issuer / TMEM owner, warps 2..5 = softmax +
-//     epilogue: each thread owns one query row (its TMEM lane) of every tile.
+//   * warp 0 = TMA producer, warp 1 = MMA issuer / TMEM owner, warps 2..9 = softmax + epilogue:
+//     two warps per TMEM lane quarter, each thread owns one query row (its TMEM lane) and 32 of
+//     the 64 columns of every tile.
 //
 // Replaces FlashInfer prefill + Triton score-sum + K/V reordering + query padding of the
 // reference (keys_values/attention/flashinfer_wrapper.py:51-273, :367-510,
@@ -49,7 +50,7 @@ int make_tmap_2d_bf16(CUtensorMap* tm, const void* ptr, uint64_t rows, uint64_t 
 constexpr int ATT_BM = 128;   // query rows per CTA
 constexpr int ATT_BN = 64;    // KV slots per tile
 constexpr int ATT_D = 128;    // head size
-constexpr int ATT_THREADS = 192;  // TMA warp + MMA warp + 4 softmax warps; two CTAs per SM
+constexpr int ATT_THREADS = 320;  // TMA warp + MMA warp + 8 softmax warps; two CTAs per SM
 constexpr int ATT_Q_BYTES = ATT_BM * ATT_D * 2;    // 32 KB: two 64-feature chunks of [128 rows x 128 B]
 constexpr int ATT_KV_BYTES = ATT_BN * ATT_D * 2;   // 16 KB: two 64-feature chunks of [64 rows x 128 B]
 constexpr int ATT_P_BYTES = ATT_BM * ATT_BN * 2;   // 16 KB: one 64-column chunk of [128 rows x 128 B]
@@ -168,7 +169,8 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* p_empty = bars + 16;
   uint64_t* o_full = bars + 17;
   uint64_t* q_ready = bars + 18;  // Q has been moved from shared memory to TMEM
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
+  uint64_t* grp_bar = bars + 19;  // barrier among the 256 softmax threads (bounded, unlike bar.sync)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -217,11 +219,12 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(&v_empty[s], 1);
     }
     mbar_init(s_full, 1);
-    mbar_init(s_empty, 4);
-    mbar_init(p_full, 4);
+    mbar_init(s_empty, 8);
+    mbar_init(p_full, 8);
     mbar_init(p_empty, 1);
     mbar_init(o_full, 1);
-    mbar_init(q_ready, 4);
+    mbar_init(q_ready, 8);
+    mbar_init(grp_bar, 256);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -364,9 +367,12 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else {
     // ------------------------------------------------- softmax + epilogue warps
-    // 4 warps, one query row (TMEM lane) per thread, 64 columns per KV tile. A second CTA on the
-    // same SM runs its own chain, which is what keeps MUFU / ALU / tensor pipes busy.
+    // 8 warps: two per TMEM lane quarter. A thread owns one query row (its TMEM lane) and 32 of the
+    // 64 columns of every KV tile (hh = which half), so the serial chain of a tile (barrier wait,
+    // TMEM load, exp2, P store, column sums) is half as long per warp and four warps per SM
+    // sub-partition (two CTAs) fill each other's latencies.
     const int quarter = warp & 3;
+    const int hh = (warp - 2) >> 2;
     const int row = quarter * 32 + lane;          // TMEM lane = query row of the tile
     const int hq = row / p.npos;                  // head within the group
     const int pl = row % p.npos;                  // position within the tile
@@ -385,52 +391,51 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // Token positions of a tile: lane holds columns lane and lane + 32 (INT_MAX beyond the cache).
     // The positions of the next tile are fetched one tile ahead.
     const int32_t* tpp = p.token_pos ? p.token_pos + b * p.tp_sb + g * p.tp_sg : nullptr;
-    auto fetch_tp = [&](int t, int& v0, int& v1) {
-      const int j0 = t * ATT_BN + lane, j1 = j0 + 32;
+    auto fetch_tp = [&](int t, int& v0) {  // lane holds column 32·hh + lane of the tile
+      const int j0 = t * ATT_BN + 32 * hh + lane;
       v0 = j0 < p.L ? (tpp ? tpp[j0] : j0) : INT_MAX;
-      v1 = j1 < p.L ? (tpp ? tpp[j1] : j1) : INT_MAX;
     };
-    int pf0 = INT_MAX, pf1 = INT_MAX, pf_t = -1;
+    int pf0 = INT_MAX, pf_t = -1;
     // Mask bits of this thread's row for a masked tile (bit e of mlo / mhi: column e / 32 + e is
     // hidden). Only columns whose token lies beyond the first query of the CTA need the per-row
     // comparison; their positions are broadcast by shuffle, so no shared memory is involved.
-    auto row_mask = [&](int v0, int v1, uint32_t& mlo, uint32_t& mhi) {
-      uint32_t n0 = __ballot_sync(0xffffffffu, v0 > qpos_min), n1 = __ballot_sync(0xffffffffu, v1 > qpos_min);
-      mlo = mhi = 0;
+    auto row_mask = [&](int v0) -> uint32_t {
+      uint32_t n0 = __ballot_sync(0xffffffffu, v0 > qpos_min), mlo = 0;
       while (n0) {
         const int e = __ffs(n0) - 1;
         n0 &= n0 - 1;
         mlo |= (uint32_t)(__shfl_sync(0xffffffffu, v0, e) > my_pos) << e;
       }
-      while (n1) {
-        const int e = __ffs(n1) - 1;
-        n1 &= n1 - 1;
-        mhi |= (uint32_t)(__shfl_sync(0xffffffffu, v1, e) > my_pos) << e;
-      }
+      return mlo;
+    };
+    uint32_t grp_phase = 0;
+    auto group_sync = [&]() -> bool {  // all 256 softmax threads; false if it ran into the wait limit
+      mbar_arrive(grp_bar);
+      const bool done = mbar_wait_bounded(grp_bar, grp_phase, abort_flag, p.status, STATUS_TIMEOUT_MISC);
+      grp_phase ^= 1;
+      return done;
     };
     // column-sum partials: slot (4·qt + warp quarter) of wpart (B,G,4·nQT,L). A warp sums the 32
-    // rows that it wrote itself, so the column sums need no barrier among the warps; lane ->
-    // columns (2·lane, 2·lane + 1) of the tile.
+    // rows x 32 columns that it wrote itself, so the column sums need no barrier among the warps.
     float* wbase = p.wpart ? p.wpart + ((((long long)b * p.G + g) * (4 * p.nQT) + 4 * qt + quarter) * p.L) : nullptr;
     if (n_active == 0 && wbase) {
-      for (int jj = lane; jj < p.L; jj += 32) wbase[jj] = 0.f;
+      for (int jj = 32 * hh + lane; jj < p.L; jj += 64) wbase[jj] = 0.f;
     }
     const uint32_t NEG_INF_BITS = 0xff800000u;
 
     // ---- Q: shared memory -> registers -> TMEM (row = lane; feature pair f/2 = column)
     if (ok) ok = mbar_wait_bounded(q_full, 0, abort_flag, p.status, STATUS_TIMEOUT_FULL);
     if (ok) {
-#pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {
-        const uint8_t* src = smem + AttSmem::Q + ch * (ATT_Q_BYTES / 2);
+      {
+        const uint8_t* src = smem + AttSmem::Q + hh * (ATT_Q_BYTES / 2);  // this warp moves feature chunk hh
         uint32_t w[32];
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
           const uint4 q4 = *reinterpret_cast<const uint4*>(src + sw128_offset(row, u));
           w[4 * u] = q4.x; w[4 * u + 1] = q4.y; w[4 * u + 2] = q4.z; w[4 * u + 3] = q4.w;
         }
-        tmem_st_32x32b_x16(tmem_Q + lane_base + (uint32_t)(32 * ch), w);
-        tmem_st_32x32b_x16(tmem_Q + lane_base + (uint32_t)(32 * ch + 16), w + 16);
+        tmem_st_32x32b_x16(tmem_Q + lane_base + (uint32_t)(32 * hh), w);
+        tmem_st_32x32b_x16(tmem_Q + lane_base + (uint32_t)(32 * hh + 16), w + 16);
       }
       tmem_st_wait();
       tc_fence_before();
@@ -438,24 +443,24 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (lane == 0) mbar_arrive(q_ready);
     }
 
-    // ---- sweep 1: exact row max and sum
+    // ---- sweep 1: exact row max and sum over this thread's 32 columns of every tile
+    constexpr int NC = ATT_BN / 2;  // columns per thread
     for (int t = 0; t < p.nT && ok; ++t) {
       const uint32_t tb = tile_bits(t, fw, fwi);
       if (!(tb & 1u)) continue;
       const bool masked = (tb & 2u) != 0;
-      int v0 = pf0, v1 = pf1;
-      if (masked && pf_t != t) fetch_tp(t, v0, v1);
+      int v0 = pf0;
+      if (masked && pf_t != t) fetch_tp(t, v0);
       if (t + 1 < p.nT) {
-        fetch_tp(t + 1, pf0, pf1);
+        fetch_tp(t + 1, pf0);
         pf_t = t + 1;
       }
       ATT_TRACE(2, 3000000 + i);
       if (!mbar_wait_bounded(s_full, i & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       ATT_TRACE(2, 3100000 + i);
       tc_fence_after();
-      uint32_t r[ATT_BN];
-      tmem_ld_32x32b_x32(tmem_S + lane_base, r);
-      tmem_ld_32x32b_x32(tmem_S + lane_base + 32u, r + 32);
+      uint32_t r[NC];
+      tmem_ld_32x32b_x32(tmem_S + lane_base + (uint32_t)(NC * hh), r);
       tmem_ld_wait();
       ATT_TRACE(2, 3200000 + i);
       // the tile is in registers: hand the S buffer back before the arithmetic
@@ -464,18 +469,15 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (lane == 0) mbar_arrive(s_empty);
       ++i;
       if (masked) {
-        uint32_t mlo, mhi;
-        row_mask(v0, v1, mlo, mhi);
+        const uint32_t mlo = row_mask(v0);
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
+        for (int e = 0; e < NC; ++e)
           if (mlo & (1u << e)) r[e] = NEG_INF_BITS;
-          if (mhi & (1u << e)) r[32 + e] = NEG_INF_BITS;
-        }
       }
       // max of the raw scores (the scale is positive): four independent chains of 3-input max
       float a0 = -INFINITY, a1 = -INFINITY, a2 = -INFINITY, a3 = -INFINITY;
 #pragma unroll
-      for (int e = 0; e < ATT_BN; e += 8) {
+      for (int e = 0; e < NC; e += 8) {
         a0 = fmax3(a0, __uint_as_float(r[e]), __uint_as_float(r[e + 1]));
         a1 = fmax3(a1, __uint_as_float(r[e + 2]), __uint_as_float(r[e + 3]));
         a2 = fmax3(a2, __uint_as_float(r[e + 4]), __uint_as_float(r[e + 5]));
@@ -485,7 +487,7 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const float2 neg_m2 = make_float2(-m_new, -m_new);
       float2 s0 = make_float2(0.f, 0.f), s1 = s0, s2 = s0, s3 = s0;
 #pragma unroll
-      for (int e = 0; e < ATT_BN; e += 8) {
+      for (int e = 0; e < NC; e += 8) {
         float2 x0 = ffma2(make_float2(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), c2, neg_m2);
         float2 x1 = ffma2(make_float2(__uint_as_float(r[e + 2]), __uint_as_float(r[e + 3])), c2, neg_m2);
         float2 x2 = ffma2(make_float2(__uint_as_float(r[e + 4]), __uint_as_float(r[e + 5])), c2, neg_m2);
@@ -500,6 +502,17 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       m = m_new;
       ATT_TRACE(2, 3300000 + i);
     }
+    // merge (m, l) of the two column halves of a row through the P area, which is idle in sweep 1
+    float2* ml_x = reinterpret_cast<float2*>(smem + AttSmem::P);
+    ml_x[hh * ATT_BM + row] = make_float2(m, l);
+    if (ok && !group_sync()) ok = false;
+    if (ok) {
+      const float2 o = ml_x[(hh ^ 1) * ATT_BM + row];
+      const float mm = fmaxf(m, o.x);
+      l = l * fast_exp2(m - mm) + o.y * fast_exp2(o.x - mm);
+      m = mm;
+      if (!group_sync()) ok = false;  // everyone has read the exchange area before P tiles land in it
+    }
     const float lse2 = l > 0.f ? m + log2f(l) : INFINITY;
     // rows beyond the end of the query get P = 0 (their Q rows are zero-filled, so S = 0)
     const float nl = row_valid ? -lse2 : -INFINITY;
@@ -508,29 +521,25 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // ---- sweep 2: P = exp2(S·c − lse), O += P V, column sums of P
     uint8_t* Ps = smem + AttSmem::P;
     for (int t = 0; t < p.nT && ok; ++t) {
-      float* wdst = wbase ? wbase + (long long)t * ATT_BN : nullptr;
+      float* wdst = wbase ? wbase + (long long)t * ATT_BN + NC * hh : nullptr;
       const uint32_t tb = tile_bits(t, fw, fwi);
       if (!(tb & 1u)) {
-        if (wdst) {
-          if (t * ATT_BN + 2 * lane < p.L) wdst[2 * lane] = 0.f;
-          if (t * ATT_BN + 2 * lane + 1 < p.L) wdst[2 * lane + 1] = 0.f;
-        }
+        if (wdst && t * ATT_BN + NC * hh + lane < p.L) wdst[lane] = 0.f;
         continue;
       }
       const bool masked = (tb & 2u) != 0;
-      int v0 = pf0, v1 = pf1;
-      if (masked && pf_t != t) fetch_tp(t, v0, v1);
+      int v0 = pf0;
+      if (masked && pf_t != t) fetch_tp(t, v0);
       if (t + 1 < p.nT) {
-        fetch_tp(t + 1, pf0, pf1);
+        fetch_tp(t + 1, pf0);
         pf_t = t + 1;
       }
       ATT_TRACE(2, 4000000 + i);
       if (!mbar_wait_bounded(s_full, i & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       ATT_TRACE(2, 4100000 + i);
       tc_fence_after();
-      uint32_t r[ATT_BN];
-      tmem_ld_32x32b_x32(tmem_S + lane_base, r);
-      tmem_ld_32x32b_x32(tmem_S + lane_base + 32u, r + 32);
+      uint32_t r[NC];
+      tmem_ld_32x32b_x32(tmem_S + lane_base + (uint32_t)(NC * hh), r);
       tmem_ld_wait();
       ATT_TRACE(2, 4200000 + i);
       tc_fence_before();
@@ -538,17 +547,14 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (lane == 0) mbar_arrive(s_empty);
       ++i;
       if (masked) {
-        uint32_t mlo, mhi;
-        row_mask(v0, v1, mlo, mhi);
+        const uint32_t mlo = row_mask(v0);
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
+        for (int e = 0; e < NC; ++e)
           if (mlo & (1u << e)) r[e] = NEG_INF_BITS;
-          if (mhi & (1u << e)) r[32 + e] = NEG_INF_BITS;
-        }
       }
-      uint32_t pk[ATT_BN / 2];
+      uint32_t pk[NC / 2];
 #pragma unroll
-      for (int e = 0; e < ATT_BN; e += 2) {
+      for (int e = 0; e < NC; e += 2) {
         const float2 x = ffma2(make_float2(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), c2, neg_lse2);
         pk[e >> 1] = pack_bf16x2(fast_exp2(x.x), fast_exp2(x.y));
       }
@@ -557,30 +563,37 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (!mbar_wait_bounded(p_empty, (j & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_MISC)) { ok = false; break; }
       ATT_TRACE(2, 4400000 + i);
 #pragma unroll
-      for (int u = 0; u < ATT_BN / 8; ++u) {
+      for (int u = 0; u < NC / 8; ++u) {
         uint4 val = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
-        *reinterpret_cast<uint4*>(Ps + sw128_offset(row, u)) = val;
+        *reinterpret_cast<uint4*>(Ps + sw128_offset(row, 4 * hh + u)) = val;
       }
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
       ATT_TRACE(2, 4500000 + i);
       ++j;
-      // column sums over this warp's 32 rows of the P tile (as rounded to bf16)
+      // column sums over this warp's 32 rows x 32 columns of the P tile (as rounded to bf16):
+      // lane -> (column pair lane & 15, half of the rows lane >> 4)
       if (wdst) {
         float2 ca = make_float2(0.f, 0.f), cb = ca;
-        const uint32_t coff = (uint32_t)((lane & 3) * 4);
-        const int cu = lane >> 2;
+        const int cp = lane & 15, rh = lane >> 4;
+        const uint32_t coff = (uint32_t)((cp & 3) * 4);
+        const int cu = 4 * hh + (cp >> 2);
 #pragma unroll
-        for (int rr = 0; rr < 32; rr += 2) {
-          const uint32_t w0 = *reinterpret_cast<const uint32_t*>(Ps + sw128_offset(quarter * 32 + rr, cu) + coff);
-          const uint32_t w1 = *reinterpret_cast<const uint32_t*>(Ps + sw128_offset(quarter * 32 + rr + 1, cu) + coff);
+        for (int rr = 0; rr < 16; rr += 2) {
+          const int r0 = quarter * 32 + rh * 16 + rr;
+          const uint32_t w0 = *reinterpret_cast<const uint32_t*>(Ps + sw128_offset(r0, cu) + coff);
+          const uint32_t w1 = *reinterpret_cast<const uint32_t*>(Ps + sw128_offset(r0 + 1, cu) + coff);
           ca = fadd2(ca, make_float2(__uint_as_float(w0 << 16), __uint_as_float(w0 & 0xffff0000u)));
           cb = fadd2(cb, make_float2(__uint_as_float(w1 << 16), __uint_as_float(w1 & 0xffff0000u)));
         }
         ca = fadd2(ca, cb);
-        if (t * ATT_BN + 2 * lane < p.L) wdst[2 * lane] = ca.x;
-        if (t * ATT_BN + 2 * lane + 1 < p.L) wdst[2 * lane + 1] = ca.y;
+        ca.x += __shfl_xor_sync(0xffffffffu, ca.x, 16);
+        ca.y += __shfl_xor_sync(0xffffffffu, ca.y, 16);
+        if (rh == 0) {
+          if (t * ATT_BN + NC * hh + 2 * cp < p.L) wdst[2 * cp] = ca.x;
+          if (t * ATT_BN + NC * hh + 2 * cp + 1 < p.L) wdst[2 * cp + 1] = ca.y;
+        }
         __syncwarp();  // all lanes have read the warp's rows before the next tile overwrites them
       }
       ATT_TRACE(2, 4600000 + i);
@@ -592,7 +605,7 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_after();
       __nv_bfloat16* dst = p.out + (((long long)b * p.T + tq) * p.H + (g * p.gs + hq)) * ATT_D;
 #pragma unroll 1
-      for (int c0 = 0; c0 < ATT_D; c0 += 32) {
+      for (int c0 = 64 * hh; c0 < 64 * hh + 64; c0 += 32) {
         uint32_t r[32];
         if (n_active > 0) {
           tmem_ld_32x32b_x32(tmem_O + lane_base + (uint32_t)c0, r);
@@ -613,7 +626,7 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           }
         }
       }
-      if (row_valid && p.lse) p.lse[((long long)b * p.H + (g * p.gs + hq)) * p.T + tq] = lse2 * 0.6931471805599453f;
+      if (hh == 0 && row_valid && p.lse) p.lse[((long long)b * p.H + (g * p.gs + hq)) * p.T + tq] = lse2 * 0.6931471805599453f;
     }
   }
   tc_fence_before();
