@@ -172,10 +172,13 @@ class CausalSelfAttention(nn.Module):
             if len(bounds) == 1:
                 y = self.kv_cache(query=q, key=k, value=v, token_idx=token_idx)
             else:
-                parts = [
-                    self.kv_cache(query=q[:, :, s:e], key=k[:, :, s:e], value=v[:, :, s:e], token_idx=token_idx[:, s:e])
-                    for s, e in bounds
-                ]
+                # torch.split, not slices: the backward of a split is ONE concatenation of the chunk
+                # gradients, whereas every slice would allocate, zero and accumulate a gradient of
+                # the size of the whole cell
+                sizes = [e - s for s, e in bounds]
+                qs, ks, vs = (torch.split(t, sizes, dim=2) for t in (q, k, v))
+                tis = torch.split(token_idx, sizes, dim=1)
+                parts = [self.kv_cache(query=qc, key=kc, value=vc, token_idx=ti) for qc, kc, vc, ti in zip(qs, ks, vs, tis)]
                 y = torch.cat(parts, dim=1)
         return self.proj(y)
 
