@@ -22,6 +22,13 @@ enum {
 };
 
 // ---- elementwise.cu
+// Gradient replay steps (csrc/quant.cu): bf16 caches, head size 128
+int kvb_replay_write(void* k_buf, void* v_buf, int32_t* token_pos, const int32_t* slots, const void* key, const void* value,
+                     void* old_k, void* old_v, int32_t* old_tp, int B, int G, int n, int D, int C, long long slot_sb,
+                     long long slot_sg, long long kv_sb, long long kv_sg, long long kv_sn, int input_pos, int* status, void* stream);
+int kvb_replay_undo(void* k_buf, void* v_buf, int32_t* token_pos, float* dk_buf, float* dv_buf, const int32_t* slots,
+                    const void* old_k, const void* old_v, const int32_t* old_tp, void* dk_new, void* dv_new, int B, int G, int n,
+                    int D, int C, long long slot_sb, long long slot_sg, int* status, void* stream);
 // Token cross-entropy (csrc/ce_loss.cu)
 int kvb_ce_loss_fwd(const void* logits, const long long* targets, float* loss, float* lse, long long rows, int V, long long ld,
                     long long ignore_index, int dtype, void* stream);

@@ -168,6 +168,78 @@ cache_write128_kernel(__nv_bfloat16* __restrict__ k_buf, __nv_bfloat16* __restri
   if (qv) quantize_row128(vx, bits, qv + dst_row * Dq, sv + dst_row, zv + dst_row, lane);
 }
 
+// ---- gradient replay: one kernel per direction instead of a dozen gathers / scatters / casts.
+// Forward of a replay step: save what the slots held (K, V rows and token positions), then write
+// the chunk's rows. bf16, rows of 128 values, one warp per new row (b, g, i).
+__global__ void __launch_bounds__(Q_WARPS * 32)
+replay_write128_kernel(__nv_bfloat16* __restrict__ k_buf, __nv_bfloat16* __restrict__ v_buf, int32_t* __restrict__ token_pos,
+                       const int32_t* __restrict__ slots, const __nv_bfloat16* __restrict__ key,
+                       const __nv_bfloat16* __restrict__ value, __nv_bfloat16* __restrict__ old_k, __nv_bfloat16* __restrict__ old_v,
+                       int32_t* __restrict__ old_tp, int B, int G, int n, int C, long long slot_sb, long long slot_sg,
+                       long long kv_sb, long long kv_sg, long long kv_sn, int input_pos, int* status) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long row = (long long)blockIdx.x * Q_WARPS + warp;
+  if (row >= (long long)B * G * n) return;
+  const int i = (int)(row % n);
+  const int g = (int)((row / n) % G);
+  const int b = (int)(row / ((long long)n * G));
+  const int slot = slots[b * slot_sb + g * slot_sg + i];
+  if (slot < 0 || slot >= C) {  // never touch memory out of bounds: record and skip
+    if (lane == 0 && status) atomicCAS(status, 0, STATUS_BAD_INDEX);
+    return;
+  }
+  const long long dst_row = ((long long)b * G + g) * C + slot;
+  const long long src = b * kv_sb + g * kv_sg + i * kv_sn + 4 * lane;
+  const uint2 kn = *reinterpret_cast<const uint2*>(key + src), vn = *reinterpret_cast<const uint2*>(value + src);
+  uint2* kd = reinterpret_cast<uint2*>(k_buf + dst_row * 128 + 4 * lane);
+  uint2* vd = reinterpret_cast<uint2*>(v_buf + dst_row * 128 + 4 * lane);
+  *reinterpret_cast<uint2*>(old_k + row * 128 + 4 * lane) = *kd;
+  *reinterpret_cast<uint2*>(old_v + row * 128 + 4 * lane) = *vd;
+  *kd = kn;
+  *vd = vn;
+  if (lane == 0) {
+    old_tp[row] = token_pos[dst_row];
+    token_pos[dst_row] = input_pos + i;
+  }
+}
+
+// Backward of a replay step: the gradients of the chunk's K, V rows are what has accumulated in
+// their slots (taken out as bf16, the slots are cleared), and the slots get their old content back.
+__global__ void __launch_bounds__(Q_WARPS * 32)
+replay_undo128_kernel(__nv_bfloat16* __restrict__ k_buf, __nv_bfloat16* __restrict__ v_buf, int32_t* __restrict__ token_pos,
+                      float* __restrict__ dk_buf, float* __restrict__ dv_buf, const int32_t* __restrict__ slots,
+                      const __nv_bfloat16* __restrict__ old_k, const __nv_bfloat16* __restrict__ old_v,
+                      const int32_t* __restrict__ old_tp, __nv_bfloat16* __restrict__ dk_new, __nv_bfloat16* __restrict__ dv_new,
+                      int B, int G, int n, int C, long long slot_sb, long long slot_sg, int* status) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long row = (long long)blockIdx.x * Q_WARPS + warp;
+  if (row >= (long long)B * G * n) return;
+  const int i = (int)(row % n);
+  const int g = (int)((row / n) % G);
+  const int b = (int)(row / ((long long)n * G));
+  const int slot = slots[b * slot_sb + g * slot_sg + i];
+  if (slot < 0 || slot >= C) {
+    if (lane == 0 && status) atomicCAS(status, 0, STATUS_BAD_INDEX);
+    return;
+  }
+  const long long dst_row = ((long long)b * G + g) * C + slot;
+  float4* dkp = reinterpret_cast<float4*>(dk_buf + dst_row * 128 + 4 * lane);
+  float4* dvp = reinterpret_cast<float4*>(dv_buf + dst_row * 128 + 4 * lane);
+  const float4 a = *dkp, c = *dvp;
+  __nv_bfloat162 a0 = __floats2bfloat162_rn(a.x, a.y), a1 = __floats2bfloat162_rn(a.z, a.w);
+  __nv_bfloat162 c0 = __floats2bfloat162_rn(c.x, c.y), c1 = __floats2bfloat162_rn(c.z, c.w);
+  uint2 ao, co;
+  ao.x = *reinterpret_cast<uint32_t*>(&a0); ao.y = *reinterpret_cast<uint32_t*>(&a1);
+  co.x = *reinterpret_cast<uint32_t*>(&c0); co.y = *reinterpret_cast<uint32_t*>(&c1);
+  *reinterpret_cast<uint2*>(dk_new + row * 128 + 4 * lane) = ao;
+  *reinterpret_cast<uint2*>(dv_new + row * 128 + 4 * lane) = co;
+  *dkp = make_float4(0.f, 0.f, 0.f, 0.f);
+  *dvp = make_float4(0.f, 0.f, 0.f, 0.f);
+  *reinterpret_cast<uint2*>(k_buf + dst_row * 128 + 4 * lane) = *reinterpret_cast<const uint2*>(old_k + row * 128 + 4 * lane);
+  *reinterpret_cast<uint2*>(v_buf + dst_row * 128 + 4 * lane) = *reinterpret_cast<const uint2*>(old_v + row * 128 + 4 * lane);
+  if (lane == 0) token_pos[dst_row] = old_tp[row];
+}
+
 template <typename T>
 __global__ void quantize_rows_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scale,
                                      int32_t* __restrict__ zp, long long rows, int D, int bits) {
@@ -318,5 +390,35 @@ extern "C" int kvb_cache_write(void* k_buf, void* v_buf, int32_t* token_pos, con
   KVB_DISPATCH_DTYPE(dtype, (cache_write_kernel<T><<<grid, Q_WARPS * 32, (size_t)Q_WARPS * D * 4, (cudaStream_t)stream>>>(
                                 (T*)k_buf, (T*)v_buf, token_pos, slots, (const T*)key, (const T*)value, qk, sk, zk, qv, sv, zv, B,
                                 G, n, D, C, slot_sb, slot_sg, input_pos, bits ? bits : 8, status)));
+  return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
+}
+
+// Replay step forward / backward for bf16 caches with head size 128 (see the kernels). key / value
+// may be strided views (strides in elements; the last axis has unit stride); old_* and d*_new are
+// contiguous (B,G,n,128) / (B,G,n). Slots of one (b, g) must be distinct.
+extern "C" int kvb_replay_write(void* k_buf, void* v_buf, int32_t* token_pos, const int32_t* slots, const void* key,
+                                const void* value, void* old_k, void* old_v, int32_t* old_tp, int B, int G, int n, int D, int C,
+                                long long slot_sb, long long slot_sg, long long kv_sb, long long kv_sg, long long kv_sn,
+                                int input_pos, int* status, void* stream) {
+  if (B <= 0 || G <= 0 || n <= 0 || C <= 0) return KVB_ERR_ARG;
+  if (D != 128 || ((kv_sb | kv_sg | kv_sn) & 3)) return KVB_ERR_UNSUPPORTED;
+  const long long rows = (long long)B * G * n;
+  const unsigned grid = (unsigned)((rows + Q_WARPS - 1) / Q_WARPS);
+  replay_write128_kernel<<<grid, Q_WARPS * 32, 0, (cudaStream_t)stream>>>(
+      (__nv_bfloat16*)k_buf, (__nv_bfloat16*)v_buf, token_pos, slots, (const __nv_bfloat16*)key, (const __nv_bfloat16*)value,
+      (__nv_bfloat16*)old_k, (__nv_bfloat16*)old_v, old_tp, B, G, n, C, slot_sb, slot_sg, kv_sb, kv_sg, kv_sn, input_pos, status);
+  return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
+}
+
+extern "C" int kvb_replay_undo(void* k_buf, void* v_buf, int32_t* token_pos, float* dk_buf, float* dv_buf, const int32_t* slots,
+                               const void* old_k, const void* old_v, const int32_t* old_tp, void* dk_new, void* dv_new, int B,
+                               int G, int n, int D, int C, long long slot_sb, long long slot_sg, int* status, void* stream) {
+  if (B <= 0 || G <= 0 || n <= 0 || C <= 0) return KVB_ERR_ARG;
+  if (D != 128) return KVB_ERR_UNSUPPORTED;
+  const long long rows = (long long)B * G * n;
+  const unsigned grid = (unsigned)((rows + Q_WARPS - 1) / Q_WARPS);
+  replay_undo128_kernel<<<grid, Q_WARPS * 32, 0, (cudaStream_t)stream>>>(
+      (__nv_bfloat16*)k_buf, (__nv_bfloat16*)v_buf, token_pos, dk_buf, dv_buf, slots, (const __nv_bfloat16*)old_k,
+      (const __nv_bfloat16*)old_v, old_tp, (__nv_bfloat16*)dk_new, (__nv_bfloat16*)dv_new, B, G, n, C, slot_sb, slot_sg, status);
   return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
 }

@@ -32,6 +32,7 @@ from typing import Any, Dict, List, Optional
 import torch
 
 from keys_values_b200 import ops
+from keys_values_b200.ops import cuda as _cu
 from keys_values_b200.kvcache.base import KVCacheReplayLog
 
 
@@ -83,14 +84,21 @@ class CacheWriteSDPA(torch.autograd.Function):
     @staticmethod
     def forward(ctx, query, key, value, token, state: ReplayState, slots, new_length: int, scale: float, sliding_window, softcap, saved=None):
         B, G, n, D = key.shape
-        idx = slots.to(torch.int64)
-        idx4 = idx.unsqueeze(-1).expand(-1, -1, -1, D)
-        old_k = state.k_buf.gather(2, idx4)
-        old_v = state.v_buf.gather(2, idx4)
-        old_tp = state.token_pos.gather(2, idx)
         old_length = state.current_length
         input_pos = state.input_pos
-        ops.cache_write(state.k_buf, state.v_buf, state.token_pos, slots, key, value, input_pos)
+        fused = (state.k_buf.is_cuda and state.dk_buf.is_contiguous() and state.token_pos.is_contiguous()
+                 and _cu.replay_supported(state.k_buf, key) and state.k_buf.shape[0] == B)
+        if fused:
+            # save the old content of the slots and write the chunk: one kernel
+            idx = slots if slots.dtype == torch.int32 else slots.to(torch.int32)
+            old_k, old_v, old_tp = _cu.replay_write(state.k_buf, state.v_buf, state.token_pos, idx, key, value, input_pos)
+        else:
+            idx = slots.to(torch.int64)
+            idx4 = idx.unsqueeze(-1).expand(-1, -1, -1, D)
+            old_k = state.k_buf.gather(2, idx4)
+            old_v = state.v_buf.gather(2, idx4)
+            old_tp = state.token_pos.gather(2, idx)
+            ops.cache_write(state.k_buf, state.v_buf, state.token_pos, slots, key, value, input_pos)
         state.current_length = new_length
         state.input_pos = input_pos + n
         L = new_length
@@ -106,6 +114,7 @@ class CacheWriteSDPA(torch.autograd.Function):
         ctx.save_for_backward(query, out, lse, idx, old_k, old_v, old_tp)
         ctx.state = state
         ctx.meta = (input_pos, old_length, new_length, scale, sliding_window, softcap, key.dtype)
+        ctx.fused = fused
         return out, token.clone()
 
     @staticmethod
@@ -116,19 +125,24 @@ class CacheWriteSDPA(torch.autograd.Function):
         if state.current_length != L or state.input_pos != input_pos + idx.shape[2]:
             raise RuntimeError("replay steps are being differentiated out of order")
         D = old_k.shape[-1]
-        idx4 = idx.unsqueeze(-1).expand(-1, -1, -1, D)
         dq, _, _ = ops.sdpa_bwd(
             grad_out.contiguous(), query, state.k_buf[:, :, :L], state.v_buf[:, :, :L], out, lse, scale, input_pos,
             state.token_pos[:, :, :L], sliding_window, softcap, dk_accum=state.dk_buf, dv_accum=state.dv_buf,
         )
-        dk_new = state.dk_buf.gather(2, idx4)
-        dv_new = state.dv_buf.gather(2, idx4)
-        state.dk_buf.scatter_(2, idx4, 0.0)
-        state.dv_buf.scatter_(2, idx4, 0.0)
-        # undo the write
-        state.k_buf.scatter_(2, idx4, old_k)
-        state.v_buf.scatter_(2, idx4, old_v)
-        state.token_pos.scatter_(2, idx, old_tp)
+        if ctx.fused:
+            # gradients of the chunk's rows out of the accumulators, slots cleared and restored: one kernel
+            dk_new, dv_new = _cu.replay_undo(state.k_buf, state.v_buf, state.token_pos, state.dk_buf, state.dv_buf, idx,
+                                                  old_k, old_v, old_tp)
+        else:
+            idx4 = idx.unsqueeze(-1).expand(-1, -1, -1, D)
+            dk_new = state.dk_buf.gather(2, idx4)
+            dv_new = state.dv_buf.gather(2, idx4)
+            state.dk_buf.scatter_(2, idx4, 0.0)
+            state.dv_buf.scatter_(2, idx4, 0.0)
+            # undo the write
+            state.k_buf.scatter_(2, idx4, old_k)
+            state.v_buf.scatter_(2, idx4, old_v)
+            state.token_pos.scatter_(2, idx, old_tp)
         state.current_length = old_length
         state.input_pos = input_pos
         return dq.to(query.dtype), dk_new.to(kv_dtype), dv_new.to(kv_dtype), grad_token, None, None, None, None, None, None, None

@@ -328,6 +328,52 @@ def cache_write_quant(k_buf, v_buf, token_pos, slots, key, value, input_pos, qk,
     _cache_write(k_buf, v_buf, token_pos, slots, key, value, input_pos, qk, sk, zk, qv, sv, zv, bits)
 
 
+# ----------------------------------------------------------- gradient replay
+def replay_supported(k_buf: torch.Tensor, key: torch.Tensor) -> bool:
+    return (k_buf.is_cuda and k_buf.dtype == torch.bfloat16 and key.dtype == torch.bfloat16 and k_buf.shape[-1] == 128
+            and k_buf.is_contiguous() and key.stride(-1) == 1 and all(st % 4 == 0 for st in key.stride()[:3]))
+
+
+def replay_write(k_buf, v_buf, token_pos, slots, key, value, input_pos: int):
+    """Saves what ``slots`` hold (returns ``old_k, old_v (B,G,n,D)``, ``old_tp (B,G,n)``), then writes
+    ``key / value`` and the token positions ``input_pos + i`` there: one kernel."""
+    B, G, n, D = key.shape
+    C = k_buf.shape[2]
+    if value.stride() != key.stride():
+        value = value.contiguous()
+        key = key.contiguous()
+    slots = slots if slots.dtype == torch.int32 else slots.to(torch.int32)
+    if slots.stride(2) != 1:
+        slots = slots.contiguous()
+    old_k = torch.empty((B, G, n, D), dtype=k_buf.dtype, device=k_buf.device)
+    old_v = torch.empty_like(old_k)
+    old_tp = torch.empty((B, G, n), dtype=torch.int32, device=k_buf.device)
+    st = status_word(k_buf.device)
+    _check(lib().kvb_replay_write(_p(k_buf), _p(v_buf), _p(token_pos), _p(slots), _p(key), _p(value), _p(old_k), _p(old_v), _p(old_tp),
+                                  B, G, n, D, C, _ll(slots.stride(0)), _ll(slots.stride(1)), _ll(key.stride(0)), _ll(key.stride(1)),
+                                  _ll(key.stride(2)), int(input_pos), _p(st), _stream(key)), "replay_write")
+    _count()
+    return old_k, old_v, old_tp
+
+
+def replay_undo(k_buf, v_buf, token_pos, dk_buf, dv_buf, slots, old_k, old_v, old_tp):
+    """Takes the accumulated gradients of the chunk's rows out of ``dk_buf / dv_buf`` (returned as
+    bf16 ``(B,G,n,D)``, the slots are cleared) and restores the old content of the slots: one kernel."""
+    B, G, n, D = old_k.shape
+    C = k_buf.shape[2]
+    slots = slots if slots.dtype == torch.int32 else slots.to(torch.int32)
+    if slots.stride(2) != 1:
+        slots = slots.contiguous()
+    dk_new = torch.empty((B, G, n, D), dtype=k_buf.dtype, device=k_buf.device)
+    dv_new = torch.empty_like(dk_new)
+    st = status_word(k_buf.device)
+    _check(lib().kvb_replay_undo(_p(k_buf), _p(v_buf), _p(token_pos), _p(dk_buf), _p(dv_buf), _p(slots), _p(old_k), _p(old_v),
+                                 _p(old_tp), _p(dk_new), _p(dv_new), B, G, n, D, C, _ll(slots.stride(0)), _ll(slots.stride(1)),
+                                 _p(st), _stream(old_k)), "replay_undo")
+    _count()
+    return dk_new, dv_new
+
+
 # ---------------------------------------------------------------------- H2O
 def h2o_update(scores, weights, k_select, n_evictable, normalize=False, token_pos=None, input_pos=0, prefill_length=0):
     B, G, C = scores.shape

@@ -1,0 +1,60 @@
+"""End-to-end gradients of the chunked, cache-based training pass on the GPU (tcgen05 attention
+forward / backward, fused replay steps, fused norms) against whole-sequence autograd."""
+import pytest
+import torch
+
+from keys_values_b200.kvcache.factory import KVCacheFactory
+from keys_values_b200.kvcache.gradient.main import LongContextGradientModel, NaiveGPTAndHeadModel
+from keys_values_b200.models import lora as lora_mod
+from keys_values_b200.models.head_model import CrossEntropyOnLogits
+
+pytestmark = pytest.mark.gpu
+
+
+def _model(dev, dtype):
+    torch.manual_seed(0)
+    cfg = lora_mod.Config.from_name("tiny-qwen3", lora_r=4, lora_alpha=8, lora_query=True, lora_key=True, lora_value=True,
+                                    lora_projection=True)
+    m = lora_mod.GPT(cfg)
+    m.apply(m._init_weights)
+    for n, p in m.named_parameters():
+        if "lora_B" in n:
+            torch.nn.init.normal_(p, std=0.05)
+    lora_mod.mark_only_lora_as_trainable(m)
+    return cfg, m.to(device=dev, dtype=dtype)
+
+
+def _grads(m):
+    g = {n: p.grad.float().clone() for n, p in m.named_parameters() if p.grad is not None}
+    m.zero_grad()
+    return g
+
+
+@pytest.mark.parametrize("cache_name,save_attn", [("h2o-default", True), ("h2o-default", False), ("h2o-torch-quantized8", True)])
+def test_chunked_gradients_match_whole_sequence_autograd(cache_name, save_attn, monkeypatch):
+    dev, dtype = torch.device("cuda", 0), torch.bfloat16
+    cfg, m = _model(dev, dtype)
+    head = CrossEntropyOnLogits(cfg)
+    T, C, cs = 640, 768, 128  # the cache holds the whole sequence: nothing is evicted, so both passes see the same attention
+    ids = torch.randint(0, cfg.vocab_size, (1, T), device=dev)
+    tg = torch.randint(0, cfg.vocab_size, (1, 96), device=dev)
+    m.assign_kv_caches(KVCacheFactory.create(m, cache_name, 1, C, dtype=dtype, device=dev, cache_kwargs=dict(max_chunk_size=cs)))
+    # prefill 256 tokens, then chunks of 128 that are written into free slots
+    import keys_values_b200.long_context as lc
+
+    monkeypatch.setattr(lc, "create_chunk_sizes", lambda *a, **k: [256, 128, 128, 128])
+    gm = LongContextGradientModel(m, head, layers_per_cell=1, chunk_size=cs, save_attention_outputs=save_attn)
+    gm.train()
+    loss = gm(ids, tg)
+    loss.backward()
+    g1 = _grads(m)
+    m.clear_kv_caches() if hasattr(m, "clear_kv_caches") else None
+    l2 = NaiveGPTAndHeadModel(m, head)(ids, tg)
+    l2.backward()
+    g2 = _grads(m)
+    quant = "quantized" in cache_name
+    assert abs(float(loss.value) - float(l2.detach())) < (0.05 if quant else 0.02)
+    assert g1.keys() == g2.keys() and len(g1) > 0
+    num = sum(((g1[k] - g2[k]) ** 2).sum() for k in g1) ** 0.5
+    den = sum((g2[k] ** 2).sum() for k in g1) ** 0.5
+    assert float(num / den) < (0.12 if quant else 0.05), float(num / den)
