@@ -546,17 +546,20 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
           tmem_ld_32x32b_x32(tmem_A2 + lane_base + (uint32_t)c0, r2v);
           tmem_ld_wait();
           if (row_valid) {
-            float4* dvp = reinterpret_cast<float4*>(p.dv + off + c0);
-            float4* dkp = reinterpret_cast<float4*>(p.dk + off + c0);
+            // accumulate with vector reductions: no load -> add -> store chain in the epilogue. Every
+            // address is touched by this CTA only, so the result does not depend on any order.
+            float* dvp = p.dv + off + c0;
+            float* dkp = p.dk + off + c0;
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
-              float4 a = dvp[u], c = dkp[u];
-              a.x += __uint_as_float(r1v[4 * u]); a.y += __uint_as_float(r1v[4 * u + 1]);
-              a.z += __uint_as_float(r1v[4 * u + 2]); a.w += __uint_as_float(r1v[4 * u + 3]);
-              c.x += __uint_as_float(r2v[4 * u]); c.y += __uint_as_float(r2v[4 * u + 1]);
-              c.z += __uint_as_float(r2v[4 * u + 2]); c.w += __uint_as_float(r2v[4 * u + 3]);
-              dvp[u] = a;
-              dkp[u] = c;
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dvp + 4 * u), "f"(__uint_as_float(r1v[4 * u])),
+                           "f"(__uint_as_float(r1v[4 * u + 1])), "f"(__uint_as_float(r1v[4 * u + 2])),
+                           "f"(__uint_as_float(r1v[4 * u + 3]))
+                           : "memory");
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dkp + 4 * u), "f"(__uint_as_float(r2v[4 * u])),
+                           "f"(__uint_as_float(r2v[4 * u + 1])), "f"(__uint_as_float(r2v[4 * u + 2])),
+                           "f"(__uint_as_float(r2v[4 * u + 3]))
+                           : "memory");
             }
           }
         }
