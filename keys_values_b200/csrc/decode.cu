@@ -29,6 +29,7 @@ constexpr int DEC_D = 128;
 constexpr int DEC_SPLIT = 256;    // slots per CTA
 constexpr int DEC_THREADS = 128;  // 4 warps
 constexpr int DEC_MAX_GS = 16;
+constexpr int DEC_BATCH = 4;     // groups of four slots whose loads are issued together
 constexpr int DEC_HB = 8;         // heads of a group handled by one CTA (more heads: more CTAs along z)
 
 struct DecParams {
@@ -67,12 +68,26 @@ __device__ __forceinline__ float dec_u8_to_f32(uint32_t w, int idx) {
   return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7440u | (uint32_t)idx)) - 8388608.f;
 }
 
-// 16 elements of row `row` for feature lane fl, as floats (codes are not de-quantized here).
+// Raw 16 elements of row `row` for feature lane fl (32 bytes of bf16, 16 of int8, 8 of int4).
 template <int BITS>
-__device__ __forceinline__ void dec_load_frag(const void* base, long long row, int fl, float* x) {
+__device__ __forceinline__ void dec_load_raw(const void* base, long long row, int fl, uint4& a, uint4& c) {
   if (BITS == 16) {
     const uint4* p = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(base) + row * DEC_D);
-    const uint4 a = __ldg(p + fl), c = __ldg(p + fl + 8);
+    a = __ldg(p + fl);
+    c = __ldg(p + fl + 8);
+  } else if (BITS == 8) {
+    a = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(base) + row * DEC_D) + fl);
+  } else {
+    const uint2 v = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(base) + row * (DEC_D / 2)) + fl);
+    a.x = v.x;
+    a.y = v.y;
+  }
+}
+
+// ... as floats (codes are not de-quantized here).
+template <int BITS>
+__device__ __forceinline__ void dec_convert(const uint4& a, const uint4& c, float* x) {
+  if (BITS == 16) {
     const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&a);
     const __nv_bfloat162* hc = reinterpret_cast<const __nv_bfloat162*>(&c);
 #pragma unroll
@@ -82,13 +97,11 @@ __device__ __forceinline__ void dec_load_frag(const void* base, long long row, i
       x[8 + 2 * j] = g.x; x[8 + 2 * j + 1] = g.y;
     }
   } else if (BITS == 8) {
-    const uint4 v = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(base) + row * DEC_D) + fl);
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
     for (int j = 0; j < 16; ++j) x[j] = dec_u8_to_f32(w[j >> 2], j & 3);
   } else {
-    const uint2 v = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(base) + row * (DEC_D / 2)) + fl);
-    const uint32_t w[2] = {v.x, v.y};
+    const uint32_t w[2] = {a.x, a.y};
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const uint32_t byte = (w[j >> 2] >> (8 * (j & 3))) & 0xFFu;
@@ -140,40 +153,51 @@ decode_partial_kernel(const DecParams p) {
   float lmax[GS];
 #pragma unroll
   for (int h = 0; h < GS; ++h) lmax[h] = -FLT_MAX;
-#pragma unroll 4
-  for (int jb = warp * 4; jb < n; jb += DEC_THREADS / 8) {  // warp-uniform trip count (shuffles inside)
-    const int jj = jb + sub;
-    const bool valid = jj < n;
-    const int j = j0 + (valid ? jj : 0);
-    // the cache row is loaded unconditionally (no branch between the loads of the unrolled
-    // iterations); the row of the token being decoded is then replaced by its exact values
-    float x[16];
-    float kscale = 1.f, kzp = 0.f;
-    dec_load_frag<BITS>(p.kq, row0 + j, fl, x);
-    if (BITS != 16) {
-      kscale = __ldg(p.ks + row0 + j);
-      kzp = (float)__ldg(p.kz + row0 + j);
-    }
-    if (j == ns) {
-      const __nv_bfloat16* kr = p.k_new + ((long long)b * p.G + g) * DEC_D;
+  // DEC_BATCH groups of four slots per iteration: all their loads are issued before the first
+  // conversion, so that 8 x 16 bytes (bf16) are in flight per lane
+  for (int jb0 = warp * 4; jb0 < n; jb0 += DEC_BATCH * (DEC_THREADS / 8)) {  // warp-uniform trip count (shuffles inside)
+    uint4 ra[DEC_BATCH], rc[DEC_BATCH];
+    float ksc[DEC_BATCH], kz[DEC_BATCH];
 #pragma unroll
-      for (int k = 0; k < 16; ++k) x[k] = __bfloat162float(kr[dec_feature<BITS>(fl, k)]);
-      kscale = 1.f;
-      kzp = 0.f;
+    for (int q = 0; q < DEC_BATCH; ++q) {
+      const int jj = min(jb0 + q * (DEC_THREADS / 8) + sub, n - 1);  // rows beyond the split re-read its last row
+      dec_load_raw<BITS>(p.kq, row0 + j0 + jj, fl, ra[q], rc[q]);
+      ksc[q] = 1.f;
+      kz[q] = 0.f;
+      if (BITS != 16) {
+        ksc[q] = __ldg(p.ks + row0 + j0 + jj);
+        kz[q] = (float)__ldg(p.kz + row0 + j0 + jj);
+      }
     }
 #pragma unroll
-    for (int h = 0; h < GS; ++h) {
-      float acc = 0.f;
+    for (int q = 0; q < DEC_BATCH; ++q) {
+      const int jj = jb0 + q * (DEC_THREADS / 8) + sub;
+      const bool valid = jj < n;
+      const int j = j0 + jj;
+      float x[16];
+      dec_convert<BITS>(ra[q], rc[q], x);
+      float kscale = ksc[q], kzp = kz[q];
+      if (valid && j == ns) {  // the token being decoded: exact values instead of the cache row
+        const __nv_bfloat16* kr = p.k_new + ((long long)b * p.G + g) * DEC_D;
 #pragma unroll
-      for (int k = 0; k < 16; ++k) acc = fmaf(qf[h][k], x[k], acc);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-      const float sv = p.scale * kscale * (acc - kzp * qsum[h]);
-      if (valid) lmax[h] = fmaxf(lmax[h], sv);
-      if (fl == 0 && valid) {
-        sc[h][jj] = sv;
-        p.logits[(head0 + h) * p.L + j] = sv;
+        for (int k = 0; k < 16; ++k) x[k] = __bfloat162float(kr[dec_feature<BITS>(fl, k)]);
+        kscale = 1.f;
+        kzp = 0.f;
+      }
+#pragma unroll
+      for (int h = 0; h < GS; ++h) {
+        float acc = 0.f;
+#pragma unroll
+        for (int k = 0; k < 16; ++k) acc = fmaf(qf[h][k], x[k], acc);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+        const float sv = p.scale * kscale * (acc - kzp * qsum[h]);
+        if (valid) lmax[h] = fmaxf(lmax[h], sv);
+        if (fl == 0 && valid) {
+          sc[h][jj] = sv;
+          p.logits[(head0 + h) * p.L + j] = sv;
+        }
       }
     }
   }
@@ -236,23 +260,30 @@ decode_partial_kernel(const DecParams p) {
   for (int h = 0; h < GS; ++h)
 #pragma unroll
     for (int k = 0; k < 16; ++k) acc[h][k] = 0.f;
-#pragma unroll 4
-  for (int jb = warp * 4; jb < n; jb += DEC_THREADS / 8) {
-    const int jj = min(jb + sub, n - 1);
-    const bool valid = jb + sub < n;
-    const int j = j0 + jj;
-    float x[16];
-    dec_load_frag<BITS>(p.vq, row0 + j, fl, x);
-    if (j == ns) {
-      const __nv_bfloat16* vr = p.v_new + ((long long)b * p.G + g) * DEC_D;
+  for (int jb0 = warp * 4; jb0 < n; jb0 += DEC_BATCH * (DEC_THREADS / 8)) {
+    uint4 ra[DEC_BATCH], rc[DEC_BATCH];
 #pragma unroll
-      for (int k = 0; k < 16; ++k) x[k] = __bfloat162float(vr[dec_feature<BITS>(fl, k)]);
+    for (int q = 0; q < DEC_BATCH; ++q) {
+      const int jj = min(jb0 + q * (DEC_THREADS / 8) + sub, n - 1);
+      dec_load_raw<BITS>(p.vq, row0 + j0 + jj, fl, ra[q], rc[q]);
     }
 #pragma unroll
-    for (int h = 0; h < GS; ++h) {
-      const float ps = valid ? sc[h][jj] : 0.f;
+    for (int q = 0; q < DEC_BATCH; ++q) {
+      const int jj = jb0 + q * (DEC_THREADS / 8) + sub;
+      const bool valid = jj < n;
+      float x[16];
+      dec_convert<BITS>(ra[q], rc[q], x);
+      if (valid && j0 + jj == ns) {
+        const __nv_bfloat16* vr = p.v_new + ((long long)b * p.G + g) * DEC_D;
 #pragma unroll
-      for (int k = 0; k < 16; ++k) acc[h][k] = fmaf(ps, x[k], acc[h][k]);
+        for (int k = 0; k < 16; ++k) x[k] = __bfloat162float(vr[dec_feature<BITS>(fl, k)]);
+      }
+#pragma unroll
+      for (int h = 0; h < GS; ++h) {
+        const float ps = valid ? sc[h][jj] : 0.f;
+#pragma unroll
+        for (int k = 0; k < 16; ++k) acc[h][k] = fmaf(ps, x[k], acc[h][k]);
+      }
     }
   }
   // reduce over the four slot lanes of the warp, then over the warps
