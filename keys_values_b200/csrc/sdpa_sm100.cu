@@ -29,9 +29,10 @@
 //     the CTA take the mask-free path. In a masked tile only the columns whose token lies
 //     beyond the first query need a per-row comparison; their positions travel by warp
 //     shuffle and end up as a 64-bit mask per row, without shared memory or block barriers.
-//   * warp 0 = TMA producer, warp 1 = MMA issuer / TMEM owner, warps 2..9 = softmax + epilogue:
-//     two warps per TMEM lane quarter, each thread owns one query row (its TMEM lane) and 32 of
-//     the 64 columns of every tile.
+//   * warp 0 = TMA producer, warp 1 = MMA issuer / TMEM owner, then the softmax + epilogue warps.
+//     Two instantiations: 4 softmax warps (a thread owns a query row = its TMEM lane and all 64
+//     columns of a tile; used for plain causal attention) and 8 softmax warps (two per TMEM lane
+//     quarter, 32 columns per thread; used over an evicting cache, where most tiles need masks).
 //
 // Replaces FlashInfer prefill + Triton score-sum + K/V reordering + query padding of the
 // reference (keys_values/attention/flashinfer_wrapper.py:51-273, :367-510,
@@ -50,7 +51,11 @@ int make_tmap_2d_bf16(CUtensorMap* tm, const void* ptr, uint64_t rows, uint64_t 
 constexpr int ATT_BM = 128;   // query rows per CTA
 constexpr int ATT_BN = 64;    // KV slots per tile
 constexpr int ATT_D = 128;    // head size
-constexpr int ATT_THREADS = 320;  // TMA warp + MMA warp + 8 softmax warps; two CTAs per SM
+// TMA warp + MMA warp + SW softmax warps; two CTAs per SM. SW = 4: a thread owns one query row and all
+// 64 columns of a tile (best when few tiles need masks: prefill, plain causal attention); SW = 8: two
+// warps per TMEM lane quarter, 32 columns per thread (best when most tiles hold tokens of the current
+// chunk, as in training over an evicting cache, where building the masks dominates the chain).
+constexpr int att_threads(int sw) { return 64 + 32 * sw; }
 constexpr int ATT_Q_BYTES = ATT_BM * ATT_D * 2;    // 32 KB: two 64-feature chunks of [128 rows x 128 B]
 constexpr int ATT_KV_BYTES = ATT_BN * ATT_D * 2;   // 16 KB: two 64-feature chunks of [64 rows x 128 B]
 constexpr int ATT_P_BYTES = ATT_BM * ATT_BN * 2;   // 16 KB: one 64-column chunk of [128 rows x 128 B]
@@ -148,7 +153,8 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-__global__ void __launch_bounds__(ATT_THREADS, 2)
+template <int SW>
+__global__ void __launch_bounds__(att_threads(SW), 2)
 sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const AttParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -188,7 +194,7 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   // memory inside its tile loop
   uint32_t* tflags = reinterpret_cast<uint32_t*>(smem + AttSmem::TF);
   constexpr int TF_TILES = 1024;
-  for (int w = threadIdx.x; w < TF_TILES / 16; w += ATT_THREADS) {
+  for (int w = threadIdx.x; w < TF_TILES / 16; w += att_threads(SW)) {
     uint32_t bits = 0;
 #pragma unroll 4
     for (int i = 0; i < 16; ++i) {
@@ -219,12 +225,12 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(&v_empty[s], 1);
     }
     mbar_init(s_full, 1);
-    mbar_init(s_empty, 8);
-    mbar_init(p_full, 8);
+    mbar_init(s_empty, SW);
+    mbar_init(p_full, SW);
     mbar_init(p_empty, 1);
     mbar_init(o_full, 1);
-    mbar_init(q_ready, 8);
-    mbar_init(grp_bar, 256);
+    mbar_init(q_ready, SW);
+    mbar_init(grp_bar, 32 * SW);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -372,7 +378,9 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // TMEM load, exp2, P store, column sums) is half as long per warp and four warps per SM
     // sub-partition (two CTAs) fill each other's latencies.
     const int quarter = warp & 3;
-    const int hh = (warp - 2) >> 2;
+    const int hh = SW == 8 ? (warp - 2) >> 2 : 0;
+    constexpr int NC = SW == 8 ? ATT_BN / 2 : ATT_BN;  // columns per thread
+    constexpr int NW = NC / 32;                       // 32-column words per thread
     const int row = quarter * 32 + lane;          // TMEM lane = query row of the tile
     const int hq = row / p.npos;                  // head within the group
     const int pl = row % p.npos;                  // position within the tile
@@ -391,22 +399,31 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // Token positions of a tile: lane holds columns lane and lane + 32 (INT_MAX beyond the cache).
     // The positions of the next tile are fetched one tile ahead.
     const int32_t* tpp = p.token_pos ? p.token_pos + b * p.tp_sb + g * p.tp_sg : nullptr;
-    auto fetch_tp = [&](int t, int& v0) {  // lane holds column 32·hh + lane of the tile
-      const int j0 = t * ATT_BN + 32 * hh + lane;
-      v0 = j0 < p.L ? (tpp ? tpp[j0] : j0) : INT_MAX;
-    };
-    int pf0 = INT_MAX, pf_t = -1;
-    // Mask bits of this thread's row for a masked tile (bit e of mlo / mhi: column e / 32 + e is
-    // hidden). Only columns whose token lies beyond the first query of the CTA need the per-row
-    // comparison; their positions are broadcast by shuffle, so no shared memory is involved.
-    auto row_mask = [&](int v0) -> uint32_t {
-      uint32_t n0 = __ballot_sync(0xffffffffu, v0 > qpos_min), mlo = 0;
-      while (n0) {
-        const int e = __ffs(n0) - 1;
-        n0 &= n0 - 1;
-        mlo |= (uint32_t)(__shfl_sync(0xffffffffu, v0, e) > my_pos) << e;
+    // lane holds columns NC·hh + 32·w + lane (w < NW) of the tile
+    auto fetch_tp = [&](int t, int (&v)[NW]) {
+#pragma unroll
+      for (int w = 0; w < NW; ++w) {
+        const int j0 = t * ATT_BN + NC * hh + 32 * w + lane;
+        v[w] = j0 < p.L ? (tpp ? tpp[j0] : j0) : INT_MAX;
       }
-      return mlo;
+    };
+    int pf[NW], pf_t = -1;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) pf[w] = INT_MAX;
+    // Mask bits of this thread's row for a masked tile (bit e of word w: column 32·w + e of the thread's
+    // columns is hidden). Only columns whose token lies beyond the first query of the CTA need the
+    // per-row comparison; their positions are broadcast by shuffle, so no shared memory is involved.
+    auto row_mask = [&](const int (&v)[NW], uint32_t (&mk)[NW]) {
+#pragma unroll
+      for (int w = 0; w < NW; ++w) {
+        uint32_t n0 = __ballot_sync(0xffffffffu, v[w] > qpos_min);
+        mk[w] = 0;
+        while (n0) {
+          const int e = __ffs(n0) - 1;
+          n0 &= n0 - 1;
+          mk[w] |= (uint32_t)(__shfl_sync(0xffffffffu, v[w], e) > my_pos) << e;
+        }
+      }
     };
     uint32_t grp_phase = 0;
     auto group_sync = [&]() -> bool {  // all 256 softmax threads; false if it ran into the wait limit
@@ -419,23 +436,25 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // rows x 32 columns that it wrote itself, so the column sums need no barrier among the warps.
     float* wbase = p.wpart ? p.wpart + ((((long long)b * p.G + g) * (4 * p.nQT) + 4 * qt + quarter) * p.L) : nullptr;
     if (n_active == 0 && wbase) {
-      for (int jj = 32 * hh + lane; jj < p.L; jj += 64) wbase[jj] = 0.f;
+      for (int jj = NC * hh + lane; jj < p.L; jj += 32)
+        if ((jj % ATT_BN) / NC == hh) wbase[jj] = 0.f;
     }
     const uint32_t NEG_INF_BITS = 0xff800000u;
 
     // ---- Q: shared memory -> registers -> TMEM (row = lane; feature pair f/2 = column)
     if (ok) ok = mbar_wait_bounded(q_full, 0, abort_flag, p.status, STATUS_TIMEOUT_FULL);
     if (ok) {
-      {
-        const uint8_t* src = smem + AttSmem::Q + hh * (ATT_Q_BYTES / 2);  // this warp moves feature chunk hh
+#pragma unroll
+      for (int ch = (SW == 8 ? hh : 0); ch < (SW == 8 ? hh + 1 : 2); ++ch) {  // feature chunk(s) that this warp moves
+        const uint8_t* src = smem + AttSmem::Q + ch * (ATT_Q_BYTES / 2);
         uint32_t w[32];
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
           const uint4 q4 = *reinterpret_cast<const uint4*>(src + sw128_offset(row, u));
           w[4 * u] = q4.x; w[4 * u + 1] = q4.y; w[4 * u + 2] = q4.z; w[4 * u + 3] = q4.w;
         }
-        tmem_st_32x32b_x16(tmem_Q + lane_base + (uint32_t)(32 * hh), w);
-        tmem_st_32x32b_x16(tmem_Q + lane_base + (uint32_t)(32 * hh + 16), w + 16);
+        tmem_st_32x32b_x16(tmem_Q + lane_base + (uint32_t)(32 * ch), w);
+        tmem_st_32x32b_x16(tmem_Q + lane_base + (uint32_t)(32 * ch + 16), w + 16);
       }
       tmem_st_wait();
       tc_fence_before();
@@ -444,15 +463,16 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
 
     // ---- sweep 1: exact row max and sum over this thread's 32 columns of every tile
-    constexpr int NC = ATT_BN / 2;  // columns per thread
     for (int t = 0; t < p.nT && ok; ++t) {
       const uint32_t tb = tile_bits(t, fw, fwi);
       if (!(tb & 1u)) continue;
       const bool masked = (tb & 2u) != 0;
-      int v0 = pf0;
+      int v0[NW];
+#pragma unroll
+      for (int w = 0; w < NW; ++w) v0[w] = pf[w];
       if (masked && pf_t != t) fetch_tp(t, v0);
       if (t + 1 < p.nT) {
-        fetch_tp(t + 1, pf0);
+        fetch_tp(t + 1, pf);
         pf_t = t + 1;
       }
       ATT_TRACE(2, 3000000 + i);
@@ -460,7 +480,8 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       ATT_TRACE(2, 3100000 + i);
       tc_fence_after();
       uint32_t r[NC];
-      tmem_ld_32x32b_x32(tmem_S + lane_base + (uint32_t)(NC * hh), r);
+#pragma unroll
+      for (int w = 0; w < NW; ++w) tmem_ld_32x32b_x32(tmem_S + lane_base + (uint32_t)(NC * hh + 32 * w), r + 32 * w);
       tmem_ld_wait();
       ATT_TRACE(2, 3200000 + i);
       // the tile is in registers: hand the S buffer back before the arithmetic
@@ -469,10 +490,11 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (lane == 0) mbar_arrive(s_empty);
       ++i;
       if (masked) {
-        const uint32_t mlo = row_mask(v0);
+        uint32_t mk[NW];
+        row_mask(v0, mk);
 #pragma unroll
         for (int e = 0; e < NC; ++e)
-          if (mlo & (1u << e)) r[e] = NEG_INF_BITS;
+          if (mk[e >> 5] & (1u << (e & 31))) r[e] = NEG_INF_BITS;
       }
       // max of the raw scores (the scale is positive): four independent chains of 3-input max
       float a0 = -INFINITY, a1 = -INFINITY, a2 = -INFINITY, a3 = -INFINITY;
@@ -502,16 +524,18 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       m = m_new;
       ATT_TRACE(2, 3300000 + i);
     }
-    // merge (m, l) of the two column halves of a row through the P area, which is idle in sweep 1
-    float2* ml_x = reinterpret_cast<float2*>(smem + AttSmem::P);
-    ml_x[hh * ATT_BM + row] = make_float2(m, l);
-    if (ok && !group_sync()) ok = false;
-    if (ok) {
-      const float2 o = ml_x[(hh ^ 1) * ATT_BM + row];
-      const float mm = fmaxf(m, o.x);
-      l = l * fast_exp2(m - mm) + o.y * fast_exp2(o.x - mm);
-      m = mm;
-      if (!group_sync()) ok = false;  // everyone has read the exchange area before P tiles land in it
+    if (SW == 8) {
+      // merge (m, l) of the two column halves of a row through the P area, which is idle in sweep 1
+      float2* ml_x = reinterpret_cast<float2*>(smem + AttSmem::P);
+      ml_x[hh * ATT_BM + row] = make_float2(m, l);
+      if (ok && !group_sync()) ok = false;
+      if (ok) {
+        const float2 o = ml_x[(hh ^ 1) * ATT_BM + row];
+        const float mm = fmaxf(m, o.x);
+        l = l * fast_exp2(m - mm) + o.y * fast_exp2(o.x - mm);
+        m = mm;
+        if (!group_sync()) ok = false;  // everyone has read the exchange area before P tiles land in it
+      }
     }
     const float lse2 = l > 0.f ? m + log2f(l) : INFINITY;
     // rows beyond the end of the query get P = 0 (their Q rows are zero-filled, so S = 0)
@@ -524,14 +548,20 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       float* wdst = wbase ? wbase + (long long)t * ATT_BN + NC * hh : nullptr;
       const uint32_t tb = tile_bits(t, fw, fwi);
       if (!(tb & 1u)) {
-        if (wdst && t * ATT_BN + NC * hh + lane < p.L) wdst[lane] = 0.f;
+        if (wdst) {
+#pragma unroll
+          for (int w = 0; w < NW; ++w)
+            if (t * ATT_BN + NC * hh + 32 * w + lane < p.L) wdst[32 * w + lane] = 0.f;
+        }
         continue;
       }
       const bool masked = (tb & 2u) != 0;
-      int v0 = pf0;
+      int v0[NW];
+#pragma unroll
+      for (int w = 0; w < NW; ++w) v0[w] = pf[w];
       if (masked && pf_t != t) fetch_tp(t, v0);
       if (t + 1 < p.nT) {
-        fetch_tp(t + 1, pf0);
+        fetch_tp(t + 1, pf);
         pf_t = t + 1;
       }
       ATT_TRACE(2, 4000000 + i);
@@ -539,7 +569,8 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       ATT_TRACE(2, 4100000 + i);
       tc_fence_after();
       uint32_t r[NC];
-      tmem_ld_32x32b_x32(tmem_S + lane_base + (uint32_t)(NC * hh), r);
+#pragma unroll
+      for (int w = 0; w < NW; ++w) tmem_ld_32x32b_x32(tmem_S + lane_base + (uint32_t)(NC * hh + 32 * w), r + 32 * w);
       tmem_ld_wait();
       ATT_TRACE(2, 4200000 + i);
       tc_fence_before();
@@ -547,10 +578,11 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (lane == 0) mbar_arrive(s_empty);
       ++i;
       if (masked) {
-        const uint32_t mlo = row_mask(v0);
+        uint32_t mk[NW];
+        row_mask(v0, mk);
 #pragma unroll
         for (int e = 0; e < NC; ++e)
-          if (mlo & (1u << e)) r[e] = NEG_INF_BITS;
+          if (mk[e >> 5] & (1u << (e & 31))) r[e] = NEG_INF_BITS;
       }
       uint32_t pk[NC / 2];
 #pragma unroll
@@ -565,31 +597,35 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
       for (int u = 0; u < NC / 8; ++u) {
         uint4 val = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
-        *reinterpret_cast<uint4*>(Ps + sw128_offset(row, 4 * hh + u)) = val;
+        *reinterpret_cast<uint4*>(Ps + sw128_offset(row, (NC / 8) * hh + u)) = val;
       }
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
       ATT_TRACE(2, 4500000 + i);
       ++j;
-      // column sums over this warp's 32 rows x 32 columns of the P tile (as rounded to bf16):
-      // lane -> (column pair lane & 15, half of the rows lane >> 4)
+      // column sums over this warp's 32 rows x NC columns of the P tile (as rounded to bf16):
+      // lane -> (column pair lane % (NC/2), part of the rows lane / (NC/2))
       if (wdst) {
+        constexpr int NP = NC / 2;       // column pairs of this warp
+        constexpr int RPL = 32 / (32 / NP);  // rows per lane
         float2 ca = make_float2(0.f, 0.f), cb = ca;
-        const int cp = lane & 15, rh = lane >> 4;
+        const int cp = lane % NP, rh = lane / NP;
         const uint32_t coff = (uint32_t)((cp & 3) * 4);
-        const int cu = 4 * hh + (cp >> 2);
+        const int cu = (NC / 8) * hh + (cp >> 2);
 #pragma unroll
-        for (int rr = 0; rr < 16; rr += 2) {
-          const int r0 = quarter * 32 + rh * 16 + rr;
+        for (int rr = 0; rr < RPL; rr += 2) {
+          const int r0 = quarter * 32 + rh * RPL + rr;
           const uint32_t w0 = *reinterpret_cast<const uint32_t*>(Ps + sw128_offset(r0, cu) + coff);
           const uint32_t w1 = *reinterpret_cast<const uint32_t*>(Ps + sw128_offset(r0 + 1, cu) + coff);
           ca = fadd2(ca, make_float2(__uint_as_float(w0 << 16), __uint_as_float(w0 & 0xffff0000u)));
           cb = fadd2(cb, make_float2(__uint_as_float(w1 << 16), __uint_as_float(w1 & 0xffff0000u)));
         }
         ca = fadd2(ca, cb);
-        ca.x += __shfl_xor_sync(0xffffffffu, ca.x, 16);
-        ca.y += __shfl_xor_sync(0xffffffffu, ca.y, 16);
+        if (NP < 32) {
+          ca.x += __shfl_xor_sync(0xffffffffu, ca.x, 16);
+          ca.y += __shfl_xor_sync(0xffffffffu, ca.y, 16);
+        }
         if (rh == 0) {
           if (t * ATT_BN + NC * hh + 2 * cp < p.L) wdst[2 * cp] = ca.x;
           if (t * ATT_BN + NC * hh + 2 * cp + 1 < p.L) wdst[2 * cp + 1] = ca.y;
@@ -605,7 +641,7 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_after();
       __nv_bfloat16* dst = p.out + (((long long)b * p.T + tq) * p.H + (g * p.gs + hq)) * ATT_D;
 #pragma unroll 1
-      for (int c0 = 64 * hh; c0 < 64 * hh + 64; c0 += 32) {
+      for (int c0 = (ATT_D / (SW / 4)) * hh; c0 < (ATT_D / (SW / 4)) * (hh + 1); c0 += 32) {
         uint32_t r[32];
         if (n_active > 0) {
           tmem_ld_32x32b_x32(tmem_O + lane_base + (uint32_t)c0, r);
@@ -739,10 +775,14 @@ extern "C" int kvb_sdpa_fwd(const void* q, const void* k, const void* v, const i
   att_tile_minmax_kernel<<<B * G * p.nT, ATT_BN, 0, s>>>(token_pos, tmin, tmax, G, kv_len, p.nT, tp_sb, tp_sg);
   static bool attr_set = false;
   if (!attr_set) {
-    cudaFuncSetAttribute(sdpa_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AttSmem::TOTAL);
+    cudaFuncSetAttribute(sdpa_fwd_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttSmem::TOTAL);
+    cudaFuncSetAttribute(sdpa_fwd_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttSmem::TOTAL);
     attr_set = true;
   }
-  sdpa_fwd_kernel<<<B * G * p.nQT, ATT_THREADS, AttSmem::TOTAL, s>>>(tmQ, tmK, tmV, p);
+  // explicit token positions = an evicting cache: most tiles hold tokens of the current chunk and need
+  // masks, which the 8-warp variant builds faster; plain causal attention runs best with 4 softmax warps
+  if (token_pos) sdpa_fwd_kernel<8><<<B * G * p.nQT, att_threads(8), AttSmem::TOTAL, s>>>(tmQ, tmK, tmV, p);
+  else sdpa_fwd_kernel<4><<<B * G * p.nQT, att_threads(4), AttSmem::TOTAL, s>>>(tmQ, tmK, tmV, p);
   if (weights) {
     dim3 grid((kv_len + 255) / 256, B * G);
     att_reduce_weights_kernel<<<grid, 256, 0, s>>>(p.wpart, weights, 4 * p.nQT, kv_len, 1.f / gs);
