@@ -1,7 +1,7 @@
 """Kernel micro-benchmarks: CUDA-event timing after warm-up, with an L2 flush
 (a write larger than the 126 MB L2) between timed iterations.
 
-    python -m keys_values_b200.tools.microbench sdpa|sdpa_bwd|gemm|elementwise|all [--out file.jsonl]
+    python -m keys_values_b200.tools.microbench sdpa|sdpa_train|sdpa_bwd|gemm|elementwise|all [--out file.jsonl]
 
 ``sdpa`` covers the SDPA-with-weights grid: bf16 GQA 32/8 heads, head size 128,
 batch 1 and 4, query length {1, 256, 2048}, KV length {4096, 16384, 32768}.
@@ -106,6 +106,38 @@ def bench_sdpa_bwd(out, peaks):
              "frac_of_measured_peak": flops / ms / 1e9 / peaks["bf16_tflops"]})
 
 
+def bench_sdpa_train(out, peaks):
+    """The attention calls of one (layer, chunk) of the training step: ``q`` new tokens whose K/V sit
+    in random slots of a full cache of ``kv`` slots (an evicting cache), forward with weights and
+    backward."""
+    from keys_values_b200.ops import cuda as cu
+
+    dev = torch.device("cuda")
+    flush = _flush_buf(dev)
+    H, G, D = 32, 8, 128
+    scale = 1 / math.sqrt(D)
+    for B, T, L in ((1, 1024, 16384), (1, 2048, 16384), (4, 1024, 16384)):
+        q = torch.randn(B, H, T, D, device=dev, dtype=torch.bfloat16)
+        k = torch.randn(B, G, L, D, device=dev, dtype=torch.bfloat16)
+        v = torch.randn(B, G, L, D, device=dev, dtype=torch.bfloat16)
+        tp = torch.stack([torch.stack([torch.randperm(L, device=dev) for _ in range(G)]) for _ in range(B)]).to(torch.int32)
+        newslots = torch.randperm(L, device=dev)[:T]
+        tp[:, :, newslots] = (torch.arange(T, device=dev) + 2 * L).to(torch.int32)
+        ip = 2 * L
+        ms_f = time_fn(lambda: cu.sdpa_fwd(q, k, v, scale, ip, tp, True), flush=flush)
+        o, _, lse = cu.sdpa_fwd(q, k, v, scale, ip, tp, False)
+        go = torch.randn_like(o)
+        dk = torch.zeros(B, G, L, D, device=dev)
+        dv = torch.zeros_like(dk)
+        ms_b = time_fn(lambda: cu.sdpa_bwd(go, q, k, v, o, lse, scale, ip, tp, dk, dv), flush=flush)
+        cu.check_status(dev)
+        flops = 4.0 * B * H * T * L * D
+        out({"bench": "sdpa_train_chunk", "B": B, "q": T, "kv": L, "fwd_us": ms_f * 1e3, "bwd_us": ms_b * 1e3,
+             "fwd_tflops": flops / ms_f / 1e9, "bwd_tflops": 2.5 * flops / ms_b / 1e9,
+             "fwd_frac_of_measured_peak": flops / ms_f / 1e9 / peaks["bf16_tflops"],
+             "bwd_frac_of_measured_peak": 2.5 * flops / ms_b / 1e9 / peaks["bf16_tflops"]})
+
+
 def bench_gemm(out, peaks):
     from keys_values_b200.ops import cuda as cu
 
@@ -180,6 +212,8 @@ def main():
         bench_gemm(out, peaks)
     if args.which in ("sdpa", "all"):
         bench_sdpa(out, peaks)
+    if args.which in ("sdpa_train", "all"):
+        bench_sdpa_train(out, peaks)
     if args.which in ("sdpa_bwd", "all"):
         bench_sdpa_bwd(out, peaks)
     if args.which in ("elementwise", "all"):
