@@ -129,6 +129,70 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const long long total = (long long)ex.rows_per_chunk * vec_per_row;
       const __nv_bfloat16* sp = ex.ag_src[src];
       __nv_bfloat16* dp = ex.ag_stage + (long long)src * ex.rows_per_chunk * ex.ag_ld;
+      if (ex.ag_ld == (long long)K) {
+        // Contiguous shard: the TMA engine moves it, peer memory -> shared memory -> local staging, in
+        // pieces of AG_PIECE bytes through a ring of AG_RING pieces, driven by one thread. A CTA keeps
+        // AG_RING x AG_PIECE bytes in flight, so a few copy CTAs saturate the link and the rest of the
+        // SMs stay with the product.
+        constexpr uint32_t AG_PIECE = 16384;
+        constexpr int AG_RING = 12;
+        extern __shared__ uint8_t ag_smem_raw[];
+        uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(ag_smem_raw) + 1023) & ~uintptr_t(1023));
+        uint64_t* rbar = reinterpret_cast<uint64_t*>(ring + (size_t)AG_RING * AG_PIECE);
+        __shared__ int ag_abort;
+        if (threadIdx.x == 0) {
+          const long long bytes = total * 16;
+          const long long n_piece = (bytes + AG_PIECE - 1) / AG_PIECE;
+          const uint8_t* gs = reinterpret_cast<const uint8_t*>(sp);
+          uint8_t* gd = reinterpret_cast<uint8_t*>(dp);
+          if (qi == 1) {
+            ag_abort = 0;
+            for (int r = 0; r < AG_RING; ++r) mbar_init(&rbar[r], 1);
+            mbar_fence_init();
+          }
+          // pieces blockIdx.x, blockIdx.x + n_copy, ... of this shard
+          const long long first = blockIdx.x, step = ex.ag_copy_ctas;
+          const long long mine = first < n_piece ? (n_piece - first + step - 1) / step : 0;
+          auto piece_bytes = [&](long long k) -> uint32_t {
+            const long long off = (first + k * step) * AG_PIECE;
+            return (uint32_t)(bytes - off < AG_PIECE ? bytes - off : AG_PIECE);
+          };
+          auto issue_load = [&](long long k, uint32_t use) {  // `use`: how often this ring slot has been used before
+            const int sl = (int)(k % AG_RING);
+            (void)use;
+            mbar_expect_tx(&rbar[sl], piece_bytes(k));
+            bulk_load(ring + (size_t)sl * AG_PIECE, gs + (first + k * step) * AG_PIECE, piece_bytes(k), &rbar[sl]);
+          };
+          // ring slot sl has been used (qi - 1) * uses_per_shard + ... times: track phases explicitly
+          static_assert(AG_RING <= 32, "phase bits");
+          uint32_t& phases = *reinterpret_cast<uint32_t*>(&rbar[AG_RING]);
+          if (qi == 1) phases = 0;
+          for (long long k = 0; k < mine && k < AG_RING; ++k) issue_load(k, 0);
+          for (long long k = 0; k < mine && ok_s; ++k) {
+            const int sl = (int)(k % AG_RING);
+            if (!mbar_wait_bounded(&rbar[sl], (phases >> sl) & 1u, &ag_abort, status, STATUS_TIMEOUT_FULL, ex.wait_limit)) {
+              ok_s = 0;
+              break;
+            }
+            phases ^= 1u << sl;
+            bulk_store(gd + (first + k * step) * AG_PIECE, ring + (size_t)sl * AG_PIECE, piece_bytes(k));
+            bulk_commit();
+            if (k + AG_RING < mine) {
+              bulk_wait_read_all();  // the slot's store has read it: the slot can take the next piece
+              issue_load(k + AG_RING, 0);
+            }
+          }
+          bulk_wait_all();  // the staged pieces are in local memory
+        }
+        __threadfence();
+        __syncthreads();
+        if (!ok_s) return;
+        if (threadIdx.x == 0) {
+          red_release_gpu_add(ex.ag_flags_w + src, 1u);
+          red_release_sys_add(ex.ag_pulled[src], 1u);
+        }
+        continue;
+      }
       // remote loads take microseconds: keep 16 of them in flight per thread
       constexpr int CU = 16;
       const long long cstride = (long long)ex.ag_copy_ctas * blockDim.x;

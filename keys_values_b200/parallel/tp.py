@@ -93,7 +93,7 @@ class TPContext:
         # CTAs that pull the peers' shards: the remote fraction (world − 1) / world of the activation must
         # arrive while the local fraction is being multiplied, so more ranks need more copy CTAs
         if copy_ctas is None:
-            copy_ctas = min(32, 4 + 4 * world)
+            copy_ctas = min(16, 2 + 2 * world)  # each keeps 192 KB in flight through the TMA engine
         self.timeout_s, self.copy_ctas = timeout_s, copy_ctas
         self.max_rows, self.max_features = max_rows, max_features
         torch.cuda.set_device(self.device)
