@@ -16,7 +16,7 @@ REF_ROOT = Path(__file__).resolve().parent / "_ref"
 
 def _probe() -> str:
     if not (REF_ROOT / "keys_values").is_dir():
-        return "baseline/_ref is missing (pip install --no-index --no-deps --target baseline/_ref /root/reference was not run)"
+        return "baseline/_ref is missing (the offline pip install of the reference with --target baseline/_ref was not run)"
     for mod in ("litgpt", "lightning", "jsonargparse"):
         try:
             importlib.import_module(mod)
