@@ -22,7 +22,7 @@ def _commands() -> Dict[str, Callable]:
     from keys_values_b200.evaluation import longcontext_eval, longcontext_eval_ext
     from keys_values_b200.finetune import longcon_offload_full, longcon_offload_lora, longcontext_full, longcontext_lora
     from keys_values_b200.generate import base as generate_base
-    from keys_values_b200.tools import recompute_val_losses
+    from keys_values_b200.tools import convert_hf_checkpoint, recompute_val_losses
 
     return {
         "finetune_long_full": longcontext_full.setup,
@@ -33,11 +33,12 @@ def _commands() -> Dict[str, Callable]:
         "eval_long_ext": longcontext_eval_ext.setup,
         "recomp_val_losses": recompute_val_losses.setup,
         "generate": generate_base.main,
+        "convert_hf_checkpoint": convert_hf_checkpoint.setup,
     }
 
 
 PARSER_DATA = ("finetune_long_full", "finetune_long_lora", "finetune_offload_full", "finetune_offload_lora", "eval_long", "eval_long_ext",
-               "recomp_val_losses", "generate")
+               "recomp_val_losses", "generate", "convert_hf_checkpoint")
 
 
 class TeeOutput:
