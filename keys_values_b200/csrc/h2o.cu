@@ -26,7 +26,8 @@ __device__ __forceinline__ uint32_t ordered_key(float f) {
 __global__ void __launch_bounds__(H2O_THREADS, 1)
 h2o_update_kernel(float* __restrict__ scores, const float* __restrict__ weights, const int32_t* __restrict__ token_pos,
                   int32_t* __restrict__ out_idx, int G, int C, int n_evict, int k_select, int kpad, int normalize, int input_pos,
-                  int prefill_length, long long sc_sb, long long sc_sg, long long tp_sb, long long tp_sg) {
+                  int prefill_length, long long sc_sb, long long sc_sg, long long tp_sb, long long tp_sg,
+                  const int* __restrict__ pos_ptr) {
   extern __shared__ uint32_t smem_u[];
   uint32_t* keys = smem_u;                       // [n_evict] selection keys
   uint32_t* sort_key = keys + n_evict;           // [kpad]
@@ -37,13 +38,14 @@ h2o_update_kernel(float* __restrict__ scores, const float* __restrict__ weights,
 
   const int b = blockIdx.x / G, g = blockIdx.x % G;
   float* sc = scores + b * sc_sb + g * sc_sg;
-  const float* w = weights + ((long long)b * G + g) * C;
+  const float* w = weights ? weights + ((long long)b * G + g) * C : nullptr;  // null: select only
   const int32_t* tp = token_pos ? token_pos + b * tp_sb + g * tp_sg : nullptr;
   const int tid = threadIdx.x;
+  if (pos_ptr) input_pos = *pos_ptr + 1;  // device-resident position of the token just written; scores are aged to the next one
 
   // 1) accumulate and build selection keys
   for (int j = tid; j < C; j += H2O_THREADS) {
-    const float s = sc[j] + w[j];
+    const float s = sc[j] + (w ? w[j] : 0.f);
     sc[j] = s;
     if (j < n_evict) {
       float sel = s;
@@ -198,6 +200,6 @@ extern "C" int kvb_h2o_update(float* scores, const float* weights, const int32_t
   }
   h2o_update_kernel<<<B * G, H2O_THREADS, smem, (cudaStream_t)stream>>>(scores, weights, token_pos, out_idx, G, C, n_evictable,
                                                                        k_select, kpad, normalize, input_pos, prefill_length,
-                                                                       sc_sb, sc_sg, tp_sb, tp_sg);
+                                                                       sc_sb, sc_sg, tp_sb, tp_sg, kvb_position_source());
   return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
 }

@@ -61,7 +61,12 @@ int kvb_cache_write(void* k_buf, void* v_buf, int32_t* token_pos, const int32_t*
                     uint8_t* qk, float* sk, int32_t* zk, uint8_t* qv, float* sv, int32_t* zv, int B, int G, int n, int D, int C,
                     long long slot_sb, long long slot_sg, int input_pos, int bits, int dtype, int* status, void* stream);
 
-// ---- h2o.cu
+// Device word that overrides the host ``input_pos`` of kvb_cache_write / kvb_h2o_update while set
+// (NULL clears it): lets a captured decode step be replayed at later positions.
+void kvb_set_position_source(const int* device_word);
+const int* kvb_position_source();
+
+// ---- h2o.cu (weights may be NULL: selection only, scores unchanged)
 int kvb_h2o_update(float* scores, const float* weights, const int32_t* token_pos, int32_t* out_idx, int B, int G, int C,
                    int n_evictable, int k_select, int normalize, int input_pos, int prefill_length, long long sc_sb,
                    long long sc_sg, long long tp_sb, long long tp_sg, void* stream);

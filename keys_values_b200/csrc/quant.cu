@@ -143,10 +143,12 @@ cache_write128_kernel(__nv_bfloat16* __restrict__ k_buf, __nv_bfloat16* __restri
                       const int32_t* __restrict__ slots, const __nv_bfloat16* __restrict__ key,
                       const __nv_bfloat16* __restrict__ value, uint8_t* __restrict__ qk, float* __restrict__ sk,
                       int32_t* __restrict__ zk, uint8_t* __restrict__ qv, float* __restrict__ sv, int32_t* __restrict__ zv, int B,
-                      int G, int n, int C, long long slot_sb, long long slot_sg, int input_pos, int bits, int* status) {
+                      int G, int n, int C, long long slot_sb, long long slot_sg, int input_pos, const int* __restrict__ pos_ptr, int bits,
+                      int* status) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long row = (long long)blockIdx.x * Q_WARPS + warp;
   if (row >= (long long)B * G * n) return;
+  if (pos_ptr) input_pos = *pos_ptr;  // position kept on the device (captured decode step)
   const int i = (int)(row % n);
   const int g = (int)((row / n) % G);
   const int b = (int)(row / ((long long)n * G));
@@ -288,12 +290,14 @@ __global__ void cache_write_kernel(T* __restrict__ k_buf, T* __restrict__ v_buf,
                                    const int32_t* __restrict__ slots, const T* __restrict__ key, const T* __restrict__ value,
                                    uint8_t* __restrict__ qk, float* __restrict__ sk, int32_t* __restrict__ zk,
                                    uint8_t* __restrict__ qv, float* __restrict__ sv, int32_t* __restrict__ zv, int B, int G, int n,
-                                   int D, int C, long long slot_sb, long long slot_sg, int input_pos, int bits, int* status) {
+                                   int D, int C, long long slot_sb, long long slot_sg, int input_pos, const int* __restrict__ pos_ptr,
+                                   int bits, int* status) {
   extern __shared__ float sm[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float* xs = sm + warp * D;
   const long long row = (long long)blockIdx.x * Q_WARPS + warp;
   if (row >= (long long)B * G * n) return;
+  if (pos_ptr) input_pos = *pos_ptr;
   const int i = (int)(row % n);
   const int g = (int)((row / n) % G);
   const int b = (int)(row / ((long long)n * G));
@@ -371,6 +375,13 @@ extern "C" int kvb_dequantize_rows(const uint8_t* q, const float* scale, const i
   return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
 }
 
+// While a position source is set, cache writes and the H2O update take the position of the step's
+// first token from that device word instead of their host argument, so that a captured CUDA graph
+// of a decode step can be replayed for later positions. The pointer must stay valid until cleared.
+static const int* g_position_source = nullptr;
+extern "C" void kvb_set_position_source(const int* device_word) { g_position_source = device_word; }
+extern "C" const int* kvb_position_source() { return g_position_source; }
+
 extern "C" int kvb_cache_write(void* k_buf, void* v_buf, int32_t* token_pos, const int32_t* slots, const void* key,
                                const void* value, uint8_t* qk, float* sk, int32_t* zk, uint8_t* qv, float* sv, int32_t* zv, int B,
                                int G, int n, int D, int C, long long slot_sb, long long slot_sg, int input_pos, int bits,
@@ -384,12 +395,12 @@ extern "C" int kvb_cache_write(void* k_buf, void* v_buf, int32_t* token_pos, con
   if (dtype == 1 && D == 128 && al(key, 7) && al(value, 7) && al(k_buf, 7) && al(v_buf, 7) && al(qk, 3) && al(qv, 3)) {
     cache_write128_kernel<<<grid, Q_WARPS * 32, 0, (cudaStream_t)stream>>>(
         (__nv_bfloat16*)k_buf, (__nv_bfloat16*)v_buf, token_pos, slots, (const __nv_bfloat16*)key, (const __nv_bfloat16*)value, qk,
-        sk, zk, qv, sv, zv, B, G, n, C, slot_sb, slot_sg, input_pos, bits ? bits : 8, status);
+        sk, zk, qv, sv, zv, B, G, n, C, slot_sb, slot_sg, input_pos, g_position_source, bits ? bits : 8, status);
     return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
   }
   KVB_DISPATCH_DTYPE(dtype, (cache_write_kernel<T><<<grid, Q_WARPS * 32, (size_t)Q_WARPS * D * 4, (cudaStream_t)stream>>>(
                                 (T*)k_buf, (T*)v_buf, token_pos, slots, (const T*)key, (const T*)value, qk, sk, zk, qv, sv, zv, B,
-                                G, n, D, C, slot_sb, slot_sg, input_pos, bits ? bits : 8, status)));
+                                G, n, D, C, slot_sb, slot_sg, input_pos, g_position_source, bits ? bits : 8, status)));
   return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
 }
 

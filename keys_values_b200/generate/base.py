@@ -58,6 +58,8 @@ def batched_sample(logits_stack: torch.Tensor, kwargs: Union[dict, List[dict]]) 
     if isinstance(kwargs, dict):
         kwargs = [kwargs] * B
     assert len(kwargs) == B
+    if all(kw.get("temperature", 1.0) == 0.0 or kw.get("top_k") == 1 for kw in kwargs):
+        return torch.argmax(logits_stack[:, -1], dim=-1, keepdim=True)  # greedy rows: one reduction for the batch
     return torch.stack([sample(logits_stack[b : b + 1], **kw) for b, kw in enumerate(kwargs)], dim=0)
 
 
@@ -82,9 +84,12 @@ def batched_generate_fn(
     stop_tokens: Tuple[List[int], ...] = (),
     include_prompt: bool = True,
     include_eos: bool = True,
+    use_graph: bool = True,
 ) -> Iterator[List[Optional[torch.Tensor]]]:
     """Yields, step by step, one token (or ``None`` once a row has stopped) per batch row.
-    ``prompts (B, T)`` must have equal lengths (left-padded batches)."""
+    ``prompts (B, T)`` must have equal lengths (left-padded batches). On a GPU the single-token
+    steps are replayed from one CUDA graph as soon as all caches are full
+    (:class:`keys_values_b200.generate.decode_graph.Decoder`); ``use_graph=False`` keeps them eager."""
     if prompts.ndim == 1:
         prompts = prompts.unsqueeze(0)
     B, T = prompts.shape
@@ -96,6 +101,9 @@ def batched_generate_fn(
             yield [prompts[b, t : t + 1] for b in range(B)]
     logits = _prefill(model, prompts, prompt_chunksize, max_returned_tokens)
     tokens = batched_sample(logits, sample_args).view(B, 1).to(torch.int64)
+    from keys_values_b200.generate.decode_graph import Decoder
+
+    decoder = Decoder(model, B, use_graph=use_graph and prompts.is_cuda)
     stop_progress = [[0] * len(stop_tokens) for _ in range(B)]
     stopped = [False] * B
     max_stop = max((len(s) for s in stop_tokens), default=0)
@@ -117,7 +125,7 @@ def batched_generate_fn(
         yield out
         if all(stopped) or step == max_returned_tokens - T - 1:
             break
-        tokens = batched_next_token(model, tokens, sample_args).view(B, 1)
+        tokens = batched_sample(decoder(tokens)[:, -1:], sample_args).to(torch.int64).view(B, 1)
 
 
 @torch.inference_mode()

@@ -105,7 +105,13 @@ class AttnWeightsKVCache(KVCacheWithBuffers):
     def next_positions(self, num: int) -> Optional[torch.Tensor]:
         if self._next_positions is None:
             return None
+        if num > self._next_positions.shape[-1]:
+            # a single-token step selected only a few slots: select again from the unchanged scores
+            self._next_positions = self._reselect(num)
         return self._next_positions[:, :, :num]
+
+    def _reselect(self, num: int) -> torch.Tensor:
+        raise IndexError(f"only {self._next_positions.shape[-1]} next positions are available, {num} needed")
 
     def reset(self) -> None:
         super().reset()

@@ -52,16 +52,38 @@ class H2OKVCache(AttnWeightsKVCache):
     def _plain(self) -> bool:
         return type(self)._instantaneous_score is H2OKVCache._instantaneous_score and type(self)._modify_scores is H2OKVCache._modify_scores
 
+    # slots selected after a single-token step (the next step of a generation needs one; a longer
+    # chunk that follows selects again from the same scores, see ``_reselect``)
+    DECODE_SELECT = 8
+
+    def _fused_select(self, attn_weights: Optional[torch.Tensor], k: int) -> torch.Tensor:
+        """Fused: scores += w (skipped for ``None``), (age-normalise), k smallest among the evictable
+        slots. The result lives in a buffer kept per ``k``, so that a captured decode step and the
+        eager steps before it exchange the slots through one address."""
+        B = self.batch_size
+        key = (B, k)
+        out = self._select_out.get(key) if hasattr(self, "_select_out") else None
+        if out is None or out.device != self.scores.device:
+            if not hasattr(self, "_select_out"):
+                self._select_out = {}
+            out = self._select_out[key] = torch.empty((B, self.n_query_groups, k), dtype=torch.int32, device=self.scores.device)
+        return ops.h2o_update(
+            self.scores[:B], attn_weights, k, self.cache_length - self.grace_period,
+            normalize=self.normalize_scores, token_pos=self.token_pos[:B],
+            input_pos=self.input_pos, prefill_length=self.prefill_length, out=out,
+        )
+
+    def _reselect(self, num: int) -> torch.Tensor:
+        if self._plain() and self.max_chunk_size is not None and self.current_length == self.cache_length:
+            return self._fused_select(None, max(num, self.max_chunk_size))
+        return super()._reselect(num)
+
     def _select_after_accumulate(self, attn_weights: torch.Tensor, num: int) -> None:
         B, L, C = self.batch_size, self.current_length, self.cache_length
         limit = C - self.grace_period
         if L == C and self._plain() and self.max_chunk_size is not None:
-            # Fused: scores += w, (age-normalise), k smallest among the evictable slots
-            self._next_positions = ops.h2o_update(
-                self.scores[:B], attn_weights, self.max_chunk_size, limit,
-                normalize=self.normalize_scores, token_pos=self.token_pos[:B],
-                input_pos=self.input_pos, prefill_length=self.prefill_length,
-            )
+            k = min(self.max_chunk_size, self.DECODE_SELECT) if num == 1 else self.max_chunk_size
+            self._next_positions = self._fused_select(attn_weights, k)
             return
         self.scores[:B, :, :L] += self._instantaneous_score(attn_weights, num)
         if L < C:

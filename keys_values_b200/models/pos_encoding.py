@@ -15,6 +15,12 @@ import torch
 from keys_values_b200.config import Config
 from keys_values_b200.ops import reference as ref
 
+
+def _position_context():
+    from keys_values_b200 import ops
+
+    return ops.position_context()
+
 DEFAULT_YARN_ALPHA = 1.0
 DEFAULT_YARN_BETA = 32.0
 
@@ -155,6 +161,16 @@ class LinearPositionEncoding(PositionEncoding):
             self._device = torch.device(device)
             self._cos = self._cos.to(self._device)
             self._sin = self._sin.to(self._device)
+        ctx = _position_context() if length == 1 else None
+        if ctx is not None:
+            # captured decode step: the row is gathered by the device-resident position, once per step
+            ind = None if self.rope_local_base_freq is None else self.rope_indices[block_idx]
+            key = ("rope", id(self), ind)
+            rows = ctx.cache.get(key)
+            if rows is None:
+                cos, sin = (self._cos, self._sin) if ind is None else (self._cos[:, :, ind], self._sin[:, :, ind])
+                rows = ctx.cache[key] = (cos.index_select(0, ctx.word), sin.index_select(0, ctx.word))
+            return rows
         if self.rope_local_base_freq is None:
             return self._cos[input_pos : input_pos + length], self._sin[input_pos : input_pos + length]
         ind = self.rope_indices[block_idx]

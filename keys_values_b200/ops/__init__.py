@@ -271,10 +271,24 @@ def cache_write_quant(k_buf, v_buf, token_pos, slots, key, value, input_pos: int
         z[:B].scatter_(2, idx, xz)
 
 
-def h2o_update(scores, weights, k_select: int, n_evictable: int, normalize=False, token_pos=None, input_pos=0, prefill_length=0):
+def h2o_update(scores, weights, k_select: int, n_evictable: int, normalize=False, token_pos=None, input_pos=0, prefill_length=0,
+               out=None):
+    """``weights=None`` selects without accumulating; ``out`` (int32 ``(B,G,k_select)``) receives the result."""
     if scores.is_cuda:
-        return _cuda().h2o_update(scores, weights, k_select, n_evictable, normalize, token_pos, input_pos, prefill_length)
-    return ref.h2o_update(scores, weights, k_select, n_evictable, normalize, token_pos, input_pos, prefill_length)
+        return _cuda().h2o_update(scores, weights, k_select, n_evictable, normalize, token_pos, input_pos, prefill_length, out)
+    res = ref.h2o_update(scores, weights, k_select, n_evictable, normalize, token_pos, input_pos, prefill_length)
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
+
+
+def position_context():
+    """The active device-resident position of a captured decode step (``ops.cuda.device_position``), or ``None``."""
+    import sys
+
+    mod = sys.modules.get("keys_values_b200.ops.cuda")
+    return None if mod is None else mod.position_context()
 
 
 class _CrossEntropyFn(torch.autograd.Function):

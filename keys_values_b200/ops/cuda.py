@@ -375,17 +375,27 @@ def replay_undo(k_buf, v_buf, token_pos, dk_buf, dv_buf, slots, old_k, old_v, ol
 
 
 # ---------------------------------------------------------------------- H2O
-def h2o_update(scores, weights, k_select, n_evictable, normalize=False, token_pos=None, input_pos=0, prefill_length=0):
+def h2o_update(scores, weights, k_select, n_evictable, normalize=False, token_pos=None, input_pos=0, prefill_length=0, out=None):
+    """``weights`` may be ``None`` (selection only). ``out (B,G,k_select)`` int32 contiguous receives the
+    result when given, so that a consumer captured in a CUDA graph reads a fixed address."""
     B, G, C = scores.shape
     if k_select > 4096 or (n_evictable * 4 + 8 * 2 ** math.ceil(math.log2(max(k_select, 2)))) > 200 * 1024:
         # cold path: full sort / very large selections stay with the library routine
         from keys_values_b200.ops import reference as ref
 
-        return ref.h2o_update(scores, weights, k_select, n_evictable, normalize, token_pos, input_pos, prefill_length)
-    weights = weights.contiguous()
+        res = ref.h2o_update(scores, weights, k_select, n_evictable, normalize, token_pos, input_pos, prefill_length)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
+    if weights is not None:
+        weights = weights.contiguous()
     if scores.stride(2) != 1:
         raise NativeError("h2o_update: scores must be contiguous along the slot axis")
-    out = torch.empty((B, G, k_select), dtype=torch.int32, device=scores.device)
+    if out is None:
+        out = torch.empty((B, G, k_select), dtype=torch.int32, device=scores.device)
+    elif out.shape != (B, G, k_select) or out.dtype != torch.int32 or not out.is_contiguous():
+        raise NativeError("h2o_update: out must be a contiguous int32 (B, G, k_select) tensor")
     tp = token_pos if normalize else None
     _check(lib().kvb_h2o_update(_p(scores), _p(weights), _p(tp), _p(out), B, G, C, n_evictable, k_select, int(normalize),
                                 int(input_pos), int(prefill_length or 0), _ll(scores.stride(0)), _ll(scores.stride(1)),
@@ -393,6 +403,44 @@ def h2o_update(scores, weights, k_select, n_evictable, normalize=False, token_po
                                 _stream(scores)), "h2o_update")
     _count()
     return out
+
+
+# ------------------------------------------------- device-resident position (captured decode steps)
+_POSITION: Optional["device_position"] = None
+
+
+def position_context() -> Optional["device_position"]:
+    """The active :class:`device_position` (``.word``: the int32 device word; ``.cache``: values derived
+    from it once per step, e.g. the gathered RoPE rows), or ``None``."""
+    return _POSITION
+
+
+class device_position:
+    """While active, cache writes and the H2O update read the position of the step's token from
+    ``word`` (int32, one element, on the GPU) instead of their host argument, and the position
+    encoding gathers its table row by it: a decode step captured in a CUDA graph then serves every
+    later position (the graph increments the word itself)."""
+
+    def __init__(self, word: torch.Tensor):
+        if not (word.is_cuda and word.dtype == torch.int32 and word.numel() == 1):
+            raise NativeError("device_position: need one int32 word on the GPU")
+        self.word = word
+        self.cache: dict = {}
+
+    def __enter__(self):
+        global _POSITION
+        if _POSITION is not None:
+            raise NativeError("device_position: already active")
+        _POSITION = self
+        lib().kvb_set_position_source.restype = None
+        lib().kvb_set_position_source(_p(self.word))
+        return self
+
+    def __exit__(self, *exc):
+        global _POSITION
+        _POSITION = None
+        lib().kvb_set_position_source(None)
+        return False
 
 
 # --------------------------------------------------------------------- GEMM

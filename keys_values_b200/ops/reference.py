@@ -260,7 +260,8 @@ def h2o_update(
     ``k_select`` smallest (optionally age-normalised) scores among the first
     ``n_evictable`` slots, ascending, int32 ``(B,G,k_select)``
     (``keys_values/kvcache/attn_weights.py:721-783``, ``h2o.py:175-199``)."""
-    scores += weights
+    if weights is not None:  # None: selection only
+        scores += weights
     s = scores[:, :, :n_evictable]
     if normalize:
         age = input_pos - torch.clamp(token_pos[:, :, :n_evictable].to(torch.int64), min=prefill_length - 1)

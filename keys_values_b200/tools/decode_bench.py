@@ -4,7 +4,8 @@
         [--decode 512] [--cache-name h2o-torch-quantized4] [--cache-length 16384] [--n-layer N]
 
 Random-init weights of the named architecture, synthetic prompts. Prefill is timed as one chunked
-pass over the prompts (CUDA events); decode as ``--decode`` greedy single-token steps. Prints one JSON
+pass over the prompts (CUDA events); decode as ``--decode`` greedy single-token steps (replayed from a
+CUDA graph unless ``--no-graph``). Prints one JSON
 line with prefill tokens/s and decode tokens/s (all batch rows together).
 """
 from __future__ import annotations
@@ -15,7 +16,8 @@ import json
 import torch
 
 from keys_values_b200.config import Config
-from keys_values_b200.generate.base import _prefill, batched_next_token
+from keys_values_b200.generate.base import _prefill, batched_sample
+from keys_values_b200.generate.decode_graph import Decoder
 from keys_values_b200.kvcache.factory import KVCacheFactory
 from keys_values_b200.models.model import GPT
 
@@ -29,6 +31,7 @@ def main():
     ap.add_argument("--cache-name", default="h2o-torch-quantized4")
     ap.add_argument("--cache-length", type=int, default=16384)
     ap.add_argument("--chunk-size", type=int, default=2048)
+    ap.add_argument("--no-graph", action="store_true", help="eager single-token steps instead of CUDA graph replays")
     ap.add_argument("--n-layer", type=int, default=None, help="fewer layers (the result is then marked reduced)")
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
@@ -53,12 +56,14 @@ def main():
         logits = _prefill(model, prompts, args.chunk_size, max_len)
         e[1].record()
         tokens = logits.argmax(-1).view(args.batch, 1)
-        for _ in range(8):
-            tokens = batched_next_token(model, tokens, dict(temperature=0.0)).view(args.batch, 1)
+        decoder = Decoder(model, args.batch, use_graph=not args.no_graph)
+        greedy = dict(temperature=0.0)
+        for _ in range(8):  # two eager steps, the capture, five replays
+            tokens = batched_sample(decoder(tokens)[:, -1:], greedy).view(args.batch, 1)
         torch.cuda.synchronize()
         e[2].record()
         for _ in range(args.decode):
-            tokens = batched_next_token(model, tokens, dict(temperature=0.0)).view(args.batch, 1)
+            tokens = batched_sample(decoder(tokens)[:, -1:], greedy).view(args.batch, 1)
         e[3].record()
         torch.cuda.synchronize()
     from keys_values_b200.ops import cuda as cu
@@ -68,7 +73,8 @@ def main():
     print(json.dumps({
         "bench": "chunked inference", "model": args.model + (f" (REDUCED to {args.n_layer} layers)" if args.n_layer else ""),
         "batch": args.batch, "prompt": args.prompt, "decode_steps": args.decode, "cache": args.cache_name,
-        "cache_length": args.cache_length, "prefill_tokens_per_s": args.batch * args.prompt / t_pre,
+        "cache_length": args.cache_length,
+        "decode_mode": "cuda graph" if decoder.graph is not None else f"eager ({decoder.reason or 'requested'})", "prefill_tokens_per_s": args.batch * args.prompt / t_pre,
         "decode_tokens_per_s": args.batch * args.decode / t_dec, "ms_per_decode_step": 1e3 * t_dec / args.decode,
         "peak_mem_gb": torch.cuda.max_memory_allocated(dev) / 2**30,
     }), flush=True)
