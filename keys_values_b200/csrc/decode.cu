@@ -26,10 +26,10 @@
 namespace kvb {
 
 constexpr int DEC_D = 128;
-constexpr int DEC_SPLIT = 256;    // slots per CTA
+constexpr int DEC_SPLIT = 256;    // slots per CTA (shortest split; the scratch is laid out for it)
+constexpr int DEC_SPLIT_MAX = 1024;
 constexpr int DEC_THREADS = 128;  // 4 warps
 constexpr int DEC_MAX_GS = 16;
-constexpr int DEC_BATCH = 4;     // groups of four slots whose loads are issued together
 constexpr int DEC_HB = 8;         // heads of a group handled by one CTA (more heads: more CTAs along z)
 
 struct DecParams {
@@ -47,277 +47,536 @@ struct DecParams {
   float* part_l;                // (B,H,nS)
   float* part_o;                // (B,H,nS,D)
   float* lse;                   // (B,H)
-  int B, H, G, L, C, gs, nS;
+  int B, H, G, L, C, gs, nS, split;
   float scale;
 };
 
-// Feature that element k (0..15) of a lane's row fragment holds; fl = lane & 7.
-//   bf16 : two 16-byte units, fl and fl + 8        -> features 8 fl + k, 64 + 8 fl + (k − 8)
-//   int8 : one 16-byte unit                        -> features 16 fl + k
-//   int4 : 8 bytes, byte i = (feature i, feature i + 64) as (high, low) nibble
-//                                                  -> features 8 fl + k, 64 + 8 fl + (k − 8)
+// ---------------------------------------------------------------------------------------------
+// The partial kernel multiplies with mma.sync m16n8k16 (fp32 accumulate): per CTA the problem is
+// (256 slots x 128 features) x (128 x up to 8 heads), N = 8 is the whole width of the product, far
+// below a tcgen05 tile, and the kernel is bound by the HBM read of the cache; what the tensor
+// pipe takes away is the de-quantize + FMA work of the CUDA cores (about 12 instructions per cache
+// element and head before), which made the int8 / int4 kernels compute bound.
+//
+//   S^T (16 slots x 8 heads)    = K tile (16 slots x 128 features) · Q^T      8 k-steps
+//   O^T (128 features x 8 heads) = V^T tile (128 features x 16 slots) · P^T   8 m-tiles
+//
+// No operand passes through shared memory. A dot product does not care about the order of its
+// terms, so every lane declares the bytes it loaded (whole 16-byte units of a cache row) to be the
+// fragment columns it owns, and the Q fragments are gathered once with the same permutation:
+//   pass A, lane (r = lane / 4, c = lane % 4): rows r and r + 8 of the tile, 32 features each;
+//   pass B, lane (r, c): 16 features (8 m-tiles x {row r, row r + 8}) of the slots 2c, 2c+1, 2c+8,
+//   2c+9 of the tile; the pairs (slot, slot + 1) that an A register wants are put together by
+//   the same PRMT / LOP3 that expands the codes.
+// Codes become fp16 exactly and without arithmetic: 0x6400 | code is 1024 + code; the offset joins
+// the zero point (x = (code' − (zp + 1024)) · scale stays folded into the products, whose terms
+// are exact in the fp32 accumulator; the zero-point sum of the output uses P as rounded to fp16). bf16 caches use the bf16 MMA
+// on the raw rows. The row of the token being decoded (full precision, k_new / v_new) is in one
+// tile of one CTA: there the CUDA cores compute its score and its share of the output.
+// ---------------------------------------------------------------------------------------------
+// Feature held by element e of fragment register `slot` (0: columns 2c, 2c+1; 1: columns 2c+8, 2c+9)
+// in k-step s of pass A for lane column c.
 template <int BITS>
-__device__ __forceinline__ int dec_feature(int fl, int k) {
-  if (BITS == 8) return 16 * fl + k;
-  return k < 8 ? 8 * fl + k : 64 + 8 * fl + (k - 8);
+__device__ __forceinline__ int deca_feature(int c, int s, int slot, int e) {
+  // lane column c holds the 16-byte units c, 4 + c, ... of a row, so that one load instruction of
+  // the warp covers contiguous 64 bytes of each row
+  if (BITS == 4) return ((s & 1) ? 64 : 0) + 16 * c + 4 * (s >> 1) + slot + 2 * e;
+  if (BITS == 8) return 64 * (s >> 2) + 16 * c + 4 * (s & 3) + 2 * slot + e;
+  return 32 * (s >> 1) + 8 * c + 4 * (s & 1) + 2 * slot + e;
+}
+// Feature of row r (e = 0) or r + 8 (e = 1) of m-tile m in pass B.
+template <int BITS>
+__device__ __forceinline__ int decb_feature(int r, int m, int e) {
+  // bf16: row lane r holds the units r and 8 + r of a slot (contiguous 128 bytes per instruction)
+  if (BITS == 8) return 16 * r + 2 * m + e;
+  return (m >= 4 ? 64 : 0) + 8 * r + 2 * (m & 3) + e;
 }
 
-// Byte `idx` of w as a float without the conversion unit: the byte becomes the low mantissa bits
-// of 2^23 (one PRMT), and 2^23 is subtracted (one FADD).
-__device__ __forceinline__ float dec_u8_to_f32(uint32_t w, int idx) {
-  return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7440u | (uint32_t)idx)) - 8388608.f;
-}
-
-// Raw 16 elements of row `row` for feature lane fl (32 bytes of bf16, 16 of int8, 8 of int4).
+// Two floats as one operand register: fp16 pair for quantized caches, bf16 pair for bf16 caches.
 template <int BITS>
-__device__ __forceinline__ void dec_load_raw(const void* base, long long row, int fl, uint4& a, uint4& c) {
+__device__ __forceinline__ uint32_t dec_pack2(float lo, float hi) {
   if (BITS == 16) {
-    const uint4* p = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(base) + row * DEC_D);
-    a = __ldg(p + fl);
-    c = __ldg(p + fl + 8);
-  } else if (BITS == 8) {
-    a = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(base) + row * DEC_D) + fl);
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+  const __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+template <int BITS>
+__device__ __forceinline__ void dec_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  if (BITS == 16) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
   } else {
-    const uint2 v = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(base) + row * (DEC_D / 2)) + fl);
-    a.x = v.x;
-    a.y = v.y;
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
   }
 }
 
-// ... as floats (codes are not de-quantized here).
+// 16-byte units of one row that a lane holds in pass A / of one slot in pass B
+template <int BITS> struct DecRaw { static constexpr int UA = BITS == 16 ? 4 : (BITS == 8 ? 2 : 1), WB = BITS == 16 ? 8 : (BITS == 8 ? 4 : 2); };
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async8(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// One tile (16 slots) of a warp in shared memory, lane-private: every lane copies exactly the bytes
+// its own fragments are made of and reads nothing else, so no barrier is needed, only the wait
+// for its own copies. Units are stored lane-major ((unit · 32 + lane) · 16 bytes): conflict free.
+//   K: units [rowsel · UA + i], rowsel 0 = slot r, 1 = slot r + 8
+//   V: words of the four slots 2c, 2c+1, 2c+8, 2c+9 (bf16 / int8: 16-byte units; int4: 8-byte pieces)
+//   scales: ks, kz, vs, vz of the slots r and r + 8 (quantized caches)
 template <int BITS>
-__device__ __forceinline__ void dec_convert(const uint4& a, const uint4& c, float* x) {
-  if (BITS == 16) {
-    const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&a);
-    const __nv_bfloat162* hc = reinterpret_cast<const __nv_bfloat162*>(&c);
+struct DecStage {
+  static constexpr int UA = DecRaw<BITS>::UA, WB = DecRaw<BITS>::WB;
+  static constexpr int K_BYTES = 2 * UA * 512;
+  static constexpr int V_BYTES = 4 * WB * 4 * 32;
+  static constexpr int S_BYTES = BITS == 16 ? 0 : 8 * 4 * 32;
+  static constexpr int BYTES = K_BYTES + V_BYTES + S_BYTES;
+  static constexpr int STAGES = BITS == 4 ? 5 : 3;  // 96 / 60 / 60 KB per CTA: two (bf16) or three CTAs per SM
+};
+
+// kb / vb: this lane's byte address of (first row of the split, unit c) resp. (…, unit r); row
+// offsets within a split fit 32 bits.
+template <int BITS>
+__device__ __forceinline__ void dec_stage_issue(uint8_t* st, const DecParams& p, const uint8_t* kb, const uint8_t* vb,
+                                                long long row0j0, int tb, int n, int lane) {
+  using S = DecStage<BITS>;
+  const int r = lane >> 2, c = lane & 3;
+  constexpr int row_bytes = BITS == 16 ? 256 : (BITS == 8 ? 128 : 64);
+  const int jlo = min(tb + r, n - 1), jhi = min(tb + r + 8, n - 1);  // rows beyond the split re-read its last row
+  const uint8_t* klo = kb + (unsigned)(jlo * row_bytes);
+  const uint8_t* khi = kb + (unsigned)(jhi * row_bytes);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 f = __bfloat1622float2(ha[j]), g = __bfloat1622float2(hc[j]);
-      x[2 * j] = f.x; x[2 * j + 1] = f.y;
-      x[8 + 2 * j] = g.x; x[8 + 2 * j + 1] = g.y;
+  for (int i = 0; i < S::UA; ++i) {
+    cp_async16(st + ((i * 32) + lane) * 16, klo + 64 * i);
+    cp_async16(st + (((S::UA + i) * 32) + lane) * 16, khi + 64 * i);
+  }
+  uint8_t* vst = st + S::K_BYTES;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int jv = min(tb + 2 * c + (i & 1) + 8 * (i >> 1), n - 1);
+    const uint8_t* vr = vb + (unsigned)(jv * row_bytes);
+    if (BITS == 16) {
+      cp_async16(vst + (((2 * i) * 32) + lane) * 16, vr);
+      cp_async16(vst + (((2 * i + 1) * 32) + lane) * 16, vr + 128);
+    } else if (BITS == 8) {
+      cp_async16(vst + ((i * 32) + lane) * 16, vr);
+    } else {
+      cp_async8(vst + ((i * 32) + lane) * 8, vr);
     }
+  }
+  if (BITS != 16) {
+    uint8_t* sst = st + S::K_BYTES + S::V_BYTES;
+    const long long rlo = row0j0 + jlo, rhi = row0j0 + jhi;
+    cp_async4(sst + (0 * 32 + lane) * 4, p.ks + rlo);
+    cp_async4(sst + (1 * 32 + lane) * 4, p.ks + rhi);
+    cp_async4(sst + (2 * 32 + lane) * 4, p.kz + rlo);
+    cp_async4(sst + (3 * 32 + lane) * 4, p.kz + rhi);
+    cp_async4(sst + (4 * 32 + lane) * 4, p.vs + rlo);
+    cp_async4(sst + (5 * 32 + lane) * 4, p.vs + rhi);
+    cp_async4(sst + (6 * 32 + lane) * 4, p.vz + rlo);
+    cp_async4(sst + (7 * 32 + lane) * 4, p.vz + rhi);
+  }
+}
+
+// ... as the A registers of k-step s for this row: x0 = columns (2c, 2c+1), x1 = columns (2c+8, 2c+9)
+template <int BITS>
+__device__ __forceinline__ void deca_frag(const uint4 (&u)[DecRaw<BITS>::UA], int s, uint32_t& x0, uint32_t& x1) {
+  const uint32_t* w = reinterpret_cast<const uint32_t*>(u);
+  if (BITS == 16) {
+    x0 = w[2 * s];
+    x1 = w[2 * s + 1];
   } else if (BITS == 8) {
-    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-    for (int j = 0; j < 16; ++j) x[j] = dec_u8_to_f32(w[j >> 2], j & 3);
+    x0 = __byte_perm(w[s], 0x64646464u, 0x4140);
+    x1 = __byte_perm(w[s], 0x64646464u, 0x4342);
   } else {
-    const uint32_t w[2] = {a.x, a.y};
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const uint32_t byte = (w[j >> 2] >> (8 * (j & 3))) & 0xFFu;
-      x[j] = __uint_as_float(0x4B000000u | (byte >> 4)) - 8388608.f;
-      x[8 + j] = __uint_as_float(0x4B000000u | (byte & 0xFu)) - 8388608.f;
+    const uint32_t v = w[s >> 1];
+    if (s & 1) {  // low nibbles: features 64 + ...
+      x0 = (v & 0x000F000Fu) | 0x64006400u;
+      x1 = ((v >> 8) & 0x000F000Fu) | 0x64006400u;
+    } else {
+      x0 = ((v >> 4) & 0x000F000Fu) | 0x64006400u;
+      x1 = ((v >> 12) & 0x000F000Fu) | 0x64006400u;
     }
   }
 }
 
-// One CTA = (batch, KV group, split of DEC_SPLIT slots, block of GS heads). A warp handles four
-// slots at a time: 8 lanes per slot, 16 features per lane, so that a row is read as whole
-// 16-byte units, coalesced, several loads in flight per lane. Scores are reduced over the 8
-// lanes by shuffles; p·V accumulates in registers (GS x 16 per lane) and is reduced once.
-template <int BITS, int GS>
+// A registers of m-tile m for one pair of slots (wa: the even slot, wb: the odd one):
+// x0 = (row r; slot, slot + 1), x1 = (row r + 8; slot, slot + 1)
+template <int BITS>
+__device__ __forceinline__ void decb_frag(const uint32_t (&wa)[DecRaw<BITS>::WB], const uint32_t (&wb)[DecRaw<BITS>::WB], int m,
+                                          uint32_t& x0, uint32_t& x1) {
+  if (BITS == 16) {
+    x0 = __byte_perm(wa[m], wb[m], 0x5410);
+    x1 = __byte_perm(wa[m], wb[m], 0x7632);
+  } else if (BITS == 8) {
+    const uint32_t t = __byte_perm(wa[m >> 1], wb[m >> 1], (m & 1) ? 0x7362 : 0x5140);
+    x0 = __byte_perm(t, 0x64646464u, 0x4140);
+    x1 = __byte_perm(t, 0x64646464u, 0x4342);
+  } else {
+    const int pi = m & 3;  // bytes (2 (pi & 1), +1) of word pi >> 1
+    const uint32_t t = __byte_perm(wa[pi >> 1], wb[pi >> 1], (pi & 1) ? 0x7632 : 0x5410);
+    if (m >= 4) {  // low nibbles: features 64 + ...
+      x0 = (t & 0x000F000Fu) | 0x64006400u;
+      x1 = ((t >> 8) & 0x000F000Fu) | 0x64006400u;
+    } else {
+      x0 = ((t >> 4) & 0x000F000Fu) | 0x64006400u;
+      x1 = ((t >> 12) & 0x000F000Fu) | 0x64006400u;
+    }
+  }
+}
+
+// One CTA = (batch, KV group, split of p.split slots, block of up to 8 heads). A warp owns a
+// quarter of the split, tile by tile (16 slots), and runs on its own (online softmax per warp): a
+// ring of lane-private stages in shared memory is filled with cp.async several tiles ahead, so that
+// the HBM latency is covered by bytes in flight, not by registers or occupancy; scores,
+// exponentials (handed from the score layout to the P^T operand layout through a warp-private patch
+// of shared memory) and the product with V follow without a block-wide barrier; the four warps
+// merge their (max, sum, O) once at the end.
+template <int BITS>
 __global__ void __launch_bounds__(DEC_THREADS)
 decode_partial_kernel(const DecParams p) {
-  __shared__ float sc[GS][DEC_SPLIT];           // scores, later p · v_scale
-  __shared__ float red[DEC_THREADS / 32][GS];   // per-warp reductions
-  __shared__ float stat[2][GS];                 // block max, Σ p · v_scale · v_zero_point
-  __shared__ float ored[DEC_THREADS / 32][GS][DEC_D];
-  const int bg = blockIdx.x, split = blockIdx.y, h0 = blockIdx.z * GS;
+  using ST = DecStage<BITS>;
+  constexpr int NW = DEC_THREADS / 32;
+  constexpr int PST = 24;                             // row stride of the P patch (floats)
+  extern __shared__ __align__(16) uint8_t dec_dsm[];
+  __shared__ __align__(16) float psm[NW][DEC_HB][PST];
+  __shared__ float wm[NW][DEC_HB], wl[NW][DEC_HB], wz[NW][DEC_HB];
+  const int bg = blockIdx.x, split = blockIdx.y, h0 = blockIdx.z * DEC_HB;
+  const int nh = min(DEC_HB, p.gs - h0);  // heads of this CTA
   const int b = bg / p.G, g = bg % p.G;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int fl = lane & 7, sub = lane >> 3;
-  const int j0 = split * DEC_SPLIT, j1 = min(j0 + DEC_SPLIT, p.L);
+  const int r = lane >> 2, c = lane & 3;
+  const int j0 = split * p.split, j1 = min(j0 + p.split, p.L);
   const int n = j1 - j0;
   const long long row0 = ((long long)b * p.G + g) * p.C;
   const int ns = p.new_slot ? p.new_slot[b * p.G + g] : -1;
-  const long long head0 = (long long)b * p.H + g * p.gs + h0;  // first head of this CTA
+  const int ns_tile = (ns >= j0 && ns < j1) ? (ns - j0) >> 4 : -1;  // tile of this CTA that holds the new token
+  const long long head0 = (long long)b * p.H + g * p.gs + h0;       // first head of this CTA
+  const int wslots = p.split / NW;                                   // slots of a warp (a multiple of 16)
+  const int wbase = warp * wslots;                                   // first slot of this warp within the split
+  const int ntiles = wbase < n ? (min(wslots, n - wbase) + 15) >> 4 : 0;
+  const int ha = 2 * c, hb = 2 * c + 1;                              // heads of this lane's scores and outputs
+  uint8_t* wst = dec_dsm + (size_t)warp * ST::STAGES * ST::BYTES;
+  constexpr int row_bytes = BITS == 16 ? 256 : (BITS == 8 ? 128 : 64);
+  const uint8_t* kb = reinterpret_cast<const uint8_t*>(p.kq) + (row0 + j0) * row_bytes + c * 16;
+  const uint8_t* vb = reinterpret_cast<const uint8_t*>(p.vq) + (row0 + j0) * row_bytes + r * (BITS == 4 ? 8 : 16);
 
-  // query fragment of this lane and Σ_i q_i per head (for the zero-point term)
-  float qf[GS][16], qsum[GS];
+  // the first tiles are requested before anything else
 #pragma unroll
-  for (int h = 0; h < GS; ++h) {
-    const __nv_bfloat16* qr = p.q + (head0 + h) * DEC_D;
-    float s = 0.f;
-#pragma unroll
-    for (int k = 0; k < 16; ++k) {
-      qf[h][k] = __bfloat162float(qr[dec_feature<BITS>(fl, k)]);
-      s += qf[h][k];
-    }
-    s += __shfl_xor_sync(0xffffffffu, s, 1);
-    s += __shfl_xor_sync(0xffffffffu, s, 2);
-    s += __shfl_xor_sync(0xffffffffu, s, 4);
-    qsum[h] = s;
+  for (int t = 0; t < ST::STAGES - 1; ++t) {
+    if (t < ntiles) dec_stage_issue<BITS>(wst + t * ST::BYTES, p, kb, vb, row0 + j0, wbase + 16 * t, n, lane);
+    cp_async_commit();
   }
 
-  // ---- pass A: raw scores
-  float lmax[GS];
+  // Q fragments of head r (B operand of the score product) and Σ_f q_f for the heads ha, hb
+  uint32_t qb[8][2];
+  float qsum0, qsum1;
+  {
+    float s = 0.f;
+    const __nv_bfloat16* qr = p.q + (head0 + min(r, nh - 1)) * DEC_D;
 #pragma unroll
-  for (int h = 0; h < GS; ++h) lmax[h] = -FLT_MAX;
-  // DEC_BATCH groups of four slots per iteration: all their loads are issued before the first
-  // conversion, so that 8 x 16 bytes (bf16) are in flight per lane
-  for (int jb0 = warp * 4; jb0 < n; jb0 += DEC_BATCH * (DEC_THREADS / 8)) {  // warp-uniform trip count (shuffles inside)
-    uint4 ra[DEC_BATCH], rc[DEC_BATCH];
-    float ksc[DEC_BATCH], kz[DEC_BATCH];
+    for (int ks = 0; ks < 8; ++ks)
 #pragma unroll
-    for (int q = 0; q < DEC_BATCH; ++q) {
-      const int jj = min(jb0 + q * (DEC_THREADS / 8) + sub, n - 1);  // rows beyond the split re-read its last row
-      dec_load_raw<BITS>(p.kq, row0 + j0 + jj, fl, ra[q], rc[q]);
-      ksc[q] = 1.f;
-      kz[q] = 0.f;
-      if (BITS != 16) {
-        ksc[q] = __ldg(p.ks + row0 + j0 + jj);
-        kz[q] = (float)__ldg(p.kz + row0 + j0 + jj);
-      }
-    }
-#pragma unroll
-    for (int q = 0; q < DEC_BATCH; ++q) {
-      const int jj = jb0 + q * (DEC_THREADS / 8) + sub;
-      const bool valid = jj < n;
-      const int j = j0 + jj;
-      float x[16];
-      dec_convert<BITS>(ra[q], rc[q], x);
-      float kscale = ksc[q], kzp = kz[q];
-      if (valid && j == ns) {  // the token being decoded: exact values instead of the cache row
-        const __nv_bfloat16* kr = p.k_new + ((long long)b * p.G + g) * DEC_D;
-#pragma unroll
-        for (int k = 0; k < 16; ++k) x[k] = __bfloat162float(kr[dec_feature<BITS>(fl, k)]);
-        kscale = 1.f;
-        kzp = 0.f;
-      }
-#pragma unroll
-      for (int h = 0; h < GS; ++h) {
-        float acc = 0.f;
-#pragma unroll
-        for (int k = 0; k < 16; ++k) acc = fmaf(qf[h][k], x[k], acc);
-        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-        acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-        const float sv = p.scale * kscale * (acc - kzp * qsum[h]);
-        if (valid) lmax[h] = fmaxf(lmax[h], sv);
-        if (fl == 0 && valid) {
-          sc[h][jj] = sv;
-          p.logits[(head0 + h) * p.L + j] = sv;
+      for (int sl = 0; sl < 2; ++sl) {
+        float a = __bfloat162float(qr[deca_feature<BITS>(c, ks, sl, 0)]);
+        float e = __bfloat162float(qr[deca_feature<BITS>(c, ks, sl, 1)]);
+        if (r >= nh) a = e = 0.f;
+        const uint32_t pk = dec_pack2<BITS>(a, e);
+        qb[ks][sl] = pk;
+        if (BITS == 16) {
+          s += a + e;
+        } else {  // the sum of what the tensor core multiplies with: the fp16 values
+          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&pk));
+          s += f.x + f.y;
         }
       }
-    }
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    qsum0 = __shfl_sync(0xffffffffu, s, 8 * c);
+    qsum1 = __shfl_sync(0xffffffffu, s, 8 * c + 4);
   }
+
+  float m0 = -FLT_MAX, m1 = -FLT_MAX;       // running maxima of the heads ha, hb (equal in all row lanes)
+  float l0 = 0.f, l1 = 0.f, z0 = 0.f, z1 = 0.f;  // this lane's share of Σ p and Σ p · v_scale · v_zp
+  float acc[8][4];
 #pragma unroll
-  for (int h = 0; h < GS; ++h) {
-    const float m = warp_max(lmax[h]);
-    if (lane == 0) red[warp][h] = m;
-  }
-  __syncthreads();
-  if (tid < GS) {
-    float m = -FLT_MAX;
-    for (int w = 0; w < DEC_THREADS / 32; ++w) m = fmaxf(m, red[w][tid]);
-    stat[0][tid] = m;
-  }
-  __syncthreads();
-  // ---- p = exp(s − m) with the V scale folded in; block sums of p and of p · v_scale · v_zp
-  float lsum[GS], zsum[GS];
-#pragma unroll
-  for (int h = 0; h < GS; ++h) lsum[h] = zsum[h] = 0.f;
-  for (int jj = tid; jj < n; jj += DEC_THREADS) {
-    const int j = j0 + jj;
-    float vscale = 1.f, vzp = 0.f;
-    if (BITS != 16 && j != ns) {
-      vscale = __ldg(p.vs + row0 + j);
-      vzp = (float)__ldg(p.vz + row0 + j);
+  for (int m = 0; m < 8; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
+
+  for (int t = 0; t < ntiles; ++t) {
+    {  // keep the ring full: tile t + STAGES − 1 goes where tile t − 1 was
+      const int tn = t + ST::STAGES - 1;
+      if (tn < ntiles) dec_stage_issue<BITS>(wst + (tn % ST::STAGES) * ST::BYTES, p, kb, vb, row0 + j0, wbase + 16 * tn, n, lane);
+      cp_async_commit();
+      cp_async_wait<ST::STAGES - 1>();  // this lane's copies of tile t have landed
     }
-#pragma unroll
-    for (int h = 0; h < GS; ++h) {
-      const float pr = __expf(sc[h][jj] - stat[0][h]);
-      lsum[h] += pr;
-      zsum[h] += pr * vscale * vzp;
-      sc[h][jj] = pr * vscale;
+    const uint8_t* st = wst + (t % ST::STAGES) * ST::BYTES;
+    const int tb = wbase + 16 * t;
+    const int jlo = tb + r, jhi = tb + r + 8;
+    const bool has_new = (tb >> 4) == ns_tile;
+    float kslo = 1.f, kshi = 1.f, kzlo = 0.f, kzhi = 0.f, vslo = 1.f, vshi = 1.f, vzlo = 0.f, vzhi = 0.f;
+    if (BITS != 16) {
+      const uint8_t* sst = st + ST::K_BYTES + ST::V_BYTES;
+      kslo = *reinterpret_cast<const float*>(sst + (0 * 32 + lane) * 4);
+      kshi = *reinterpret_cast<const float*>(sst + (1 * 32 + lane) * 4);
+      kzlo = (float)*reinterpret_cast<const int32_t*>(sst + (2 * 32 + lane) * 4) + 1024.f;  // codes enter as 1024 + code
+      kzhi = (float)*reinterpret_cast<const int32_t*>(sst + (3 * 32 + lane) * 4) + 1024.f;
+      vslo = *reinterpret_cast<const float*>(sst + (4 * 32 + lane) * 4);
+      vshi = *reinterpret_cast<const float*>(sst + (5 * 32 + lane) * 4);
+      vzlo = (float)*reinterpret_cast<const int32_t*>(sst + (6 * 32 + lane) * 4) + 1024.f;
+      vzhi = (float)*reinterpret_cast<const int32_t*>(sst + (7 * 32 + lane) * 4) + 1024.f;
     }
-  }
-  __syncthreads();  // red is reused
+    // ---- scores: d[0], [1]: slot jlo, heads ha, hb; d[2], [3]: slot jhi
+    float d[4] = {0.f, 0.f, 0.f, 0.f};
+    {
+      uint4 ulo[ST::UA], uhi[ST::UA];
 #pragma unroll
-  for (int h = 0; h < GS; ++h) {
-    const float s1 = warp_sum(lsum[h]), s2 = warp_sum(zsum[h]);
-    if (lane == 0) {
-      red[warp][h] = s1;
-      ored[warp][h][0] = s2;
-    }
-  }
-  __syncthreads();
-  if (tid < GS) {
-    float s1 = 0.f, s2 = 0.f;
-    for (int w = 0; w < DEC_THREADS / 32; ++w) {
-      s1 += red[w][tid];
-      s2 += ored[w][tid][0];
-    }
-    const long long idx = (head0 + tid) * p.nS + split;
-    p.part_m[idx] = stat[0][tid];
-    p.part_l[idx] = s1;
-    stat[1][tid] = s2;
-  }
-  __syncthreads();
-  // ---- pass B: O += (p · v_scale) · code ; the zero-point term is subtracted once at the end
-  float acc[GS][16];
+      for (int i = 0; i < ST::UA; ++i) {
+        ulo[i] = *reinterpret_cast<const uint4*>(st + ((i * 32) + lane) * 16);
+        uhi[i] = *reinterpret_cast<const uint4*>(st + (((ST::UA + i) * 32) + lane) * 16);
+      }
+      float d2[4] = {0.f, 0.f, 0.f, 0.f};  // two chains of four dependent MMAs instead of one of eight
 #pragma unroll
-  for (int h = 0; h < GS; ++h)
-#pragma unroll
-    for (int k = 0; k < 16; ++k) acc[h][k] = 0.f;
-  for (int jb0 = warp * 4; jb0 < n; jb0 += DEC_BATCH * (DEC_THREADS / 8)) {
-    uint4 ra[DEC_BATCH], rc[DEC_BATCH];
-#pragma unroll
-    for (int q = 0; q < DEC_BATCH; ++q) {
-      const int jj = min(jb0 + q * (DEC_THREADS / 8) + sub, n - 1);
-      dec_load_raw<BITS>(p.vq, row0 + j0 + jj, fl, ra[q], rc[q]);
-    }
-#pragma unroll
-    for (int q = 0; q < DEC_BATCH; ++q) {
-      const int jj = jb0 + q * (DEC_THREADS / 8) + sub;
-      const bool valid = jj < n;
-      float x[16];
-      dec_convert<BITS>(ra[q], rc[q], x);
-      if (valid && j0 + jj == ns) {
-        const __nv_bfloat16* vr = p.v_new + ((long long)b * p.G + g) * DEC_D;
-#pragma unroll
-        for (int k = 0; k < 16; ++k) x[k] = __bfloat162float(vr[dec_feature<BITS>(fl, k)]);
+      for (int ks = 0; ks < 8; ++ks) {
+        uint32_t a[4];
+        deca_frag<BITS>(ulo, ks, a[0], a[2]);
+        deca_frag<BITS>(uhi, ks, a[1], a[3]);
+        if (ks & 1) dec_mma<BITS>(d2, a, qb[ks][0], qb[ks][1]);
+        else dec_mma<BITS>(d, a, qb[ks][0], qb[ks][1]);
       }
 #pragma unroll
-      for (int h = 0; h < GS; ++h) {
-        const float ps = valid ? sc[h][jj] : 0.f;
+      for (int i = 0; i < 4; ++i) d[i] += d2[i];
+    }
+    if (has_new) {
+      // The tile with the token being decoded: the cache row of its slot is stale. Its exact
+      // score q_h · k_new is computed by the whole warp (lane (r, c): head r, the 32 features of
+      // its Q fragments) and replaces what the tensor core made of the stale row.
+      const __nv_bfloat16* kr = p.k_new + ((long long)b * p.G + g) * DEC_D;
+      float dn = 0.f;
 #pragma unroll
-        for (int k = 0; k < 16; ++k) acc[h][k] = fmaf(ps, x[k], acc[h][k]);
+      for (int ks = 0; ks < 8; ++ks)
+#pragma unroll
+        for (int sl = 0; sl < 2; ++sl) {
+          float2 qf;
+          if (BITS == 16) qf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qb[ks][sl]));
+          else qf = __half22float2(*reinterpret_cast<const __half2*>(&qb[ks][sl]));
+          dn = fmaf(qf.x, __bfloat162float(kr[deca_feature<BITS>(c, ks, sl, 0)]), dn);
+          dn = fmaf(qf.y, __bfloat162float(kr[deca_feature<BITS>(c, ks, sl, 1)]), dn);
+        }
+      dn += __shfl_xor_sync(0xffffffffu, dn, 1);
+      dn += __shfl_xor_sync(0xffffffffu, dn, 2);
+      const float dna = __shfl_sync(0xffffffffu, dn, 8 * c), dnb = __shfl_sync(0xffffffffu, dn, 8 * c + 4);  // heads ha, hb
+      if (j0 + jlo == ns) { d[0] = dna; d[1] = dnb; kslo = 1.f; kzlo = 0.f; vslo = 1.f; vzlo = 0.f; }
+      if (j0 + jhi == ns) { d[2] = dna; d[3] = dnb; kshi = 1.f; kzhi = 0.f; vshi = 1.f; vzhi = 0.f; }
+    }
+    float s00 = p.scale * kslo * (d[0] - kzlo * qsum0), s01 = p.scale * kslo * (d[1] - kzlo * qsum1);
+    float s10 = p.scale * kshi * (d[2] - kzhi * qsum0), s11 = p.scale * kshi * (d[3] - kzhi * qsum1);
+    float mx0 = -FLT_MAX, mx1 = -FLT_MAX;
+    if (jlo < n) {
+      if (ha < nh) p.logits[(head0 + ha) * p.L + j0 + jlo] = s00;
+      if (hb < nh) p.logits[(head0 + hb) * p.L + j0 + jlo] = s01;
+      mx0 = s00;
+      mx1 = s01;
+    } else {
+      s00 = s01 = -FLT_MAX;
+    }
+    if (jhi < n) {
+      if (ha < nh) p.logits[(head0 + ha) * p.L + j0 + jhi] = s10;
+      if (hb < nh) p.logits[(head0 + hb) * p.L + j0 + jhi] = s11;
+      mx0 = fmaxf(mx0, s10);
+      mx1 = fmaxf(mx1, s11);
+    } else {
+      s10 = s11 = -FLT_MAX;
+    }
+    // ---- online softmax: new maxima over the row lanes; what has been accumulated shrinks by exp(m − m')
+#pragma unroll
+    for (int o = 4; o < 32; o <<= 1) {
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+    }
+    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+    const float al0 = __expf(m0 - mn0), al1 = __expf(m1 - mn1);
+    m0 = mn0;
+    m1 = mn1;
+    if (__any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f)) {
+      l0 *= al0; z0 *= al0;
+      l1 *= al1; z1 *= al1;
+#pragma unroll
+      for (int m = 0; m < 8; ++m) {
+        acc[m][0] *= al0; acc[m][2] *= al0;
+        acc[m][1] *= al1; acc[m][3] *= al1;
       }
     }
-  }
-  // reduce over the four slot lanes of the warp, then over the warps
-#pragma unroll
-  for (int h = 0; h < GS; ++h)
-#pragma unroll
-    for (int k = 0; k < 16; ++k) {
-      float v = acc[h][k];
-      v += __shfl_xor_sync(0xffffffffu, v, 8);
-      v += __shfl_xor_sync(0xffffffffu, v, 16);
-      if (sub == 0) ored[warp][h][dec_feature<BITS>(fl, k)] = v;
+    {
+      const float p00 = s00 == -FLT_MAX ? 0.f : __expf(s00 - m0), p01 = s01 == -FLT_MAX ? 0.f : __expf(s01 - m1);
+      const float p10 = s10 == -FLT_MAX ? 0.f : __expf(s10 - m0), p11 = s11 == -FLT_MAX ? 0.f : __expf(s11 - m1);
+      l0 += p00 + p10;
+      l1 += p01 + p11;
+      float a00 = p00 * vslo, a01 = p01 * vslo, a10 = p10 * vshi, a11 = p11 * vshi;
+      if (BITS != 16) {  // as the tensor core will see them, so that the offset of the codes cancels exactly
+        a00 = __half2float(__float2half_rn(a00)); a01 = __half2float(__float2half_rn(a01));
+        a10 = __half2float(__float2half_rn(a10)); a11 = __half2float(__float2half_rn(a11));
+      }
+      z0 += a00 * vzlo + a10 * vzhi;
+      z1 += a01 * vzlo + a11 * vzhi;
+      psm[warp][ha][r] = a00;
+      psm[warp][hb][r] = a01;
+      psm[warp][ha][r + 8] = a10;
+      psm[warp][hb][r + 8] = a11;
     }
+    __syncwarp();
+    // ---- O^T += V^T tile · P^T
+    if (has_new) {
+      // the new token's share p · v_new is added on the CUDA cores (every (feature, head) of the
+      // accumulator tile has one owner); its stale cache row then multiplies with zero
+      const int sidx = ns - j0 - tb;
+      const float pa = psm[warp][ha][sidx], pb = psm[warp][hb][sidx];
+      const __nv_bfloat16* vr = p.v_new + ((long long)b * p.G + g) * DEC_D;
+#pragma unroll
+      for (int m = 0; m < 8; ++m) {
+        const float v0 = __bfloat162float(vr[decb_feature<BITS>(r, m, 0)]), v1 = __bfloat162float(vr[decb_feature<BITS>(r, m, 1)]);
+        acc[m][0] = fmaf(pa, v0, acc[m][0]);
+        acc[m][1] = fmaf(pb, v0, acc[m][1]);
+        acc[m][2] = fmaf(pa, v1, acc[m][2]);
+        acc[m][3] = fmaf(pb, v1, acc[m][3]);
+      }
+      __syncwarp();
+      if (lane < DEC_HB) psm[warp][lane][sidx] = 0.f;
+      __syncwarp();
+    }
+    {
+      const float2 p0 = *reinterpret_cast<const float2*>(&psm[warp][r][2 * c]);
+      const float2 p1 = *reinterpret_cast<const float2*>(&psm[warp][r][2 * c + 8]);
+      const uint32_t pb0 = dec_pack2<BITS>(p0.x, p0.y), pb1 = dec_pack2<BITS>(p1.x, p1.y);
+      uint32_t vw[4][ST::WB];
+      const uint8_t* vst = st + ST::K_BYTES;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (BITS == 16) {
+          const uint4 x = *reinterpret_cast<const uint4*>(vst + (((2 * i) * 32) + lane) * 16);
+          const uint4 y = *reinterpret_cast<const uint4*>(vst + (((2 * i + 1) * 32) + lane) * 16);
+          vw[i][0] = x.x; vw[i][1] = x.y; vw[i][2] = x.z; vw[i][3] = x.w;
+          vw[i][4 % ST::WB] = y.x; vw[i][5 % ST::WB] = y.y; vw[i][6 % ST::WB] = y.z; vw[i][7 % ST::WB] = y.w;
+        } else if (BITS == 8) {
+          const uint4 x = *reinterpret_cast<const uint4*>(vst + ((i * 32) + lane) * 16);
+          vw[i][0] = x.x; vw[i][1] = x.y; vw[i][2 % ST::WB] = x.z; vw[i][3 % ST::WB] = x.w;
+        } else {
+          const uint2 x = *reinterpret_cast<const uint2*>(vst + ((i * 32) + lane) * 8);
+          vw[i][0] = x.x; vw[i][1] = x.y;
+        }
+      }
+#pragma unroll
+      for (int m = 0; m < 8; ++m) {
+        uint32_t a[4];
+        decb_frag<BITS>(vw[0], vw[1], m, a[0], a[1]);
+        decb_frag<BITS>(vw[2], vw[3], m, a[2], a[3]);
+        dec_mma<BITS>(acc[m], a, pb0, pb1);
+      }
+    }
+    __syncwarp();  // the P patch is rewritten by the next tile
+  }
+  cp_async_wait<0>();
+  // ---- the warp's totals (over the row lanes), then the merge of the four warps
+#pragma unroll
+  for (int o = 4; o < 32; o <<= 1) {
+    l0 += __shfl_xor_sync(0xffffffffu, l0, o);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, o);
+    z0 += __shfl_xor_sync(0xffffffffu, z0, o);
+    z1 += __shfl_xor_sync(0xffffffffu, z1, o);
+  }
+  if (r == 0) {
+    wm[warp][ha] = m0; wm[warp][hb] = m1;
+    wl[warp][ha] = l0; wl[warp][hb] = l1;
+    wz[warp][ha] = z0; wz[warp][hb] = z1;
+  }
+  // acc[m][0], [1]: feature (r, m, 0), heads ha, hb; [2], [3]: feature (r, m, 1). The warp's output
+  // tile (8 heads x 128 floats) goes where its own stages were: all its copies have landed and been read.
+  float(*ored)[DEC_D] = reinterpret_cast<float(*)[DEC_D]>(wst);
+#pragma unroll
+  for (int m = 0; m < 8; ++m) {
+    const int f0 = decb_feature<BITS>(r, m, 0), f1 = decb_feature<BITS>(r, m, 1);
+    ored[ha][f0] = acc[m][0];
+    ored[hb][f0] = acc[m][1];
+    ored[ha][f1] = acc[m][2];
+    ored[hb][f1] = acc[m][3];
+  }
   __syncthreads();
-  for (int i = tid; i < GS * DEC_D; i += DEC_THREADS) {
+  for (int i = tid; i < nh * DEC_D; i += DEC_THREADS) {
     const int h = i / DEC_D, d = i % DEC_D;
-    float s = 0.f;
+    float M = -FLT_MAX;
 #pragma unroll
-    for (int w = 0; w < DEC_THREADS / 32; ++w) s += ored[w][h][d];
-    p.part_o[((head0 + h) * p.nS + split) * DEC_D + d] = s - stat[1][h];
+    for (int w2 = 0; w2 < NW; ++w2) M = fmaxf(M, wm[w2][h]);
+    float o = 0.f, l = 0.f, z = 0.f;
+#pragma unroll
+    for (int w2 = 0; w2 < NW; ++w2) {
+      const float f = wm[w2][h] == -FLT_MAX ? 0.f : __expf(wm[w2][h] - M);  // a warp without slots has nothing to add
+      const float* ow = reinterpret_cast<const float*>(dec_dsm + (size_t)w2 * ST::STAGES * ST::BYTES);
+      o += f * ow[h * DEC_D + d];
+      l += f * wl[w2][h];
+      z += f * wz[w2][h];
+    }
+    p.part_o[((head0 + h) * p.nS + split) * DEC_D + d] = o - z;
+    if (d == 0) {
+      const long long idx = (head0 + h) * p.nS + split;
+      p.part_m[idx] = M;
+      p.part_l[idx] = l;
+    }
   }
 }
 
+template <int BITS>
+constexpr int dec_dyn_smem() { return (DEC_THREADS / 32) * DecStage<BITS>::STAGES * DecStage<BITS>::BYTES; }
+
 __global__ void decode_merge_kernel(const DecParams p) {
   const int bh = blockIdx.x, d = threadIdx.x;  // 128 threads
+  __shared__ float wgt[DEC_THREADS];
+  __shared__ float red[2][DEC_THREADS / 32];
   const float* pm = p.part_m + (long long)bh * p.nS;
   const float* pl = p.part_l + (long long)bh * p.nS;
   float M = -FLT_MAX;
-  for (int s = 0; s < p.nS; ++s) M = fmaxf(M, pm[s]);
+  for (int s = d; s < p.nS; s += DEC_THREADS) M = fmaxf(M, pm[s]);
+  M = warp_max(M);
+  if ((d & 31) == 0) red[0][d >> 5] = M;
+  __syncthreads();
+  M = fmaxf(fmaxf(red[0][0], red[0][1]), fmaxf(red[0][2], red[0][3]));
   float Lsum = 0.f, o = 0.f;
-  for (int s = 0; s < p.nS; ++s) {
-    const float w = __expf(pm[s] - M);
-    Lsum += pl[s] * w;
-    o += p.part_o[((long long)bh * p.nS + s) * DEC_D + d] * w;
+  for (int s0 = 0; s0 < p.nS; s0 += DEC_THREADS) {  // nS <= 128 for every context the scratch was sized for; the loop covers more
+    const int cnt = min(DEC_THREADS, p.nS - s0);
+    __syncthreads();
+    if (d < cnt) {
+      const float w = __expf(pm[s0 + d] - M);
+      wgt[d] = w;
+      Lsum += pl[s0 + d] * w;
+    }
+    __syncthreads();
+    const float* po = p.part_o + ((long long)bh * p.nS + s0) * DEC_D + d;
+    int s = 0;
+    for (; s + 8 <= cnt; s += 8) {  // eight independent loads in flight
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = po[(long long)(s + u) * DEC_D];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) o = fmaf(v[u], wgt[s + u], o);
+    }
+    for (; s < cnt; ++s) o = fmaf(po[(long long)s * DEC_D], wgt[s], o);
   }
+  Lsum = warp_sum(Lsum);
+  if ((d & 31) == 0) red[1][d >> 5] = Lsum;
+  __syncthreads();
+  Lsum = red[1][0] + red[1][1] + red[1][2] + red[1][3];
   p.out[(long long)bh * DEC_D + d] = __float2bfloat16_rn(o / Lsum);
   if (d == 0) p.lse[bh] = M + logf(Lsum);
 }
@@ -357,7 +616,12 @@ extern "C" int kvb_decode_attn(const void* q, const void* kq, const void* vq, co
   p.k_new = (const __nv_bfloat16*)k_new; p.v_new = (const __nv_bfloat16*)v_new; p.new_slot = k_new ? new_slot : nullptr;
   p.out = (__nv_bfloat16*)out; p.weights = weights;
   p.B = B; p.H = H; p.G = G; p.L = L; p.C = C; p.gs = gs; p.scale = scale;
-  p.nS = (L + DEC_SPLIT - 1) / DEC_SPLIT;
+  // Slots per CTA: longer splits spend less on the per-CTA prologue and merge, as long as there are
+  // CTAs for a few waves over the SMs. The scratch is laid out for the shortest split.
+  const int zb = (gs + DEC_HB - 1) / DEC_HB;
+  p.split = DEC_SPLIT;
+  while (p.split < DEC_SPLIT_MAX && (long long)B * G * zb * ((L + 2 * p.split - 1) / (2 * p.split)) >= 4 * 148) p.split *= 2;
+  p.nS = (L + p.split - 1) / p.split;
   float* sc = reinterpret_cast<float*>(scratch);
   p.logits = sc; sc += (long long)B * H * L;
   p.part_m = sc; sc += (long long)B * H * p.nS;
@@ -365,22 +629,19 @@ extern "C" int kvb_decode_attn(const void* q, const void* kq, const void* vq, co
   p.part_o = sc; sc += (long long)B * H * p.nS * DEC_D;
   p.lse = sc;
   cudaStream_t s = (cudaStream_t)stream;
-  // heads of a group per CTA: the group size up to DEC_HB; larger groups use more CTAs along z
-  const int hb = gs < DEC_HB ? gs : DEC_HB;
-  if (gs % hb) return KVB_ERR_UNSUPPORTED;
-  dim3 grid(B * G, p.nS, gs / hb);
-#define KVB_DEC_LAUNCH(BITS_)                                                            \
-  switch (hb) {                                                                          \
-    case 1: decode_partial_kernel<BITS_, 1><<<grid, DEC_THREADS, 0, s>>>(p); break;      \
-    case 2: decode_partial_kernel<BITS_, 2><<<grid, DEC_THREADS, 0, s>>>(p); break;      \
-    case 4: decode_partial_kernel<BITS_, 4><<<grid, DEC_THREADS, 0, s>>>(p); break;      \
-    case 8: decode_partial_kernel<BITS_, 8><<<grid, DEC_THREADS, 0, s>>>(p); break;      \
-    default: return KVB_ERR_UNSUPPORTED;                                                 \
+  dim3 grid(B * G, p.nS, zb);
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return KVB_ERR_CUDA;
+  if (!attr_set[dev]) {
+    cudaFuncSetAttribute(decode_partial_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, dec_dyn_smem<16>());
+    cudaFuncSetAttribute(decode_partial_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, dec_dyn_smem<8>());
+    cudaFuncSetAttribute(decode_partial_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, dec_dyn_smem<4>());
+    attr_set[dev] = true;
   }
-  if (bits == 16) { KVB_DEC_LAUNCH(16) }
-  else if (bits == 8) { KVB_DEC_LAUNCH(8) }
-  else { KVB_DEC_LAUNCH(4) }
-#undef KVB_DEC_LAUNCH
+  if (bits == 16) decode_partial_kernel<16><<<grid, DEC_THREADS, dec_dyn_smem<16>(), s>>>(p);
+  else if (bits == 8) decode_partial_kernel<8><<<grid, DEC_THREADS, dec_dyn_smem<8>(), s>>>(p);
+  else decode_partial_kernel<4><<<grid, DEC_THREADS, dec_dyn_smem<4>(), s>>>(p);
   decode_merge_kernel<<<B * H, DEC_D, 0, s>>>(p);
   if (weights) {
     dim3 g2((L + 255) / 256, B * G);

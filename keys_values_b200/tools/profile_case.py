@@ -16,6 +16,7 @@ def main():
     ap.add_argument("--q", type=int, default=1024)
     ap.add_argument("--kv", type=int, default=16384)
     ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--bits", type=int, default=8, help="decode: 16 (bf16 cache), 8 or 4")
     args = ap.parse_args()
     from keys_values_b200.ops import cuda as cu
 
@@ -48,13 +49,21 @@ def main():
         for _ in range(args.iters):
             cu.gemm(a, b)
     elif args.which == "decode":
-        q = torch.randn(4, H, 1, D, device=dev, dtype=torch.bfloat16)
-        k = torch.randint(0, 255, (4, G, L, D), device=dev, dtype=torch.uint8)
-        v = torch.randint(0, 255, (4, G, L, D), device=dev, dtype=torch.uint8)
-        s = torch.rand(4, G, L, device=dev) * 0.01
-        z = torch.randint(100, 150, (4, G, L), device=dev, dtype=torch.int32)
-        for _ in range(args.iters):
-            cu.decode_attention(q, k, v, scale, L, True, quant=(s, z, s, z, 8))
+        Bd = max(args.batch, 4)
+        q = torch.randn(Bd, H, 1, D, device=dev, dtype=torch.bfloat16)
+        if args.bits == 16:
+            k = torch.randn(Bd, G, L, D, device=dev, dtype=torch.bfloat16)
+            v = torch.randn_like(k)
+            for _ in range(args.iters):
+                cu.decode_attention(q, k, v, scale, L, True)
+        else:
+            Dq = D if args.bits == 8 else D // 2
+            k = torch.randint(0, 255, (Bd, G, L, Dq), device=dev, dtype=torch.uint8)
+            v = torch.randint(0, 255, (Bd, G, L, Dq), device=dev, dtype=torch.uint8)
+            s = torch.rand(Bd, G, L, device=dev) * 0.01
+            z = torch.randint(0, 15, (Bd, G, L), device=dev, dtype=torch.int32)
+            for _ in range(args.iters):
+                cu.decode_attention(q, k, v, scale, L, True, quant=(s, z, s, z, args.bits))
     elif args.which == "allreduce":
         # one rank: the kernel runs its barrier, pull, reduce and push paths on local memory only
         import os

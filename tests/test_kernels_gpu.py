@@ -268,7 +268,8 @@ def test_sdpa_bwd(B, H, G, T, L, mode):
 
 
 @pytest.mark.parametrize("bits", [16, 8, 4])
-@pytest.mark.parametrize("B,H,G,L,C", [(1, 32, 8, 4096, 4096), (2, 8, 2, 1500, 2048), (1, 4, 4, 100, 128)])
+@pytest.mark.parametrize("B,H,G,L,C", [(1, 32, 8, 4096, 4096), (2, 8, 2, 1500, 2048), (1, 4, 4, 100, 128), (2, 14, 2, 777, 1024),
+                                       (1, 32, 2, 300, 512)])
 def test_decode_attention(bits, B, H, G, L, C):
     D = 128
     scale = 1.0 / math.sqrt(D)
