@@ -132,63 +132,63 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// One tile (16 slots) of a warp in shared memory, lane-private: every lane copies exactly the bytes
-// its own fragments are made of and reads nothing else, so no barrier is needed, only the wait
-// for its own copies. Units are stored lane-major ((unit · 32 + lane) · 16 bytes): conflict free.
-//   K: units [rowsel · UA + i], rowsel 0 = slot r, 1 = slot r + 8
-//   V: words of the four slots 2c, 2c+1, 2c+8, 2c+9 (bf16 / int8: 16-byte units; int4: 8-byte pieces)
-//   scales: ks, kz, vs, vz of the slots r and r + 8 (quantized caches)
+// One tile (16 slots) of a warp in shared memory. The 16 K rows of a tile are contiguous in the
+// cache (and so are the V rows, and each of the four scale / zero-point vectors), so the warp copies
+// them linearly: every cp.async instruction of the warp covers 512 contiguous bytes, whole 128-byte
+// lines (a copy in which each lane fetched the bytes of its own fragments touched eight half lines
+// per instruction and kept the load/store pipe busy with five times the wavefronts). The 16-byte
+// unit a lane copies is not, in general, one it will read: the destination is the place where the
+// lane that owns it in the MMA fragments looks for it, and a __syncwarp() follows the wait.
+//   K unit (row, u):  owner r = row & 7, rowsel = row >> 3, c = u & 3, i = u >> 2;
+//                     16-byte position (rowsel · UA + i) · 32 + ((r ^ i) · 4 + c)
+//   V unit (slot s, u) of bf16 / int8: owner c = (s & 7) >> 1, r = u & 7, j = u >> 3,
+//                     islot = (s & 1) + 2 (s >> 3); position (islot · J + j) · 32 + r · 4 + (c ^ (r >> 1))
+//   V of int4 (8-byte pieces, two per copied unit): byte ((islot · 4 + c) · 8 + r) · 8
+//   scales: [ks | kz | vs | vz][16 slots], one instruction of 16 lanes
+// The XOR terms spread the writes of one instruction and the reads of one fragment load evenly over
+// the banks (four wavefronts per 512 bytes, the minimum).
 template <int BITS>
 struct DecStage {
   static constexpr int UA = DecRaw<BITS>::UA, WB = DecRaw<BITS>::WB;
-  static constexpr int K_BYTES = 2 * UA * 512;
-  static constexpr int V_BYTES = 4 * WB * 4 * 32;
-  static constexpr int S_BYTES = BITS == 16 ? 0 : 8 * 4 * 32;
+  static constexpr int UR = BITS == 16 ? 16 : (BITS == 8 ? 8 : 4);  // 16-byte units per cache row
+  static constexpr int K_BYTES = 16 * UR * 16;
+  static constexpr int V_BYTES = 16 * UR * 16;
+  static constexpr int S_BYTES = BITS == 16 ? 0 : 4 * 16 * 4;
   static constexpr int BYTES = K_BYTES + V_BYTES + S_BYTES;
-  static constexpr int STAGES = BITS == 4 ? 5 : 3;  // 96 / 60 / 60 KB per CTA: two (bf16) or three CTAs per SM
+  static constexpr int STAGES = BITS == 4 ? 6 : (BITS == 8 ? 4 : 3);  // 96 / 66 / 51 KB per CTA: two or three CTAs per SM
 };
 
-// kb / vb: this lane's byte address of (first row of the split, unit c) resp. (…, unit r); row
-// offsets within a split fit 32 bits.
+// kt / vt: byte address of the first row of the split in the K / V cache (16-byte aligned).
 template <int BITS>
-__device__ __forceinline__ void dec_stage_issue(uint8_t* st, const DecParams& p, const uint8_t* kb, const uint8_t* vb,
+__device__ __forceinline__ void dec_stage_issue(uint8_t* st, const DecParams& p, const uint8_t* kt, const uint8_t* vt,
                                                 long long row0j0, int tb, int n, int lane) {
   using S = DecStage<BITS>;
-  const int r = lane >> 2, c = lane & 3;
-  constexpr int row_bytes = BITS == 16 ? 256 : (BITS == 8 ? 128 : 64);
-  const int jlo = min(tb + r, n - 1), jhi = min(tb + r + 8, n - 1);  // rows beyond the split re-read its last row
-  const uint8_t* klo = kb + (unsigned)(jlo * row_bytes);
-  const uint8_t* khi = kb + (unsigned)(jhi * row_bytes);
+  constexpr int UR = S::UR, row_bytes = UR * 16;
 #pragma unroll
-  for (int i = 0; i < S::UA; ++i) {
-    cp_async16(st + ((i * 32) + lane) * 16, klo + 64 * i);
-    cp_async16(st + (((S::UA + i) * 32) + lane) * 16, khi + 64 * i);
-  }
-  uint8_t* vst = st + S::K_BYTES;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int jv = min(tb + 2 * c + (i & 1) + 8 * (i >> 1), n - 1);
-    const uint8_t* vr = vb + (unsigned)(jv * row_bytes);
-    if (BITS == 16) {
-      cp_async16(vst + (((2 * i) * 32) + lane) * 16, vr);
-      cp_async16(vst + (((2 * i + 1) * 32) + lane) * 16, vr + 128);
-    } else if (BITS == 8) {
-      cp_async16(vst + ((i * 32) + lane) * 16, vr);
-    } else {
-      cp_async8(vst + ((i * 32) + lane) * 8, vr);
+  for (int k = 0; k < UR / 2; ++k) {
+    const int gu = k * 32 + lane;          // unit of the tile
+    const int row = gu / UR, u = gu % UR;  // slot of the tile, unit of the row
+    const unsigned src = (unsigned)(min(tb + row, n - 1) * row_bytes + u * 16);  // rows beyond the split re-read its last row
+    {
+      const int r = row & 7, rowsel = row >> 3, c = u & 3, i = u >> 2;
+      cp_async16(st + ((rowsel * S::UA + i) * 32 + ((r ^ i) * 4 + c)) * 16, kt + src);
+    }
+    {
+      const int c = (row & 7) >> 1, islot = (row & 1) + 2 * (row >> 3);
+      uint8_t* vst = st + S::K_BYTES;
+      if (BITS == 4) {
+        cp_async16(vst + ((islot * 4 + c) * 8 + 2 * u) * 8, vt + src);
+      } else {
+        const int r = u & 7, j = u >> 3;
+        cp_async16(vst + ((islot * (UR / 8) + j) * 32 + r * 4 + (c ^ (r >> 1))) * 16, vt + src);
+      }
     }
   }
-  if (BITS != 16) {
-    uint8_t* sst = st + S::K_BYTES + S::V_BYTES;
-    const long long rlo = row0j0 + jlo, rhi = row0j0 + jhi;
-    cp_async4(sst + (0 * 32 + lane) * 4, p.ks + rlo);
-    cp_async4(sst + (1 * 32 + lane) * 4, p.ks + rhi);
-    cp_async4(sst + (2 * 32 + lane) * 4, p.kz + rlo);
-    cp_async4(sst + (3 * 32 + lane) * 4, p.kz + rhi);
-    cp_async4(sst + (4 * 32 + lane) * 4, p.vs + rlo);
-    cp_async4(sst + (5 * 32 + lane) * 4, p.vs + rhi);
-    cp_async4(sst + (6 * 32 + lane) * 4, p.vz + rlo);
-    cp_async4(sst + (7 * 32 + lane) * 4, p.vz + rhi);
+  if (BITS != 16 && lane < 16) {
+    const int arr = lane >> 2, q4 = lane & 3;
+    const int slot = min(tb + 4 * q4, ((n - 1) >> 2) << 2);  // units beyond the split re-read its last one
+    const void* base = arr == 0 ? (const void*)p.ks : arr == 1 ? (const void*)p.kz : arr == 2 ? (const void*)p.vs : (const void*)p.vz;
+    cp_async16(st + S::K_BYTES + S::V_BYTES + (arr * 16 + 4 * q4) * 4, reinterpret_cast<const uint8_t*>(base) + (row0j0 + slot) * 4);
   }
 }
 
@@ -272,8 +272,8 @@ decode_partial_kernel(const DecParams p) {
   const int ha = 2 * c, hb = 2 * c + 1;                              // heads of this lane's scores and outputs
   uint8_t* wst = dec_dsm + (size_t)warp * ST::STAGES * ST::BYTES;
   constexpr int row_bytes = BITS == 16 ? 256 : (BITS == 8 ? 128 : 64);
-  const uint8_t* kb = reinterpret_cast<const uint8_t*>(p.kq) + (row0 + j0) * row_bytes + c * 16;
-  const uint8_t* vb = reinterpret_cast<const uint8_t*>(p.vq) + (row0 + j0) * row_bytes + r * (BITS == 4 ? 8 : 16);
+  const uint8_t* kb = reinterpret_cast<const uint8_t*>(p.kq) + (row0 + j0) * row_bytes;
+  const uint8_t* vb = reinterpret_cast<const uint8_t*>(p.vq) + (row0 + j0) * row_bytes;
 
   // the first tiles are requested before anything else
 #pragma unroll
@@ -321,7 +321,8 @@ decode_partial_kernel(const DecParams p) {
       const int tn = t + ST::STAGES - 1;
       if (tn < ntiles) dec_stage_issue<BITS>(wst + (tn % ST::STAGES) * ST::BYTES, p, kb, vb, row0 + j0, wbase + 16 * tn, n, lane);
       cp_async_commit();
-      cp_async_wait<ST::STAGES - 1>();  // this lane's copies of tile t have landed
+      cp_async_wait<ST::STAGES - 1>();  // this lane's copies of tile t have landed ...
+      __syncwarp();                      // ... and so have those of the other lanes
     }
     const uint8_t* st = wst + (t % ST::STAGES) * ST::BYTES;
     const int tb = wbase + 16 * t;
@@ -329,15 +330,14 @@ decode_partial_kernel(const DecParams p) {
     const bool has_new = (tb >> 4) == ns_tile;
     float kslo = 1.f, kshi = 1.f, kzlo = 0.f, kzhi = 0.f, vslo = 1.f, vshi = 1.f, vzlo = 0.f, vzhi = 0.f;
     if (BITS != 16) {
-      const uint8_t* sst = st + ST::K_BYTES + ST::V_BYTES;
-      kslo = *reinterpret_cast<const float*>(sst + (0 * 32 + lane) * 4);
-      kshi = *reinterpret_cast<const float*>(sst + (1 * 32 + lane) * 4);
-      kzlo = (float)*reinterpret_cast<const int32_t*>(sst + (2 * 32 + lane) * 4) + 1024.f;  // codes enter as 1024 + code
-      kzhi = (float)*reinterpret_cast<const int32_t*>(sst + (3 * 32 + lane) * 4) + 1024.f;
-      vslo = *reinterpret_cast<const float*>(sst + (4 * 32 + lane) * 4);
-      vshi = *reinterpret_cast<const float*>(sst + (5 * 32 + lane) * 4);
-      vzlo = (float)*reinterpret_cast<const int32_t*>(sst + (6 * 32 + lane) * 4) + 1024.f;
-      vzhi = (float)*reinterpret_cast<const int32_t*>(sst + (7 * 32 + lane) * 4) + 1024.f;
+      const float* sst = reinterpret_cast<const float*>(st + ST::K_BYTES + ST::V_BYTES);
+      const int32_t* szt = reinterpret_cast<const int32_t*>(sst);
+      if (jlo < n) {  // codes enter as 1024 + code: the offset joins the zero point
+        kslo = sst[r]; kzlo = (float)szt[16 + r] + 1024.f; vslo = sst[32 + r]; vzlo = (float)szt[48 + r] + 1024.f;
+      }
+      if (jhi < n) {
+        kshi = sst[r + 8]; kzhi = (float)szt[16 + r + 8] + 1024.f; vshi = sst[32 + r + 8]; vzhi = (float)szt[48 + r + 8] + 1024.f;
+      }
     }
     // ---- scores: d[0], [1]: slot jlo, heads ha, hb; d[2], [3]: slot jhi
     float d[4] = {0.f, 0.f, 0.f, 0.f};
@@ -345,8 +345,8 @@ decode_partial_kernel(const DecParams p) {
       uint4 ulo[ST::UA], uhi[ST::UA];
 #pragma unroll
       for (int i = 0; i < ST::UA; ++i) {
-        ulo[i] = *reinterpret_cast<const uint4*>(st + ((i * 32) + lane) * 16);
-        uhi[i] = *reinterpret_cast<const uint4*>(st + (((ST::UA + i) * 32) + lane) * 16);
+        ulo[i] = *reinterpret_cast<const uint4*>(st + ((i * 32) + ((r ^ i) * 4 + c)) * 16);
+        uhi[i] = *reinterpret_cast<const uint4*>(st + (((ST::UA + i) * 32) + ((r ^ i) * 4 + c)) * 16);
       }
       float d2[4] = {0.f, 0.f, 0.f, 0.f};  // two chains of four dependent MMAs instead of one of eight
 #pragma unroll
@@ -465,16 +465,17 @@ decode_partial_kernel(const DecParams p) {
       const uint8_t* vst = st + ST::K_BYTES;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
+        const int vpos = r * 4 + (c ^ (r >> 1));
         if (BITS == 16) {
-          const uint4 x = *reinterpret_cast<const uint4*>(vst + (((2 * i) * 32) + lane) * 16);
-          const uint4 y = *reinterpret_cast<const uint4*>(vst + (((2 * i + 1) * 32) + lane) * 16);
+          const uint4 x = *reinterpret_cast<const uint4*>(vst + (((2 * i) * 32) + vpos) * 16);
+          const uint4 y = *reinterpret_cast<const uint4*>(vst + (((2 * i + 1) * 32) + vpos) * 16);
           vw[i][0] = x.x; vw[i][1] = x.y; vw[i][2] = x.z; vw[i][3] = x.w;
           vw[i][4 % ST::WB] = y.x; vw[i][5 % ST::WB] = y.y; vw[i][6 % ST::WB] = y.z; vw[i][7 % ST::WB] = y.w;
         } else if (BITS == 8) {
-          const uint4 x = *reinterpret_cast<const uint4*>(vst + ((i * 32) + lane) * 16);
+          const uint4 x = *reinterpret_cast<const uint4*>(vst + ((i * 32) + vpos) * 16);
           vw[i][0] = x.x; vw[i][1] = x.y; vw[i][2 % ST::WB] = x.z; vw[i][3 % ST::WB] = x.w;
         } else {
-          const uint2 x = *reinterpret_cast<const uint2*>(vst + ((i * 32) + lane) * 8);
+          const uint2 x = *reinterpret_cast<const uint2*>(vst + ((i * 4 + c) * 8 + r) * 8);
           vw[i][0] = x.x; vw[i][1] = x.y;
         }
       }
@@ -611,6 +612,9 @@ extern "C" int kvb_decode_attn(const void* q, const void* kq, const void* vq, co
   if (gs > DEC_MAX_GS) return KVB_ERR_UNSUPPORTED;
   if (bits != 16 && bits != 8 && bits != 4) return KVB_ERR_ARG;
   if (bits != 16 && (!ks || !kz || !vs || !vz)) return KVB_ERR_ARG;
+  // the warp copies rows and scale vectors as 16-byte units
+  if (bits != 16 && (C & 3)) return KVB_ERR_UNSUPPORTED;
+  if (((uintptr_t)kq | (uintptr_t)vq | (uintptr_t)ks | (uintptr_t)kz | (uintptr_t)vs | (uintptr_t)vz) & 15) return KVB_ERR_UNSUPPORTED;
   DecParams p;
   p.q = (const __nv_bfloat16*)q; p.kq = kq; p.vq = vq; p.ks = ks; p.kz = kz; p.vs = vs; p.vz = vz;
   p.k_new = (const __nv_bfloat16*)k_new; p.v_new = (const __nv_bfloat16*)v_new; p.new_slot = k_new ? new_slot : nullptr;

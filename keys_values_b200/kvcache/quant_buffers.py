@@ -147,7 +147,9 @@ class QuantizedKVCacheBuffers(KVCacheBuffers):
 
     def supports_direct_decode(self) -> bool:
         qk = self.quantizer_k
-        return self._fusable() and qk.buffers_are_allocated and qk.quant_buffer.is_cuda and self.head_size == 128
+        # the decode kernel copies cache rows and scale vectors in 16-byte units
+        return (self._fusable() and qk.buffers_are_allocated and qk.quant_buffer.is_cuda and self.head_size == 128
+                and self.cache_length % 4 == 0)
 
     def decode_attention(self, query, scale, need_weights):
         """Attention of one new token straight from the quantized storage; the row
