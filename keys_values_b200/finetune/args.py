@@ -73,6 +73,8 @@ class OptimizerArgs:
     beta2: float = 0.95
     eps: float = 1e-8
     momentum: float = 0.0
+    # master weights, fp32 gradients and optimizer moments in pinned host memory (finetune_offload_*)
+    host_offload: bool = False
 
     def __post_init__(self):
         if self.name not in SUPPORTED_OPTIMIZERS:
@@ -87,6 +89,10 @@ class OptimizerArgs:
             kw.update(betas=(self.beta1, self.beta2), eps=self.eps)
         if self.name in ("SGD", "RMSprop"):
             kw.update(momentum=self.momentum)
+        if self.host_offload:
+            from keys_values_b200.optimize.host_optimizer import HostOffloadOptimizer
+
+            return HostOffloadOptimizer(params, lambda host_params: cls(host_params, **kw))
         return cls(params, **kw)
 
 

@@ -182,7 +182,7 @@ def main(rank: int, local_rank: int, world_size: int, *, checkpoint_dir, out_dir
     steps_per_epoch = max(1, len(train_loader) // accum)
     max_steps = train.max_steps or (train.epochs or 1) * steps_per_epoch
     warmup = min(max_steps, train.lr_warmup_steps or int((train.lr_warmup_fraction or 0.0) * max_steps))
-    scheduler = fu.get_lr_scheduler(opt, warmup_steps=warmup, max_steps=max_steps, min_lr=train.min_lr)
+    scheduler = fu.get_lr_scheduler(getattr(opt, "optimizer", opt), warmup_steps=warmup, max_steps=max_steps, min_lr=train.min_lr)
     state = TrainingStateVars()
     if resume_dir is not None:
         st = restore_from_training_state(resume_dir, opt, scheduler, rank, world_size)
@@ -308,7 +308,10 @@ def fit(*, model, optimizer, scheduler, train_loader, val_loader, batch_transfor
         if recorder is not None:
             recorder.stop()
         if train.max_norm is not None:
-            torch.nn.utils.clip_grad_norm_([p for p in params if p.grad is not None], train.max_norm)
+            if hasattr(optimizer, "clip_grad_norm_"):  # gradients are clipped where the optimizer lives (host)
+                optimizer.clip_grad_norm_(train.max_norm)
+            else:
+                torch.nn.utils.clip_grad_norm_([p for p in params if p.grad is not None], train.max_norm)
         optimizer.step()
         scheduler.step()
         state.step_count += 1

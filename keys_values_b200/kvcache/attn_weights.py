@@ -34,6 +34,43 @@ class AttnWeightsReplayLog(KVCacheReplayLog):
     pass
 
 
+def update_token_positions(token_positions: torch.Tensor, input_pos: int, num: int, batch_size: int, index: Optional[torch.Tensor],
+                           grace_period: int = 0, next_grace_pos: Optional[int] = None):
+    """Plain-PyTorch statement of what a cache write does to ``token_positions (bs,G,C)`` when ``num``
+    tokens from position ``input_pos`` arrive (the CUDA path writes the positions inside the cache-write
+    kernel). While the cache fills, slot = position. Once it is full the tokens go to the slots
+    ``index (batch_size,G,num)``; with a grace ring in the last ``grace_period`` slots, the
+    ``min(num, grace_period)`` oldest ring entries (positions from ``input_pos - grace_period``) move
+    to the first slots of ``index`` and the newest tokens take their place in the ring. Returns
+    ``None`` or ``(ring_slots (batch_size,G,n2), n1, prefix)`` for the grace case
+    (``keys_values/kvcache/attn_weights.py:214-317``)."""
+    bs, G, C = token_positions.shape
+    if not (1 <= batch_size <= bs and num >= 1 and input_pos >= 0):
+        raise ValueError("need 1 <= batch_size <= token_positions.shape[0], num >= 1, input_pos >= 0")
+    dev, dt = token_positions.device, token_positions.dtype
+    if input_pos < C:
+        if input_pos + num > C:
+            raise ValueError(f"input_pos + num = {input_pos + num} > cache_length {C} while the cache is filling")
+        token_positions[:batch_size, :, input_pos : input_pos + num] = torch.arange(input_pos, input_pos + num, dtype=dt, device=dev)
+        return None
+    if index is None or tuple(index.shape) != (batch_size, G, num):
+        raise ValueError(f"index must have shape {(batch_size, G, num)}")
+    result = None
+    start = input_pos
+    if grace_period > 0:
+        if next_grace_pos is None:
+            raise ValueError("next_grace_pos is needed with a grace period")
+        n2 = min(num, grace_period)
+        n1, prefix = num - n2, C - grace_period
+        ring = (torch.arange(n2, device=dev) + (next_grace_pos - prefix)) % grace_period + prefix
+        token_positions[:batch_size, :, ring] = torch.arange(input_pos + n1, input_pos + num, dtype=dt, device=dev)
+        start = input_pos - grace_period
+        result = (ring.view(1, 1, n2).expand(batch_size, G, n2), n1, prefix)
+    new = torch.arange(start, start + num, dtype=dt, device=dev).view(1, 1, num).expand(batch_size, G, num)
+    token_positions[:batch_size].scatter_(-1, index.to(torch.int64), new)
+    return result
+
+
 class AttnWeightsKVCache(KVCacheWithBuffers):
     def __init__(
         self,

@@ -64,3 +64,47 @@ class ModelFromFlatVectorsFactory:
         for (name, host_mod), (_, dev_mod) in zip(names_and_modules_for_shard(self.gpt_model, shard), clones):
             grads = AccessWeightsGradients(dev_mod).get_gradients()
             AccessWeightsGradients(host_mod).accumulate_gradients(grads)
+
+
+class GPTShardCellBlock:
+    """Device copies of the blocks of shard ``h{a}:{b}`` as one callable unit with the interface of
+    :class:`keys_values_b200.kvcache.stack_layers.CellBlocks` (``keys_values/optimize/model_factory.py:444-489``)."""
+
+    def __init__(self, gpt_model, shard: str, device):
+        m = re.fullmatch(r"h(\d+):(\d+)", shard)
+        if not m:
+            raise ValueError("shard must be a stack of layers 'h<a>:<b>'")
+        self.config = gpt_model.config
+        self._first = int(m.group(1))
+        self._factory = ModelFromFlatVectorsFactory(gpt_model, device)
+        self._shard = shard
+        self._clones = self._factory.create(shard)
+
+    @property
+    def first_layer_idx(self) -> int:
+        return self._first
+
+    @property
+    def num_layers(self) -> int:
+        return len(self._clones)
+
+    def blocks(self) -> List[torch.nn.Module]:
+        return [mod for _, mod in self._clones]
+
+    def assign_kv_caches(self, caches) -> None:
+        for b, c in zip(self.blocks(), caches):
+            b.attn.kv_cache = c
+
+    def get_kv_caches(self) -> List:
+        return [b.attn.kv_cache for b in self.blocks()]
+
+    def forward(self, x: torch.Tensor, idx: torch.Tensor, mha, chunk_sizes=None) -> torch.Tensor:
+        for b in self.blocks():
+            x = b(x, idx, mha, chunk_sizes=chunk_sizes)
+        return x
+
+    __call__ = forward
+
+    def return_gradients(self) -> None:
+        """Accumulate the gradients of the copies into the host model."""
+        self._factory.return_gradients(self._shard, self._clones)

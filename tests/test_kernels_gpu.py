@@ -347,3 +347,31 @@ def test_ce_loss_kernels(dtype, V):
     tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
     assert _rel_err(logits.grad, lf.grad) < tol
     assert loss[3] == 0 and logits.grad[3].abs().max() == 0
+
+
+def test_verification_api_and_host_optimizer_on_gpu():
+    """The user-facing equivalence check (kernels against the fp32 restatement) and the host-resident
+    optimizer with pinned staging on a GPU."""
+    from keys_values_b200.attention.verification import verify_backend_equivalence, verify_backend_equivalence_batch
+    from keys_values_b200.optimize.host_optimizer import HostOffloadOptimizer
+
+    D = 128
+    scale = 1.0 / math.sqrt(D)
+    mk = lambda *s: torch.randn(*s, device=DEV, dtype=torch.bfloat16)  # noqa: E731
+    cases = [
+        dict(query=mk(1, 8, 64, D), key=mk(1, 2, 512, D), value=mk(1, 2, 512, D), scale_factor=scale, input_pos=448, return_attn_weights=True),
+        dict(query=mk(2, 8, 1, D), key=mk(2, 2, 300, D), value=mk(2, 2, 300, D), scale_factor=scale, input_pos=299, return_attn_weights=True),
+    ]
+    passed, failed, results = verify_backend_equivalence_batch(cases, log_results=False)
+    assert (passed, failed) == (2, 0) and all(r.weights_max_diff is not None for r in results)
+    bad = verify_backend_equivalence(**cases[0], rtol=0.0, atol=0.0, log_results=False)
+    assert not bad and bad.output_max_diff > 0
+    w = torch.nn.Parameter(torch.ones(1000, device=DEV, dtype=torch.bfloat16))
+    opt = HostOffloadOptimizer([w], lambda ps: torch.optim.AdamW(ps, lr=1e-2, weight_decay=0.0))
+    assert opt.host_params[0].is_pinned()
+    for _ in range(3):
+        opt.zero_grad()
+        w.grad = torch.ones_like(w)
+        opt.step()
+    torch.cuda.synchronize()
+    assert abs(float(w.detach()[0]) - 0.97) < 5e-3 and abs(float(opt.host_params[0].detach()[0]) - 0.97) < 1e-4

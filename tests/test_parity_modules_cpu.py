@@ -1,0 +1,188 @@
+"""Modules that mirror smaller parts of the reference: host-resident optimizer, evaluation loaders,
+sequence-classification dataset, token-position update, trackers and debug helpers, shard copies."""
+import copy
+
+import pytest
+import torch
+
+from keys_values_b200.config import Config
+from keys_values_b200.models.model import GPT
+
+
+def _tiny():
+    torch.manual_seed(0)
+    cfg = Config.from_name("tiny-qwen3")
+    m = GPT(cfg)
+    m.apply(m._init_weights)
+    return cfg, m
+
+
+def test_host_offload_optimizer_matches_plain_adamw():
+    from keys_values_b200.finetune.args import OptimizerArgs
+
+    torch.manual_seed(0)
+    net_a = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.Tanh(), torch.nn.Linear(32, 4))
+    net_b = copy.deepcopy(net_a)
+    opt_a = OptimizerArgs(learning_rate=1e-2, weight_decay=0.1).create(list(net_a.parameters()))
+    opt_b = OptimizerArgs(learning_rate=1e-2, weight_decay=0.1, host_offload=True).create(list(net_b.parameters()))
+    assert type(opt_b).__name__ == "HostOffloadOptimizer" and opt_b.param_groups[0]["lr"] == 1e-2
+    for step in range(4):
+        x = torch.randn(8, 16)
+        for net, opt in ((net_a, opt_a), (net_b, opt_b)):
+            opt.zero_grad(set_to_none=True)
+            net(x).square().mean().backward()
+            if step == 2:
+                if hasattr(opt, "clip_grad_norm_"):
+                    opt.clip_grad_norm_(0.05)
+                else:
+                    torch.nn.utils.clip_grad_norm_(net.parameters(), 0.05)
+            opt.step()
+    for pa, pb in zip(net_a.parameters(), net_b.parameters()):
+        torch.testing.assert_close(pa, pb, atol=1e-6, rtol=1e-5)
+    # the state round-trips through the checkpoint interface
+    st = opt_b.state_dict()
+    opt_b.load_state_dict(st)
+    assert opt_b.host_bytes() > 0
+
+
+def test_host_offload_optimizer_keeps_fp32_master_for_bf16_weights():
+    from keys_values_b200.optimize.host_optimizer import HostOffloadOptimizer
+
+    w = torch.nn.Parameter(torch.ones(64, dtype=torch.bfloat16))
+    opt = HostOffloadOptimizer([w], lambda ps: torch.optim.SGD(ps, lr=1e-3))
+    for _ in range(10):  # ten updates of 1e-3 · 0.25: each is below bf16 resolution at 1.0, their sum is not
+        opt.zero_grad()
+        w.grad = torch.full_like(w, 0.25)
+        opt.step()
+    assert abs(float(opt.host_params[0].detach()[0]) - (1 - 10 * 2.5e-4)) < 1e-6
+    assert float(w.detach()[0]) < 1.0  # the accumulated change reached the bf16 copy
+
+
+def test_evaluation_loader_orders_tasks_and_lengths():
+    from keys_values_b200.data.constants import ORIG_IDX_NAME, TASK_NAME
+    from keys_values_b200.data.evaluation import EvaluationDataLoader, SimilarSequenceLengthWithTasksSampler
+
+    lengths = [50, 10, 40, 20, 30]
+    sampler = SimilarSequenceLengthWithTasksSampler(lengths, micro_batch_size=2, num_tasks=2)
+    assert len(sampler) == 6 and sampler.batch_size == 2
+    dataset = [{"x": i} for i in range(5)] + [{"__pad__": True}]
+    loader = EvaluationDataLoader(dataset, sampler, lambda items: {"items": items}, ["ckpt_a", "ckpt_b"], delay_tokenization=True)
+    jobs = list(loader)
+    assert [j[TASK_NAME] for j in jobs] == ["ckpt_a"] * 3 + ["ckpt_b"] * 3
+    assert [j[ORIG_IDX_NAME] for j in jobs[:3]] == [[1, 3], [4, 2], [0, 5]]  # shortest first, pad entry last
+    assert "items" not in jobs[0]
+    full = iter(loader).fetch_full(jobs[1])
+    assert [it["x"] for it in full["items"]] == [4, 2]
+    with pytest.raises(ValueError):
+        list(EvaluationDataLoader(dataset[:5], sampler, lambda x: x, ["a", "b"]))
+
+
+def test_sequence_classification_dataset_and_collate():
+    from keys_values_b200.data.sequence_classification import SequenceClassificationDataset, get_seq_class_collate_fn
+
+    class Tok:
+        def encode(self, text, bos=False, eos=False, max_length=-1):
+            ids = [ord(ch) % 50 for ch in text] + ([1] if eos else [])
+            return torch.tensor(ids[:max_length] if max_length > 0 else ids)
+
+    data = [dict(instruction="abc", output="yes"), dict(instruction="defgh", output="no"), {"__pad__": True}]
+    ds = SequenceClassificationDataset(data, Tok(), None, ["no", "yes"])
+    assert ds[0]["labels"] == 1 and ds[1]["labels"] == 0 and ds[0]["input_ids"].tolist()[-1] == 1
+    assert ds[0]["token_counts"] == {"raw_plus_prompt_template": 4, "raw": 4}
+    batch = get_seq_class_collate_fn(pad_id=0)([ds[0], ds[1], ds[2]])
+    assert batch["input_ids"].shape == (2, 6) and batch["labels"].tolist() == [1, 0]
+    with pytest.raises(ValueError):
+        SequenceClassificationDataset([dict(instruction="a", output="maybe")], Tok(), None, ["no", "yes"])
+    with pytest.raises(ValueError):
+        SequenceClassificationDataset([{"__pad__": True}, dict(instruction="a", output="no")], Tok(), None, ["no", "yes"])
+
+
+def test_update_token_positions_matches_cache_state():
+    from keys_values_b200.kvcache.attn_weights import update_token_positions
+
+    tp = torch.zeros(2, 2, 8, dtype=torch.int32)
+    assert update_token_positions(tp, 0, 8, 2, None) is None
+    assert tp[1, 1].tolist() == list(range(8))
+    index = torch.tensor([[[3, 5], [0, 1]], [[7, 6], [2, 4]]], dtype=torch.int32)
+    update_token_positions(tp, 8, 2, 2, index)
+    assert tp[0, 0].tolist() == [0, 1, 2, 8, 4, 9, 6, 7] and tp[1, 1].tolist() == [0, 1, 10 - 2, 3, 9, 5, 6, 7]
+    # grace ring of 2 slots (6, 7): the oldest ring entry moves to the evicted slot, the new token takes its place
+    tp = torch.arange(8, dtype=torch.int32).view(1, 1, 8).repeat(1, 1, 1)
+    ring, n1, prefix = update_token_positions(tp, 8, 1, 1, torch.tensor([[[2]]], dtype=torch.int32), grace_period=2, next_grace_pos=6)
+    assert (n1, prefix) == (0, 6) and ring.tolist() == [[[6]]]
+    assert tp[0, 0].tolist() == [0, 1, 6, 3, 4, 5, 8, 7]
+
+
+def test_tracker_and_debug_utils(tmp_path):
+    from keys_values_b200.tools import debug_utils as du
+    from keys_values_b200.tools import tracker
+
+    x = torch.randn(100)
+    assert tracker.track(x) is x  # disarmed
+    f = tmp_path / "bad.pt"
+    tracker.initialize_weights_tracker(str(f), threshold=50.0)
+    try:
+        assert tracker.track(x, "fine") is x
+        y = x.clone()
+        y[3] = float("nan")
+        tracker.set_message_postfix("layer 3")
+        with pytest.raises(AssertionError, match="1 of 100 entries are NaN: here: layer 3"):
+            tracker.track(y, "here")
+        assert torch.isnan(torch.load(f)[3])
+        with pytest.raises(AssertionError, match=r"\|elem\| > 50"):
+            tracker.track(x * 1e4)
+        lin = torch.nn.Linear(4, 4)
+        tracker.set_message_postfix(None)
+        tracker.track_weights(lin, "after step")
+    finally:
+        tracker.initialize_weights_tracker(None)
+    v = torch.arange(101, dtype=torch.float32)
+    for q in (0.0, 0.01, 0.5, 0.9, 1.0):
+        torch.testing.assert_close(du.torch_quantile(v, q), torch.quantile(v, q))
+    m = torch.randn(7, 33)
+    torch.testing.assert_close(du.torch_quantile(m, 0.3, dim=1), torch.quantile(m, 0.3, dim=1))
+    assert du.size_quantiles(v).count("|") == 3 and du.for_debug(v).device.type == "cpu"
+    du.debug_compare_dicts({"a": v}, {"a": v.clone()})
+    with pytest.raises(AssertionError):
+        du.debug_compare_dicts({"a": v}, {"a": v + 1})
+    with pytest.raises(ValueError):
+        du.debug_compare_dicts({"a": v}, {"b": v})
+
+
+def test_shard_cell_block_and_replay_logs():
+    from keys_values_b200.kvcache.factory import KVCacheFactory
+    from keys_values_b200.kvcache.gradient import get_replay_logs
+    from keys_values_b200.optimize.grad_accumulate import DistributedPrimitives
+    from keys_values_b200.optimize.model_factory import GPTShardCellBlock
+
+    cfg, m = _tiny()
+    shard = GPTShardCellBlock(m, "h0:2", "cpu")
+    assert (shard.first_layer_idx, shard.num_layers) == (0, 2)
+    x = torch.randn(1, 6, cfg.n_embd, requires_grad=True)
+    idx = torch.randint(0, cfg.vocab_size, (1, 6))
+    y = shard(x, idx, m.mha)
+    y_ref = x
+    for b in m.transformer.h:
+        y_ref = b(y_ref, idx, m.mha)
+    torch.testing.assert_close(y, y_ref)
+    y.sum().backward()
+    shard.return_gradients()
+    assert all(p.grad is not None for p in m.transformer.h[1].parameters())
+    with pytest.raises(ValueError):
+        GPTShardCellBlock(m, "wte", "cpu")
+    caches = KVCacheFactory.create(m, "h2o-default", 1, 16, dtype=torch.float32, cache_kwargs=dict(max_chunk_size=4))
+    m.assign_kv_caches(caches)
+    with pytest.raises(IndexError):
+        get_replay_logs(m)
+    for c in caches:
+        c.switch_replay_logging(True)
+    m.max_seq_length = 64
+    with torch.no_grad():
+        m(torch.randint(0, cfg.vocab_size, (1, 16)))
+        m(torch.randint(0, cfg.vocab_size, (1, 4)))
+    logs = get_replay_logs(m)
+    assert len(logs) == cfg.n_layer and all(log is not None for log in logs)
+    assert DistributedPrimitives.world_size() == 1 and DistributedPrimitives.rank() == 0
+    t = torch.ones(3)
+    DistributedPrimitives.all_reduce_mean(t)
+    assert t.tolist() == [1, 1, 1]
