@@ -37,10 +37,17 @@ def store_eval_metrics(path: Path, rows: List[Dict[str, Any]]) -> None:
         w.writerows(rows)
 
 
-def store_generated_samples(path: Path, prompts: List[str], generated: List[str]) -> None:
+GENERATED_SAMPLES_FILENAME = "generated_samples_{}.yaml"
+
+
+def store_generated_samples(path: Path, references: List[str], generated: List[str], scores: Optional[List[float]] = None) -> None:
+    """One YAML document per sample: reference answer, generated text and (if given) its score."""
     with open(path, "w") as fp:
-        for p, g in zip(prompts, generated):
-            fp.write(yaml.safe_dump({"prompt_tail": p[-400:], "generated": g}) + "---\n")
+        for i, (r, g) in enumerate(zip(references, generated)):
+            doc = {"reference": r, "generated": g}
+            if scores is not None:
+                doc["score"] = float(scores[i])
+            fp.write(yaml.safe_dump(doc) + "---\n")
 
 
 def setup(out_dir: Union[str, Path], checkpoints: Optional[List[str]] = None, data=None, kv_cache: Optional[KVCacheArgs] = None,
@@ -77,7 +84,12 @@ def main(rank: int, local_rank: int, world_size: int, *, out_dir, checkpoints, d
     transform = BatchTransformFactory.from_head_model(head_name)
     if data is None:
         raise ValueError("eval_long_ext needs a data module (--data …)")
-    data.connect(batch_size=batch_size, num_devices=1, rank=0)
+    tokenizer = None
+    if (base_dir / "tokenizer.json").is_file() or (base_dir / "tokenizer.model").is_file():
+        from keys_values_b200.tokenizer import Tokenizer
+
+        tokenizer = Tokenizer(base_dir)
+    data.connect(tokenizer=tokenizer, batch_size=batch_size, num_devices=1, rank=0)
     data.setup()
     loader = data.val_dataloader()
     current, model = None, None
@@ -104,6 +116,19 @@ def main(rank: int, local_rank: int, world_size: int, *, out_dir, checkpoints, d
                     loss = model(tb["input_ids"].to(device), tb["targets"].to(device))
                 rows = [{"task": task.key, "batch": b_idx, "row": i, "loss": float(l), "num_tokens": int(tb["input_ids"].shape[1]),
                          "time": time.perf_counter() - t0} for i, l in enumerate(loss.float().view(-1))]
+                if eval.sample_metric is not None and tokenizer is not None:
+                    # generated answers of this batch, scored (keys_values/evaluation/longcontext_eval_ext.py:671-841)
+                    from keys_values_b200.evaluation.evaluator import SampleBasedMetricsEvaluator, split_prompts_and_references
+
+                    prompts, refs = split_prompts_and_references(batch, tokenizer, getattr(tokenizer, "pad_id", None) or 0)
+                    gpt.reset()
+                    gpt.max_seq_length = prompts.shape[1] + (eval.max_new_tokens or 64)
+                    res = SampleBasedMetricsEvaluator(gpt, tokenizer, eval.sample_metric, eval.max_new_tokens or 64, kv.chunk_size)(
+                        prompts.to(device), refs)
+                    for row, sc in zip(rows, res["scores"]):
+                        row[eval.sample_metric] = sc
+                    store_generated_samples(helper.task_dir(task) / GENERATED_SAMPLES_FILENAME.format(b_idx), [r[0] for r in refs],
+                                            res["generated"], res["scores"])
                 store_eval_metrics(helper.result_path(task, b_idx), rows)
                 done = True
             finally:

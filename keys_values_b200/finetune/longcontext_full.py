@@ -200,7 +200,7 @@ def main(rank: int, local_rank: int, world_size: int, *, checkpoint_dir, out_dir
     fit(model=model, optimizer=opt, scheduler=scheduler, train_loader=train_loader, val_loader=val_loader, batch_transform=batch_transform,
         train=train, eval=eval, state=state, max_steps=max_steps, accum=accum, device=device, rank=rank, world_size=world_size,
         grad_reducer=grad_reducer, logger=logger, out_dir=out_dir, checkpoint_dir=Path(checkpoint_dir), lora=lora is not None,
-        hparams=hparams, profile_grad_times=profile_grad_times, record_gpu_memory_snapshots=record_gpu_memory_snapshots)
+        hparams=hparams, profile_grad_times=profile_grad_times, record_gpu_memory_snapshots=record_gpu_memory_snapshots, tokenizer=tokenizer)
     if rank == 0:
         final = out_dir / "final"
         fu.save_model_checkpoint(gpt_model, head_model, final, lora=lora is not None)
@@ -231,12 +231,33 @@ def validate(model: LongContextGradientModel, val_loader, batch_transform, devic
     return torch.stack(losses).mean() if losses else torch.tensor(float("nan"), device=device)
 
 
-def validate_and_all_reduce(model, val_loader, batch_transform, device, eval: EvalArgs, world_size: int) -> Dict[str, float]:
+def validate_sample_metric(model, val_loader, tokenizer, device, eval: EvalArgs, world_size: int) -> Dict[str, float]:
+    """Generate answers for validation batches and score them (``eval.sample_metric``)
+    (``keys_values/finetune/longcontext_full.py:1880-1903``)."""
+    from keys_values_b200.evaluation.evaluator import sample_metric_on_loader
+
+    gpt = model.gpt_model
+    width = gpt.max_seq_length
+    try:
+        res = sample_metric_on_loader(gpt, tokenizer, val_loader, eval.sample_metric, device, eval.sample_metric_max_batches,
+                                      eval.max_new_tokens or 64, model.chunk_size, getattr(tokenizer, "pad_id", None) or 0)
+    finally:
+        gpt.reset()
+        gpt.max_seq_length = width
+    mean = _all_reduce_mean(torch.tensor(res["mean"], device=device), world_size)
+    return {f"val_{eval.sample_metric}": float(mean)}
+
+
+def validate_and_all_reduce(model, val_loader, batch_transform, device, eval: EvalArgs, world_size: int, tokenizer=None) -> Dict[str, float]:
     t0 = time.perf_counter()
     val_loss = validate(model, val_loader, batch_transform, device, eval.max_iters)
     val_loss = _all_reduce_mean(val_loss.to(device), world_size)
     v = float(val_loss)
-    return {"val_loss": v, "val_ppl": math.exp(v) if v < 50 else float("inf"), "val_time": time.perf_counter() - t0}
+    metrics = {"val_loss": v, "val_ppl": math.exp(v) if v < 50 else float("inf")}
+    if eval.sample_metric is not None and tokenizer is not None:
+        metrics.update(validate_sample_metric(model, val_loader, tokenizer, device, eval, world_size))
+    metrics["val_time"] = time.perf_counter() - t0
+    return metrics
 
 
 def save_checkpoint_regular(model: LongContextGradientModel, out_dir: Path, step: int, checkpoint_dir: Path, lora: bool, hparams, rank: int,
@@ -258,11 +279,11 @@ def save_checkpoint_regular(model: LongContextGradientModel, out_dir: Path, step
 
 def fit(*, model, optimizer, scheduler, train_loader, val_loader, batch_transform, train: TrainArgs, eval: EvalArgs, state: TrainingStateVars,
         max_steps: int, accum: int, device, rank: int, world_size: int, grad_reducer, logger, out_dir: Path, checkpoint_dir: Path, lora: bool,
-        hparams, profile_grad_times: int = 0, record_gpu_memory_snapshots: Optional[int] = None) -> None:
+        hparams, profile_grad_times: int = 0, record_gpu_memory_snapshots: Optional[int] = None, tokenizer=None) -> None:
     ts_manager = TrainingStateManager(out_dir, rank, world_size)
     train_iter = CycleIterator(train_loader)
     if eval.initial_validation:
-        metrics = validate_and_all_reduce(model, val_loader, batch_transform, device, eval, world_size)
+        metrics = validate_and_all_reduce(model, val_loader, batch_transform, device, eval, world_size, tokenizer)
         if rank == 0:
             print(f"initial validation: {metrics}")
             logger.log_dict(metrics, step=state.step_count)
@@ -336,7 +357,7 @@ def fit(*, model, optimizer, scheduler, train_loader, val_loader, batch_transfor
                     w.writerows(recs)
             return
         if eval.interval and state.step_count % eval.interval == 0:
-            metrics = validate_and_all_reduce(model, val_loader, batch_transform, device, eval, world_size)
+            metrics = validate_and_all_reduce(model, val_loader, batch_transform, device, eval, world_size, tokenizer)
             if rank == 0:
                 logger.log_dict(metrics, step=state.step_count)
                 print(f"validation: {metrics}")
@@ -349,7 +370,7 @@ def fit(*, model, optimizer, scheduler, train_loader, val_loader, batch_transfor
             if world_size > 1:
                 dist.barrier()
     if eval.final_validation:
-        metrics = validate_and_all_reduce(model, val_loader, batch_transform, device, eval, world_size)
+        metrics = validate_and_all_reduce(model, val_loader, batch_transform, device, eval, world_size, tokenizer)
         if rank == 0:
             logger.log_dict(metrics, step=state.step_count)
             print(f"final validation: {metrics}")

@@ -33,7 +33,7 @@ def main():
                     except ValueError as ex:
                         health.mark_failed(repr(ex))
                 os._exit(0)  # leaves between steps: nothing of this rank is in flight
-            health.enter_step(step, grace_s=2.0)  # host rendezvous before this step's collectives
+            health.enter_step(step, grace_s=8.0)  # host rendezvous before this step's collectives
             dist.all_reduce(x)
         print("NOT DETECTED", flush=True)
     except RankFailure as ex:

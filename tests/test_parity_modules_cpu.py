@@ -186,3 +186,30 @@ def test_shard_cell_block_and_replay_logs():
     t = torch.ones(3)
     DistributedPrimitives.all_reduce_mean(t)
     assert t.tolist() == [1, 1, 1]
+
+
+def test_sample_metric_on_loader_generates_and_scores():
+    from keys_values_b200.evaluation.evaluator import sample_metric_on_loader, split_prompts_and_references
+    from keys_values_b200.kvcache.factory import KVCacheFactory
+
+    class Tok:
+        eos_id, pad_id = 1, 0
+
+        def decode(self, ids):
+            return " ".join(str(int(i)) for i in ids)
+
+    cfg, m = _tiny()
+    m.eval()
+    ids = torch.tensor([[5, 6, 7, 8, 9, 1, 0, 0], [11, 12, 13, 14, 15, 16, 17, 1]])
+    labels = torch.full_like(ids, -100)
+    labels[0, 4:6] = ids[0, 4:6]
+    labels[1, 6:8] = ids[1, 6:8]
+    batch = {"input_ids": ids, "labels": labels}
+    prompts, refs = split_prompts_and_references(batch, Tok())
+    assert prompts.tolist() == [[0, 0, 5, 6, 7, 8], [11, 12, 13, 14, 15, 16]] and refs == [["9"], ["17"]]
+    m.assign_kv_caches(KVCacheFactory.create(m, "dense-default", 2, 32, dtype=torch.float32))
+    seen = []
+    res = sample_metric_on_loader(m, Tok(), [batch, batch], "exact_match", torch.device("cpu"), max_batches=1, max_new_tokens=3,
+                                  prompt_chunksize=4, on_batch=lambda k, r: seen.append((k, r["generated"], r["references"])))
+    assert res["num_samples"] == 2 and 0.0 <= res["mean"] <= 1.0
+    assert len(seen) == 1 and len(seen[0][1]) == 2 and seen[0][2] == ["9", "17"]
