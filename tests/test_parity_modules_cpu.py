@@ -213,3 +213,104 @@ def test_sample_metric_on_loader_generates_and_scores():
                                   prompt_chunksize=4, on_batch=lambda k, r: seen.append((k, r["generated"], r["references"])))
     assert res["num_samples"] == 2 and 0.0 <= res["mean"] <= 1.0
     assert len(seen) == 1 and len(seen[0][1]) == 2 and seen[0][2] == ["9", "17"]
+
+
+def test_merge_lora_and_peft_import(tmp_path):
+    import yaml
+
+    from keys_values_b200.finetune.utils import LIT_MODEL_FNAME, load_model_checkpoint, save_model_checkpoint
+    from keys_values_b200.models import lora as lora_mod
+    from keys_values_b200.tools import merge_lora
+
+    base_cfg = Config.from_name("tiny-gpt")
+    torch.manual_seed(0)
+    base = GPT(base_cfg)
+    base.apply(base._init_weights)
+    base_dir = tmp_path / "base"
+    base_dir.mkdir()
+    base_cfg.save(base_dir / "model_config.yaml")
+    torch.save({"model": base.state_dict()}, base_dir / LIT_MODEL_FNAME)
+    largs = dict(r=4, alpha=8, dropout=0.0, query=True, key=False, value=True, projection=True, mlp=False, head=False)
+    lcfg = lora_mod.Config.from_checkpoint(base_dir, lora_r=4, lora_alpha=8, lora_query=True, lora_value=True, lora_projection=True)
+    lm = lora_mod.GPT(lcfg)
+    load_model_checkpoint(lm, base_dir)
+    for n, p in lm.named_parameters():
+        if "lora_" in n:
+            torch.nn.init.normal_(p, std=0.05)
+    fin = tmp_path / "out" / "final"
+    save_model_checkpoint(lm, None, fin, lora=True)
+    (fin / "hyperparameters.yaml").write_text(yaml.safe_dump({"lora": largs}))
+    ids = torch.randint(0, base_cfg.vocab_size, (1, 12))
+    lm.eval()
+    with torch.no_grad():
+        want = lm(ids)
+    merged_dir = merge_lora.merge(fin, base_dir)
+    plain = GPT(Config.from_checkpoint(merged_dir))
+    load_model_checkpoint(plain, merged_dir)
+    plain.eval()
+    with torch.no_grad():
+        torch.testing.assert_close(plain(ids), want, atol=1e-5, rtol=1e-4)
+    with torch.no_grad():
+        assert float((plain(ids) - base.eval()(ids)).abs().max()) > 1e-4  # the adapter did change the model
+
+    # PEFT layout → fused qkv adapters: same tensors, stacked in q, v order
+    qkv = lm.transformer.h[0].attn.qkv
+    r = 4
+    A, B = qkv.lora_A.detach(), qkv.lora_B.detach()
+    q_out = base_cfg.n_head * base_cfg.head_size
+    peft = {
+        "base_model.model.model.layers.0.self_attn.q_proj.lora_A.weight": A[:r], "base_model.model.model.layers.0.self_attn.q_proj.lora_B.weight": B[:q_out],
+        "base_model.model.model.layers.0.self_attn.v_proj.lora_A.default.weight": A[r:], "base_model.model.model.layers.0.self_attn.v_proj.lora_B.default.weight": B[q_out:],
+        "base_model.model.model.layers.0.self_attn.o_proj.lora_A.weight": lm.transformer.h[0].attn.proj.lora_A.detach(),
+        "base_model.model.model.layers.0.self_attn.o_proj.lora_B.weight": lm.transformer.h[0].attn.proj.lora_B.detach(),
+    }
+    sd = merge_lora.peft_to_lora_state_dict(peft, ("q_proj", "v_proj"))
+    torch.testing.assert_close(sd["transformer.h.0.attn.qkv.lora_A"], A)
+    torch.testing.assert_close(sd["transformer.h.0.attn.qkv.lora_B"], B)
+    assert "transformer.h.0.attn.proj.lora_B" in sd
+    with pytest.raises(ValueError):
+        merge_lora.peft_to_lora_state_dict(peft, ("q_proj", "k_proj", "v_proj"))
+
+
+def test_experiment_files_and_token_counts(tmp_path):
+    import csv
+
+    import yaml
+
+    from keys_values_b200.tools import dataset_token_counts as dtc
+    from keys_values_b200.tools import experiment_files as ef
+
+    ev = tmp_path / "run" / "h2o-default__final" / "eval"
+    ev.mkdir(parents=True)
+    for b, (loss, score) in enumerate(((2.0, 1.0), (4.0, 0.0))):
+        with open(ev / f"eval_metrics_{b}.csv", "w", newline="") as fp:
+            w = csv.DictWriter(fp, fieldnames=["task", "batch", "row", "loss", "num_tokens", "time", "exact_match"])
+            w.writeheader()
+            w.writerow(dict(task="h2o-default__final", batch=b, row=0, loss=loss, num_tokens=100 * (b + 1), time=1.5, exact_match=score))
+        (ev / f"generated_samples_{b}.yaml").write_text(yaml.safe_dump({"reference": "a b", "generated": "a b c d", "score": score}) + "---\n")
+    (ev / "batch_7.lock").write_text("123")
+    run = tmp_path / "run"
+    table = ef.result_table(run)
+    assert len(table) == 1 and abs(table[0]["loss"] - (2 * 100 + 4 * 200) / 300) < 1e-9 and table[0]["exact_match"] == 0.5 and table[0]["time"] == 3.0
+    assert (run / ef.METRICS_ALL).is_file()
+    assert ef.collect_gen_samples(run) == {"h2o-default__final": 2}
+    stats = ef.sample_stats(run)
+    assert stats[0]["samples"] == 2 and stats[0]["length_ratio_mean"] == 2.0 and stats[0]["score_mean"] == 0.5
+    assert ef.cleanup_evaluation(run) == 1 and not (ev / "batch_7.lock").exists() and (ev / "eval_metrics_0.csv").exists()
+    assert ef.cleanup_gen_samples(run) == 2 and (ev / ef.SAMPLES_ALL).exists()
+    (run / "metrics.csv").write_text("step,loss,val_loss\n1,3.0,\n2,2.5,2.75\n4,2.0,2.5\n")
+    assert ef.collect_val_loss(run) == {2: 2.75, 4: 2.5} and (run / "val_losses.yaml").is_file()
+    step = run / "step-000002"
+    step.mkdir()
+    for name in ("lit_model.lora.pth", "tokenizer.json", "training_state.pt"):
+        (step / name).write_text("x")
+    assert ef.strip_checkpoints(run) == 2 and (step / "lit_model.lora.pth").exists()
+    jl = tmp_path / "evaluation.jsonl"
+    jl.write_text('{"answer": "x", "prediction": "y z"}\n')
+    assert ef.convert_samples(jl, tmp_path / "s.yaml") == 1 and "y z" in (tmp_path / "s.yaml").read_text()
+    ef.main(["result-table", str(run)])
+    # token counts
+    data = tmp_path / "d.jsonl"
+    data.write_text('{"instruction": "a b c", "output": "d"}\n{"instruction": "a", "output": "b"}\n')
+    counts = dtc.token_counts(dtc.load_records(data), lambda s: s.split(), ["instruction", "output"])
+    assert counts == [4, 2] and dtc.summarize(counts)["max"] == 4
