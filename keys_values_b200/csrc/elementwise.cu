@@ -212,6 +212,79 @@ rmsnorm_bwd_bf16_kernel(const __nv_bfloat16* __restrict__ gy, const __nv_bfloat1
   }
 }
 
+// Few rows (single-token decode steps: rows = batch size): one CTA per row, so that a row is spread
+// over 8 warps and the loads of x, the residual and the weight are all in flight before the one
+// block-wide reduction; the warp-per-row kernel above serialises three memory round trips on a
+// handful of warps. dim is a multiple of 256 and at most 256 · 8 · RMS_ROW_UNITS.
+constexpr int RMS_ROW_THREADS = 256;
+constexpr int RMS_ROW_UNITS = 3;
+__global__ void __launch_bounds__(RMS_ROW_THREADS)
+rmsnorm_fwd_fewrows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                           const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ sum_out,
+                           float* __restrict__ rstd, int dim, float eps, int unit) {
+  __shared__ float red[RMS_ROW_THREADS / 32];
+  const long long base = (long long)blockIdx.x * dim;
+  const int units = dim / 8, tid = threadIdx.x;
+  uint4 v[RMS_ROW_UNITS], rv[RMS_ROW_UNITS], wv[RMS_ROW_UNITS];
+#pragma unroll
+  for (int c = 0; c < RMS_ROW_UNITS; ++c) {
+    const int u = tid + c * RMS_ROW_THREADS;
+    v[c] = rv[c] = wv[c] = make_uint4(0, 0, 0, 0);
+    if (u < units) {
+      v[c] = *reinterpret_cast<const uint4*>(x + base + u * 8);
+      if (res) rv[c] = *reinterpret_cast<const uint4*>(res + base + u * 8);
+      if (w) wv[c] = *reinterpret_cast<const uint4*>(w + u * 8);
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < RMS_ROW_UNITS; ++c) {
+    __nv_bfloat162* a = reinterpret_cast<__nv_bfloat162*>(&v[c]);
+    const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&rv[c]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 f = __bfloat1622float2(a[j]);
+      if (res) {
+        const float2 fb = __bfloat1622float2(b[j]);
+        a[j] = __floats2bfloat162_rn(f.x + fb.x, f.y + fb.y);  // the sum as the next layer will read it
+        f = __bfloat1622float2(a[j]);
+      }
+      ss += f.x * f.x + f.y * f.y;
+    }
+    const int u = tid + c * RMS_ROW_THREADS;
+    if (res && u < units) *reinterpret_cast<uint4*>(sum_out + base + u * 8) = v[c];
+  }
+  ss = warp_sum(ss);
+  if ((tid & 31) == 0) red[tid >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < RMS_ROW_THREADS / 32; ++i) tot += red[i];
+  const float r = rsqrtf(tot / dim + eps);
+  if (tid == 0 && rstd) rstd[blockIdx.x] = r;
+#pragma unroll
+  for (int c = 0; c < RMS_ROW_UNITS; ++c) {
+    const int u = tid + c * RMS_ROW_THREADS;
+    if (u >= units) continue;
+    __nv_bfloat162* a = reinterpret_cast<__nv_bfloat162*>(&v[c]);
+    const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&wv[c]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 f = __bfloat1622float2(a[j]);
+      f.x *= r;
+      f.y *= r;
+      if (w) {
+        float2 ww = __bfloat1622float2(b[j]);
+        if (unit) { ww.x += 1.f; ww.y += 1.f; }
+        f.x *= ww.x;
+        f.y *= ww.y;
+      }
+      a[j] = __floats2bfloat162_rn(f.x, f.y);
+    }
+    *reinterpret_cast<uint4*>(y + base + u * 8) = v[c];
+  }
+}
+
 #define KVB_RMS_DISPATCH(NCV, ...)                                  \
   switch (NCV) {                                                    \
     case 4: { constexpr int NC = 4; __VA_ARGS__; break; }           \
@@ -592,6 +665,12 @@ extern "C" int kvb_add_rmsnorm_fwd(const void* x, const void* res, const void* w
                                    long long rows, int dim, float eps, int add_unit_offset, void* stream) {
   if (rows <= 0 || dim <= 0 || ((res == nullptr) != (sum_out == nullptr))) return KVB_ERR_ARG;
   if (!rms_fast_dim(dim)) return KVB_ERR_UNSUPPORTED;
+  if (rows <= 64 && dim <= 256 * 8 * RMS_ROW_UNITS) {
+    rmsnorm_fwd_fewrows_kernel<<<(unsigned)rows, RMS_ROW_THREADS, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, (__nv_bfloat16*)sum_out, rstd,
+        dim, eps, add_unit_offset);
+    return check_launch();
+  }
   const unsigned grid = (unsigned)((rows + EW_WARPS - 1) / EW_WARPS);
   KVB_RMS_DISPATCH(dim / 256, (rmsnorm_fwd_bf16_kernel<NC><<<grid, EW_WARPS * 32, 0, (cudaStream_t)stream>>>(
                                   (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w, (__nv_bfloat16*)y,

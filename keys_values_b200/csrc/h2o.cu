@@ -17,6 +17,7 @@ namespace kvb {
 
 constexpr int H2O_THREADS = 1024;
 constexpr int H2O_MAX_K = 4096;
+constexpr int H2O_SMALL_K = 32;  // up to here the slots are found by repeated block-wide minima
 
 __device__ __forceinline__ uint32_t ordered_key(float f) {
   uint32_t u = __float_as_uint(f);
@@ -64,6 +65,41 @@ h2o_update_kernel(float* __restrict__ scores, const float* __restrict__ weights,
   }
   __syncthreads();
 
+  // 2a) few slots (the selection after a single-token step): k block-wide minima of (key, index),
+  //     each removed before the next; the same order as the general path (ascending key, ties by index)
+  if (k_select <= H2O_SMALL_K) {
+    __shared__ unsigned long long wmin[H2O_THREADS / 32];
+    int32_t* out = out_idx + ((long long)b * G + g) * k_select;
+    for (int it = 0; it < k_select; ++it) {
+      unsigned long long best = ~0ull;
+      for (int j = tid; j < n_evict; j += H2O_THREADS) {
+        const unsigned long long cand = ((unsigned long long)keys[j] << 32) | (unsigned)j;
+        best = cand < best ? cand : best;
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+        best = other < best ? other : best;
+      }
+      if ((tid & 31) == 0) wmin[tid >> 5] = best;
+      __syncthreads();
+      if (tid < 32) {
+        unsigned long long v = wmin[tid];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const unsigned long long other = __shfl_xor_sync(0xffffffffu, v, o);
+          v = other < v ? other : v;
+        }
+        if (tid == 0) {
+          const int idx = (int)(v & 0xffffffffu);
+          out[it] = idx;
+          keys[idx] = 0xFFFFFFFFu;  // scores are finite, so no live key has this value: the slot is out of the race
+        }
+      }
+      __syncthreads();
+    }
+    return;
+  }
   // 2) radix select: find the k-th smallest key exactly
   uint32_t mask = 0;
   for (int pass = 0; pass < 4; ++pass) {

@@ -140,7 +140,8 @@ def test_cache_write(bits):
     _cuda().check_status(DEV)
 
 
-@pytest.mark.parametrize("C,k,normalize", [(512, 64, False), (16384, 1024, False), (1000, 100, True)])
+@pytest.mark.parametrize("C,k,normalize", [(512, 64, False), (16384, 1024, False), (1000, 100, True), (16384, 8, False), (777, 1, True),
+                                           (4096, 32, True)])
 def test_h2o_update(C, k, normalize):
     B, G = 2, 4
     scores = torch.rand(B, G, C, device=DEV)
@@ -296,14 +297,13 @@ def test_decode_attention(bits, B, H, G, L, C):
     torch.testing.assert_close(w, w_r, atol=1e-3, rtol=2e-2)
 
 
-@pytest.mark.parametrize("dim", [1024, 2560, 3072])
-def test_add_rmsnorm_fused(dim):
+@pytest.mark.parametrize("dim,rows", [(1024, 777), (2560, 777), (3072, 777), (4096, 4), (2560, 1), (5120, 64)])
+def test_add_rmsnorm_fused(dim, rows):
     """s = x + res; y = rmsnorm(s): one kernel forward, one kernel backward (with the gradient of
     the residual path added in the same pass), against the fp32 restatement."""
     from keys_values_b200 import ops
 
     torch.manual_seed(0)
-    rows = 777
     x = torch.randn(rows, dim, device=DEV, dtype=torch.bfloat16, requires_grad=True)
     r = torch.randn(rows, dim, device=DEV, dtype=torch.bfloat16, requires_grad=True)
     w = (torch.randn(dim, device=DEV) * 0.1 + 1).to(torch.bfloat16)
