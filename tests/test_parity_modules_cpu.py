@@ -314,3 +314,31 @@ def test_experiment_files_and_token_counts(tmp_path):
     data.write_text('{"instruction": "a b c", "output": "d"}\n{"instruction": "a", "output": "b"}\n')
     counts = dtc.token_counts(dtc.load_records(data), lambda s: s.split(), ["instruction", "output"])
     assert counts == [4, 2] and dtc.summarize(counts)["max"] == 4
+
+
+def test_kvcache_test_utils():
+    from keys_values_b200.attention.base import DefaultKeysAndValues
+    from keys_values_b200.kvcache import test_utils as tu
+    from keys_values_b200.kvcache.base import KVCacheParams
+
+    params = KVCacheParams(max_batch_size=2, n_query_groups=2, cache_length=16, head_size=8, n_head=4, dtype=torch.float32)
+    cache = tu.create_kv_cache("h2o-default", params, max_chunk_size=4)
+    log = tu.record_forward_calls(cache)
+    args = tu.random_args_cache_forward(params, 20, vocab_size=50)
+    out0 = cache(**tu.range_from_args(args, 0, 16))
+    out1 = cache(**tu.range_from_args(args, 16, 20))
+    assert out0.shape == (2, 16, 32) and out1.shape == (2, 4, 32)
+    assert [c.inputs.input_pos for c in log] == [0, 16] and log[1].token_positions.shape == (2, 2, 16)
+    idx = tu.random_index(params, 4, 12, 5)
+    assert idx.shape == (2, 2, 5) and int(idx.min()) >= 4 and int(idx.max()) < 12
+    assert all(len(set(r.tolist())) == 5 for r in idx.view(-1, 5))
+    q, (k, v) = tu.random_tensor(params, 3, is_query=True), tu.random_keys_values(params, 10)
+    w = tu.compute_attn_weights(q, DefaultKeysAndValues(k, v))
+    assert w.shape == (2, 2, 10) and torch.allclose(w.sum(-1), torch.full((2, 2), 3.0), atol=1e-4)
+    m = tu.attention_mask_forward(3, 5, torch.float32)
+    assert m.shape == (1, 1, 3, 5) and float(m[0, 0, 0, 3]) < -1e30 and float(m[0, 0, 2, 4]) == 0.0 and tu.attention_mask_forward(1, 5, torch.float32) is None
+    assert tu.tensor_is_simple(q) and not tu.tensor_is_simple(q[:, :1].expand(2, 4, 3, 8))
+    names = tu.cache_names_and_devices(["h2o-default", "dense-bnb-quantized8"])
+    assert ("h2o-default", torch.device("cpu")) in names and all("bnb" not in n or tu.have_bitsandbytes() for n, _ in names)
+    tok = tu.MockTokenizer()
+    assert tok.encode(tu.sequence_of_words(5), eos=True).tolist()[-1] == tok.eos_id and len(tu.product_with_devices([1, 2], ["a"])) >= 2
