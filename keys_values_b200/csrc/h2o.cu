@@ -44,18 +44,53 @@ h2o_update_kernel(float* __restrict__ scores, const float* __restrict__ weights,
   const int tid = threadIdx.x;
   if (pos_ptr) input_pos = *pos_ptr + 1;  // device-resident position of the token just written; scores are aged to the next one
 
-  // 1) accumulate and build selection keys
-  for (int j = tid; j < C; j += H2O_THREADS) {
-    const float s = sc[j] + (w ? w[j] : 0.f);
-    sc[j] = s;
-    if (j < n_evict) {
-      float sel = s;
-      if (normalize) {
-        int t = tp[j];
-        if (t < prefill_length - 1) t = prefill_length - 1;
-        sel = __fdiv_rn(s, (float)(input_pos - t));
+  // 1) accumulate and build selection keys. Only B·G CTAs run, so the pass is bound by the latency of
+  //    its loads: with 16-byte accesses all of a row's scores and weights are requested in one or two
+  //    rounds (4 x 4 slots per thread and round).
+  auto key_of = [&](float s, int j, int t) {
+    float sel = s;
+    if (normalize) {
+      if (t < prefill_length - 1) t = prefill_length - 1;
+      sel = __fdiv_rn(s, (float)(input_pos - t));
+    }
+    keys[j] = ordered_key(sel);
+  };
+  const bool vec = (C & 3) == 0 && ((reinterpret_cast<uintptr_t>(sc) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(tp)) & 15) == 0;
+  if (vec) {
+    constexpr int UB = 4;
+    const int nv = C >> 2;
+    for (int q0 = tid; q0 < nv; q0 += UB * H2O_THREADS) {
+      float4 sv[UB], wv[UB];
+      int4 tv[UB];
+#pragma unroll
+      for (int u = 0; u < UB; ++u) {
+        const int q = q0 + u * H2O_THREADS;
+        sv[u] = wv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        tv[u] = make_int4(0, 0, 0, 0);
+        if (q < nv) {
+          sv[u] = reinterpret_cast<const float4*>(sc)[q];
+          if (w) wv[u] = reinterpret_cast<const float4*>(w)[q];
+          if (normalize && 4 * q < n_evict) tv[u] = reinterpret_cast<const int4*>(tp)[q];
+        }
       }
-      keys[j] = ordered_key(sel);
+#pragma unroll
+      for (int u = 0; u < UB; ++u) {
+        const int q = q0 + u * H2O_THREADS;
+        if (q >= nv) break;
+        const float4 s4 = make_float4(sv[u].x + wv[u].x, sv[u].y + wv[u].y, sv[u].z + wv[u].z, sv[u].w + wv[u].w);
+        if (w) reinterpret_cast<float4*>(sc)[q] = s4;
+        const int j = 4 * q;
+        if (j < n_evict) key_of(s4.x, j, tv[u].x);
+        if (j + 1 < n_evict) key_of(s4.y, j + 1, tv[u].y);
+        if (j + 2 < n_evict) key_of(s4.z, j + 2, tv[u].z);
+        if (j + 3 < n_evict) key_of(s4.w, j + 3, tv[u].w);
+      }
+    }
+  } else {
+    for (int j = tid; j < C; j += H2O_THREADS) {
+      const float s = sc[j] + (w ? w[j] : 0.f);
+      if (w) sc[j] = s;
+      if (j < n_evict) key_of(s, j, normalize ? tp[j] : 0);
     }
   }
   if (tid == 0) {
@@ -69,13 +104,21 @@ h2o_update_kernel(float* __restrict__ scores, const float* __restrict__ weights,
   //     each removed before the next; the same order as the general path (ascending key, ties by index)
   if (k_select <= H2O_SMALL_K) {
     __shared__ unsigned long long wmin[H2O_THREADS / 32];
+    __shared__ unsigned long long chosen;
     int32_t* out = out_idx + ((long long)b * G + g) * k_select;
-    for (int it = 0; it < k_select; ++it) {
+    // every thread keeps the minimum of its own slots (j = tid, tid + 1024, ...); after a slot has
+    // been taken only its owner scans again
+    auto scan = [&]() {
       unsigned long long best = ~0ull;
       for (int j = tid; j < n_evict; j += H2O_THREADS) {
         const unsigned long long cand = ((unsigned long long)keys[j] << 32) | (unsigned)j;
         best = cand < best ? cand : best;
       }
+      return best;
+    };
+    unsigned long long mine = scan();
+    for (int it = 0; it < k_select; ++it) {
+      unsigned long long best = mine;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) {
         const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
@@ -91,12 +134,14 @@ h2o_update_kernel(float* __restrict__ scores, const float* __restrict__ weights,
           v = other < v ? other : v;
         }
         if (tid == 0) {
+          chosen = v;
           const int idx = (int)(v & 0xffffffffu);
           out[it] = idx;
           keys[idx] = 0xFFFFFFFFu;  // scores are finite, so no live key has this value: the slot is out of the race
         }
       }
       __syncthreads();
+      if ((int)(chosen & 0xffffffffu) % H2O_THREADS == tid) mine = scan();
     }
     return;
   }
