@@ -118,6 +118,8 @@ class KVCacheWithBuffers(DefaultKVCache):
             input_pos=self.input_pos, current_length=self.current_length, batch_size=self.batch_size,
             token_pos=self.token_positions().clone(),
         )
+        if getattr(self, "next_grace_pos", None) is not None:
+            snap["next_grace_pos"] = int(self.next_grace_pos)  # oldest entry of the grace ring
         if hasattr(self.kv_buffers, "snapshot"):
             snap["quantized"] = self.kv_buffers.snapshot()
             snap["num_bits"] = self.kv_buffers.num_bits

@@ -49,9 +49,11 @@ class ReplayState:
         self.current_length = 0
         self.input_pos = 0
         self.cache_length = cache_length
+        self.next_grace_pos: Optional[int] = None  # oldest entry of the grace ring (caches with a grace period)
 
     def restore(self, snap: Optional[Dict[str, Any]]) -> None:
         """Load the state at the left edge of a cell (``None`` = empty cache)."""
+        self.next_grace_pos = None if snap is None else snap.get("next_grace_pos")
         if snap is None:
             self.current_length = 0
             self.input_pos = 0
@@ -82,10 +84,26 @@ class CacheWriteSDPA(torch.autograd.Function):
     """One replay step: write ``key/value`` at ``slots``, attend with ``query``."""
 
     @staticmethod
-    def forward(ctx, query, key, value, token, state: ReplayState, slots, new_length: int, scale: float, sliding_window, softcap, saved=None):
+    def forward(ctx, query, key, value, token, state: ReplayState, slots, new_length: int, scale: float, sliding_window, softcap, saved=None,
+                move=None):
+        """``move = (src (B,G,n2), dst (B,G,n2), first_pos, next_grace_pos_after)``: grace ring of a full cache.
+        Before the chunk is written, the rows in the ring slots ``src`` (the oldest ring entries, token
+        positions from ``first_pos``) are copied to the evicted slots ``dst``; the chunk's last ``n2``
+        tokens then take the ring slots (``slots`` already says so). The copy is undone in ``backward``,
+        where the gradient collected by a copy returns to the ring slot its row came from."""
         B, G, n, D = key.shape
         old_length = state.current_length
         input_pos = state.input_pos
+        moved = None
+        if move is not None:
+            src, dst, first_pos, ngp_after = move
+            src4, dst4 = src.unsqueeze(-1).expand(-1, -1, -1, D), dst.unsqueeze(-1).expand(-1, -1, -1, D)
+            moved = (src, dst, state.k_buf.gather(2, dst4), state.v_buf.gather(2, dst4), state.token_pos.gather(2, dst), state.next_grace_pos)
+            state.k_buf.scatter_(2, dst4, state.k_buf.gather(2, src4))
+            state.v_buf.scatter_(2, dst4, state.v_buf.gather(2, src4))
+            pos = torch.arange(first_pos, first_pos + src.shape[2], dtype=torch.int32, device=src.device)
+            state.token_pos.scatter_(2, dst, pos.view(1, 1, -1).expand_as(dst).contiguous())
+            state.next_grace_pos = ngp_after
         fused = (state.k_buf.is_cuda and state.dk_buf.is_contiguous() and state.token_pos.is_contiguous()
                  and _cu.replay_supported(state.k_buf, key) and state.k_buf.shape[0] == B)
         if fused:
@@ -115,6 +133,7 @@ class CacheWriteSDPA(torch.autograd.Function):
         ctx.state = state
         ctx.meta = (input_pos, old_length, new_length, scale, sliding_window, softcap, key.dtype)
         ctx.fused = fused
+        ctx.moved = moved
         return out, token.clone()
 
     @staticmethod
@@ -143,9 +162,20 @@ class CacheWriteSDPA(torch.autograd.Function):
             state.k_buf.scatter_(2, idx4, old_k)
             state.v_buf.scatter_(2, idx4, old_v)
             state.token_pos.scatter_(2, idx, old_tp)
+        if ctx.moved is not None:
+            # undo the copy ring -> evicted slots: what the copies collected belongs to the rows in the ring
+            src, dst, old_k2, old_v2, old_tp2, ngp_before = ctx.moved
+            src4, dst4 = src.unsqueeze(-1).expand(-1, -1, -1, D), dst.unsqueeze(-1).expand(-1, -1, -1, D)
+            for buf in (state.dk_buf, state.dv_buf):
+                buf.scatter_add_(2, src4, buf.gather(2, dst4))
+                buf.scatter_(2, dst4, 0.0)
+            state.k_buf.scatter_(2, dst4, old_k2)
+            state.v_buf.scatter_(2, dst4, old_v2)
+            state.token_pos.scatter_(2, dst, old_tp2)
+            state.next_grace_pos = ngp_before
         state.current_length = old_length
         state.input_pos = input_pos
-        return dq.to(query.dtype), dk_new.to(kv_dtype), dv_new.to(kv_dtype), grad_token, None, None, None, None, None, None, None
+        return dq.to(query.dtype), dk_new.to(kv_dtype), dv_new.to(kv_dtype), grad_token, None, None, None, None, None, None, None, None
 
 
 class TrainingReplayCache(torch.nn.Module):
@@ -153,9 +183,8 @@ class TrainingReplayCache(torch.nn.Module):
     Follows the slot decisions of ``replay_log``; no scores are computed."""
 
     def __init__(self, state: ReplayState, replay_log: KVCacheReplayLog, mha, block_idx: int, n_head: int, saved=None):
-        if getattr(replay_log, "grace_period", 0):
-            raise NotImplementedError("gradient computation with grace_period > 0 is not supported")
         super().__init__()
+        self.grace_period = int(getattr(replay_log, "grace_period", 0) or 0)
         self.state = state
         self.replay_log = replay_log
         self.mha = mha
@@ -183,16 +212,32 @@ class TrainingReplayCache(torch.nn.Module):
         if log.token_chunks[self._chunk_idx] != n:
             raise ValueError(f"chunk {self._chunk_idx} has {log.token_chunks[self._chunk_idx]} tokens in the replay log, got {n}")
         slots = log.slot_positions[self._chunk_idx]
-        if slots is None:  # prefill
+        g, C = self.grace_period, self.cache_length
+        is_prefill = slots is None
+        if is_prefill:
             B = key.shape[0]
+            st.next_grace_pos = C - g if g > 0 else None
             slots = torch.arange(n, dtype=torch.int32, device=key.device).view(1, 1, n).expand(B, self.n_query_groups, n)
             new_length = n
         else:
             new_length = min(self.cache_length, max(st.current_length, st.current_length + n if st.current_length < self.cache_length else 0))
         self._chunk_idx += 1
+        move = None
+        if g > 0 and not is_prefill and st.current_length == C:
+            # full cache with a grace ring (keys_values/kvcache/attn_weights.py:637-783): the logged slots are
+            # those of the evicted entries; the oldest ring entries move there, the newest tokens enter the ring
+            if st.next_grace_pos is None:
+                raise RuntimeError("the KV checkpoint of this cell does not carry the position of the grace ring")
+            prefix, n2 = C - g, min(n, g)
+            ring = ((torch.arange(n2, device=key.device) + (st.next_grace_pos - prefix)) % g + prefix)
+            ring = ring.view(1, 1, n2).expand(key.shape[0], self.n_query_groups, n2)
+            index = slots.to(torch.int64)
+            ngp_after = st.next_grace_pos if n > g else (st.next_grace_pos - prefix + n) % g + prefix
+            move = (ring.contiguous(), index[:, :, :n2].contiguous(), st.input_pos - g, ngp_after)
+            slots = torch.cat((index[:, :, n2:], ring), dim=-1).to(torch.int32)
         out, self.token = CacheWriteSDPA.apply(
             query, key, value, self.token, st, slots, new_length,
             self.mha.pos_encoding.sdpa_scale_factor(), self.mha.sliding_window(self.block_idx),
-            self.mha.config.attention_logit_softcapping, self.saved,
+            self.mha.config.attention_logit_softcapping, self.saved, move,
         )
         return out

@@ -206,3 +206,61 @@ def test_dora_forward_matches_definition():
     y0 = lin(x)
     lin.merge()
     torch.testing.assert_close(lin(x), y0, atol=1e-5, rtol=1e-5)
+
+
+@pytest.mark.parametrize("chunk", [8, 24])
+def test_gradients_with_grace_period(chunk, monkeypatch):
+    """Score-based cache with a grace ring (the newest tokens cannot be evicted): the replay moves the
+    oldest ring entries to the evicted slots as the forward pass did. Multi-cell equals single-cell, the
+    training pass equals the inference pass, and the gradient agrees with finite differences in fp64."""
+    import keys_values_b200.kvcache.h2o as h2o_mod
+
+    # The slots to evict are chosen by age instead of by score, so that the decisions do not depend on
+    # the weights and finite differences are a valid oracle (the gradient treats decisions as constants).
+    def oldest_first(scores, weights, k_select, n_evictable, normalize=False, token_pos=None, input_pos=0, prefill_length=0, out=None):
+        if weights is not None:
+            scores += weights
+        return torch.argsort(token_pos[:, :, :n_evictable], dim=-1)[:, :, :k_select].to(torch.int32)
+
+    monkeypatch.setattr(h2o_mod.ops, "h2o_update", oldest_first)
+    torch.manual_seed(0)
+    cfg = lora_mod.Config.from_name("tiny-gpt", lora_r=4, lora_alpha=8, lora_query=True, lora_value=True)
+    m = lora_mod.GPT(cfg)
+    m.apply(m._init_weights)
+    for n, p in m.named_parameters():
+        if "lora_B" in n:
+            torch.nn.init.normal_(p, std=0.05)
+    lora_mod.mark_only_lora_as_trainable(m)
+    m = m.double()
+    head = CrossEntropyOnLogits(cfg)
+    ids, tg = torch.randint(0, 512, (2, 150)), torch.randint(0, 512, (2, 40))
+    kw = dict(max_chunk_size=chunk, grace_period=12)  # chunks shorter and longer than the ring
+    m.assign_kv_caches(KVCacheFactory.create(m, "h2o-default", 2, 48, dtype=torch.float64, cache_kwargs=kw))
+    res = []
+    for mult, layers in ((1.0, 1), (100.0, 2)):
+        gm = LongContextGradientModel(m, head, layers_per_cell=layers, chunk_size=chunk, chunks_per_cell_multiplier=mult)
+        gm.train()
+        loss = gm(ids, tg)
+        loss.backward()
+        res.append((loss.item(), _grads(m), len(gm.cells)))
+    assert res[0][2] > 2 and res[1][2] == 1 and abs(res[0][0] - res[1][0]) < 1e-9
+    for k in res[0][1]:
+        torch.testing.assert_close(res[0][1][k], res[1][1][k], atol=1e-9, rtol=1e-7)
+    gm.eval()
+    with torch.no_grad():
+        assert abs(float(gm(ids, tg).mean()) - res[0][0]) < 1e-9
+    # central differences along a random direction in two parameters (the slot decisions are not differentiated)
+    names = [n for n in res[0][1] if "lora_B" in n][:2]
+    params = dict(m.named_parameters())
+    for n in names:
+        d = torch.randn_like(params[n])
+        eps = 1e-3  # the loss comes back in fp32
+        vals = []
+        for sgn in (1.0, -1.0):
+            with torch.no_grad():
+                params[n].add_(sgn * eps * d)
+                vals.append(float(gm(ids, tg).mean()))
+                params[n].sub_(sgn * eps * d)
+        fd = (vals[0] - vals[1]) / (2 * eps)
+        an = float((res[0][1][n] * d).sum())
+        assert abs(fd - an) <= 5e-3 * abs(an) + 2e-4, (n, fd, an)
