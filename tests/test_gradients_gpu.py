@@ -58,3 +58,27 @@ def test_chunked_gradients_match_whole_sequence_autograd(cache_name, save_attn, 
     num = sum(((g1[k] - g2[k]) ** 2).sum() for k in g1) ** 0.5
     den = sum((g2[k] ** 2).sum() for k in g1) ** 0.5
     assert float(num / den) < (0.12 if quant else 0.05), float(num / den)
+
+
+def test_grace_period_gradients_multi_cell_equal_single_cell_on_gpu():
+    """The grace-ring move of the replay on the GPU (fused write kernels around plain gather/scatter
+    moves): gradients do not depend on how the sequence is cut into cells."""
+    dev, dtype = torch.device("cuda", 0), torch.bfloat16
+    cfg, m = _model(dev, dtype)
+    head = CrossEntropyOnLogits(cfg)
+    ids = torch.randint(0, cfg.vocab_size, (1, 900), device=dev)
+    tg = torch.randint(0, cfg.vocab_size, (1, 128), device=dev)
+    m.assign_kv_caches(KVCacheFactory.create(m, "h2o-default", 1, 256, dtype=dtype, device=dev,
+                                             cache_kwargs=dict(max_chunk_size=64, grace_period=40)))
+    res = []
+    for mult in (1.0, 100.0):
+        gm = LongContextGradientModel(m, head, layers_per_cell=1, chunk_size=64, chunks_per_cell_multiplier=mult)
+        gm.train()
+        loss = gm(ids, tg)
+        loss.backward()
+        res.append((float(loss.value), _grads(m), len(gm.cells)))
+    assert res[0][2] > res[1][2] == 1
+    assert abs(res[0][0] - res[1][0]) < 2e-2
+    num = sum(((res[0][1][k] - res[1][1][k]) ** 2).sum() for k in res[0][1]) ** 0.5
+    den = sum((res[1][1][k] ** 2).sum() for k in res[0][1]) ** 0.5
+    assert float(num / den) < 0.1, float(num / den)
