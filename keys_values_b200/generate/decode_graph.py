@@ -94,13 +94,11 @@ class DecodeGraph:
     def step(self, tokens: torch.Tensor) -> torch.Tensor:
         model = self.model
         input_pos = model.get_kv_caches()[0].input_pos
+        if input_pos + 1 > model.max_seq_length:
+            raise ValueError(f"Cannot forward sequence: input_pos {input_pos} + 1 > max_seq_length {model.max_seq_length}")
         if self.graph is None:
-            if input_pos + 1 > model.max_seq_length:
-                raise ValueError(f"Cannot forward sequence: input_pos {input_pos} + 1 > max_seq_length {model.max_seq_length}")
-            self._capture(tokens)
+            self._capture(tokens)  # moves the host counters on, like every eager call
         else:
-            if input_pos + 1 > model.max_seq_length:
-                raise ValueError(f"Cannot forward sequence: input_pos {input_pos} + 1 > max_seq_length {model.max_seq_length}")
             self.tokens.copy_(tokens)
             self._advance_host()
         self.graph.replay()
