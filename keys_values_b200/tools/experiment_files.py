@@ -33,8 +33,8 @@ import yaml
 SAMPLES_GLOB = "generated_samples_[0-9]*.yaml"
 SAMPLES_ALL = "generated_samples_all.yaml"
 METRICS_ALL = "eval_metrics_all.csv"
-REMOVABLE_FROM_CHECKPOINTS = ("tokenizer.json", "tokenizer_config.json", "tokenizer.model", "generation_config.json", "training_state.pt",
-                              "optimizer.pt")
+REMOVABLE_FROM_CHECKPOINTS = ("tokenizer.json", "tokenizer_config.json", "tokenizer.model", "generation_config.json", "training_state.pth",
+                              "training_state.pt", "optimizer.pt")
 
 
 def _task_dirs(out_dir: Path, eval_dir: str) -> List[Path]:

@@ -112,6 +112,29 @@ def test_cli_finetune_lora_then_resume_then_eval(tmp_path):
     assert "step 3/3" in r.stdout and "step 1/3" not in r.stdout
 
 
+def test_cli_finetune_offload_lora_with_host_optimizer(tmp_path):
+    """``finetune_offload_lora``: optimizer state and fp32 master weights on the host, checkpoints offloaded,
+    gradient clipping done where the optimizer lives; the run resumes from its training state."""
+    from keys_values_b200.config import Config
+
+    ckpt = tmp_path / "ckpt"
+    ckpt.mkdir()
+    Config.from_name("tiny-gpt").save(ckpt / "model_config.yaml")
+    out = tmp_path / "out"
+    common = [str(ckpt), "--out_dir", str(out), "--precision", "32-true", "--kv_cache.name", "h2o-default", "--kv_cache.cache_length", "64",
+              "--kv_cache.chunk_size", "16", "--lora.r", "4", "--train.global_batch_size", "1", "--train.micro_batch_size", "1",
+              "--train.save_interval", "2", "--train.lr_warmup_steps", "1", "--train.max_norm", "0.5", "--eval.interval", "2",
+              "--eval.max_iters", "1", "--yarn_rope", "false"]
+    r = _run_cli(["finetune_offload_lora", *common, "--train.max_steps", "2"], tmp_path)
+    assert r.returncode == 0, r.stdout + r.stderr
+    hp = (out / "final" / "hyperparameters.yaml").read_text()
+    assert "host_offload: true" in hp and "offload_checkpoints: true" in hp
+    assert (out / "step-000002" / "training_state.pth").is_file()
+    r = _run_cli(["finetune_offload_lora", *common, "--train.max_steps", "3", "--resume", "auto"], tmp_path)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "step 3/3" in r.stdout
+
+
 def test_evaluation_lock_grid(tmp_path):
     from keys_values_b200.evaluation.tasks import EvaluationTasks, EvaluationWithTasksHelper
 
