@@ -135,7 +135,8 @@ class AttnWeightsKVCache(KVCacheWithBuffers):
         for name in self._score_buffer_names():
             t = self._scores.get(name)
             if t is None or t.device != torch.device(device):
-                self._scores[name] = torch.zeros(shape, dtype=torch.float32, device=device)
+                with torch.inference_mode(False):
+                    self._scores[name] = torch.zeros(shape, dtype=torch.float32, device=device)
             else:
                 t.zero_()
 

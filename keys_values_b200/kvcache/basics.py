@@ -52,7 +52,8 @@ class KVCacheWithBuffers(DefaultKVCache):
 
     def _alloc_token_pos(self, device) -> None:
         if self.token_pos is None or self.token_pos.device != torch.device(device):
-            self.token_pos = torch.zeros((self.max_batch_size, self.n_query_groups, self.cache_length), dtype=torch.int32, device=device)
+            with torch.inference_mode(False):
+                self.token_pos = torch.zeros((self.max_batch_size, self.n_query_groups, self.cache_length), dtype=torch.int32, device=device)
 
     def token_positions(self) -> torch.Tensor:
         return self.token_pos[: self.batch_size, :, : self.current_length]

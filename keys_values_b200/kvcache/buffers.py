@@ -134,8 +134,9 @@ class DefaultKVCacheBuffers(KVCacheBuffers):
         if self.k is None or self.k.device != torch.device(device) or self.k.dtype != dtype:
             p = self.params
             shape = (p.max_batch_size, p.n_query_groups, self.cache_length, p.head_size)
-            self.k = torch.zeros(shape, device=device, dtype=dtype)
-            self.v = torch.zeros(shape, device=device, dtype=dtype)
+            with torch.inference_mode(False):  # persistent state: usable in training passes after a generation
+                self.k = torch.zeros(shape, device=device, dtype=dtype)
+                self.v = torch.zeros(shape, device=device, dtype=dtype)
             self.params = KVCacheBuffersParams(p.max_batch_size, p.n_query_groups, p.head_size, dtype, torch.device(device))
 
     def deallocate(self) -> None:

@@ -66,7 +66,8 @@ class H2OKVCache(AttnWeightsKVCache):
         if out is None or out.device != self.scores.device:
             if not hasattr(self, "_select_out"):
                 self._select_out = {}
-            out = self._select_out[key] = torch.empty((B, self.n_query_groups, k), dtype=torch.int32, device=self.scores.device)
+            with torch.inference_mode(False):
+                out = self._select_out[key] = torch.empty((B, self.n_query_groups, k), dtype=torch.int32, device=self.scores.device)
         return ops.h2o_update(
             self.scores[:B], attn_weights, k, self.cache_length - self.grace_period,
             normalize=self.normalize_scores, token_pos=self.token_pos[:B],

@@ -42,8 +42,9 @@ class DequantizedKVCacheBuffers:
         p = self.params
         if self.k is None or self.k.device != torch.device(device) or self.k.dtype != dtype:
             shape = (p.max_batch_size, p.n_query_groups, self.cache_length, p.head_size)
-            self.k = torch.empty(shape, device=device, dtype=dtype)
-            self.v = torch.empty(shape, device=device, dtype=dtype)
+            with torch.inference_mode(False):  # persistent state: usable in training passes after a generation
+                self.k = torch.empty(shape, device=device, dtype=dtype)
+                self.v = torch.empty(shape, device=device, dtype=dtype)
             self.owner = None
 
     def deallocate(self) -> None:

@@ -56,10 +56,11 @@ class TorchBasicQuantizer(Quantizer):
             return
         B, G, C, _ = self.shape
         self._device = device
-        self.quant_buffer = torch.zeros((B, G, C, self._last_dim()), dtype=torch.uint8, device=device)
         meta_shape = (B, C) if self.blocks_over_heads else (B, G, C)
-        self.quant_scales = torch.ones(meta_shape, dtype=torch.float32, device=device)
-        self.quant_zero_points = torch.zeros(meta_shape, dtype=torch.int32, device=device)
+        with torch.inference_mode(False):  # persistent state: usable in training passes after a generation
+            self.quant_buffer = torch.zeros((B, G, C, self._last_dim()), dtype=torch.uint8, device=device)
+            self.quant_scales = torch.ones(meta_shape, dtype=torch.float32, device=device)
+            self.quant_zero_points = torch.zeros(meta_shape, dtype=torch.int32, device=device)
 
     def deallocate(self) -> None:
         self.quant_buffer = self.quant_scales = self.quant_zero_points = None

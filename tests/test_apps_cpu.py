@@ -206,3 +206,15 @@ def test_tools_and_flat_vectors(tmp_path):
     assert log.log(0)["grad_norm"] > 0
     lim = TemporaryArrayLimit(4.0)
     assert lim() == 4.0 and lim.reduce() == 3.0 and lim.reduce() == 2.0
+
+
+def test_grpo_example_runs_after_generation_in_inference_mode():
+    """The example samples completions (inference mode) and then differentiates through the same caches:
+    persistent cache state must not be made of inference tensors."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("grpo_demo", ROOT / "examples" / "grpo_long_context_demo.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    reward = mod.main(["--steps", "2"])
+    assert 0.0 <= reward <= 1.0
