@@ -211,6 +211,8 @@ def main():
         from baseline.reference_arm import run_reference
 
         out = run_reference(args)
+        if int(os.environ.get("RANK", "0")) != 0:
+            out = {}  # one line per job: rank 0 prints it
     else:
         out = run_b200(args)
     if out:
