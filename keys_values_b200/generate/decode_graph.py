@@ -4,7 +4,8 @@ A decode step of a 32-layer model is some six hundred small launches (five GEMMs
 cache write, the split-KV attention, the score update and slot selection per layer): the host needs
 longer to issue them than the GPU to run them. Once every cache is full, nothing in such a step
 depends on the host any more except the position of the token: the slot to overwrite comes from
-the previous step's selection (a device buffer), all shapes are constant. The position is therefore
+the previous step's selection (a device buffer; H2O) or follows from the position (last-recent ring), all
+shapes are constant. The position is therefore
 kept in a device word (``ops.cuda.device_position``): the cache write, the score normalisation and
 the RoPE row read it there, and the captured step increments it. One ``cudaGraphLaunch`` then
 replaces the launches of a step.
@@ -43,6 +44,7 @@ class DecodeGraph:
     @staticmethod
     def why_not(model: GPT) -> Optional[str]:
         """``None`` if the next single-token step of ``model`` can be captured, else the reason."""
+        from keys_values_b200.kvcache.basics import LastRecentlyInsertedKVCache
         from keys_values_b200.kvcache.h2o import H2OKVCache
 
         if not torch.cuda.is_available() or model.lm_head.weight.device.type != "cuda":
@@ -52,13 +54,20 @@ class DecodeGraph:
         if torch.is_grad_enabled():
             return "gradients are enabled"
         for cache in model.get_kv_caches():
-            if not isinstance(cache, H2OKVCache) or not cache._plain() or cache.max_chunk_size is None:
-                return "only caches of the plain H2O family with max_chunk_size select their slots on the device"
-            if cache.current_length != cache.cache_length or cache._use_initial_rule or cache._next_positions is None:
-                return "a cache is not full yet (its length still changes from step to step)"
-            if cache.grace_period != 0:
-                return "grace_period > 0 keeps a ring position on the host"
-            if cache._do_replay_log or cache.attn_recorder is not None or cache.debug_next_positions is not None:
+            if type(cache) is LastRecentlyInsertedKVCache:
+                # ring of the most recent tokens: the slot is a function of the position
+                if cache.current_length != cache.cache_length:
+                    return "a cache is not full yet (its length still changes from step to step)"
+            elif isinstance(cache, H2OKVCache) and cache._plain() and cache.max_chunk_size is not None:
+                if cache.current_length != cache.cache_length or cache._use_initial_rule or cache._next_positions is None:
+                    return "a cache is not full yet (its length still changes from step to step)"
+                if cache.grace_period != 0:
+                    return "grace_period > 0 keeps a ring position on the host"
+                if cache.debug_next_positions is not None:
+                    return "replay logging or recording is switched on"
+            else:
+                return "only last-recent caches and the plain H2O family with max_chunk_size choose their slots on the device"
+            if cache._do_replay_log or cache.attn_recorder is not None:
                 return "replay logging or recording is switched on"
             if cache.mha.sliding_window(cache.block_idx) is not None or cache.config.attention_logit_softcapping is not None:
                 return "sliding windows and logit soft-capping are not served by the decode kernel"
@@ -72,7 +81,7 @@ class DecodeGraph:
     # --------------------------------------------------------------------- capture
     def _advance_host(self) -> None:
         for cache in self.model.get_kv_caches():
-            cache._input_pos += 1
+            cache.advance_host_counters()
 
     def _capture(self, tokens: torch.Tensor) -> None:
         from keys_values_b200.ops import cuda as cu

@@ -211,6 +211,10 @@ class DefaultKVCache(KVCache):
     def _update(self, *args, **kwargs) -> None:
         pass
 
+    def advance_host_counters(self) -> None:
+        """One token has been processed by a captured decode step: move the host counters on."""
+        self._input_pos += 1
+
     def _can_decode_direct(self, query: torch.Tensor) -> bool:
         """True if a single new token can be served by the decode kernel that reads
         the cache storage directly (quantized storage included)."""

@@ -8,6 +8,7 @@ from typing import Any, Dict, Optional, Tuple
 
 import torch
 
+from keys_values_b200 import ops
 from keys_values_b200.attention.base import KeysAndValues
 from keys_values_b200.config import Config
 from keys_values_b200.kvcache.base import DefaultKVCache, KVCacheParams, KVCacheReplayLog
@@ -210,8 +211,21 @@ class LastRecentlyInsertedKVCache(KVCacheWithBuffers):
         n = key.shape[2]
         self.next_position = n if n < self.cache_length else self._ring_start()
 
+    def advance_host_counters(self) -> None:
+        """One token has been processed by a captured decode step: move the host counters on."""
+        C, s = self.cache_length, self._ring_start()
+        self._input_pos += 1
+        nxt = self.next_position + 1
+        self.next_position = nxt if nxt < C else (nxt - C) % (C - s) + s
+
     def _next_slots(self, n: int, B: int, device) -> torch.Tensor:
         L, C, s = self.current_length, self.cache_length, self._ring_start()
+        ctx = ops.position_context() if n == 1 else None
+        if ctx is not None:
+            # captured decode step of a full cache: the slot follows from the device-resident position
+            pos = ctx.word.to(torch.int64)
+            slot = (pos - C) % (C - s) + s
+            return slot.to(torch.int32).view(1, 1, 1).expand(B, self.n_query_groups, 1)
         pos = torch.arange(n, dtype=torch.int64, device=device) + self.next_position
         # positions past the end wrap into the ring [s, C)
         pos = torch.where(pos < C, pos, (pos - C) % (C - s) + s)

@@ -21,7 +21,7 @@ def _setup(cache_name, B, C, cache_kwargs=None):
     m = GPT(cfg)
     m.apply(m._init_weights)
     m = m.to(device=dev, dtype=dtype).eval()
-    kw = dict(max_chunk_size=64)
+    kw = dict(max_chunk_size=64) if "h2o" in cache_name else {}
     kw.update(cache_kwargs or {})
     m.assign_kv_caches(KVCacheFactory.create(m, cache_name, B, C, dtype=dtype, device=dev, cache_kwargs=kw))
     return cfg, m, dev
@@ -36,6 +36,7 @@ def _prefill(m, prompts, total):
 
 @pytest.mark.parametrize("cache_name,cache_kwargs", [
     ("h2o-default", None), ("h2o-torch-quantized8", None), ("h2o-torch-quantized4", None), ("h2o-default", dict(normalize_scores=True)),
+    ("lastrec-default", None), ("lastrec-torch-quantized8", None),
 ])
 def test_graph_decode_equals_eager(cache_name, cache_kwargs):
     B, C, T, steps = 2, 256, 600, 24
