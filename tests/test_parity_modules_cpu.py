@@ -342,3 +342,12 @@ def test_kvcache_test_utils():
     assert ("h2o-default", torch.device("cpu")) in names and all("bnb" not in n or tu.have_bitsandbytes() for n, _ in names)
     tok = tu.MockTokenizer()
     assert tok.encode(tu.sequence_of_words(5), eos=True).tolist()[-1] == tok.eos_id and len(tu.product_with_devices([1, 2], ["a"])) >= 2
+
+
+def test_profile_caches_tool_on_cpu():
+    from keys_values_b200.tools.profile_caches import profile
+
+    rows = profile("tiny-gpt", ["dense-default", "lastrec-default", "h2o-torch-quantized8", "no-such-cache"], batch=1, seq_len=96,
+                   cache_length=32, chunk_size=8, device=torch.device("cpu"), dtype=torch.float32)
+    assert [r["cache"] for r in rows] == ["dense-default", "lastrec-default", "h2o-torch-quantized8", "no-such-cache"]
+    assert all(r["tokens_per_s"] > 0 for r in rows[:3]) and "error" in rows[3]
