@@ -144,3 +144,101 @@ extern "C" int kvb_ce_loss_bwd(const void* logits, const long long* targets, con
   else return KVB_ERR_ARG;
   return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Greedy sampling: index of the largest logit of every row (the first one among equals, as
+// torch.argmax), in two stages so that a handful of rows of a 128k vocabulary use the whole GPU:
+// ARGMAX_SPLITS CTAs per row reduce a slice each, the last CTA to finish a row combines them.
+// ---------------------------------------------------------------------------------------------
+namespace kvb {
+constexpr int ARGMAX_SPLITS = 32;
+constexpr int ARGMAX_THREADS = 256;
+
+__device__ __forceinline__ void argmax_combine(float& v, int& i, float ov, int oi) {
+  if (ov > v || (ov == v && oi < i)) {
+    v = ov;
+    i = oi;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(ARGMAX_THREADS)
+argmax_rows_kernel(const T* __restrict__ logits, long long* __restrict__ out, float* __restrict__ part_v, int* __restrict__ part_i,
+                   unsigned* __restrict__ counters, int V, long long ld) {
+  __shared__ float sv[ARGMAX_THREADS / 32];
+  __shared__ int si[ARGMAX_THREADS / 32];
+  __shared__ int last;
+  const int row = blockIdx.y, split = blockIdx.x, tid = threadIdx.x;
+  const T* x = logits + (long long)row * ld;
+  const int per = (V + ARGMAX_SPLITS - 1) / ARGMAX_SPLITS;
+  const int j0 = split * per, j1 = min(V, j0 + per);
+  float v = -INFINITY;
+  int idx = 0x7fffffff;
+  for (int j = j0 + tid; j < j1; j += ARGMAX_THREADS) {
+    float f = to_f32(x[j]);
+    if (f != f) f = INFINITY;  // a NaN ranks with +inf: it wins, like in torch.argmax
+    if (f > v || (f == v && j < idx)) {
+      v = f;
+      idx = j;
+    }
+  }
+  auto block_reduce = [&]() {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) argmax_combine(v, idx, __shfl_xor_sync(0xffffffffu, v, o), __shfl_xor_sync(0xffffffffu, idx, o));
+    if ((tid & 31) == 0) {
+      sv[tid >> 5] = v;
+      si[tid >> 5] = idx;
+    }
+    __syncthreads();
+    if (tid < 32) {
+      v = tid < ARGMAX_THREADS / 32 ? sv[tid] : -INFINITY;
+      idx = tid < ARGMAX_THREADS / 32 ? si[tid] : 0x7fffffff;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) argmax_combine(v, idx, __shfl_xor_sync(0xffffffffu, v, o), __shfl_xor_sync(0xffffffffu, idx, o));
+    }
+  };
+  block_reduce();
+  if (tid == 0) {
+    part_v[row * ARGMAX_SPLITS + split] = v;
+    part_i[row * ARGMAX_SPLITS + split] = idx;
+    __threadfence();
+    last = atomicAdd(counters + row, 1u) == ARGMAX_SPLITS - 1;
+  }
+  __syncthreads();
+  if (!last) return;
+  __threadfence();
+  if (tid < 32) {
+    v = tid < ARGMAX_SPLITS ? reinterpret_cast<volatile float*>(part_v)[row * ARGMAX_SPLITS + tid] : -INFINITY;
+    idx = tid < ARGMAX_SPLITS ? reinterpret_cast<volatile int*>(part_i)[row * ARGMAX_SPLITS + tid] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) argmax_combine(v, idx, __shfl_xor_sync(0xffffffffu, v, o), __shfl_xor_sync(0xffffffffu, idx, o));
+    if (tid == 0) {
+      out[row] = idx == 0x7fffffff ? 0 : idx;
+      counters[row] = 0;  // ready for the next call
+    }
+  }
+}
+}  // namespace kvb
+
+// logits (rows, V), row stride ld (elements), dtype 0 = fp32, 1 = bf16; out int64 (rows), rows <= 65535.
+// scratch: kvb_argmax_scratch_bytes(rows) bytes. Its first ARGMAX_MAX_ROWS words are the per-row counters,
+// at the same place for every number of rows: zero before the first call, left zero by every call; the
+// partial results of the current call lie behind them.
+namespace kvb { constexpr long long ARGMAX_MAX_ROWS = 65536; }
+extern "C" long long kvb_argmax_scratch_bytes(long long rows) { return kvb::ARGMAX_MAX_ROWS * 4 + rows * kvb::ARGMAX_SPLITS * 8; }
+
+extern "C" int kvb_argmax_rows(const void* logits, long long* out, void* scratch, long long rows, int V, long long ld, int dtype,
+                               void* stream) {
+  using namespace kvb;
+  if (rows <= 0 || rows > 65535 || V <= 0 || ld < V || !scratch) return KVB_ERR_ARG;
+  unsigned* counters = reinterpret_cast<unsigned*>(scratch);
+  float* part_v = reinterpret_cast<float*>(counters + ARGMAX_MAX_ROWS);
+  int* part_i = reinterpret_cast<int*>(part_v + rows * ARGMAX_SPLITS);
+  dim3 grid(ARGMAX_SPLITS, (unsigned)rows);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == 0) argmax_rows_kernel<float><<<grid, ARGMAX_THREADS, 0, s>>>((const float*)logits, out, part_v, part_i, counters, V, ld);
+  else if (dtype == 1)
+    argmax_rows_kernel<__nv_bfloat16><<<grid, ARGMAX_THREADS, 0, s>>>((const __nv_bfloat16*)logits, out, part_v, part_i, counters, V, ld);
+  else return KVB_ERR_ARG;
+  return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
+}

@@ -71,6 +71,10 @@ int kvb_h2o_update(float* scores, const float* weights, const int32_t* token_pos
                    int n_evictable, int k_select, int normalize, int input_pos, int prefill_length, long long sc_sb,
                    long long sc_sg, long long tp_sb, long long tp_sg, void* stream);
 
+// ---- ce_loss.cu: greedy sampling
+long long kvb_argmax_scratch_bytes(long long rows);
+int kvb_argmax_rows(const void* logits, long long* out, void* scratch, long long rows, int V, long long ld, int dtype, void* stream);
+
 // ---- gemm_sm100.cu
 int kvb_gemm_bf16(const void* A, const void* B, const void* A2, const void* B2, void* C, const void* residual, int M, int N,
                   int K, int K2, long long lda, long long ldb, long long lda2, long long ldb2, long long ldc, int* status,

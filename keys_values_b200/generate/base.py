@@ -59,7 +59,9 @@ def batched_sample(logits_stack: torch.Tensor, kwargs: Union[dict, List[dict]]) 
         kwargs = [kwargs] * B
     assert len(kwargs) == B
     if all(kw.get("temperature", 1.0) == 0.0 or kw.get("top_k") == 1 for kw in kwargs):
-        return torch.argmax(logits_stack[:, -1], dim=-1, keepdim=True)  # greedy rows: one reduction for the batch
+        from keys_values_b200 import ops
+
+        return ops.argmax_rows(logits_stack[:, -1]).unsqueeze(-1)  # greedy rows: one reduction for the batch
     return torch.stack([sample(logits_stack[b : b + 1], **kw) for b, kw in enumerate(kwargs)], dim=0)
 
 

@@ -326,3 +326,11 @@ def decode_attention(query, key, value, scale, input_pos, token_pos=None, return
         return _cuda().decode_attention(query, key.contiguous(), value.contiguous(), scale, key.shape[2], return_weights)
     out, w = ref.sdpa(query, key, value, scale, input_pos, token_pos, return_weights)
     return out, w
+
+
+def argmax_rows(logits: torch.Tensor) -> torch.Tensor:
+    """``logits (R, V)`` → int64 ``(R,)``: greedy sampling. On a GPU a two-stage kernel spreads the few rows of a
+    decode step over the whole device."""
+    if logits.is_cuda and logits.dtype in (torch.float32, torch.bfloat16) and logits.ndim == 2 and logits.stride(-1) == 1 and logits.shape[0] <= 65535:
+        return _cuda().argmax_rows(logits)
+    return torch.argmax(logits, dim=-1)

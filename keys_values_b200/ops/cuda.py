@@ -134,6 +134,26 @@ def ce_loss_fwd(logits: torch.Tensor, targets: torch.Tensor, ignore_index: int):
     return loss, lse
 
 
+_ARGMAX_SCRATCH: dict = {}
+
+
+def argmax_rows(logits: torch.Tensor) -> torch.Tensor:
+    """Index of the largest entry of every row of ``logits (R, V)`` (fp32 / bf16, unit stride along V): int64 ``(R,)``."""
+    R, V = logits.shape
+    lib().kvb_argmax_scratch_bytes.restype = ctypes.c_longlong
+    key = logits.device.index or 0
+    buf = _ARGMAX_SCRATCH.get(key)
+    need = int(lib().kvb_argmax_scratch_bytes(_ll(R)))
+    if buf is None or buf.numel() < need:
+        # counters first (zero between calls), partial results behind them: sized for at least 64 rows
+        buf = _ARGMAX_SCRATCH[key] = torch.zeros(max(need, int(lib().kvb_argmax_scratch_bytes(_ll(64)))), dtype=torch.uint8, device=logits.device)
+    out = torch.empty(R, dtype=torch.int64, device=logits.device)
+    _check(lib().kvb_argmax_rows(_p(logits), _p(out), _p(buf), _ll(R), V, _ll(logits.stride(0)), 0 if logits.dtype == torch.float32 else 1,
+                                 _stream(logits)), "argmax_rows")
+    _count()
+    return out
+
+
 def ce_loss_bwd(logits: torch.Tensor, targets: torch.Tensor, lse: torch.Tensor, grad: torch.Tensor, ignore_index: int):
     N, V = logits.shape
     dlogits = torch.empty((N, V), dtype=logits.dtype, device=logits.device)

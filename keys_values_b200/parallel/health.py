@@ -53,11 +53,14 @@ class RankHealth:
     # -------------------------------------------------------------------- check
     def _peer_state(self, r: int) -> (Optional[str], int):
         failed = None
-        if self.store.check([self._fail_key(r)]):
-            failed = self.store.get(self._fail_key(r)).decode()
-        step = -1
-        if self.store.check([self._key(r)]):
-            step = int(self.store.get(self._key(r)).decode())
+        try:
+            if self.store.check([self._fail_key(r)]):
+                failed = self.store.get(self._fail_key(r)).decode()
+            step = -1
+            if self.store.check([self._key(r)]):
+                step = int(self.store.get(self._key(r)).decode())
+        except Exception as ex:  # the process that serves the store is gone
+            raise RankFailure({0: f"key-value store unreachable: {type(ex).__name__}"}) from ex
         return failed, step
 
     def laggards(self, step: int, grace_s: float = 5.0) -> Dict[int, str]:

@@ -38,6 +38,10 @@ def main():
         print("NOT DETECTED", flush=True)
     except RankFailure as ex:
         print("DETECTED", sorted(ex.ranks), next(iter(ex.ranks.values())), flush=True)
+    if rank == 0:
+        import time
+
+        time.sleep(3.0)  # this process serves the key-value store: the other survivors are still reading it
     os._exit(0)  # the group cannot be torn down collectively any more
 
 

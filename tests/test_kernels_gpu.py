@@ -375,3 +375,22 @@ def test_verification_api_and_host_optimizer_on_gpu():
         opt.step()
     torch.cuda.synchronize()
     assert abs(float(w.detach()[0]) - 0.97) < 5e-3 and abs(float(opt.host_params[0].detach()[0]) - 0.97) < 1e-4
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("R,V", [(4, 128256), (1, 1000), (7, 33)])
+def test_argmax_rows(dtype, R, V):
+    from keys_values_b200 import ops
+
+    x = torch.randn(R, V + 5, device=DEV, dtype=dtype)[:, :V]  # rows with a stride
+    x[0, V // 2] = 100.0
+    if V > 40 and R > 1:
+        x[-1, 17] = x[-1, 40] = 50.0  # equal maxima: the first one counts
+    for _ in range(2):  # the counters of the work space return to zero
+        got = ops.argmax_rows(x)
+        assert got.dtype == torch.int64 and got.shape == (R,)
+        assert bool(((got >= 0) & (got < V)).all())  # checked before anything indexes with it
+        assert torch.equal(x.gather(1, got.view(-1, 1)).view(-1), x.max(dim=-1).values)
+        assert int(got[0]) == V // 2
+        if V > 40 and R > 1:
+            assert int(got[-1]) == 17
