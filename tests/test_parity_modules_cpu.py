@@ -351,3 +351,26 @@ def test_profile_caches_tool_on_cpu():
                    cache_length=32, chunk_size=8, device=torch.device("cpu"), dtype=torch.float32)
     assert [r["cache"] for r in rows] == ["dense-default", "lastrec-default", "h2o-torch-quantized8", "no-such-cache"]
     assert all(r["tokens_per_s"] > 0 for r in rows[:3]) and "error" in rows[3]
+
+
+def test_analyze_gradient_data(tmp_path):
+    from keys_values_b200.tools import analyze_gradient_data as agd
+
+    torch.manual_seed(0)
+    nets = [torch.nn.Linear(4, 3) for _ in range(2)]
+    nets[1].load_state_dict(nets[0].state_dict())
+    befores = []
+    for r, net in enumerate(nets):
+        net(torch.randn(5, 4)).sum().backward()
+        befores.append(agd.record_gradients(net, lambda n: n == "weight"))
+    mean = {k: (befores[0][k] + befores[1][k]) / 2 for k in befores[0]}
+    for r in range(2):
+        agd.save_record(tmp_path, 0, r, befores[r], mean)
+    recs = agd.load_records(tmp_path, 0, 2)
+    agd.check_consistency(recs, "iteration 0")
+    agd.main([str(tmp_path), "--iters", "0", "--devices", "2"])
+    agd.save_record(tmp_path, 1, 0, befores[0], mean)
+    agd.save_record(tmp_path, 1, 1, befores[1], {k: v * 1.5 for k, v in mean.items()})
+    with pytest.raises(ValueError, match="differs between rank 0 and rank 1"):
+        agd.check_consistency(agd.load_records(tmp_path, 1, 2), "iteration 1")
+    assert "zeros: 1 of 4" in agd.text_histogram(torch.tensor([0.0, 1e-3, 1e-2, 1.0]))
