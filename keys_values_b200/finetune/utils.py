@@ -144,7 +144,8 @@ class CSVLogger:
 
 
 def choose_logger(logger_name: str, out_dir: Path, name: str = "metrics", **kwargs):
-    """``csv`` (default) or ``tensorboard`` if it is installed; ``wandb``/``mlflow`` need their packages."""
+    """``csv`` (default), ``tensorboard``, ``wandb`` or ``mlflow`` (the last three need their packages);
+    every logger has ``log_dict(metrics, step)`` (``keys_values/finetune/utils.py:265-325``)."""
     if logger_name == "csv":
         return CSVLogger(out_dir, name + ".csv")
     if logger_name == "tensorboard":
@@ -160,7 +161,28 @@ def choose_logger(logger_name: str, out_dir: Path, name: str = "metrics", **kwar
                         self.w.add_scalar(k, v, step)
 
         return _TB()
-    if logger_name in ("wandb", "mlflow"):
-        __import__(logger_name)
-        raise NotImplementedError(f"{logger_name} logger: package found but not wired in this build")
+    if logger_name == "wandb":
+        import wandb  # optional dependency
+
+        class _WandB:
+            def __init__(self):
+                self.run = wandb.init(project=kwargs.get("project", name), dir=str(out_dir), resume=kwargs.get("resume", "allow"))
+
+            def log_dict(self, metrics, step=None):
+                self.run.log({k: v for k, v in metrics.items() if isinstance(v, (int, float))}, step=step)
+
+        return _WandB()
+    if logger_name == "mlflow":
+        import mlflow  # optional dependency
+
+        class _MLflow:
+            def __init__(self):
+                mlflow.set_tracking_uri(kwargs.get("tracking_uri", (Path(out_dir) / "logs" / "mlruns").resolve().as_uri()))
+                mlflow.set_experiment(kwargs.get("experiment", name))
+                self.run = mlflow.start_run()
+
+            def log_dict(self, metrics, step=None):
+                mlflow.log_metrics({k: float(v) for k, v in metrics.items() if isinstance(v, (int, float))}, step=step)
+
+        return _MLflow()
     raise ValueError(f"`--logger_name={logger_name}` is not a valid option. Choose from 'csv', 'tensorboard', 'wandb', 'mlflow'.")
