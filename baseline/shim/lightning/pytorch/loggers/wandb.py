@@ -1,0 +1,1 @@
+from lightning.pytorch.loggers import CSVLogger  # noqa: F401

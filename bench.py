@@ -45,6 +45,10 @@ def parse_args():
     ap.add_argument("--num-targets", type=int, default=1024)
     ap.add_argument("--n-layer", type=int, default=None, help="debug only: fewer layers (marks the result as reduced)")
     ap.add_argument("--cache-name", type=str, default="h2o-torch-quantized8")
+    ap.add_argument("--ref-fused", action="store_true", help="reference arm: switch on its fused Triton RoPE/RMSNorm/SwiGLU")
+    ap.add_argument("--ref-time-budget", type=float, default=1500.0,
+                    help="reference arm: seconds the whole run may take; steps/warmup are lowered to fit and reported")
+    ap.add_argument("--ref-allow-cpu", action="store_true", help="reference arm: debug run on the CPU in fp32")
     return ap.parse_args()
 
 
