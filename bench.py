@@ -29,8 +29,6 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-PUBLISHED_TOKENS_PER_S = 900.0  # derived from the reference's published ≈140 s per 2×64k-token step on 1×A100-40GB
-
 
 def parse_args():
     ap = argparse.ArgumentParser()
@@ -186,7 +184,9 @@ def run_b200(args) -> dict:
         "ms_per_step": ms_dev / args.steps,
         "higher_is_better": True,
         "scaling": "weak",
-        "vs_baseline": None if reduced else value / PUBLISHED_TOKENS_PER_S,
+        # the reference publishes no number for this config or for this hardware (its figures are A100 runs of
+        # another shape): the comparison is the reference arm (--impl reference) on the same machine
+        "vs_baseline": None,
         "dtype": "bf16",
         "data": "synthetic uniform-random token ids, random-init weights",
         "impl": "b200",
@@ -214,7 +214,15 @@ def main():
     if args.impl == "reference":
         from baseline.reference_arm import run_reference
 
-        out = run_reference(args)
+        try:
+            out = run_reference(args)
+        except Exception as ex:  # the contract: say why in one line and exit 0
+            import traceback
+
+            traceback.print_exc()
+            out = {"impl": "reference", "unavailable": f"the reference's own code raised {type(ex).__name__}: {str(ex)[:300]}"}
+            print(json.dumps(out), flush=True)
+            os._exit(0)  # peers of a multi-rank job end through their process-group timeout
         if int(os.environ.get("RANK", "0")) != 0:
             out = {}  # one line per job: rank 0 prints it
     else:

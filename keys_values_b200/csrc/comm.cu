@@ -211,7 +211,10 @@ extern "C" int kvb_allreduce_mean(void* const* bases, void* const* flags, int ra
   }
   const long long limit = (long long)(timeout_s * 1.9e9);
   if (n_ctas <= 0) {
-    // enough CTAs to cover the shard once, between 4 and one per SM (all must be co-resident)
+    // Enough CTAs to cover the shard once, between 4 and one per SM. The grid barrier needs every CTA
+    // of the launch resident at once: one per SM is safe only while nothing else occupies the SMs, so a
+    // caller that runs this launch next to compute kernels passes a small n_ctas (the data-parallel
+    // reducer uses 32) instead of this default.
     const long long esz = dtype == 0 ? 4 : 2;
     const long long vec_per_rank = (count * esz / 16 + world - 1) / world;
     const long long want = (vec_per_rank + (long long)COMM_THREADS * COMM_UNROLL - 1) / ((long long)COMM_THREADS * COMM_UNROLL);

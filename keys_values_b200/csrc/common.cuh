@@ -281,4 +281,19 @@ __device__ __forceinline__ uint32_t sw128_offset(int r, int c16) {
   return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + (((c16) ^ (r & 7)) << 4));
 }
 
+
+// Launch attributes such as the dynamic shared memory limit are per device: a call site keeps one
+// flag per device and sets its attributes on the first launch there.
+struct PerDeviceOnce {
+  bool done[64] = {};
+  // true on the first call with the current device, and every time if the device cannot be read
+  bool first() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;
+    if (done[dev]) return false;
+    done[dev] = true;
+    return true;
+  }
+};
+
 }  // namespace kvb

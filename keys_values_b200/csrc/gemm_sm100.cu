@@ -555,10 +555,9 @@ static int launch_gemm(const void* A, const void* B, const void* A2, const void*
     tmA2 = tmA;
     tmB2 = tmB;
   }
-  static bool attr_set = false;
-  if (!attr_set) {
+  static kvb::PerDeviceOnce attr_once;
+  if (attr_once.first()) {
     cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
-    attr_set = true;
   }
   const int num_tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN);
   GemmExtra ex;

@@ -274,10 +274,9 @@ extern "C" int kvb_h2o_update(float* scores, const float* weights, const int32_t
   while (kpad < k_select) kpad <<= 1;
   const size_t smem = (size_t)n_evictable * 4 + (size_t)kpad * 8;
   if (smem > 200 * 1024) return KVB_ERR_TOO_LARGE;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static kvb::PerDeviceOnce attr_once;
+  if (attr_once.first()) {
     cudaFuncSetAttribute(h2o_update_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    attr_set = true;
   }
   h2o_update_kernel<<<B * G, H2O_THREADS, smem, (cudaStream_t)stream>>>(scores, weights, token_pos, out_idx, G, C, n_evictable,
                                                                        k_select, kpad, normalize, input_pos, prefill_length,

@@ -670,11 +670,10 @@ extern "C" int kvb_sdpa_bwd(const void* q, const void* k, const void* v, const i
   if ((rc = kvb_att_tile_minmax(token_pos, tmin, tmax, B, G, kv_len, tp_sb, tp_sg, 128, stream))) return rc;
   const long long rows = (long long)B * q_len * H;
   att_delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, delta, B, q_len, H);
-  static bool attr_set = false;
-  if (!attr_set) {
+  static kvb::PerDeviceOnce attr_once;
+  if (attr_once.first()) {
     cudaFuncSetAttribute(sdpa_bwd_kernel<MODE_DQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwSmem::TOTAL);
     cudaFuncSetAttribute(sdpa_bwd_kernel<MODE_DKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwSmem::TOTAL);
-    attr_set = true;
   }
   // The two launches are independent (dQ | dK, dV). They run on two streams, forked from and joined
   // back into the caller's stream, so that the tail of one grid (256 CTAs of the dQ launch fill

@@ -773,11 +773,10 @@ extern "C" int kvb_sdpa_fwd(const void* q, const void* k, const void* v, const i
   if ((rc = make_tmap_4d_bf16(&tmV, v, ATT_D, kv_len, G, B, ATT_D, k_sg, k_sb, 64, ATT_BN, 1))) return rc;
 
   att_tile_minmax_kernel<<<B * G * p.nT, ATT_BN, 0, s>>>(token_pos, tmin, tmax, G, kv_len, p.nT, tp_sb, tp_sg);
-  static bool attr_set = false;
-  if (!attr_set) {
+  static kvb::PerDeviceOnce attr_once;
+  if (attr_once.first()) {
     cudaFuncSetAttribute(sdpa_fwd_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttSmem::TOTAL);
     cudaFuncSetAttribute(sdpa_fwd_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttSmem::TOTAL);
-    attr_set = true;
   }
   // explicit token positions = an evicting cache: most tiles hold tokens of the current chunk and need
   // masks, which the 8-warp variant builds faster; plain causal attention runs best with 4 softmax warps

@@ -97,11 +97,17 @@ def build_lora_training_setup(
     grad_kwargs: Optional[Dict[str, Any]] = None,
     head_model: Optional[HeadModel] = None,
     overlap_allreduce: bool = True,
+    train_all_parameters: bool = False,
 ) -> TrainingSetup:
+    """``train_all_parameters=True`` turns the set-up into a full fine-tune: every weight of the
+    model (embeddings, norms, linears, head) is trainable, not only the LoRA factors."""
     config, gpt = create_lora_model(
         model_name, device, dtype, lora_r=lora_r, lora_alpha=lora_alpha, lora_targets=lora_targets,
         n_layer=n_layer, yarn_rope=yarn_rope, seed=seed,
     )
+    if train_all_parameters:
+        for p in gpt.parameters():
+            p.requires_grad_(True)
     ck = dict(cache_kwargs or {})
     cname, _ = split_name(cache_name)
     if "h2o" in cname and "max_chunk_size" not in ck:
@@ -132,6 +138,28 @@ def _free_after_oom(setup: TrainingSetup) -> None:
         torch.cuda.empty_cache()
 
 
+def check_native_status(setup: TrainingSetup, device) -> None:
+    """Reads the device status word before the optimizer may use the gradients of this step. A kernel
+    whose bounded wait ran out returns without doing its work (gradients not reduced, a tile not
+    computed); stepping on that would let the replicas diverge silently. Raises ``RankFailure`` (data
+    parallel) or ``NativeError`` and marks this rank as failed for its peers."""
+    device = torch.device(device)
+    if device.type != "cuda":
+        return
+    try:
+        if setup.grad_reducer is not None:
+            setup.grad_reducer.check()
+        else:
+            from keys_values_b200.ops import cuda as _cu
+
+            _cu.check_status(device)
+    except Exception as ex:
+        health = setup.extras.get("health")
+        if health is not None:
+            health.mark_failed(f"{type(ex).__name__}: {ex}")
+        raise
+
+
 def training_step(setup: TrainingSetup, input_ids: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
     """Forward, backward, gradient all-reduce (mean over ranks), clipping, optimizer
     step. Returns the (local) loss as a 0-d device tensor."""
@@ -158,6 +186,7 @@ def training_step(setup: TrainingSetup, input_ids: torch.Tensor, targets: torch.
         loss = attempt(0.0, True)
     if setup.grad_reducer is not None:
         setup.grad_reducer.finish_step()
+    check_native_status(setup, input_ids.device)
     if setup.max_norm is not None:
         params = [p for g in setup.optimizer.param_groups for p in g["params"] if p.grad is not None]
         torch.nn.utils.clip_grad_norm_(params, setup.max_norm)

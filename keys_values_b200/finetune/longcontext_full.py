@@ -253,6 +253,9 @@ def validate_and_all_reduce(model, val_loader, batch_transform, device, eval: Ev
     val_loss = validate(model, val_loader, batch_transform, device, eval.max_iters)
     val_loss = _all_reduce_mean(val_loss.to(device), world_size)
     v = float(val_loss)
+    from keys_values_b200 import ops as _ops
+
+    _ops.check_status(device)  # the loss has just been read: a kernel that gave up during validation is reported here
     metrics = {"val_loss": v, "val_ppl": math.exp(v) if v < 50 else float("inf")}
     if eval.sample_metric is not None and tokenizer is not None:
         metrics.update(validate_sample_metric(model, val_loader, tokenizer, device, eval, world_size))
@@ -326,6 +329,11 @@ def fit(*, model, optimizer, scheduler, train_loader, val_loader, batch_transfor
             state.iter_num += 1
         if grad_reducer is not None:
             grad_reducer.finish_step()
+            grad_reducer.check()  # raises RankFailure if a wait of the all-reduce ran out: no step on unreduced gradients
+        elif device.type == "cuda":
+            from keys_values_b200.ops import cuda as _cu
+
+            _cu.check_status(device)
         if recorder is not None:
             recorder.stop()
         if train.max_norm is not None:

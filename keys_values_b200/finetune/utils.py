@@ -69,10 +69,17 @@ def _load_sd(path: Path) -> Dict[str, torch.Tensor]:
 
 def load_model_checkpoint(gpt_model, checkpoint_dir: Path, resume_dir: Optional[Path] = None, head_model=None, strict: Optional[bool] = None) -> None:
     """Base weights from ``checkpoint_dir/lit_model.pth`` (strict unless the model has LoRA
-    parameters), then LoRA / head weights from ``resume_dir`` (or ``checkpoint_dir``)."""
+    parameters), then LoRA / head weights from ``resume_dir`` (or ``checkpoint_dir``). A full
+    fine-tune saves all weights as ``lit_model.pth`` in its step folders: when resuming one,
+    that file in ``resume_dir`` replaces the base weights."""
     checkpoint_dir = Path(checkpoint_dir)
     has_lora = any("lora_" in n for n, _ in gpt_model.named_parameters())
     base = checkpoint_dir / LIT_MODEL_FNAME
+    if resume_dir is not None and not has_lora:
+        resumed = Path(resume_dir) / LIT_MODEL_FNAME
+        if not resumed.is_file():
+            raise FileNotFoundError(f"cannot resume a full fine-tune: {resumed} does not exist")
+        base = resumed
     if base.is_file() and base.stat().st_size > 0:
         gpt_model.load_state_dict(_load_sd(base), strict=(not has_lora) if strict is None else strict)
     for d in ([Path(resume_dir)] if resume_dir is not None else []) + [checkpoint_dir]:

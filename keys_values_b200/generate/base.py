@@ -11,6 +11,7 @@ from typing import Any, Dict, Iterator, List, Optional, Sequence, Tuple, Union
 
 import torch
 
+from keys_values_b200 import ops as _ops
 from keys_values_b200.long_context import LongContextInferenceModel
 from keys_values_b200.models.head_model import CrossEntropyOnLogits
 from keys_values_b200.models.model import GPT
@@ -113,6 +114,7 @@ def batched_generate_fn(
     for step in range(max_returned_tokens - T):
         out: List[Optional[torch.Tensor]] = []
         vals = tokens.view(-1).tolist()
+        _ops.check_status(tokens.device)  # the host has just waited for the step: a kernel that gave up is reported here
         for b in range(B):
             if stopped[b]:
                 out.append(None)

@@ -277,7 +277,11 @@ class LongContextGradientModel(LongContextInferenceModel):
                 g = g * (gpt.config.n_embd**0.5)
             grad = torch.zeros_like(wte, dtype=torch.float32)
             grad.index_add_(0, input_ids.reshape(-1), g.reshape(-1, g.shape[-1]).float())
-            wte.grad = grad.to(wte.dtype) if wte.grad is None else wte.grad + grad.to(wte.dtype)
+            if wte.grad is None:
+                wte.grad = grad.to(wte.dtype)
+            else:
+                # in place: ``.grad`` may be a view into a flat gradient arena that is reduced over ranks
+                wte.grad.add_(grad.to(wte.dtype))
         if self.row_done_hook is not None:
             self.row_done_hook(-1, 0)
         self.clear()

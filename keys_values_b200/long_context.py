@@ -216,10 +216,21 @@ class LongContextInferenceModel(GPTAndHeadModel):
     # --------------------------------------------------------------- forward
     def forward(self, input_ids: torch.Tensor, targets: Optional[torch.Tensor] = None, scale_factor: float = 1.0):
         """With ``targets``: loss per batch row ``(B,)`` (normalised by the number of
-        target entries). Without: logits of the final position ``(B, 1, vocab)``."""
+        target entries). Without: logits of the final position ``(B, 1, vocab)``. The result
+        stays on the device; callers that read it on the host follow the read with
+        :func:`keys_values_b200.ops.check_status` (see :meth:`loss_value`)."""
         self._init_members_from_tokens(input_ids, targets)
         with torch.no_grad():
             return self._forward_internal(input_ids, targets, scale_factor)
+
+    def loss_value(self, input_ids: torch.Tensor, targets: torch.Tensor, scale_factor: float = 1.0) -> torch.Tensor:
+        """:meth:`forward` followed by a host read of the loss and of the device status word: raises if a
+        kernel of the pass reported that it gave up on a wait. Returns the per-row loss on the host."""
+        from keys_values_b200 import ops as _ops
+
+        loss = self.forward(input_ids, targets, scale_factor).detach().float().cpu()
+        _ops.check_status(input_ids.device)
+        return loss
 
     def _forward_internal(self, input_ids, targets, scale_factor: float = 1.0):
         gpt, head = self.gpt_model, self.head_model

@@ -3,9 +3,12 @@
 Every op has exactly one GPU implementation, a hand-written sm_100a kernel in
 ``keys_values_b200/csrc`` reached through :mod:`keys_values_b200.ops.cuda`, and a
 plain PyTorch restatement in :mod:`keys_values_b200.ops.reference` that serves
-CPU tensors and is the oracle in the tests. A CUDA tensor never falls back to
-the PyTorch restatement silently: if the native library cannot be loaded on a
-machine with a GPU, the first call raises.
+CPU tensors and is the oracle in the tests. If the native library cannot be loaded
+on a machine with a GPU, the first call raises. A CUDA tensor whose shape or dtype a
+kernel does not cover (for example a head size that has no instantiation, fp16
+activations for the fused norms) is served by the PyTorch restatement on the GPU, and
+the first such call of each op says so in a ``RuntimeWarning``; set
+``KVB200_STRICT_NATIVE=1`` to turn that into an error.
 """
 from __future__ import annotations
 
@@ -20,6 +23,31 @@ def _cuda():
     from keys_values_b200.ops import cuda as _c
 
     return _c
+
+
+_NOTICED = set()
+
+
+def _restatement_on_gpu(op: str, why: str) -> None:
+    """Called when a CUDA tensor is about to be served by the PyTorch restatement."""
+    import os
+    import warnings
+
+    msg = f"keys_values_b200.ops.{op}: no native kernel for {why}; using the PyTorch restatement on the GPU"
+    if os.environ.get("KVB200_STRICT_NATIVE", "0") == "1":
+        raise RuntimeError(msg)
+    if (op, why) not in _NOTICED:
+        _NOTICED.add((op, why))
+        warnings.warn(msg, RuntimeWarning, stacklevel=3)
+
+
+def check_status(device) -> None:
+    """Synchronising check of the device status word (no-op for CPU devices): raises
+    :class:`keys_values_b200.ops.cuda.NativeError` if a kernel reported that it gave up on a wait or
+    skipped a bad index since the last check. Call it where the host reads a result anyway."""
+    device = torch.device(device)
+    if device.type == "cuda":
+        _cuda().check_status(device)
 
 
 def native_launches() -> int:
@@ -130,6 +158,8 @@ def qknorm_rope(
         return _QKNormRopeFn.apply(
             qkv.contiguous(), cos, sin, q_weight, k_weight, n_head, n_query_groups, head_size, eps, rope_n_elem, add_unit_offset
         )
+    if qkv.is_cuda:
+        _restatement_on_gpu("qknorm_rope", f"head size {head_size}, {rope_n_elem} rotary elements, dtype {qkv.dtype}")
     return ref.qknorm_rope(qkv, n_head, n_query_groups, head_size, cos, sin, q_weight, k_weight, eps, rope_n_elem, add_unit_offset)
 
 
@@ -167,7 +197,14 @@ def sdpa_fwd(
     """Returns ``(out (B,q,H·D), weights (B,G,kv) fp32 | None, lse (B,H,q) fp32)``."""
     if query.is_cuda and _cuda().sdpa_supported(query, key, sliding_window, softcap):
         return _cuda().sdpa_fwd(query, key, value, scale, input_pos, token_pos, return_weights)
+    if query.is_cuda:
+        _restatement_on_gpu("sdpa_fwd", _sdpa_shape_text(query, sliding_window, softcap))
     return ref.sdpa(query, key, value, scale, input_pos, token_pos, return_weights, sliding_window, softcap, return_lse=True)
+
+
+def _sdpa_shape_text(query, sliding_window, softcap) -> str:
+    return (f"head size {query.shape[-1]}, dtype {query.dtype}"
+            + (", sliding window" if sliding_window is not None else "") + (", logit soft-capping" if softcap is not None else ""))
 
 
 def sdpa_bwd(
@@ -190,6 +227,8 @@ def sdpa_bwd(
     first ``kv`` slots instead and ``None`` is returned for them."""
     if query.is_cuda and _cuda().sdpa_supported(query, key, sliding_window, softcap):
         return _cuda().sdpa_bwd(grad_out, query, key, value, out, lse, scale, input_pos, token_pos, dk_accum, dv_accum)
+    if query.is_cuda:
+        _restatement_on_gpu("sdpa_bwd", _sdpa_shape_text(query, sliding_window, softcap))
     dq, dk, dv = ref.sdpa_backward(grad_out, query, key, value, scale, input_pos, token_pos, sliding_window, softcap)
     if dk_accum is not None:
         L = key.shape[2]
@@ -324,6 +363,8 @@ def decode_attention(query, key, value, scale, input_pos, token_pos=None, return
     before the query position). Returns ``(out (B,1,H·D), weights (B,G,L) | None)``."""
     if query.is_cuda and _cuda().decode_supported(query, key.shape[1]):
         return _cuda().decode_attention(query, key.contiguous(), value.contiguous(), scale, key.shape[2], return_weights)
+    if query.is_cuda:
+        _restatement_on_gpu("decode_attention", f"head size {query.shape[-1]}, dtype {query.dtype}, {query.shape[1]} heads over {key.shape[1]} groups")
     out, w = ref.sdpa(query, key, value, scale, input_pos, token_pos, return_weights)
     return out, w
 

@@ -23,6 +23,9 @@ import torch
 import torch.distributed as dist
 
 
+OVERLAP_COMM_CTAS = 32
+
+
 class GradientReducer:
     def __init__(self, params: Sequence[torch.nn.Parameter], world_size: int, rank: int, device, overlap: bool = True,
                  use_fused: Optional[bool] = None, group=None):
@@ -42,6 +45,7 @@ class GradientReducer:
         self.offsets: Dict[int, Tuple[int, int]] = {}
         off = 0
         align = 16 // torch.empty((), dtype=self.dtype).element_size()
+        self._align = align
         for p in self.params:
             n = p.numel()
             self.offsets[id(p)] = (off, n)
@@ -51,7 +55,10 @@ class GradientReducer:
         if self.use_fused:
             from keys_values_b200.parallel.symm import SymmetricArena
 
-            self.symm = SymmetricArena(self.numel, self.dtype, self.device, world_size, rank, group)
+            # Under overlap the all-reduce runs next to the backward kernels (one CTA per SM each): its grid
+            # barrier needs all of its CTAs resident at once, so the grid stays far below the SM count.
+            self.symm = SymmetricArena(self.numel, self.dtype, self.device, world_size, rank, group,
+                                       n_ctas=OVERLAP_COMM_CTAS if self.overlap else 0)
             self.flat = self.symm.tensor
         else:
             self.flat = torch.zeros(self.numel, dtype=self.dtype, device=self.device)
@@ -59,7 +66,7 @@ class GradientReducer:
             o, n = self.offsets[id(p)]
             p.grad = self.flat[o : o + n].view_as(p)
         self.comm_stream = torch.cuda.Stream(device=self.device) if self.overlap else None
-        self._ranges: Optional[Dict[int, Tuple[int, int]]] = None
+        self._ranges: Optional[Dict[int, List[Tuple[int, int]]]] = None
         self._covered = set()
         self.num_reductions = 0
 
@@ -102,12 +109,29 @@ class GradientReducer:
         if self._ranges is None:
             self.reduce_range_async(0, self.numel)
         else:
-            for key, (lo, hi) in self._ranges.items():
-                if key not in self._covered:
-                    self.reduce_range_async(lo, hi)
+            pending = [seg for key, segs in self._ranges.items() if key not in self._covered for seg in segs]
+            for lo, hi in _merge_segments(pending):
+                self.reduce_range_async(lo, hi)
             self._covered.clear()
         if self.comm_stream is not None:
             torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
+
+    def check(self) -> None:
+        """Synchronising check that no kernel of the step gave up on a wait (a lost peer, a flag that never
+        came): the gradients are then not reduced and must not reach the optimizer. Raises
+        :class:`keys_values_b200.parallel.health.RankFailure` after putting the arena's flags back in order."""
+        if self.device.type != "cuda":
+            return
+        from keys_values_b200.ops import cuda as _cu
+
+        try:
+            _cu.check_status(self.device)
+        except _cu.NativeError as ex:
+            if self.symm is not None:
+                self.symm.reset_sync()
+            from keys_values_b200.parallel.health import RankFailure
+
+            raise RankFailure({self.rank: f"gradient all-reduce did not complete: {ex}"}) from ex
 
     # ------------------------------------------------- overlap with backward
     def row_done_hook(self, gpt_model) -> Callable[[int, int], None]:
@@ -115,9 +139,14 @@ class GradientReducer:
         when the gradients of layers ``[first, end)`` are final (``first == n_layer``
         stands for the head, ``first == -1`` for the embeddings at the very end).
         Parameters outside the GPT model (head-model weights) are reduced by
-        :meth:`finish_step`."""
+        :meth:`finish_step`.
+
+        Each key owns a list of disjoint arena segments, never their hull: parameters that
+        become final at the same time need not be neighbours in the arena (``lm_head`` comes
+        first and ``ln_f`` last in ``parameters()`` order, with every layer between them), and
+        a reduction must not touch slots whose gradients are still being accumulated."""
         n_layer = gpt_model.config.n_layer
-        ranges: Dict[int, Tuple[int, int]] = {}
+        ranges: Dict[int, List[Tuple[int, int]]] = {}
         seen = set()
         for name, p in gpt_model.named_parameters():
             if id(p) not in self.offsets:
@@ -129,23 +158,37 @@ class GradientReducer:
             elif name.startswith("transformer.wte"):
                 layer = -1
             o, n = self.offsets[id(p)]
-            lo, hi = ranges.get(layer, (o, o + n))
-            ranges[layer] = (min(lo, o), max(hi, o + n))
+            ranges.setdefault(layer, []).append((o, self._slot_end(o, n)))
         rest = [self.offsets[id(p)] for p in self.params if id(p) not in seen]
         if rest:
-            ranges[n_layer + 1] = (min(o for o, _ in rest), max(o + n for o, n in rest))
-        self._ranges = ranges
+            ranges[n_layer + 1] = [(o, self._slot_end(o, n)) for o, n in rest]
+        self._ranges = {k: _merge_segments(v) for k, v in ranges.items()}
         self._covered = set()
 
         def hook(first: int, end: int) -> None:
             keys = [-1] if first == -1 else list(range(first, end))
-            los = [ranges[k][0] for k in keys if k in ranges and k not in self._covered]
-            his = [ranges[k][1] for k in keys if k in ranges and k not in self._covered]
-            self._covered.update(k for k in keys if k in ranges)
-            if los:
-                self.reduce_range_async(min(los), max(his))
+            keys = [k for k in keys if k in self._ranges and k not in self._covered]
+            self._covered.update(keys)
+            for lo, hi in _merge_segments([seg for k in keys for seg in self._ranges[k]]):
+                self.reduce_range_async(lo, hi)
 
         return hook
+
+    def _slot_end(self, offset: int, numel: int) -> int:
+        """End of a parameter's slot including its alignment padding (which holds zeros), so that
+        neighbouring slots merge into one reduction."""
+        return min(self.numel, offset + (numel + self._align - 1) // self._align * self._align)
+
+
+def _merge_segments(segments: Sequence[Tuple[int, int]]) -> List[Tuple[int, int]]:
+    """Sorted union of half-open segments; touching or overlapping ones become one."""
+    out: List[Tuple[int, int]] = []
+    for lo, hi in sorted(segments):
+        if out and lo <= out[-1][1]:
+            out[-1] = (out[-1][0], max(out[-1][1], hi))
+        else:
+            out.append((lo, hi))
+    return out
 
 
 def all_reduce_scalar_mean(x: torch.Tensor, world_size: int, group=None) -> torch.Tensor:

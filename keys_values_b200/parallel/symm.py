@@ -98,6 +98,17 @@ class SymmetricArena:
         self._epoch += 3
         _cu._count()
 
+    def reset_sync(self) -> None:
+        """After a wait that ran out: the kernel left its grid-barrier words and this rank's flags in a
+        state of the abandoned launch. Clear them so that a later launch (after the ranks have agreed to go
+        on) does not see stale arrivals. Every rank that goes on must call this."""
+        self._sync.zero_()
+        esize = torch.empty((), dtype=self.dtype).element_size()
+        whole = torch.as_tensor(self._raw, device=self.device)
+        whole[self.data_bytes : self.data_bytes + FLAG_BYTES].zero_()
+        self._epoch = 1
+        torch.cuda.synchronize(self.device)
+
     def close(self) -> None:
         lib = _cu.lib()
         for p in self._opened:

@@ -66,14 +66,20 @@ def case_allreduce(rank, world, dev):
         arena.close()
 
 
-def case_dp_train(rank, world, dev):
+def case_dp_train_full(rank, world, dev):
+    """Data-parallel step with every parameter trainable (embeddings, head and norms too): their
+    arena slots are not neighbours, and the embedding gradient is accumulated last."""
+    case_dp_train(rank, world, dev, train_all_parameters=True)
+
+
+def case_dp_train(rank, world, dev, train_all_parameters=False):
     """Data-parallel LoRA step: gradients after the reducer equal the mean of the per-rank
     gradients computed without it."""
     from keys_values_b200.finetune.engine import build_lora_training_setup
 
     dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
     kw = dict(cache_name="h2o-torch-quantized8", cache_length=128, chunk_size=32, lora_r=4, lora_alpha=8, micro_batch_size=1,
-              yarn_rope=False, seed=7)
+              yarn_rope=False, seed=7, train_all_parameters=train_all_parameters)
     name = "tiny-qwen3" if dev.type == "cuda" else "tiny-gpt"
     setup = build_lora_training_setup(name, dev, dtype, world_size=world, rank=rank, **kw)
     solo = build_lora_training_setup(name, dev, dtype, world_size=1, rank=0, **kw)
@@ -100,6 +106,8 @@ def case_dp_train(rank, world, dev):
 
         cu.check_status(dev)
     assert ref, "no gradients"
+    if train_all_parameters:
+        assert "transformer.wte.weight" in ref and "lm_head.weight" in ref or "lm_head.linear.weight" in ref
     for n, p in setup.gpt_model.named_parameters():
         if n in ref:
             tol = 3e-2 if dtype == torch.bfloat16 else 1e-5

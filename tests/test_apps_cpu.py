@@ -112,6 +112,31 @@ def test_cli_finetune_lora_then_resume_then_eval(tmp_path):
     assert "step 3/3" in r.stdout and "step 1/3" not in r.stdout
 
 
+def test_cli_finetune_full_resume_restores_trained_weights(tmp_path):
+    """A resumed full fine-tune starts from the weights saved at the step it resumes from, not from the base
+    checkpoint: resuming at the last step and saving at once must reproduce that step's ``lit_model.pth``."""
+    from keys_values_b200.config import Config
+
+    ckpt = tmp_path / "ckpt"
+    ckpt.mkdir()
+    Config.from_name("tiny-gpt").save(ckpt / "model_config.yaml")
+    out = tmp_path / "out"
+    common = [str(ckpt), "--out_dir", str(out), "--precision", "32-true", "--kv_cache.name", "h2o-default", "--kv_cache.cache_length", "64",
+              "--kv_cache.chunk_size", "16", "--train.global_batch_size", "1", "--train.micro_batch_size", "1",
+              "--train.save_interval", "2", "--train.lr_warmup_steps", "1", "--eval.interval", "100", "--eval.max_iters", "1",
+              "--eval.final_validation", "false", "--yarn_rope", "false", "--train.max_steps", "2"]
+    r = _run_cli(["finetune_long_full", *common], tmp_path)
+    assert r.returncode == 0, r.stdout + r.stderr
+    saved = torch.load(out / "step-000002" / "lit_model.pth", weights_only=True)["model"]
+    (out / "final" / "lit_model.pth").unlink()
+    r = _run_cli(["finetune_long_full", *common, "--resume", "auto"], tmp_path)
+    assert r.returncode == 0, r.stdout + r.stderr
+    final = torch.load(out / "final" / "lit_model.pth", weights_only=True)["model"]
+    assert saved.keys() == final.keys()
+    for k in saved:
+        assert torch.equal(saved[k], final[k]), k
+
+
 def test_cli_finetune_offload_lora_with_host_optimizer(tmp_path):
     """``finetune_offload_lora``: optimizer state and fp32 master weights on the host, checkpoints offloaded,
     gradient clipping done where the optimizer lives; the run resumes from its training state."""

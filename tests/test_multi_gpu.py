@@ -39,6 +39,12 @@ def test_dp_gradients_match_on_cpu_ranks():
     _run("dp_train", 2)
 
 
+def test_dp_full_finetune_gradients_match_on_cpu_ranks():
+    """All parameters trainable: the embedding gradient is added in place into the arena and the head's
+    segments (first and last slot of the arena) are reduced without touching the layers between them."""
+    _run("dp_train_full", 2)
+
+
 @pytest.mark.gpu
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_fused_allreduce_matches_nccl():
@@ -49,6 +55,12 @@ def test_fused_allreduce_matches_nccl():
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_dp_gradients_match_on_gpus():
     _run("dp_train", 2)
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_dp_full_finetune_gradients_match_on_gpus():
+    _run("dp_train_full", 2)
 
 
 @pytest.mark.gpu
