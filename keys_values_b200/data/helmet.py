@@ -2,7 +2,7 @@
 ``load_helmet_dev_eval.py``).
 
 The task files (JSON lines with ``context``/``question``/``answers``-style fields) must be
-present under ``data_dir``: this environment has no network access, so nothing is downloaded.
+present under ``data_dir``: nothing is downloaded by this loader.
 Records are turned into instruction/output pairs with the task's template and served through
 :class:`SequenceLengthFilteredDataModule` (length filter by ``max_length`` such as ``64k``)."""
 from __future__ import annotations

@@ -23,7 +23,7 @@ from keys_values_b200 import ops
 from keys_values_b200.attention.base import DefaultKeysAndValues, KeysAndValues
 from keys_values_b200.kvcache.base import KVCacheParams, bits_for_torch_dtype
 from keys_values_b200.kvcache.buffers import KVCacheBuffers, KVCacheBuffersParams
-from keys_values_b200.kvcache.quantize import BitsAndBytesQuantizer, Quantizer, TorchBasicQuantizer
+from keys_values_b200.kvcache.quantize import Quantizer, TorchBasicQuantizer
 
 
 class DequantizedKVCacheBuffers:
@@ -250,7 +250,12 @@ def get_quant_kwargs(params: KVCacheParams, qname: str, cache_kwargs: Dict[str, 
     if qname.startswith("torch-quantized"):
         quantizer_type = TorchBasicQuantizer
     elif qname.startswith("bnb-quantized"):
-        quantizer_type = BitsAndBytesQuantizer
+        # The bitsandbytes block-wise quantizer of the reference (keys_values/kvcache/quantize/bitsandbytes.py)
+        # is an optional back-end that needs that package; the framework's own storage formats are torch-quantized*.
+        raise ImportError(
+            f"buffer type {qname!r} needs the optional 'bitsandbytes' package, which this framework does not bind; "
+            f"use 'torch-quantized{qname[-1]}' (same bit width, asymmetric per-row quantization) instead"
+        )
     else:
         raise ValueError(f"qname = {qname} not supported")
     quant_kwargs["num_bits"] = int(qname[-1])

@@ -33,17 +33,18 @@ class HeadModel(torch.nn.Module):
         raise NotImplementedError
 
     @staticmethod
-    def _check_model_outputs_targets(model_outputs, targets, final_dim: int) -> Optional[int]:
-        if model_outputs.ndim != 3 or model_outputs.shape[-1] != final_dim:
-            raise ValueError(f"model_outputs.shape = {tuple(model_outputs.shape)}, must be 3D with final size {final_dim}")
+    def _target_offset(model_outputs: torch.Tensor, targets: Optional[torch.Tensor], width: int) -> Optional[int]:
+        """Number of leading positions of the chunk that carry no target: targets are right-aligned with
+        the chunk's outputs ``(B, T, width)``. ``None`` without targets. Raises on mismatched shapes."""
+        shape = tuple(model_outputs.shape)
+        if len(shape) != 3 or shape[2] != width:
+            raise ValueError(f"head expects outputs of shape (batch, tokens, {width}), got {shape}")
         if targets is None:
             return None
-        if targets.ndim != 2 or targets.shape[0] != model_outputs.shape[0]:
-            raise ValueError(f"model_outputs.shape = {tuple(model_outputs.shape)}, targets.shape = {tuple(targets.shape)}: Not compatible")
-        diff = model_outputs.shape[-2] - targets.shape[-1]
-        if diff < 0:
-            raise ValueError("model_outputs must not be shorter than targets")
-        return diff
+        if targets.ndim != 2 or targets.shape[0] != shape[0] or targets.shape[1] > shape[1]:
+            raise ValueError(f"targets of shape {tuple(targets.shape)} do not fit outputs of shape {shape}: "
+                             "same batch size and at most as many positions are required")
+        return shape[1] - targets.shape[1]
 
     def clone(self, device=None) -> "HeadModel":
         other = copy.deepcopy(self)
@@ -65,7 +66,7 @@ class CrossEntropyOnLogits(HeadModel):
     def forward(self, model_outputs, targets, input_pos):
         if targets is None:
             return torch.zeros(model_outputs.shape[0], device=model_outputs.device, dtype=torch.float32)
-        diff = self._check_model_outputs_targets(model_outputs, targets, self._vocab_size)
+        diff = self._target_offset(model_outputs, targets, self._vocab_size)
         logits = model_outputs[:, diff:, :]
         losses = ops.cross_entropy_rows(logits.reshape(-1, self._vocab_size), targets, IGNORE_INDEX)
         return losses.view(targets.shape).sum(dim=-1)
@@ -84,14 +85,18 @@ class SequenceClassificationOnLogits(HeadModel):
     def __init__(self, config: Config, class_label_tokens: List[int]):
         super().__init__()
         self._vocab_size = config.padded_vocab_size
-        self.num_classes = len(class_label_tokens)
-        if self.num_classes < 2:
-            raise ValueError(f"class_label_tokens = {class_label_tokens} must have at least 2 elements")
-        if not all(x == int(x) and 0 <= x < self._vocab_size for x in class_label_tokens):
-            raise ValueError(f"class_label_tokens = {class_label_tokens} must be in [0, {self._vocab_size})")
-        if len(set(class_label_tokens)) != self.num_classes:
-            raise ValueError(f"class_label_tokens = {class_label_tokens} must not have duplicates")
-        self.class_label_tokens = tuple(class_label_tokens)
+        labels = tuple(int(t) for t in class_label_tokens)
+        problems = []
+        if len(labels) < 2:
+            problems.append("fewer than two classes")
+        if any(a != b for a, b in zip(labels, class_label_tokens)) or any(not 0 <= t < self._vocab_size for t in labels):
+            problems.append(f"token ids outside 0..{self._vocab_size - 1}")
+        if len(set(labels)) < len(labels):
+            problems.append("repeated token ids")
+        if problems:
+            raise ValueError(f"class_label_tokens {list(class_label_tokens)}: " + ", ".join(problems))
+        self.num_classes = len(labels)
+        self.class_label_tokens = labels
 
     def needs_logits(self) -> bool:
         return True
@@ -101,7 +106,7 @@ class SequenceClassificationOnLogits(HeadModel):
             return torch.zeros(model_outputs.shape[0], device=model_outputs.device, dtype=torch.float32)
         if targets.shape[-1] != 1:
             raise ValueError(f"targets.length = {targets.shape[-1]}, must be 1")
-        self._check_model_outputs_targets(model_outputs, targets, self._vocab_size)
+        self._target_offset(model_outputs, targets, self._vocab_size)
         selected = model_outputs[:, -1, list(self.class_label_tokens)].float()
         return F.cross_entropy(selected, targets.reshape(-1), reduction="none")
 
@@ -119,38 +124,36 @@ class SequenceClassification(HeadModel):
 
     def __init__(self, config: Config, num_classes: int = 2, pool_type: str = "last"):
         super().__init__()
-        if num_classes < 2:
-            raise ValueError(f"num_classes = {num_classes} must be >= 2")
-        if pool_type not in SUPPORTED_POOL_TYPES:
-            raise ValueError(f"pool_type = {pool_type} must be one of {SUPPORTED_POOL_TYPES}")
+        if num_classes < 2 or pool_type not in SUPPORTED_POOL_TYPES:
+            raise ValueError(f"need num_classes >= 2 and pool_type in {SUPPORTED_POOL_TYPES}, got {num_classes} and {pool_type!r}")
         self.num_classes, self.n_embd, self.pool_type = num_classes, config.n_embd, pool_type
         self.linear_head = torch.nn.Linear(config.n_embd, num_classes, bias=True)
-        self._num_tokens = None
-        self._accumulated_state = None
+        self._seen = 0       # tokens of the current sequence consumed so far
+        self._running = None  # sum of their hidden states (mean pooling only)
 
     def needs_logits(self) -> bool:
         return False
 
     def forward(self, model_outputs, targets, input_pos) -> Union[torch.Tensor, float]:
-        self._check_model_outputs_targets(model_outputs, targets, self.n_embd)
-        if targets is not None and targets.shape[-1] != 1:
-            raise ValueError(f"targets.length = {targets.shape[-1]}, must be 1")
-        num = model_outputs.shape[-2]
+        """Consumes the hidden states of one chunk. Chunks of a sequence arrive in order, the first one with
+        ``input_pos == 0``; the chunk that carries the ``(B, 1)`` class targets ends the sequence and returns
+        the per-row cross-entropy, all earlier chunks return 0."""
+        self._target_offset(model_outputs, targets, self.n_embd)
+        if targets is not None and targets.shape[1] != 1:
+            raise ValueError(f"one class label per row is expected, got targets of shape {tuple(targets.shape)}")
         if input_pos == 0:
-            self._accumulated_state = 0 if self.pool_type == "mean" else None
-            self._num_tokens = 0
-        else:
-            assert self._num_tokens is not None, "First call must be with input_pos=0"
-            assert input_pos == self._num_tokens, f"input_pos = {input_pos} != {self._num_tokens} = num_tokens"
+            self._seen, self._running = 0, None
+        elif input_pos != self._seen:
+            raise ValueError(f"chunks must arrive in order: got input_pos {input_pos} after {self._seen} tokens")
         if self.pool_type == "mean":
-            self._accumulated_state = model_outputs.sum(dim=-2) + self._accumulated_state
-        self._num_tokens += num
+            chunk_sum = model_outputs.sum(dim=1)
+            self._running = chunk_sum if self._running is None else self._running + chunk_sum
+        self._seen += model_outputs.shape[1]
         if targets is None:
             return 0
-        state = self._accumulated_state / self._num_tokens if self.pool_type == "mean" else model_outputs[..., -1, :]
-        self._accumulated_state = None
-        logits = self.linear_head(state)
-        return F.cross_entropy(logits.float(), targets.reshape(-1), reduction="none")
+        pooled = self._running / self._seen if self.pool_type == "mean" else model_outputs[:, -1, :]
+        self._running = None
+        return F.cross_entropy(self.linear_head(pooled).float(), targets.reshape(-1), reduction="none")
 
     def num_target_entries(self, targets):
         return None

@@ -8,6 +8,7 @@ kernels rather than compile-time constants.
 from __future__ import annotations
 
 import math
+from dataclasses import dataclass
 from typing import Any, Dict, Optional, Tuple
 
 import torch
@@ -86,188 +87,187 @@ class PositionEncoding:
         raise NotImplementedError
 
 
-class LinearPositionEncoding(PositionEncoding):
-    """Linear interpolation with a fixed factor (``config.rope_adjustments['factor']``)
-    and fixed attention scale; supports Gemma-3 style local/global bases."""
+@dataclass(frozen=True)
+class _Stretch:
+    """How the rotary frequencies are stretched for one context width. ``ramp`` is ``None`` for a
+    uniform stretch by ``by``; otherwise ``(trained_width, low, high)`` of the wavelength ramp that
+    leaves high frequencies alone and stretches low ones by ``by``."""
 
-    def __init__(self, config: Config, device: Optional[torch.device] = None, do_set_context_width: bool = True):
-        self.rope_base = config.rope_base
+    by: float
+    ramp: Optional[Tuple[int, float, float]] = None
+
+    def as_rope_cache_args(self) -> Dict[str, Any]:
+        args: Dict[str, Any] = {"factor": self.by}
+        if self.ramp is not None:
+            args.update(original_max_seq_len=self.ramp[0], low_freq_factor=self.ramp[1], high_freq_factor=self.ramp[2])
+        return args
+
+
+def _ramp_bounds(low: Optional[float], high: Optional[float]) -> Tuple[float, float]:
+    low = DEFAULT_YARN_ALPHA if low is None else low
+    high = DEFAULT_YARN_BETA if high is None else high
+    if not 0 < low < high:
+        raise ValueError(f"frequency ramp needs 0 < low_freq_factor < high_freq_factor, got {low} and {high}")
+    return low, high
+
+
+class _RotaryTables(PositionEncoding):
+    """Table engine shared by the three rotary variants. A variant says, for a context width, how the
+    frequencies are stretched (:meth:`_stretch_for`) and which attention temperature goes with it
+    (:meth:`_scale_for`); this class owns the cos / sin tables for the current width, rebuilds them
+    when the answer for a new width differs, hands out row slices (or, inside a captured decode step,
+    the row selected by the device-resident position), and applies the rotation."""
+
+    def __init__(self, config: Config, device: Optional[torch.device]):
         self.n_elem = config.rope_n_elem
-        self.condense_ratio = config.rope_condense_ratio
-        self.rope_local_base_freq = config.rope_local_base_freq
         self.rope_indices = config.rope_indices
-        self._fixed_factor = None
-        if config.rope_adjustments is not None:
-            self._fixed_factor = config.rope_adjustments.get("factor")
-            if self._fixed_factor is None:
-                raise ValueError("config.rope_adjustments must include 'factor'")
-        self.train_context_width = config.block_size
-        self._device = device if device is not None else torch.get_default_device()
-        self._cos = self._sin = None
-        temp = config.attention_scores_scalar if config.attention_scores_scalar is not None else config.head_size
-        self._sdpa_scale_factor = 1.0 / math.sqrt(temp)
-        self._context_width = config.block_size
-        if do_set_context_width:
-            self.set_context_width(self._context_width)
+        self._bases = (config.rope_base, config.rope_local_base_freq)
+        self._condense = config.rope_condense_ratio
+        self._plain_scale = 1.0 / math.sqrt(config.attention_scores_scalar or config.head_size)
+        self._where = torch.device(device) if device is not None else torch.get_default_device()
+        self._width = 0
+        self._built_for: Optional[Tuple[int, _Stretch]] = None
+        self._table: Optional[Tuple[torch.Tensor, torch.Tensor]] = None
+        self._scale = self._plain_scale
 
+    # -- what a variant decides
+    def _stretch_for(self, width: int) -> _Stretch:
+        raise NotImplementedError
+
+    def _scale_for(self, width: int) -> float:
+        return self._plain_scale
+
+    # -- interface
     @property
     def context_width(self) -> int:
-        return self._context_width
+        return self._width
 
     @property
-    def device(self):
-        return self._device
+    def device(self) -> torch.device:
+        return self._where
+
+    def sdpa_scale_factor(self) -> float:
+        return self._scale
 
     def set_context_width(self, width: int):
         if width <= 0:
-            raise ValueError(f"width = {width}: Must be positive")
-        if width == self._context_width and self._cos is not None and not self._is_dynamic():
-            return
-        self._context_width = width
-        self._precompute()
+            raise ValueError(f"context width must be positive, got {width}")
+        self._width = int(width)
+        self._scale = self._scale_for(self._width)
+        wanted = (self._width, self._stretch_for(self._width))
+        if wanted != self._built_for:
+            self._table = build_rope_cache(
+                seq_len=self._width, n_elem=self.n_elem, device=self._where, base=self._bases[0], condense_ratio=self._condense,
+                extra_config=wanted[1].as_rope_cache_args(), rope_local_base_freq=self._bases[1],
+            )
+            self._built_for = wanted
 
-    def _is_dynamic(self) -> bool:
-        return False
-
-    def sdpa_scale_factor(self) -> float:
-        return self._sdpa_scale_factor
-
-    def _factor(self) -> float:
-        if self._fixed_factor is None:
-            return max(1.0, self.context_width / self.train_context_width)
-        return self._fixed_factor
-
-    def _precompute_extra_args(self) -> Optional[Dict[str, Any]]:
-        return {"factor": self._factor()}
-
-    def _precompute(self):
-        self._cos, self._sin = build_rope_cache(
-            seq_len=self.context_width,
-            n_elem=self.n_elem,
-            device=self._device,
-            base=self.rope_base,
-            condense_ratio=self.condense_ratio,
-            extra_config=self._precompute_extra_args(),
-            rope_local_base_freq=self.rope_local_base_freq,
-        )
+    def _layer_tables(self, block_idx: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
+        device = torch.device(device)
+        if self._table[0].device != device:
+            self._where = device
+            self._table = (self._table[0].to(device), self._table[1].to(device))
+        if self._bases[1] is None:
+            return self._table
+        which = self.rope_indices[block_idx]  # 0: global base, 1: local base
+        return self._table[0][:, :, which], self._table[1][:, :, which]
 
     def tables(self, input_pos: int, length: int, block_idx: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
-        """Slices ``(length, n_elem)`` of the cos/sin tables for ``block_idx``."""
-        if input_pos < 0 or input_pos + length > self.context_width:
-            raise ValueError(
-                f"input_pos = {input_pos}, length = {length}: need 0 <= input_pos, input_pos + length <= {self.context_width}"
-            )
-        if self._cos.device != torch.device(device):
-            self._device = torch.device(device)
-            self._cos = self._cos.to(self._device)
-            self._sin = self._sin.to(self._device)
+        """Rows ``input_pos … input_pos + length`` of the cos / sin tables of layer ``block_idx``."""
+        if not 0 <= input_pos <= self._width - length:
+            raise ValueError(f"positions {input_pos} … {input_pos + length} lie outside the context width {self._width}")
+        cos, sin = self._layer_tables(block_idx, device)
         ctx = _position_context() if length == 1 else None
-        if ctx is not None:
-            # captured decode step: the row is gathered by the device-resident position, once per step
-            ind = None if self.rope_local_base_freq is None else self.rope_indices[block_idx]
-            key = ("rope", id(self), ind)
-            rows = ctx.cache.get(key)
-            if rows is None:
-                cos, sin = (self._cos, self._sin) if ind is None else (self._cos[:, :, ind], self._sin[:, :, ind])
-                rows = ctx.cache[key] = (cos.index_select(0, ctx.word), sin.index_select(0, ctx.word))
-            return rows
-        if self.rope_local_base_freq is None:
-            return self._cos[input_pos : input_pos + length], self._sin[input_pos : input_pos + length]
-        ind = self.rope_indices[block_idx]
-        return self._cos[input_pos : input_pos + length, :, ind], self._sin[input_pos : input_pos + length, :, ind]
+        if ctx is None:
+            return cos[input_pos : input_pos + length], sin[input_pos : input_pos + length]
+        # captured decode step: the row follows the device-resident position; gathered once per step and layer kind
+        key = ("rope", id(self), None if self._bases[1] is None else self.rope_indices[block_idx])
+        if key not in ctx.cache:
+            ctx.cache[key] = (cos.index_select(0, ctx.word), sin.index_select(0, ctx.word))
+        return ctx.cache[key]
 
     def __call__(self, x: torch.Tensor, input_pos: int, block_idx: int, **kwargs) -> torch.Tensor:
         if x.ndim < 2 or x.shape[-1] != self.n_elem:
-            raise ValueError(f"x.shape = {x.shape}, last dimension must be {self.n_elem}")
+            raise ValueError(f"expected (..., T, {self.n_elem}), got {tuple(x.shape)}")
         cos, sin = self.tables(input_pos, x.shape[-2], block_idx, x.device)
-        return apply_rope(x, cos.unsqueeze(0), sin.unsqueeze(0))
+        return apply_rope(x, cos[None], sin[None])
+
+
+class LinearPositionEncoding(_RotaryTables):
+    """Position interpolation: every frequency is divided by one factor. The factor is
+    ``config.rope_adjustments['factor']`` when the config carries adjustments, else it follows the
+    context width (``max(1, width / block_size)``). The attention scale is the plain ``1/sqrt(D)``.
+    Gemma-3 style local / global bases are supported through ``rope_local_base_freq``."""
+
+    def __init__(self, config: Config, device: Optional[torch.device] = None, do_set_context_width: bool = True):
+        super().__init__(config, device)
+        self.train_context_width = config.block_size
+        self._pinned: Optional[float] = None
+        if config.rope_adjustments is not None:
+            if "factor" not in config.rope_adjustments or config.rope_adjustments["factor"] is None:
+                raise ValueError("rope_adjustments without a 'factor' entry")
+            self._pinned = float(config.rope_adjustments["factor"])
+        if do_set_context_width:
+            self.set_context_width(config.block_size)
+
+    def _stretch_by(self, width: int) -> float:
+        return self._pinned if self._pinned is not None else max(1.0, width / self.train_context_width)
+
+    def _stretch_for(self, width: int) -> _Stretch:
+        return _Stretch(self._stretch_by(width))
 
 
 class AdjustedPositionEncoding(LinearPositionEncoding):
-    """Non-dynamic Llama-3 style frequency adjustment (``rope_adjustments`` with
-    ``factor, original_max_seq_len, low_freq_factor, high_freq_factor``)."""
+    """Llama-3 style adjustment with a fixed factor: ``rope_adjustments`` holds ``factor``,
+    ``original_max_seq_len`` and optionally ``low_freq_factor`` / ``high_freq_factor``. Changing the
+    context width only changes the table length, never the frequencies."""
 
     def __init__(self, config: Config, device: Optional[torch.device] = None):
+        adj = config.rope_adjustments or {}
+        if adj.get("original_max_seq_len") is None:
+            raise ValueError("rope_adjustments['original_max_seq_len'] is required for the adjusted encoding")
         super().__init__(config, device, do_set_context_width=False)
-        if config.rope_adjustments is None:
-            raise ValueError("config.rope_adjustments must be given")
-        self.train_context_width = config.rope_adjustments.get("original_max_seq_len")
-        if self.train_context_width is None:
-            raise ValueError("Must have config.rope_adjustments['original_max_seq_len']")
-        alpha = config.rope_adjustments.get("low_freq_factor", DEFAULT_YARN_ALPHA)
-        beta = config.rope_adjustments.get("high_freq_factor", DEFAULT_YARN_BETA)
-        if not (0 < alpha < beta):
-            raise ValueError(f"alpha = {alpha}, beta = {beta}: Must be 0 < alpha < beta")
-        self.alpha, self.beta = alpha, beta
-        self._context_width = None
-        self.set_context_width(max(config.block_size, int(self._fixed_factor * self.train_context_width)))
+        self.train_context_width = int(adj["original_max_seq_len"])
+        self.alpha, self.beta = _ramp_bounds(adj.get("low_freq_factor"), adj.get("high_freq_factor"))
+        self.set_context_width(max(config.block_size, int(self._pinned * self.train_context_width)))
 
-    def _precompute_extra_args(self):
-        return {
-            **super()._precompute_extra_args(),
-            "original_max_seq_len": self.train_context_width,
-            "low_freq_factor": self.alpha,
-            "high_freq_factor": self.beta,
-        }
+    def _stretch_for(self, width: int) -> _Stretch:
+        return _Stretch(self._pinned, (self.train_context_width, self.alpha, self.beta))
 
 
 class YaRNPositionEncoding(LinearPositionEncoding):
-    """Dynamic YaRN (Peng et al., ICLR 2024): the interpolation factor and the
-    attention temperature follow the current context width."""
+    """Dynamic YaRN (Peng et al., ICLR 2024). With ``s = max(1, width / trained_width)`` for the current
+    context width, low frequencies are stretched by ``s`` along the ``alpha … beta`` wavelength ramp and
+    the attention scale becomes ``(0.1·ln s + 1)² / sqrt(D)``; both follow :meth:`set_context_width`.
+    ``rope_adjustments`` may supply the ramp bounds, the trained width and (through ``factor``) the
+    initial context width; ``alpha`` / ``beta`` arguments must then agree with it."""
 
     def __init__(self, config: Config, alpha: Optional[float] = None, beta: Optional[float] = None, device=None):
-        super().__init__(config, device, do_set_context_width=False)
+        adj = dict(config.rope_adjustments or {})
+        for name, given in (("low_freq_factor", alpha), ("high_freq_factor", beta)):
+            if adj.get(name) is not None and given is not None and given != adj[name]:
+                raise ValueError(f"rope_adjustments[{name!r}] = {adj[name]} contradicts the argument {given}")
+        initial_factor = adj.pop("factor", None)
+        _RotaryTables.__init__(self, config, device)
+        self._pinned = None
         self.head_size = config.head_size
-        train_context_width = None
-        factor = None
-        if config.rope_adjustments is not None:
-            ra = config.rope_adjustments
-            if ra.get("low_freq_factor") is not None:
-                if alpha is not None and alpha != ra["low_freq_factor"]:
-                    raise ValueError("Cannot have config.rope_adjustments['low_freq_factor'] and alpha")
-                alpha = ra["low_freq_factor"]
-            if ra.get("high_freq_factor") is not None:
-                if beta is not None and beta != ra["high_freq_factor"]:
-                    raise ValueError("Cannot have config.rope_adjustments['high_freq_factor'] and beta")
-                beta = ra["high_freq_factor"]
-            train_context_width = ra.get("original_max_seq_len")
-            factor = ra.get("factor")
-        if train_context_width is not None:
-            self.train_context_width = train_context_width
-        if factor is not None:
-            self._context_width = int(factor * self.train_context_width)
-        alpha = DEFAULT_YARN_ALPHA if alpha is None else alpha
-        beta = DEFAULT_YARN_BETA if beta is None else beta
-        if not (0 < alpha < beta):
-            raise ValueError(f"alpha = {alpha}, beta = {beta}: Must be 0 < alpha < beta")
-        self.alpha, self.beta = alpha, beta
-        self._sdpa_scale_factor = None
-        self._fixed_factor = None
-        width = self._context_width
-        self._context_width = None
-        self.set_context_width(width)
+        self.train_context_width = int(adj.get("original_max_seq_len") or config.block_size)
+        low, high = adj.get("low_freq_factor"), adj.get("high_freq_factor")
+        self.alpha, self.beta = _ramp_bounds(alpha if low is None else low, beta if high is None else high)
+        start = config.block_size if initial_factor is None else int(initial_factor * self.train_context_width)
+        self.set_context_width(start)
 
-    def _is_dynamic(self) -> bool:
-        return True
+    def _stretch_for(self, width: int) -> _Stretch:
+        return _Stretch(self._stretch_by(width), (self.train_context_width, self.alpha, self.beta))
 
-    def _precompute_extra_args(self):
-        return {
-            "factor": self._factor(),
-            "original_max_seq_len": self.train_context_width,
-            "low_freq_factor": self.alpha,
-            "high_freq_factor": self.beta,
-        }
-
-    def _precompute(self):
-        super()._precompute()
-        sqrt_inv_t = 0.1 * math.log(self._factor()) + 1.0
-        self._sdpa_scale_factor = sqrt_inv_t * sqrt_inv_t / math.sqrt(self.head_size)
+    def _scale_for(self, width: int) -> float:
+        root = 0.1 * math.log(self._stretch_by(width)) + 1.0
+        return root * root / math.sqrt(self.head_size)
 
 
 def position_encoding_factory(config: Config, do_yarn: bool = False, **kwargs) -> PositionEncoding:
     if do_yarn:
         return YaRNPositionEncoding(config, **kwargs)
-    ra = config.rope_adjustments
-    if ra is not None and "original_max_seq_len" in ra:
+    if (config.rope_adjustments or {}).get("original_max_seq_len") is not None:
         return AdjustedPositionEncoding(config, **kwargs)
     return LinearPositionEncoding(config, **kwargs)
