@@ -81,11 +81,11 @@ int kvb_gemm_bf16(const void* A, const void* B, const void* A2, const void* B2, 
                   int max_ctas, void* stream);
 
 // ---- sdpa_sm100.cu
-// Diagnostics: device-side timeline of CTA 0 of later kvb_sdpa_fwd launches (see sdpa_sm100.cu).
-int kvb_sdpa_fwd_set_trace(void* buf, int cap);
+// Diagnostics: per-phase cycle counters of CTA 0 of later kvb_sdpa_fwd launches (4 roles x 8 int64, see sdpa_sm100.cu).
+int kvb_sdpa_fwd_set_trace(void* buf);
 int kvb_sdpa_bwd_set_trace(void* buf, int cap, int mode);
 // scratch: kvb_sdpa_fwd_scratch_bytes(...) bytes of device memory owned by the caller
-long long kvb_sdpa_fwd_scratch_bytes(int B, int H, int G, int q_len, int kv_len, int want_weights);
+long long kvb_sdpa_fwd_scratch_bytes(int B, int H, int G, int q_len, int kv_len);
 int kvb_sdpa_fwd(const void* q, const void* k, const void* v, const int32_t* token_pos, void* out, float* lse, float* weights,
                  void* scratch, int B, int H, int G, int q_len, int kv_len, long long k_sb, long long k_sg, long long tp_sb,
                  long long tp_sg, float scale, int input_pos, int* status, void* stream);

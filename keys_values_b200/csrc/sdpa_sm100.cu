@@ -1,42 +1,42 @@
-// SDPA forward for sm_100a that also returns the per-KV-slot summed attention
-// weights (the H2O score input), with the causal mask taken from token positions.
+// SDPA forward for sm_100a with summed attention weights: one flash sweep for the output and the row
+// normalisers, and a column-owner kernel for the per-slot weight sums.
 //
 //   out[b, t, h, :]   = softmax_j(scale · q[b,h,t]·k[b,g,j] | token_pos[b,g,j] <= input_pos + t) · v[b,g,:]
 //   lse[b, h, t]      = natural-log normaliser of that softmax
 //   weights[b, g, j]  = (1 / (H/G)) · sum over t and over the H/G heads of group g of the softmax weight of slot j
 //
-// Design (bf16, head size 128):
-//   * CTA tile = 128 query rows = (128 / gs) consecutive positions x gs heads of one KV
-//     group (gs = H/G), so every K/V tile is loaded once per group, not once per head.
-//   * S = Q K^T (M=128, N=64) and O += P V (M=128, N=128) run on tcgen05.mma. Q is moved once
-//     from shared memory into TMEM and is the A operand of every QK MMA from there, so that
-//     those MMAs read only K from shared memory (operand traffic from shared memory, 128 B per
-//     clock, is what bounds tcgen05 at these tile sizes). S has one TMEM buffer: the softmax
-//     warps pull a tile into registers and hand the buffer back at once, so the next QK runs
-//     during their arithmetic. O stays in TMEM. K tiles of 64 slots arrive by TMA into a
-//     4-stage ring, V tiles into a 2-stage ring (128B swizzle; no multicast). V is consumed as
-//     an MN-major B operand.
-//   * A CTA uses 112.5 KB of shared memory and 256 TMEM columns, so two CTAs share an SM:
-//     while one waits on its MMA -> softmax -> MMA chain the other one issues.
-//   * Two sweeps over the KV tiles: sweep 1 computes the exact row log-sum-exp (online
-//     max / sum), sweep 2 recomputes S, forms the already-normalised P = exp2(S·c − lse),
-//     accumulates O without any rescaling and takes the column sums of P. The column
-//     sums of a tile are complete once its P tile is written, so they are stored as
-//     deterministic per-(query tile) partials and reduced by a second small kernel:
-//     no atomics, hence run-to-run identical eviction decisions.
-//   * KV tiles whose smallest token position lies beyond the last query of the CTA are
-//     skipped by every role; tiles that contain no position beyond the first query of
-//     the CTA take the mask-free path. In a masked tile only the columns whose token lies
-//     beyond the first query need a per-row comparison; their positions travel by warp
-//     shuffle and end up as a 64-bit mask per row, without shared memory or block barriers.
-//   * warp 0 = TMA producer, warp 1 = MMA issuer / TMEM owner, then the softmax + epilogue warps.
-//     Two instantiations: 4 softmax warps (a thread owns a query row = its TMEM lane and all 64
-//     columns of a tile; used for plain causal attention) and 8 softmax warps (two per TMEM lane
-//     quarter, 32 columns per thread; used over an evicting cache, where most tiles need masks).
+// Kernel A (flash_fwd_kernel), one CTA per SM, per (batch, KV group, pair of query tiles):
+//   * A query tile is 128 rows = npos consecutive positions x gs = H/G heads of one KV group, position
+//     major (row = position · gs + head), so a K/V tile is read once per group. npos = 128 / gs (any
+//     gs <= 128; rows beyond npos · gs are zero and ignored).
+//   * S = Q K^T (M = 128, N = 128, both operands in shared memory) and O += P V run on tcgen05.mma with
+//     accumulators in TMEM: S0 | S1 | O0 | O1, 128 columns each, all 512 columns of the SM.
+//     Online softmax in one sweep over the KV tiles: the softmax warps read S from TMEM, write the
+//     unnormalised P = exp2(S·c − m) back into the columns of S as packed bf16, and P is the A operand
+//     of the PV MMA straight from TMEM, so neither S nor P touches shared memory. The running
+//     maximum m of a row is only raised when it grows by more than 8 (a factor 256), in which case the
+//     warp rescales its rows of O in TMEM; after the first tiles that is rare.
+//   * Two query tiles per CTA, one softmax warpgroup each: while one warpgroup works on its S tile the
+//     tensor core runs PV and the next QK of the other.
+//   * K and V tiles of 128 slots arrive by TMA (128B swizzle, no multicast) in one ring of four 32 KB
+//     stages in the order K0 V0 K1 V1 ...; V is consumed as an MN-major B operand.
+//   * Masks come from token positions. A tile that holds no token beyond the first query of the CTA is
+//     mask free. Slots whose token lies beyond the last query of the CTA are hidden from all of its rows:
+//     they are masked by the tensor core itself, through one more K = 16 step of S whose A operand is a
+//     column of ones and whose B operand holds 0 or -inf per slot (written by the producer warp from a
+//     padded copy of the positions). Over an evicting cache that covers nearly all hidden slots; the few
+//     slots in between are patched column by column in TMEM, and a tile with many of them (the diagonal
+//     of plain causal attention) is compared element by element. Tiles that no query can see are skipped.
 //
-// Replaces FlashInfer prefill + Triton score-sum + K/V reordering + query padding of the
-// reference (keys_values/attention/flashinfer_wrapper.py:51-273, :367-510,
-// csrc/kernels/sdpa_prefill.cu, attention/sdpa_wrapper.py:66-432).
+// Kernel B (colsum_kernel), per (batch, KV group, KV tile of 128 slots): S^T = K Q^T per query tile
+//   on tcgen05 (M = 128 slots, N = 128 query rows), four S^T buffers in TMEM. A thread owns one slot
+//   and adds exp2(S·c − lse_row) over the 128 query rows of every tile from registers: no shared
+//   memory, no atomics, no partial buffers, a fixed order (run-to-run identical eviction decisions).
+//   Position-major query rows turn the causal mask of a slot into one threshold on the column index.
+//
+// Replaces FlashInfer prefill + Triton score-sum + K/V reordering + query padding of the reference
+// (keys_values/attention/flashinfer_wrapper.py:51-273, :367-510, csrc/kernels/sdpa_prefill.cu,
+// attention/sdpa_wrapper.py:66-432).
 #include <cuda.h>
 #include <limits.h>
 
@@ -45,63 +45,81 @@
 
 namespace kvb {
 
-int make_tmap_2d_bf16(CUtensorMap* tm, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
-                      uint32_t box_cols);
+constexpr int F2_T = 128;                        // rows of a query tile, slots of a KV tile, head size
+constexpr int F2_TILE_BYTES = F2_T * F2_T * 2;   // 32 KB: two 64-feature chunks of [128 rows x 128 B]
+constexpr int F2_CHUNK_BYTES = F2_TILE_BYTES / 2;
+constexpr int F2_STAGES = 4;
+constexpr int F2_THREADS = 64 + 256;             // TMA warp, MMA warp, two softmax warpgroups
+constexpr int F2_MAX_FLAG_TILES = 4096;           // tiles whose flags live in shared memory (one byte each)
+constexpr float F2_RESCALE_STEP = 8.0f;          // log2 units
+constexpr int F2_PATCH_MAX_COLS = 6;             // masked tiles with at most this many candidate columns are patched in TMEM
+// Bias operand tiles of the extra K = 16 step of S: 128 rows x 16 bf16, K-major without swizzle. A core
+// matrix is 8 rows x 16 bytes, stored contiguously (128 B); groups of 8 rows follow one another (stride byte
+// offset 128 B), the second core matrix along K lies 2 KB further (leading byte offset).
+constexpr int F2_BIAS_TILE_BYTES = 128 * 16 * 2;
+constexpr uint32_t F2_BIAS_LBO = 2048, F2_BIAS_SBO = 128;
+__device__ __forceinline__ uint32_t f2_bias_offset(int row) { return (uint32_t)((row >> 3) * F2_BIAS_SBO + (row & 7) * 16); }
+// descriptor of such a tile: no swizzle (layout type 0), version 1
+__device__ __forceinline__ uint64_t f2_bias_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+  d |= (uint64_t)((F2_BIAS_LBO >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((F2_BIAS_SBO >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
+  return d;
+}
 
-constexpr int ATT_BM = 128;   // query rows per CTA
-constexpr int ATT_BN = 64;    // KV slots per tile
-constexpr int ATT_D = 128;    // head size
-// TMA warp + MMA warp + SW softmax warps; two CTAs per SM. SW = 4: a thread owns one query row and all
-// 64 columns of a tile (best when few tiles need masks: prefill, plain causal attention); SW = 8: two
-// warps per TMEM lane quarter, 32 columns per thread (best when most tiles hold tokens of the current
-// chunk, as in training over an evicting cache, where building the masks dominates the chain).
-constexpr int att_threads(int sw) { return 64 + 32 * sw; }
-constexpr int ATT_Q_BYTES = ATT_BM * ATT_D * 2;    // 32 KB: two 64-feature chunks of [128 rows x 128 B]
-constexpr int ATT_KV_BYTES = ATT_BN * ATT_D * 2;   // 16 KB: two 64-feature chunks of [64 rows x 128 B]
-constexpr int ATT_P_BYTES = ATT_BM * ATT_BN * 2;   // 16 KB: one 64-column chunk of [128 rows x 128 B]
-constexpr int ATT_TMEM_COLS = 256;                 // Q as bf16 pairs (64 columns) | S (64) | O (128)
-constexpr int ATT_KSTAGES = 4;
-
-// Shared memory of one CTA: 112.5 KB, so that two CTAs fit into the 228 KB of an SM (each
-// CTA also costs 1 KB of system reserve). The dynamic shared memory window must be 1024-byte
-// aligned for the 128B-swizzled tiles; the kernel checks this and reports instead of running.
-struct AttSmem {
-  static constexpr int K = 0;                              // ring of ATT_KSTAGES K tiles
-  static constexpr int Q = K + 2 * ATT_KV_BYTES;           // Q lands in K stages 2, 3 and moves on to TMEM
-  static constexpr int V = K + ATT_KSTAGES * ATT_KV_BYTES; // ring of 2 V tiles
-  static constexpr int P = V + 2 * ATT_KV_BYTES;
-  static constexpr int TF = P + ATT_P_BYTES;   // 2 bits per KV tile (active, masked) for the first 1024 tiles
-  static constexpr int BAR = TF + 256;
+struct F2Smem {
+  static constexpr int Q = 0;                                   // two query tiles
+  static constexpr int KV = Q + 2 * F2_TILE_BYTES;              // ring of K / V tiles
+  static constexpr int TF = KV + F2_STAGES * F2_TILE_BYTES;     // one byte per KV tile: bit 0 active, bit 1 masked
+  static constexpr int QX = TF + F2_MAX_FLAG_TILES;             // [128 x 16] bf16, column 0 = 1: A operand of the bias step
+  static constexpr int KX = QX + F2_BIAS_TILE_BYTES;            // per ring stage: [128 x 16] bf16, column 0 = 0 or -inf
+  static constexpr int BAR = KX + F2_STAGES * F2_BIAS_TILE_BYTES;
   static constexpr int TOTAL = BAR + 256;
 };
-static_assert(ATT_Q_BYTES == 2 * ATT_KV_BYTES, "Q must fit into two K stages");
+static_assert(F2Smem::TOTAL <= 232448, "shared memory of the flash kernel exceeds the limit of a CTA");
 
-struct AttParams {
-  const int32_t* token_pos;  // (B,G,L) with strides tp_sb, tp_sg, or nullptr (slot j holds token j)
+struct F2Params {
+  const int32_t* pos;        // (B,G,nT*128) padded token positions (INT_MAX beyond the cache)
   const int32_t* tile_min;   // (B,G,nT)
   const int32_t* tile_max;   // (B,G,nT)
   __nv_bfloat16* out;        // (B,T,H,D)
-  float* lse;                // (B,H,T)
-  float* wpart;              // (B,G,4*nQT,L) or nullptr
-  int B, H, G, T, L, nT, nQT, gs, npos;
-  long long tp_sb, tp_sg;
+  float* lse;                // (B,H,T) natural log, or nullptr
+  float* lse2;               // (B,G,nQT,128) log2 normaliser per packed query row, +inf for rows without a query
+  float* weights;            // (B,G,L) or nullptr
+  int B, H, G, T, L, nT, nQT, gs, npos, rows_used;
   float scale_log2;          // scale * log2(e)
+  float inv_gs;
   int input_pos;
   int* status;
-  long long* trace;          // optional timeline of CTA 0: per role trace_cap (tag, clock) pairs
-  int trace_cap;
+  long long* trace;          // optional phase profile of CTA 0: 4 roles x 8 cycle counters
 };
 
-// Timeline event of one role (0 producer, 1 MMA issuer, 2 first softmax warp) of CTA 0.
-#define ATT_TRACE(role, tag)                                              \
-  do {                                                                    \
-    if (p.trace && blockIdx.x == 0 && tr_n < p.trace_cap) {               \
-      p.trace[((role) * p.trace_cap + tr_n) * 2] = (long long)(tag);      \
-      p.trace[((role) * p.trace_cap + tr_n) * 2 + 1] = clock64();         \
-      ++tr_n;                                                             \
-    }                                                                     \
+// Optional phase profile of CTA 0 (diagnostics): each role adds the cycles spent since its previous mark to one of
+// eight counters and writes them once at the end, so that the measurement costs a clock read per mark.
+// Roles: 0 MMA issuer, 1 / 2 first warp of softmax warpgroup 0 / 1, 3 producer.
+__device__ __forceinline__ uint32_t f2_clock() {
+  uint32_t c;
+  asm volatile("mov.u32 %0, %%clock;" : "=r"(c));
+  return c;
+}
+#define F2_TRACE_DECL(active) uint32_t tr_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const bool tr_on = p.trace != nullptr && blockIdx.x == 0 && (active); uint32_t tr_last = tr_on ? f2_clock() : 0u
+#define F2_MARK(k)                                \
+  do {                                            \
+    if (tr_on) {                                  \
+      const uint32_t now_ = f2_clock();           \
+      tr_acc[k] += now_ - tr_last;                \
+      tr_last = now_;                             \
+    }                                             \
+  } while (0)
+#define F2_TRACE_STORE(role)                                                         \
+  do {                                                                               \
+    if (tr_on)                                                                       \
+      for (int k_ = 0; k_ < 8; ++k_) p.trace[(role) * 8 + k_] = (long long)tr_acc[k_]; \
   } while (0)
 
+// Per-tile min / max of the token positions for tiles of blockDim.x (64 or 128) slots (used by the backward kernels).
 __global__ void att_tile_minmax_kernel(const int32_t* __restrict__ tp, int32_t* __restrict__ tmin, int32_t* __restrict__ tmax, int G,
                                        int L, int nT, long long tp_sb, long long tp_sg) {
   // one block per tile; blockDim.x = tile size (64 or 128)
@@ -136,162 +154,223 @@ __global__ void att_tile_minmax_kernel(const int32_t* __restrict__ tp, int32_t* 
   }
 }
 
-// weights[b,g,j] = inv_gs * sum_qt wpart[b,g,qt,j]
-__global__ void att_reduce_weights_kernel(const float* __restrict__ wpart, float* __restrict__ weights, int nQT, int L, float inv_gs) {
-  const long long bg = blockIdx.y;
-  const int j = blockIdx.x * blockDim.x + threadIdx.x;
-  if (j >= L) return;
-  const float* p = wpart + bg * nQT * (long long)L + j;
-  float s = 0.f;
-  for (int q = 0; q < nQT; ++q) s += p[(long long)q * L];
-  weights[bg * L + j] = s * inv_gs;
+// tile_min / tile_max of the token positions per tile of 128 slots and a padded copy of the positions.
+__global__ void f2_prepare_kernel(const int32_t* __restrict__ tp, int32_t* __restrict__ tmin, int32_t* __restrict__ tmax,
+                                  int32_t* __restrict__ pos, int G, int L, int nT, long long tp_sb, long long tp_sg) {
+  const int t = blockIdx.x % nT;
+  const int bg = blockIdx.x / nT;
+  const int b = bg / G, g = bg % G;
+  const int j = t * F2_T + threadIdx.x;
+  int lo = INT_MAX, hi = INT_MIN, v = INT_MAX;
+  if (j < L) {
+    v = tp ? tp[b * tp_sb + g * tp_sg + j] : j;
+    lo = hi = v;
+  }
+  pos[(long long)blockIdx.x * F2_T + threadIdx.x] = v;
+  for (int o = 16; o > 0; o >>= 1) {
+    lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+    hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+  }
+  __shared__ int slo[4], shi[4];
+  if ((threadIdx.x & 31) == 0) {
+    slo[threadIdx.x >> 5] = lo;
+    shi[threadIdx.x >> 5] = hi;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 4; ++w) {
+      lo = min(lo, slo[w]);
+      hi = max(hi, shi[w]);
+    }
+    if ((t + 1) * F2_T > L) hi = INT_MAX;  // ragged last tile always takes the masked path
+    tmin[blockIdx.x] = lo;
+    tmax[blockIdx.x] = hi;
+  }
 }
 
-__device__ __forceinline__ float fast_exp2(float x) {
+__device__ __forceinline__ float f2_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 
-template <int SW>
-__global__ void __launch_bounds__(att_threads(SW), 2)
-sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                const __grid_constant__ CUtensorMap tmV, const AttParams p) {
+// exp2 of two values on the FMA pipe instead of the special-function unit (16 results per clock and SM,
+// which is what bounds a softmax at head size 128): round to the nearest integer n with the 1.5·2^23
+// trick, a cubic for 2^f on f = x − n in [−0.5, 0.5] (relative error 7.5e-5, far below the bf16 rounding of
+// P), and n added into the exponent field. Inputs below −126 (masked scores arrive as −inf) give ~1e-38.
+__device__ __forceinline__ float2 f2_exp2_poly2(float2 x) {
+  x.x = fmaxf(x.x, -126.f);
+  x.y = fmaxf(x.y, -126.f);
+  const float2 magic = make_float2(12582912.f, 12582912.f);
+  const float2 t = fadd2(x, magic);
+  const float2 n = fadd2(t, make_float2(-12582912.f, -12582912.f));
+  const float2 f = ffma2(n, make_float2(-1.f, -1.f), x);
+  float2 q = ffma2(make_float2(0.0551716194f, 0.0551716194f), f, make_float2(0.242611118f, 0.242611118f));
+  q = ffma2(q, f, make_float2(0.693260995f, 0.693260995f));
+  q = ffma2(q, f, make_float2(0.999928074f, 0.999928074f));
+  float2 r;
+  r.x = __int_as_float(__float_as_int(q.x) + (__float_as_int(t.x) << 23));
+  r.y = __int_as_float(__float_as_int(q.y) + (__float_as_int(t.y) << 23));
+  return r;
+}
+// of every 8 pairs of scores, the pairs listed here take the FMA-pipe exponential
+// (none in the flash kernel: once the softmax warps were off the critical path, the tensor-core side bounded it
+// and the extra FMA-pipe instructions cost more than the shorter exponential phase gained)
+__device__ __forceinline__ constexpr bool f2_pair_on_fma(int pair) { return false && pair < 0; }
+// the column-sum kernel is bound by the exponentials alone: 3 of 8 pairs go to the FMA pipe
+__device__ __forceinline__ constexpr bool cs_pair_on_fma(int pair) { return (pair & 7) == 0 || (pair & 7) == 3 || (pair & 7) == 6; }
+
+// Rows of a query tile that TMA does not write (npos · gs < 128) are cleared once, so that their
+// scores are finite zeros.
+__device__ __forceinline__ void f2_zero_unused_rows(uint8_t* tile, int rows_used, int tid, int nthreads) {
+  const int n16 = (F2_T - rows_used) * 8 * 2;  // 16-byte units: rows x 8 units x 2 chunks
+  for (int u = tid; u < n16; u += nthreads) {
+    const int chunk = u / ((F2_T - rows_used) * 8);
+    const int rem = u % ((F2_T - rows_used) * 8);
+    const int row = rows_used + rem / 8;
+    *reinterpret_cast<uint4*>(tile + chunk * F2_CHUNK_BYTES + sw128_offset(row, rem % 8)) = make_uint4(0, 0, 0, 0);
+  }
+}
+
+__global__ void __launch_bounds__(F2_THREADS, 1)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const F2Params p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   if (smem_u32(smem) & 1023u) {  // swizzled tiles need a 1024-byte aligned window: report, do not run
     if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, STATUS_TIMEOUT_MISC);
     return;
   }
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + AttSmem::BAR);
-  uint64_t* q_full = bars + 0;
-  uint64_t* k_full = bars + 1;    // [4]
-  uint64_t* k_empty = bars + 5;   // [4]
-  uint64_t* v_full = bars + 9;    // [2]
-  uint64_t* v_empty = bars + 11;  // [2]
-  uint64_t* s_full = bars + 13;
-  uint64_t* s_empty = bars + 14;
-  uint64_t* p_full = bars + 15;
-  uint64_t* p_empty = bars + 16;
-  uint64_t* o_full = bars + 17;
-  uint64_t* q_ready = bars + 18;  // Q has been moved from shared memory to TMEM
-  uint64_t* grp_bar = bars + 19;  // barrier among the 256 softmax threads (bounded, unlike bar.sync)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + F2Smem::BAR);
+  uint64_t* q_full = bars + 0;     // [2]
+  uint64_t* kv_full = bars + 2;    // [4]
+  uint64_t* kv_empty = bars + 6;   // [4]
+  uint64_t* s_full = bars + 10;    // [2]
+  uint64_t* p_full = bars + 12;    // [2]
+  uint64_t* o_full = bars + 14;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint8_t* tflags = smem + F2Smem::TF;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // block -> (query tile, group, batch); query tiles fastest so that co-resident CTAs share K/V in L2
-  const int qt = blockIdx.x % p.nQT;
-  const int g = (blockIdx.x / p.nQT) % p.G;
-  const int b = blockIdx.x / (p.nQT * p.G);
-  const int t0 = qt * p.npos;
+  const int nPair = (p.nQT + 1) / 2;
+  const int pair = blockIdx.x % nPair;
+  const int g = (blockIdx.x / nPair) % p.G;
+  const int b = blockIdx.x / (nPair * p.G);
+  const int t0 = 2 * pair * p.npos;  // first position of the pair
   const int qpos_min = p.input_pos + t0;
-  const int qpos_max = p.input_pos + min(t0 + p.npos, p.T) - 1;
-  const int32_t* tmin = p.tile_min + ((long long)b * p.G + g) * p.nT;
-  const int32_t* tmax = p.tile_max + ((long long)b * p.G + g) * p.nT;
+  const int qpos_max = p.input_pos + min(t0 + 2 * p.npos, p.T) - 1;
+  const long long bg = (long long)b * p.G + g;
+  const int32_t* tmin = p.tile_min + bg * p.nT;
+  const int32_t* tmax = p.tile_max + bg * p.nT;
 
-  // (active, masked) bits of the KV tiles for this query tile, so that no role reads global
-  // memory inside its tile loop
-  uint32_t* tflags = reinterpret_cast<uint32_t*>(smem + AttSmem::TF);
-  constexpr int TF_TILES = 1024;
-  for (int w = threadIdx.x; w < TF_TILES / 16; w += att_threads(SW)) {
-    uint32_t bits = 0;
-#pragma unroll 4
-    for (int i = 0; i < 16; ++i) {
-      const int t = w * 16 + i;
-      if (t < p.nT) bits |= ((uint32_t)(tmin[t] <= qpos_max) | ((uint32_t)(tmax[t] > qpos_min) << 1)) << (2 * i);
-    }
-    tflags[w] = bits;
-  }
-  // bit 0: active, bit 1: masked. Shared memory is slow to reach while the tensor core streams its
-  // operands from it, so each role keeps the word of 16 tiles in a register.
-  auto tile_bits = [&](int t, uint32_t& fw, int& fwi) -> uint32_t {
-    if (t >= TF_TILES) return (uint32_t)(tmin[t] <= qpos_max) | ((uint32_t)(tmax[t] > qpos_min) << 1);
-    if ((t >> 4) != fwi) {
-      fwi = t >> 4;
-      fw = tflags[fwi];
-    }
-    return (fw >> ((t & 15) * 2)) & 3u;
+  for (int t = threadIdx.x; t < min(p.nT, F2_MAX_FLAG_TILES); t += F2_THREADS)
+    tflags[t] = (uint8_t)((tmin[t] <= qpos_max) | ((tmax[t] > qpos_min) << 1));
+  auto tile_bits = [&](int t) -> uint32_t {
+    if (t >= F2_MAX_FLAG_TILES) return (uint32_t)(tmin[t] <= qpos_max) | ((uint32_t)(tmax[t] > qpos_min) << 1);
+    return tflags[t];
   };
-
+  if (p.rows_used < F2_T) {
+    f2_zero_unused_rows(smem + F2Smem::Q, p.rows_used, threadIdx.x, F2_THREADS);
+    f2_zero_unused_rows(smem + F2Smem::Q + F2_TILE_BYTES, p.rows_used, threadIdx.x, F2_THREADS);
+    fence_proxy_async_smem();
+  }
+  // bias operands: zero everywhere, then ones in column 0 of the A tile (the producer fills column 0 of the B tiles)
+  for (int u = threadIdx.x; u < (1 + F2_STAGES) * F2_BIAS_TILE_BYTES / 16; u += F2_THREADS)
+    *reinterpret_cast<uint4*>(smem + F2Smem::QX + 16 * u) = make_uint4(0, 0, 0, 0);
+  __syncthreads();
+  if (threadIdx.x < F2_T) *reinterpret_cast<uint16_t*>(smem + F2Smem::QX + f2_bias_offset(threadIdx.x)) = 0x3F80;  // bf16 1.0
+  fence_proxy_async_smem();
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
-    for (int s = 0; s < ATT_KSTAGES; ++s) {
-      mbar_init(&k_full[s], 1);
-      mbar_init(&k_empty[s], 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], 4);
     }
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&v_full[s], 1);
-      mbar_init(&v_empty[s], 1);
+    for (int s = 0; s < F2_STAGES; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
     }
-    mbar_init(s_full, 1);
-    mbar_init(s_empty, SW);
-    mbar_init(p_full, SW);
-    mbar_init(p_empty, 1);
     mbar_init(o_full, 1);
-    mbar_init(q_ready, SW);
-    mbar_init(grp_bar, 32 * SW);
     *abort_flag = 0;
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, ATT_TMEM_COLS);
+    tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // Q stays in TMEM as the A operand of S = Q K^T, so that each QK MMA reads only K from shared
-  // memory. S has one buffer: the softmax warps pull a tile into registers and hand the buffer
-  // back at once, so that the next QK runs during their arithmetic.
-  const uint32_t tmem_Q = tmem_base;           // columns [0,64): 128 features as bf16 pairs
-  const uint32_t tmem_S = tmem_base + 64;      // columns [64,128)
-  const uint32_t tmem_O = tmem_base + 128;     // columns [128,256)
-
+  // columns: S0 [0,128) | S1 [128,256) | O0 [256,384) | O1 [384,512); P aliases the first 64 columns of its S
   int n_active = 0;
-  for (int w = 0; w < TF_TILES / 16; ++w) n_active += __popc(tflags[w] & 0x55555555u);
-  for (int t = TF_TILES; t < p.nT; ++t) n_active += (tmin[t] <= qpos_max);
+  for (int t = 0; t < p.nT; ++t) n_active += (int)(tile_bits(t) & 1u);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0 && n_active > 0) {
-      tma_prefetch_desc(&tmQ);
-      tma_prefetch_desc(&tmK);
-      tma_prefetch_desc(&tmV);
-      mbar_expect_tx(q_full, ATT_Q_BYTES);
-      tma_load_4d(smem + AttSmem::Q, &tmQ, q_full, 0, t0, g * p.gs, b);
-      tma_load_4d(smem + AttSmem::Q + ATT_Q_BYTES / 2, &tmQ, q_full, 64, t0, g * p.gs, b);
-      uint32_t i = 0, j = 0;
-      bool ok = true;
-      int tr_n = 0;
-      uint32_t fw = 0;
-      int fwi = -1;
-      for (int sweep = 0; sweep < 2 && ok; ++sweep) {
-        for (int t = 0; t < p.nT && ok; ++t) {
-          if (!(tile_bits(t, fw, fwi) & 1u)) continue;
-          const int ks = i % ATT_KSTAGES;
-          // stages 2 and 3 first hold Q
-          if (i == 2 && !mbar_wait_bounded(q_ready, 0, abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) { ok = false; break; }
-          if (!mbar_wait_bounded(&k_empty[ks], ((i / ATT_KSTAGES) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) { ok = false; break; }
-          ATT_TRACE(0, 100000 + sweep * 50000 + t);
-          uint8_t* kd = smem + AttSmem::K + ks * ATT_KV_BYTES;
-          mbar_expect_tx(&k_full[ks], ATT_KV_BYTES);
-          tma_load_4d(kd, &tmK, &k_full[ks], 0, t * ATT_BN, g, b);
-          tma_load_4d(kd + ATT_KV_BYTES / 2, &tmK, &k_full[ks], 64, t * ATT_BN, g, b);
-          ++i;
-          if (sweep == 1) {
-            const int vs = j & 1;
-            if (!mbar_wait_bounded(&v_empty[vs], ((j >> 1) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) { ok = false; break; }
-            uint8_t* vd = smem + AttSmem::V + vs * ATT_KV_BYTES;
-            mbar_expect_tx(&v_full[vs], ATT_KV_BYTES);
-            tma_load_4d(vd, &tmV, &v_full[vs], 0, t * ATT_BN, g, b);
-            tma_load_4d(vd + ATT_KV_BYTES / 2, &tmV, &v_full[vs], 64, t * ATT_BN, g, b);
-            ++j;
-          }
+    // Lane 0 issues the copies; all lanes write the bias column of a masked K tile (4 slots per lane).
+    if (n_active > 0) {
+      if (lane == 0) {
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+        const uint32_t q_bytes = (uint32_t)p.rows_used * 128u * 2u;
+        for (int w = 0; w < 2; ++w) {
+          uint8_t* qd = smem + F2Smem::Q + w * F2_TILE_BYTES;
+          mbar_expect_tx(&q_full[w], q_bytes);
+          tma_load_4d(qd, &tmQ, &q_full[w], 0, g * p.gs, t0 + w * p.npos, b);
+          tma_load_4d(qd + F2_CHUNK_BYTES, &tmQ, &q_full[w], 64, g * p.gs, t0 + w * p.npos, b);
         }
       }
-      if (!ok) {  // let copies in flight land before the CTA's shared memory is released
+      const int32_t* pos_row = p.pos + bg * p.nT * F2_T;
+      uint32_t seq = 0;
+      bool ok = true;
+      F2_TRACE_DECL(lane == 0);
+      int4 pv_next = make_int4(0, 0, 0, 0);
+      {
+        int tf = 0;
+        while (tf < p.nT && !(tile_bits(tf) & 1u)) ++tf;
+        if (tf < p.nT && (tile_bits(tf) & 2u)) pv_next = __ldg(reinterpret_cast<const int4*>(pos_row + (long long)tf * F2_T) + lane);
+      }
+      for (int t = 0; t < p.nT && ok; ++t) {
+        const uint32_t tb = tile_bits(t);
+        if (!(tb & 1u)) continue;
+        for (int kv = 0; kv < 2 && ok; ++kv) {
+          const int st = seq % F2_STAGES;
+          int4 pv = pv_next;
+          if (kv == 0) {
+            // positions of the next active tile travel while this one is handled
+            int tn = t + 1;
+            while (tn < p.nT && !(tile_bits(tn) & 1u)) ++tn;
+            if (tn < p.nT && (tile_bits(tn) & 2u)) pv_next = __ldg(reinterpret_cast<const int4*>(pos_row + (long long)tn * F2_T) + lane);
+          }
+          F2_MARK(2);
+          ok = mbar_wait_bounded(&kv_empty[st], ((seq / F2_STAGES) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_EMPTY);
+          F2_MARK(kv);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          if (kv == 0 && (tb & 2u)) {
+            uint8_t* kx = smem + F2Smem::KX + st * F2_BIAS_TILE_BYTES;
+            *reinterpret_cast<uint16_t*>(kx + f2_bias_offset(4 * lane + 0)) = pv.x > qpos_max ? 0xFF80 : 0;  // bf16 -inf
+            *reinterpret_cast<uint16_t*>(kx + f2_bias_offset(4 * lane + 1)) = pv.y > qpos_max ? 0xFF80 : 0;
+            *reinterpret_cast<uint16_t*>(kx + f2_bias_offset(4 * lane + 2)) = pv.z > qpos_max ? 0xFF80 : 0;
+            *reinterpret_cast<uint16_t*>(kx + f2_bias_offset(4 * lane + 3)) = pv.w > qpos_max ? 0xFF80 : 0;
+            fence_proxy_async_smem();
+            __syncwarp();
+          }
+          if (lane == 0) {
+            uint8_t* d = smem + F2Smem::KV + st * F2_TILE_BYTES;
+            const CUtensorMap* tm = kv == 0 ? &tmK : &tmV;
+            mbar_expect_tx(&kv_full[st], F2_TILE_BYTES);
+            tma_load_4d(d, tm, &kv_full[st], 0, t * F2_T, g, b);
+            tma_load_4d(d + F2_CHUNK_BYTES, tm, &kv_full[st], 64, t * F2_T, g, b);
+          }
+          ++seq;
+        }
+      }
+      F2_TRACE_STORE(3);
+      if (!ok && lane == 0) {  // let copies in flight land before the CTA's shared memory is released
         long long c0 = clock64();
         while (clock64() - c0 < 2000000LL) {
         }
@@ -300,392 +379,550 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer
     if (lane == 0 && n_active > 0) {
-      constexpr uint32_t idesc_qk = make_idesc_bf16(ATT_BM, ATT_BN, 0, 0);  // Q, K both K-major
-      constexpr uint32_t idesc_pv = make_idesc_bf16(ATT_BM, ATT_D, 0, 1);   // P K-major, V MN-major
-      const uint32_t p_addr = smem_u32(smem + AttSmem::P);
-      bool ok = mbar_wait_bounded(q_ready, 0, abort_flag, p.status, STATUS_TIMEOUT_FULL);
+      constexpr uint32_t idesc_qk = make_idesc_bf16(F2_T, F2_T, 0, 0);  // Q, K both K-major
+      constexpr uint32_t idesc_pv = make_idesc_bf16(F2_T, F2_T, 0, 1);  // P K-major (TMEM), V MN-major
+      bool ok = true;
+      F2_TRACE_DECL(true);
+      for (int w = 0; w < 2 && ok; ++w) ok = mbar_wait_bounded(&q_full[w], 0, abort_flag, p.status, STATUS_TIMEOUT_FULL);
       tc_fence_after();
-      uint32_t i = 0, j = 0;
-      int tr_n = 0;
-      auto issue_qk = [&]() -> bool {
-        const int ks = i % ATT_KSTAGES;
-        ATT_TRACE(1, 1000000 + i);
-        if (!mbar_wait_bounded(&k_full[ks], (i / ATT_KSTAGES) & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL)) return false;
-        ATT_TRACE(1, 1100000 + i);
-        if (!mbar_wait_bounded(s_empty, (i & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) return false;
-        ATT_TRACE(1, 1200000 + i);
-        tc_fence_after();
-        const uint32_t k_addr = smem_u32(smem + AttSmem::K + ks * ATT_KV_BYTES);
+      // stages are used in the order K0 V0 K1 V1 ...: tile i reads K from sequence number 2i and V from 2i + 1
+      auto stage_addr = [&](uint32_t s) { return smem_u32(smem + F2Smem::KV + (s % F2_STAGES) * F2_TILE_BYTES); };
+      auto wait_stage = [&](uint32_t s) {
+        return mbar_wait_bounded(&kv_full[s % F2_STAGES], (s / F2_STAGES) & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL);
+      };
+      auto issue_qk = [&](int w, uint32_t kseq, bool masked) {
+        const uint32_t q_addr = smem_u32(smem + F2Smem::Q + w * F2_TILE_BYTES);
+        const uint32_t k_addr = stage_addr(kseq);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          // 16 features per step: 8 TMEM columns of Q; chunk kk/4 of K, 32 bytes per step inside the swizzled row
-          const uint32_t k_off = (uint32_t)((kk >> 2) * (ATT_KV_BYTES / 2) + (kk & 3) * 32);
-          umma_f16_ts(tmem_S, tmem_Q + 8 * kk, make_smem_desc_sw128(k_addr + k_off, 16, 1024), idesc_qk, kk != 0);
+          // 16 features per step: chunk kk/4, 32 bytes per step inside the swizzled 128-byte row
+          const uint32_t off = (uint32_t)((kk >> 2) * F2_CHUNK_BYTES + (kk & 3) * 32);
+          umma_f16_ss(tmem_base + (uint32_t)(w * F2_T), make_smem_desc_sw128(q_addr + off, 16, 1024),
+                      make_smem_desc_sw128(k_addr + off, 16, 1024), idesc_qk, kk != 0);
         }
-        umma_commit(&k_empty[ks]);
-        umma_commit(s_full);
-        ATT_TRACE(1, 1300000 + i);
-        ++i;
-        return true;
+        if (masked)  // S += 1 · bias^T: -inf for the slots that no row of this CTA may see
+          umma_f16_ss(tmem_base + (uint32_t)(w * F2_T), f2_bias_desc(smem_u32(smem + F2Smem::QX)),
+                      f2_bias_desc(smem_u32(smem + F2Smem::KX + (kseq % F2_STAGES) * F2_BIAS_TILE_BYTES)), idesc_qk, 1);
+        umma_commit(&s_full[w]);
       };
-      auto issue_pv = [&]() -> bool {
-        const int vs = j & 1;
-        ATT_TRACE(1, 2000000 + j);
-        // V first: it does not depend on the softmax, so only the wait for P is on the critical path
-        if (!mbar_wait_bounded(&v_full[vs], (j >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL)) return false;
-        ATT_TRACE(1, 2100000 + j);
-        if (!mbar_wait_bounded(p_full, j & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL)) return false;
-        ATT_TRACE(1, 2200000 + j);
-        tc_fence_after();
-        const uint32_t v_addr = smem_u32(smem + AttSmem::V + vs * ATT_KV_BYTES);
+      // the issuer walks the active tiles in step with the producer
+      int t_next = 0;
+      auto next_active_masked = [&]() -> bool {
+        while (t_next < p.nT && !(tile_bits(t_next) & 1u)) ++t_next;
+        const bool m = t_next < p.nT && (tile_bits(t_next) & 2u);
+        ++t_next;
+        return m;
+      };
+      auto issue_pv = [&](int w, uint32_t vseq, bool first) {
+        const uint32_t v_addr = stage_addr(vseq);
 #pragma unroll
-        for (int kk = 0; kk < ATT_BN / 16; ++kk) {
-          // A = P: K-major, 16 kv columns (32 B) per step inside the single 64-column chunk
-          const uint32_t a_off = (uint32_t)(kk * 32);
-          // B = V: MN-major; 16 kv rows per step (2048 B); the two 64-wide d chunks are LBO apart
-          const uint32_t b_off = (uint32_t)(kk * 16 * 128);
-          umma_f16_ss(tmem_O, make_smem_desc_sw128(p_addr + a_off, 16, 1024),
-                      make_smem_desc_sw128(v_addr + b_off, ATT_KV_BYTES / 2, 1024), idesc_pv, (j | kk) != 0);
+        for (int kk = 0; kk < 8; ++kk) {
+          // A = P from TMEM: 16 slots = 8 columns of packed bf16 pairs per step.
+          // B = V: MN-major; 16 slot rows per step (2048 B); the two 64-wide feature chunks are LBO apart.
+          umma_f16_ts(tmem_base + (uint32_t)(2 * F2_T + w * F2_T), tmem_base + (uint32_t)(w * F2_T + 8 * kk),
+                      make_smem_desc_sw128(v_addr + (uint32_t)(kk * 16 * 128), F2_CHUNK_BYTES, 1024), idesc_pv,
+                      (first && kk == 0) ? 0u : 1u);
         }
-        umma_commit(&v_empty[vs]);
-        umma_commit(p_empty);
-        ATT_TRACE(1, 2300000 + j);
-        ++j;
-        return true;
       };
-      // sweep 1: S only
-      uint32_t fw = 0;
-      int fwi = -1;
-      for (int t = 0; t < p.nT && ok; ++t) {
-        if (!(tile_bits(t, fw, fwi) & 1u)) continue;
-        ok = issue_qk();
+      // prologue: S0 and S1 of the first tile
+      if (ok) ok = wait_stage(0);
+      if (ok) {
+        tc_fence_after();
+        const bool m0 = next_active_masked();
+        issue_qk(0, 0, m0);
+        issue_qk(1, 0, m0);
+        umma_commit(&kv_empty[0]);
       }
-      // sweep 2: QK of the next tile is issued before PV of the current one
-      bool pending = false;
-      for (int t = 0; t < p.nT && ok; ++t) {
-        if (!(tile_bits(t, fw, fwi) & 1u)) continue;
-        ok = issue_qk();
-        if (ok && pending) ok = issue_pv();
-        pending = true;
+      for (int i = 0; i < n_active && ok; ++i) {
+        const uint32_t vseq = 2u * i + 1, knext = 2u * i + 2;
+        const bool more = i + 1 < n_active;
+        F2_MARK(6);
+        if (!(ok = wait_stage(vseq))) break;
+        F2_MARK(4);
+        if (more && !(ok = wait_stage(knext))) break;
+        F2_MARK(5);
+        const bool m_next = more ? next_active_masked() : false;
+        for (int w = 0; w < 2 && ok; ++w) {
+          F2_MARK(6);
+          if (!(ok = mbar_wait_bounded(&p_full[w], i & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL))) break;
+          F2_MARK(2 * w);
+          tc_fence_after();
+          issue_pv(w, vseq, i == 0);
+          if (w == 1) umma_commit(&kv_empty[vseq % F2_STAGES]);
+          if (more) {
+            issue_qk(w, knext, m_next);
+            if (w == 1) umma_commit(&kv_empty[knext % F2_STAGES]);
+          }
+          F2_MARK(2 * w + 1);
+        }
       }
-      if (ok && pending) ok = issue_pv();
       if (ok) umma_commit(o_full);
+      F2_TRACE_STORE(0);
     }
   } else {
     // ------------------------------------------------- softmax + epilogue warps
-    // 8 warps: two per TMEM lane quarter. A thread owns one query row (its TMEM lane) and 32 of the
-    // 64 columns of every KV tile (hh = which half), so the serial chain of a tile (barrier wait,
-    // TMEM load, exp2, P store, column sums) is half as long per warp and four warps per SM
-    // sub-partition (two CTAs) fill each other's latencies.
-    const int quarter = warp & 3;
-    const int hh = SW == 8 ? (warp - 2) >> 2 : 0;
-    constexpr int NC = SW == 8 ? ATT_BN / 2 : ATT_BN;  // columns per thread
-    constexpr int NW = NC / 32;                       // 32-column words per thread
-    const int row = quarter * 32 + lane;          // TMEM lane = query row of the tile
-    const int hq = row / p.npos;                  // head within the group
-    const int pl = row % p.npos;                  // position within the tile
-    const int tq = t0 + pl;
-    const bool row_valid = tq < p.T;
+    const int wg = (warp - 2) >> 2;               // which query tile of the pair
+    const int quarter = warp & 3;                 // TMEM lane quarter this warp may access
+    const int row = quarter * 32 + lane;          // TMEM lane = packed query row
+    const int pl = row / p.gs, hq = row % p.gs;   // position within the tile, head within the group
+    const int qt = 2 * pair + wg;
+    const int tq = qt * p.npos + pl;
+    const bool row_valid = row < p.rows_used && tq < p.T;
     const int my_pos = p.input_pos + tq;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tmem_S = tmem_base + (uint32_t)(wg * F2_T) + lane_base;
+    const uint32_t tmem_O = tmem_base + (uint32_t)(2 * F2_T + wg * F2_T) + lane_base;
     const float c = p.scale_log2;
     const float2 c2 = make_float2(c, c);
-    bool ok = n_active > 0;
-    uint32_t i = 0, j = 0;
-    float m = -1e30f, l = 0.f;
-    int tr_n = (warp == 2 && lane == 0) ? 0 : (1 << 30);  // only the first softmax warp records
-    uint32_t fw = 0;
-    int fwi = -1;
-    // Token positions of a tile: lane holds columns lane and lane + 32 (INT_MAX beyond the cache).
-    // The positions of the next tile are fetched one tile ahead.
-    const int32_t* tpp = p.token_pos ? p.token_pos + b * p.tp_sb + g * p.tp_sg : nullptr;
-    // lane holds columns NC·hh + 32·w + lane (w < NW) of the tile
-    auto fetch_tp = [&](int t, int (&v)[NW]) {
+    const int32_t* pos_row = p.pos + bg * p.nT * F2_T;
+    // smallest and largest position among the 32 rows of this warp (rows beyond the query included)
+    int wpos_min = my_pos, wpos_max = my_pos;
 #pragma unroll
-      for (int w = 0; w < NW; ++w) {
-        const int j0 = t * ATT_BN + NC * hh + 32 * w + lane;
-        v[w] = j0 < p.L ? (tpp ? tpp[j0] : j0) : INT_MAX;
-      }
-    };
-    int pf[NW], pf_t = -1;
-#pragma unroll
-    for (int w = 0; w < NW; ++w) pf[w] = INT_MAX;
-    // Mask bits of this thread's row for a masked tile (bit e of word w: column 32·w + e of the thread's
-    // columns is hidden). Only columns whose token lies beyond the first query of the CTA need the
-    // per-row comparison; their positions are broadcast by shuffle, so no shared memory is involved.
-    auto row_mask = [&](const int (&v)[NW], uint32_t (&mk)[NW]) {
-#pragma unroll
-      for (int w = 0; w < NW; ++w) {
-        uint32_t n0 = __ballot_sync(0xffffffffu, v[w] > qpos_min);
-        mk[w] = 0;
-        while (n0) {
-          const int e = __ffs(n0) - 1;
-          n0 &= n0 - 1;
-          mk[w] |= (uint32_t)(__shfl_sync(0xffffffffu, v[w], e) > my_pos) << e;
-        }
-      }
-    };
-    uint32_t grp_phase = 0;
-    auto group_sync = [&]() -> bool {  // all 256 softmax threads; false if it ran into the wait limit
-      mbar_arrive(grp_bar);
-      const bool done = mbar_wait_bounded(grp_bar, grp_phase, abort_flag, p.status, STATUS_TIMEOUT_MISC);
-      grp_phase ^= 1;
-      return done;
-    };
-    // column-sum partials: slot (4·qt + warp quarter) of wpart (B,G,4·nQT,L). A warp sums the 32
-    // rows x 32 columns that it wrote itself, so the column sums need no barrier among the warps.
-    float* wbase = p.wpart ? p.wpart + ((((long long)b * p.G + g) * (4 * p.nQT) + 4 * qt + quarter) * p.L) : nullptr;
-    if (n_active == 0 && wbase) {
-      for (int jj = NC * hh + lane; jj < p.L; jj += 32)
-        if ((jj % ATT_BN) / NC == hh) wbase[jj] = 0.f;
+    for (int o = 16; o > 0; o >>= 1) {
+      wpos_min = min(wpos_min, __shfl_xor_sync(0xffffffffu, wpos_min, o));
+      wpos_max = max(wpos_max, __shfl_xor_sync(0xffffffffu, wpos_max, o));
     }
-    const uint32_t NEG_INF_BITS = 0xff800000u;
-
-    // ---- Q: shared memory -> registers -> TMEM (row = lane; feature pair f/2 = column)
-    if (ok) ok = mbar_wait_bounded(q_full, 0, abort_flag, p.status, STATUS_TIMEOUT_FULL);
-    if (ok) {
+    // Positions of the slots of the next masked tile (lane holds slots 4·lane .. 4·lane+3): requested one
+    // tile ahead, because they come from L2 and are needed the moment the tile's scores are complete.
+    int4 pf_v = make_int4(0, 0, 0, 0);
+    int pf_t = -1;
+    auto request_positions = [&](int t) {
+      pf_v = __ldg(reinterpret_cast<const int4*>(pos_row + (long long)t * F2_T) + lane);
+      pf_t = t;
+    };
+    auto next_active = [&](int t) {
+      int tn = t + 1;
+      while (tn < p.nT && !(tile_bits(tn) & 1u)) ++tn;
+      return tn;
+    };
+    bool ok = n_active > 0;
+    float m_used = -1e30f, l = 0.f;
+    int i = 0;
+    F2_TRACE_DECL((warp == 2 || warp == 6) && lane == 0);  // the first warp of each warpgroup records
+    {
+      const int tf = next_active(-1);
+      if (ok && tf < p.nT && (tile_bits(tf) & 2u)) request_positions(tf);
+    }
+    for (int t = 0; t < p.nT && ok; ++t) {
+      const uint32_t tb = tile_bits(t);
+      if (!(tb & 1u)) continue;
+      // Masks. Slots beyond the last query of the CTA arrive as -inf from the MMA. What is left are slots
+      // whose token lies between the first row of this warp and the last query of the CTA: few over an
+      // evicting cache, and then patched column by column in TMEM before the tile is read (a column
+      // address may be a run-time value, a register index may not); many on the diagonal of plain causal
+      // attention, and then the tile is compared element by element and written back.
+      uint32_t m_all[4] = {0, 0, 0, 0}, m_some[4] = {0, 0, 0, 0};
+      int mpos[4] = {0, 0, 0, 0};
+      int n_cand = 0;
+      if (tb & 2u) {
+        if (pf_t != t) request_positions(t);
+        mpos[0] = pf_v.x; mpos[1] = pf_v.y; mpos[2] = pf_v.z; mpos[3] = pf_v.w;
 #pragma unroll
-      for (int ch = (SW == 8 ? hh : 0); ch < (SW == 8 ? hh + 1 : 2); ++ch) {  // feature chunk(s) that this warp moves
-        const uint8_t* src = smem + AttSmem::Q + ch * (ATT_Q_BYTES / 2);
-        uint32_t w[32];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const uint4 q4 = *reinterpret_cast<const uint4*>(src + sw128_offset(row, u));
-          w[4 * u] = q4.x; w[4 * u + 1] = q4.y; w[4 * u + 2] = q4.z; w[4 * u + 3] = q4.w;
+        for (int cc = 0; cc < 4; ++cc) {
+          const uint32_t cand = __ballot_sync(0xffffffffu, mpos[cc] > wpos_min && mpos[cc] <= qpos_max);
+          m_all[cc] = __ballot_sync(0xffffffffu, mpos[cc] > wpos_max && mpos[cc] <= qpos_max);
+          m_some[cc] = cand & ~m_all[cc];
+          n_cand += __popc(cand);
         }
-        tmem_st_32x32b_x16(tmem_Q + lane_base + (uint32_t)(32 * ch), w);
-        tmem_st_32x32b_x16(tmem_Q + lane_base + (uint32_t)(32 * ch + 16), w + 16);
       }
+      {
+        const int tn = next_active(t);
+        if (tn < p.nT && (tile_bits(tn) & 2u)) request_positions(tn);
+      }
+      F2_MARK(6);
+      if (!mbar_wait_bounded(&s_full[wg], i & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) {
+        ok = false;
+        break;
+      }
+      F2_MARK(0);
+      tc_fence_after();
+      if (n_cand > F2_PATCH_MAX_COLS) {
+        // element by element: the masked tile goes back to TMEM, the two passes below read it from there
+        const int4* pp = reinterpret_cast<const int4*>(pos_row + (long long)t * F2_T);
+#pragma unroll 1
+        for (int c0 = 0; c0 < F2_T; c0 += 32) {
+          uint32_t x[32];
+          tmem_ld_32x32b_x32(tmem_S + (uint32_t)c0, x);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; e += 4) {
+            const int4 v = __ldg(pp + ((c0 + e) >> 2));
+            if (v.x > my_pos) x[e] = 0xff800000u;
+            if (v.y > my_pos) x[e + 1] = 0xff800000u;
+            if (v.z > my_pos) x[e + 2] = 0xff800000u;
+            if (v.w > my_pos) x[e + 3] = 0xff800000u;
+          }
+          tmem_st_32x32b_x16(tmem_S + (uint32_t)c0, x);
+          tmem_st_32x32b_x16(tmem_S + (uint32_t)(c0 + 16), x + 16);
+        }
+        tmem_st_wait();
+      } else if (n_cand > 0) {
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          uint32_t bits = m_all[cc];  // hidden from every row of this warp: no need to look at the scores
+          while (bits) {
+            const int src = __ffs(bits) - 1;
+            bits &= bits - 1;
+            tmem_st_32x32b_x1(tmem_S + (uint32_t)(4 * src + cc), 0xff800000u);
+          }
+          bits = m_some[cc];          // hidden from some rows
+          while (bits) {
+            const int src = __ffs(bits) - 1;
+            bits &= bits - 1;
+            const int pe = __shfl_sync(0xffffffffu, mpos[cc], src);
+            const uint32_t col = tmem_S + (uint32_t)(4 * src + cc);
+            uint32_t a = tmem_ld_32x32b_x1(col);
+            tmem_ld_wait();
+            if (pe > my_pos) a = 0xff800000u;
+            tmem_st_32x32b_x1(col, a);
+          }
+        }
+        tmem_st_wait();
+      }
+      F2_MARK(1);
+      // pass 1: maximum of the row; the scores stay in TMEM, 32 of them are in registers at a time
+      float a8[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) a8[u] = -INFINITY;
+      {
+        uint32_t x[2][32];
+        tmem_ld_32x32b_x32(tmem_S, x[0]);
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          tmem_ld_wait();
+          if (w < 3) tmem_ld_32x32b_x32(tmem_S + (uint32_t)(32 * (w + 1)), x[(w + 1) & 1]);
+#pragma unroll
+          for (int e = 0; e < 32; e += 16) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              a8[u] = fmax3(a8[u], __uint_as_float(x[w & 1][e + 2 * u]), __uint_as_float(x[w & 1][e + 2 * u + 1]));
+          }
+        }
+      }
+      F2_MARK(2);
+      const float m_tile = fmax3(fmax3(a8[0], a8[1], a8[2]), fmax3(a8[3], a8[4], a8[5]), fmaxf(a8[6], a8[7])) * c;  // -inf: all hidden
+      // raise the reference maximum of the row only when it grows by more than the step
+      const bool raise = m_tile > m_used + F2_RESCALE_STEP;
+      const float m_new = raise ? m_tile : m_used;
+      if (i > 0 && __any_sync(0xffffffffu, raise)) {
+        // the PV MMA of the previous tile finished before this tile's S was signalled: O may be rescaled
+        const float f = raise ? f2_exp2(m_used - m_new) : 1.f;
+        l *= f;
+#pragma unroll 1
+        for (int c0 = 0; c0 < F2_T; c0 += 32) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(tmem_O + (uint32_t)c0, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * f);
+          tmem_st_32x32b_x16(tmem_O + (uint32_t)c0, o);
+          tmem_st_32x32b_x16(tmem_O + (uint32_t)(c0 + 16), o + 16);
+        }
+      }
+      m_used = m_new;
+      F2_MARK(3);
+      // pass 2: P = exp2(S·c − m) as packed bf16 into the first 64 columns of S. Chunk u of the scores
+      // (columns 32u ..) is in registers before P of chunk u (columns 16u ..) overwrites older columns.
+      const float2 neg_m2 = make_float2(-m_used, -m_used);
+      float2 s0 = make_float2(0.f, 0.f), s1 = s0;
+      {
+        uint32_t x[2][32];
+        tmem_ld_32x32b_x32(tmem_S, x[0]);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          tmem_ld_wait();
+          if (u < 3) tmem_ld_32x32b_x32(tmem_S + (uint32_t)(32 * (u + 1)), x[(u + 1) & 1]);
+          uint32_t pk[16];
+#pragma unroll
+          for (int e = 0; e < 32; e += 4) {
+            const float2 x0 = ffma2(make_float2(__uint_as_float(x[u & 1][e]), __uint_as_float(x[u & 1][e + 1])), c2, neg_m2);
+            const float2 x1 = ffma2(make_float2(__uint_as_float(x[u & 1][e + 2]), __uint_as_float(x[u & 1][e + 3])), c2, neg_m2);
+            const float2 y0 = f2_pair_on_fma(e >> 1) ? f2_exp2_poly2(x0) : make_float2(f2_exp2(x0.x), f2_exp2(x0.y));
+            const float2 y1 = f2_pair_on_fma((e >> 1) + 1) ? f2_exp2_poly2(x1) : make_float2(f2_exp2(x1.x), f2_exp2(x1.y));
+            s0 = fadd2(s0, y0);
+            s1 = fadd2(s1, y1);
+            pk[e >> 1] = pack_bf16x2(y0.x, y0.y);
+            pk[(e >> 1) + 1] = pack_bf16x2(y1.x, y1.y);
+          }
+          // the load of chunk u + 1 (columns 32(u+1) ..) must have left TMEM before P of chunk u lands on
+          // columns 16u .. 16u+15 only if those overlap, which they never do (16u + 16 <= 32(u + 1))
+          tmem_st_32x32b_x16(tmem_S + (uint32_t)(16 * u), pk);
+        }
+      }
+      s0 = fadd2(s0, s1);
+      l += s0.x + s0.y;
+      F2_MARK(4);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(q_ready);
-    }
-
-    // ---- sweep 1: exact row max and sum over this thread's 32 columns of every tile
-    for (int t = 0; t < p.nT && ok; ++t) {
-      const uint32_t tb = tile_bits(t, fw, fwi);
-      if (!(tb & 1u)) continue;
-      const bool masked = (tb & 2u) != 0;
-      int v0[NW];
-#pragma unroll
-      for (int w = 0; w < NW; ++w) v0[w] = pf[w];
-      if (masked && pf_t != t) fetch_tp(t, v0);
-      if (t + 1 < p.nT) {
-        fetch_tp(t + 1, pf);
-        pf_t = t + 1;
-      }
-      ATT_TRACE(2, 3000000 + i);
-      if (!mbar_wait_bounded(s_full, i & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
-      ATT_TRACE(2, 3100000 + i);
-      tc_fence_after();
-      uint32_t r[NC];
-#pragma unroll
-      for (int w = 0; w < NW; ++w) tmem_ld_32x32b_x32(tmem_S + lane_base + (uint32_t)(NC * hh + 32 * w), r + 32 * w);
-      tmem_ld_wait();
-      ATT_TRACE(2, 3200000 + i);
-      // the tile is in registers: hand the S buffer back before the arithmetic
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(s_empty);
+      if (lane == 0) mbar_arrive(&p_full[wg]);
+      F2_MARK(5);
       ++i;
-      if (masked) {
-        uint32_t mk[NW];
-        row_mask(v0, mk);
-#pragma unroll
-        for (int e = 0; e < NC; ++e)
-          if (mk[e >> 5] & (1u << (e & 31))) r[e] = NEG_INF_BITS;
-      }
-      // max of the raw scores (the scale is positive): four independent chains of 3-input max
-      float a0 = -INFINITY, a1 = -INFINITY, a2 = -INFINITY, a3 = -INFINITY;
-#pragma unroll
-      for (int e = 0; e < NC; e += 8) {
-        a0 = fmax3(a0, __uint_as_float(r[e]), __uint_as_float(r[e + 1]));
-        a1 = fmax3(a1, __uint_as_float(r[e + 2]), __uint_as_float(r[e + 3]));
-        a2 = fmax3(a2, __uint_as_float(r[e + 4]), __uint_as_float(r[e + 5]));
-        a3 = fmax3(a3, __uint_as_float(r[e + 6]), __uint_as_float(r[e + 7]));
-      }
-      const float m_new = fmaxf(m, fmax3(a0, a1, fmaxf(a2, a3)) * c);
-      const float2 neg_m2 = make_float2(-m_new, -m_new);
-      float2 s0 = make_float2(0.f, 0.f), s1 = s0, s2 = s0, s3 = s0;
-#pragma unroll
-      for (int e = 0; e < NC; e += 8) {
-        float2 x0 = ffma2(make_float2(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), c2, neg_m2);
-        float2 x1 = ffma2(make_float2(__uint_as_float(r[e + 2]), __uint_as_float(r[e + 3])), c2, neg_m2);
-        float2 x2 = ffma2(make_float2(__uint_as_float(r[e + 4]), __uint_as_float(r[e + 5])), c2, neg_m2);
-        float2 x3 = ffma2(make_float2(__uint_as_float(r[e + 6]), __uint_as_float(r[e + 7])), c2, neg_m2);
-        s0 = fadd2(s0, make_float2(fast_exp2(x0.x), fast_exp2(x0.y)));
-        s1 = fadd2(s1, make_float2(fast_exp2(x1.x), fast_exp2(x1.y)));
-        s2 = fadd2(s2, make_float2(fast_exp2(x2.x), fast_exp2(x2.y)));
-        s3 = fadd2(s3, make_float2(fast_exp2(x3.x), fast_exp2(x3.y)));
-      }
-      s0 = fadd2(fadd2(s0, s1), fadd2(s2, s3));
-      l = l * fast_exp2(m - m_new) + (s0.x + s0.y);
-      m = m_new;
-      ATT_TRACE(2, 3300000 + i);
-    }
-    if (SW == 8) {
-      // merge (m, l) of the two column halves of a row through the P area, which is idle in sweep 1
-      float2* ml_x = reinterpret_cast<float2*>(smem + AttSmem::P);
-      ml_x[hh * ATT_BM + row] = make_float2(m, l);
-      if (ok && !group_sync()) ok = false;
-      if (ok) {
-        const float2 o = ml_x[(hh ^ 1) * ATT_BM + row];
-        const float mm = fmaxf(m, o.x);
-        l = l * fast_exp2(m - mm) + o.y * fast_exp2(o.x - mm);
-        m = mm;
-        if (!group_sync()) ok = false;  // everyone has read the exchange area before P tiles land in it
-      }
-    }
-    const float lse2 = l > 0.f ? m + log2f(l) : INFINITY;
-    // rows beyond the end of the query get P = 0 (their Q rows are zero-filled, so S = 0)
-    const float nl = row_valid ? -lse2 : -INFINITY;
-    const float2 neg_lse2 = make_float2(nl, nl);
-
-    // ---- sweep 2: P = exp2(S·c − lse), O += P V, column sums of P
-    uint8_t* Ps = smem + AttSmem::P;
-    for (int t = 0; t < p.nT && ok; ++t) {
-      float* wdst = wbase ? wbase + (long long)t * ATT_BN + NC * hh : nullptr;
-      const uint32_t tb = tile_bits(t, fw, fwi);
-      if (!(tb & 1u)) {
-        if (wdst) {
-#pragma unroll
-          for (int w = 0; w < NW; ++w)
-            if (t * ATT_BN + NC * hh + 32 * w + lane < p.L) wdst[32 * w + lane] = 0.f;
-        }
-        continue;
-      }
-      const bool masked = (tb & 2u) != 0;
-      int v0[NW];
-#pragma unroll
-      for (int w = 0; w < NW; ++w) v0[w] = pf[w];
-      if (masked && pf_t != t) fetch_tp(t, v0);
-      if (t + 1 < p.nT) {
-        fetch_tp(t + 1, pf);
-        pf_t = t + 1;
-      }
-      ATT_TRACE(2, 4000000 + i);
-      if (!mbar_wait_bounded(s_full, i & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
-      ATT_TRACE(2, 4100000 + i);
-      tc_fence_after();
-      uint32_t r[NC];
-#pragma unroll
-      for (int w = 0; w < NW; ++w) tmem_ld_32x32b_x32(tmem_S + lane_base + (uint32_t)(NC * hh + 32 * w), r + 32 * w);
-      tmem_ld_wait();
-      ATT_TRACE(2, 4200000 + i);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(s_empty);
-      ++i;
-      if (masked) {
-        uint32_t mk[NW];
-        row_mask(v0, mk);
-#pragma unroll
-        for (int e = 0; e < NC; ++e)
-          if (mk[e >> 5] & (1u << (e & 31))) r[e] = NEG_INF_BITS;
-      }
-      uint32_t pk[NC / 2];
-#pragma unroll
-      for (int e = 0; e < NC; e += 2) {
-        const float2 x = ffma2(make_float2(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), c2, neg_lse2);
-        pk[e >> 1] = pack_bf16x2(fast_exp2(x.x), fast_exp2(x.y));
-      }
-      // the PV MMA of the previous tile must have finished reading P
-      ATT_TRACE(2, 4300000 + i);
-      if (!mbar_wait_bounded(p_empty, (j & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_MISC)) { ok = false; break; }
-      ATT_TRACE(2, 4400000 + i);
-#pragma unroll
-      for (int u = 0; u < NC / 8; ++u) {
-        uint4 val = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
-        *reinterpret_cast<uint4*>(Ps + sw128_offset(row, (NC / 8) * hh + u)) = val;
-      }
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
-      ATT_TRACE(2, 4500000 + i);
-      ++j;
-      // column sums over this warp's 32 rows x NC columns of the P tile (as rounded to bf16):
-      // lane -> (column pair lane % (NC/2), part of the rows lane / (NC/2))
-      if (wdst) {
-        constexpr int NP = NC / 2;       // column pairs of this warp
-        constexpr int RPL = 32 / (32 / NP);  // rows per lane
-        float2 ca = make_float2(0.f, 0.f), cb = ca;
-        const int cp = lane % NP, rh = lane / NP;
-        const uint32_t coff = (uint32_t)((cp & 3) * 4);
-        const int cu = (NC / 8) * hh + (cp >> 2);
-#pragma unroll
-        for (int rr = 0; rr < RPL; rr += 2) {
-          const int r0 = quarter * 32 + rh * RPL + rr;
-          const uint32_t w0 = *reinterpret_cast<const uint32_t*>(Ps + sw128_offset(r0, cu) + coff);
-          const uint32_t w1 = *reinterpret_cast<const uint32_t*>(Ps + sw128_offset(r0 + 1, cu) + coff);
-          ca = fadd2(ca, make_float2(__uint_as_float(w0 << 16), __uint_as_float(w0 & 0xffff0000u)));
-          cb = fadd2(cb, make_float2(__uint_as_float(w1 << 16), __uint_as_float(w1 & 0xffff0000u)));
-        }
-        ca = fadd2(ca, cb);
-        if (NP < 32) {
-          ca.x += __shfl_xor_sync(0xffffffffu, ca.x, 16);
-          ca.y += __shfl_xor_sync(0xffffffffu, ca.y, 16);
-        }
-        if (rh == 0) {
-          if (t * ATT_BN + NC * hh + 2 * cp < p.L) wdst[2 * cp] = ca.x;
-          if (t * ATT_BN + NC * hh + 2 * cp + 1 < p.L) wdst[2 * cp + 1] = ca.y;
-        }
-        __syncwarp();  // all lanes have read the warp's rows before the next tile overwrites them
-      }
-      ATT_TRACE(2, 4600000 + i);
     }
 
-    // ---- epilogue: O (already normalised) -> bf16 -> out; lse
+    F2_TRACE_STORE(1 + wg);
+    // ---- epilogue: O / l -> bf16 -> out; normalisers
     if (ok) ok = mbar_wait_bounded(o_full, 0, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL);
     if (ok || n_active == 0) {
       tc_fence_after();
-      __nv_bfloat16* dst = p.out + (((long long)b * p.T + tq) * p.H + (g * p.gs + hq)) * ATT_D;
+      const float inv_l = l > 0.f ? 1.f / l : 0.f;
+      const float lse2 = l > 0.f ? m_used + log2f(l) : INFINITY;
+      // tcgen05.ld is warp-collective: rows without a query take part in the loads and skip the stores
+      __nv_bfloat16* dst = p.out + (((long long)b * p.T + (row_valid ? tq : 0)) * p.H + (g * p.gs + (row_valid ? hq : 0))) * F2_T;
 #pragma unroll 1
-      for (int c0 = (ATT_D / (SW / 4)) * hh; c0 < (ATT_D / (SW / 4)) * (hh + 1); c0 += 32) {
-        uint32_t r[32];
+      for (int c0 = 0; c0 < F2_T; c0 += 32) {
+        uint32_t o[32];
         if (n_active > 0) {
-          tmem_ld_32x32b_x32(tmem_O + lane_base + (uint32_t)c0, r);
+          tmem_ld_32x32b_x32(tmem_O + (uint32_t)c0, o);
           tmem_ld_wait();
         } else {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) r[e] = 0;
+          for (int e = 0; e < 32; ++e) o[e] = 0;
         }
         if (row_valid) {
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
-            uint4 o;
-            o.x = pack_bf16x2(__uint_as_float(r[8 * u + 0]), __uint_as_float(r[8 * u + 1]));
-            o.y = pack_bf16x2(__uint_as_float(r[8 * u + 2]), __uint_as_float(r[8 * u + 3]));
-            o.z = pack_bf16x2(__uint_as_float(r[8 * u + 4]), __uint_as_float(r[8 * u + 5]));
-            o.w = pack_bf16x2(__uint_as_float(r[8 * u + 6]), __uint_as_float(r[8 * u + 7]));
-            *reinterpret_cast<uint4*>(dst + c0 + 8 * u) = o;
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(o[8 * u + 0]) * inv_l, __uint_as_float(o[8 * u + 1]) * inv_l);
+            v.y = pack_bf16x2(__uint_as_float(o[8 * u + 2]) * inv_l, __uint_as_float(o[8 * u + 3]) * inv_l);
+            v.z = pack_bf16x2(__uint_as_float(o[8 * u + 4]) * inv_l, __uint_as_float(o[8 * u + 5]) * inv_l);
+            v.w = pack_bf16x2(__uint_as_float(o[8 * u + 6]) * inv_l, __uint_as_float(o[8 * u + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(dst + c0 + 8 * u) = v;
           }
         }
       }
-      if (hh == 0 && row_valid && p.lse) p.lse[((long long)b * p.H + (g * p.gs + hq)) * p.T + tq] = lse2 * 0.6931471805599453f;
+      if (row_valid && p.lse) p.lse[((long long)b * p.H + (g * p.gs + hq)) * p.T + tq] = lse2 * 0.6931471805599453f;
+      if (p.lse2 && qt < p.nQT) p.lse2[(bg * p.nQT + qt) * F2_T + row] = row_valid ? lse2 : INFINITY;
     }
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, ATT_TMEM_COLS);
+    tmem_dealloc(tmem_base, 512);
   }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+// ------------------------------------------------------------------ column sums
+constexpr int CS_QSTAGES = 4;
+constexpr int CS_SBUF = 4;
+struct CsSmem {
+  static constexpr int K = 0;
+  static constexpr int Q = K + F2_TILE_BYTES;
+  static constexpr int BAR = Q + CS_QSTAGES * F2_TILE_BYTES;
+  static constexpr int XCH = BAR + 256;   // 128 floats: sums of the second warpgroup
+  static constexpr int TOTAL = XCH + 512;
+};
 
-static int make_tmap_4d_bf16(CUtensorMap* tm, const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t d3, uint64_t s1,
-                             uint64_t s2, uint64_t s3, uint32_t b0, uint32_t b1, uint32_t b2) {
-  static EncodeTiledFn fn = nullptr;
+__global__ void __launch_bounds__(F2_THREADS, 1)
+colsum_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const F2Params p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if (smem_u32(smem) & 1023u) {
+    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, STATUS_TIMEOUT_MISC);
+    return;
+  }
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + CsSmem::BAR);
+  uint64_t* k_full = bars + 0;
+  uint64_t* q_full = bars + 1;     // [4]
+  uint64_t* q_empty = bars + 5;    // [4]
+  uint64_t* s_full = bars + 9;     // [4]
+  uint64_t* s_empty = bars + 13;   // [4]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x % p.nT;          // KV tile
+  const int g = (blockIdx.x / p.nT) % p.G;
+  const int b = blockIdx.x / (p.nT * p.G);
+  const long long bg = (long long)b * p.G + g;
+  const int tile_lo = p.tile_min[bg * p.nT + t];
+  const int tile_hi = p.tile_max[bg * p.nT + t];
+  // query tiles that can see at least one slot of this tile: those whose last position reaches tile_lo
+  // (positions grow with the tile index, so they form a suffix qt_first .. nQT-1)
+  int qt_first = 0;
+  {
+    const long long need = (long long)tile_lo - p.input_pos;  // first position index that sees the oldest slot
+    if (need > 0) qt_first = (int)min((long long)p.nQT, need / p.npos);
+    if (tile_lo == INT_MAX) qt_first = p.nQT;
+  }
+  const int n_q = p.nQT - qt_first;
+
+  if (p.rows_used < F2_T) {
+    for (int s = 0; s < CS_QSTAGES; ++s)
+      f2_zero_unused_rows(smem + CsSmem::Q + s * F2_TILE_BYTES, p.rows_used, threadIdx.x, F2_THREADS);
+    fence_proxy_async_smem();
+  }
+  if (threadIdx.x == 0) {
+    mbar_init(k_full, 1);
+    for (int s = 0; s < CS_QSTAGES; ++s) {
+      mbar_init(&q_full[s], 1);
+      mbar_init(&q_empty[s], 1);
+    }
+    for (int s = 0; s < CS_SBUF; ++s) {
+      mbar_init(&s_full[s], 1);
+      mbar_init(&s_empty[s], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0 && n_q > 0) {
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmK);
+      mbar_expect_tx(k_full, F2_TILE_BYTES);
+      tma_load_4d(smem + CsSmem::K, &tmK, k_full, 0, t * F2_T, g, b);
+      tma_load_4d(smem + CsSmem::K + F2_CHUNK_BYTES, &tmK, k_full, 64, t * F2_T, g, b);
+      const uint32_t q_bytes = (uint32_t)p.rows_used * 128u * 2u;
+      bool ok = true;
+      for (int i = 0; i < n_q && ok; ++i) {
+        const int st = i % CS_QSTAGES;
+        if (!mbar_wait_bounded(&q_empty[st], ((i / CS_QSTAGES) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) {
+          ok = false;
+          break;
+        }
+        uint8_t* qd = smem + CsSmem::Q + st * F2_TILE_BYTES;
+        mbar_expect_tx(&q_full[st], q_bytes);
+        tma_load_4d(qd, &tmQ, &q_full[st], 0, g * p.gs, (qt_first + i) * p.npos, b);
+        tma_load_4d(qd + F2_CHUNK_BYTES, &tmQ, &q_full[st], 64, g * p.gs, (qt_first + i) * p.npos, b);
+      }
+      if (!ok) {
+        long long c0 = clock64();
+        while (clock64() - c0 < 2000000LL) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_q > 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(F2_T, F2_T, 0, 0);  // K (slots = M) and Q (rows = N), both K-major
+      bool ok = mbar_wait_bounded(k_full, 0, abort_flag, p.status, STATUS_TIMEOUT_FULL);
+      const uint32_t k_addr = smem_u32(smem + CsSmem::K);
+      for (int i = 0; i < n_q && ok; ++i) {
+        const int st = i % CS_QSTAGES, sb = i % CS_SBUF;
+        if (!(ok = mbar_wait_bounded(&q_full[st], (i / CS_QSTAGES) & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL))) break;
+        if (!(ok = mbar_wait_bounded(&s_empty[sb], ((i / CS_SBUF) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY))) break;
+        tc_fence_after();
+        const uint32_t q_addr = smem_u32(smem + CsSmem::Q + st * F2_TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (uint32_t)((kk >> 2) * F2_CHUNK_BYTES + (kk & 3) * 32);
+          umma_f16_ss(tmem_base + (uint32_t)(sb * F2_T), make_smem_desc_sw128(k_addr + off, 16, 1024),
+                      make_smem_desc_sw128(q_addr + off, 16, 1024), idesc, kk != 0);
+        }
+        umma_commit(&q_empty[st]);
+        umma_commit(&s_full[sb]);
+      }
+    }
+  } else {
+    const int wg = (warp - 2) >> 2;
+    const int quarter = warp & 3;
+    const int slot_in_tile = quarter * 32 + lane;   // TMEM lane = slot of the tile
+    const int j = t * F2_T + slot_in_tile;
+    const int pj = p.pos[(bg * p.nT + t) * F2_T + slot_in_tile];
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const float c = p.scale_log2;
+    const float2 c2 = make_float2(c, c);
+    float2 acc0 = make_float2(0.f, 0.f), acc1 = acc0;
+    bool ok = true;
+    auto lse_row = [&](int i) { return p.lse2 + (bg * p.nQT + (qt_first + i)) * F2_T; };
+    auto prefetch_lse = [&](int i) {  // 512 bytes = four lines, one per 8 lanes is enough: lanes 0..3 ask
+      if (i < n_q && lane < 4) asm volatile("prefetch.global.L1 [%0];" ::"l"(lse_row(i) + 32 * lane));
+    };
+    prefetch_lse(wg);
+    for (int i = wg; i < n_q && ok; i += 2) {
+      const int qt = qt_first + i;
+      const int sb = i % CS_SBUF;
+      prefetch_lse(i + 2);
+      // row e of the query tile sits at position qt·npos + e / gs: the slot is visible from column thr on
+      const long long first_vis = ((long long)pj - p.input_pos - (long long)qt * p.npos) * p.gs;
+      const int thr = first_vis <= 0 ? 0 : (first_vis >= F2_T ? F2_T : (int)first_vis);
+      const bool masked = __any_sync(0xffffffffu, thr > 0);
+      const float4* lp = reinterpret_cast<const float4*>(lse_row(i));
+      if (!mbar_wait_bounded(&s_full[sb], (i / CS_SBUF) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      // 32 columns at a time: the next chunk of scores and of normalisers travels while this one is summed
+      const uint32_t tS = tmem_base + (uint32_t)(sb * F2_T) + lane_base;
+      uint32_t x[2][32];
+      float4 ls[2][8];
+      tmem_ld_32x32b_x32(tS, x[0]);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) ls[0][k] = __ldg(lp + k);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        tmem_ld_wait();
+        if (u < 3) {
+          tmem_ld_32x32b_x32(tS + (uint32_t)(32 * (u + 1)), x[(u + 1) & 1]);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) ls[(u + 1) & 1][k] = __ldg(lp + 8 * (u + 1) + k);
+        } else {
+          // the whole tile has left TMEM: hand the buffer back before the last chunk is summed
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&s_empty[sb]);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int e = 32 * u + 4 * k;
+          const float4 lv = ls[u & 1][k];
+          const float2 x0 = ffma2(make_float2(__uint_as_float(x[u & 1][4 * k]), __uint_as_float(x[u & 1][4 * k + 1])), c2,
+                                  make_float2(-lv.x, -lv.y));
+          const float2 x1 = ffma2(make_float2(__uint_as_float(x[u & 1][4 * k + 2]), __uint_as_float(x[u & 1][4 * k + 3])), c2,
+                                  make_float2(-lv.z, -lv.w));
+          float2 y0 = cs_pair_on_fma(2 * k) ? f2_exp2_poly2(x0) : make_float2(f2_exp2(x0.x), f2_exp2(x0.y));
+          float2 y1 = cs_pair_on_fma(2 * k + 1) ? f2_exp2_poly2(x1) : make_float2(f2_exp2(x1.x), f2_exp2(x1.y));
+          if (masked) {
+            if (e < thr) y0.x = 0.f;
+            if (e + 1 < thr) y0.y = 0.f;
+            if (e + 2 < thr) y1.x = 0.f;
+            if (e + 3 < thr) y1.y = 0.f;
+          }
+          acc0 = fadd2(acc0, y0);
+          acc1 = fadd2(acc1, y1);
+        }
+      }
+    }
+    // the two warpgroups hold the even and the odd query tiles of the same slots: add them in a fixed order
+    float* xch = reinterpret_cast<float*>(smem + CsSmem::XCH);
+    (void)tile_hi;
+    const float mine = (acc0.x + acc0.y) + (acc1.x + acc1.y);
+    if (wg == 1) xch[slot_in_tile] = mine;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    if (wg == 0 && j < p.L && p.weights) p.weights[bg * p.L + j] = ok ? (mine + xch[slot_in_tile]) * p.inv_gs : 0.f;
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+typedef CUresult (*F2EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// 4-d bf16 map: dims d0 (contiguous), d1..d3 with element strides s1..s3; box b0 x b1 x b2 x 1
+static int f2_make_tmap(CUtensorMap* tm, const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t d3, uint64_t s1,
+                        uint64_t s2, uint64_t s3, uint32_t b0, uint32_t b1, uint32_t b2) {
+  static F2EncodeTiledFn fn = nullptr;
   if (!fn) {
     void* pp = nullptr;
     cudaDriverEntryPointQueryResult q;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &pp, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
       return KVB_ERR_DRIVER;
-    fn = reinterpret_cast<EncodeTiledFn>(pp);
+    fn = reinterpret_cast<F2EncodeTiledFn>(pp);
   }
   cuuint64_t dims[4] = {d0, d1, d2, d3};
   cuuint64_t strides[3] = {s1 * 2, s2 * 2, s3 * 2};
@@ -696,6 +933,8 @@ static int make_tmap_4d_bf16(CUtensorMap* tm, const void* ptr, uint64_t d0, uint
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? KVB_OK : KVB_ERR_TMAP;
 }
+
+static inline long long f2_round4(long long x) { return (x + 3) / 4 * 4; }
 
 }  // namespace kvb
 
@@ -708,83 +947,80 @@ extern "C" int kvb_att_tile_minmax(const int32_t* token_pos, int32_t* tmin, int3
   return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
 }
 
-// Optional timeline trace of the forward kernel (diagnostics): `buf` holds 3 roles x `cap` events
-// x 2 int64 (tag, SM clock) and is filled by CTA 0 of every later kvb_sdpa_fwd launch of this
-// process; buf = NULL switches tracing off. Tags: 1e5 producer, 1e6+ QK issue, 2e6+ PV issue,
-// 3e6+ / 4e6+ softmax of sweep 1 / 2; the digits below 1e5 count tiles.
-static long long* g_att_trace = nullptr;
-static int g_att_trace_cap = 0;
-extern "C" int kvb_sdpa_fwd_set_trace(void* buf, int cap) {
-  g_att_trace = reinterpret_cast<long long*>(buf);
-  g_att_trace_cap = buf ? cap : 0;
+// Optional phase profile of the flash kernel (diagnostics): `buf` holds 4 roles x 8 int64 cycle counters, written by
+// CTA 0 of every later kvb_sdpa_fwd launch of this process; NULL switches it off. Counters: issuer 0 wait P of tile 0,
+// 1 issue PV + next QK of tile 0, 2 / 3 the same for tile 1, 4 wait V, 5 wait K, 6 rest; softmax 0 wait S, 1 masks,
+// 2 S into registers, 3 maximum and rescale, 4 exponentials, 5 hand-over of P, 6 rest; producer 0 wait for a free K
+// stage, 1 for a free V stage, 2 rest.
+static long long* g_f2_trace = nullptr;
+extern "C" int kvb_sdpa_fwd_set_trace(void* buf) {
+  g_f2_trace = reinterpret_cast<long long*>(buf);
   return KVB_OK;
 }
 
-// Scratch layout (int32 words), provided by the caller:
-//   tile_min (B*G*nT) | tile_max (B*G*nT) | wpart (B*G*4*nQT*L floats, only if weights != NULL)
-extern "C" long long kvb_sdpa_fwd_scratch_bytes(int B, int H, int G, int q_len, int kv_len, int want_weights) {
-  if (G <= 0 || H % G) return -1;
+// Scratch layout (int32 words, 16-byte aligned parts), provided by the caller:
+//   tile_min (B*G*nT) | tile_max (B*G*nT) | positions (B*G*nT*128) | lse2 (B*G*nQT*128 floats)
+extern "C" long long kvb_sdpa_fwd_scratch_bytes(int B, int H, int G, int q_len, int kv_len) {
+  if (G <= 0 || H % G || H / G > 128) return -1;
   const int gs = H / G;
-  const long long nT = (kv_len + kvb::ATT_BN - 1) / kvb::ATT_BN;
+  const long long nT = (kv_len + kvb::F2_T - 1) / kvb::F2_T;
   const long long npos = 128 / gs;
   const long long nQT = (q_len + npos - 1) / npos;
-  long long words = 2LL * B * G * nT;
-  if (want_weights) words += 4LL * B * G * nQT * kv_len;
-  return words * 4;
+  const long long bgt = kvb::f2_round4((long long)B * G * nT);
+  return (2 * bgt + (long long)B * G * nT * 128 + (long long)B * G * nQT * 128) * 4;
 }
 
+// q (B,H,T,128) contiguous bf16; k, v (B,G,L,128) bf16 with batch / group strides k_sb, k_sg (elements);
+// token_pos (B,G,L) int32 with strides, or NULL (slot j holds token j); out (B,T,H,128) bf16;
+// lse (B,H,T) fp32 or NULL; weights (B,G,L) fp32 or NULL.
 extern "C" int kvb_sdpa_fwd(const void* q, const void* k, const void* v, const int32_t* token_pos, void* out, float* lse,
-                            float* weights, void* scratch, int B, int H, int G, int q_len, int kv_len, long long k_sb,
-                            long long k_sg, long long tp_sb, long long tp_sg, float scale, int input_pos, int* status,
-                            void* stream) {
+                             float* weights, void* scratch, int B, int H, int G, int q_len, int kv_len, long long k_sb,
+                             long long k_sg, long long tp_sb, long long tp_sg, float scale, int input_pos, int* status,
+                             void* stream) {
   using namespace kvb;
   if (B <= 0 || H <= 0 || G <= 0 || q_len <= 0 || kv_len <= 0 || H % G) return KVB_ERR_ARG;
   const int gs = H / G;
-  if (gs > 128 || (gs & (gs - 1))) return KVB_ERR_UNSUPPORTED;
+  if (gs > 128) return KVB_ERR_UNSUPPORTED;
   if ((k_sb % 8) || (k_sg % 8)) return KVB_ERR_ALIGN;
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
-       reinterpret_cast<uintptr_t>(out)) & 15)
+       reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(scratch)) & 15)
     return KVB_ERR_ALIGN;
   cudaStream_t s = (cudaStream_t)stream;
-  AttParams p;
+  F2Params p;
   p.B = B; p.H = H; p.G = G; p.T = q_len; p.L = kv_len;
-  p.gs = gs; p.npos = 128 / gs;
-  p.nT = (kv_len + ATT_BN - 1) / ATT_BN;
+  p.gs = gs; p.npos = 128 / gs; p.rows_used = p.npos * gs;
+  p.nT = (kv_len + F2_T - 1) / F2_T;
   p.nQT = (q_len + p.npos - 1) / p.npos;
-  p.token_pos = token_pos; p.tp_sb = tp_sb; p.tp_sg = tp_sg;
+  const long long bgt = f2_round4((long long)B * G * p.nT);
   int32_t* sc = reinterpret_cast<int32_t*>(scratch);
   int32_t* tmin = sc;
-  int32_t* tmax = sc + (long long)B * G * p.nT;
-  p.tile_min = tmin; p.tile_max = tmax;
-  p.wpart = weights ? reinterpret_cast<float*>(sc + 2LL * B * G * p.nT) : nullptr;
-  p.out = (__nv_bfloat16*)out; p.lse = lse;
+  int32_t* tmax = sc + bgt;
+  int32_t* pos = sc + 2 * bgt;
+  float* lse2 = reinterpret_cast<float*>(pos + (long long)B * G * p.nT * 128);
+  p.tile_min = tmin; p.tile_max = tmax; p.pos = pos; p.lse2 = lse2;
+  p.out = (__nv_bfloat16*)out; p.lse = lse; p.weights = weights;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.inv_gs = 1.f / gs;
   p.input_pos = input_pos; p.status = status;
-  p.trace = g_att_trace; p.trace_cap = g_att_trace_cap;
+  p.trace = g_f2_trace;
 
   CUtensorMap tmQ, tmK, tmV;
   int rc;
-  // Q (B,H,T,D): dims (D, T, H, B); box = 64 x npos x gs
-  if ((rc = make_tmap_4d_bf16(&tmQ, q, ATT_D, q_len, H, B, ATT_D, (uint64_t)q_len * ATT_D, (uint64_t)H * q_len * ATT_D, 64,
-                              p.npos, gs)))
+  // Q (B,H,T,D) read position-major: dims (D, H, T, B) with strides (T·D, D, H·T·D); box = 64 x gs x npos
+  if ((rc = f2_make_tmap(&tmQ, q, F2_T, H, q_len, B, (uint64_t)q_len * F2_T, F2_T, (uint64_t)H * q_len * F2_T, 64, gs, p.npos)))
     return rc;
-  // K, V (B,G,L,D) with strides: dims (D, L, G, B); box = 64 x ATT_BN x 1
-  if ((rc = make_tmap_4d_bf16(&tmK, k, ATT_D, kv_len, G, B, ATT_D, k_sg, k_sb, 64, ATT_BN, 1))) return rc;
-  if ((rc = make_tmap_4d_bf16(&tmV, v, ATT_D, kv_len, G, B, ATT_D, k_sg, k_sb, 64, ATT_BN, 1))) return rc;
+  // K, V (B,G,L,D) with strides: dims (D, L, G, B); box = 64 x 128 x 1
+  if ((rc = f2_make_tmap(&tmK, k, F2_T, kv_len, G, B, F2_T, k_sg, k_sb, 64, F2_T, 1))) return rc;
+  if ((rc = f2_make_tmap(&tmV, v, F2_T, kv_len, G, B, F2_T, k_sg, k_sb, 64, F2_T, 1))) return rc;
 
-  att_tile_minmax_kernel<<<B * G * p.nT, ATT_BN, 0, s>>>(token_pos, tmin, tmax, G, kv_len, p.nT, tp_sb, tp_sg);
+  f2_prepare_kernel<<<B * G * p.nT, F2_T, 0, s>>>(token_pos, tmin, tmax, pos, G, kv_len, p.nT, tp_sb, tp_sg);
   static kvb::PerDeviceOnce attr_once;
   if (attr_once.first()) {
-    cudaFuncSetAttribute(sdpa_fwd_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttSmem::TOTAL);
-    cudaFuncSetAttribute(sdpa_fwd_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttSmem::TOTAL);
+    cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F2Smem::TOTAL);
+    cudaFuncSetAttribute(colsum_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, CsSmem::TOTAL);
   }
-  // explicit token positions = an evicting cache: most tiles hold tokens of the current chunk and need
-  // masks, which the 8-warp variant builds faster; plain causal attention runs best with 4 softmax warps
-  if (token_pos) sdpa_fwd_kernel<8><<<B * G * p.nQT, att_threads(8), AttSmem::TOTAL, s>>>(tmQ, tmK, tmV, p);
-  else sdpa_fwd_kernel<4><<<B * G * p.nQT, att_threads(4), AttSmem::TOTAL, s>>>(tmQ, tmK, tmV, p);
-  if (weights) {
-    dim3 grid((kv_len + 255) / 256, B * G);
-    att_reduce_weights_kernel<<<grid, 256, 0, s>>>(p.wpart, weights, 4 * p.nQT, kv_len, 1.f / gs);
-  }
+  const int nPair = (p.nQT + 1) / 2;
+  flash_fwd_kernel<<<B * G * nPair, F2_THREADS, F2Smem::TOTAL, s>>>(tmQ, tmK, tmV, p);
+  if (weights) colsum_kernel<<<B * G * p.nT, F2_THREADS, CsSmem::TOTAL, s>>>(tmQ, tmK, p);
   return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
 }

@@ -225,7 +225,7 @@ def sdpa_bwd(
     """Returns ``dq (B,H,q,D)``, ``dk, dv (B,G,kv,D)`` (fp32 for dk/dv). With
     ``dk_accum/dv_accum`` (fp32, cache shaped) the K/V gradients are added into their
     first ``kv`` slots instead and ``None`` is returned for them."""
-    if query.is_cuda and _cuda().sdpa_supported(query, key, sliding_window, softcap):
+    if query.is_cuda and _cuda().sdpa_bwd_supported(query, key, sliding_window, softcap):
         return _cuda().sdpa_bwd(grad_out, query, key, value, out, lse, scale, input_pos, token_pos, dk_accum, dv_accum)
     if query.is_cuda:
         _restatement_on_gpu("sdpa_bwd", _sdpa_shape_text(query, sliding_window, softcap))

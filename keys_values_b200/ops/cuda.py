@@ -489,34 +489,39 @@ def sdpa_supported(query: torch.Tensor, key: torch.Tensor, sliding_window, softc
     H, G = query.shape[1], key.shape[1]
     gs = H // G
     return (query.dtype == torch.bfloat16 and query.shape[-1] == 128 and sliding_window is None and softcap is None
-            and gs <= 128 and (gs & (gs - 1)) == 0 and query.shape[2] > 0)
+            and gs <= 128 and query.shape[2] > 0)
+
+
+def sdpa_bwd_supported(query: torch.Tensor, key: torch.Tensor, sliding_window, softcap) -> bool:
+    """The backward kernels pack the heads of a group into the 128-row tile by powers of two."""
+    gs = query.shape[1] // key.shape[1]
+    return sdpa_supported(query, key, sliding_window, softcap) and (gs & (gs - 1)) == 0
 
 
 def sdpa_fwd(query, key, value, scale, input_pos, token_pos=None, return_weights=False):
+    """SDPA forward: flash sweep (P in TMEM, online softmax) + column-owner weight sums. Returns
+    ``(out (B,T,H·D) bf16, weights (B,G,L) fp32 | None, lse (B,H,T) fp32)``; any group size up to 128."""
     B, H, T, D = query.shape
     G, L = key.shape[1], key.shape[2]
     query = query.contiguous()
     if key.stride(3) != 1 or key.stride(2) != D or key.stride() != value.stride():
         key, value = key.contiguous(), value.contiguous()
-    if token_pos is not None:
-        if token_pos.ndim == 1:
-            token_pos = token_pos.view(1, 1, L).expand(B, G, L)
-        if token_pos.dtype != torch.int32:
-            token_pos = token_pos.to(torch.int32)
-        if token_pos.stride(2) != 1:
-            token_pos = token_pos.contiguous()
+    token_pos = _norm_token_pos(token_pos, B, G, L)
     dev = query.device
     out = torch.empty((B, T, H * D), dtype=torch.bfloat16, device=dev)
     lse = torch.empty((B, H, T), dtype=torch.float32, device=dev)
     weights = torch.empty((B, G, L), dtype=torch.float32, device=dev) if return_weights else None
-    nbytes = lib().kvb_sdpa_fwd_scratch_bytes(B, H, G, T, L, int(return_weights))
+    lib().kvb_sdpa_fwd_scratch_bytes.restype = ctypes.c_longlong
+    nbytes = lib().kvb_sdpa_fwd_scratch_bytes(B, H, G, T, L)
+    if nbytes < 0:
+        raise NativeError("sdpa_fwd: unsupported head / group configuration")
     scratch = torch.empty(nbytes // 4, dtype=torch.int32, device=dev)
     st = status_word(dev)
     _check(lib().kvb_sdpa_fwd(_p(query), _p(key), _p(value), _p(token_pos), _p(out), _p(lse), _p(weights), _p(scratch), B, H, G, T, L,
-                              _ll(key.stride(0)), _ll(key.stride(1)),
-                              _ll(token_pos.stride(0) if token_pos is not None else 0),
-                              _ll(token_pos.stride(1) if token_pos is not None else 0),
-                              ctypes.c_float(scale), int(input_pos), _p(st), _stream(query)), "sdpa_fwd")
+                               _ll(key.stride(0)), _ll(key.stride(1)),
+                               _ll(token_pos.stride(0) if token_pos is not None else 0),
+                               _ll(token_pos.stride(1) if token_pos is not None else 0),
+                               ctypes.c_float(scale), int(input_pos), _p(st), _stream(query)), "sdpa_fwd")
     _count(3 if return_weights else 2)
     return out, weights, lse
 

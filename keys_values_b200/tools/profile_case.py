@@ -29,10 +29,14 @@ def main():
         q = torch.randn(B, H, T, D, device=dev, dtype=torch.bfloat16)
         k = torch.randn(B, G, L, D, device=dev, dtype=torch.bfloat16)
         v = torch.randn(B, G, L, D, device=dev, dtype=torch.bfloat16)
-        tp = torch.stack([torch.stack([torch.randperm(L, device=dev) for _ in range(G)]) for _ in range(B)]).to(torch.int32) + 4 * L
-        # the last T tokens of the sequence are in the cache
-        tp[:, :, :T] = (torch.arange(T, device=dev) + 6 * L).to(torch.int32)
+        # an evicting cache in training: old tokens everywhere, the T tokens of the current chunk scattered over the slots
         input_pos = 6 * L
+        tp = torch.empty(B, G, L, device=dev, dtype=torch.int32)
+        for b in range(B):
+            for g in range(G):
+                old = torch.randperm(input_pos, device=dev)[: L - T]
+                new = torch.arange(input_pos, input_pos + T, device=dev)
+                tp[b, g] = torch.cat((old, new))[torch.randperm(L, device=dev)].to(torch.int32)
         if args.which == "sdpa_fwd":
             for _ in range(args.iters):
                 out, w, lse = cu.sdpa_fwd(q, k, v, scale, input_pos, tp, True)

@@ -222,6 +222,39 @@ def test_sdpa_evicted_cache(B, H, G, T, L):
     _sdpa_case(B, H, G, T, L, 5 * L, "perm")
 
 
+def test_sdpa_group_size_not_a_power_of_two():
+    # 40 query heads over 8 KV heads (Qwen3-14B): 25 positions x 5 heads fill 125 of the 128 tile rows
+    _sdpa_case(1, 40, 8, 200, 1024, 5000, "perm")
+    _sdpa_case(1, 10, 2, 77, 300, 0, "arange", want_w=False)
+
+
+def test_sdpa_long_chunk_over_full_cache():
+    # the training shape: 1024 new tokens scattered over a cache of 16384 slots
+    _sdpa_case(1, 32, 8, 1024, 16384, 5 * 16384, "perm")
+
+
+def test_sdpa_plain_causal_with_weights():
+    # square causal prefill with weights: diagonal tiles take the element-wise mask path
+    _sdpa_case(2, 8, 2, 700, 700, 0, "arange")
+
+
+def test_sdpa_is_deterministic():
+    """Outputs, normalisers and the summed weights (which drive the eviction decisions) are bit-identical run to run."""
+    D, B, H, G, T, L = 128, 1, 32, 8, 512, 4096
+    q = torch.randn(B, H, T, D, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(B, G, L, D, device=DEV, dtype=torch.bfloat16)
+    v = torch.randn(B, G, L, D, device=DEV, dtype=torch.bfloat16)
+    tp = torch.stack([torch.stack([torch.randperm(L, device=DEV) for _ in range(G)]) for _ in range(B)]).to(torch.int32) + 3 * L
+    tp[:, :, ::8][:, :, :T] = (torch.arange(T, device=DEV) + 5 * L).to(torch.int32)  # the chunk's tokens, scattered
+    runs = [_cuda().sdpa_fwd(q, k, v, 1 / math.sqrt(D), 5 * L, tp, True) for _ in range(3)]
+    _cuda().check_status(DEV)
+    for r in runs[1:]:
+        assert torch.equal(r[0], runs[0][0]) and torch.equal(r[1], runs[0][1]) and torch.equal(r[2], runs[0][2])
+    # the k smallest scores (the slots H2O would evict) agree as index sets as well
+    idx = [torch.topk(r[1], 64, largest=False).indices.sort(dim=-1).values for r in runs]
+    assert all(torch.equal(i, idx[0]) for i in idx[1:])
+
+
 def test_sdpa_status_reports_timeout_free_run():
     # a healthy run leaves the status word at zero
     _sdpa_case(1, 4, 1, 32, 256, 224, "arange")
