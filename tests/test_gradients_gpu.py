@@ -82,3 +82,41 @@ def test_grace_period_gradients_multi_cell_equal_single_cell_on_gpu():
     num = sum(((res[0][1][k] - res[1][1][k]) ** 2).sum() for k in res[0][1]) ** 0.5
     den = sum((res[1][1][k] ** 2).sum() for k in res[0][1]) ** 0.5
     assert float(num / den) < 0.1, float(num / den)
+
+
+@pytest.mark.parametrize("cache_name", ["h2o-default", "h2o-torch-quantized8", "lastrec-default"])
+def test_gradients_through_eviction_match_oracle_on_gpu(cache_name):
+    """The kernels' path (tcgen05 forward / backward, fused cache writes, on-device eviction) against the
+    independent whole-sequence oracle, with a cache that evicts. The tolerance is set by the oracle's own
+    bf16 noise: the same oracle evaluated in bf16 and in fp32."""
+    from keys_values_b200.oracle import oracle_loss_and_gradients
+
+    dev, dtype = torch.device("cuda", 0), torch.bfloat16
+    cfg, m = _model(dev, dtype)
+    head = CrossEntropyOnLogits(cfg)
+    T, C, cs = 1152, 384, 128
+    ids = torch.randint(0, cfg.vocab_size, (1, T), device=dev)
+    tg = torch.randint(0, cfg.vocab_size, (1, 128), device=dev)
+    ck = dict(max_chunk_size=cs) if "h2o" in cache_name else None
+    m.assign_kv_caches(KVCacheFactory.create(m, cache_name, 1, C, dtype=dtype, device=dev, cache_kwargs=ck))
+    gm = LongContextGradientModel(m, head, layers_per_cell=1, chunk_size=cs)
+    gm.train()
+    loss = gm(ids, tg)
+    logs, cells = list(gm._replay_logs), list(gm.cells)
+    assert len(cells) > 2 and any(s is not None for s in logs[0].slot_positions)
+    loss.backward()
+    g1 = _grads(m)
+    o_loss, o16 = oracle_loss_and_gradients(m, head, ids, tg, logs, cells)
+    bits = [None if "quantized" not in cache_name else 8] * cfg.n_layer
+    m32 = m.float()
+    o_loss32, o32 = oracle_loss_and_gradients(m32, head, ids, tg, logs, cells, storage_bits=bits)
+    m.to(dtype)
+
+    def rel(a, b):
+        num = sum(((a[k].float() - b[k].float()) ** 2).sum() for k in b) ** 0.5
+        den = sum((b[k].float() ** 2).sum() for k in b) ** 0.5
+        return float(num / den)
+
+    noise = rel(o16, o32)
+    assert abs(float(loss.value) - float(o_loss32)) < 0.03
+    assert rel(g1, o32) < max(3 * noise, 0.05), (rel(g1, o32), noise)
