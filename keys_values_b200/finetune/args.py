@@ -155,13 +155,20 @@ class EvalArgs:
     micro_batch_size: Optional[int] = None
     sample_metric: Optional[str] = None
     sample_metric_max_batches: Optional[int] = None
+    generate_example: bool = True  # print a generated continuation of one validation prompt with every validation
 
 
 @dataclass
 class SDPAArgs:
-    """Kept for command-line compatibility. This framework has one SDPA implementation per
-    device (the native kernels), so the backend switches of the reference are accepted and
-    ignored; ``fused_*`` choose nothing either, the fused kernels are always used on the GPU."""
+    """Attention switches. This framework has one SDPA implementation per device (the native kernels
+    on a GPU, a blocked PyTorch restatement elsewhere), so the back-end choices of the reference
+    (``flex_attention``, ``flashinfer``, ``sdpa_kernels``, ``fused_*``) are accepted for command-line
+    compatibility and have nothing to select. Two switches act:
+
+    * ``use_eager_sdpa_always``: run the blocked PyTorch restatement on the GPU too (debugging,
+      cross-checking the kernels on real data);
+    * ``tmp_array_limit_gb``: largest score matrix the restatement forms at a time (it loops over
+      blocks of query rows beyond it). Default 2 GB."""
 
     flex_attention: bool = False
     flashinfer: bool = False

@@ -86,7 +86,7 @@ def setup(
                    optimizer=optimizer, kv_cache=kv_cache, grad=grad, sdpa=sdpa, lora=lora, head_model=head_model, seed=seed,
                    yarn_rope=yarn_rope, model_name=model_name)
     launch(main, devices, checkpoint_dir=checkpoint_dir, out_dir=out_dir, precision=precision, resume=resume, data=data, train=train,
-           eval=eval, optimizer=optimizer, kv_cache=kv_cache, grad=grad, lora=lora, head_model_name=head_model,
+           eval=eval, optimizer=optimizer, kv_cache=kv_cache, grad=grad, sdpa=sdpa, lora=lora, head_model_name=head_model,
            head_model_kwargs=head_model_kwargs or {}, logger_name=logger_name, seed=seed, yarn_rope=yarn_rope, model_name=model_name,
            hparams=hparams, profile_grad_times=profile_grad_times, record_gpu_memory_snapshots=record_gpu_memory_snapshots)
 
@@ -139,14 +139,30 @@ def wrap_gpt_model(gpt_model, head_model, kv_cache: KVCacheArgs, grad: GradientA
     )
 
 
+def apply_sdpa_args(sdpa: Optional[SDPAArgs], rank: int = 0) -> None:
+    """Puts the two acting switches of :class:`SDPAArgs` into effect and says which of the others were given
+    although they select nothing here."""
+    from keys_values_b200 import ops
+
+    sdpa = sdpa if sdpa is not None else SDPAArgs()
+    ops.set_native_attention(not sdpa.use_eager_sdpa_always)
+    ops.set_tmp_array_limit_gb(sdpa.tmp_array_limit_gb)
+    ignored = [n for n in ("flex_attention", "flashinfer") if getattr(sdpa, n)] + (["sdpa_kernels"] if sdpa.sdpa_kernels else [])
+    if ignored and rank == 0:
+        print(f"sdpa: {', '.join(ignored)} given; this framework has one attention implementation per device, nothing is selected")
+    if sdpa.use_eager_sdpa_always and rank == 0:
+        print("sdpa: attention runs in the blocked PyTorch restatement on every device (use_eager_sdpa_always)")
+
+
 def main(rank: int, local_rank: int, world_size: int, *, checkpoint_dir, out_dir, precision, resume, data, train, eval, optimizer, kv_cache,
-         grad, lora, head_model_name, head_model_kwargs, logger_name, seed, yarn_rope, model_name, hparams, profile_grad_times,
+         grad, sdpa=None, lora, head_model_name, head_model_kwargs, logger_name, seed, yarn_rope, model_name, hparams, profile_grad_times,
          record_gpu_memory_snapshots) -> None:
     cuda = torch.cuda.is_available()
     device = torch.device("cuda", local_rank) if cuda else torch.device("cpu")
     if cuda:
         torch.cuda.set_device(device)
     dtype = str_to_torch_dtype(precision)
+    apply_sdpa_args(sdpa, rank)
     torch.manual_seed(seed)
     out_dir = Path(out_dir)
     if rank == 0:
@@ -207,6 +223,8 @@ def main(rank: int, local_rank: int, world_size: int, *, checkpoint_dir, out_dir
         fu.copy_config_files(Path(checkpoint_dir), final)
         config.save(final / "model_config.yaml")
         fu.save_hyperparameters(hparams, final)
+        report = fu.finetuning_performance_report(state.train_time, state.total_tokens, state.step_count, device, out_dir)
+        print("performance report: " + ", ".join(f"{k}={v:.4g}" if isinstance(v, float) else f"{k}={v}" for k, v in report.items()))
         print(message_memory_all_devices("memory: "))
 
 
@@ -283,8 +301,34 @@ def save_checkpoint_regular(model: LongContextGradientModel, out_dir: Path, step
 def fit(*, model, optimizer, scheduler, train_loader, val_loader, batch_transform, train: TrainArgs, eval: EvalArgs, state: TrainingStateVars,
         max_steps: int, accum: int, device, rank: int, world_size: int, grad_reducer, logger, out_dir: Path, checkpoint_dir: Path, lora: bool,
         hparams, profile_grad_times: int = 0, record_gpu_memory_snapshots: Optional[int] = None, tokenizer=None) -> None:
+    from keys_values_b200.utils.recovery import OOMRetry
+
     ts_manager = TrainingStateManager(out_dir, rank, world_size)
     train_iter = CycleIterator(train_loader)
+    throughput = fu.ThroughputMonitor(world_size)
+    samples_seen = 0
+
+    def free_after_oom() -> None:
+        import gc
+
+        model.clear()  # checkpoints, replay logs and saved attention outputs of the failed attempt
+        gc.collect()
+        if device.type == "cuda":
+            torch.cuda.empty_cache()
+
+    def show_example() -> None:
+        if not (eval.generate_example and rank == 0 and val_loader is not None):
+            return
+        try:
+            batch = batch_transform(next(iter(val_loader)))
+        except StopIteration:
+            return
+        ids = batch["input_ids"][0]
+        n_t = batch["targets"].shape[1]
+        prompt = ids[: max(1, ids.numel() - n_t + 1)]
+        text = fu.generate_example(model.gpt_model, tokenizer, prompt, min(eval.max_new_tokens or 32, 64), model.chunk_size, device)
+        print(f"example continuation ({prompt.numel()} prompt tokens): {text}")
+
     if eval.initial_validation:
         metrics = validate_and_all_reduce(model, val_loader, batch_transform, device, eval, world_size, tokenizer)
         if rank == 0:
@@ -320,12 +364,25 @@ def fit(*, model, optimizer, scheduler, train_loader, val_loader, batch_transfor
                 scale = scale * float(n_tok / mean_tok.clamp(min=1))
             if grad_reducer is not None and micro < accum - 1:
                 hook, model.row_done_hook = model.row_done_hook, None  # reduce only after the last micro-batch
-            loss = model(ids, targets, scale_factor=scale)
-            loss.backward()
+
+            def attempt(_limit_gb: float, save_attention: bool):
+                if not save_attention:
+                    model.save_attention_outputs = False  # recompute in the backward pass instead
+                out = model(ids, targets, scale_factor=scale)
+                out.backward()
+                return out
+
+            if world_size == 1:
+                # out of memory in the forward or backward pass: free, give up the saved attention outputs, retry
+                # (one rank only: with several, a retry on one of them would leave the others in the all-reduce)
+                loss = OOMRetry(limits_gb=(0.0,), free_fn=free_after_oom, verbose=True).run(attempt)
+            else:
+                loss = attempt(0.0, True)
             if grad_reducer is not None and micro < accum - 1:
                 model.row_done_hook = hook
             step_loss += loss.detach().float()
             step_tokens += ids.numel()
+            samples_seen += ids.shape[0]
             state.iter_num += 1
         if grad_reducer is not None:
             grad_reducer.finish_step()
@@ -352,6 +409,8 @@ def fit(*, model, optimizer, scheduler, train_loader, val_loader, batch_transfor
             metrics = {"loss": float(step_loss), "iter": state.iter_num, "step": state.step_count, "epoch": train_iter.epoch,
                        "iter_time": dt, "tokens": step_tokens * world_size, "total_tokens": state.total_tokens,
                        "tokens_per_sec": step_tokens * world_size / dt, "learning_rate": scheduler.get_last_lr()[0]}
+            throughput.update(time=state.train_time, batches=state.iter_num, samples=samples_seen, lengths=state.total_tokens // world_size)
+            metrics.update(throughput.compute())
             logger.log_dict(metrics, step=state.step_count)
             print(f"step {state.step_count}/{max_steps} | loss {metrics['loss']:.4f} | {dt:.1f} s | {metrics['tokens_per_sec']:.0f} tok/s")
         if profile_grad_times and state.step_count >= profile_grad_times:
@@ -369,6 +428,7 @@ def fit(*, model, optimizer, scheduler, train_loader, val_loader, batch_transfor
             if rank == 0:
                 logger.log_dict(metrics, step=state.step_count)
                 print(f"validation: {metrics}")
+            show_example()
             if world_size > 1:
                 dist.barrier()
         if train.save_interval and state.step_count % train.save_interval == 0:

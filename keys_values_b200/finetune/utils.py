@@ -12,7 +12,7 @@ import math
 import shutil
 import time
 from pathlib import Path
-from typing import Any, Dict, Optional
+from typing import List, Any, Dict, Optional
 
 import torch
 import yaml
@@ -193,3 +193,73 @@ def choose_logger(logger_name: str, out_dir: Path, name: str = "metrics", **kwar
 
         return _MLflow()
     raise ValueError(f"`--logger_name={logger_name}` is not a valid option. Choose from 'csv', 'tensorboard', 'wandb', 'mlflow'.")
+
+
+class ThroughputMonitor:
+    """Running rates over the last ``window`` optimizer steps (role of Lightning's ``ThroughputMonitor`` in
+    ``keys_values/finetune/longcontext_full.py:1387``, ``:1663-1669``): ``update`` takes the cumulative
+    training time and the cumulative numbers of batches, samples and tokens; ``compute`` returns
+    ``throughput/{batches,samples,items}_per_sec`` for the whole job and ``throughput/device/...`` per GPU."""
+
+    def __init__(self, world_size: int = 1, window: int = 20):
+        self.world_size, self.window = max(1, world_size), max(2, window)
+        self._hist: List[Dict[str, float]] = []
+
+    def update(self, *, time: float, batches: int, samples: int, lengths: int) -> None:
+        self._hist.append(dict(time=float(time), batches=float(batches), samples=float(samples), lengths=float(lengths)))
+        if len(self._hist) > self.window:
+            self._hist.pop(0)
+
+    def compute(self) -> Dict[str, float]:
+        if len(self._hist) < 2:
+            return {}
+        first, last = self._hist[0], self._hist[-1]
+        dt = last["time"] - first["time"]
+        if dt <= 0:
+            return {}
+        out = {}
+        for key, name in (("batches", "batches"), ("samples", "samples"), ("lengths", "items")):
+            rate = (last[key] - first[key]) / dt
+            out[f"throughput/device/{name}_per_sec"] = rate
+            out[f"throughput/{name}_per_sec"] = rate * self.world_size
+        return out
+
+
+def finetuning_performance_report(train_time: float, total_tokens: int, steps: int, device, out_dir: Optional[Path] = None) -> Dict[str, Any]:
+    """Summary printed (and written to ``performance_report.json``) when training ends: time, throughput
+    and peak device memory (``keys_values/finetune/longcontext_full.py:909-914``)."""
+    report: Dict[str, Any] = {
+        "training_time_s": train_time, "optimizer_steps": steps, "tokens": total_tokens,
+        "tokens_per_sec": total_tokens / train_time if train_time > 0 else float("nan"),
+        "sec_per_step": train_time / steps if steps else float("nan"),
+    }
+    device = torch.device(device)
+    if device.type == "cuda":
+        report["peak_memory_gb"] = torch.cuda.max_memory_allocated(device) / 2**30
+        report["device"] = torch.cuda.get_device_name(device)
+    if out_dir is not None:
+        import json
+
+        (Path(out_dir) / "performance_report.json").write_text(json.dumps(report, indent=1))
+    return report
+
+
+def generate_example(gpt_model, tokenizer, prompt_ids: torch.Tensor, max_new_tokens: int, chunk_size: int, device) -> str:
+    """Greedy continuation of one validation prompt through the model's caches (printed with every validation,
+    ``keys_values/finetune/longcontext_full.py:1918-1962``). Leaves the caches reset and the context width
+    as it found them."""
+    from keys_values_b200.generate.base import generate
+
+    width = gpt_model.max_seq_length
+    was_training = gpt_model.training
+    gpt_model.eval()
+    try:
+        with torch.no_grad():
+            prompt = prompt_ids.to(device).view(-1)
+            out = generate(gpt_model, prompt, max_returned_tokens=prompt.numel() + max_new_tokens, prompt_chunksize=chunk_size,
+                           temperature=0.0, eos_id=getattr(tokenizer, "eos_id", None), include_prompt=False)
+        return tokenizer.decode(out) if tokenizer is not None else " ".join(str(int(t)) for t in out)
+    finally:
+        gpt_model.reset()
+        gpt_model.max_seq_length = width
+        gpt_model.train(was_training)

@@ -26,6 +26,20 @@ def _cuda():
 
 
 _NOTICED = set()
+_NATIVE_ATTENTION = True
+
+
+def set_native_attention(enabled: bool) -> None:
+    """``False`` sends every attention call (also on a GPU) to the blocked PyTorch restatement: the
+    debugging switch behind ``--sdpa.use_eager_sdpa_always``."""
+    global _NATIVE_ATTENTION
+    _NATIVE_ATTENTION = bool(enabled)
+
+
+def set_tmp_array_limit_gb(limit_gb: Optional[float]) -> None:
+    """Upper bound for the score matrix that the PyTorch restatement of attention materialises at a time
+    (it loops over blocks of query rows beyond it): ``--sdpa.tmp_array_limit_gb``."""
+    ref.TMP_ARRAY_LIMIT_GB = float(limit_gb) if limit_gb else ref.DEFAULT_TMP_ARRAY_LIMIT_GB
 
 
 def _restatement_on_gpu(op: str, why: str) -> None:
@@ -195,9 +209,9 @@ def sdpa_fwd(
     softcap: Optional[float] = None,
 ):
     """Returns ``(out (B,q,H·D), weights (B,G,kv) fp32 | None, lse (B,H,q) fp32)``."""
-    if query.is_cuda and _cuda().sdpa_supported(query, key, sliding_window, softcap):
+    if query.is_cuda and _NATIVE_ATTENTION and _cuda().sdpa_supported(query, key, sliding_window, softcap):
         return _cuda().sdpa_fwd(query, key, value, scale, input_pos, token_pos, return_weights)
-    if query.is_cuda:
+    if query.is_cuda and _NATIVE_ATTENTION:
         _restatement_on_gpu("sdpa_fwd", _sdpa_shape_text(query, sliding_window, softcap))
     return ref.sdpa(query, key, value, scale, input_pos, token_pos, return_weights, sliding_window, softcap, return_lse=True)
 
@@ -225,9 +239,9 @@ def sdpa_bwd(
     """Returns ``dq (B,H,q,D)``, ``dk, dv (B,G,kv,D)`` (fp32 for dk/dv). With
     ``dk_accum/dv_accum`` (fp32, cache shaped) the K/V gradients are added into their
     first ``kv`` slots instead and ``None`` is returned for them."""
-    if query.is_cuda and _cuda().sdpa_bwd_supported(query, key, sliding_window, softcap):
+    if query.is_cuda and _NATIVE_ATTENTION and _cuda().sdpa_bwd_supported(query, key, sliding_window, softcap):
         return _cuda().sdpa_bwd(grad_out, query, key, value, out, lse, scale, input_pos, token_pos, dk_accum, dv_accum)
-    if query.is_cuda:
+    if query.is_cuda and _NATIVE_ATTENTION:
         _restatement_on_gpu("sdpa_bwd", _sdpa_shape_text(query, sliding_window, softcap))
     dq, dk, dv = ref.sdpa_backward(grad_out, query, key, value, scale, input_pos, token_pos, sliding_window, softcap)
     if dk_accum is not None:
@@ -361,9 +375,9 @@ def cross_entropy_sum(logits: torch.Tensor, targets: torch.Tensor, ignore_index:
 def decode_attention(query, key, value, scale, input_pos, token_pos=None, return_weights=False):
     """One new query token against ``key/value (B,G,L,D)`` (all slots hold tokens at or
     before the query position). Returns ``(out (B,1,H·D), weights (B,G,L) | None)``."""
-    if query.is_cuda and _cuda().decode_supported(query, key.shape[1]):
+    if query.is_cuda and _NATIVE_ATTENTION and _cuda().decode_supported(query, key.shape[1]):
         return _cuda().decode_attention(query, key.contiguous(), value.contiguous(), scale, key.shape[2], return_weights)
-    if query.is_cuda:
+    if query.is_cuda and _NATIVE_ATTENTION:
         _restatement_on_gpu("decode_attention", f"head size {query.shape[-1]}, dtype {query.dtype}, {query.shape[1]} heads over {key.shape[1]} groups")
     out, w = ref.sdpa(query, key, value, scale, input_pos, token_pos, return_weights)
     return out, w

@@ -111,6 +111,10 @@ def build_mask(
     return mask
 
 
+DEFAULT_TMP_ARRAY_LIMIT_GB = 2.0
+TMP_ARRAY_LIMIT_GB = DEFAULT_TMP_ARRAY_LIMIT_GB  # see keys_values_b200.ops.set_tmp_array_limit_gb
+
+
 def sdpa(
     query: torch.Tensor,
     key: torch.Tensor,
@@ -128,25 +132,34 @@ def sdpa(
     ``query (B,H,q,D)``, ``key/value (B,G,kv,D)``. Returns ``out (B,q,H·D)`` and,
     if requested, ``weights (B,G,kv)`` fp32 = softmax weights summed over the
     query axis and averaged over the ``H/G`` query heads of the group, and
-    ``lse (B,H,q)`` fp32 (natural log)."""
+    ``lse (B,H,q)`` fp32 (natural log). The fp32 score matrix is formed for blocks of query
+    rows of at most ``TMP_ARRAY_LIMIT_GB`` at a time (role of the blocked eager SDPA of the
+    reference, ``keys_values/attention/base.py:660-742``)."""
     B, H, q_len, D = query.shape
     G, kv_len = key.shape[1], key.shape[2]
     gs = H // G
-    qf = query.float().view(B, G, gs, q_len, D)
     kf = key.float()
     vf = value.float()
-    scores = torch.einsum("bgsqd,bgkd->bgsqk", qf, kf) * scale
-    if softcap is not None:
-        scores = torch.tanh(scores / softcap) * softcap
-    mask = build_mask(token_pos, input_pos, q_len, kv_len, B, G, query.device, sliding_window)
-    scores = scores.masked_fill(~mask.unsqueeze(2), float("-inf"))
-    lse = torch.logsumexp(scores, dim=-1)
-    probs = torch.exp(scores - lse.unsqueeze(-1))
-    out = torch.einsum("bgsqk,bgkd->bgsqd", probs, vf)
-    out = out.reshape(B, H, q_len, D).transpose(1, 2).reshape(B, q_len, H * D).to(query.dtype)
-    weights = probs.sum(dim=(2, 3)) / gs if return_weights else None
+    rows = max(1, int(TMP_ARRAY_LIMIT_GB * 2**30 / (4.0 * B * H * kv_len)))
+    outs, lses = [], []
+    weights = torch.zeros((B, G, kv_len), dtype=torch.float32, device=query.device) if return_weights else None
+    for r0 in range(0, q_len, rows):
+        r1 = min(q_len, r0 + rows)
+        qf = query[:, :, r0:r1].float().reshape(B, G, gs, r1 - r0, D)
+        scores = torch.einsum("bgsqd,bgkd->bgsqk", qf, kf) * scale
+        if softcap is not None:
+            scores = torch.tanh(scores / softcap) * softcap
+        mask = build_mask(token_pos, input_pos + r0, r1 - r0, kv_len, B, G, query.device, sliding_window)
+        scores = scores.masked_fill(~mask.unsqueeze(2), float("-inf"))
+        lse = torch.logsumexp(scores, dim=-1)
+        probs = torch.exp(scores - lse.unsqueeze(-1))
+        outs.append(torch.einsum("bgsqk,bgkd->bgsqd", probs, vf).reshape(B, H, r1 - r0, D))
+        lses.append(lse.reshape(B, H, r1 - r0))
+        if return_weights:
+            weights += probs.sum(dim=(2, 3)) / gs
+    out = torch.cat(outs, dim=2).transpose(1, 2).reshape(B, q_len, H * D).to(query.dtype)
     if return_lse:
-        return out, weights, lse.reshape(B, H, q_len)
+        return out, weights, torch.cat(lses, dim=2)
     return out, weights
 
 

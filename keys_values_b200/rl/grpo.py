@@ -49,7 +49,7 @@ class GRPOLossHeadModel(HeadModel):
     def forward(self, model_outputs, targets, input_pos):
         if targets is None:
             return torch.zeros(model_outputs.shape[0], device=model_outputs.device, dtype=torch.float32)
-        diff = self._check_model_outputs_targets(model_outputs, targets, self._vocab_size)
+        diff = self._target_offset(model_outputs, targets, self._vocab_size)
         n = targets.shape[1]
         # position of this chunk's targets inside the full target sequence (targets are right-aligned)
         end_pos = input_pos + model_outputs.shape[1]

@@ -29,7 +29,7 @@ class LogProbsHeadModel(HeadModel):
     def forward(self, model_outputs, targets, input_pos):
         if targets is None:
             return torch.zeros(model_outputs.shape[0], device=model_outputs.device, dtype=torch.float32)
-        diff = self._check_model_outputs_targets(model_outputs, targets, self._vocab_size)
+        diff = self._target_offset(model_outputs, targets, self._vocab_size)
         logits = model_outputs[:, diff:, :].float() / self.temperature
         safe = targets.clamp(min=0)
         lp = torch.gather(F.log_softmax(logits, dim=-1), 2, safe.unsqueeze(-1)).squeeze(-1)

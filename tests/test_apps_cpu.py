@@ -107,7 +107,16 @@ def test_cli_finetune_lora_then_resume_then_eval(tmp_path):
     assert (out / "step-000002" / "training_state.pth").is_file()
     rows = list(csv.DictReader(open(out / "logs" / "metrics.csv")))
     assert any(r_.get("loss") for r_ in rows) and any(r_.get("val_loss") for r_ in rows)
-    r = _run_cli(["finetune_long_lora", *common, "--train.max_steps", "3", "--resume", "auto"], tmp_path)
+    # throughput monitor, example generation with the validation, final performance report
+    assert any(r_.get("throughput/items_per_sec") for r_ in rows)
+    assert "example continuation" in r.stdout and "performance report:" in r.stdout
+    import json
+
+    report = json.loads((out / "performance_report.json").read_text())
+    assert report["optimizer_steps"] == 2 and report["tokens"] > 0 and report["tokens_per_sec"] > 0
+    r = _run_cli(["finetune_long_lora", *common, "--train.max_steps", "3", "--resume", "auto", "--sdpa.use_eager_sdpa_always", "true",
+                  "--sdpa.tmp_array_limit_gb", "0.001", "--sdpa.flex_attention", "true"], tmp_path)
+    assert "flex_attention given" in r.stdout and "blocked PyTorch restatement" in r.stdout
     assert r.returncode == 0, r.stdout + r.stderr
     assert "step 3/3" in r.stdout and "step 1/3" not in r.stdout
 
@@ -158,6 +167,32 @@ def test_cli_finetune_offload_lora_with_host_optimizer(tmp_path):
     r = _run_cli(["finetune_offload_lora", *common, "--train.max_steps", "3", "--resume", "auto"], tmp_path)
     assert r.returncode == 0, r.stdout + r.stderr
     assert "step 3/3" in r.stdout
+
+
+def test_throughput_monitor_and_blocked_restatement():
+    from keys_values_b200 import ops
+    from keys_values_b200.finetune.utils import ThroughputMonitor
+    from keys_values_b200.ops import reference as ref
+
+    tm = ThroughputMonitor(world_size=4, window=3)
+    assert tm.compute() == {}
+    for k in range(1, 6):
+        tm.update(time=2.0 * k, batches=k, samples=2 * k, lengths=1000 * k)
+    rates = tm.compute()
+    assert rates["throughput/device/items_per_sec"] == pytest.approx(500.0) and rates["throughput/items_per_sec"] == pytest.approx(2000.0)
+    assert rates["throughput/batches_per_sec"] == pytest.approx(2.0)
+    # the restatement gives the same result whatever the block size of its score matrix
+    torch.manual_seed(0)
+    q, k, v = torch.randn(2, 4, 50, 16), torch.randn(2, 2, 90, 16), torch.randn(2, 2, 90, 16)
+    tp = torch.stack([torch.stack([torch.randperm(90) for _ in range(2)]) for _ in range(2)]).to(torch.int32)
+    whole = ref.sdpa(q, k, v, 0.25, 40, tp, True, return_lse=True)
+    ops.set_tmp_array_limit_gb(1e-5)
+    try:
+        blocked = ref.sdpa(q, k, v, 0.25, 40, tp, True, return_lse=True)
+    finally:
+        ops.set_tmp_array_limit_gb(None)
+    for a, b in zip(whole, blocked):
+        torch.testing.assert_close(a, b, atol=1e-5, rtol=1e-5)
 
 
 def test_evaluation_lock_grid(tmp_path):
