@@ -49,7 +49,10 @@ class GradientArgs:
     cell length; ``single_tokens_for_targets``: schedule target tokens as chunks of one;
     ``layercp_qname / cachecp_qname``: optional quantization of layer-input / KV checkpoints;
     ``offload_checkpoints``: keep checkpoints in pinned host memory instead of device memory;
-    ``save_attention_outputs``: keep attention outputs for the backward pass (None = auto)."""
+    ``save_attention_outputs``: keep attention outputs for the backward pass (None = auto);
+    ``offload_weights``: the transformer blocks' weights live in pinned host memory and are streamed to the
+    device block by block (``weight_slots`` device slots, default two per row of layers); the optimizer then
+    updates the trainable block parameters on the host."""
 
     layers_per_cell: int = 1
     chunks_per_cell_multiplier: float = 1.0
@@ -62,6 +65,8 @@ class GradientArgs:
     cachecp_pin_memory: bool = True
     offload_checkpoints: bool = False
     save_attention_outputs: Optional[bool] = None
+    offload_weights: bool = False
+    weight_slots: Optional[int] = None
 
 
 @dataclass

@@ -118,7 +118,7 @@ def create_gpt_model(checkpoint_dir: Path, model_name: Optional[str], lora: Opti
 
 
 def wrap_gpt_model(gpt_model, head_model, kv_cache: KVCacheArgs, grad: GradientArgs, micro_batch_size: int, device, dtype,
-                   profile_steps: bool = False) -> LongContextGradientModel:
+                   profile_steps: bool = False, weight_grad_reduce_fn=None) -> LongContextGradientModel:
     """Create the KV caches (optionally with host offload of the quantized storage), assign
     them to the model, and wrap model + head into the gradient model."""
     ck = kv_cache.resolved_cache_kwargs()
@@ -130,13 +130,19 @@ def wrap_gpt_model(gpt_model, head_model, kv_cache: KVCacheArgs, grad: GradientA
         caches = KVCacheFactory.create(gpt_model, kv_cache.name, micro_batch_size, kv_cache.cache_length, device=device, dtype=dtype,
                                        cache_kwargs=ck)
     gpt_model.assign_kv_caches(caches)
-    return LongContextGradientModel(
+    model = LongContextGradientModel(
         gpt_model, head_model, layers_per_cell=grad.layers_per_cell, chunk_size=kv_cache.chunk_size,
         randomize_chunk_sizes=kv_cache.randomize_chunk_sizes, chunks_per_cell_multiplier=grad.chunks_per_cell_multiplier,
         single_tokens_for_targets=grad.single_tokens_for_targets, offload_checkpoints=grad.offload_checkpoints,
         pin_memory=grad.layercp_pin_memory, layercp_qname=grad.layercp_qname, cachecp_qname=grad.cachecp_qname,
         save_attention_outputs=grad.save_attention_outputs, profile_steps=profile_steps,
     )
+    if grad.offload_weights:
+        from keys_values_b200.optimize.weight_streaming import WeightStreamer
+
+        model.weight_streamer = WeightStreamer(gpt_model, device, n_slots=grad.weight_slots or 2 * grad.layers_per_cell,
+                                               reduce_fn=weight_grad_reduce_fn)
+    return model
 
 
 def apply_sdpa_args(sdpa: Optional[SDPAArgs], rank: int = 0) -> None:
@@ -172,10 +178,20 @@ def main(rank: int, local_rank: int, world_size: int, *, checkpoint_dir, out_dir
     head_model = HeadModelFactory.create(head_model_name, config, **head_model_kwargs).to(device)
     resume_dir = find_resume_dir(out_dir, resume)
     fu.load_model_checkpoint(gpt_model, checkpoint_dir, resume_dir, head_model)
-    model = wrap_gpt_model(gpt_model, head_model, kv_cache, grad, train.micro_batch_size, device, dtype, profile_steps=profile_grad_times > 0)
+    reduce_fn = None
+    if world_size > 1:
+        def reduce_fn(flat: torch.Tensor) -> None:  # streamed blocks: mean over ranks before the gradients leave for the host
+            dist.all_reduce(flat, op=dist.ReduceOp.SUM)
+            flat.mul_(1.0 / world_size)
+    model = wrap_gpt_model(gpt_model, head_model, kv_cache, grad, train.micro_batch_size, device, dtype, profile_steps=profile_grad_times > 0,
+                           weight_grad_reduce_fn=reduce_fn)
     if rank == 0:
         print(f"trainable parameters: {num_parameters(gpt_model, True):,} of {num_parameters(gpt_model):,}")
     params = [p for p in gpt_model.parameters() if p.requires_grad] + [p for p in head_model.parameters() if p.requires_grad]
+    if grad.offload_weights and optimizer.host_offload:
+        # the streamed blocks' parameters already live on the host and are updated there; the optimizer keeps its
+        # state next to each parameter (host for the blocks, device for embedding and head)
+        optimizer = dataclasses.replace(optimizer, host_offload=False)
     opt = optimizer.create(params)
     # data
     tokenizer = None
@@ -209,8 +225,10 @@ def main(rank: int, local_rank: int, world_size: int, *, checkpoint_dir, out_dir
     if world_size > 1:
         from keys_values_b200.parallel.dp import GradientReducer
 
-        grad_reducer = GradientReducer(params, world_size=world_size, rank=rank, device=device)
-        model.row_done_hook = grad_reducer.row_done_hook(gpt_model)
+        resident = [p for p in params if p.device.type == device.type]  # streamed blocks reduce their own gradients
+        grad_reducer = GradientReducer(resident, world_size=world_size, rank=rank, device=device) if resident else None
+        if grad_reducer is not None:
+            model.row_done_hook = grad_reducer.row_done_hook(gpt_model)
     pad_id = getattr(tokenizer, "pad_id", None) or 0
     batch_transform = BatchTransformFactory.from_head_model(head_model_name, pad_id=pad_id)
     fit(model=model, optimizer=opt, scheduler=scheduler, train_loader=train_loader, val_loader=val_loader, batch_transform=batch_transform,
@@ -349,6 +367,8 @@ def fit(*, model, optimizer, scheduler, train_loader, val_loader, batch_transfor
             grad_reducer.flat.zero_()
         else:
             optimizer.zero_grad(set_to_none=True)
+        if getattr(model, "weight_streamer", None) is not None:
+            model.weight_streamer.zero_grad()
         step_loss = torch.zeros((), device=device)
         step_tokens = 0
         if recorder is not None:

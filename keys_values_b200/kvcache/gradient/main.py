@@ -231,8 +231,15 @@ class LongContextGradientModel(LongContextInferenceModel):
         bounds = self._row_boundaries()
         caches = gpt.get_kv_caches()
         blocks = gpt.transformer.h
+        ws = self.weight_streamer
         for r in range(len(bounds) - 2, -1, -1):
             first, end = bounds[r], bounds[r + 1]
+            if ws is not None:
+                # host-resident blocks: this row's blocks on the device with gradient buffers, the next row's on their way
+                ws.acquire_many(range(first, end), need_grad=True)
+                if r > 0:
+                    for l in range(bounds[r - 1], bounds[r]):
+                        ws.prefetch(l)
             states, tcaches = [], []
             for l in range(first, end):
                 c = caches[l]
@@ -267,8 +274,12 @@ class LongContextGradientModel(LongContextInferenceModel):
             if self._attn_saved is not None:
                 for l in range(first, end):
                     self._attn_saved[l] = None  # release as soon as the row is done
+            if ws is not None:
+                ws.release_many(range(first, end), with_gradients=True)
             if self.row_done_hook is not None:
                 self.row_done_hook(first, end)
+        if ws is not None:
+            ws.collect_gradients()
         # 3) Input embeddings
         wte = gpt.transformer.wte.weight
         if wte.requires_grad:

@@ -183,6 +183,8 @@ class LongContextInferenceModel(GPTAndHeadModel):
         self.fixed_max_seq_length: Optional[int] = None
         self.layer_input_hook: Optional[LayerInputHook] = None
         self.cell_boundary_hook: Optional[CellBoundaryHook] = None
+        # keys_values_b200.optimize.weight_streaming.WeightStreamer when the blocks' weights live on the host
+        self.weight_streamer = None
 
     # ------------------------------------------------------------ scheduling
     def _init_members_from_tokens(self, input_ids: torch.Tensor, targets: Optional[torch.Tensor]) -> None:
@@ -245,7 +247,13 @@ class LongContextInferenceModel(GPTAndHeadModel):
             for layer_idx, block in enumerate(gpt.transformer.h):
                 if self.layer_input_hook is not None:
                     self.layer_input_hook(x, layer_idx, cell.start, cell.end)
+                ws = self.weight_streamer
+                if ws is not None:  # host-resident blocks: this one on the device, the next one on its way
+                    ws.acquire(layer_idx)
+                    ws.prefetch(layer_idx + 1)
                 x = block(x, ids, gpt.mha, chunk_sizes=cell.chunk_sizes)
+                if ws is not None:
+                    ws.release(layer_idx)
                 if self.cell_boundary_hook is not None:
                     self.cell_boundary_hook(layer_idx, cell_idx, cell.end)
             if self.layer_input_hook is not None:

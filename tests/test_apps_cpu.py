@@ -169,6 +169,26 @@ def test_cli_finetune_offload_lora_with_host_optimizer(tmp_path):
     assert "step 3/3" in r.stdout
 
 
+def test_cli_finetune_offload_full_with_host_resident_weights(tmp_path):
+    """``--grad.offload_weights true``: block weights in host memory, streamed per layer; training runs and saves."""
+    from keys_values_b200.config import Config
+
+    ckpt = tmp_path / "ckpt"
+    ckpt.mkdir()
+    Config.from_name("tiny-gpt").save(ckpt / "model_config.yaml")
+    out = tmp_path / "out"
+    args = [str(ckpt), "--out_dir", str(out), "--precision", "32-true", "--kv_cache.name", "h2o-default", "--kv_cache.cache_length", "64",
+            "--kv_cache.chunk_size", "16", "--train.global_batch_size", "1", "--train.micro_batch_size", "1", "--train.save_interval", "2",
+            "--train.lr_warmup_steps", "1", "--eval.interval", "100", "--eval.max_iters", "1", "--eval.final_validation", "false",
+            "--yarn_rope", "false", "--train.max_steps", "2", "--grad.offload_weights", "true", "--grad.offload_checkpoints", "true"]
+    r = _run_cli(["finetune_offload_full", *args], tmp_path)
+    assert r.returncode == 0, r.stdout + r.stderr
+    losses = [float(x.split("loss")[1].split("|")[0]) for x in r.stdout.splitlines() if x.startswith("step ")]
+    assert len(losses) == 2 and all(l == l for l in losses)
+    sd = torch.load(out / "final" / "lit_model.pth", weights_only=True)["model"]
+    assert any(k.startswith("transformer.h.0.") for k in sd)
+
+
 def test_throughput_monitor_and_blocked_restatement():
     from keys_values_b200 import ops
     from keys_values_b200.finetune.utils import ThroughputMonitor
