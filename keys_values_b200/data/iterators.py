@@ -15,12 +15,13 @@ import torch
 
 class SimilarSequenceLengthIterator:
     def __init__(self, sequence_lengths: Sequence[int], micro_batch_size: int, num_devices: int = 1, rank: int = 0, shuffle: bool = True,
-                 longest_first: bool = False, seed: int = 0, drop_last: bool = True):
+                 longest_first: bool = False, seed: int = 0, drop_last: bool = True, shortest_first: bool = False):
         if not (0 <= rank < num_devices):
             raise ValueError(f"rank = {rank} must be in [0, {num_devices})")
         self.lengths = list(sequence_lengths)
         self.micro_batch_size, self.num_devices, self.rank = micro_batch_size, num_devices, rank
         self.shuffle, self.longest_first, self.seed, self.drop_last = shuffle, longest_first, seed, drop_last
+        self.shortest_first = shortest_first  # the first batch of every epoch holds the shortest sequences, the others are shuffled
         self.epoch = 0
         self.pos = 0
         self._batches: List[List[int]] = []
@@ -40,6 +41,8 @@ class SimilarSequenceLengthIterator:
                 batches[-1] = batches[-1] + order[: gbs - len(batches[-1])]
         if self.shuffle and not self.longest_first:
             idx = torch.randperm(len(batches), generator=g).tolist()
+            if self.shortest_first and batches:
+                idx = [len(batches) - 1] + [i for i in idx if i != len(batches) - 1]
             batches = [batches[i] for i in idx]
         self._batches = batches
 

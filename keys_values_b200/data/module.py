@@ -14,22 +14,33 @@ from keys_values_b200.data.iterators import SimilarSequenceLengthSampler
 
 
 class SequenceLengthFilteredDataModule(DataModule):
-    """Wraps lists of SFT records: computes token lengths once (cached as JSON next to the
-    data), drops records longer than ``max_seq_length`` (or shorter than ``min_seq_length``) and
-    serves length-bucketed, rank-aware batches."""
+    """Wraps lists of SFT records: token lengths are taken from the records (``num_tokens_instruction``, filled by
+    the dataset modules from their metadata files), from a JSON cache next to the data, or computed once; records
+    longer than ``max_seq_length`` (or shorter than ``min_seq_length``) are dropped; batches are length-bucketed and
+    rank-aware. With ``class_labels`` set the datasets are sequence-classification datasets (prompt + class index)."""
 
     def __init__(self, train_records: List[Dict[str, str]], val_records: List[Dict[str, str]], prompt_style=None, mask_prompt: bool = True,
                  min_seq_length: int = 0, max_seq_length: Optional[int] = None, seed: int = 42, num_workers: int = 0,
-                 length_cache: Optional[Path] = None, longest_first: bool = False):
+                 length_cache: Optional[Path] = None, longest_first: bool = False, shortest_first: bool = False, ignore_index: int = -100):
+        if longest_first and shortest_first:
+            raise ValueError("trainloader_longest_first and trainloader_shortest_first cannot both be set")
         self.train_records, self.val_records = train_records, val_records
-        self.prompt_style, self.mask_prompt = prompt_style, mask_prompt
+        self.prompt_style, self.mask_prompt, self.ignore_index = prompt_style, mask_prompt, ignore_index
         self.min_seq_length, self.max_len_filter = min_seq_length, max_seq_length
-        self.seed, self.num_workers, self.length_cache, self.longest_first = seed, num_workers, length_cache, longest_first
+        self.seed, self.num_workers, self.length_cache = seed, num_workers, length_cache
+        self.longest_first, self.shortest_first = longest_first, shortest_first
         self.num_devices, self.rank = 1, 0
+        self.tokenizer = None
+        self.class_labels: Optional[Sequence[str]] = None
         self.train_dataset = self.val_dataset = None
         self._train_lengths: List[int] = []
         self._val_lengths: List[int] = []
         self._train_loader = None
+
+    @property
+    def model_name(self) -> str:
+        """Name under which token lengths are filed: they depend on the tokenizer, i.e. on the model."""
+        return str(getattr(self.tokenizer, "model_name", None) or "default")
 
     def connect(self, tokenizer=None, batch_size: int = 1, max_seq_length: Optional[int] = None, num_devices: int = 1, rank: int = 0, **kwargs):
         super().connect(tokenizer, batch_size, max_seq_length)
@@ -37,7 +48,16 @@ class SequenceLengthFilteredDataModule(DataModule):
         if max_seq_length is not None and self.max_len_filter is None:
             self.max_len_filter = max_seq_length
 
-    def _lengths(self, dataset: SFTDataset, tag: str) -> List[int]:
+    def _make_dataset(self, records):
+        if self.class_labels is not None:
+            from keys_values_b200.data.sequence_classification import SequenceClassificationDataset
+
+            return SequenceClassificationDataset(records, self.tokenizer, self.prompt_style, self.class_labels)
+        return SFTDataset(records, self.tokenizer, self.prompt_style, -1, self.mask_prompt, self.ignore_index)
+
+    def _lengths(self, dataset, records, tag: str) -> List[int]:
+        if records and all("num_tokens_instruction" in r for r in records):
+            return [int(r["num_tokens_instruction"]) for r in records]
         if self.length_cache is not None:
             p = Path(self.length_cache) / f"lengths_{tag}.json"
             if p.is_file():
@@ -50,12 +70,11 @@ class SequenceLengthFilteredDataModule(DataModule):
             (Path(self.length_cache) / f"lengths_{tag}.json").write_text(json.dumps(lengths))
         return lengths
 
-    def _filter(self, records, tag):
-        ds = SFTDataset(records, self.tokenizer, self.prompt_style, -1, self.mask_prompt)
-        lengths = self._lengths(ds, tag)
-        hi = self.max_len_filter if self.max_len_filter is not None else float("inf")
+    def _filter(self, records, tag, apply_limit: bool = True):
+        lengths = self._lengths(self._make_dataset(records), records, tag)
+        hi = self.max_len_filter if (apply_limit and self.max_len_filter is not None) else float("inf")
         keep = [i for i, n in enumerate(lengths) if self.min_seq_length <= n <= hi]
-        return SFTDataset([records[i] for i in keep], self.tokenizer, self.prompt_style, -1, self.mask_prompt), [lengths[i] for i in keep]
+        return self._make_dataset([records[i] for i in keep]), [lengths[i] for i in keep]
 
     def setup(self, stage: str = "") -> None:
         self.train_dataset, self._train_lengths = self._filter(self.train_records, "train")
@@ -63,9 +82,16 @@ class SequenceLengthFilteredDataModule(DataModule):
 
     def _loader(self, dataset, lengths, shuffle: bool):
         sampler = SimilarSequenceLengthSampler(lengths, self.batch_size, self.num_devices, self.rank, shuffle=shuffle,
-                                               longest_first=self.longest_first, seed=self.seed, drop_last=shuffle)
+                                               longest_first=self.longest_first and shuffle, seed=self.seed, drop_last=shuffle,
+                                               shortest_first=self.shortest_first and shuffle)
         pad_id = getattr(self.tokenizer, "pad_id", None) or 0
-        return MyDataLoader(dataset, batch_sampler=sampler, num_workers=self.num_workers, collate_fn=get_sft_collate_fn(pad_id=pad_id))
+        if self.class_labels is not None:
+            from keys_values_b200.data.sequence_classification import get_seq_class_collate_fn
+
+            collate = get_seq_class_collate_fn(pad_id=pad_id)
+        else:
+            collate = get_sft_collate_fn(pad_id=pad_id)
+        return MyDataLoader(dataset, batch_sampler=sampler, num_workers=self.num_workers, collate_fn=collate)
 
     def train_dataloader(self):
         self._train_loader = self._loader(self.train_dataset, self._train_lengths, True)
