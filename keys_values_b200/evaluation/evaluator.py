@@ -7,18 +7,18 @@ from typing import Any, Callable, Dict, List, Optional, Sequence
 import torch
 
 from keys_values_b200.evaluation.metrics import METRICS
-from keys_values_b200.evaluation.response_parser import parse_answer
 from keys_values_b200.generate.base import batched_generate_fn
 
 
 class SampleBasedMetricsEvaluator:
     def __init__(self, gpt_model, tokenizer, metric: str = "sub_exact_match", max_new_tokens: int = 64, prompt_chunksize: int = 1024,
-                 parser: Callable[[str], str] = parse_answer, sample_args: Optional[dict] = None):
+                 parser: Optional[Callable[[str], str]] = None, sample_args: Optional[dict] = None):
         if metric not in METRICS:
             raise ValueError(f"metric = {metric} not supported; must be in {list(METRICS)}")
         self.gpt_model, self.tokenizer, self.metric_name, self.metric = gpt_model, tokenizer, metric, METRICS[metric]
-        self.max_new_tokens, self.prompt_chunksize, self.parser = max_new_tokens, prompt_chunksize, parser
-        self.sample_args = sample_args or dict(temperature=0.0)
+        self.max_new_tokens, self.prompt_chunksize = max_new_tokens, prompt_chunksize
+        self.parser = parser or str.strip  # the metrics strip lead-ins and quotes themselves
+        self.sample_args = {k: v for k, v in (sample_args or dict(temperature=0.0)).items() if v is not None}
 
     @torch.no_grad()
     def __call__(self, prompts: torch.Tensor, references: Sequence[Sequence[str]]) -> Dict[str, Any]:

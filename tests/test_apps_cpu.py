@@ -9,6 +9,7 @@ from pathlib import Path
 
 import pytest
 import torch
+import yaml
 
 ROOT = Path(__file__).resolve().parent.parent
 
@@ -119,6 +120,23 @@ def test_cli_finetune_lora_then_resume_then_eval(tmp_path):
     assert "flex_attention given" in r.stdout and "blocked PyTorch restatement" in r.stdout
     assert r.returncode == 0, r.stdout + r.stderr
     assert "step 3/3" in r.stdout and "step 1/3" not in r.stdout
+    # evaluation driven by a setups file: every detected checkpoint, with the cache the run was trained with and a second one
+    from keys_values_b200.evaluation import longcontext_eval_ext as ext
+
+    assert ext.detect_checkpoints(out)[0] == "final" and "step-000002" in ext.detect_checkpoints(out)
+    setups = tmp_path / "setups.yaml"
+    setups.write_text(yaml.safe_dump([{"out_dir": str(out), "model_type": "lora", "eval_tasks": ["final", "step-000002"],
+                                       "setups": ["h2o-torch-quantized8", "lastrec-default"]}]))
+    r = _run_cli(["eval_long_ext", str(setups), "--precision", "32-true", "--eval.max_iters", "2"], tmp_path)
+    assert r.returncode == 0, r.stdout + r.stderr
+    files = sorted(str(p.relative_to(out)) for p in out.glob("*__*/eval/eval_metrics_*.csv"))
+    assert len(files) == 2 * 2 * 2, files
+    rows = list(csv.DictReader(open(out / files[0])))
+    assert rows and float(rows[0]["loss"]) > 0
+    with pytest.raises(ValueError, match="model_type is 'full'"):
+        ext.load_configuration(out / "final", "full")
+    with pytest.raises(ValueError, match="skip_eval needs"):
+        ext.setup_from_file(setups, skip_eval=True)
 
 
 def test_cli_finetune_full_resume_restores_trained_weights(tmp_path):
