@@ -36,6 +36,11 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", type=str, default="b200", choices=["b200", "reference"])
+    ap.add_argument("--config", type=str, default="train", choices=["train", "inference"],
+                    help="train: long-context LoRA fine-tuning step, data parallel (the headline); inference: chunked prefill + "
+                         "greedy decoding of Llama-3-8B through an int4 H2O cache, tensor parallel over the launched ranks")
+    ap.add_argument("--batch", type=int, default=4, help="inference: prompts per batch")
+    ap.add_argument("--decode", type=int, default=512, help="inference: generated tokens per prompt")
     ap.add_argument("--model", type=str, default="Qwen3-4B")
     ap.add_argument("--seq-len", type=int, default=131072)
     ap.add_argument("--cache-length", type=int, default=16384)
@@ -209,8 +214,54 @@ def run_b200(args) -> dict:
     return result if rank == 0 else {}
 
 
+def run_inference(args) -> dict:
+    """Chunked prefill + greedy decode, tensor parallel over the launched ranks. One "step" is one batch of
+    prompts processed and decoded; the best of ``--steps`` runs is reported (``--warmup`` is covered by the
+    short-prompt pass and the untimed decode steps of every run)."""
+    from keys_values_b200.tools import decode_bench
+
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", 0)))
+    sampler.start()
+    model = "Llama-3-8B" if args.model == "Qwen3-4B" else args.model
+    seq = 65536 if args.seq_len == 131072 else args.seq_len
+    cache_name = "h2o-torch-quantized4" if args.cache_name == "h2o-torch-quantized8" else args.cache_name
+    cache_length = 8192 if args.cache_length == 16384 else args.cache_length
+    chunk = 2048 if args.chunk_size == 1024 else args.chunk_size
+    r = decode_bench.run(model, args.batch, seq, args.decode, cache_name, cache_length, chunk, True, args.n_layer, True,
+                         repeats=max(1, args.steps))
+    clocks = sampler.stop()
+    if not r:
+        return {}
+    return {
+        "metric": "long-ctx inference tokens/s (prefill + decode)", "value": r["total_tokens_per_s"], "unit": "tokens/s", "n_gpus": world,
+        "steps": max(1, args.steps), "warmup": args.warmup, "ms_per_step": 1e3 * (r["prefill_s"] + r["decode_s"]), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform-random token ids, random-init weights",
+        "impl": "b200", "prefill_tokens_per_s": r["prefill_tokens_per_s"], "decode_tokens_per_s": r["decode_tokens_per_s"],
+        "ms_per_decode_step": r["ms_per_decode_step"],
+        "config": {"model": r["model"] + "-architecture", "global_batch": args.batch, "seq_len": seq, "parallelism": f"tp{world}",
+                   "cache": cache_name, "cache_length": cache_length, "chunk_size": chunk, "decode_tokens": args.decode,
+                   "prefill_path": r["prefill_path"], "decode_mode": r["decode_mode"],
+                   "l2": "weights and caches (>16 GB) exceed the 126 MB L2"},
+        "clocks": clocks,
+        # prompts come from pinned host memory inside the timed prefill, the generated tokens are read back inside the timed decode
+        "e2e": {"value": r["total_tokens_per_s"], "unit": "tokens/s", "h2d_bytes_per_step": r["h2d_bytes"], "d2h_bytes_per_step": r["d2h_bytes"]},
+        "gpu_launches": r["native_launches"], "ranks_generated_same_tokens": r["ranks_generated_same_tokens"], "peak_mem_gb": r["peak_mem_gb"],
+    }
+
+
 def main():
     args = parse_args()
+    if args.config == "inference" and args.impl == "reference":
+        # the reference has no tensor parallelism and no chunked-inference benchmark of this shape
+        print(json.dumps({"impl": "reference", "unavailable": "the inference configuration has a reference arm at the kernel level only "
+                          "(keys_values_b200.tools.microbench reference); the reference library has no tensor parallelism"}), flush=True)
+        return
+    if args.config == "inference":
+        out = run_inference(args)
+        if out:
+            print(json.dumps(out), flush=True)
+        return
     if args.impl == "reference":
         from baseline.reference_arm import run_reference
 

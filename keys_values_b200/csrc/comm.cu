@@ -172,6 +172,86 @@ allreduce_mean_kernel(CommPeers peers, int rank, int world, long long start, lon
   cross_gpu_barrier(peers, rank, world, epoch0 + 1, sync, status, limit);
 }
 
+// One-shot all-reduce (sum) for small payloads (decode steps under tensor parallelism: a few rows of the hidden
+// state). Every rank's producer kernel has written its partial result into its own slot of symmetric memory
+// before this launch (same stream). Each CTA tells every peer "my slot is ready" (one flag word per writer rank
+// and CTA, so there is no grid barrier and no assumption on which CTAs are resident together), waits for the
+// peers' words, then reads its part of ALL slots with plain peer loads, sums in fp32 in rank order (identical
+// bits on every rank), adds an optional residual and writes the local output. One NVLink round trip.
+//
+// A slot must not be rewritten while a peer may still read it: the caller rotates over several slots
+// ("sites"); a rank cannot be more than one call ahead of a peer, because every call waits for the peer's
+// word of that call, so a distance of two calls between uses of one site is enough.
+//
+// The epoch is epoch_base + *epoch_word: in a captured decode step the base is frozen in the graph and the
+// device word, which the graph advances once per replay, makes the epochs of later replays larger.
+constexpr int ONESHOT_MAX_CTAS = 16;
+constexpr int ONESHOT_THREADS = 256;
+
+struct OneShotPeers {
+  const void* slot[COMM_MAX_RANKS];  // this site's slot of every rank
+  uint32_t* flags[COMM_MAX_RANKS];   // this site's flag words of every rank: [COMM_MAX_RANKS][ONESHOT_MAX_CTAS]
+};
+
+__device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(ONESHOT_THREADS)
+oneshot_allreduce_kernel(OneShotPeers peers, int rank, int world, long long nvec, const T* __restrict__ residual, T* __restrict__ out,
+                         uint32_t epoch_base, const uint32_t* epoch_word, int* status, long long limit) {
+  constexpr int V = 16 / sizeof(T);
+  __shared__ int ok_s;
+  const uint32_t epoch = epoch_base + (epoch_word ? *epoch_word : 0u);
+  if (threadIdx.x == 0) ok_s = 1;
+  __syncthreads();
+  if ((int)threadIdx.x < world && (int)threadIdx.x != rank) {
+    const int peer = threadIdx.x;
+    st_release_sys(peers.flags[peer] + rank * ONESHOT_MAX_CTAS + blockIdx.x, epoch);
+    const uint32_t* mine = peers.flags[rank] + peer * ONESHOT_MAX_CTAS + blockIdx.x;
+    const long long t0 = clock64();
+    while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
+      if (clock64() - t0 > limit) {
+        if (status) atomicCAS(status, 0, STATUS_TIMEOUT_PEER_FLAG);
+        ok_s = 0;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (!ok_s) return;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    float acc[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) acc[j] = 0.f;
+    uint4 raw[COMM_MAX_RANKS];
+#pragma unroll
+    for (int r = 0; r < COMM_MAX_RANKS; ++r)
+      if (r < world) raw[r] = ld_volatile_v4(reinterpret_cast<const uint4*>(peers.slot[r]) + i);
+#pragma unroll
+    for (int r = 0; r < COMM_MAX_RANKS; ++r)
+      if (r < world) {
+        const T* e = reinterpret_cast<const T*>(&raw[r]);
+#pragma unroll
+        for (int j = 0; j < V; ++j) acc[j] += to_f32(e[j]);
+      }
+    if (residual) {
+      const uint4 rv = *(reinterpret_cast<const uint4*>(residual) + i);
+      const T* e = reinterpret_cast<const T*>(&rv);
+#pragma unroll
+      for (int j = 0; j < V; ++j) acc[j] += to_f32(e[j]);
+    }
+    uint4 ov;
+    T* o = reinterpret_cast<T*>(&ov);
+#pragma unroll
+    for (int j = 0; j < V; ++j) o[j] = from_f32<T>(acc[j]);
+    *(reinterpret_cast<uint4*>(out) + i) = ov;
+  }
+}
+
 }  // namespace kvb
 
 using namespace kvb;
@@ -236,6 +316,46 @@ extern "C" int kvb_allreduce_mean(void* const* bases, void* const* flags, int ra
       if ((start % 8) || (count % 8)) return KVB_ERR_ALIGN;
       allreduce_mean_kernel<__half><<<n_ctas, COMM_THREADS, 0, s>>>(peers, rank, world, start, count, scale, epoch0,
                                                                    (uint32_t*)local_sync, status, limit);
+      break;
+    default:
+      return KVB_ERR_ARG;
+  }
+  return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
+}
+
+// slots/flags: arrays of `world` device pointers (this site's slot and flag block of every rank, mapped into this
+// process). count elements, a multiple of 16/sizeof(T); slots, residual and out 16-byte aligned. dtype as above.
+extern "C" int kvb_oneshot_allreduce(void* const* slots, void* const* flags, int rank, int world, long long count,
+                                     const void* residual, void* out, unsigned epoch_base, const void* epoch_word, int dtype,
+                                     int* status, double timeout_s, void* stream) {
+  if (world < 1 || world > COMM_MAX_RANKS || rank < 0 || rank >= world || count <= 0) return KVB_ERR_ARG;
+  const long long esz = dtype == 0 ? 4 : 2;
+  if ((count * esz) % 16) return KVB_ERR_ALIGN;
+  OneShotPeers peers;
+  for (int r = 0; r < world; ++r) {
+    if (((uintptr_t)slots[r]) % 16) return KVB_ERR_ALIGN;
+    peers.slot[r] = slots[r];
+    peers.flags[r] = reinterpret_cast<uint32_t*>(flags[r]);
+  }
+  if (((uintptr_t)out) % 16 || ((uintptr_t)residual) % 16) return KVB_ERR_ALIGN;
+  const long long nvec = count * esz / 16;
+  long long ctas = (nvec + ONESHOT_THREADS - 1) / ONESHOT_THREADS;
+  if (ctas > ONESHOT_MAX_CTAS) ctas = ONESHOT_MAX_CTAS;
+  const long long limit = (long long)(timeout_s * 1.9e9);
+  cudaStream_t s = (cudaStream_t)stream;
+  const uint32_t* ew = reinterpret_cast<const uint32_t*>(epoch_word);
+  switch (dtype) {
+    case 0:
+      oneshot_allreduce_kernel<float><<<(int)ctas, ONESHOT_THREADS, 0, s>>>(peers, rank, world, nvec, (const float*)residual, (float*)out,
+                                                                           epoch_base, ew, status, limit);
+      break;
+    case 1:
+      oneshot_allreduce_kernel<__nv_bfloat16><<<(int)ctas, ONESHOT_THREADS, 0, s>>>(
+          peers, rank, world, nvec, (const __nv_bfloat16*)residual, (__nv_bfloat16*)out, epoch_base, ew, status, limit);
+      break;
+    case 2:
+      oneshot_allreduce_kernel<__half><<<(int)ctas, ONESHOT_THREADS, 0, s>>>(peers, rank, world, nvec, (const __half*)residual, (__half*)out,
+                                                                           epoch_base, ew, status, limit);
       break;
     default:
       return KVB_ERR_ARG;

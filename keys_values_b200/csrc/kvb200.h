@@ -118,6 +118,13 @@ int kvb_ipc_close_handle(void* ptr);
 int kvb_allreduce_mean(void* const* bases, void* const* flags, int rank, int world, long long start, long long count,
                        float scale, unsigned epoch0, void* local_sync, int dtype, int n_ctas, int* status, double timeout_s,
                        void* stream);
+// Sum over ranks of `count` elements that every rank holds in its slot of symmetric memory (small payloads; one
+// NVLink round trip), plus an optional local residual, written to the local `out`. Epoch = epoch_base + *epoch_word.
+int kvb_oneshot_allreduce(void* const* slots, void* const* flags, int rank, int world, long long count, const void* residual,
+                          void* out, unsigned epoch_base, const void* epoch_word, int dtype, int* status, double timeout_s,
+                          void* stream);
+#define KVB_ONESHOT_MAX_CTAS 16
+#define KVB_COMM_MAX_RANKS 16
 
 
 // ---- gemm_sm100.cu: GEMM fused with a collective over peer memory (tensor parallelism)

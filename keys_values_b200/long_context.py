@@ -235,6 +235,9 @@ class LongContextInferenceModel(GPTAndHeadModel):
         return loss
 
     def _forward_internal(self, input_ids, targets, scale_factor: float = 1.0):
+        def _dense(t):  # blocks of a tensor-parallel shard may hand on token rows sharded over the ranks
+            return t.full() if hasattr(t, "full") else t
+
         gpt, head = self.gpt_model, self.head_model
         n_layer = gpt.config.n_layer
         seq_length = input_ids.shape[1]
@@ -246,6 +249,7 @@ class LongContextInferenceModel(GPTAndHeadModel):
             x = gpt.embed(ids)
             for layer_idx, block in enumerate(gpt.transformer.h):
                 if self.layer_input_hook is not None:
+                    x = _dense(x)
                     self.layer_input_hook(x, layer_idx, cell.start, cell.end)
                 ws = self.weight_streamer
                 if ws is not None:  # host-resident blocks: this one on the device, the next one on its way
@@ -257,8 +261,10 @@ class LongContextInferenceModel(GPTAndHeadModel):
                 if self.cell_boundary_hook is not None:
                     self.cell_boundary_hook(layer_idx, cell_idx, cell.end)
             if self.layer_input_hook is not None:
+                x = _dense(x)
                 self.layer_input_hook(x, n_layer, cell.start, cell.end)
             if targets is not None:
+                x = _dense(x)
                 pos = cell.start
                 for c in cell.chunk_sizes:
                     t_chunk = get_chunk_of_targets(targets, pos, pos + c, seq_length)

@@ -162,9 +162,15 @@ class CausalSelfAttention(nn.Module):
         mha: MultiHeadSelfAttention,
         chunk_sizes: Optional[Sequence[int]] = None,
     ) -> torch.Tensor:
-        B, T, _ = x.shape
+        return self.proj(self.attend(self._qkv_apply(x), token_idx, mha, chunk_sizes))
+
+    def attend(self, qkv: torch.Tensor, token_idx: torch.Tensor, mha: MultiHeadSelfAttention,
+               chunk_sizes: Optional[Sequence[int]] = None) -> torch.Tensor:
+        """Everything between the QKV projection and the output projection: split, QK norm, RoPE, cache update
+        and attention. ``qkv (B, T, (H + 2G)·D)`` → ``(B, T, H·D)``."""
+        B, T, _ = qkv.shape
         input_pos = 0 if self.kv_cache is None else self.kv_cache.input_pos
-        q, k, v = self._split_norm_rope(self._qkv_apply(x), mha, input_pos)
+        q, k, v = self._split_norm_rope(qkv, mha, input_pos)
         if self.kv_cache is None:
             y, _ = mha(query=q, k_and_v=DefaultKeysAndValues(k, v), block_idx=self.block_idx)
         else:
@@ -180,7 +186,7 @@ class CausalSelfAttention(nn.Module):
                 tis = torch.split(token_idx, sizes, dim=1)
                 parts = [self.kv_cache(query=qc, key=kc, value=vc, token_idx=ti) for qc, kc, vc, ti in zip(qs, ks, vs, tis)]
                 y = torch.cat(parts, dim=1)
-        return self.proj(y)
+        return y
 
     def create_default_kv_cache(self, batch_size: int, dtype=None, max_sequence_length: Optional[int] = None, device=None):
         from keys_values_b200.kvcache.basics import DenseKVCache

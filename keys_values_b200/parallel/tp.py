@@ -268,3 +268,442 @@ class TPModel:
             a = ops.swiglu(h[:, : w.inter_local].contiguous(), h[:, w.inter_local :].contiguous())
             x_shard = ctx.gemm_reduce_scatter(a, w.mlp_proj, residual=x_shard)
         return x_shard
+
+
+# =====================================================================================================
+# Tensor-parallel model that runs through the ordinary single-GPU stack
+# =====================================================================================================
+#
+# ``TPGPT`` is a :class:`GPT` whose blocks hold this rank's shard of the attention heads and of the MLP
+# columns; the two row-parallel projections of a block end in an all-reduce. Activations between blocks are
+# replicated, so everything that works with a ``GPT`` (caches and their eviction policies, chunked
+# inference, generation, the captured decode step, evaluation) works with a ``TPGPT`` unchanged, for any
+# batch size and any number of rows. The all-reduce is this package's own: a one-shot peer-memory kernel
+# for the few rows of a decode step (one NVLink round trip, graph-capturable), the two-shot in-place kernel
+# of :class:`SymmetricArena` for the chunks of a prefill.
+
+
+class TPComm:
+    """All-reduce (sum) of the outputs of row-parallel linears over the ranks of ``group``.
+
+    The producer GEMM writes straight into symmetric memory (:meth:`out_buffer`), :meth:`all_reduce`
+    returns the sum (plus an optional residual). Small payloads (up to ``small_bytes``) are reduced by
+    ``kvb_oneshot_allreduce``; they rotate over slots ("sites") so that a slot is never rewritten while a
+    peer may still read it. Eager calls use the sites ``[0, EAGER_SITES)`` with epochs counted on the host;
+    calls recorded into a CUDA graph use the sites above them with epochs ``k + 1 + *epoch_word`` (``k``: index
+    of the call in the captured step; the graph adds the number of captured calls to the device word at its
+    end, so every replay has fresh epochs). Larger payloads use two alternating arenas, grown on demand,
+    and the two-shot kernel. On CPU ranks (gloo) the library all-reduce stands in, so that the host logic is
+    testable without GPUs."""
+
+    EAGER_SITES = 64
+    GRAPH_SITES = 128
+
+    def __init__(self, world: int, rank: int, device, group=None, small_bytes: int = 256 << 10, timeout_s: float = 20.0,
+                 dtype: torch.dtype = torch.bfloat16):
+        self.world, self.rank, self.group = world, rank, group
+        self.device = torch.device(device)
+        self.native = self.device.type == "cuda" and world > 1
+        self.small_bytes, self.timeout_s, self.dtype = small_bytes, timeout_s, dtype
+        self.eager_calls = 0           # one-shot calls issued eagerly so far
+        self.captured_calls = 0        # one-shot calls recorded in the graph that is being (or was last) captured
+        self._capturing = False
+        self._large: List[Optional["SymmetricArena"]] = [None, None]
+        self._large_numel = 0
+        self._large_calls = 0
+        self._pending: Optional[tuple] = None
+        if self.native:
+            n_sites = self.EAGER_SITES + self.GRAPH_SITES
+            self._flag_bytes = 16 * 16 * 4  # [writer rank][CTA] words per site
+            self.slots = _SymmBuffer(n_sites * small_bytes, self.device, world, rank, group)
+            self.flags = _SymmBuffer(n_sites * self._flag_bytes, self.device, world, rank, group)
+            self.epoch_word = torch.zeros(1, dtype=torch.int32, device=self.device)
+            dist.barrier(group=group)
+
+    # ----------------------------------------------------------------------- buffers
+    def _next_site(self) -> int:
+        if self._capturing:
+            return self.EAGER_SITES + self.captured_calls % self.GRAPH_SITES
+        return self.eager_calls % self.EAGER_SITES
+
+    def out_buffer(self, rows: int, features: int, dtype: torch.dtype) -> torch.Tensor:
+        """``(rows, features)`` tensor for the partial result of this rank; hand it to :meth:`all_reduce` next."""
+        if not self.native:
+            return torch.empty((rows, features), dtype=dtype, device=self.device)
+        if dtype != self.dtype:
+            raise ValueError(f"this communicator reduces {self.dtype}, got {dtype}")
+        esz = torch.empty((), dtype=dtype).element_size()
+        nbytes = rows * features * esz
+        if nbytes <= self.small_bytes and nbytes % 16 == 0:
+            site = self._next_site()
+            buf = self.slots.bytes[site * self.small_bytes : site * self.small_bytes + nbytes].view(dtype).view(rows, features)
+            self._pending = ("small", site, buf)
+            return buf
+        if self._capturing:
+            raise RuntimeError(f"a payload of {nbytes} bytes cannot be reduced inside a captured step (limit {self.small_bytes})")
+        numel = rows * features
+        if numel > self._large_numel:
+            self._grow_large(numel)
+        par = self._large_calls & 1
+        buf = self._large[par].tensor[:numel].view(rows, features)
+        self._pending = ("large", par, buf)
+        return buf
+
+    def _grow_large(self, numel: int) -> None:
+        from keys_values_b200.parallel.symm import SymmetricArena
+
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)  # nobody still reads an arena that is about to go
+        for a in self._large:
+            if a is not None:
+                a.close()
+        numel = (numel + 4095) // 4096 * 4096
+        self._large = [SymmetricArena(numel, self.dtype, self.device, self.world, self.rank, self.group, self.timeout_s) for _ in range(2)]
+        self._large_numel = numel
+
+    # --------------------------------------------------------------------- all-reduce
+    def all_reduce(self, buf: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Sum of ``buf (rows, features)`` over the ranks (+ ``residual``). The result may live in
+        symmetric memory that the call after the next one reuses: consume it before."""
+        if self.world == 1:
+            return buf if residual is None else buf + residual
+        if not self.native:
+            dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=self.group)
+            return buf if residual is None else buf + residual
+        kind, idx, mine = self._pending or (None, None, None)
+        if mine is None or mine.data_ptr() != buf.data_ptr():
+            # a tensor that was not produced into symmetric memory: copy it in
+            mine = self.out_buffer(buf.shape[0], buf.shape[1], buf.dtype)
+            mine.copy_(buf)
+            kind, idx, _ = self._pending
+        self._pending = None
+        if kind == "large":
+            arena = self._large[idx]
+            self._large_calls += 1
+            arena.all_reduce_mean_(0, buf.numel(), scale=1.0)
+            return mine if residual is None else mine + residual
+        site = idx
+        out = torch.empty_like(mine)
+        st = _cu.status_word(self.device)
+        if residual is not None:
+            residual = residual.contiguous()
+        if self._capturing:
+            base, word = self.captured_calls + 1, self.epoch_word
+        else:
+            base, word = self.eager_calls + 1, None
+        _cu._check(
+            _cu.lib().kvb_oneshot_allreduce(
+                self.slots.ptr_array(site * self.small_bytes), self.flags.ptr_array(site * self._flag_bytes), self.rank, self.world,
+                ctypes.c_longlong(mine.numel()), _cu._p(residual), _cu._p(out), ctypes.c_uint(base & 0xFFFFFFFF),
+                _cu._p(word), _cu._code(mine.dtype), _cu._p(st), ctypes.c_double(self.timeout_s), _cu._stream(mine),
+            ),
+            "oneshot_allreduce",
+        )
+        _cu._count()
+        if self._capturing:
+            self.captured_calls += 1
+        else:
+            self.eager_calls += 1
+        return out
+
+    # ------------------------------------------------------------------ graph capture
+    def begin_capture(self) -> None:
+        self._capturing, self.captured_calls = True, 0
+
+    def end_capture(self) -> None:
+        """Last operation inside the capture: every replay moves the epochs of the captured calls on."""
+        self._capturing = False
+        if self.native and self.captured_calls:
+            if self.captured_calls % self.GRAPH_SITES == 1:
+                raise RuntimeError("the last captured all-reduce would share its slot with the first one of the next replay")
+            self.epoch_word.add_(self.captured_calls)
+
+    def close(self) -> None:
+        if self.native:
+            for a in self._large:
+                if a is not None:
+                    a.close()
+            self._large = [None, None]
+            self.slots.close()
+            self.flags.close()
+
+
+class RowParallelLinear(torch.nn.Linear):
+    """``all_reduce(x_shard @ W_shard^T) (+ bias)``: the weight holds this rank's columns; the bias is kept by
+    rank 0 only (the sum over ranks adds it once)."""
+
+    comm: Optional[TPComm] = None
+
+    @classmethod
+    def from_linear(cls, linear: torch.nn.Linear, comm: TPComm) -> "RowParallelLinear":
+        new = cls.__new__(cls)
+        torch.nn.Module.__init__(new)
+        new.in_features, new.out_features = linear.in_features, linear.out_features
+        new.weight = linear.weight
+        new.bias = linear.bias
+        new.comm = comm
+        return new
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        comm = self.comm
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, x.shape[-1])
+        if torch.is_grad_enabled() and (x.requires_grad or self.weight.requires_grad):
+            y = _AllReduceSum.apply(torch.nn.functional.linear(x2, self.weight, self.bias), comm)
+            return y.view(*lead, self.out_features)
+        buf = comm.out_buffer(x2.shape[0], self.out_features, x.dtype)
+        if self.bias is not None:
+            torch.addmm(self.bias, x2, self.weight.t(), out=buf)
+        else:
+            torch.mm(x2, self.weight.t(), out=buf)
+        return comm.all_reduce(buf).view(*lead, self.out_features)
+
+
+class _AllReduceSum(torch.autograd.Function):
+    """Sum over ranks in the forward pass; the gradient of a sum reaches every rank unchanged."""
+
+    @staticmethod
+    def forward(ctx, x, comm):
+        return comm.all_reduce(x.contiguous().clone())
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+class _CopyToShards(torch.autograd.Function):
+    """Identity in the forward pass (the replicated input of column-parallel linears); the gradients of the
+    ranks' shards are summed in the backward pass."""
+
+    @staticmethod
+    def forward(ctx, x, comm):
+        ctx.comm = comm
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        return ctx.comm.all_reduce(g.contiguous().clone().view(-1, g.shape[-1])).view_as(g), None
+
+
+def local_config(config, world: int):
+    """The configuration of one rank's shard: heads, KV heads and MLP width divided by ``world``."""
+    import dataclasses
+
+    H, G, I = config.n_head, config.n_query_groups, config.intermediate_size
+    if G % world or I % world:
+        raise ValueError(f"n_query_groups = {G} and intermediate_size = {I} must be divisible by the tensor-parallel size {world}")
+    if config.norm_qk and config.norm_qk_type == "olmo2":
+        raise NotImplementedError("a QK norm over all heads at once cannot be sharded over heads")
+    if config.mlp_class_name == "LLaMAMoE":
+        raise NotImplementedError("mixture-of-experts blocks are not sharded")
+    return dataclasses.replace(config, n_head=H // world, n_query_groups=G // world, intermediate_size=I // world, head_size=config.head_size)
+
+
+def shard_state_dict(state_dict, config, world: int, rank: int):
+    """State dict of the whole model → state dict of the shard of ``rank`` (see :func:`local_config`)."""
+    H, G, D, I = config.n_head, config.n_query_groups, config.head_size, config.intermediate_size
+    gs = H // G
+    g0, g1 = rank * (G // world), (rank + 1) * (G // world)
+    i0, i1 = rank * (I // world), (rank + 1) * (I // world)
+    out = {}
+    for key, t in state_dict.items():
+        if ".attn.qkv." in key:
+            out[key] = torch.cat((t[g0 * gs * D : g1 * gs * D], t[H * D + g0 * D : H * D + g1 * D],
+                                  t[(H + G) * D + g0 * D : (H + G) * D + g1 * D])).contiguous()
+        elif key.endswith(".attn.proj.weight"):
+            out[key] = t[:, g0 * gs * D : g1 * gs * D].contiguous()
+        elif ".mlp.fc" in key:
+            out[key] = t[i0:i1].contiguous()
+        elif key.endswith(".mlp.proj.weight"):
+            out[key] = t[:, i0:i1].contiguous()
+        elif key.endswith(".attn.proj.bias") or key.endswith(".mlp.proj.bias"):
+            out[key] = t if rank == 0 else torch.zeros_like(t)
+        else:
+            out[key] = t
+    return out
+
+
+class RowShard:
+    """Token rows of an activation ``(B, T, E)`` sharded over the ranks (flattened batch-major; rank ``r`` holds
+    rows ``[r·n, (r+1)·n)``). Blocks of a :class:`TPGPT` pass it from one to the next on the fused path; whoever
+    needs the whole tensor calls :meth:`full` (one all-gather, cached) or indexes it."""
+
+    def __init__(self, rows: torch.Tensor, shape, comm: "TPComm"):
+        self.rows, self.shape, self.comm = rows, tuple(shape), comm
+        self._full: Optional[torch.Tensor] = None
+
+    def full(self) -> torch.Tensor:
+        if self._full is None:
+            out = torch.empty((self.rows.shape[0] * self.comm.world, self.rows.shape[1]), dtype=self.rows.dtype, device=self.rows.device)
+            dist.all_gather_into_tensor(out, self.rows.contiguous(), group=self.comm.group)
+            self._full = out.view(self.shape)
+        return self._full
+
+    def __getitem__(self, idx):
+        return self.full()[idx]
+
+    @property
+    def dtype(self):
+        return self.rows.dtype
+
+    @property
+    def device(self):
+        return self.rows.device
+
+
+def dense(x):
+    """The whole tensor behind ``x`` (a tensor, or a :class:`RowShard`)."""
+    return x.full() if isinstance(x, RowShard) else x
+
+
+def _tpgpt_class():
+    from keys_values_b200 import ops
+    from keys_values_b200.models.model import GPT, Block, LLaMAMLP, RMSNorm
+
+    class TPBlock(Block):
+        """A block of the shard. Inference chunks whose rows divide by ``128 · world`` take the fused path:
+        all-gather→QKV GEMM, attention over this rank's heads, projection GEMM→reduce-scatter (+ residual),
+        all-gather→MLP-up GEMM, SwiGLU, MLP-down GEMM→reduce-scatter (+ residual), with the activations
+        between blocks sharded over token rows. Everything else (decode steps, ragged chunks, training) runs
+        the ordinary block with the all-reduce inside the row-parallel projections."""
+
+        owner = None  # the TPGPT, set after construction (not a sub-module: no reference cycle in the module tree)
+
+        def _fusable(self, rows: int) -> bool:
+            gpt = self.owner()
+            c = self.config
+            return (
+                gpt is not None and gpt.fused_prefill and gpt.tp_comm.native and not torch.is_grad_enabled()
+                and rows % (128 * gpt.tp_comm.world) == 0 and rows // gpt.tp_comm.world >= 128
+                and type(self.mlp) is LLaMAMLP and isinstance(self.norm_1, RMSNorm) and isinstance(self.norm_2, RMSNorm)
+                and not c.parallel_residual and not c.post_attention_norm and not c.post_mlp_norm and not c.bias and not c.attn_bias
+                and self.attn.kv_cache is not None and type(self.attn.qkv) is torch.nn.Linear
+                and self.attn.qkv.weight.dtype == torch.bfloat16
+            )
+
+        def forward(self, x, token_idx, mha, chunk_sizes=None):
+            B, T = token_idx.shape
+            if not self._fusable(B * T):
+                return super().forward(dense(x), token_idx, mha, chunk_sizes=chunk_sizes)
+            gpt = self.owner()
+            comm, c = gpt.tp_comm, self.config
+            world, rank = comm.world, comm.rank
+            E = c.n_embd
+            rows = B * T // world
+            ctx = gpt.fused_context(B * T)
+            if isinstance(x, RowShard):
+                xs = x.rows
+            else:
+                xs = x.reshape(B * T, E)[rank * rows : (rank + 1) * rows]
+            ctx.stage_view(rows, E).copy_(self.norm_1(xs))
+            qkv = ctx.allgather_gemm(rows, self.attn.qkv.weight).view(B, T, -1)
+            y = self.attn.attend(qkv, token_idx, mha, chunk_sizes)
+            xs = ctx.gemm_reduce_scatter(y.reshape(B * T, -1), self.attn.proj.weight, residual=xs)
+            ctx.stage_view(rows, E).copy_(self.norm_2(xs))
+            h = ctx.allgather_gemm(rows, gpt.fc_weight(self))
+            inter = c.intermediate_size
+            a = ops.swiglu(h[:, :inter], h[:, inter:])
+            xs = ctx.gemm_reduce_scatter(a, self.mlp.proj.weight, residual=xs)
+            return RowShard(xs, (B, T, E), comm)
+
+    class TPGPT(GPT):
+        """This rank's shard of a model (``full_config`` describes the whole). Built empty; fill it with
+        ``load_state_dict(shard_state_dict(full_state_dict, full_config, world, rank))`` or initialise it
+        at random. ``tp_comm`` is read by the captured decode step. ``fused_prefill=False`` keeps every chunk
+        on the all-reduce path."""
+
+        def __init__(self, full_config, comm: TPComm, fused_prefill: bool = True, **mha_kwargs):
+            super().__init__(local_config(full_config, comm.world), **mha_kwargs)
+            import weakref
+
+            self.full_config = full_config
+            self.tp_comm = comm
+            self.fused_prefill = fused_prefill
+            self._fused_ctx: Optional[TPContext] = None
+            self._fc_cat = {}
+            for block in self.transformer.h:
+                block.owner = weakref.ref(self)
+                block.attn.proj = RowParallelLinear.from_linear(block.attn.proj, comm)
+                block.mlp.proj = RowParallelLinear.from_linear(block.mlp.proj, comm)
+                # the inputs of the column-parallel linears (after the norms; the residual path is replicated)
+                block.attn.register_forward_pre_hook(self._shard_input_hook)
+                block.mlp.register_forward_pre_hook(self._shard_input_hook)
+                # per-head QK norms: one weight serves all heads, every rank sees the gradient of its heads only
+                for norm in (block.attn.norm_q, block.attn.norm_k):
+                    if norm is not None:
+                        for p in norm.parameters():
+                            p.register_hook(self._sum_over_ranks)
+
+        def _make_block(self, config, block_idx):
+            return TPBlock(config, block_idx)
+
+        def _sum_over_ranks(self, g):
+            return self.tp_comm.all_reduce(g.reshape(1, -1).clone()).view_as(g)
+
+        def _shard_input_hook(self, module, args):
+            # training: the gradient of the input of column-parallel linears is the sum over the ranks' shards
+            x = args[0]
+            if torch.is_grad_enabled() and x.requires_grad:
+                return (_CopyToShards.apply(x, self.tp_comm),) + tuple(args[1:])
+            return None
+
+        # ------------------------------------------------------------------ fused path
+        def fused_context(self, total_rows: int) -> TPContext:
+            ctx = self._fused_ctx
+            if ctx is None or total_rows > ctx.max_rows:
+                if ctx is not None:
+                    torch.cuda.synchronize(self.tp_comm.device)
+                    dist.barrier(group=self.tp_comm.group)
+                    ctx.close()
+                comm = self.tp_comm
+                ctx = TPContext(comm.world, comm.rank, comm.device, total_rows, self.config.n_embd, comm.group, comm.timeout_s)
+                self._fused_ctx = ctx
+            return ctx
+
+        def fc_weight(self, block) -> torch.Tensor:
+            """``fc_1 | fc_2`` of a block as one matrix (one all-gather→GEMM for both); the two parameters become
+            views of it the first time it is asked for, so the weights are not held twice."""
+            key = id(block)
+            w = self._fc_cat.get(key)
+            f1, f2 = block.mlp.fc_1.weight, block.mlp.fc_2.weight
+            if w is None or f1.data_ptr() != w.data_ptr():
+                w = torch.cat((f1.data, f2.data)).contiguous()
+                n = f1.shape[0]
+                f1.data, f2.data = w[:n], w[n:]
+                self._fc_cat[key] = w
+            return w
+
+        def forward(self, idx, skip_lm_head: bool = False, chunk_sizes=None):
+            if idx.ndim == 1:
+                idx = idx.unsqueeze(0)
+            T = idx.size(1)
+            caches = self.get_kv_caches()
+            input_pos = caches[0].input_pos if caches[0] is not None else 0
+            if input_pos + T > self.max_seq_length:
+                raise ValueError(f"Cannot forward sequence: input_pos {input_pos} + {T} > max_seq_length {self.max_seq_length}")
+            x = self.embed(idx)
+            hook = self._start_of_layer_hook
+            for block_idx, block in enumerate(self.transformer.h):
+                if hook is not None:
+                    x = dense(x)
+                    hook(x, block_idx)
+                x = block(x, idx, self.mha, chunk_sizes=chunk_sizes)
+            x = dense(x)
+            if hook is not None:
+                hook(x, self.config.n_layer)
+            return x if skip_lm_head else self.head(x)
+
+        def close(self) -> None:
+            if self._fused_ctx is not None:
+                self._fused_ctx.close()
+                self._fused_ctx = None
+
+    return TPGPT, TPBlock
+
+
+def __getattr__(name):
+    if name in ("TPGPT", "TPBlock"):
+        gpt_cls, block_cls = _tpgpt_class()
+        globals()["TPGPT"], globals()["TPBlock"] = gpt_cls, block_cls
+        return globals()[name]
+    raise AttributeError(name)

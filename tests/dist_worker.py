@@ -202,5 +202,100 @@ def case_tp_model(rank, world, dev):
     ctx.close()
 
 
+def case_tp_gpt(rank, world, dev):
+    """The sharded model through the ordinary stack (prefill, chunks, single-token decode steps, batch 2, H2O
+    caches that evict) equals the whole model; on GPUs the decode steps also run as a captured graph."""
+    from keys_values_b200.config import Config
+    from keys_values_b200.generate.decode_graph import Decoder
+    from keys_values_b200.kvcache.factory import KVCacheFactory
+    from keys_values_b200.models.model import GPT
+    from keys_values_b200.ops import cuda as cu
+    from keys_values_b200.parallel.tp import TPComm, TPGPT, shard_state_dict
+
+    cuda = dev.type == "cuda"
+    dtype = torch.bfloat16 if cuda else torch.float32
+    torch.manual_seed(5)
+    cfg = Config.from_name("tiny-qwen3")
+    full = GPT(cfg)
+    full.apply(full._init_weights)
+    full = full.to(device=dev, dtype=dtype).eval()
+    comm = TPComm(world, rank, dev, dtype=dtype)
+    shard = TPGPT(cfg, comm).to(device=dev, dtype=dtype).eval()
+    shard.load_state_dict(shard_state_dict(full.state_dict(), cfg, world, rank))
+    B, T0, Tc, C, n_dec = 2, 192, 64, 256, 6
+    ids = torch.randint(0, cfg.vocab_size, (B, T0 + 3 * Tc + n_dec), device=dev)
+    dist.broadcast(ids, 0)
+    name = "h2o-default"
+    outs = []
+    for model in (full, shard):
+        model.assign_kv_caches(KVCacheFactory.create(model, name, B, C, dtype=dtype, device=dev, cache_kwargs=dict(max_chunk_size=Tc)))
+        model.max_seq_length = ids.shape[1]
+        model.reset()
+        res = []
+        with torch.no_grad():
+            res.append(model(ids[:, :T0])[:, -1])
+            pos = T0
+            for _ in range(3):
+                res.append(model(ids[:, pos : pos + Tc])[:, -1])
+                pos += Tc
+            decoder = Decoder(model, B, use_graph=cuda, warmup=2)
+            for _ in range(n_dec):
+                res.append(decoder(ids[:, pos : pos + 1])[:, -1].clone())
+                pos += 1
+            if cuda:
+                assert decoder.graph is not None, decoder.reason
+        outs.append(torch.stack(res).float())
+    if cuda:
+        torch.cuda.synchronize(dev)
+        cu.check_status(dev)
+    want, got = outs
+    err = (got - want).norm() / want.norm()
+    assert err < (3e-2 if cuda else 1e-4), f"relative error of the logits {err}"
+    # every rank holds the same bits (the sum runs in rank order everywhere)
+    gathered = [torch.empty_like(got) for _ in range(world)]
+    dist.all_gather(gathered, got)
+    if cuda:
+        assert all(torch.equal(g, got) for g in gathered)
+    comm.close()
+
+
+def case_tp_gpt_grads(rank, world, dev):
+    """Training through the sharded model: the gradients of a rank's shard are the matching slices of the
+    whole model's gradients, those of replicated parameters (norms, embedding, head) are equal on every rank."""
+    from keys_values_b200.config import Config
+    from keys_values_b200.models.model import GPT
+    from keys_values_b200.parallel.tp import TPComm, TPGPT, shard_state_dict
+
+    cuda = dev.type == "cuda"
+    dtype = torch.bfloat16 if cuda else torch.float32
+    torch.manual_seed(6)
+    cfg = Config.from_name("tiny-qwen3")
+    full = GPT(cfg)
+    full.apply(full._init_weights)
+    full = full.to(device=dev, dtype=dtype)
+    comm = TPComm(world, rank, dev, dtype=dtype)
+    shard = TPGPT(cfg, comm).to(device=dev, dtype=dtype)
+    shard.load_state_dict(shard_state_dict(full.state_dict(), cfg, world, rank))
+    ids = torch.randint(0, cfg.vocab_size, (2, 96), device=dev)
+    tg = torch.randint(0, cfg.vocab_size, (2 * 96,), device=dev)
+    dist.broadcast(ids, 0)
+    dist.broadcast(tg, 0)
+    losses = []
+    for model in (full, shard):
+        logits = model(ids)
+        loss = torch.nn.functional.cross_entropy(logits.view(-1, logits.shape[-1]).float(), tg)
+        loss.backward()
+        losses.append(loss.detach().float())
+    assert abs(losses[0] - losses[1]) < (2e-2 if cuda else 1e-5), losses
+    want = shard_state_dict({n: p.grad for n, p in full.named_parameters()}, cfg, world, rank)
+    tol = 6e-2 if cuda else 1e-4
+    for n, p in shard.named_parameters():
+        assert p.grad is not None, n
+        w, g = want[n].float(), p.grad.float()
+        err = (g - w).norm() / w.norm().clamp(min=1e-6)
+        assert err < tol, f"{n}: relative gradient error {err}"
+    comm.close()
+
+
 if __name__ == "__main__":
     main()

@@ -103,7 +103,7 @@ def test_gradients_through_eviction_match_oracle_on_gpu(cache_name):
     gm.train()
     loss = gm(ids, tg)
     logs, cells = list(gm._replay_logs), list(gm.cells)
-    assert len(cells) > 2 and any(s is not None for s in logs[0].slot_positions)
+    assert len(cells) >= 2 and any(s is not None for s in logs[0].slot_positions)
     loss.backward()
     g1 = _grads(m)
     o_loss, o16 = oracle_loss_and_gradients(m, head, ids, tg, logs, cells)

@@ -45,6 +45,27 @@ def test_dp_full_finetune_gradients_match_on_cpu_ranks():
     _run("dp_train_full", 2)
 
 
+def test_tp_sharded_model_matches_whole_model_on_cpu_ranks():
+    """Sharding of heads and MLP columns, row-parallel all-reduce, per-head eviction: two gloo ranks."""
+    _run("tp_gpt", 2)
+
+
+def test_tp_sharded_model_gradients_on_cpu_ranks():
+    _run("tp_gpt_grads", 2)
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tp_sharded_model_with_captured_decode_steps_on_gpus():
+    _run("tp_gpt", 2)
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tp_sharded_model_gradients_on_gpus():
+    _run("tp_gpt_grads", 2)
+
+
 @pytest.mark.gpu
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_fused_allreduce_matches_nccl():
