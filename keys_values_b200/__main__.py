@@ -105,7 +105,7 @@ def build_kwargs(fn: Callable, argv: List[str]) -> Dict[str, Any]:
     hints = _resolved_hints(fn)
     values: Dict[str, Any] = {}
     nested: Dict[str, Dict[str, str]] = {}
-    positionals = [n for n, p in sig.parameters.items() if p.default is inspect.Parameter.empty and p.kind != p.VAR_KEYWORD]
+    positionals = [n for n, p in sig.parameters.items() if p.kind in (p.POSITIONAL_ONLY, p.POSITIONAL_OR_KEYWORD)]
     i, pos_i = 0, 0
     file_cfg: Dict[str, Any] = {}
     while i < len(argv):

@@ -81,6 +81,11 @@ class SimilarSequenceLengthSampler(torch.utils.data.Sampler):
         self.iterator = SimilarSequenceLengthIterator(*args, **kwargs)
 
     def __iter__(self):
+        if not self.iterator.shuffle:
+            # an evaluation pass that stopped early (a limit on the number of batches) must not make the next pass
+            # start in the middle: batch k of every pass is the same batch. Training samplers (shuffled) keep their
+            # position, which is what resuming in the middle of an epoch needs.
+            self.iterator.pos = 0
         return iter(self.iterator)
 
     def __len__(self) -> int:

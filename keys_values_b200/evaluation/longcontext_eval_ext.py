@@ -88,7 +88,7 @@ def setup_from_file(setups_filename: Union[str, Path], data=None, devices: int =
                     sample_metric_max_generated_tokens: int = 64, sample_metric_temperature: float = 0.0,
                     sample_metric_top_k: Optional[int] = None, sample_metric_top_p: float = 1.0,
                     num_store_generated_samples: Optional[int] = None, skip_eval: bool = False, max_iters: Optional[int] = None,
-                    attention_forward_temp_size_gb: Optional[float] = None) -> None:
+                    attention_forward_temp_size_gb: Optional[float] = None, tp: int = 1) -> None:
     """Evaluate every checkpoint of every setup listed in ``setups_filename`` (see :func:`load_setups`)
     (``keys_values/evaluation/longcontext_eval_ext.py:120-262``).
 
@@ -119,7 +119,7 @@ def setup_from_file(setups_filename: Union[str, Path], data=None, devices: int =
         kv_cache = KVCacheArgs(**kv_fields)
         eval_args = EvalArgs(max_new_tokens=sample_metric_max_generated_tokens, max_iters=max_iters, sample_metric=use_sample_metric)
         sample_args = dict(temperature=sample_metric_temperature, top_k=sample_metric_top_k, top_p=sample_metric_top_p)
-        launch(main, devices, out_dir=out_dir, checkpoints=names, data=data, kv_cache=kv_cache, eval=eval_args, precision=precision,
+        launch(main, devices if tp == 1 else tp, tp=tp, out_dir=out_dir, checkpoints=names, data=data, kv_cache=kv_cache, eval=eval_args, precision=precision,
                eval_dir=eval_dir, setups=rec.get("setups") or [kv_cache.name], batch_size=batch_size, hp=hp, model_name=hp.get("model_name"),
                seed=seed, sample_args=sample_args, num_store_generated_samples=num_store_generated_samples, skip_eval=skip_eval)
 
@@ -149,7 +149,7 @@ def setup(out_dir: Union[str, Path], checkpoints: Optional[List[str]] = None, da
           batch_size: int = 1, model_name: Optional[str] = None, seed: int = 1337, use_sample_metric: Optional[str] = None,
           sample_metric_max_generated_tokens: int = 64, sample_metric_temperature: float = 0.0, sample_metric_top_k: Optional[int] = None,
           sample_metric_top_p: float = 1.0, num_store_generated_samples: Optional[int] = None, skip_eval: bool = False,
-          attention_forward_temp_size_gb: Optional[float] = None) -> None:
+          attention_forward_temp_size_gb: Optional[float] = None, tp: int = 1) -> None:
     """``out_dir``: output directory of a fine-tuning run, or a setups file (see :func:`setup_from_file`);
     ``checkpoints``: names of its sub-directories to evaluate (default ``final``). The KV-cache setup defaults to
     the one the run was trained with."""
@@ -162,13 +162,13 @@ def setup(out_dir: Union[str, Path], checkpoints: Optional[List[str]] = None, da
                                sample_metric_max_generated_tokens=sample_metric_max_generated_tokens,
                                sample_metric_temperature=sample_metric_temperature, sample_metric_top_k=sample_metric_top_k,
                                sample_metric_top_p=sample_metric_top_p, num_store_generated_samples=num_store_generated_samples,
-                               skip_eval=skip_eval, max_iters=eval.max_iters, attention_forward_temp_size_gb=attention_forward_temp_size_gb)
+                               skip_eval=skip_eval, max_iters=eval.max_iters, attention_forward_temp_size_gb=attention_forward_temp_size_gb, tp=tp)
     hp = load_configuration(out_dir)
     if kv_cache is None:
         kv_cache = KVCacheArgs(**{k: v for k, v in (hp.get("kv_cache") or {}).items() if k in KVCacheArgs.__dataclass_fields__})
     if use_sample_metric is not None:
         eval = EvalArgs(**{**eval.__dict__, "sample_metric": use_sample_metric, "max_new_tokens": sample_metric_max_generated_tokens})
-    launch(main, devices, out_dir=out_dir, checkpoints=checkpoints or ["final"], data=data, kv_cache=kv_cache, eval=eval, precision=precision,
+    launch(main, devices if tp == 1 else tp, tp=tp, out_dir=out_dir, checkpoints=checkpoints or ["final"], data=data, kv_cache=kv_cache, eval=eval, precision=precision,
            eval_dir=eval_dir, setups=setups or [kv_cache.name], batch_size=batch_size, hp=hp, model_name=model_name or hp.get("model_name"),
            seed=seed, sample_args=dict(temperature=sample_metric_temperature, top_k=sample_metric_top_k, top_p=sample_metric_top_p),
            num_store_generated_samples=num_store_generated_samples, skip_eval=skip_eval)
@@ -176,7 +176,10 @@ def setup(out_dir: Union[str, Path], checkpoints: Optional[List[str]] = None, da
 
 def main(rank: int, local_rank: int, world_size: int, *, out_dir, checkpoints, data, kv_cache, eval, precision, eval_dir, setups, batch_size, hp,
          model_name, seed: Optional[int] = None, sample_args: Optional[dict] = None, num_store_generated_samples: Optional[int] = None,
-         skip_eval: bool = False) -> None:
+         skip_eval: bool = False, tp: int = 1) -> None:
+    """One worker. ``tp == 1``: every launched rank is an independent worker that claims batches through the lock
+    files. ``tp > 1``: the launched ranks form ONE worker whose model is sharded over them (heads and MLP columns);
+    rank 0 claims the batches and writes the results, the others follow its decisions."""
     from keys_values_b200.finetune.longcontext_full import create_gpt_model, wrap_gpt_model
     from keys_values_b200.finetune.args import GradientArgs
     from keys_values_b200.finetune.utils import load_model_checkpoint
@@ -188,6 +191,16 @@ def main(rank: int, local_rank: int, world_size: int, *, out_dir, checkpoints, d
     lora = LoRAArgs(**lora_cfg) if isinstance(lora_cfg, dict) else None
     base_dir = Path(hp.get("checkpoint_dir", out_dir))
     helper = EvaluationWithTasksHelper(out_dir, eval_dir)
+    comm = None
+    if tp > 1:
+        import torch.distributed as dist
+
+        from keys_values_b200.parallel.tp import TPComm, tp_model_from
+
+        if world_size != tp:
+            raise ValueError(f"tp = {tp} needs {tp} launched ranks, got {world_size}")
+        comm = TPComm(tp, rank, device, dtype=dtype)
+    writer = comm is None or rank == 0
     if seed is not None:
         torch.manual_seed(seed)  # the same on every worker: sampled answers do not depend on who claims a batch
     tasks = EvaluationTasks(setups, [c if Path(c).is_absolute() else str(Path(out_dir) / c) for c in checkpoints])
@@ -215,15 +228,27 @@ def main(rank: int, local_rank: int, world_size: int, *, out_dir, checkpoints, d
         for b_idx, batch in enumerate(loader):
             if eval.max_iters is not None and b_idx >= eval.max_iters:
                 break
-            lock = helper.get_lock(task, b_idx)
-            if lock is None:
+            lock = helper.get_lock(task, b_idx) if writer else None
+            if comm is not None:
+                decision = [lock is not None]
+                dist.broadcast_object_list(decision, src=0)
+                if not decision[0]:
+                    continue
+            elif lock is None:
                 continue
             done = False
             try:
                 if current != task:
-                    config, gpt = create_gpt_model(base_dir, model_name, lora, device, dtype, hp.get("yarn_rope", True))
+                    if seed is not None:
+                        torch.manual_seed(seed)  # whatever a checkpoint leaves to the initialisation is the same for every task and worker
+                    config, gpt = create_gpt_model(base_dir, model_name, lora, device if comm is None else "cpu", dtype,
+                                                   hp.get("yarn_rope", True))
                     head = HeadModelFactory.create(head_name, config).to(device)
                     load_model_checkpoint(gpt, base_dir, Path(task.checkpoint), head)
+                    if comm is not None:
+                        if current is not None:
+                            model.gpt_model.close()
+                        gpt = tp_model_from(gpt, comm, device, dtype, yarn_rope=hp.get("yarn_rope", True))
                     kv = KVCacheArgs(**{**kv_cache.__dict__, "name": task.setup_name})
                     model = wrap_gpt_model(gpt, head, kv, GradientArgs(), batch_size, device, dtype)
                     model.eval()
@@ -251,11 +276,17 @@ def main(rank: int, local_rank: int, world_size: int, *, out_dir, checkpoints, d
                         row[eval.sample_metric] = sc
                     keep = len(refs) if num_store_generated_samples is None else max(
                         0, min(len(refs), num_store_generated_samples - stored.get(task.key, 0)))
-                    if keep:
+                    if keep and writer:
                         store_generated_samples(helper.task_dir(task) / GENERATED_SAMPLES_FILENAME.format(b_idx), [r[0] for r in refs][:keep],
                                                 res["generated"][:keep], res["scores"][:keep])
                         stored[task.key] = stored.get(task.key, 0) + keep
-                store_eval_metrics(helper.result_path(task, b_idx), rows)
+                if writer:
+                    store_eval_metrics(helper.result_path(task, b_idx), rows)
                 done = True
             finally:
-                helper.release(lock, done)
+                if lock is not None:
+                    helper.release(lock, done)
+    if comm is not None:
+        if model is not None:
+            model.gpt_model.close()
+        comm.close()

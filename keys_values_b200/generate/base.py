@@ -153,8 +153,20 @@ def generate(model: GPT, prompt: torch.Tensor, max_returned_tokens: int, prompt_
 
 def main(checkpoint_dir: str, prompt: str = "What food do llamas eat?", *, max_new_tokens: int = 50, cache_name: str = "h2o-default",
          cache_length: int = 4096, chunk_size: int = 1024, temperature: float = 0.8, top_k: Optional[int] = 50, top_p: float = 1.0,
-         precision: Optional[str] = None, device: Optional[str] = None) -> str:
-    """CLI body of ``keys_values_b200 generate``: load a checkpoint directory, generate a reply."""
+         precision: Optional[str] = None, device: Optional[str] = None, tp: int = 1, seed: int = 1337) -> Optional[str]:
+    """CLI body of ``keys_values_b200 generate``: load a checkpoint directory, generate a reply. ``tp > 1``: the
+    model is sharded over ``tp`` ranks of this node (one process per GPU; gloo ranks on a machine without GPUs)."""
+    from keys_values_b200.parallel.launch import launch
+
+    result: List[str] = []
+    launch(_generate_rank, tp, checkpoint_dir=checkpoint_dir, prompt=prompt, max_new_tokens=max_new_tokens, cache_name=cache_name,
+           cache_length=cache_length, chunk_size=chunk_size, temperature=temperature, top_k=top_k, top_p=top_p, precision=precision,
+           device=device, seed=seed, result=result)
+    return result[0] if result else None  # spawned ranks print the text; it comes back only from an in-process run
+
+
+def _generate_rank(rank: int, local_rank: int, world: int, *, checkpoint_dir, prompt, max_new_tokens, cache_name, cache_length, chunk_size,
+                   temperature, top_k, top_p, precision, device, seed, result) -> None:
     from pathlib import Path
 
     from keys_values_b200.config import Config
@@ -165,16 +177,30 @@ def main(checkpoint_dir: str, prompt: str = "What food do llamas eat?", *, max_n
     from keys_values_b200.utils import get_default_supported_precision, str_to_torch_dtype
 
     ckpt = Path(checkpoint_dir)
-    dev = torch.device(device or ("cuda" if torch.cuda.is_available() else "cpu"))
+    if device is not None:
+        dev = torch.device(device)
+    else:
+        dev = torch.device("cuda", local_rank) if torch.cuda.is_available() else torch.device("cpu")
     dtype = str_to_torch_dtype(precision or get_default_supported_precision(False))
     config = Config.from_checkpoint(ckpt)
     tokenizer = Tokenizer(ckpt)
     style = load_prompt_style(ckpt) if has_prompt_style(ckpt) else Default()
-    with torch.device(dev):
-        model = GPT(config)
-    model = model.to(dtype)
-    load_model_checkpoint(model, ckpt)
+    comm = None
+    if world > 1:
+        from keys_values_b200.parallel.tp import TPComm, TPGPT, load_sharded_checkpoint
+
+        comm = TPComm(world, rank, dev, dtype=dtype)
+        with torch.device(dev):
+            model = TPGPT(config, comm)
+        model = model.to(dtype)
+        load_sharded_checkpoint(model, ckpt)
+    else:
+        with torch.device(dev):
+            model = GPT(config)
+        model = model.to(dtype)
+        load_model_checkpoint(model, ckpt)
     model.eval()
+    torch.manual_seed(seed)  # every rank draws the same samples
     ids = tokenizer.encode(style.apply(prompt), device=dev).to(torch.int64)
     total = ids.numel() + max_new_tokens
     model.max_seq_length = total
@@ -182,5 +208,9 @@ def main(checkpoint_dir: str, prompt: str = "What food do llamas eat?", *, max_n
                                                  device=dev, dtype=dtype))
     out = generate(model, ids, total, chunk_size, temperature, top_k, top_p, eos_id=tokenizer.eos_id, include_prompt=False)
     text = tokenizer.decode(out)
-    print(text)
-    return text
+    if rank == 0:
+        print(text)
+    result.append(text)
+    if comm is not None:
+        model.close()
+        comm.close()

@@ -523,6 +523,55 @@ def shard_state_dict(state_dict, config, world: int, rank: int):
     return out
 
 
+def load_sharded_checkpoint(model, checkpoint_dir) -> None:
+    """Fill a :class:`TPGPT` with its shard of ``checkpoint_dir/lit_model.pth`` (the file of the whole model,
+    memory-mapped: a rank reads only the slices it keeps)."""
+    from pathlib import Path
+
+    path = Path(checkpoint_dir) / "lit_model.pth"
+    if not path.is_file() or path.stat().st_size == 0:
+        return  # a directory with only the configuration: the random initialisation stays (tests, benchmarks)
+    sd = torch.load(path, map_location="cpu", mmap=True, weights_only=True)
+    sd = sd.get("model", sd)
+    comm = model.tp_comm
+    model.load_state_dict(shard_state_dict(sd, model.full_config, comm.world, comm.rank))
+
+
+def plain_state_dict(gpt_model) -> dict:
+    """State dict of a model in the key layout of the plain :class:`GPT`; LoRA adapters are merged into the
+    linears they decorate first (the model is changed in place)."""
+    from keys_values_b200.models import lora as lora_mod
+
+    if any(isinstance(m, lora_mod.LoRALinear) for m in gpt_model.modules()):
+        lora_mod.merge_lora_weights(gpt_model)
+    out = {}
+    for k, v in gpt_model.state_dict().items():
+        if "lora_" in k:
+            continue
+        out[k.replace(".linear.", ".")] = v
+    return out
+
+
+def tp_model_from(gpt_model, comm: "TPComm", device, dtype, yarn_rope: bool = True):
+    """Shard a whole model (on the host; LoRA adapters are merged) over the ranks of ``comm``: returns this rank's
+    :class:`TPGPT` on ``device``."""
+    import dataclasses
+
+    from keys_values_b200.config import Config
+    from keys_values_b200.models.pos_encoding import position_encoding_factory
+
+    src = gpt_model.config
+    cfg = Config(**{f.name: getattr(src, f.name) for f in dataclasses.fields(Config) if f.init})
+    sd = shard_state_dict(plain_state_dict(gpt_model), cfg, comm.world, comm.rank)
+    local = local_config(cfg, comm.world)
+    cls = globals().get("TPGPT") or __getattr__("TPGPT")
+    with torch.device(device):
+        model = cls(cfg, comm, pos_encoding=position_encoding_factory(local, do_yarn=yarn_rope, device=device))
+    model = model.to(dtype)
+    model.load_state_dict(sd)
+    return model
+
+
 class RowShard:
     """Token rows of an activation ``(B, T, E)`` sharded over the ranks (flattened batch-major; rank ``r`` holds
     rows ``[r·n, (r+1)·n)``). Blocks of a :class:`TPGPT` pass it from one to the next on the fused path; whoever

@@ -215,7 +215,7 @@ def case_tp_gpt(rank, world, dev):
     cuda = dev.type == "cuda"
     dtype = torch.bfloat16 if cuda else torch.float32
     torch.manual_seed(5)
-    cfg = Config.from_name("tiny-qwen3")
+    cfg = Config.from_name(os.environ.get("KVB200_TEST_MODEL", "tiny-qwen3"))
     full = GPT(cfg)
     full.apply(full._init_weights)
     full = full.to(device=dev, dtype=dtype).eval()
