@@ -52,7 +52,9 @@ class GradientArgs:
     ``save_attention_outputs``: keep attention outputs for the backward pass (None = auto);
     ``offload_weights``: the transformer blocks' weights live in pinned host memory and are streamed to the
     device block by block (``weight_slots`` device slots, default two per row of layers); the optimizer then
-    updates the trainable block parameters on the host."""
+    updates the trainable block parameters on the host;
+    ``profile_parts``: print a ``cProfile`` report (cumulative time) of the forward and / or backward part of the
+    step; with ``profile_exit`` the process ends after the first report."""
 
     layers_per_cell: int = 1
     chunks_per_cell_multiplier: float = 1.0
@@ -67,6 +69,8 @@ class GradientArgs:
     save_attention_outputs: Optional[bool] = None
     offload_weights: bool = False
     weight_slots: Optional[int] = None
+    profile_parts: Optional[str] = None  # "forward" | "backward" | "both": cProfile report of that part of every step
+    profile_exit: bool = False           # end the process after the first report
 
 
 @dataclass

@@ -136,6 +136,7 @@ def wrap_gpt_model(gpt_model, head_model, kv_cache: KVCacheArgs, grad: GradientA
         single_tokens_for_targets=grad.single_tokens_for_targets, offload_checkpoints=grad.offload_checkpoints,
         pin_memory=grad.layercp_pin_memory, layercp_qname=grad.layercp_qname, cachecp_qname=grad.cachecp_qname,
         save_attention_outputs=grad.save_attention_outputs, profile_steps=profile_steps,
+        profile_parts=grad.profile_parts, profile_exit=grad.profile_exit,
     )
     if grad.offload_weights:
         from keys_values_b200.optimize.weight_streaming import WeightStreamer

@@ -62,6 +62,8 @@ class LossValue:
         return f"LossValue({self._value})"
 
 
+from keys_values_b200.tools.profiling import nvtx_mark  # noqa: E402
+
 class LongContextGradientModel(LongContextInferenceModel):
     def __init__(
         self,
@@ -80,6 +82,8 @@ class LongContextGradientModel(LongContextInferenceModel):
         row_done_hook: Optional[Callable[[int, int], None]] = None,
         average_loss_per_batch: bool = False,
         save_attention_outputs: Optional[bool] = None,
+        profile_parts: Optional[str] = None,
+        profile_exit: bool = False,
         **kwargs,
     ):
         super().__init__(
@@ -96,6 +100,9 @@ class LongContextGradientModel(LongContextInferenceModel):
         self.row_done_hook = row_done_hook
         self.average_loss_per_batch = average_loss_per_batch
         self.profile_steps = profile_steps
+        from keys_values_b200.tools.profiling import PartProfiler
+
+        self.part_profiler = PartProfiler(profile_parts, exit_after=profile_exit)  # cProfile of "forward" / "backward" / "both"
         # Keep the attention outputs and normalisers of the forward pass (B·T·H·D values per
         # layer) so that the backward pass only recomputes the linear parts. None = decide
         # from the free device memory.
@@ -117,6 +124,7 @@ class LongContextGradientModel(LongContextInferenceModel):
         if not self.training or targets is None:
             return super().forward(input_ids, targets, scale_factor)
         t0 = time.perf_counter()
+        self.part_profiler.start("forward")
         self._init_members_from_tokens(input_ids, targets)
         gpt = self.gpt_model
         B, T = input_ids.shape
@@ -132,6 +140,8 @@ class LongContextGradientModel(LongContextInferenceModel):
         n_cells = len(self.cells)
 
         def layer_hook(x, layer_idx, start, end):
+            if layer_idx == 0:
+                nvtx_mark(f"forward: cell {start}:{end}")
             if layer_idx in self._layer_ckpt.slots:
                 self._layer_ckpt.write(layer_idx, start, end, x)
 
@@ -174,6 +184,7 @@ class LongContextGradientModel(LongContextInferenceModel):
             if dev.type == "cuda":
                 torch.cuda.synchronize(dev)
             self.profile_records.append(dict(forward_time=time.perf_counter() - t0))
+        self.part_profiler.stop("forward", dev)
         return LossValue(loss_rows.mean(), self)
 
     def _decide_save_attention(self, B: int, T: int, dev, dtype) -> bool:
@@ -194,6 +205,7 @@ class LongContextGradientModel(LongContextInferenceModel):
         if self._status != "forward_done":
             raise RuntimeError("forward (in training mode) must be called before backward")
         t0 = time.perf_counter()
+        self.part_profiler.start("backward")
         input_ids, targets, scale_factor = self._inputs
         gpt, head = self.gpt_model, self.head_model
         B, T = input_ids.shape
@@ -234,6 +246,7 @@ class LongContextGradientModel(LongContextInferenceModel):
         ws = self.weight_streamer
         for r in range(len(bounds) - 2, -1, -1):
             first, end = bounds[r], bounds[r + 1]
+            nvtx_mark(f"backward: layers {first}:{end}")
             if ws is not None:
                 # host-resident blocks: this row's blocks on the device with gradient buffers, the next row's on their way
                 ws.acquire_many(range(first, end), need_grad=True)
@@ -302,6 +315,7 @@ class LongContextGradientModel(LongContextInferenceModel):
             self.profile_records[-1]["backward_time"] = time.perf_counter() - t0
             if dev.type == "cuda":
                 self.profile_records[-1]["peak_memory_gb"] = torch.cuda.max_memory_allocated(dev) / 2**30
+        self.part_profiler.stop("backward", dev)
 
     def clear(self) -> None:
         self._attn_saved = None

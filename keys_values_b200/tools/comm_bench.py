@@ -43,6 +43,7 @@ def _timed(fn, iters=10, warmup=3):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", default=None)
+    ap.add_argument("--only", default="all", choices=["all", "oneshot", "allreduce", "tp_gemm"])
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -67,8 +68,35 @@ def main():
                 fh.write(line + "\n")
                 fh.flush()
 
+    # ------------------------------------------- one-shot all-reduce (decode steps under tensor parallelism)
+    if args.only in ("all", "oneshot"):
+        from keys_values_b200.parallel.tp import TPComm
+
+        comm = TPComm(world, rank, dev)
+        for rows, feat in ((4, 4096), (16, 4096), (32, 4096)):
+            src = torch.randn(rows, feat, device=dev, dtype=torch.bfloat16)
+            res = torch.randn(rows, feat, device=dev, dtype=torch.bfloat16)
+            ref = src.clone()
+
+            def fused(k=16):
+                for _ in range(k):  # a burst, as in a decode step: launch latency overlaps across calls
+                    comm.out_buffer(rows, feat, torch.bfloat16).copy_(src)
+                    comm.all_reduce(comm._pending[2], residual=res)
+
+            def lib(k=16):
+                for _ in range(k):
+                    ref.copy_(src)
+                    dist.all_reduce(ref)
+                    torch.add(ref, res)
+
+            ms_f, ms_n = _timed(fused) / 16, _timed(lib) / 16
+            cu.check_status(dev)
+            out({"bench": "oneshot_allreduce_bf16_plus_residual", "world": world, "rows": rows, "features": feat,
+                 "bytes": rows * feat * 2, "fused_us": ms_f * 1e3, "nccl_plus_add_us": ms_n * 1e3})
+        comm.close()
+
     # ---------------------------------------------------------------- all-reduce (gradient mean)
-    for mib in (16, 128, 1024):
+    for mib in ((16, 128, 1024) if args.only in ("all", "allreduce") else ()):
         n = mib * 2**20 // 2
         arena = SymmetricArena(n, torch.bfloat16, dev, world, rank)
         arena.tensor.normal_()
@@ -84,7 +112,7 @@ def main():
 
     # ------------------------------------------- all-gather -> GEMM and GEMM -> reduce-scatter
     # token-parallel rows of a cell of the flagship model (n_embd 2560, MLP 9728, QKV 6144)
-    for rows, K, N in ((2048, 2560, 6144), (2048, 2560, 9728), (4096, 2560, 9728)):
+    for rows, K, N in (((2048, 2560, 6144), (2048, 2560, 9728), (4096, 2560, 9728)) if args.only in ("all", "tp_gemm") else ()):
         M = world * rows
         ctx = TPContext(world, rank, dev, max_rows=M, max_features=max(K, N))
         shard = torch.randn(rows, K, device=dev, dtype=torch.bfloat16)

@@ -264,3 +264,34 @@ def test_gradients_with_grace_period(chunk, monkeypatch):
         fd = (vals[0] - vals[1]) / (2 * eps)
         an = float((res[0][1][n] * d).sum())
         assert abs(fd - an) <= 5e-3 * abs(an) + 2e-4, (n, fd, an)
+
+
+def test_profile_parts_reports_forward_and_backward(capsys):
+    """``profile_parts``: a cProfile report per part of the step, the step itself unchanged."""
+    from keys_values_b200.config import Config
+    from keys_values_b200.kvcache.factory import KVCacheFactory
+    from keys_values_b200.kvcache.gradient.main import LongContextGradientModel
+    from keys_values_b200.models.head_model import CrossEntropyOnLogits
+    from keys_values_b200.models.model import GPT
+
+    torch.manual_seed(0)
+    cfg = Config.from_name("tiny-gpt")
+    losses = []
+    for parts in (None, "both"):
+        torch.manual_seed(1)
+        gpt = GPT(cfg)
+        gpt.apply(gpt._init_weights)
+        gpt.assign_kv_caches(KVCacheFactory.create(gpt, "lastrec-default", 1, 48, dtype=torch.float32))
+        gm = LongContextGradientModel(gpt, CrossEntropyOnLogits(cfg), layers_per_cell=1, chunk_size=16, profile_parts=parts)
+        gm.train()
+        ids, tg = torch.arange(96).view(1, 96) % cfg.vocab_size, torch.arange(16).view(1, 16)
+        loss = gm(ids, tg)
+        loss.backward()
+        losses.append(float(loss))
+        if parts:
+            assert set(gm.part_profiler.reports) == {"forward", "backward"}
+            assert "cumulative" in gm.part_profiler.reports["backward"]
+    assert losses[0] == losses[1]
+    assert "cProfile of the forward part" in capsys.readouterr().out
+    with pytest.raises(ValueError):
+        LongContextGradientModel(gpt, CrossEntropyOnLogits(cfg), layers_per_cell=1, chunk_size=16, profile_parts="sideways")
