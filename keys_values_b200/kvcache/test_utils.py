@@ -202,3 +202,85 @@ def record_forward_calls(cache: KVCache) -> List[ForwardInputOutput]:
 
     cache.forward = wrapped
     return log
+
+
+# ---------------------------------------------------------------------------------------------------
+# Before / after snapshots: freeze what a cache does today, check a changed implementation against it
+# (role of ``keys_values/kvcache/test_before_after.py:142-343``)
+# ---------------------------------------------------------------------------------------------------
+def _cache_state(cache: KVCache) -> Dict[str, torch.Tensor]:
+    """What defines a cache after a call: keys and values as attention sees them, token positions, and the
+    scores of score-based policies."""
+    state: Dict[str, torch.Tensor] = {}
+    if cache.current_length > 0:
+        kv = cache.get_keys_values()
+        if kv is not None:
+            state["keys"], state["values"] = kv.keys().detach().float().cpu(), kv.values().detach().float().cpu()
+        if hasattr(cache, "token_positions"):
+            state["token_positions"] = cache.token_positions().detach().cpu()
+    scores = getattr(cache, "scores", None)
+    if torch.is_tensor(scores):
+        state["scores"] = scores.detach().float().cpu()
+    return state
+
+
+class ForwardSnapshots:
+    """``ForwardSnapshots(cache, path_mask, num_steps).store()`` writes one file per ``forward`` call
+    (``path_mask.format(k)``: inputs, output, state afterwards). With a changed implementation,
+    ``.compare(**tolerances)`` feeds every call the STORED inputs (so that small differences do not drift from
+    call to call into different eviction decisions) and checks output and state against the files; the indices
+    of the calls that were compared are in ``.compared``."""
+
+    def __init__(self, cache: KVCache, path_mask: str, num_steps: int):
+        self.cache, self.path_mask, self.num_steps = cache, path_mask, num_steps
+        self.compared: List[int] = []
+        self._inner = cache.forward
+        self._k = 0
+
+    def _restore(self) -> None:
+        self.cache.forward = self._inner
+
+    def store(self) -> "ForwardSnapshots":
+        def wrapped(query, key, value, token_idx):
+            pos = self.cache.input_pos
+            out = self._inner(query, key, value, token_idx)
+            if self._k < self.num_steps:
+                cpu = lambda t: None if t is None else t.detach().cpu().clone()  # noqa: E731
+                torch.save({"inputs": dict(query=cpu(query), key=cpu(key), value=cpu(value), token_idx=cpu(token_idx), input_pos=pos),
+                            "output": cpu(out).float(), "state": _cache_state(self.cache)}, self.path_mask.format(self._k))
+            self._k += 1
+            return out
+
+        self.cache.forward = wrapped
+        return self
+
+    def compare(self, **tol) -> "ForwardSnapshots":
+        tol = tol or dict(atol=1e-5, rtol=1e-5)
+
+        def wrapped(query, key, value, token_idx):
+            if self._k >= self.num_steps:
+                self._k += 1
+                return self._inner(query, key, value, token_idx)
+            rec = torch.load(self.path_mask.format(self._k), weights_only=False)
+            inp = rec["inputs"]
+            if inp["input_pos"] != self.cache.input_pos:
+                raise AssertionError(f"call {self._k}: input_pos {self.cache.input_pos}, snapshot has {inp['input_pos']}")
+            to = lambda t, like: None if t is None else t.to(device=like.device, dtype=like.dtype)  # noqa: E731
+            out = self._inner(to(inp["query"], query), to(inp["key"], key), to(inp["value"], value),
+                              None if token_idx is None else to(inp["token_idx"], token_idx))
+            torch.testing.assert_close(out.detach().float().cpu(), rec["output"], msg=lambda m: f"call {self._k}, output: {m}", **tol)
+            now = _cache_state(self.cache)
+            for name, want in rec["state"].items():
+                if name == "token_positions":
+                    assert torch.equal(now[name], want), f"call {self._k}: token positions differ"
+                else:
+                    torch.testing.assert_close(now[name], want, msg=lambda m, n=name: f"call {self._k}, {n}: {m}", **tol)
+            self.compared.append(self._k)
+            self._k += 1
+            return out
+
+        self.cache.forward = wrapped
+        return self
+
+    def stop(self) -> None:
+        self._restore()

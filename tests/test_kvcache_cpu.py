@@ -205,3 +205,43 @@ def test_smart_lastrec_protects_initial_part():
     tp = caches[0].token_positions()[0, 0]
     assert tp[:5].tolist() == [0, 1, 2, 3, 4]
     assert tp.max().item() == C + 40 - 1
+
+
+def test_before_after_snapshots_catch_a_changed_cache(tmp_path):
+    """Freeze the calls of an H2O cache, replay them through an identical cache (passes) and through one whose
+    score update was tampered with (fails at the first call where a different slot is evicted)."""
+    from keys_values_b200.kvcache.test_utils import ForwardSnapshots
+
+    C, chunk = 32, 4
+    idx = torch.randint(0, 512, (2, C + 4 * chunk), generator=torch.Generator().manual_seed(3))
+    mask = str(tmp_path / "call_{}.pt")
+
+    def run(mode, tamper=False):
+        torch.manual_seed(1)
+        m = _model()
+        caches = KVCacheFactory.create(m, "h2o-default", 2, C, dtype=torch.float32, cache_kwargs=dict(max_chunk_size=chunk))
+        m.assign_kv_caches(caches)
+        m.reset()
+        snap = ForwardSnapshots(caches[0], mask, num_steps=5)
+        getattr(snap, mode)()
+        if tamper:
+            inner = caches[0]._update if hasattr(caches[0], "_update") else None
+            assert inner is not None
+
+            def noisy(*a, **k):
+                out = inner(*a, **k)
+                caches[0].scores.mul_(-1.0)  # evict the most attended tokens instead of the least
+                return out
+
+            caches[0]._update = noisy
+        with torch.no_grad():
+            m(idx[:, :C])
+            for s in range(C, idx.shape[1], chunk):
+                m(idx[:, s : s + chunk])
+        snap.stop()
+        return snap
+
+    run("store")
+    assert run("compare").compared == [0, 1, 2, 3, 4]
+    with pytest.raises(AssertionError):
+        run("compare", tamper=True)
