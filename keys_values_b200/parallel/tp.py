@@ -496,30 +496,99 @@ def local_config(config, world: int):
         raise NotImplementedError("a QK norm over all heads at once cannot be sharded over heads")
     if config.mlp_class_name == "LLaMAMoE":
         raise NotImplementedError("mixture-of-experts blocks are not sharded")
-    return dataclasses.replace(config, n_head=H // world, n_query_groups=G // world, intermediate_size=I // world, head_size=config.head_size)
+    return dataclasses.replace(config, n_head=H // world, n_query_groups=G // world, intermediate_size=I // world, head_size=config.head_size)  # keeps the class: LoRA fields survive
+
+
+def _shard_rule(key: str, config):
+    """How the tensor ``key`` of a whole model is split over ranks: ``(kind, axis)`` with kind in
+    ``rep`` (replicated), ``rank0`` (kept by rank 0, zero elsewhere: biases of row-parallel linears),
+    ``qkv`` (the q | k | v row segments, each split over KV groups), ``qkv_lora`` (the same for the rows of the
+    enabled segments of a LoRA ``B``), ``heads`` (the H·D axis), ``inter`` (the MLP axis)."""
+    leaf = key.rsplit(".", 1)[-1]
+    weight_like = leaf in ("weight", "bias")
+    if ".attn.qkv." in key:
+        if leaf == "lora_A":
+            return "rep", 0
+        if leaf == "lora_B":
+            return "qkv_lora", 0
+        return ("qkv", 0) if weight_like else ("rep", 0)
+    if ".attn.proj." in key:
+        if leaf == "weight" or leaf == "lora_A":
+            return "heads", 1
+        return ("rank0", 0) if leaf == "bias" else ("rep", 0)
+    if ".mlp.fc" in key:
+        if leaf == "lora_A":
+            return "rep", 0
+        return ("inter", 0) if (weight_like or leaf == "lora_B") else ("rep", 0)
+    if ".mlp.proj." in key:
+        if leaf == "weight" or leaf == "lora_A":
+            return "inter", 1
+        return ("rank0", 0) if leaf == "bias" else ("rep", 0)
+    return "rep", 0
+
+
+def _qkv_segments(config, rows: int):
+    """Row segments ``(start, rows_per_group)`` of a fused q | k | v tensor with ``rows`` rows: all three for the
+    projection itself, only the LoRA-enabled ones for a LoRA ``B``."""
+    H, G, D = config.n_head, config.n_query_groups, config.head_size
+    full = [(H // G) * D, D, D]  # rows per KV group of the q, k and v segments
+    if rows == (H + 2 * G) * D:
+        per_group = full
+    else:
+        enabled = [getattr(config, f"lora_{n}", False) for n in ("query", "key", "value")]
+        per_group = [w for w, e in zip(full, enabled) if e]
+        if rows != sum(per_group) * G:
+            raise ValueError(f"cannot interpret a fused qkv tensor with {rows} rows")
+    segs, start = [], 0
+    for w in per_group:
+        segs.append((start, w))
+        start += w * G
+    return segs
 
 
 def shard_state_dict(state_dict, config, world: int, rank: int):
-    """State dict of the whole model → state dict of the shard of ``rank`` (see :func:`local_config`)."""
-    H, G, D, I = config.n_head, config.n_query_groups, config.head_size, config.intermediate_size
-    gs = H // G
+    """State dict of the whole model (plain or LoRA) → state dict of the shard of ``rank`` (see
+    :func:`local_config`). Column-parallel linears keep their rows and the rows of their LoRA ``B`` (``A`` is
+    replicated), row-parallel linears their columns and the columns of their LoRA ``A`` (``B`` is replicated)."""
+    G, I = config.n_query_groups, config.intermediate_size
+    D, gs = config.head_size, config.n_head // config.n_query_groups
     g0, g1 = rank * (G // world), (rank + 1) * (G // world)
     i0, i1 = rank * (I // world), (rank + 1) * (I // world)
     out = {}
     for key, t in state_dict.items():
-        if ".attn.qkv." in key:
-            out[key] = torch.cat((t[g0 * gs * D : g1 * gs * D], t[H * D + g0 * D : H * D + g1 * D],
-                                  t[(H + G) * D + g0 * D : (H + G) * D + g1 * D])).contiguous()
-        elif key.endswith(".attn.proj.weight"):
-            out[key] = t[:, g0 * gs * D : g1 * gs * D].contiguous()
-        elif ".mlp.fc" in key:
-            out[key] = t[i0:i1].contiguous()
-        elif key.endswith(".mlp.proj.weight"):
-            out[key] = t[:, i0:i1].contiguous()
-        elif key.endswith(".attn.proj.bias") or key.endswith(".mlp.proj.bias"):
-            out[key] = t if rank == 0 else torch.zeros_like(t)
-        else:
+        kind, axis = _shard_rule(key, config)
+        if kind == "rep":
             out[key] = t
+        elif kind == "rank0":
+            out[key] = t if rank == 0 else torch.zeros_like(t)
+        elif kind in ("qkv", "qkv_lora"):
+            out[key] = torch.cat([t[s + g0 * w : s + g1 * w] for s, w in _qkv_segments(config, t.shape[0])]).contiguous()
+        elif kind == "heads":
+            out[key] = t.narrow(axis, g0 * gs * D, (g1 - g0) * gs * D).contiguous()
+        else:
+            out[key] = t.narrow(axis, i0, i1 - i0).contiguous()
+    return out
+
+
+def unshard_state_dict(shards, config):
+    """Inverse of :func:`shard_state_dict`: the state dicts of all ranks (in rank order) → the whole model's."""
+    world = len(shards)
+    G = config.n_query_groups
+    out = {}
+    for key, t0 in shards[0].items():
+        kind, axis = _shard_rule(key, config)
+        if kind in ("rep", "rank0"):
+            out[key] = t0
+        elif kind in ("qkv", "qkv_lora"):
+            rows = t0.shape[0] * world
+            parts = []
+            for s, w in _qkv_segments(config, rows):
+                local_start = s // world
+                for sh in shards:
+                    parts.append(sh[key][local_start : local_start + w * (G // world)])
+            out[key] = torch.cat(parts).contiguous()
+        else:
+            out[key] = torch.cat([sh[key] for sh in shards], dim=axis).contiguous()
     return out
 
 
@@ -605,9 +674,14 @@ def dense(x):
     return x.full() if isinstance(x, RowShard) else x
 
 
-def _tpgpt_class():
+def _tp_classes(lora: bool):
     from keys_values_b200 import ops
-    from keys_values_b200.models.model import GPT, Block, LLaMAMLP, RMSNorm
+    from keys_values_b200.models.model import LLaMAMLP, RMSNorm
+
+    if lora:
+        from keys_values_b200.models.lora import GPT, Block
+    else:
+        from keys_values_b200.models.model import GPT, Block
 
     class TPBlock(Block):
         """A block of the shard. Inference chunks whose rows divide by ``128 · world`` take the fused path:
@@ -670,18 +744,33 @@ def _tpgpt_class():
             self.fused_prefill = fused_prefill
             self._fused_ctx: Optional[TPContext] = None
             self._fc_cat = {}
+            if lora and getattr(full_config, "lora_kind", "default") != "default":
+                raise NotImplementedError("tensor parallelism supports plain LoRA adapters (lora_kind = 'default')")
             for block in self.transformer.h:
                 block.owner = weakref.ref(self)
-                block.attn.proj = RowParallelLinear.from_linear(block.attn.proj, comm)
-                block.mlp.proj = RowParallelLinear.from_linear(block.mlp.proj, comm)
+                for holder, name in ((block.attn, "proj"), (block.mlp, "proj")):
+                    mod = getattr(holder, name)
+                    if type(mod) is torch.nn.Linear:
+                        setattr(holder, name, RowParallelLinear.from_linear(mod, comm))
+                    else:  # a LoRA linear: W holds this rank's columns, A its columns too, B is replicated
+                        mod.register_forward_hook(self._sum_output_hook)
                 # the inputs of the column-parallel linears (after the norms; the residual path is replicated)
                 block.attn.register_forward_pre_hook(self._shard_input_hook)
                 block.mlp.register_forward_pre_hook(self._shard_input_hook)
-                # per-head QK norms: one weight serves all heads, every rank sees the gradient of its heads only
-                for norm in (block.attn.norm_q, block.attn.norm_k):
-                    if norm is not None:
-                        for p in norm.parameters():
-                            p.register_hook(self._sum_over_ranks)
+                # Replicated parameters of which every rank sees a part of the gradient: the per-head QK norms (one
+                # weight serves all heads), LoRA A of column-parallel linears and LoRA B of row-parallel linears
+                shared = [p for norm in (block.attn.norm_q, block.attn.norm_k) if norm is not None for p in norm.parameters()]
+                for mod, which in ((block.attn.qkv, "lora_A"), (getattr(block.mlp, "fc_1", None), "lora_A"),
+                                   (getattr(block.mlp, "fc_2", None), "lora_A"), (getattr(block.mlp, "fc", None), "lora_A"),
+                                   (block.attn.proj, "lora_B"), (block.mlp.proj, "lora_B")):
+                    p = getattr(mod, which, None) if mod is not None else None
+                    if isinstance(p, torch.nn.Parameter):
+                        shared.append(p)
+                for p in shared:
+                    p.register_hook(self._sum_over_ranks)
+
+        def _sum_output_hook(self, module, args, output):
+            return _AllReduceSum.apply(output.reshape(-1, output.shape[-1]), self.tp_comm).view_as(output)
 
         def _make_block(self, config, block_idx):
             return TPBlock(config, block_idx)
@@ -747,12 +836,15 @@ def _tpgpt_class():
                 self._fused_ctx.close()
                 self._fused_ctx = None
 
+    TPGPT.__name__ = TPGPT.__qualname__ = "TPLoRAGPT" if lora else "TPGPT"
     return TPGPT, TPBlock
 
 
 def __getattr__(name):
     if name in ("TPGPT", "TPBlock"):
-        gpt_cls, block_cls = _tpgpt_class()
-        globals()["TPGPT"], globals()["TPBlock"] = gpt_cls, block_cls
+        globals()["TPGPT"], globals()["TPBlock"] = _tp_classes(False)
+        return globals()[name]
+    if name == "TPLoRAGPT":
+        globals()["TPLoRAGPT"] = _tp_classes(True)[0]
         return globals()[name]
     raise AttributeError(name)

@@ -297,5 +297,110 @@ def case_tp_gpt_grads(rank, world, dev):
     comm.close()
 
 
+def case_tp_lora_grads(rank, world, dev):
+    """LoRA under tensor parallelism (A of column-parallel and B of row-parallel linears replicated, the other
+    factor sharded): loss and the gradients of all adapter tensors equal those of the whole LoRA model."""
+    from keys_values_b200.models import lora as lora_mod
+    from keys_values_b200.parallel.tp import TPComm, TPLoRAGPT, shard_state_dict
+
+    cuda = dev.type == "cuda"
+    dtype = torch.bfloat16 if cuda else torch.float32
+    torch.manual_seed(8)
+    cfg = lora_mod.Config.from_name("tiny-qwen3", lora_r=4, lora_alpha=8, lora_query=True, lora_key=True, lora_value=True,
+                                    lora_projection=True, lora_mlp=True)
+    full = lora_mod.GPT(cfg)
+    full.apply(full._init_weights)
+    for n, p in full.named_parameters():
+        if "lora_B" in n:
+            torch.nn.init.normal_(p, std=0.05)
+    lora_mod.mark_only_lora_as_trainable(full)
+    full = full.to(device=dev, dtype=dtype)
+    comm = TPComm(world, rank, dev, dtype=dtype)
+    shard = TPLoRAGPT(cfg, comm).to(device=dev, dtype=dtype)
+    shard.load_state_dict(shard_state_dict(full.state_dict(), cfg, world, rank))
+    lora_mod.mark_only_lora_as_trainable(shard)
+    ids = torch.randint(0, cfg.vocab_size, (2, 80), device=dev)
+    tg = torch.randint(0, cfg.vocab_size, (2 * 80,), device=dev)
+    dist.broadcast(ids, 0)
+    dist.broadcast(tg, 0)
+    losses = []
+    for model in (full, shard):
+        logits = model(ids)
+        loss = torch.nn.functional.cross_entropy(logits.view(-1, logits.shape[-1]).float(), tg)
+        loss.backward()
+        losses.append(loss.detach().float())
+    assert abs(losses[0] - losses[1]) < (2e-2 if cuda else 1e-5), losses
+    want = shard_state_dict({n: p.grad for n, p in full.named_parameters() if p.grad is not None}, cfg, world, rank)
+    tol = 8e-2 if cuda else 1e-4
+    n_checked = 0
+    for n, p in shard.named_parameters():
+        if not p.requires_grad:
+            continue
+        w, g = want[n].float(), p.grad.float()
+        err = (g - w).norm() / w.norm().clamp(min=1e-6)
+        assert err < tol, f"{n}: relative gradient error {err}"
+        n_checked += 1
+    assert n_checked >= 2 * 10  # A and B of qkv, proj, fc_1, fc_2, mlp.proj in both layers
+    comm.close()
+
+
+def case_tp_train(rank, world, dev):
+    """The chunked gradient engine (cells, activation checkpoints, replay through the cache) on a LoRA shard:
+    loss and adapter gradients equal the whole model's; every rank evicts for its own KV heads."""
+    from keys_values_b200.kvcache.factory import KVCacheFactory
+    from keys_values_b200.kvcache.gradient.main import LongContextGradientModel
+    from keys_values_b200.models import lora as lora_mod
+    from keys_values_b200.models.head_model import CrossEntropyOnLogits
+    from keys_values_b200.parallel.tp import TPComm, TPLoRAGPT, shard_state_dict
+
+    cuda = dev.type == "cuda"
+    dtype = torch.bfloat16 if cuda else torch.float32
+    torch.manual_seed(9)
+    cfg = lora_mod.Config.from_name("tiny-qwen3", lora_r=4, lora_alpha=8, lora_query=True, lora_value=True, lora_projection=True)
+    full = lora_mod.GPT(cfg)
+    full.apply(full._init_weights)
+    for n, p in full.named_parameters():
+        if "lora_B" in n:
+            torch.nn.init.normal_(p, std=0.05)
+    lora_mod.mark_only_lora_as_trainable(full)
+    full = full.to(device=dev, dtype=dtype)
+    comm = TPComm(world, rank, dev, dtype=dtype)
+    shard = TPLoRAGPT(cfg, comm).to(device=dev, dtype=dtype)
+    shard.load_state_dict(shard_state_dict(full.state_dict(), cfg, world, rank))
+    lora_mod.mark_only_lora_as_trainable(shard)
+    T, C, cs = (1024, 256, 128) if cuda else (320, 96, 32)
+    ids = torch.randint(0, cfg.vocab_size, (1, T), device=dev)
+    tg = torch.randint(0, cfg.vocab_size, (1, cs), device=dev)
+    dist.broadcast(ids, 0)
+    dist.broadcast(tg, 0)
+    for name, exact in (("lastrec-default", True), ("h2o-torch-quantized8", False)):
+        losses, grads = [], []
+        for model in (full, shard):
+            for p in model.parameters():
+                p.grad = None
+            ck = dict(max_chunk_size=cs) if "h2o" in name else None
+            model.assign_kv_caches(KVCacheFactory.create(model, name, 1, C, dtype=dtype, device=dev, cache_kwargs=ck))
+            gm = LongContextGradientModel(model, CrossEntropyOnLogits(model.config), layers_per_cell=1, chunk_size=cs)
+            gm.train()
+            loss = gm(ids, tg)
+            loss.backward()
+            losses.append(float(loss))
+            grads.append({n: p.grad.detach().clone() for n, p in model.named_parameters() if p.grad is not None})
+        tol = (3e-2 if cuda else 1e-4) if exact else 5e-2
+        assert abs(losses[0] - losses[1]) < tol * max(1.0, abs(losses[0])), (name, losses)
+        if exact:
+            want = shard_state_dict(grads[0], cfg, world, rank)
+            for n, g in grads[1].items():
+                w = want[n].float()
+                err = (g.float() - w).norm() / w.norm().clamp(min=1e-6)
+                assert err < (8e-2 if cuda else 1e-3), f"{name} {n}: relative gradient error {err}"
+    if cuda:
+        from keys_values_b200.ops import cuda as cu
+
+        torch.cuda.synchronize(dev)
+        cu.check_status(dev)
+    comm.close()
+
+
 if __name__ == "__main__":
     main()

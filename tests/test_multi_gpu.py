@@ -54,6 +54,26 @@ def test_tp_sharded_model_gradients_on_cpu_ranks():
     _run("tp_gpt_grads", 2)
 
 
+def test_tp_long_context_training_step_on_cpu_ranks():
+    _run("tp_train", 2)
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tp_long_context_training_step_on_gpus():
+    _run("tp_train", 2)
+
+
+def test_tp_lora_gradients_on_cpu_ranks():
+    _run("tp_lora_grads", 2)
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tp_lora_gradients_on_gpus():
+    _run("tp_lora_grads", 2)
+
+
 @pytest.mark.gpu
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_tp_sharded_model_with_captured_decode_steps_on_gpus():
