@@ -49,9 +49,12 @@ def create_lora_model(
     yarn_rope: bool = True,
     seed: int = 0,
     config_overrides: Optional[Dict[str, Any]] = None,
+    tp_comm=None,
 ):
     """Random-init LoRA model on ``device`` (weights are loaded separately from a
-    ``lit_model.pth`` with :func:`keys_values_b200.finetune.utils.load_model_checkpoint`)."""
+    ``lit_model.pth`` with :func:`keys_values_b200.finetune.utils.load_model_checkpoint`). With ``tp_comm`` the
+    model is this rank's shard (:class:`keys_values_b200.parallel.tp.TPLoRAGPT`); the returned configuration is
+    the whole model's."""
     flags = {f"lora_{t}": True for t in lora_targets}
     over = dict(config_overrides or {})
     if n_layer is not None:
@@ -65,7 +68,13 @@ def create_lora_model(
     torch.set_default_dtype(dtype)
     try:
         with torch.device(device):
-            model = lora_mod.GPT(config, pos_encoding=pos)
+            if tp_comm is not None:
+                from keys_values_b200.parallel.tp import TPLoRAGPT, local_config
+
+                pos = position_encoding_factory(local_config(config, tp_comm.world), do_yarn=yarn_rope, device=device)
+                model = TPLoRAGPT(config, tp_comm, pos_encoding=pos)
+            else:
+                model = lora_mod.GPT(config, pos_encoding=pos)
     finally:
         torch.set_default_dtype(prev)
     model.apply(model._init_weights)
@@ -98,12 +107,37 @@ def build_lora_training_setup(
     head_model: Optional[HeadModel] = None,
     overlap_allreduce: bool = True,
     train_all_parameters: bool = False,
+    tp_size: int = 1,
 ) -> TrainingSetup:
     """``train_all_parameters=True`` turns the set-up into a full fine-tune: every weight of the
-    model (embeddings, norms, linears, head) is trainable, not only the LoRA factors."""
+    model (embeddings, norms, linears, head) is trainable, not only the LoRA factors.
+
+    ``tp_size > 1``: the ``world_size`` ranks form ``world_size / tp_size`` data-parallel replicas of a model that
+    is sharded over ``tp_size`` consecutive ranks (heads, KV heads and MLP columns; every rank keeps the caches and
+    the eviction state of its KV heads). Ranks of one replica must be fed the same batch; ``seed`` must then be
+    the same on all ranks (replicated parameters are initialised from it)."""
+    tp_comm, dp_group, dp_world, dp_rank = None, None, world_size, rank
+    if tp_size > 1:
+        import torch.distributed as dist
+
+        from keys_values_b200.parallel.tp import TPComm
+
+        if world_size % tp_size:
+            raise ValueError(f"world_size = {world_size} must be a multiple of tp_size = {tp_size}")
+        dp_world, dp_rank, tp_rank = world_size // tp_size, rank // tp_size, rank % tp_size
+        tp_group = None
+        for k in range(dp_world):  # every rank creates every group, in the same order
+            grp = dist.new_group(list(range(k * tp_size, (k + 1) * tp_size)))
+            if k == dp_rank:
+                tp_group = grp
+        for k in range(tp_size):
+            grp = dist.new_group(list(range(k, world_size, tp_size)))
+            if k == tp_rank:
+                dp_group = grp
+        tp_comm = TPComm(tp_size, tp_rank, device, group=tp_group, dtype=dtype)
     config, gpt = create_lora_model(
         model_name, device, dtype, lora_r=lora_r, lora_alpha=lora_alpha, lora_targets=lora_targets,
-        n_layer=n_layer, yarn_rope=yarn_rope, seed=seed,
+        n_layer=n_layer, yarn_rope=yarn_rope, seed=seed, tp_comm=tp_comm,
     )
     if train_all_parameters:
         for p in gpt.parameters():
@@ -120,10 +154,13 @@ def build_lora_training_setup(
     params = [p for p in gpt.parameters() if p.requires_grad] + [p for p in head.parameters() if p.requires_grad]
     optimizer = torch.optim.AdamW(params, lr=learning_rate, weight_decay=weight_decay, fused=torch.device(device).type == "cuda")
     setup = TrainingSetup(config, gpt, head, model, optimizer, world_size=world_size, rank=rank, max_norm=max_norm)
-    if world_size > 1:
+    if tp_comm is not None:
+        setup.extras.update(tp_comm=tp_comm, dp_group=dp_group, dp_world=dp_world, dp_rank=dp_rank)
+    if dp_world > 1:
         from keys_values_b200.parallel.dp import GradientReducer
 
-        setup.grad_reducer = GradientReducer(params, world_size=world_size, rank=rank, device=device, overlap=overlap_allreduce)
+        setup.grad_reducer = GradientReducer(params, world_size=dp_world, rank=dp_rank, device=device, overlap=overlap_allreduce,
+                                             group=dp_group)
         if overlap_allreduce:
             model.row_done_hook = setup.grad_reducer.row_done_hook(gpt)
     return setup
@@ -188,8 +225,13 @@ def training_step(setup: TrainingSetup, input_ids: torch.Tensor, targets: torch.
         setup.grad_reducer.finish_step()
     check_native_status(setup, input_ids.device)
     if setup.max_norm is not None:
-        params = [p for g in setup.optimizer.param_groups for p in g["params"] if p.grad is not None]
-        torch.nn.utils.clip_grad_norm_(params, setup.max_norm)
+        if setup.extras.get("tp_comm") is not None:
+            from keys_values_b200.parallel.tp import clip_grad_norm_sharded
+
+            clip_grad_norm_sharded(setup.gpt_model, setup.max_norm)
+        else:
+            params = [p for g in setup.optimizer.param_groups for p in g["params"] if p.grad is not None]
+            torch.nn.utils.clip_grad_norm_(params, setup.max_norm)
     setup.optimizer.step()
     if setup.scheduler is not None:
         setup.scheduler.step()

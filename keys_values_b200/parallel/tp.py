@@ -592,6 +592,33 @@ def unshard_state_dict(shards, config):
     return out
 
 
+def clip_grad_norm_sharded(model, max_norm: float) -> torch.Tensor:
+    """Gradient clipping for a shard: the norm is that of the whole model (squares of sharded tensors summed over
+    the ranks, replicated tensors counted once), so every rank scales by the same factor and replicated
+    parameters stay equal. Returns the norm."""
+    comm = model.tp_comm
+    cfg = model.full_config
+    sq_sharded = torch.zeros((), dtype=torch.float32, device=comm.device)
+    sq_rep = torch.zeros((), dtype=torch.float32, device=comm.device)
+    grads = []
+    for name, p in model.named_parameters():
+        if p.grad is None:
+            continue
+        grads.append(p.grad)
+        sq = p.grad.float().pow(2).sum()
+        if _shard_rule(name, cfg)[0] in ("rep", "rank0"):
+            sq_rep = sq_rep + sq
+        else:
+            sq_sharded = sq_sharded + sq
+    if comm.world > 1:
+        dist.all_reduce(sq_sharded, op=dist.ReduceOp.SUM, group=comm.group)  # a scalar: library plumbing
+    norm = (sq_sharded + sq_rep).sqrt()
+    factor = (max_norm / (norm + 1e-6)).clamp(max=1.0)
+    for g in grads:
+        g.mul_(factor.to(g.dtype))
+    return norm
+
+
 def load_sharded_checkpoint(model, checkpoint_dir) -> None:
     """Fill a :class:`TPGPT` with its shard of ``checkpoint_dir/lit_model.pth`` (the file of the whole model,
     memory-mapped: a rank reads only the slices it keeps)."""
@@ -754,6 +781,11 @@ def _tp_classes(lora: bool):
                         setattr(holder, name, RowParallelLinear.from_linear(mod, comm))
                     else:  # a LoRA linear: W holds this rank's columns, A its columns too, B is replicated
                         mod.register_forward_hook(self._sum_output_hook)
+                    bias = getattr(getattr(holder, name), "bias", None)
+                    if bias is not None and comm.rank != 0:
+                        # the sum over ranks must add the bias once: rank 0 owns it, the others hold a frozen zero
+                        bias.data.zero_()
+                        bias.requires_grad_(False)
                 # the inputs of the column-parallel linears (after the norms; the residual path is replicated)
                 block.attn.register_forward_pre_hook(self._shard_input_hook)
                 block.mlp.register_forward_pre_hook(self._shard_input_hook)

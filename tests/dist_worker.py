@@ -6,6 +6,7 @@ single-process result or with NCCL, and prints ``OK`` on success.
 """
 import os
 import sys
+import zlib
 from pathlib import Path
 
 sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
@@ -400,6 +401,77 @@ def case_tp_train(rank, world, dev):
         torch.cuda.synchronize(dev)
         cu.check_status(dev)
     comm.close()
+
+
+def case_dp_tp_train(rank, world, dev):
+    """Data parallel x tensor parallel (world 4 = 2 replicas x 2 shards): after the step's reductions every rank
+    holds its shard of the MEAN over the replicas of the whole model's gradients; one optimizer step with
+    clipping keeps replicated parameters equal on all ranks."""
+    from keys_values_b200.finetune.engine import build_lora_training_setup, training_step
+    from keys_values_b200.kvcache.factory import KVCacheFactory
+    from keys_values_b200.kvcache.gradient.main import LongContextGradientModel
+    from keys_values_b200.models import lora as lora_mod
+    from keys_values_b200.models.head_model import CrossEntropyOnLogits
+    from keys_values_b200.models.pos_encoding import position_encoding_factory
+    from keys_values_b200.parallel.tp import shard_state_dict, unshard_state_dict
+
+    cuda = dev.type == "cuda"
+    dtype = torch.bfloat16 if cuda else torch.float32
+    tp = 2
+    dp_rank, tp_rank = rank // tp, rank % tp
+    T, C, cs = (512, 128, 64) if cuda else (192, 64, 32)
+    setup = build_lora_training_setup("tiny-qwen3", dev, dtype, cache_name="lastrec-default", cache_length=C, chunk_size=cs, lora_r=4,
+                                      lora_alpha=8, micro_batch_size=1, world_size=world, rank=rank, yarn_rope=False, seed=11,
+                                      max_norm=0.5, tp_size=tp, overlap_allreduce=cuda)
+    cfg = setup.config
+    with torch.no_grad():
+        for n, p in setup.gpt_model.named_parameters():
+            if "lora_B" in n:  # same values on every rank: seeded by name
+                g = torch.Generator().manual_seed(zlib.crc32(n.encode()) % 10_000)
+                p.copy_((torch.randn(p.shape, generator=g) * 0.05).to(p))
+    # the whole model, rebuilt on every rank from the shards of replica 0
+    shards = [None] * world
+    dist.all_gather_object(shards, {k: v.detach().cpu() for k, v in setup.gpt_model.state_dict().items()})
+    whole_sd = unshard_state_dict(shards[:tp], cfg)
+    whole = lora_mod.GPT(cfg, pos_encoding=position_encoding_factory(cfg, do_yarn=False, device=dev))
+    whole.load_state_dict(whole_sd)
+    whole = whole.to(device=dev, dtype=dtype)
+    lora_mod.mark_only_lora_as_trainable(whole)
+    gen = torch.Generator().manual_seed(21)
+    data = [(torch.randint(0, cfg.vocab_size, (1, T), generator=gen), torch.randint(0, cfg.vocab_size, (1, cs), generator=gen)) for _ in range(world // tp)]
+    mean_grads = None
+    for ids, tg in data:
+        for p in whole.parameters():
+            p.grad = None
+        whole.assign_kv_caches(KVCacheFactory.create(whole, "lastrec-default", 1, C, dtype=dtype, device=dev))
+        gm = LongContextGradientModel(whole, CrossEntropyOnLogits(cfg), layers_per_cell=1, chunk_size=cs)
+        gm.train()
+        gm(ids.to(dev), tg.to(dev)).backward()
+        gr = {n: p.grad.detach().float() / len(data) for n, p in whole.named_parameters() if p.grad is not None}
+        mean_grads = gr if mean_grads is None else {n: mean_grads[n] + g for n, g in gr.items()}
+    want = shard_state_dict(mean_grads, cfg, tp, tp_rank)
+    # this rank's step on the batch of its replica, without the optimizer: forward, backward, reductions
+    ids, tg = data[dp_rank]
+    setup.optimizer.zero_grad(set_to_none=False)
+    setup.grad_reducer.begin_step()
+    setup.model(ids.to(dev), tg.to(dev)).backward()
+    setup.grad_reducer.finish_step()
+    if cuda:
+        torch.cuda.synchronize(dev)
+    for n, p in setup.gpt_model.named_parameters():
+        if p.requires_grad:
+            w = want[n].to(dev)
+            err = (p.grad.float() - w).norm() / w.norm().clamp(min=1e-6)
+            assert err < (0.1 if cuda else 1e-3), f"{n}: relative gradient error {err}"
+    # a full step (with clipping by the whole model's norm): replicated tensors stay equal everywhere
+    loss = training_step(setup, ids.to(dev), tg.to(dev))
+    assert torch.isfinite(loss)
+    rep = torch.cat([p.detach().float().reshape(-1) for n, p in setup.gpt_model.named_parameters() if n.endswith("attn.qkv.lora_A")])
+    everyone = [torch.empty_like(rep) for _ in range(world)]
+    dist.all_gather(everyone, rep)
+    for other in everyone:
+        torch.testing.assert_close(other, rep, atol=0 if not cuda else 1e-6, rtol=0)
+    setup.extras["tp_comm"].close()
 
 
 if __name__ == "__main__":

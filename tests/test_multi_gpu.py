@@ -64,6 +64,16 @@ def test_tp_long_context_training_step_on_gpus():
     _run("tp_train", 2)
 
 
+def test_dp_x_tp_training_step_on_cpu_ranks():
+    _run("dp_tp_train", 4)
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
+def test_dp_x_tp_training_step_on_gpus():
+    _run("dp_tp_train", 4)
+
+
 def test_tp_lora_gradients_on_cpu_ranks():
     _run("tp_lora_grads", 2)
 
