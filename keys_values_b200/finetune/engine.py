@@ -108,6 +108,7 @@ def build_lora_training_setup(
     overlap_allreduce: bool = True,
     train_all_parameters: bool = False,
     tp_size: int = 1,
+    kv_cpu_offload: bool = False,
 ) -> TrainingSetup:
     """``train_all_parameters=True`` turns the set-up into a full fine-tune: every weight of the
     model (embeddings, norms, linears, head) is trainable, not only the LoRA factors.
@@ -146,7 +147,12 @@ def build_lora_training_setup(
     cname, _ = split_name(cache_name)
     if "h2o" in cname and "max_chunk_size" not in ck:
         ck["max_chunk_size"] = chunk_size
-    caches = KVCacheFactory.create(gpt, cache_name, micro_batch_size, cache_length, device=device, dtype=dtype, cache_kwargs=ck)
+    if kv_cpu_offload:  # quantized storage of all layers in pinned host memory, one layer at a time on the device
+        caches, offloader = KVCacheFactory.create_cpu_offloading(gpt, cache_name, micro_batch_size, cache_length, device=device, dtype=dtype,
+                                                                 cache_kwargs=ck)
+        gpt._kv_offloader = offloader
+    else:
+        caches = KVCacheFactory.create(gpt, cache_name, micro_batch_size, cache_length, device=device, dtype=dtype, cache_kwargs=ck)
     gpt.assign_kv_caches(caches)
     head = head_model if head_model is not None else CrossEntropyOnLogits(config)
     model = LongContextGradientModel(gpt, head, layers_per_cell=layers_per_cell, chunk_size=chunk_size, **(grad_kwargs or {}))

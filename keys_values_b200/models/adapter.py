@@ -26,22 +26,28 @@ class CausalSelfAttention(base.CausalSelfAttention):
             self.adapter_wte = nn.Embedding(config.adapter_prompt_length, config.n_embd)
             self.gating_factor = nn.Parameter(torch.zeros(1, 1, config.n_head, 1))
 
-    def forward(self, x, token_idx, mha, chunk_sizes=None):
-        y = super().forward(x, token_idx, mha, chunk_sizes)
-        if self.block_idx < self.config.adapter_start_layer:
-            return y
+    def attend(self, qkv, token_idx, mha, chunk_sizes=None):
+        """Attention over the sequence plus, from ``adapter_start_layer`` on, the gated attention of the same
+        queries (after QK norm and RoPE) over the learnable prefix: ``y + g_h · softmax(q k_p^T / sqrt(D)) v_p`` per
+        head, added BEFORE the output projection (one projection, one bias). The prefix keys and values are the
+        K and V parts of ``qkv(prefix)``, without position encoding."""
         c = self.config
-        B, T, _ = x.shape
+        use_prefix = self.block_idx >= c.adapter_start_layer
+        if use_prefix:
+            input_pos = 0 if self.kv_cache is None else self.kv_cache.input_pos  # before the cache moves on
+            q, _, _ = self._split_norm_rope(qkv, mha, input_pos)  # (B, H, T, D)
+        y = super().attend(qkv, token_idx, mha, chunk_sizes)
+        if not use_prefix:
+            return y
+        B, T, _ = qkv.shape
         H, G, D = c.n_head, c.n_query_groups, c.head_size
-        prefix = self.adapter_wte.weight.unsqueeze(0)
-        qkv_p = self.qkv(prefix)
-        _, k_p, v_p = qkv_p.split((H * D, G * D, G * D), dim=-1)
-        q = self.qkv(x)[..., : H * D].view(B, T, H, D)
-        k_p = k_p.view(1, -1, G, D).repeat_interleave(H // G, dim=2)
-        v_p = v_p.view(1, -1, G, D).repeat_interleave(H // G, dim=2)
-        att = torch.einsum("bthd,xphd->bthp", q, k_p) / math.sqrt(D)
-        ay = torch.einsum("bthp,xphd->bthd", att.softmax(-1), v_p)
-        return y + self.proj((self.gating_factor * ay).reshape(B, T, H * D))
+        prefix = self.adapter_wte.weight.unsqueeze(0).to(qkv.dtype)
+        _, k_p, v_p = self.qkv(prefix).split((H * D, G * D, G * D), dim=-1)
+        k_p = k_p.view(-1, G, D).repeat_interleave(H // G, dim=1)  # (P, H, D)
+        v_p = v_p.view(-1, G, D).repeat_interleave(H // G, dim=1)
+        att = torch.einsum("bhtd,phd->bhtp", q.float(), k_p.float()) / math.sqrt(D)
+        ay = torch.einsum("bhtp,phd->bthd", att.softmax(-1), v_p.float())  # (B, T, H, D)
+        return y + (self.gating_factor.float() * ay).reshape(B, T, H * D).to(y.dtype)
 
 
 class Block(base.Block):

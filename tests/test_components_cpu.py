@@ -143,3 +143,44 @@ def test_adapters_train_only_their_own_parameters():
     m2 = adapter_v2.GPT(cfg2)
     assert any(isinstance(mod, adapter_v2.AdapterV2Linear) for mod in m2.modules())
     assert m2(ids).shape == (2, 12, cfg2.padded_vocab_size)
+
+
+def test_adapter_v1_prefix_attention_matches_a_plain_restatement():
+    """Gated prefix attention as LitGPT defines it: queries after QK norm and RoPE, prefix keys / values from
+    ``qkv(prefix)`` without position encoding, per-head gate, added before the single output projection."""
+    import math
+
+    torch.manual_seed(0)
+    cfg = adapter.Config.from_name("tiny-qwen3", adapter_prompt_length=5, adapter_start_layer=1, bias=True)
+    m = adapter.GPT(cfg)
+    m.apply(m._init_weights)
+    with torch.no_grad():
+        for blk in m.transformer.h:
+            torch.nn.init.normal_(blk.attn.proj.bias, std=0.1)
+            if hasattr(blk.attn, "gating_factor"):
+                torch.nn.init.normal_(blk.attn.gating_factor, std=0.5)
+    ids = torch.randint(0, cfg.vocab_size, (2, 24))
+    H, G, D = cfg.n_head, cfg.n_query_groups, cfg.head_size
+
+    def plain_attention(attn, x):
+        B, T, _ = x.shape
+        q, k, v = attn._split_norm_rope(attn.qkv(x), m.mha, 0)  # (B, H|G, T, D), after norm and RoPE
+        kr, vr = k.repeat_interleave(H // G, dim=1), v.repeat_interleave(H // G, dim=1)
+        causal = torch.ones(T, T, dtype=torch.bool).tril()
+        att = (q @ kr.transpose(-1, -2)) / math.sqrt(D)
+        y = att.masked_fill(~causal, float("-inf")).softmax(-1) @ vr  # (B, H, T, D)
+        if attn.block_idx >= cfg.adapter_start_layer:
+            _, ak, av = attn.qkv(attn.adapter_wte.weight.unsqueeze(0)).split((H * D, G * D, G * D), dim=-1)
+            ak = ak.view(1, -1, G, D).transpose(1, 2).repeat_interleave(H // G, dim=1)  # (1, H, P, D)
+            av = av.view(1, -1, G, D).transpose(1, 2).repeat_interleave(H // G, dim=1)
+            ay = ((q @ ak.transpose(-1, -2)) / math.sqrt(D)).softmax(-1) @ av
+            y = y + attn.gating_factor.view(1, H, 1, 1) * ay
+        return attn.proj(y.transpose(1, 2).reshape(B, T, H * D))
+
+    with torch.no_grad():
+        x = m.embed(ids)
+        for blk in m.transformer.h:
+            got = blk.attn(blk.norm_1(x), ids, m.mha)
+            want = plain_attention(blk.attn, blk.norm_1(x))
+            torch.testing.assert_close(got, want, atol=2e-5, rtol=1e-4)
+            x = blk(x, ids, m.mha)
