@@ -379,3 +379,34 @@ def test_evaluation_sampler_restarts_after_an_early_stop():
     head = [b for _, b in zip(range(2), train)]
     rest = list(train)
     assert len(rest) == 4 and not set(map(tuple, head)) & set(map(tuple, rest))  # a training epoch goes on where it stopped
+
+
+def test_result_collection_and_log_scraping(tmp_path):
+    from keys_values_b200.tools import collect_eval_results as cer
+    from keys_values_b200.tools import extract_times_from_logs as etl
+
+    out = tmp_path / "run1"
+    for task, losses in (("h2o-default__step-000100", (2.0, 4.0)), ("h2o-default__final", (1.0, 3.0))):
+        d = out / task / "eval"
+        d.mkdir(parents=True)
+        for b, loss in enumerate(losses):
+            with open(d / f"eval_metrics_{b}.csv", "w") as fp:
+                fp.write("task,batch,row,loss,num_tokens,time,sub_exact_match\n")
+                fp.write(f"{task},{b},0,{loss},{100 * (b + 1)},0.5,{float(b)}\n")
+        (d / "batch_7.lock").write_text("123")
+    rows = cer.collect(out, expected_batches=3)
+    assert [r["checkpoint"] for r in rows] == ["step-000100", "final"]
+    assert rows[0]["mean_loss"] == pytest.approx((2.0 * 100 + 4.0 * 200) / 300) and rows[0]["sub_exact_match"] == 0.5
+    assert rows[0]["pending_batches"] == 1 and rows[0]["complete"] is False and rows[0]["batches"] == 2
+    assert cer.best_checkpoint(rows)["run1/h2o-default"]["checkpoint"] == "final"
+    assert "| run1 | h2o-default | final |" in cer.to_markdown(rows)
+    logs = tmp_path / "logs"
+    logs.mkdir()
+    for r, extra in ((0, 0.0), (1, 0.4)):
+        (logs / f"gpu{r}.log").write_text("\n".join(
+            f"step {k}/3 | loss {3.0 - 0.1 * k:.3f} | {10.0 + extra + k:.2f} s | {1000.0:.1f} tok/s" for k in (1, 2, 3))
+            + "\nvalidation: {'val_loss': 2.5, 'val_time': 12.0}\npeak memory 84.6 GB\n")
+    rec = etl.load(logs)
+    assert [s["iter_time"] for s in rec["train"]] == [11.4, 12.4, 13.4] and rec["train"][0]["tokens_per_sec"] == 2000.0
+    assert rec["val"][0]["after_step"] == 3 and max(rec["peak_memory_gb"]) == 84.6
+    assert etl.summarize(rec["train"], skip=1)["median_s"] == pytest.approx(12.9)
