@@ -43,7 +43,7 @@ def _cuda():
 
 
 def test_attention_backward_stays_inside_its_gradient_buffers():
-    B, H, G, T, L, D = 1, 6, 2, 77, 333, 128
+    B, H, G, T, L, D = 1, 8, 2, 77, 333, 128
     g = Guarded()
     q = torch.randn(B, H, T, D, device=DEV, dtype=torch.bfloat16)
     k = torch.randn(B, G, L, D, device=DEV, dtype=torch.bfloat16)
