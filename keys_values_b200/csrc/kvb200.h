@@ -126,6 +126,14 @@ int kvb_oneshot_allreduce(void* const* slots, void* const* flags, int rank, int 
 #define KVB_ONESHOT_MAX_CTAS 16
 #define KVB_COMM_MAX_RANKS 16
 
+// ---- host_pool.cpp: pinned host memory pool (one slab, first-fit ranges of 256-byte granularity) and async copies
+int kvb_host_pool_create(void** pool_out, long long bytes, int pinned);
+int kvb_host_pool_destroy(void* pool);
+int kvb_host_pool_alloc(void* pool, long long bytes, void** ptr_out);  // KVB_ERR_TOO_LARGE: no free range fits
+int kvb_host_pool_free(void* pool, void* ptr);
+int kvb_host_pool_stats(void* pool, long long* out6);  // capacity, in use, peak, largest free range, allocations, failures
+int kvb_copy_async(void* dst, const void* src, long long bytes, int kind, void* stream);  // kind 1: H2D, 2: D2H
+
 
 // ---- gemm_sm100.cu: GEMM fused with a collective over peer memory (tensor parallelism)
 int kvb_gemm_reduce_scatter(const void* A, const void* B, void* out, const void* residual, void* const* recv_bufs,

@@ -50,7 +50,12 @@ def to_host_async(t: torch.Tensor, pin_memory: bool) -> Tuple[torch.Tensor, Any]
     if t.device.type != "cuda":
         return t.clone(), None
     side = _SideStream.get(t.device)
-    host = torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=pin_memory)
+    if pin_memory:
+        from keys_values_b200.utils.host_pool import pinned_empty
+
+        host = pinned_empty(t.shape, t.dtype)  # a range of the pinned pool: no cudaHostAlloc per checkpoint
+    else:
+        host = torch.empty(t.shape, dtype=t.dtype, device="cpu")
     side.wait_stream(torch.cuda.current_stream(t.device))
     with torch.cuda.stream(side):
         host.copy_(t, non_blocking=True)

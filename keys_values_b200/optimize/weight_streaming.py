@@ -176,7 +176,9 @@ class WeightStreamer:
                 done.record(torch.cuda.current_stream(self.device))
                 with torch.cuda.stream(self.copy_stream):
                     self.copy_stream.wait_event(done)
-                    staged = torch.empty(lay.numel, dtype=lay.dtype, pin_memory=True)
+                    from keys_values_b200.utils.host_pool import pinned_empty
+
+                    staged = pinned_empty((lay.numel,), lay.dtype)  # from the pinned pool: no cudaHostAlloc per block
                     staged.copy_(g, non_blocking=True)
                     ev = torch.cuda.Event()
                     ev.record(self.copy_stream)

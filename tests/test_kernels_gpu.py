@@ -266,7 +266,8 @@ def _rel_err(a, b):
 
 
 @pytest.mark.parametrize("B,H,G,T,L,mode", [(1, 4, 1, 32, 128, "arange"), (1, 8, 2, 256, 256, "prefill"), (2, 8, 2, 100, 1000, "perm"),
-                                             (1, 32, 8, 256, 2048, "perm"), (1, 4, 4, 64, 300, "perm")])
+                                             (1, 32, 8, 256, 2048, "perm"), (1, 4, 4, 64, 300, "perm"),
+                                             (1, 10, 2, 100, 700, "perm"), (2, 7, 1, 64, 300, "arange")])  # group sizes 5 and 7: padded heads
 def test_sdpa_bwd(B, H, G, T, L, mode):
     if mode == "prefill":
         mode = "arange"
