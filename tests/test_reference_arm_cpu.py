@@ -36,3 +36,25 @@ def test_reference_arm_reports_unavailable_without_gpu():
     assert r.returncode == 0
     out = json.loads([ln for ln in r.stdout.splitlines() if ln.startswith("{")][-1])
     assert out["impl"] == "reference" and "unavailable" in out
+
+
+@pytest.mark.skipif(not (ROOT / "baseline" / "_ref" / "keys_values").is_dir(), reason="reference not installed under baseline/_ref")
+def test_reference_arm_runs_on_two_ranks():
+    """The launch the benchmark driver uses for N > 1 (``torch.distributed.run``), on two CPU ranks over gloo: the
+    reference's gradient all-reduce through the stand-in Fabric, one JSON line from rank 0."""
+    import socket
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), str(ROOT / "bench.py"), "--impl", "reference", "--ref-allow-cpu", "--gpus", "2", "--model",
+           "tiny-qwen3", "--seq-len", "384", "--cache-length", "128", "--chunk-size", "64", "--num-targets", "64", "--steps", "1",
+           "--warmup", "1"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, cwd=ROOT, env={**__import__("os").environ, "CUDA_VISIBLE_DEVICES": ""})
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    lines = [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
+    assert len(lines) == 1, lines
+    out = json.loads(lines[0])
+    assert out["impl"] == "reference" and "unavailable" not in out, out
+    assert out["n_gpus"] == 2 and out["value"] > 0
