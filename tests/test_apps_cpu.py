@@ -410,3 +410,31 @@ def test_result_collection_and_log_scraping(tmp_path):
     assert [s["iter_time"] for s in rec["train"]] == [11.4, 12.4, 13.4] and rec["train"][0]["tokens_per_sec"] == 2000.0
     assert rec["val"][0]["after_step"] == 3 and max(rec["peak_memory_gb"]) == 84.6
     assert etl.summarize(rec["train"], skip=1)["median_s"] == pytest.approx(12.9)
+
+
+def test_per_weight_size_log_and_plot(tmp_path):
+    from keys_values_b200.models import lora as lora_mod
+    from keys_values_b200.tools import plot_size_log
+    from keys_values_b200.tools.size_log import PerWeightSizeLog, SizeLogMapper
+
+    torch.manual_seed(0)
+    cfg = lora_mod.Config.from_name("tiny-gpt", lora_r=2, lora_query=True, lora_value=True)
+    m = lora_mod.GPT(cfg)
+    lora_mod.mark_only_lora_as_trainable(m)
+    mapper = SizeLogMapper([(r"transformer\.h\.(\d+)\.attn\.qkv\.lora_[AB]", "layer {0} qkv LoRA")])
+    log = PerWeightSizeLog(m, mapper)
+    opt = torch.optim.SGD([p for p in m.parameters() if p.requires_grad], lr=0.5)
+    for step in range(4):
+        loss = m(torch.randint(0, 512, (2, 16))).float().pow(2).mean()
+        opt.zero_grad()
+        loss.backward()
+        log.log(step)
+        opt.step()
+    log.write(tmp_path)
+    assert mapper.labels == ["layer 0 qkv LoRA", "layer 1 qkv LoRA"]  # A and B of a layer pooled into one row
+    series, names = plot_size_log.load_tables(tmp_path, "gradients")
+    assert len(series[(0, "max")]) == 4 and names[1] == "layer 1 qkv LoRA"
+    assert all(a[1] <= b[1] for a, b in zip(series[(0, "0.5")], series[(0, "max")]))
+    plot_size_log.main([str(tmp_path), "--table", "gradients", "--top_n", "2", "--log"])
+    svg = (tmp_path / "size_gradients.svg").read_text()
+    assert svg.count("<polyline") == 2 * 3 and "layer 0 qkv LoRA" in svg
