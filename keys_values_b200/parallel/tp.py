@@ -592,6 +592,23 @@ def unshard_state_dict(shards, config):
     return out
 
 
+def gather_whole_state_dict(model, only_trainable: bool = False, dst: int = 0):
+    """The state dict of the whole model, put together from the shards of the ranks of the model's tensor-parallel
+    group, on the group's rank ``dst`` (``None`` elsewhere): what a checkpoint of a run under tensor parallelism
+    stores, readable by a run on any number of GPUs. ``only_trainable`` keeps the tensors that are being trained
+    (LoRA factors), as a LoRA checkpoint does. The tensors travel as host copies through the process group."""
+    comm = model.tp_comm
+    trainable = {n for n, p in model.named_parameters() if p.requires_grad}
+    mine = {k: v.detach().cpu() for k, v in model.state_dict().items() if not only_trainable or k in trainable}
+    if comm.world == 1:
+        return mine
+    shards = [None] * comm.world if comm.rank == dst else None
+    dist.gather_object(mine, shards, dst=dist.get_global_rank(comm.group, dst) if comm.group is not None else dst, group=comm.group)
+    if comm.rank != dst:
+        return None
+    return unshard_state_dict(shards, model.full_config)
+
+
 def clip_grad_norm_sharded(model, max_norm: float) -> torch.Tensor:
     """Gradient clipping for a shard: the norm is that of the whole model (squares of sharded tensors summed over
     the ranks, replicated tensors counted once), so every rank scales by the same factor and replicated

@@ -342,6 +342,17 @@ def case_tp_lora_grads(rank, world, dev):
         assert err < tol, f"{n}: relative gradient error {err}"
         n_checked += 1
     assert n_checked >= 2 * 10  # A and B of qkv, proj, fc_1, fc_2, mlp.proj in both layers
+    # a checkpoint written under tensor parallelism is the whole model's
+    from keys_values_b200.parallel.tp import gather_whole_state_dict
+
+    whole = gather_whole_state_dict(shard, only_trainable=True)
+    if rank == 0:
+        ref_sd = {k: v.cpu() for k, v in full.state_dict().items() if "lora_" in k}
+        assert set(whole) == set(ref_sd)
+        for k, v in ref_sd.items():
+            assert torch.equal(whole[k], v), k
+    else:
+        assert whole is None
     comm.close()
 
 
