@@ -68,8 +68,11 @@ def setup(
     model_name: Optional[str] = None,
     profile_grad_times: int = 0,
     record_gpu_memory_snapshots: Optional[int] = None,
+    tp: int = 1,
 ) -> None:
     """Entry point of ``finetune_long_full`` (and, with ``lora`` given, ``finetune_long_lora``).
+    ``tp > 1``: the ``devices`` ranks form ``devices / tp`` data-parallel replicas of a model sharded over ``tp``
+    consecutive ranks (heads, KV heads, MLP columns); checkpoints are written for the whole model.
     ``checkpoint_dir`` holds ``lit_model.pth`` and ``model_config.yaml``; with ``model_name`` the
     architecture is taken from the registry and weights are initialised randomly if no
     ``lit_model.pth`` is present."""
@@ -81,17 +84,22 @@ def setup(
     split_name(kv_cache.name)  # validates the cache name
     if devices < 1:
         raise ValueError("devices must be >= 1")
+    if tp < 1 or devices % tp:
+        raise ValueError(f"devices = {devices} must be a multiple of tp = {tp}")
+    if tp > 1 and (grad.offload_weights or optimizer.host_offload):
+        raise ValueError("tensor parallelism does not combine with host-resident weights or optimizer state")
     precision = precision or get_default_supported_precision(training=True)
     hparams = dict(checkpoint_dir=str(checkpoint_dir), out_dir=str(out_dir), precision=precision, devices=devices, train=train, eval=eval,
                    optimizer=optimizer, kv_cache=kv_cache, grad=grad, sdpa=sdpa, lora=lora, head_model=head_model, seed=seed,
-                   yarn_rope=yarn_rope, model_name=model_name)
-    launch(main, devices, checkpoint_dir=checkpoint_dir, out_dir=out_dir, precision=precision, resume=resume, data=data, train=train,
+                   yarn_rope=yarn_rope, model_name=model_name, tp=tp)
+    launch(main, devices, tp=tp, checkpoint_dir=checkpoint_dir, out_dir=out_dir, precision=precision, resume=resume, data=data, train=train,
            eval=eval, optimizer=optimizer, kv_cache=kv_cache, grad=grad, sdpa=sdpa, lora=lora, head_model_name=head_model,
            head_model_kwargs=head_model_kwargs or {}, logger_name=logger_name, seed=seed, yarn_rope=yarn_rope, model_name=model_name,
            hparams=hparams, profile_grad_times=profile_grad_times, record_gpu_memory_snapshots=record_gpu_memory_snapshots)
 
 
-def create_gpt_model(checkpoint_dir: Path, model_name: Optional[str], lora: Optional[LoRAArgs], device, dtype, yarn_rope: bool):
+def create_gpt_model(checkpoint_dir: Path, model_name: Optional[str], lora: Optional[LoRAArgs], device, dtype, yarn_rope: bool, tp_comm=None):
+    """Returns ``(config of the whole model, model)``; with ``tp_comm`` the model is this rank's shard."""
     from keys_values_b200.models import lora as lora_mod
     from keys_values_b200.models.model import GPT
 
@@ -103,12 +111,18 @@ def create_gpt_model(checkpoint_dir: Path, model_name: Optional[str], lora: Opti
         config = cfg_cls.from_name(model_name, **kwargs)
     else:
         raise FileNotFoundError(f"{checkpoint_dir}/model_config.yaml not found and no model_name given")
-    pos = position_encoding_factory(config, do_yarn=yarn_rope, device=device)
     prev = torch.get_default_dtype()
     torch.set_default_dtype(dtype)
     try:
         with torch.device(device):
-            model = (lora_mod.GPT if lora is not None else GPT)(config, pos_encoding=pos)
+            if tp_comm is not None:
+                from keys_values_b200.parallel import tp as tp_mod
+
+                pos = position_encoding_factory(tp_mod.local_config(config, tp_comm.world), do_yarn=yarn_rope, device=device)
+                model = (tp_mod.TPLoRAGPT if lora is not None else tp_mod.TPGPT)(config, tp_comm, pos_encoding=pos)
+            else:
+                pos = position_encoding_factory(config, do_yarn=yarn_rope, device=device)
+                model = (lora_mod.GPT if lora is not None else GPT)(config, pos_encoding=pos)
     finally:
         torch.set_default_dtype(prev)
     model.apply(model._init_weights)
@@ -163,7 +177,7 @@ def apply_sdpa_args(sdpa: Optional[SDPAArgs], rank: int = 0) -> None:
 
 def main(rank: int, local_rank: int, world_size: int, *, checkpoint_dir, out_dir, precision, resume, data, train, eval, optimizer, kv_cache,
          grad, sdpa=None, lora, head_model_name, head_model_kwargs, logger_name, seed, yarn_rope, model_name, hparams, profile_grad_times,
-         record_gpu_memory_snapshots) -> None:
+         record_gpu_memory_snapshots, tp: int = 1) -> None:
     cuda = torch.cuda.is_available()
     device = torch.device("cuda", local_rank) if cuda else torch.device("cpu")
     if cuda:
@@ -175,7 +189,21 @@ def main(rank: int, local_rank: int, world_size: int, *, checkpoint_dir, out_dir
     if rank == 0:
         out_dir.mkdir(parents=True, exist_ok=True)
     logger = fu.choose_logger(logger_name, out_dir) if rank == 0 else None
-    config, gpt_model = create_gpt_model(checkpoint_dir, model_name, lora, device, dtype, yarn_rope)
+    # layout of the ranks: dp_world replicas of a model sharded over tp consecutive ranks
+    tp_comm, dp_group, dp_world, dp_rank = None, None, world_size, rank
+    if tp > 1:
+        from keys_values_b200.parallel.tp import TPComm
+
+        dp_world, dp_rank, tp_rank = world_size // tp, rank // tp, rank % tp
+        tp_group = None
+        for k in range(dp_world):  # every rank creates every group, in the same order
+            grp = dist.new_group(list(range(k * tp, (k + 1) * tp)))
+            tp_group = grp if k == dp_rank else tp_group
+        for k in range(tp):
+            grp = dist.new_group(list(range(k, world_size, tp)))
+            dp_group = grp if k == tp_rank else dp_group
+        tp_comm = TPComm(tp, tp_rank, device, group=tp_group, dtype=dtype)
+    config, gpt_model = create_gpt_model(checkpoint_dir, model_name, lora, device, dtype, yarn_rope, tp_comm=tp_comm)
     head_model = HeadModelFactory.create(head_model_name, config, **head_model_kwargs).to(device)
     resume_dir = find_resume_dir(out_dir, resume)
     fu.load_model_checkpoint(gpt_model, checkpoint_dir, resume_dir, head_model)
@@ -204,30 +232,31 @@ def main(rank: int, local_rank: int, world_size: int, *, checkpoint_dir, out_dir
         from keys_values_b200.data.module import SyntheticLongContext
 
         data = SyntheticLongContext(config.vocab_size, seq_lengths=(4 * kv_cache.cache_length,), num_targets=kv_cache.chunk_size)
-    data.connect(tokenizer=tokenizer, batch_size=train.micro_batch_size, max_seq_length=train.max_seq_length, num_devices=world_size, rank=rank)
+    # the ranks of a replica read the same batches
+    data.connect(tokenizer=tokenizer, batch_size=train.micro_batch_size, max_seq_length=train.max_seq_length, num_devices=dp_world, rank=dp_rank)
     if rank == 0:
         data.prepare_data()
     if world_size > 1:
         dist.barrier()
     data.setup()
     train_loader, val_loader = data.train_dataloader(), data.val_dataloader()
-    accum = train.gradient_accumulation_iters(world_size)
+    accum = train.gradient_accumulation_iters(dp_world)
     steps_per_epoch = max(1, len(train_loader) // accum)
     max_steps = train.max_steps or (train.epochs or 1) * steps_per_epoch
     warmup = min(max_steps, train.lr_warmup_steps or int((train.lr_warmup_fraction or 0.0) * max_steps))
     scheduler = fu.get_lr_scheduler(getattr(opt, "optimizer", opt), warmup_steps=warmup, max_steps=max_steps, min_lr=train.min_lr)
     state = TrainingStateVars()
     if resume_dir is not None:
-        st = restore_from_training_state(resume_dir, opt, scheduler, rank, world_size)
+        st = restore_from_training_state(resume_dir, opt, scheduler, rank, world_size, tp_rank=rank % tp if tp > 1 else None)
         state.iter_num, state.step_count = st["iter_num"], st["step_count"]
         if hasattr(train_loader, "load_state_dict"):
             train_loader.load_state_dict(st.get("iterator", {}))
     grad_reducer = None
-    if world_size > 1:
+    if dp_world > 1:
         from keys_values_b200.parallel.dp import GradientReducer
 
         resident = [p for p in params if p.device.type == device.type]  # streamed blocks reduce their own gradients
-        grad_reducer = GradientReducer(resident, world_size=world_size, rank=rank, device=device) if resident else None
+        grad_reducer = GradientReducer(resident, world_size=dp_world, rank=dp_rank, device=device, group=dp_group) if resident else None
         if grad_reducer is not None:
             model.row_done_hook = grad_reducer.row_done_hook(gpt_model)
     pad_id = getattr(tokenizer, "pad_id", None) or 0
@@ -235,10 +264,11 @@ def main(rank: int, local_rank: int, world_size: int, *, checkpoint_dir, out_dir
     fit(model=model, optimizer=opt, scheduler=scheduler, train_loader=train_loader, val_loader=val_loader, batch_transform=batch_transform,
         train=train, eval=eval, state=state, max_steps=max_steps, accum=accum, device=device, rank=rank, world_size=world_size,
         grad_reducer=grad_reducer, logger=logger, out_dir=out_dir, checkpoint_dir=Path(checkpoint_dir), lora=lora is not None,
-        hparams=hparams, profile_grad_times=profile_grad_times, record_gpu_memory_snapshots=record_gpu_memory_snapshots, tokenizer=tokenizer)
+        hparams=hparams, profile_grad_times=profile_grad_times, record_gpu_memory_snapshots=record_gpu_memory_snapshots, tokenizer=tokenizer,
+        dp_world=dp_world, tp=tp)
+    final = out_dir / "final"
+    fu.save_model_checkpoint(gpt_model, head_model, final, lora=lora is not None, rank=rank)  # a collective under tensor parallelism
     if rank == 0:
-        final = out_dir / "final"
-        fu.save_model_checkpoint(gpt_model, head_model, final, lora=lora is not None)
         fu.copy_config_files(Path(checkpoint_dir), final)
         config.save(final / "model_config.yaml")
         fu.save_hyperparameters(hparams, final)
@@ -303,10 +333,10 @@ def validate_and_all_reduce(model, val_loader, batch_transform, device, eval: Ev
 def save_checkpoint_regular(model: LongContextGradientModel, out_dir: Path, step: int, checkpoint_dir: Path, lora: bool, hparams, rank: int,
                             state: TrainingStateVars, intermed_save_num: Optional[int]) -> Path:
     step_dir = out_dir / f"step-{step:06d}"
+    fu.save_model_checkpoint(model.gpt_model, model.head_model, step_dir, lora=lora, rank=rank)  # a collective under tensor parallelism
     if rank == 0:
-        fu.save_model_checkpoint(model.gpt_model, model.head_model, step_dir, lora=lora)
         fu.copy_config_files(checkpoint_dir, step_dir)
-        model.gpt_model.config.save(step_dir / "model_config.yaml")
+        getattr(model.gpt_model, "full_config", model.gpt_model.config).save(step_dir / "model_config.yaml")
         fu.save_hyperparameters(hparams, step_dir)
         state.saved_dirs.append(str(step_dir))
         if intermed_save_num is not None:
@@ -319,12 +349,15 @@ def save_checkpoint_regular(model: LongContextGradientModel, out_dir: Path, step
 
 def fit(*, model, optimizer, scheduler, train_loader, val_loader, batch_transform, train: TrainArgs, eval: EvalArgs, state: TrainingStateVars,
         max_steps: int, accum: int, device, rank: int, world_size: int, grad_reducer, logger, out_dir: Path, checkpoint_dir: Path, lora: bool,
-        hparams, profile_grad_times: int = 0, record_gpu_memory_snapshots: Optional[int] = None, tokenizer=None) -> None:
+        hparams, profile_grad_times: int = 0, record_gpu_memory_snapshots: Optional[int] = None, tokenizer=None,
+        dp_world: Optional[int] = None, tp: int = 1) -> None:
+    """``world_size`` ranks in ``dp_world`` replicas (default: every rank is a replica) of ``tp`` shards each."""
     from keys_values_b200.utils.recovery import OOMRetry
 
-    ts_manager = TrainingStateManager(out_dir, rank, world_size)
+    dp_world = world_size if dp_world is None else dp_world
+    ts_manager = TrainingStateManager(out_dir, rank, world_size, tp_rank=rank % tp if tp > 1 else None)
     train_iter = CycleIterator(train_loader)
-    throughput = fu.ThroughputMonitor(world_size)
+    throughput = fu.ThroughputMonitor(dp_world)
     samples_seen = 0
 
     def free_after_oom() -> None:
@@ -415,7 +448,11 @@ def fit(*, model, optimizer, scheduler, train_loader, val_loader, batch_transfor
         if recorder is not None:
             recorder.stop()
         if train.max_norm is not None:
-            if hasattr(optimizer, "clip_grad_norm_"):  # gradients are clipped where the optimizer lives (host)
+            if tp > 1:  # the norm of the whole model: sharded tensors summed over the ranks, replicated ones counted once
+                from keys_values_b200.parallel.tp import clip_grad_norm_sharded
+
+                clip_grad_norm_sharded(model.gpt_model, train.max_norm)
+            elif hasattr(optimizer, "clip_grad_norm_"):  # gradients are clipped where the optimizer lives (host)
                 optimizer.clip_grad_norm_(train.max_norm)
             else:
                 torch.nn.utils.clip_grad_norm_([p for p in params if p.grad is not None], train.max_norm)
@@ -423,14 +460,14 @@ def fit(*, model, optimizer, scheduler, train_loader, val_loader, batch_transfor
         scheduler.step()
         state.step_count += 1
         step_loss = _all_reduce_mean(step_loss, world_size)
-        state.total_tokens += step_tokens * world_size
+        state.total_tokens += step_tokens * dp_world
         dt = time.perf_counter() - t0
         state.train_time += dt
         if rank == 0 and state.step_count % train.log_interval == 0:
             metrics = {"loss": float(step_loss), "iter": state.iter_num, "step": state.step_count, "epoch": train_iter.epoch,
-                       "iter_time": dt, "tokens": step_tokens * world_size, "total_tokens": state.total_tokens,
-                       "tokens_per_sec": step_tokens * world_size / dt, "learning_rate": scheduler.get_last_lr()[0]}
-            throughput.update(time=state.train_time, batches=state.iter_num, samples=samples_seen, lengths=state.total_tokens // world_size)
+                       "iter_time": dt, "tokens": step_tokens * dp_world, "total_tokens": state.total_tokens,
+                       "tokens_per_sec": step_tokens * dp_world / dt, "learning_rate": scheduler.get_last_lr()[0]}
+            throughput.update(time=state.train_time, batches=state.iter_num, samples=samples_seen, lengths=state.total_tokens // dp_world)
             metrics.update(throughput.compute())
             logger.log_dict(metrics, step=state.step_count)
             print(f"step {state.step_count}/{max_steps} | loss {metrics['loss']:.4f} | {dt:.1f} s | {metrics['tokens_per_sec']:.0f} tok/s")

@@ -49,15 +49,26 @@ def lora_state_dict(model: torch.nn.Module) -> Dict[str, torch.Tensor]:
 
 def save_model_checkpoint(gpt_model, head_model, out_dir: Path, lora: bool = False, rank: int = 0) -> None:
     """Rank 0 writes ``lit_model.lora.pth`` (LoRA tensors only) or ``lit_model.pth``, and
-    ``head_model.pth`` if the head has weights."""
+    ``head_model.pth`` if the head has weights. A tensor-parallel shard (``gpt_model.tp_comm``) makes this a
+    collective of its group: the whole model's tensors are put together first, so the file is the same as a
+    run on one GPU writes, and every rank must call."""
+    whole = None
+    if getattr(gpt_model, "tp_comm", None) is not None and gpt_model.tp_comm.world > 1:
+        from keys_values_b200.parallel.tp import gather_whole_state_dict
+
+        from keys_values_b200.models.lora import lora_filter
+
+        whole = gather_whole_state_dict(gpt_model, only_trainable=lora)  # LoRA runs move only the adapter tensors
+        if whole is not None and lora:
+            whole = {k: v for k, v in whole.items() if lora_filter(k, v)}
     if rank != 0:
         return
     out_dir = Path(out_dir)
     out_dir.mkdir(parents=True, exist_ok=True)
     if lora:
-        torch.save({"model": lora_state_dict(gpt_model)}, out_dir / LORA_WEIGHTS_FNAME)
+        torch.save({"model": whole if whole is not None else lora_state_dict(gpt_model)}, out_dir / LORA_WEIGHTS_FNAME)
     else:
-        torch.save({"model": gpt_model.state_dict()}, out_dir / LIT_MODEL_FNAME)
+        torch.save({"model": whole if whole is not None else gpt_model.state_dict()}, out_dir / LIT_MODEL_FNAME)
     if head_model is not None and any(True for _ in head_model.parameters()):
         torch.save({"model": head_model.state_dict()}, out_dir / HEAD_MODEL_FNAME)
 
@@ -73,6 +84,15 @@ def load_model_checkpoint(gpt_model, checkpoint_dir: Path, resume_dir: Optional[
     fine-tune saves all weights as ``lit_model.pth`` in its step folders: when resuming one,
     that file in ``resume_dir`` replaces the base weights."""
     checkpoint_dir = Path(checkpoint_dir)
+    comm = getattr(gpt_model, "tp_comm", None)
+    if comm is not None and comm.world > 1:
+        # a tensor-parallel shard keeps its slices of every tensor of the (memory-mapped) files of the whole model
+        from keys_values_b200.parallel.tp import shard_state_dict
+
+        def load(path):
+            return shard_state_dict(_load_sd(path), gpt_model.full_config, comm.world, comm.rank)
+    else:
+        load = _load_sd
     has_lora = any("lora_" in n for n, _ in gpt_model.named_parameters())
     base = checkpoint_dir / LIT_MODEL_FNAME
     if resume_dir is not None and not has_lora:
@@ -81,11 +101,11 @@ def load_model_checkpoint(gpt_model, checkpoint_dir: Path, resume_dir: Optional[
             raise FileNotFoundError(f"cannot resume a full fine-tune: {resumed} does not exist")
         base = resumed
     if base.is_file() and base.stat().st_size > 0:
-        gpt_model.load_state_dict(_load_sd(base), strict=(not has_lora) if strict is None else strict)
+        gpt_model.load_state_dict(load(base), strict=(not has_lora) if strict is None else strict)
     for d in ([Path(resume_dir)] if resume_dir is not None else []) + [checkpoint_dir]:
         for fname in (LORA_WEIGHTS_FNAME, LORA_WEIGHTS_FNAME_OLD):
             if has_lora and (d / fname).is_file():
-                gpt_model.load_state_dict(_load_sd(d / fname), strict=False)
+                gpt_model.load_state_dict(load(d / fname), strict=False)
                 break
         if head_model is not None and (d / HEAD_MODEL_FNAME).is_file():
             head_model.load_state_dict(_load_sd(d / HEAD_MODEL_FNAME))
