@@ -228,7 +228,7 @@ def run_inference(args) -> dict:
     cache_name = "h2o-torch-quantized4" if args.cache_name == "h2o-torch-quantized8" else args.cache_name
     cache_length = 8192 if args.cache_length == 16384 else args.cache_length
     chunk = 2048 if args.chunk_size == 1024 else args.chunk_size
-    r = decode_bench.run(model, args.batch, seq, args.decode, cache_name, cache_length, chunk, True, args.n_layer, True,
+    r = decode_bench.run(model, args.batch, seq, args.decode, cache_name, cache_length, chunk, True, args.n_layer, None,
                          repeats=max(1, args.steps))
     clocks = sampler.stop()
     if not r:

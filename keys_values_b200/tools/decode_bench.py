@@ -23,7 +23,7 @@ import torch
 
 def run(model_name: str = "Llama-3-8B", batch: int = 4, prompt: int = 65536, decode: int = 512, cache_name: str = "h2o-torch-quantized4",
         cache_length: int = 8192, chunk_size: int = 2048, use_graph: bool = True, n_layer: Optional[int] = None,
-        fused_prefill: bool = True, warmup_decode: int = 8, repeats: int = 1) -> dict:
+        fused_prefill: Optional[bool] = None, warmup_decode: int = 8, repeats: int = 1) -> dict:
     """One measurement; returns the result record on rank 0 and ``{}`` elsewhere. The process group is set up
     (and torn down) here when the environment names more than one rank."""
     import torch.distributed as dist
@@ -109,7 +109,7 @@ def run(model_name: str = "Llama-3-8B", batch: int = 4, prompt: int = 65536, dec
     result = {
         "bench": "chunked inference", "model": model_name + (f" (REDUCED to {n_layer} layers)" if n_layer else ""),
         "tp": world, "batch": batch, "prompt": prompt, "decode_steps": decode, "cache": cache_name, "cache_length": cache_length,
-        "chunk_size": chunk_size, "prefill_path": ("fused all-gather/GEMM/reduce-scatter" if fused_prefill else "all-reduce") if world > 1 else "single GPU",
+        "chunk_size": chunk_size, "prefill_path": ("fused all-gather/GEMM/reduce-scatter" if model.fused_prefill else "all-reduce") if world > 1 else "single GPU",
         "decode_mode": "cuda graph" if decoder.graph is not None else f"eager ({decoder.reason or 'requested'})",
         "prefill_tokens_per_s": batch * prompt / t_pre, "decode_tokens_per_s": batch * decode / t_dec,
         "ms_per_decode_step": 1e3 * t_dec / decode, "prefill_s": t_pre, "decode_s": t_dec,
@@ -137,11 +137,12 @@ def main():
     ap.add_argument("--chunk-size", type=int, default=2048)
     ap.add_argument("--no-graph", action="store_true", help="eager single-token steps instead of CUDA graph replays")
     ap.add_argument("--no-fused-prefill", action="store_true", help="tensor parallel: all-reduce path for the prefill chunks too")
+    ap.add_argument("--fused-prefill", action="store_true", help="tensor parallel: fused path below 8 ranks too (default: from 8 ranks on)")
     ap.add_argument("--n-layer", type=int, default=None, help="fewer layers (the result is then marked reduced)")
     ap.add_argument("--repeats", type=int, default=1)
     args = ap.parse_args()
     out = run(args.model, args.batch, args.prompt, args.decode, args.cache_name, args.cache_length, args.chunk_size, not args.no_graph,
-              args.n_layer, not args.no_fused_prefill, repeats=args.repeats)
+              args.n_layer, False if args.no_fused_prefill else (True if args.fused_prefill else None), repeats=args.repeats)
     if out:
         print(json.dumps(out), flush=True)
 
