@@ -125,6 +125,23 @@ def compute_loss_for_chunk(
     x = model_outputs[:, -n_t:, :]
     B = x.shape[0]
     vocab = gpt_model.config.padded_vocab_size
+    comm = getattr(gpt_model, "tp_comm", None)
+    if (comm is not None and comm.world > 1 and getattr(gpt_model, "vocab_parallel_loss", True) and type(head_model).__name__ == "CrossEntropyOnLogits"
+            and isinstance(gpt_model.lm_head, torch.nn.Linear) and gpt_model.lm_head.bias is None
+            and gpt_model.config.final_logit_softcapping is None):
+        # tensor-parallel shard: every rank forms the logits of its slice of the vocabulary only
+        from keys_values_b200.parallel.tp import vocab_parallel_cross_entropy
+
+        bytes_per_pos = B * (vocab // comm.world + 1) * 4
+        piece = max(1, MAX_LOGITS_BYTES // bytes_per_pos)
+        total = None
+        for s in range(0, n_t, piece):
+            e = min(s + piece, n_t)
+            h = gpt_model.transformer.ln_f(x[:, s:e, :])
+            rows = vocab_parallel_cross_entropy(h.reshape(-1, h.shape[-1]), gpt_model.lm_head.weight, targets[:, s:e], comm)
+            part = rows.view(B, e - s).sum(dim=-1)
+            total = part if total is None else total + part
+        return total
     bytes_per_pos = B * vocab * 4
     piece = max(1, MAX_LOGITS_BYTES // bytes_per_pos)
     total = None

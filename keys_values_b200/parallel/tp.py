@@ -485,6 +485,62 @@ class _CopyToShards(torch.autograd.Function):
         return ctx.comm.all_reduce(g.contiguous().clone().view(-1, g.shape[-1])).view_as(g), None
 
 
+class _GatherColumns(torch.autograd.Function):
+    """``(rows,)`` per rank → ``(rows, world)`` on every rank. What follows is computed identically everywhere (one
+    loss, replicated), so the gradient of a rank's own column is the gradient of its input."""
+
+    @staticmethod
+    def forward(ctx, x, comm):
+        ctx.rank = comm.rank
+        parts = [torch.empty_like(x) for _ in range(comm.world)]
+        dist.all_gather(parts, x.contiguous(), group=comm.group)
+        return torch.stack(parts, dim=1)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g[:, ctx.rank].contiguous(), None
+
+
+class _SumScalars(torch.autograd.Function):
+    """Sum over ranks of a small fp32 tensor (library all-reduce: these are per-row scalars); identity backward."""
+
+    @staticmethod
+    def forward(ctx, x, comm):
+        y = x.contiguous().clone()
+        dist.all_reduce(y, op=dist.ReduceOp.SUM, group=comm.group)
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+def vocab_parallel_cross_entropy(x: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor, comm: "TPComm",
+                                 ignore_index: int = -100) -> torch.Tensor:
+    """Token cross-entropy with the vocabulary split over the ranks: rank ``r`` multiplies ``x (rows, E)`` (the final
+    hidden states after ``ln_f``, replicated) with rows ``[r·V/world, (r+1)·V/world)`` of the head's weight only, so
+    the logits of a position never exist in one place. Per row the ranks exchange two numbers (the log-sum-exp of
+    their slice and, from the owner, the target's logit): ``loss = logsumexp_r(lse_r) − logit_target``. Returns the
+    per-row losses (0 where ``targets == ignore_index``); differentiable in ``x`` and ``weight``."""
+    V = weight.shape[0]
+    world, rank = comm.world, comm.rank
+    per = (V + world - 1) // world
+    v0, v1 = min(rank * per, V), min((rank + 1) * per, V)
+    tg = targets.reshape(-1)
+    if torch.is_grad_enabled() and x.requires_grad:
+        x = _CopyToShards.apply(x, comm)  # every rank contributes the part of dL/dx that runs through its slice
+    if torch.is_grad_enabled() and weight.requires_grad:
+        weight = _CopyToShards.apply(weight, comm)  # replicated parameter: rank r produces the gradient of its rows only
+    logits = torch.nn.functional.linear(x, weight[v0:v1]).float()  # (rows, V_local)
+    lse_local = torch.logsumexp(logits, dim=-1) if v1 > v0 else torch.full_like(tg, float("-inf"), dtype=torch.float32)
+    lse = torch.logsumexp(_GatherColumns.apply(lse_local, comm), dim=1)
+    mine = (tg >= v0) & (tg < v1)
+    picked = logits.gather(1, (tg - v0).clamp(0, max(v1 - v0 - 1, 0)).unsqueeze(1)).squeeze(1)
+    target_logit = _SumScalars.apply(torch.where(mine, picked, torch.zeros_like(picked)), comm)
+    loss = lse - target_logit
+    return torch.where(tg == ignore_index, torch.zeros_like(loss), loss)
+
+
 def local_config(config, world: int):
     """The configuration of one rank's shard: heads, KV heads and MLP width divided by ``world``."""
     import dataclasses
