@@ -481,3 +481,43 @@ def test_cli_finetune_lora_tensor_parallel_writes_whole_model_checkpoints(tmp_pa
     assert "step 3/3" in r.stdout and "step 1/3" not in r.stdout
     r = _run_cli(["eval_long", str(two), "--precision", "32-true", "--eval.max_iters", "1"], tmp_path)
     assert r.returncode == 0, r.stdout + r.stderr
+
+
+def test_grpo_trainer_reference_policy_iterations_and_statistics():
+    """KL against the policy with its adapters switched off, two optimisation steps per rollout, two reward
+    functions, masking of truncated completions; the adapters change and the statistics are reported."""
+    from keys_values_b200.kvcache.factory import KVCacheFactory
+    from keys_values_b200.kvcache.gradient.main import LongContextGradientModel
+    from keys_values_b200.kvcache.test_utils import MockTokenizer
+    from keys_values_b200.models import lora as lora_mod
+    from keys_values_b200.rl.grpo import GRPOLongContextTrainer, GRPOLossHeadModel, adapters_disabled
+
+    torch.manual_seed(0)
+    cfg = lora_mod.Config.from_name("tiny-gpt", lora_r=2, lora_query=True, lora_value=True)
+    m = lora_mod.GPT(cfg)
+    m.apply(m._init_weights)
+    for n, p in m.named_parameters():
+        if "lora_B" in n:
+            torch.nn.init.normal_(p, std=0.05)
+    lora_mod.mark_only_lora_as_trainable(m)
+    ids = torch.randint(0, 500, (1, 40))
+    with torch.no_grad():
+        with_adapters = m(ids)
+        with adapters_disabled(m):
+            without = m(ids)
+        again = m(ids)
+    assert not torch.allclose(with_adapters, without) and torch.equal(with_adapters, again)
+    m.assign_kv_caches(KVCacheFactory.create(m, "dense-default", 4, 128, dtype=torch.float32))
+    head = GRPOLossHeadModel(cfg, beta=0.05)
+    gm = LongContextGradientModel(m, head, layers_per_cell=1, chunk_size=16)
+    opt = torch.optim.SGD([p for p in m.parameters() if p.requires_grad], lr=0.05)
+    tok = MockTokenizer()
+    tok.eos_id = None
+    trainer = GRPOLongContextTrainer(gm, opt, tok, [lambda c, meta: float(sum(c) % 7), lambda c, meta: -0.1 * len(c)], num_generations=4,
+                                     max_new_tokens=6, reward_weights=[1.0, 0.5], num_iterations=2, max_norm=1.0)
+    before = {n: p.detach().clone() for n, p in m.named_parameters() if p.requires_grad}
+    stats = trainer.step(torch.randint(0, 500, (1, 30)))
+    assert any(not torch.equal(before[n], p) for n, p in m.named_parameters() if p.requires_grad)
+    assert {"loss", "mean_reward", "kl", "clip_fraction", "mean_completion_length", "truncated_fraction"} <= set(stats)
+    assert stats["kl"] >= 0.0 and stats["truncated_fraction"] == 1.0 and stats["mean_completion_length"] == 6.0
+    assert trainer.history == [stats]
