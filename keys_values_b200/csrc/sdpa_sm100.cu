@@ -40,6 +40,8 @@
 #include <cuda.h>
 #include <limits.h>
 
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "kvb200.h"
 
@@ -94,6 +96,11 @@ struct F2Params {
   int input_pos;
   int* status;
   long long* trace;          // optional phase profile of CTA 0: 4 roles x 8 cycle counters
+  // split over the KV axis (few query tiles): grid.y = n_split CTAs per query-tile pair, each over tiles_per_split KV
+  // tiles; they write normalised fp32 partial outputs and their log2 normalisers, a merge kernel combines them
+  int n_split, tiles_per_split;
+  float* part_o;             // (n_split, B, H, T, D)
+  float* part_lse2;          // (n_split, B, H, T), -inf for a split that saw no visible slot
 };
 
 // Optional phase profile of CTA 0 (diagnostics): each role adds the cycles spent since its previous mark to one of
@@ -264,10 +271,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int32_t* tmin = p.tile_min + bg * p.nT;
   const int32_t* tmax = p.tile_max + bg * p.nT;
 
+  // the KV tiles of this CTA: all of them, or the range of its split (tiles outside count as inactive)
+  const int split = p.n_split > 1 ? (int)blockIdx.y : 0;
+  const int t_lo = p.n_split > 1 ? split * p.tiles_per_split : 0;
+  const int t_hi = p.n_split > 1 ? min(p.nT, t_lo + p.tiles_per_split) : p.nT;
   for (int t = threadIdx.x; t < min(p.nT, F2_MAX_FLAG_TILES); t += F2_THREADS)
-    tflags[t] = (uint8_t)((tmin[t] <= qpos_max) | ((tmax[t] > qpos_min) << 1));
+    tflags[t] = (t >= t_lo && t < t_hi) ? (uint8_t)((tmin[t] <= qpos_max) | ((tmax[t] > qpos_min) << 1)) : (uint8_t)0;
   auto tile_bits = [&](int t) -> uint32_t {
-    if (t >= F2_MAX_FLAG_TILES) return (uint32_t)(tmin[t] <= qpos_max) | ((uint32_t)(tmax[t] > qpos_min) << 1);
+    if (t >= F2_MAX_FLAG_TILES)
+      return (t >= t_lo && t < t_hi) ? ((uint32_t)(tmin[t] <= qpos_max) | ((uint32_t)(tmax[t] > qpos_min) << 1)) : 0u;
     return tflags[t];
   };
   if (p.rows_used < F2_T) {
@@ -667,6 +679,30 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tc_fence_after();
       const float inv_l = l > 0.f ? 1.f / l : 0.f;
       const float lse2 = l > 0.f ? m_used + log2f(l) : INFINITY;
+      if (p.n_split > 1) {
+        // partial result of this split: normalised fp32 rows and their log2 normaliser
+        const long long prow = (((long long)split * p.B + b) * p.H + (g * p.gs + (row_valid ? hq : 0))) * p.T + (row_valid ? tq : 0);
+        float* pdst = p.part_o + prow * F2_T;
+#pragma unroll 1
+        for (int c0 = 0; c0 < F2_T; c0 += 32) {
+          uint32_t o[32];
+          if (n_active > 0) {
+            tmem_ld_32x32b_x32(tmem_O + (uint32_t)c0, o);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) o[e] = 0;
+          }
+          if (row_valid) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              *reinterpret_cast<float4*>(pdst + c0 + 4 * u) =
+                  make_float4(__uint_as_float(o[4 * u]) * inv_l, __uint_as_float(o[4 * u + 1]) * inv_l,
+                              __uint_as_float(o[4 * u + 2]) * inv_l, __uint_as_float(o[4 * u + 3]) * inv_l);
+          }
+        }
+        if (row_valid) p.part_lse2[prow] = l > 0.f ? lse2 : -INFINITY;
+      } else {
       // tcgen05.ld is warp-collective: rows without a query take part in the loads and skip the stores
       __nv_bfloat16* dst = p.out + (((long long)b * p.T + (row_valid ? tq : 0)) * p.H + (g * p.gs + (row_valid ? hq : 0))) * F2_T;
 #pragma unroll 1
@@ -693,6 +729,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       if (row_valid && p.lse) p.lse[((long long)b * p.H + (g * p.gs + hq)) * p.T + tq] = lse2 * 0.6931471805599453f;
       if (p.lse2 && qt < p.nQT) p.lse2[(bg * p.nQT + qt) * F2_T + row] = row_valid ? lse2 : INFINITY;
+      }
     }
   }
   tc_fence_before();
@@ -700,6 +737,53 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// Combines the partial results of the splits of a query row: out = Σ_s w_s O_s / Σ_s w_s with w_s = 2^(lse2_s − max),
+// in a fixed order of the splits. One warp per packed query row (the rows of the lse2 layout, padding rows included,
+// which get +inf there as in the unsplit kernel); lane l holds features 4l .. 4l+3.
+__global__ void __launch_bounds__(256) flash_merge_kernel(const F2Params p) {
+  const long long wrow = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);  // index into (B, G, nQT, 128)
+  const int lane = threadIdx.x & 31;
+  if (wrow >= (long long)p.B * p.G * p.nQT * F2_T) return;
+  const int row = (int)(wrow % F2_T);
+  const int qt = (int)((wrow / F2_T) % p.nQT);
+  const long long bg = wrow / ((long long)F2_T * p.nQT);
+  const int g = (int)(bg % p.G), b = (int)(bg / p.G);
+  const int pl = row / p.gs, hq = row % p.gs;
+  const int tq = qt * p.npos + pl;
+  const bool row_valid = row < p.rows_used && tq < p.T;
+  if (!row_valid) {
+    if (lane == 0 && p.lse2) p.lse2[wrow] = INFINITY;
+    return;
+  }
+  const int h = g * p.gs + hq;
+  const long long stride = (long long)p.B * p.H * p.T;  // rows per split
+  const long long prow = ((long long)b * p.H + h) * p.T + tq;
+  float mx = -INFINITY;
+  for (int sidx = 0; sidx < p.n_split; ++sidx) mx = fmaxf(mx, p.part_lse2[sidx * stride + prow]);
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float total = 0.f;
+  if (mx > -INFINITY) {
+    for (int sidx = 0; sidx < p.n_split; ++sidx) {
+      const float w = exp2f(p.part_lse2[sidx * stride + prow] - mx);
+      if (w > 0.f) {
+        const float4 o = *reinterpret_cast<const float4*>(p.part_o + (sidx * stride + prow) * F2_T + 4 * lane);
+        acc.x += w * o.x; acc.y += w * o.y; acc.z += w * o.z; acc.w += w * o.w;
+        total += w;
+      }
+    }
+  }
+  const float inv = total > 0.f ? 1.f / total : 0.f;
+  uint2 v;
+  v.x = pack_bf16x2(acc.x * inv, acc.y * inv);
+  v.y = pack_bf16x2(acc.z * inv, acc.w * inv);
+  *reinterpret_cast<uint2*>(p.out + (((long long)b * p.T + tq) * p.H + h) * F2_T + 4 * lane) = v;
+  if (lane == 0) {
+    const float lse2 = total > 0.f ? mx + log2f(total) : INFINITY;
+    if (p.lse) p.lse[prow] = lse2 * 0.6931471805599453f;
+    if (p.lse2) p.lse2[wrow] = lse2;
   }
 }
 
@@ -960,6 +1044,22 @@ extern "C" int kvb_sdpa_fwd_set_trace(void* buf) {
 
 // Scratch layout (int32 words, 16-byte aligned parts), provided by the caller:
 //   tile_min (B*G*nT) | tile_max (B*G*nT) | positions (B*G*nT*128) | lse2 (B*G*nQT*128 floats)
+// Number of CTAs along the KV axis per query-tile pair: 1 unless the launch would leave most SMs idle (few queries:
+// short chunks at batch 1) while the cache is long enough to give every split at least 8 tiles.
+static int f2_num_splits(long long ctas, long long nT) {
+  static const int enabled = [] {
+    const char* e = getenv("KVB200_F2_SPLIT");  // "0" switches the split off (diagnostics)
+    return (e && e[0] == '0') ? 0 : 1;
+  }();
+  if (!enabled || ctas <= 0 || ctas * 2 > 148 || nT < 16) return 1;
+  long long n = 148 / ctas;
+  if (n > nT / 8) n = nT / 8;
+  if (n > 8) n = 8;
+  return n < 2 ? 1 : (int)n;
+}
+
+//   ... | split partials: part_lse2 (n_split*B*H*T floats) | part_o (n_split*B*H*T*128 floats), present when the
+//   launch is split over the KV axis (f2_num_splits)
 extern "C" long long kvb_sdpa_fwd_scratch_bytes(int B, int H, int G, int q_len, int kv_len) {
   if (G <= 0 || H % G || H / G > 128) return -1;
   const int gs = H / G;
@@ -967,7 +1067,10 @@ extern "C" long long kvb_sdpa_fwd_scratch_bytes(int B, int H, int G, int q_len, 
   const long long npos = 128 / gs;
   const long long nQT = (q_len + npos - 1) / npos;
   const long long bgt = kvb::f2_round4((long long)B * G * nT);
-  return (2 * bgt + (long long)B * G * nT * 128 + (long long)B * G * nQT * 128) * 4;
+  long long words = 2 * bgt + (long long)B * G * nT * 128 + (long long)B * G * nQT * 128;
+  const int n_split = f2_num_splits((long long)B * G * ((nQT + 1) / 2), nT);
+  if (n_split > 1) words += kvb::f2_round4((long long)n_split * B * H * q_len) + (long long)n_split * B * H * q_len * 128;
+  return words * 4;
 }
 
 // q (B,H,T,128) contiguous bf16; k, v (B,G,L,128) bf16 with batch / group strides k_sb, k_sg (elements);
@@ -1020,7 +1123,15 @@ extern "C" int kvb_sdpa_fwd(const void* q, const void* k, const void* v, const i
     cudaFuncSetAttribute(colsum_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, CsSmem::TOTAL);
   }
   const int nPair = (p.nQT + 1) / 2;
-  flash_fwd_kernel<<<B * G * nPair, F2_THREADS, F2Smem::TOTAL, s>>>(tmQ, tmK, tmV, p);
+  p.n_split = f2_num_splits((long long)B * G * nPair, p.nT);
+  p.tiles_per_split = (p.nT + p.n_split - 1) / p.n_split;
+  p.part_lse2 = lse2 + (long long)B * G * p.nQT * 128;
+  p.part_o = p.part_lse2 + f2_round4((long long)p.n_split * B * H * q_len);
+  flash_fwd_kernel<<<dim3(B * G * nPair, p.n_split), F2_THREADS, F2Smem::TOTAL, s>>>(tmQ, tmK, tmV, p);
+  if (p.n_split > 1) {
+    const long long rows = (long long)B * G * p.nQT * F2_T;
+    flash_merge_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(p);
+  }
   if (weights) colsum_kernel<<<B * G * p.nT, F2_THREADS, CsSmem::TOTAL, s>>>(tmQ, tmK, p);
   return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
 }

@@ -184,3 +184,33 @@ def test_adapter_v1_prefix_attention_matches_a_plain_restatement():
             want = plain_attention(blk.attn, blk.norm_1(x))
             torch.testing.assert_close(got, want, atol=2e-5, rtol=1e-4)
             x = blk(x, ids, m.mha)
+
+
+def test_tensor_parallel_sharding_rules_round_trip():
+    """Plain and LoRA state dicts: shard over 2 and 4 ranks, put back together, and get the same tensors; the
+    shards have the shapes of a model built from the local configuration."""
+    from keys_values_b200.config import Config
+    from keys_values_b200.models import lora as lora_mod
+    from keys_values_b200.models.model import GPT
+    from keys_values_b200.parallel.tp import local_config, shard_state_dict, unshard_state_dict
+
+    torch.manual_seed(0)
+    plain_cfg = Config.from_name("tiny-qwen3", n_query_groups=4, bias=True)
+    lora_cfg = lora_mod.Config.from_name("tiny-qwen3", n_query_groups=4, lora_r=4, lora_query=True, lora_value=True, lora_projection=True, lora_mlp=True)
+    for cfg, cls in ((plain_cfg, GPT), (lora_cfg, lora_mod.GPT)):
+        whole = cls(cfg)
+        for p in whole.parameters():
+            torch.nn.init.normal_(p)
+        sd = whole.state_dict()
+        for world in (2, 4):
+            shards = [shard_state_dict(sd, cfg, world, r) for r in range(world)]
+            local = cls(local_config(cfg, world)).state_dict()
+            assert all(tuple(shards[0][k].shape) == tuple(local[k].shape) for k in local), "shard shapes"
+            back = unshard_state_dict([{k: (v if not k.endswith("proj.bias") or r == 0 else v) for k, v in sh.items()}
+                                       for r, sh in enumerate(shards)], cfg)
+            assert all(torch.equal(back[k], sd[k]) for k in sd)
+            # row-parallel biases live on rank 0 only
+            bias_keys = [k for k in sd if k.endswith("attn.proj.bias") or k.endswith("mlp.proj.bias")]
+            assert all(float(shards[1][k].abs().sum()) == 0.0 for k in bias_keys)
+    with pytest.raises(ValueError):
+        local_config(plain_cfg, 3)

@@ -233,6 +233,14 @@ def test_sdpa_long_chunk_over_full_cache():
     _sdpa_case(1, 32, 8, 1024, 16384, 5 * 16384, "perm")
 
 
+@pytest.mark.parametrize("B,H,G,T,L,mode", [(1, 8, 2, 100, 3000, "perm"), (1, 4, 1, 64, 8192, "perm"), (1, 5, 1, 60, 4100, "perm"),
+                                             (1, 8, 2, 128, 2048, "arange")])
+def test_sdpa_few_queries_split_over_the_cache(B, H, G, T, L, mode):
+    """Few query tiles and a long cache: the flash sweep is split over the KV axis (several CTAs per query-tile
+    pair, fp32 partials, a merge in a fixed order); one tensor-parallel rank with a single KV group is the typical case."""
+    _sdpa_case(B, H, G, T, L, 4 * L if mode == "perm" else L - T, mode)
+
+
 def test_sdpa_plain_causal_with_weights():
     # square causal prefill with weights: diagonal tiles take the element-wise mask path
     _sdpa_case(2, 8, 2, 700, 700, 0, "arange")
@@ -240,7 +248,7 @@ def test_sdpa_plain_causal_with_weights():
 
 def test_sdpa_is_deterministic():
     """Outputs, normalisers and the summed weights (which drive the eviction decisions) are bit-identical run to run."""
-    D, B, H, G, T, L = 128, 1, 32, 8, 512, 4096
+    D, B, H, G, T, L = 128, 1, 32, 8, 512, 4096  # 64 CTAs: split over the KV axis, partials merged in a fixed order
     q = torch.randn(B, H, T, D, device=DEV, dtype=torch.bfloat16)
     k = torch.randn(B, G, L, D, device=DEV, dtype=torch.bfloat16)
     v = torch.randn(B, G, L, D, device=DEV, dtype=torch.bfloat16)
