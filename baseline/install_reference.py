@@ -1,6 +1,6 @@
 """Completes the offline install of the reference under ``baseline/_ref`` for use on a B200.
 
-Step 0 (done once by hand, recorded in DESIGN.md)::
+Step 0 (done once by hand)::
 
     python -m pip install --no-index --no-build-isolation --no-deps --find-links /opt/wheelhouse \
         --target baseline/_ref <checkout of the reference>
@@ -28,6 +28,7 @@ compiled into it.
 from __future__ import annotations
 
 import argparse
+import os
 import importlib.util
 import shutil
 import sys
@@ -67,8 +68,8 @@ def copy_package_data(src_pkg: Path) -> None:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--source", type=Path, default=Path("/root/reference"),
-                    help="checkout of the reference that holds keys_values/csrc")
+    ap.add_argument("--source", type=Path, default=Path(os.environ.get("KEYS_VALUES_REFERENCE", "reference")),
+                    help="checkout of the reference that holds keys_values/csrc (default: $KEYS_VALUES_REFERENCE or ./reference)")
     ap.add_argument("--no-ext", action="store_true", help="copy the package data only")
     args = ap.parse_args()
     csrc = args.source / "keys_values" / "csrc"
