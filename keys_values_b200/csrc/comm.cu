@@ -252,6 +252,106 @@ oneshot_allreduce_kernel(OneShotPeers peers, int rank, int world, long long nvec
   }
 }
 
+
+// One-shot all-reduce fused with the residual add and the RMSNorm that follows it in a transformer block:
+//   x_new = Σ_r partial_r + residual      (written to out_x: the residual stream)
+//   normed = x_new · rsqrt(mean(x_new²) + eps) · w   (written to out_normed: the input of the next linears)
+// One CTA per row (a decode step has a handful of rows), so the row's sum of squares never leaves the CTA; a thread
+// keeps its up to ONESHOT_NORM_VEC 16-byte pieces of the row in registers between the two passes. Same flag
+// protocol and epochs as oneshot_allreduce_kernel (flag word of CTA = row).
+constexpr int ONESHOT_NORM_VEC = 4;  // 16-byte vectors per thread: rows of up to 4 · 256 · 8 = 8192 16-bit features
+
+template <typename T>
+__global__ void __launch_bounds__(ONESHOT_THREADS)
+oneshot_allreduce_norm_kernel(OneShotPeers peers, int rank, int world, int feat, const T* __restrict__ residual,
+                              const T* __restrict__ norm_w, float eps, int unit_offset, T* __restrict__ out_x,
+                              T* __restrict__ out_normed, uint32_t epoch_base, const uint32_t* epoch_word, int* status,
+                              long long limit) {
+  constexpr int V = 16 / sizeof(T);
+  __shared__ int ok_s;
+  __shared__ float red_s[ONESHOT_THREADS / 32];
+  const uint32_t epoch = epoch_base + (epoch_word ? *epoch_word : 0u);
+  if (threadIdx.x == 0) ok_s = 1;
+  __syncthreads();
+  if ((int)threadIdx.x < world && (int)threadIdx.x != rank) {
+    const int peer = threadIdx.x;
+    st_release_sys(peers.flags[peer] + rank * ONESHOT_MAX_CTAS + blockIdx.x, epoch);
+    const uint32_t* mine = peers.flags[rank] + peer * ONESHOT_MAX_CTAS + blockIdx.x;
+    const long long t0 = clock64();
+    while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
+      if (clock64() - t0 > limit) {
+        if (status) atomicCAS(status, 0, STATUS_TIMEOUT_PEER_FLAG);
+        ok_s = 0;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (!ok_s) return;
+  const int nvec = feat / V;
+  const long long row0 = (long long)blockIdx.x * nvec;  // in vectors
+  float x[ONESHOT_NORM_VEC][V];
+  float sq = 0.f;
+#pragma unroll
+  for (int k = 0; k < ONESHOT_NORM_VEC; ++k) {
+    const int i = k * ONESHOT_THREADS + threadIdx.x;
+    if (i < nvec) {
+      float acc[V];
+#pragma unroll
+      for (int j = 0; j < V; ++j) acc[j] = 0.f;
+      uint4 raw[COMM_MAX_RANKS];  // all ranks' pieces are requested before the first one is used
+#pragma unroll
+      for (int r = 0; r < COMM_MAX_RANKS; ++r)
+        if (r < world) raw[r] = ld_volatile_v4(reinterpret_cast<const uint4*>(peers.slot[r]) + row0 + i);
+#pragma unroll
+      for (int r = 0; r < COMM_MAX_RANKS; ++r)
+        if (r < world) {
+          const T* e = reinterpret_cast<const T*>(&raw[r]);
+#pragma unroll
+          for (int j = 0; j < V; ++j) acc[j] += to_f32(e[j]);
+        }
+      if (residual) {
+        const uint4 rv = *(reinterpret_cast<const uint4*>(residual) + row0 + i);
+        const T* e = reinterpret_cast<const T*>(&rv);
+#pragma unroll
+        for (int j = 0; j < V; ++j) acc[j] += to_f32(e[j]);
+      }
+      uint4 ov;
+      T* o = reinterpret_cast<T*>(&ov);
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        o[j] = from_f32<T>(acc[j]);
+        x[k][j] = to_f32(o[j]);  // the norm sees the residual stream as it is stored
+        sq += x[k][j] * x[k][j];
+      }
+      *(reinterpret_cast<uint4*>(out_x) + row0 + i) = ov;
+    }
+  }
+  sq = warp_sum(sq);
+  if ((threadIdx.x & 31) == 0) red_s[threadIdx.x >> 5] = sq;
+  __syncthreads();
+  float total = 0.f;
+#pragma unroll
+  for (int w = 0; w < ONESHOT_THREADS / 32; ++w) total += red_s[w];
+  const float rstd = rsqrtf(total / (float)feat + eps);
+#pragma unroll
+  for (int k = 0; k < ONESHOT_NORM_VEC; ++k) {
+    const int i = k * ONESHOT_THREADS + threadIdx.x;
+    if (i < nvec) {
+      const uint4 wv = *(reinterpret_cast<const uint4*>(norm_w) + i);
+      const T* we = reinterpret_cast<const T*>(&wv);
+      uint4 ov;
+      T* o = reinterpret_cast<T*>(&ov);
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const float w = to_f32(we[j]) + (unit_offset ? 1.f : 0.f);
+        o[j] = from_f32<T>(x[k][j] * rstd * w);
+      }
+      *(reinterpret_cast<uint4*>(out_normed) + row0 + i) = ov;
+    }
+  }
+}
+
 }  // namespace kvb
 
 using namespace kvb;
@@ -360,5 +460,36 @@ extern "C" int kvb_oneshot_allreduce(void* const* slots, void* const* flags, int
     default:
       return KVB_ERR_ARG;
   }
+  return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
+}
+
+// The same with the residual add and the RMSNorm of the next sub-block fused in: rows <= 16 (one CTA per row),
+// features a multiple of 8 and at most 8192, 16-bit dtypes (1 bf16, 2 fp16). out_x = sum + residual (residual may be
+// NULL), out_normed = rmsnorm(out_x) * norm_w (norm_w + 1 with unit_offset).
+extern "C" int kvb_oneshot_allreduce_norm(void* const* slots, void* const* flags, int rank, int world, int rows, int features,
+                                          const void* residual, const void* norm_w, float eps, int unit_offset, void* out_x,
+                                          void* out_normed, unsigned epoch_base, const void* epoch_word, int dtype, int* status,
+                                          double timeout_s, void* stream) {
+  if (world < 1 || world > COMM_MAX_RANKS || rank < 0 || rank >= world || rows <= 0 || features <= 0) return KVB_ERR_ARG;
+  if (rows > ONESHOT_MAX_CTAS || (features % 8) || features > ONESHOT_NORM_VEC * ONESHOT_THREADS * 8) return KVB_ERR_UNSUPPORTED;
+  if (dtype != 1 && dtype != 2) return KVB_ERR_UNSUPPORTED;
+  OneShotPeers peers;
+  for (int r = 0; r < world; ++r) {
+    if (((uintptr_t)slots[r]) % 16) return KVB_ERR_ALIGN;
+    peers.slot[r] = slots[r];
+    peers.flags[r] = reinterpret_cast<uint32_t*>(flags[r]);
+  }
+  if ((((uintptr_t)out_x) | ((uintptr_t)out_normed) | ((uintptr_t)residual) | ((uintptr_t)norm_w)) % 16) return KVB_ERR_ALIGN;
+  const long long limit = (long long)(timeout_s * 1.9e9);
+  cudaStream_t s = (cudaStream_t)stream;
+  const uint32_t* ew = reinterpret_cast<const uint32_t*>(epoch_word);
+  if (dtype == 1)
+    oneshot_allreduce_norm_kernel<__nv_bfloat16><<<rows, ONESHOT_THREADS, 0, s>>>(
+        peers, rank, world, features, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)norm_w, eps, unit_offset,
+        (__nv_bfloat16*)out_x, (__nv_bfloat16*)out_normed, epoch_base, ew, status, limit);
+  else
+    oneshot_allreduce_norm_kernel<__half><<<rows, ONESHOT_THREADS, 0, s>>>(peers, rank, world, features, (const __half*)residual,
+                                                                         (const __half*)norm_w, eps, unit_offset, (__half*)out_x,
+                                                                         (__half*)out_normed, epoch_base, ew, status, limit);
   return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
 }

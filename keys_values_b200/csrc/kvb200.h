@@ -123,6 +123,9 @@ int kvb_allreduce_mean(void* const* bases, void* const* flags, int rank, int wor
 int kvb_oneshot_allreduce(void* const* slots, void* const* flags, int rank, int world, long long count, const void* residual,
                           void* out, unsigned epoch_base, const void* epoch_word, int dtype, int* status, double timeout_s,
                           void* stream);
+int kvb_oneshot_allreduce_norm(void* const* slots, void* const* flags, int rank, int world, int rows, int features,
+                               const void* residual, const void* norm_w, float eps, int unit_offset, void* out_x, void* out_normed,
+                               unsigned epoch_base, const void* epoch_word, int dtype, int* status, double timeout_s, void* stream);
 #define KVB_ONESHOT_MAX_CTAS 16
 #define KVB_COMM_MAX_RANKS 16
 

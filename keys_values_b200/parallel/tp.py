@@ -406,6 +406,45 @@ class TPComm:
             self.eager_calls += 1
         return out
 
+    def all_reduce_add_norm(self, buf: torch.Tensor, residual: Optional[torch.Tensor], norm_weight: torch.Tensor, eps: float,
+                            unit_offset: bool = False):
+        """``x = sum over ranks of buf + residual`` and ``rmsnorm(x) · norm_weight`` in one kernel (a decode step's
+        handful of rows: one CTA per row). ``buf`` must come from :meth:`out_buffer`. Returns ``(x, normed)``."""
+        rows, feat = buf.shape
+        fused = (self.native and self._pending is not None and self._pending[0] == "small" and self._pending[2].data_ptr() == buf.data_ptr()
+                 and rows <= 16 and feat % 8 == 0 and feat <= 8192 and buf.dtype in (torch.bfloat16, torch.float16)
+                 and norm_weight.dtype == buf.dtype)
+        if not fused:
+            from keys_values_b200 import ops
+
+            x = self.all_reduce(buf, residual)
+            return x, ops.rmsnorm(x, norm_weight, eps, unit_offset)
+        _, site, mine = self._pending
+        self._pending = None
+        out_x, out_n = torch.empty_like(mine), torch.empty_like(mine)
+        st = _cu.status_word(self.device)
+        if residual is not None:
+            residual = residual.contiguous()
+        if self._capturing:
+            base, word = self.captured_calls + 1, self.epoch_word
+        else:
+            base, word = self.eager_calls + 1, None
+        _cu._check(
+            _cu.lib().kvb_oneshot_allreduce_norm(
+                self.slots.ptr_array(site * self.small_bytes), self.flags.ptr_array(site * self._flag_bytes), self.rank, self.world,
+                rows, feat, _cu._p(residual), _cu._p(norm_weight.contiguous()), ctypes.c_float(eps), int(bool(unit_offset)), _cu._p(out_x),
+                _cu._p(out_n), ctypes.c_uint(base & 0xFFFFFFFF), _cu._p(word), _cu._code(mine.dtype), _cu._p(st),
+                ctypes.c_double(self.timeout_s), _cu._stream(mine),
+            ),
+            "oneshot_allreduce_norm",
+        )
+        _cu._count()
+        if self._capturing:
+            self.captured_calls += 1
+        else:
+            self.eager_calls += 1
+        return out_x, out_n
+
     # ------------------------------------------------------------------ graph capture
     def begin_capture(self) -> None:
         self._capturing, self.captured_calls = True, 0
@@ -804,9 +843,38 @@ def _tp_classes(lora: bool):
                 and self.attn.qkv.weight.dtype == torch.bfloat16
             )
 
+        def _few_rows(self, rows: int) -> bool:
+            """Single-token steps: the residual add and the RMSNorm after each all-reduce run inside its kernel."""
+            gpt = self.owner()
+            c = self.config
+            return (
+                gpt is not None and gpt.tp_comm.native and not torch.is_grad_enabled() and rows <= 16
+                and c.n_embd % 8 == 0 and c.n_embd <= 8192 and rows * c.n_embd * 2 <= gpt.tp_comm.small_bytes
+                and isinstance(self.norm_1, RMSNorm) and isinstance(self.norm_2, RMSNorm) and not c.parallel_residual
+                and not c.post_attention_norm and not c.post_mlp_norm and type(self.attn.proj) is RowParallelLinear
+                and type(self.mlp.proj) is RowParallelLinear and self.attn.proj.bias is None and self.mlp.proj.bias is None
+                and self.attn.proj.weight.dtype == gpt.tp_comm.dtype
+            )
+
+        def _forward_few_rows(self, x, token_idx, mha, chunk_sizes):
+            comm = self.owner().tp_comm
+            B, T, E = x.shape
+            rows = B * T
+            x2 = x.reshape(rows, E)
+            y = self.attn.attend(self.attn.qkv(self.norm_1(x)), token_idx, mha, chunk_sizes)
+            buf = comm.out_buffer(rows, E, x.dtype)
+            torch.mm(y.reshape(rows, -1), self.attn.proj.weight.t(), out=buf)
+            x2, normed = comm.all_reduce_add_norm(buf, x2, self.norm_2.weight, self.norm_2.eps, self.norm_2.add_unit_offset)
+            a = ops.swiglu(self.mlp.fc_1(normed), self.mlp.fc_2(normed))  # the caller checked that this is a SwiGLU MLP
+            buf = comm.out_buffer(rows, E, x.dtype)
+            torch.mm(a, mlp.proj.weight.t(), out=buf)
+            return comm.all_reduce(buf, residual=x2).view(B, T, E)
+
         def forward(self, x, token_idx, mha, chunk_sizes=None):
             B, T = token_idx.shape
             if not self._fusable(B * T):
+                if type(self.mlp) is LLaMAMLP and self._few_rows(B * T):
+                    return self._forward_few_rows(dense(x), token_idx, mha, chunk_sizes)
                 return super().forward(dense(x), token_idx, mha, chunk_sizes=chunk_sizes)
             gpt = self.owner()
             comm, c = gpt.tp_comm, self.config
