@@ -867,7 +867,7 @@ def _tp_classes(lora: bool):
             x2, normed = comm.all_reduce_add_norm(buf, x2, self.norm_2.weight, self.norm_2.eps, self.norm_2.add_unit_offset)
             a = ops.swiglu(self.mlp.fc_1(normed), self.mlp.fc_2(normed))  # the caller checked that this is a SwiGLU MLP
             buf = comm.out_buffer(rows, E, x.dtype)
-            torch.mm(a, mlp.proj.weight.t(), out=buf)
+            torch.mm(a, self.mlp.proj.weight.t(), out=buf)
             return comm.all_reduce(buf, residual=x2).view(B, T, E)
 
         def forward(self, x, token_idx, mha, chunk_sizes=None):

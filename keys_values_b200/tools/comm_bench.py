@@ -108,6 +108,8 @@ def main():
             out({"bench": "oneshot_allreduce_bf16_plus_residual", "world": world, "rows": rows, "features": feat, "bytes": rows * feat * 2,
                  "calls_per_graph": K, "fused_us_per_call": ms_f * 1e3, "nccl_plus_add_us_per_call": ms_n * 1e3,
                  "note": "each call includes a copy of the payload (the producer's write); graph replay, max over ranks"})
+            del g_f, g_n  # the graphs hold communicator work: gone before the buffers and the process group are
+            torch.cuda.synchronize()
         comm.close()
 
     # ---------------------------------------------------------------- all-reduce (gradient mean)
