@@ -1,25 +1,26 @@
-"""Tensor parallelism over KV heads with fused GEMM + collective kernels.
+"""Tensor parallelism over KV heads.
 
-Layout (per transformer block, ``tp`` ranks on one NVSwitch node):
+Two layers live here.
 
-* ``qkv`` and the MLP up projections are column parallel: rank ``r`` holds the
-  query heads / KV heads / MLP columns of its shard; the attention projection and
-  the MLP down projection are row parallel.
-* Between blocks the activations are sharded over *tokens* (sequence parallel).
-  A block therefore is: all-gather→QKV GEMM, local cache update + attention for
-  the rank's KV heads (cache policy state is per KV head, so eviction needs no
-  communication), attn-out GEMM→reduce-scatter (+ residual), all-gather→MLP-up
-  GEMM, MLP-down GEMM→reduce-scatter (+ residual).
+**Fused GEMM + collective kernels** (:class:`TPContext`, ``csrc/gemm_sm100.cu``). Between blocks the activations are
+sharded over *tokens*; a block is all-gather→QKV GEMM, local cache update + attention for the rank's KV heads (cache
+policy state is per KV head, so eviction needs no communication), attn-out GEMM→reduce-scatter (+ residual),
+all-gather→MLP-up GEMM, MLP-down GEMM→reduce-scatter (+ residual). The reduce-scatter is the GEMM's epilogue
+(finished tiles are stored straight into the owner rank's receive buffer over NVLink, remote owners first), and the
+all-gather feeds the GEMM's TMA producer chunk by chunk from a local staging buffer that copy CTAs of the same kernel
+fill from the peers.
 
-Both collectives are fused into the tcgen05 GEMM kernel of ``csrc/gemm_sm100.cu``:
-the reduce-scatter is the GEMM's epilogue (finished tiles are stored straight
-into the owner rank's receive buffer over NVLink, remote owners first), and the
-all-gather feeds the GEMM's TMA producer chunk by chunk from a local staging
-buffer that copy CTAs of the same kernel fill from the peers. NCCL is used only
-to exchange the IPC handles and in the reference path of the tests.
+**A sharded model that runs through the ordinary stack** (:class:`TPComm`, ``TPGPT`` / ``TPLoRAGPT``, ``TPBlock``).
+``qkv`` and the MLP up projections are column parallel, the attention and MLP output projections row parallel and end
+in this package's all-reduce (``csrc/comm.cu``: one-shot kernel for the rows of a decode step, fused with the residual
+add and the next RMSNorm; two-shot kernel for prefill chunks); chunks whose rows divide by ``128 · world`` may take the
+fused path above. Caches, chunked inference, generation with the captured decode step, evaluation, autograd (LoRA
+included), data parallel x tensor parallel training and checkpoints of the whole model work as with a ``GPT``. The
+sharding rules are in :mod:`keys_values_b200.parallel.tp_shard`.
 
-The reference library has no tensor parallelism (``README.md:273-275``); this
-module is additive API.
+NCCL is used to exchange the IPC handles, for per-row scalars (vocabulary-parallel loss, gradient norm), to gather
+token-sharded rows at the end of a chunk, and in the reference paths of the tests. The reference library has no tensor
+parallelism (``README.md:273-275``); this module is additive API.
 """
 from __future__ import annotations
 
@@ -580,111 +581,9 @@ def vocab_parallel_cross_entropy(x: torch.Tensor, weight: torch.Tensor, targets:
     return torch.where(tg == ignore_index, torch.zeros_like(loss), loss)
 
 
-def local_config(config, world: int):
-    """The configuration of one rank's shard: heads, KV heads and MLP width divided by ``world``."""
-    import dataclasses
-
-    H, G, I = config.n_head, config.n_query_groups, config.intermediate_size
-    if G % world or I % world:
-        raise ValueError(f"n_query_groups = {G} and intermediate_size = {I} must be divisible by the tensor-parallel size {world}")
-    if config.norm_qk and config.norm_qk_type == "olmo2":
-        raise NotImplementedError("a QK norm over all heads at once cannot be sharded over heads")
-    if config.mlp_class_name == "LLaMAMoE":
-        raise NotImplementedError("mixture-of-experts blocks are not sharded")
-    return dataclasses.replace(config, n_head=H // world, n_query_groups=G // world, intermediate_size=I // world, head_size=config.head_size)  # keeps the class: LoRA fields survive
-
-
-def _shard_rule(key: str, config):
-    """How the tensor ``key`` of a whole model is split over ranks: ``(kind, axis)`` with kind in
-    ``rep`` (replicated), ``rank0`` (kept by rank 0, zero elsewhere: biases of row-parallel linears),
-    ``qkv`` (the q | k | v row segments, each split over KV groups), ``qkv_lora`` (the same for the rows of the
-    enabled segments of a LoRA ``B``), ``heads`` (the H·D axis), ``inter`` (the MLP axis)."""
-    leaf = key.rsplit(".", 1)[-1]
-    weight_like = leaf in ("weight", "bias")
-    if ".attn.qkv." in key:
-        if leaf == "lora_A":
-            return "rep", 0
-        if leaf == "lora_B":
-            return "qkv_lora", 0
-        return ("qkv", 0) if weight_like else ("rep", 0)
-    if ".attn.proj." in key:
-        if leaf == "weight" or leaf == "lora_A":
-            return "heads", 1
-        return ("rank0", 0) if leaf == "bias" else ("rep", 0)
-    if ".mlp.fc" in key:
-        if leaf == "lora_A":
-            return "rep", 0
-        return ("inter", 0) if (weight_like or leaf == "lora_B") else ("rep", 0)
-    if ".mlp.proj." in key:
-        if leaf == "weight" or leaf == "lora_A":
-            return "inter", 1
-        return ("rank0", 0) if leaf == "bias" else ("rep", 0)
-    return "rep", 0
-
-
-def _qkv_segments(config, rows: int):
-    """Row segments ``(start, rows_per_group)`` of a fused q | k | v tensor with ``rows`` rows: all three for the
-    projection itself, only the LoRA-enabled ones for a LoRA ``B``."""
-    H, G, D = config.n_head, config.n_query_groups, config.head_size
-    full = [(H // G) * D, D, D]  # rows per KV group of the q, k and v segments
-    if rows == (H + 2 * G) * D:
-        per_group = full
-    else:
-        enabled = [getattr(config, f"lora_{n}", False) for n in ("query", "key", "value")]
-        per_group = [w for w, e in zip(full, enabled) if e]
-        if rows != sum(per_group) * G:
-            raise ValueError(f"cannot interpret a fused qkv tensor with {rows} rows")
-    segs, start = [], 0
-    for w in per_group:
-        segs.append((start, w))
-        start += w * G
-    return segs
-
-
-def shard_state_dict(state_dict, config, world: int, rank: int):
-    """State dict of the whole model (plain or LoRA) → state dict of the shard of ``rank`` (see
-    :func:`local_config`). Column-parallel linears keep their rows and the rows of their LoRA ``B`` (``A`` is
-    replicated), row-parallel linears their columns and the columns of their LoRA ``A`` (``B`` is replicated)."""
-    G, I = config.n_query_groups, config.intermediate_size
-    D, gs = config.head_size, config.n_head // config.n_query_groups
-    g0, g1 = rank * (G // world), (rank + 1) * (G // world)
-    i0, i1 = rank * (I // world), (rank + 1) * (I // world)
-    out = {}
-    for key, t in state_dict.items():
-        kind, axis = _shard_rule(key, config)
-        if kind == "rep":
-            out[key] = t
-        elif kind == "rank0":
-            out[key] = t if rank == 0 else torch.zeros_like(t)
-        elif kind in ("qkv", "qkv_lora"):
-            out[key] = torch.cat([t[s + g0 * w : s + g1 * w] for s, w in _qkv_segments(config, t.shape[0])]).contiguous()
-        elif kind == "heads":
-            out[key] = t.narrow(axis, g0 * gs * D, (g1 - g0) * gs * D).contiguous()
-        else:
-            out[key] = t.narrow(axis, i0, i1 - i0).contiguous()
-    return out
-
-
-def unshard_state_dict(shards, config):
-    """Inverse of :func:`shard_state_dict`: the state dicts of all ranks (in rank order) → the whole model's."""
-    world = len(shards)
-    G = config.n_query_groups
-    out = {}
-    for key, t0 in shards[0].items():
-        kind, axis = _shard_rule(key, config)
-        if kind in ("rep", "rank0"):
-            out[key] = t0
-        elif kind in ("qkv", "qkv_lora"):
-            rows = t0.shape[0] * world
-            parts = []
-            for s, w in _qkv_segments(config, rows):
-                local_start = s // world
-                for sh in shards:
-                    parts.append(sh[key][local_start : local_start + w * (G // world)])
-            out[key] = torch.cat(parts).contiguous()
-        else:
-            out[key] = torch.cat([sh[key] for sh in shards], dim=axis).contiguous()
-    return out
+from keys_values_b200.parallel.tp_shard import (  # noqa: E402,F401  (re-exported)
+    _qkv_segments, _shard_rule, local_config, shard_state_dict, unshard_state_dict,
+)
 
 
 def gather_whole_state_dict(model, only_trainable: bool = False, dst: int = 0):
