@@ -56,7 +56,10 @@ struct BwParams {
   float* dk;            // (B,G,C,D) accumulated
   float* dv;
   int B, H, G, T, L, nT, nQT, gs, npos;
-  int hgs, hnpos;       // a 64-row half of a query tile covers hgs heads x hnpos positions
+  // Query rows are packed head-major: a 128-row tile of the dQ launch holds npos = 128 / gs (rounded down) positions
+  // x gs heads (rows_used of 128 rows), a 64-column unit of the dK/dV launch holds hnpos = 64 / gs positions x gs
+  // heads (cols_used of 64 columns); a column tile of the dK/dV launch is two units = npos_col positions, nCT tiles.
+  int rows_used, hnpos, cols_used, npos_col, nCT;
   long long tp_sb, tp_sg, dk_sb, dk_sg;
   float scale, scale_log2;
   int input_pos;
@@ -132,16 +135,17 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_row_tiles = MODE == MODE_DQ ? p.nQT : p.nT;
+  const int qtile_pos = MODE == MODE_DQ ? p.npos : p.npos_col;  // positions per query tile of this launch
   const int rt = blockIdx.x % n_row_tiles;                 // row tile: query tile (DQ) or KV tile (DKV)
   const int g = (blockIdx.x / n_row_tiles) % p.G;
   const int b = blockIdx.x / (n_row_tiles * p.G);
   const int32_t* tmin = p.tile_min + ((long long)b * p.G + g) * p.nT;
   const int32_t* tmax = p.tile_max + ((long long)b * p.G + g) * p.nT;
-  const int n_col_tiles = MODE == MODE_DQ ? p.nT : p.nQT;
+  const int n_col_tiles = MODE == MODE_DQ ? p.nT : p.nCT;
 
   // (kv tile t, query tile qt) is active iff some slot of t is visible to some query of qt
-  auto qpos_min_of = [&](int qt) { return p.input_pos + qt * p.npos; };
-  auto qpos_max_of = [&](int qt) { return p.input_pos + min((qt + 1) * p.npos, p.T) - 1; };
+  auto qpos_min_of = [&](int qt) { return p.input_pos + qt * qtile_pos; };
+  auto qpos_max_of = [&](int qt) { return p.input_pos + min((qt + 1) * qtile_pos, p.T) - 1; };
   auto active_g = [&](int ct) -> bool {
     return MODE == MODE_DQ ? (tmin[ct] <= qpos_max_of(rt)) : (tmin[rt] <= qpos_max_of(ct));
   };
@@ -160,6 +164,25 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
     return ct;
   };
 
+  // Rows that no TMA box ever writes (group sizes that do not divide the tile: 128 − rows_used rows of the row
+  // operands in the dQ launch, 64 − cols_used rows of every streamed unit in the dK/dV launch) are zeroed once: they
+  // enter MMAs as operand rows, and 0 · anything finite is 0 while stale shared memory could hold NaN patterns.
+  if (MODE == MODE_DQ && p.rows_used < 128) {
+    const int n16 = (128 - p.rows_used) * 8;  // 16-byte pieces per 64-feature chunk
+    for (int i = threadIdx.x; i < 4 * n16; i += BW_THREADS) {
+      uint8_t* chunk = smem + (i / n16 < 2 ? S::R1 : S::R2) + ((i / n16) & 1) * (BW_TILE_BYTES / 2);
+      *reinterpret_cast<uint4*>(chunk + p.rows_used * 128 + (i % n16) * 16) = make_uint4(0, 0, 0, 0);
+    }
+    fence_proxy_async_smem();
+  }
+  if (MODE == MODE_DKV && p.cols_used < 64) {
+    const int n16 = (64 - p.cols_used) * 8;
+    for (int i = threadIdx.x; i < BW_STAGES * 4 * n16; i += BW_THREADS) {
+      uint8_t* chunk = smem + S::C + (i / n16) * (BW_UNIT_BYTES / 2);  // stage-major: C1 lo | C1 hi | C2 lo | C2 hi
+      *reinterpret_cast<uint4*>(chunk + p.cols_used * 128 + (i % n16) * 16) = make_uint4(0, 0, 0, 0);
+    }
+    fence_proxy_async_smem();
+  }
   if (threadIdx.x == 0) {
     mbar_init(r_full, 1);
     for (int s = 0; s < BW_STAGES; ++s) {
@@ -202,7 +225,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
       tma_prefetch_desc(&tmR2);
       tma_prefetch_desc(&tmC1);
       tma_prefetch_desc(&tmC2);
-      mbar_expect_tx(r_full, 2 * BW_TILE_BYTES);
+      mbar_expect_tx(r_full, MODE == MODE_DQ ? (uint32_t)(4 * p.rows_used * 128) : (uint32_t)(2 * BW_TILE_BYTES));
       {
         const int c1 = MODE == MODE_DQ ? rt * p.npos : rt * 128;
         const int c2 = MODE == MODE_DQ ? g * p.gs : g;
@@ -224,14 +247,11 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
           if (MODE == MODE_DQ) {
             x1 = ct * 128 + h * 64;
             x2 = g;
-          } else if (p.gs >= 2) {
-            x1 = ct * p.npos;
-            x2 = g * p.gs + h * p.hgs;
-          } else {
-            x1 = ct * p.npos + h * 64;
-            x2 = g;
+          } else {  // unit h of query tile ct: hnpos positions x all gs heads of the group
+            x1 = ct * p.npos_col + h * p.hnpos;
+            x2 = g * p.gs;
           }
-          mbar_expect_tx(&c_full[st], 2 * BW_UNIT_BYTES);
+          mbar_expect_tx(&c_full[st], MODE == MODE_DQ ? (uint32_t)(2 * BW_UNIT_BYTES) : (uint32_t)(4 * p.cols_used * 128));
           tma_load_4d(c1, &tmC1, &c_full[st], 0, x1, x2, b);
           tma_load_4d(c1 + BW_UNIT_BYTES / 2, &tmC1, &c_full[st], 64, x1, x2, b);
           tma_load_4d(c2, &tmC2, &c_full[st], 0, x1, x2, b);
@@ -366,7 +386,8 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
     if (MODE == MODE_DQ) {
       hq = row / p.npos;
       tq = rt * p.npos + row % p.npos;
-      row_valid = tq < p.T;
+      row_valid = row < p.rows_used && tq < p.T;
+      if (!row_valid) hq = 0;
       row_pos = p.input_pos + tq;
       if (row_valid) {
         const long long idx = ((long long)b * p.H + g * p.gs + hq) * p.T + tq;
@@ -381,9 +402,11 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
     // MODE_DKV: statistics of query tile ct, column cc <-> (head cc / npos, position cc % npos);
     // threads 0..127 fetch −lse·log2(e), threads 128..255 fetch −delta·scale
     auto fetch_stat = [&](int ct) -> float {
-      const int cc = tid & 127;
-      const int c_hq = cc / p.npos, c_tq = ct * p.npos + cc % p.npos;
-      if (ct >= n_col_tiles || c_tq >= p.T) return tid < 128 ? -INFINITY : 0.f;
+      const int cc = tid & 127;                       // column of the tile: unit cc / 64, column cu of the unit
+      const int cu = cc & 63;
+      const int c_hq = cu / p.hnpos, c_tq = ct * p.npos_col + (cc >> 6) * p.hnpos + cu % p.hnpos;
+      // columns beyond the unit's heads (padding) and positions beyond the chunk: P = exp2(x − inf) = 0, dS = 0
+      if (ct >= n_col_tiles || cu >= p.cols_used || c_tq >= p.T) return tid < 128 ? -INFINITY : 0.f;
       const long long idx = ((long long)b * p.H + g * p.gs + c_hq) * p.T + c_tq;
       return tid < 128 ? -p.lse[idx] * 1.4426950408889634f : -p.delta[idx] * p.scale;
     };
@@ -438,7 +461,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
       float stat_next = 0.f;
       if (MODE == MODE_DKV) stat_next = fetch_stat(ct_next);  // in flight while this tile is processed
       const int sbuf = s & 1;
-      const int cpos0 = p.input_pos + ct * p.npos;  // MODE_DKV: position of column cc is cpos0 + cc % npos
+      const int cpos0 = p.input_pos + ct * p.npos_col;  // MODE_DKV: first position of the query tile
       for (int h = 0; h < 2 && ok; ++h) {
         const int cc0 = 64 * h + 32 * hh;  // first column of this thread within the 128-column tile
         // MODE_DQ: lane holds the token position of column cc0 + lane (asked for before the wait)
@@ -471,8 +494,14 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
               hide |= (uint32_t)(__shfl_sync(0xffffffffu, v_tp, e) > row_pos) << e;
             }
           } else if (__any_sync(0xffffffffu, row_tp > cpos0)) {
+            // column cu of unit h holds position cpos0 + h·hnpos + cu % hnpos (head-major columns)
+            const int upos0 = cpos0 + h * p.hnpos;
+            int pp_ = (32 * hh) % p.hnpos;
 #pragma unroll
-            for (int e = 0; e < 32; ++e) hide |= (uint32_t)(row_tp > cpos0 + ((cc0 + e) & (p.npos - 1))) << e;
+            for (int e = 0; e < 32; ++e) {
+              hide |= (uint32_t)(row_tp > upos0 + pp_) << e;
+              pp_ = pp_ + 1 == p.hnpos ? 0 : pp_ + 1;
+            }
           }
         }
         uint32_t pk[16], dk_[16];
@@ -632,13 +661,14 @@ extern "C" int kvb_sdpa_bwd(const void* q, const void* k, const void* v, const i
   using namespace kvb;
   if (B <= 0 || H <= 0 || G <= 0 || q_len <= 0 || kv_len <= 0 || H % G) return KVB_ERR_ARG;
   const int gs = H / G;
-  if (gs > 128 || (gs & (gs - 1))) return KVB_ERR_UNSUPPORTED;
+  if (gs > 64) return KVB_ERR_UNSUPPORTED;  // a 64-column unit of the dK/dV launch holds all heads of a group
   if ((k_sb % 8) || (k_sg % 8) || (dk_sb % 4) || (dk_sg % 4)) return KVB_ERR_ALIGN;
   cudaStream_t s = (cudaStream_t)stream;
   BwParams p;
   p.B = B; p.H = H; p.G = G; p.T = q_len; p.L = kv_len;
-  p.gs = gs; p.npos = 128 / gs;
-  p.hgs = gs >= 2 ? gs / 2 : 1; p.hnpos = 64 / p.hgs;
+  p.gs = gs; p.npos = 128 / gs; p.rows_used = p.npos * gs;
+  p.hnpos = 64 / gs; p.cols_used = p.hnpos * gs; p.npos_col = 2 * p.hnpos;
+  p.nCT = (q_len + p.npos_col - 1) / p.npos_col;
   p.nT = (kv_len + 127) / 128;
   p.nQT = (q_len + p.npos - 1) / p.npos;
   p.token_pos = token_pos; p.tp_sb = tp_sb; p.tp_sg = tp_sg;
@@ -652,16 +682,17 @@ extern "C" int kvb_sdpa_bwd(const void* q, const void* k, const void* v, const i
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
   p.input_pos = input_pos; p.status = status;
 
-  // full (128-row) boxes for the row operands, half (64-row) boxes for the streamed units
+  // row operands: boxes of npos positions x gs heads (dQ launch) or 128 slots (dK/dV launch); streamed units: boxes of
+  // 64 slots (dQ launch) or hnpos positions x gs heads (dK/dV launch)
   CUtensorMap tmQ, tmdO, tmK, tmV, tmQh, tmdOh, tmKh, tmVh;
   int rc;
   const uint64_t qT = (uint64_t)q_len, HT = (uint64_t)H * q_len;
   // Q (B,H,T,D): dims (D,T,H,B)
   if ((rc = bw_make_tmap_4d(&tmQ, q, 128, q_len, H, B, 128, qT * 128, HT * 128, 64, p.npos, gs))) return rc;
-  if ((rc = bw_make_tmap_4d(&tmQh, q, 128, q_len, H, B, 128, qT * 128, HT * 128, 64, p.hnpos, p.hgs))) return rc;
+  if ((rc = bw_make_tmap_4d(&tmQh, q, 128, q_len, H, B, 128, qT * 128, HT * 128, 64, p.hnpos, gs))) return rc;
   // dO (B,T,H,D) viewed with dims (D,T,H,B): T stride H*D, H stride D
   if ((rc = bw_make_tmap_4d(&tmdO, dout, 128, q_len, H, B, (uint64_t)H * 128, 128, HT * 128, 64, p.npos, gs))) return rc;
-  if ((rc = bw_make_tmap_4d(&tmdOh, dout, 128, q_len, H, B, (uint64_t)H * 128, 128, HT * 128, 64, p.hnpos, p.hgs))) return rc;
+  if ((rc = bw_make_tmap_4d(&tmdOh, dout, 128, q_len, H, B, (uint64_t)H * 128, 128, HT * 128, 64, p.hnpos, gs))) return rc;
   if ((rc = bw_make_tmap_4d(&tmK, k, 128, kv_len, G, B, 128, k_sg, k_sb, 64, 128, 1))) return rc;
   if ((rc = bw_make_tmap_4d(&tmV, v, 128, kv_len, G, B, 128, k_sg, k_sb, 64, 128, 1))) return rc;
   if ((rc = bw_make_tmap_4d(&tmKh, k, 128, kv_len, G, B, 128, k_sg, k_sb, 64, 64, 1))) return rc;

@@ -493,28 +493,9 @@ def sdpa_supported(query: torch.Tensor, key: torch.Tensor, sliding_window, softc
 
 
 def sdpa_bwd_supported(query: torch.Tensor, key: torch.Tensor, sliding_window, softcap) -> bool:
-    """Same shapes as the forward. The backward kernels pack the heads of a group into the 128-row tile by
-    powers of two; other group sizes (5: Qwen3-14B, 7: Qwen2.5-7B) are padded to the next power of two with
-    heads that contribute nothing (see :func:`sdpa_bwd`)."""
-    return sdpa_supported(query, key, sliding_window, softcap)
-
-
-def _pad_group_heads(query, grad_out, out, lse, G: int):
-    """Pads every KV group from ``gs`` to the next power of two heads. The extra heads have zero queries, zero
-    output gradients and a huge log-sum-exp: their probabilities are exactly 0, so are their contributions to dK
-    and dV, and their dQ rows are dropped by the caller."""
-    B, H, T, D = query.shape
-    gs = H // G
-    gp = 1 << (gs - 1).bit_length()
-    q = query.new_zeros((B, G, gp, T, D))
-    q[:, :, :gs] = query.view(B, G, gs, T, D)
-    go = grad_out.new_zeros((B, T, G, gp, D))
-    go[:, :, :, :gs] = grad_out.view(B, T, G, gs, D)
-    o = out.new_zeros((B, T, G, gp, D))
-    o[:, :, :, :gs] = out.view(B, T, G, gs, D)
-    l = lse.new_full((B, G, gp, T), 1e30)
-    l[:, :, :gs] = lse.view(B, G, gs, T)
-    return q.view(B, G * gp, T, D), go.view(B, T, G * gp * D), o.view(B, T, G * gp * D), l.view(B, G * gp, T), gs, gp
+    """Same shapes as the forward, with at most 64 query heads per KV head (a 64-column unit of the dK/dV launch
+    holds all heads of a group). Any group size: 5 (Qwen3-14B) packs 25 positions x 5 heads into the 128-row tile."""
+    return sdpa_supported(query, key, sliding_window, softcap) and query.shape[1] // key.shape[1] <= 64
 
 
 def sdpa_fwd(query, key, value, scale, input_pos, token_pos=None, return_weights=False):
@@ -569,11 +550,6 @@ def sdpa_bwd(grad_out, query, key, value, out, lse, scale, input_pos, token_pos=
     query = query.contiguous()
     grad_out = grad_out.contiguous()
     out = out.contiguous()
-    gs_real = H // G
-    padded = (gs_real & (gs_real - 1)) != 0
-    if padded:
-        query, grad_out, out, lse, gs_real, gs_pad = _pad_group_heads(query, grad_out, out, lse.contiguous(), G)
-        H_real, H = H, G * gs_pad
     if key.stride(3) != 1 or key.stride(2) != D or key.stride() != value.stride():
         key, value = key.contiguous(), value.contiguous()
     token_pos = _norm_token_pos(token_pos, B, G, L)
@@ -594,8 +570,6 @@ def sdpa_bwd(grad_out, query, key, value, out, lse, scale, input_pos, token_pos=
                               _ll(dk_accum.stride(0)), _ll(dk_accum.stride(1)), ctypes.c_float(scale), int(input_pos), _p(st),
                               _stream(query)), "sdpa_bwd")
     _count(4)
-    if padded:
-        dq = dq.view(B, G, gs_pad, T, D)[:, :, :gs_real].reshape(B, H_real, T, D)
     if own:
         return dq, dk_accum, dv_accum
     return dq, None, None

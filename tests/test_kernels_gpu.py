@@ -275,7 +275,8 @@ def _rel_err(a, b):
 
 @pytest.mark.parametrize("B,H,G,T,L,mode", [(1, 4, 1, 32, 128, "arange"), (1, 8, 2, 256, 256, "prefill"), (2, 8, 2, 100, 1000, "perm"),
                                              (1, 32, 8, 256, 2048, "perm"), (1, 4, 4, 64, 300, "perm"),
-                                             (1, 10, 2, 100, 700, "perm"), (2, 7, 1, 64, 300, "arange")])  # group sizes 5 and 7: padded heads
+                                             (1, 10, 2, 100, 700, "perm"), (2, 7, 1, 64, 300, "arange"), (1, 40, 8, 130, 1024, "perm"),
+                                             (1, 3, 1, 50, 200, "perm"), (1, 12, 2, 77, 500, "perm")])  # group sizes 5, 7, 3, 6: rows and columns of a tile not all used
 def test_sdpa_bwd(B, H, G, T, L, mode):
     if mode == "prefill":
         mode = "arange"
