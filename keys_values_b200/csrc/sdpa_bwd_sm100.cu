@@ -57,9 +57,13 @@ struct BwParams {
   float* dv;
   int B, H, G, T, L, nT, nQT, gs, npos;
   // Query rows are packed head-major: a 128-row tile of the dQ launch holds npos = 128 / gs (rounded down) positions
-  // x gs heads (rows_used of 128 rows), a 64-column unit of the dK/dV launch holds hnpos = 64 / gs positions x gs
-  // heads (cols_used of 64 columns); a column tile of the dK/dV launch is two units = npos_col positions, nCT tiles.
+  // x gs heads (rows_used of 128 rows), a 64-column unit of the dK/dV launch holds hnpos positions x u_heads
+  // heads (cols_used of 64 columns); a column tile of the dK/dV launch is two units and spans npos_col positions.
   int rows_used, hnpos, cols_used, npos_col, nCT;
+  // Unit h of a column tile holds u_heads heads x hnpos positions, from head h·u_dh and position h·u_dp of the tile:
+  // half of the heads over all positions of the tile when the group size is an even power of two (u_dh = gs / 2,
+  // u_dp = 0), all heads over half of the positions otherwise (u_dh = 0, u_dp = hnpos).
+  int u_heads, u_dh, u_dp;
   long long tp_sb, tp_sg, dk_sb, dk_sg;
   float scale, scale_log2;
   int input_pos;
@@ -247,9 +251,9 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
           if (MODE == MODE_DQ) {
             x1 = ct * 128 + h * 64;
             x2 = g;
-          } else {  // unit h of query tile ct: hnpos positions x all gs heads of the group
-            x1 = ct * p.npos_col + h * p.hnpos;
-            x2 = g * p.gs;
+          } else {  // unit h of query tile ct
+            x1 = ct * p.npos_col + h * p.u_dp;
+            x2 = g * p.gs + h * p.u_dh;
           }
           mbar_expect_tx(&c_full[st], MODE == MODE_DQ ? (uint32_t)(2 * BW_UNIT_BYTES) : (uint32_t)(4 * p.cols_used * 128));
           tma_load_4d(c1, &tmC1, &c_full[st], 0, x1, x2, b);
@@ -404,7 +408,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
     auto fetch_stat = [&](int ct) -> float {
       const int cc = tid & 127;                       // column of the tile: unit cc / 64, column cu of the unit
       const int cu = cc & 63;
-      const int c_hq = cu / p.hnpos, c_tq = ct * p.npos_col + (cc >> 6) * p.hnpos + cu % p.hnpos;
+      const int c_hq = (cc >> 6) * p.u_dh + cu / p.hnpos, c_tq = ct * p.npos_col + (cc >> 6) * p.u_dp + cu % p.hnpos;
       // columns beyond the unit's heads (padding) and positions beyond the chunk: P = exp2(x − inf) = 0, dS = 0
       if (ct >= n_col_tiles || cu >= p.cols_used || c_tq >= p.T) return tid < 128 ? -INFINITY : 0.f;
       const long long idx = ((long long)b * p.H + g * p.gs + c_hq) * p.T + c_tq;
@@ -495,12 +499,17 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
             }
           } else if (__any_sync(0xffffffffu, row_tp > cpos0)) {
             // column cu of unit h holds position cpos0 + h·hnpos + cu % hnpos (head-major columns)
-            const int upos0 = cpos0 + h * p.hnpos;
-            int pp_ = (32 * hh) % p.hnpos;
+            const int upos0 = cpos0 + h * p.u_dp;
+            if ((p.hnpos & (p.hnpos - 1)) == 0) {
 #pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              hide |= (uint32_t)(row_tp > upos0 + pp_) << e;
-              pp_ = pp_ + 1 == p.hnpos ? 0 : pp_ + 1;
+              for (int e = 0; e < 32; ++e) hide |= (uint32_t)(row_tp > upos0 + ((32 * hh + e) & (p.hnpos - 1))) << e;
+            } else {
+              int pp_ = (32 * hh) % p.hnpos;
+#pragma unroll
+              for (int e = 0; e < 32; ++e) {
+                hide |= (uint32_t)(row_tp > upos0 + pp_) << e;
+                pp_ = pp_ + 1 == p.hnpos ? 0 : pp_ + 1;
+              }
             }
           }
         }
@@ -667,7 +676,14 @@ extern "C" int kvb_sdpa_bwd(const void* q, const void* k, const void* v, const i
   BwParams p;
   p.B = B; p.H = H; p.G = G; p.T = q_len; p.L = kv_len;
   p.gs = gs; p.npos = 128 / gs; p.rows_used = p.npos * gs;
-  p.hnpos = 64 / gs; p.cols_used = p.hnpos * gs; p.npos_col = 2 * p.hnpos;
+  if (gs >= 2 && (gs & (gs - 1)) == 0) {  // half of the heads x all positions of the tile per unit
+    p.u_heads = gs / 2; p.u_dh = gs / 2; p.u_dp = 0;
+    p.hnpos = 128 / gs; p.npos_col = p.hnpos;
+  } else {                                 // all heads x half of the positions of the tile per unit
+    p.u_heads = gs; p.u_dh = 0;
+    p.hnpos = 64 / gs; p.u_dp = p.hnpos; p.npos_col = 2 * p.hnpos;
+  }
+  p.cols_used = p.hnpos * p.u_heads;
   p.nCT = (q_len + p.npos_col - 1) / p.npos_col;
   p.nT = (kv_len + 127) / 128;
   p.nQT = (q_len + p.npos - 1) / p.npos;
@@ -689,10 +705,10 @@ extern "C" int kvb_sdpa_bwd(const void* q, const void* k, const void* v, const i
   const uint64_t qT = (uint64_t)q_len, HT = (uint64_t)H * q_len;
   // Q (B,H,T,D): dims (D,T,H,B)
   if ((rc = bw_make_tmap_4d(&tmQ, q, 128, q_len, H, B, 128, qT * 128, HT * 128, 64, p.npos, gs))) return rc;
-  if ((rc = bw_make_tmap_4d(&tmQh, q, 128, q_len, H, B, 128, qT * 128, HT * 128, 64, p.hnpos, gs))) return rc;
+  if ((rc = bw_make_tmap_4d(&tmQh, q, 128, q_len, H, B, 128, qT * 128, HT * 128, 64, p.hnpos, p.u_heads))) return rc;
   // dO (B,T,H,D) viewed with dims (D,T,H,B): T stride H*D, H stride D
   if ((rc = bw_make_tmap_4d(&tmdO, dout, 128, q_len, H, B, (uint64_t)H * 128, 128, HT * 128, 64, p.npos, gs))) return rc;
-  if ((rc = bw_make_tmap_4d(&tmdOh, dout, 128, q_len, H, B, (uint64_t)H * 128, 128, HT * 128, 64, p.hnpos, gs))) return rc;
+  if ((rc = bw_make_tmap_4d(&tmdOh, dout, 128, q_len, H, B, (uint64_t)H * 128, 128, HT * 128, 64, p.hnpos, p.u_heads))) return rc;
   if ((rc = bw_make_tmap_4d(&tmK, k, 128, kv_len, G, B, 128, k_sg, k_sb, 64, 128, 1))) return rc;
   if ((rc = bw_make_tmap_4d(&tmV, v, 128, kv_len, G, B, 128, k_sg, k_sb, 64, 128, 1))) return rc;
   if ((rc = bw_make_tmap_4d(&tmKh, k, 128, kv_len, G, B, 128, k_sg, k_sb, 64, 64, 1))) return rc;
