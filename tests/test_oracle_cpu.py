@@ -17,35 +17,17 @@ DATA = Path(__file__).resolve().parent / "data"
 
 
 def _lora_model(seed=0, name="tiny-gpt", **kw):
-    torch.manual_seed(seed)
-    cfg = lora_mod.Config.from_name(name, lora_r=4, lora_alpha=8, lora_query=True, lora_key=True, lora_value=True, lora_projection=True, **kw)
-    m = lora_mod.GPT(cfg)
-    m.apply(m._init_weights)
-    for n, p in m.named_parameters():
-        if "lora_B" in n:
-            torch.nn.init.normal_(p, std=0.05)
-    lora_mod.mark_only_lora_as_trainable(m)
-    return cfg, m
+    from keys_values_b200.kvcache.test_utils_advanced import small_lora_model
+
+    return small_lora_model(seed, name, **kw)
 
 
 def _engine_and_oracle(name, B=2, T=200, n_t=64, C=64, chunk=16, lpc=1, seed=0, **cache_kwargs):
-    _, m = _lora_model(seed)
-    head = CrossEntropyOnLogits(m.config)
-    g = torch.Generator().manual_seed(seed + 1)
-    ids, tg = torch.randint(0, 512, (B, T), generator=g), torch.randint(0, 512, (B, n_t), generator=g)
-    ck = dict(cache_kwargs)
-    if "h2o" in name:
-        ck.setdefault("max_chunk_size", chunk)
-    m.assign_kv_caches(KVCacheFactory.create(m, name, B, C, dtype=torch.float32, cache_kwargs=ck or None))
-    gm = LongContextGradientModel(m, head, layers_per_cell=lpc, chunk_size=chunk)
-    gm.train()
-    loss = gm(ids, tg)
-    logs, cells = list(gm._replay_logs), list(gm.cells)
-    loss.backward()
-    engine = {n: p.grad.clone() for n, p in m.named_parameters() if p.grad is not None}
-    m.zero_grad()
-    o_loss, oracle = oracle_loss_and_gradients(m, head, ids, tg, logs, cells)
-    return float(loss.value), engine, float(o_loss), oracle, logs, len(cells)
+    from keys_values_b200.kvcache.test_utils_advanced import oracle_for, run_gradient_case
+
+    case = run_gradient_case(name, B, T, n_t, C, chunk, lpc, seed, cache_kwargs=cache_kwargs)
+    o_loss, oracle = oracle_for(case)
+    return case.loss, case.gradients, o_loss, oracle, case.replay_logs, len(case.cells)
 
 
 @pytest.mark.parametrize("name", ["h2o-default", "h2o-vlen-default", "h2o-orig-default", "lastrec-default"])
@@ -192,3 +174,15 @@ if __name__ == "__main__":  # python tests/test_oracle_cpu.py  rewrites the froz
     DATA.mkdir(exist_ok=True)
     (DATA / "config1.json").write_text(json.dumps(compute_config1(), indent=1))
     print("written", DATA / "config1.json")
+
+
+def test_package_builders_for_gradient_tests():
+    """The helpers a test of a new policy would use: one call runs the step, one call checks it against the oracle."""
+    from keys_values_b200.kvcache.test_utils_advanced import assert_matches_oracle, run_gradient_case
+
+    case = run_gradient_case("h2o-default", batch_size=1, seq_length=160, num_targets=32, cache_length=48, chunk_size=16, layers_per_cell=2)
+    assert case.evicts and len(case.cells) > 1 and case.gradients
+    assert_matches_oracle(case)
+    case.gradients[next(iter(case.gradients))].add_(1e-2)
+    with pytest.raises(AssertionError):
+        assert_matches_oracle(case)
