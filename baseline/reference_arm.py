@@ -274,3 +274,110 @@ def run_reference(args) -> dict:
     if world > 1:
         dist.destroy_process_group()
     return result if rank == 0 else {}
+
+
+def run_reference_inference(args) -> dict:
+    """Config 4 through the reference's own generation path on ONE GPU (it has no tensor parallelism): the
+    construction sequence of its ``generate`` command (``keys_values/generate/base.py:436-640``: ``GPT(config)`` →
+    ``KVCacheFactory.create`` → ``LongContextInferenceModel`` → ``batched_generate_fn``) with random-init weights of
+    the named architecture. The first yield of its generator is the chunked prompt pass plus one sample (prefill),
+    the remaining yields are its single-token steps (decode); both are timed with CUDA events."""
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        return _unavailable("the reference has no tensor parallelism: its inference arm runs on one GPU only")
+    try:
+        _import_reference()
+    except Exception as ex:
+        return _unavailable(f"import of the reference failed: {type(ex).__name__}: {ex}")
+    import torch
+
+    on_cpu = not torch.cuda.is_available()
+    if on_cpu and not getattr(args, "ref_allow_cpu", False):
+        return _unavailable("the reference's inference arm is timed on a CUDA device")
+    from keys_values.config import Config
+    from keys_values.generate.base import batched_generate_fn
+    from keys_values.kvcache.factory import KVCacheFactory
+    from keys_values.long_context import LongContextInferenceModel
+    from keys_values.model import GPT
+    from litgpt.config import name_to_config
+
+    from bench import ClockSampler  # clock sampling only; no model or kernel code
+
+    model_name = "Llama-3-8B" if args.model == "Qwen3-4B" else args.model
+    seq = 65536 if args.seq_len == 131072 else args.seq_len
+    cache_name = "h2o-torch-quantized4" if args.cache_name == "h2o-torch-quantized8" else args.cache_name
+    cache_length = 8192 if args.cache_length == 16384 else args.cache_length
+    chunk = 2048 if args.chunk_size == 1024 else args.chunk_size
+    conf = dict(name_to_config[model_name]) if model_name in name_to_config else dict(TINY_CONFIGS[model_name])
+    if args.n_layer is not None:
+        conf["n_layer"] = args.n_layer
+    config = Config(**conf)
+    dev = torch.device("cpu") if on_cpu else torch.device("cuda", 0)
+    dtype = torch.float32 if on_cpu else torch.bfloat16
+    torch.manual_seed(0)
+    torch.set_default_dtype(dtype)
+    try:
+        with torch.device(dev):
+            gpt_model = GPT(config)
+    finally:
+        torch.set_default_dtype(torch.float32)
+    gpt_model.apply(gpt_model._init_weights)
+    gpt_model.assign_kv_caches(KVCacheFactory.create(gpt_model=gpt_model, name=cache_name, max_batch_size=args.batch, cache_length=cache_length,
+                                                     device=dev, dtype=dtype, cache_kwargs={"max_chunk_size": chunk} if "h2o" in cache_name else None))
+    gpt_model.eval()
+    model = LongContextInferenceModel(gpt_model=gpt_model, head_model=None, chunk_size=chunk)
+    gen = torch.Generator().manual_seed(7)
+    host_prompts = torch.randint(0, config.vocab_size, (args.batch, seq), generator=gen)
+    if not on_cpu:
+        host_prompts = host_prompts.pin_memory()
+    greedy = dict(temperature=0.0, top_p=0.0)
+    sampler = ClockSampler(0)
+    if not on_cpu:
+        sampler.start()
+
+    def event():
+        if on_cpu:
+            return time.perf_counter()
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        return e
+
+    def elapsed(a, b):
+        return (b - a) if on_cpu else a.elapsed_time(b) / 1e3
+
+    with torch.inference_mode():
+        # warm-up on a short prompt: kernel loading, Triton compilation, allocator
+        short = host_prompts[:, : min(seq, 2 * cache_length)].to(dev)
+        for k, _ in enumerate(batched_generate_fn(model, short, 4, sample_args=greedy)):
+            pass
+        if not on_cpu:
+            torch.cuda.synchronize(dev)
+        e0 = event()
+        prompts = host_prompts.to(dev, non_blocking=True)
+        out, e1 = [], None
+        for tokens in batched_generate_fn(model, prompts, args.decode, sample_args=greedy):
+            out.append(tokens)
+            if e1 is None:
+                e1 = event()  # the prompt pass and the first sampled token are behind us
+        host_tokens = torch.cat(out, dim=1).cpu()
+        e2 = event()
+        if not on_cpu:
+            torch.cuda.synchronize(dev)
+    t_pre, t_dec = elapsed(e0, e1), elapsed(e1, e2)
+    n_dec = max(host_tokens.shape[1] - 1, 1)
+    clocks = sampler.stop() if not on_cpu else {}
+    total = args.batch * (seq + host_tokens.shape[1]) / (t_pre + t_dec)
+    return {
+        "metric": "long-ctx inference tokens/s (prefill + decode)", "value": total, "unit": "tokens/s", "n_gpus": 1, "steps": 1,
+        "warmup": args.warmup, "ms_per_step": 1e3 * (t_pre + t_dec), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "fp32" if on_cpu else "bf16", "data": "synthetic uniform-random token ids, random-init weights", "impl": "reference",
+        "prefill_tokens_per_s": args.batch * seq / t_pre, "decode_tokens_per_s": args.batch * n_dec / t_dec,
+        "ms_per_decode_step": 1e3 * t_dec / n_dec,
+        "config": {"model": model_name + "-architecture" + (f" (REDUCED to {args.n_layer} layers)" if args.n_layer else ""),
+                   "global_batch": args.batch, "seq_len": seq, "parallelism": "tp1", "cache": cache_name, "cache_length": cache_length,
+                   "chunk_size": chunk, "decode_tokens": int(host_tokens.shape[1]),
+                   "note": "the reference's generate path: chunked prompt pass, then eager single-token steps"},
+        "clocks": clocks,
+        "e2e": {"value": total, "unit": "tokens/s", "h2d_bytes_per_step": host_prompts.numel() * host_prompts.element_size(),
+                "d2h_bytes_per_step": host_tokens.numel() * host_tokens.element_size()},
+        "peak_mem_gb": 0.0 if on_cpu else torch.cuda.max_memory_allocated(dev) / 2**30,
+    }

@@ -253,9 +253,17 @@ def run_inference(args) -> dict:
 def main():
     args = parse_args()
     if args.config == "inference" and args.impl == "reference":
-        # the reference has no tensor parallelism and no chunked-inference benchmark of this shape
-        print(json.dumps({"impl": "reference", "unavailable": "the inference configuration has a reference arm at the kernel level only "
-                          "(keys_values_b200.tools.microbench reference); the reference library has no tensor parallelism"}), flush=True)
+        from baseline.reference_arm import run_reference_inference
+
+        try:
+            out = run_reference_inference(args)
+        except Exception as ex:
+            import traceback
+
+            traceback.print_exc()
+            out = {"impl": "reference", "unavailable": f"the reference's own code raised {type(ex).__name__}: {str(ex)[:300]}"}
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps(out), flush=True)
         return
     if args.config == "inference":
         out = run_inference(args)

@@ -58,3 +58,15 @@ def test_reference_arm_runs_on_two_ranks():
     out = json.loads(lines[0])
     assert out["impl"] == "reference" and "unavailable" not in out, out
     assert out["n_gpus"] == 2 and out["value"] > 0
+
+
+@pytest.mark.skipif(not (ROOT / "baseline" / "_ref" / "keys_values").is_dir(), reason="reference not installed under baseline/_ref")
+def test_reference_inference_arm_runs_tiny_model_on_cpu():
+    """The inference configuration through the reference's own generation path (chunked prompt pass, eager steps)."""
+    cmd = [sys.executable, str(ROOT / "bench.py"), "--config", "inference", "--impl", "reference", "--ref-allow-cpu", "--model", "tiny-qwen3",
+           "--seq-len", "384", "--cache-length", "128", "--chunk-size", "64", "--batch", "2", "--decode", "6"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, cwd=ROOT, env={**__import__("os").environ, "CUDA_VISIBLE_DEVICES": ""})
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    out = json.loads([ln for ln in r.stdout.splitlines() if ln.startswith("{")][-1])
+    assert out["impl"] == "reference" and "unavailable" not in out, out
+    assert out["config"]["decode_tokens"] == 6 and out["prefill_tokens_per_s"] > 0 and out["decode_tokens_per_s"] > 0
