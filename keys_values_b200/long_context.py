@@ -229,7 +229,8 @@ class LongContextInferenceModel(GPTAndHeadModel):
             if len(sizes) > 1:
                 self.cells.append(ChunksForCell(1, tuple(sizes[1:]), sizes[0]))
         else:
-            cell_len = max(default_cell_length(gpt.config, max_c, self.chunks_per_cell_multiplier), 1)
+            # a tensor-parallel shard keeps the cell schedule of the whole model (its layer inputs are not sharded)
+            cell_len = max(default_cell_length(getattr(gpt, "full_config", gpt.config), max_c, self.chunks_per_cell_multiplier), 1)
             self.cells = get_chunks_for_cells(sizes, cell_len)
 
     # --------------------------------------------------------------- forward
