@@ -8,7 +8,7 @@ epoch (or longest first). Every rank takes its slice of each global batch. The p
 is part of ``state_dict`` so that training can resume mid-epoch."""
 from __future__ import annotations
 
-from typing import Any, Dict, Iterator, List, Optional, Sequence
+from typing import Any, Dict, Iterator, List, Sequence
 
 import torch
 

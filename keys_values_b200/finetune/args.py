@@ -4,7 +4,7 @@ Parity: ``keys_values/finetune/args.py:59-703``."""
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Dict, List, Optional, Tuple
+from typing import Any, Dict, List, Optional
 
 SUPPORTED_OPTIMIZERS = ("AdamW", "Adam", "SGD", "RMSprop", "Adagrad", "Adadelta", "Adamax")
 

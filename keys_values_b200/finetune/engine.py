@@ -8,7 +8,7 @@ builds on the same functions). Role of ``wrap_gpt_model`` and the inner part of
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Dict, List, Optional, Sequence
+from typing import Any, Dict, Optional, Sequence
 
 import torch
 

@@ -7,7 +7,7 @@ from the (quantized) cache storage. Parity: ``keys_values/generate/base.py:50-61
 """
 from __future__ import annotations
 
-from typing import Any, Dict, Iterator, List, Optional, Sequence, Tuple, Union
+from typing import Any, Iterator, List, Optional, Tuple, Union
 
 import torch
 

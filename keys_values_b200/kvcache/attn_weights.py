@@ -21,7 +21,6 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
-from keys_values_b200 import ops
 from keys_values_b200.attention.base import KeysAndValues
 from keys_values_b200.kvcache.base import KVCacheParams, KVCacheReplayLog
 from keys_values_b200.kvcache.basics import KVCacheWithBuffers

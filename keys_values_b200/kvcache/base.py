@@ -12,8 +12,8 @@ back to the host, so a (layer, chunk) step can be captured in a CUDA graph.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, replace
-from typing import Any, Dict, List, Optional, Tuple
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
 
 import torch
 

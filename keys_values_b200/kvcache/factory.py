@@ -6,15 +6,13 @@ torch-quantized4, torch-quantized8, bnb-quantized4, bnb-quantized8``.
 """
 from __future__ import annotations
 
-from dataclasses import replace
 from typing import Any, Dict, List, Optional, Tuple, Union
 
-import torch
 
 from keys_values_b200.config import Config
 from keys_values_b200.kvcache.base import KVCache, KVCacheParams
-from keys_values_b200.kvcache.basics import DenseKVCache, KVCacheWithBuffers, LastRecentlyInsertedKVCache
-from keys_values_b200.kvcache.buffers import DefaultKVCacheBuffers, KVCacheBuffersParams
+from keys_values_b200.kvcache.basics import DenseKVCache, LastRecentlyInsertedKVCache
+from keys_values_b200.kvcache.buffers import DefaultKVCacheBuffers
 from keys_values_b200.kvcache.consts import SUPPORTED_QUANTIZERS, split_name
 from keys_values_b200.kvcache.h2o import H2OKVCache, H2OOriginalKVCache, VLengthH2OKVCache
 from keys_values_b200.kvcache.qh2o import QuantizedH2OKVCache, QuantizedVLengthH2OKVCache

@@ -27,7 +27,7 @@ that autograd cannot reorder them.
 """
 from __future__ import annotations
 
-from typing import Any, Dict, List, Optional
+from typing import Any, Dict, Optional
 
 import torch
 

@@ -2,7 +2,7 @@
 the unit of a row of cells in the backward pass."""
 from __future__ import annotations
 
-from typing import List, Optional, Sequence
+from typing import List, Sequence
 
 import torch
 

@@ -13,7 +13,7 @@ from typing import Any, Dict, Iterable, List, Optional, Sequence, Tuple
 
 import torch
 
-from keys_values_b200.attention.base import DefaultKeysAndValues, KeysAndValues
+from keys_values_b200.attention.base import KeysAndValues
 from keys_values_b200.config import Config
 from keys_values_b200.kvcache.base import KVCache, KVCacheParams
 from keys_values_b200.kvcache.factory import KVCacheFactory

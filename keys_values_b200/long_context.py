@@ -14,11 +14,10 @@ chunk by chunk; this keeps the GEMMs large enough for the tensor cores.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Callable, Dict, List, Optional, Tuple, Union
+from typing import Callable, List, Optional, Tuple
 
 import torch
 
-from keys_values_b200.attention.base import do_softcapping
 from keys_values_b200.models.head_model import HeadModel
 from keys_values_b200.models.model import GPT
 

@@ -13,7 +13,6 @@ dependency from one chunk to the next.
 """
 from __future__ import annotations
 
-import math
 from typing import Any, Callable, List, Optional, Sequence
 
 import torch

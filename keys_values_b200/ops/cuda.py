@@ -11,9 +11,8 @@ from __future__ import annotations
 
 import ctypes
 import math
-import os
 from pathlib import Path
-from typing import Optional, Tuple
+from typing import Optional
 
 import torch
 

@@ -15,7 +15,6 @@ Semantics follow the reference library:
 """
 from __future__ import annotations
 
-import math
 from typing import Optional, Tuple
 
 import torch

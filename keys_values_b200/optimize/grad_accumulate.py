@@ -6,7 +6,6 @@ scatter back.
 """
 from __future__ import annotations
 
-from typing import Optional
 
 import torch
 import torch.distributed as dist

@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import copy
 import re
-from typing import Dict, List, Tuple
+from typing import List, Tuple
 
 import torch
 

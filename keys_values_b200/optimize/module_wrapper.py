@@ -4,7 +4,7 @@ layout (name, offset, shape) recorded, so that whole shards move between host an
 one copy each."""
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, List, Tuple
 
 import torch
 

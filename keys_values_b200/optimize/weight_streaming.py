@@ -21,7 +21,7 @@ and every block is copied once per (cell, layer) or per row, whichever the pass 
 """
 from __future__ import annotations
 
-from typing import Callable, Dict, Iterable, List, Optional, Sequence, Tuple
+from typing import Callable, Dict, Iterable, List, Optional, Tuple
 
 import torch
 

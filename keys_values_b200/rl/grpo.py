@@ -6,7 +6,7 @@ chunked forward / cell-wise backward as supervised fine-tuning:
 """
 from __future__ import annotations
 
-from typing import Any, Callable, Dict, List, Optional, Sequence
+from typing import Any, Dict, List, Optional, Sequence
 
 import torch
 import torch.nn.functional as F

@@ -4,7 +4,7 @@ chunk instead of summing a loss, so policies with bounded KV caches can score se
 that do not fit a dense cache."""
 from __future__ import annotations
 
-from typing import List, Optional
+from typing import List
 
 import torch
 import torch.nn.functional as F

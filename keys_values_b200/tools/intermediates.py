@@ -3,7 +3,7 @@ register on a model, run two code paths (for example chunked vs whole-sequence f
 forward vs the recomputation inside the backward pass) and list where they start to differ."""
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, List, Tuple
 
 import torch
 

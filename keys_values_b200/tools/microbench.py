@@ -11,7 +11,6 @@ from __future__ import annotations
 import argparse
 import json
 import math
-import sys
 
 import torch
 
@@ -40,7 +39,6 @@ def time_fn(fn, iters=10, warmup=3, flush=None):
 
 def bench_sdpa(out, peaks):
     from keys_values_b200.ops import cuda as cu
-    from keys_values_b200.ops import reference as ref
 
     dev = torch.device("cuda")
     flush = _flush_buf(dev)

@@ -3,7 +3,7 @@ KV-cache setup (``keys_values/scripts/recompute_val_losses.py``); uses the evalu
 from __future__ import annotations
 
 from pathlib import Path
-from typing import List, Optional, Union
+from typing import Optional, Union
 
 from keys_values_b200.evaluation import longcontext_eval_ext as ext
 from keys_values_b200.finetune.args import EvalArgs, KVCacheArgs

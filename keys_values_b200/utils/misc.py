@@ -5,7 +5,7 @@ import csv
 import enum
 import time
 from pathlib import Path
-from typing import Any, Dict, Iterable, List, Optional, Union
+from typing import Any, Dict, List, Optional, Union
 
 import torch
 
