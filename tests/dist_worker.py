@@ -485,5 +485,47 @@ def case_dp_tp_train(rank, world, dev):
     setup.extras["tp_comm"].close()
 
 
+def case_tp_vocab_ce(rank, world, dev):
+    """Vocabulary-parallel cross-entropy: per-row losses, and the gradients with respect to the hidden states and the
+    head's weight, equal those of the whole-vocabulary loss (ignored targets included; vocabulary not divisible by the
+    number of ranks); the fused all-reduce + residual + RMSNorm falls back to separate ops off the GPU."""
+    from keys_values_b200.parallel.tp import TPComm, vocab_parallel_cross_entropy
+
+    cuda = dev.type == "cuda"
+    dtype = torch.bfloat16 if cuda else torch.float32
+    comm = TPComm(world, rank, dev, dtype=dtype)
+    g = torch.Generator().manual_seed(4)
+    rows, E, V = 37, 64, 1001
+    x0 = torch.randn(rows, E, generator=g).to(dev, dtype)
+    w0 = (torch.randn(V, E, generator=g) * 0.2).to(dev, dtype)
+    tg = torch.randint(0, V, (rows,), generator=g).to(dev)
+    tg[::5] = -100
+    x1, w1 = x0.clone().requires_grad_(True), w0.clone().requires_grad_(True)
+    want = torch.nn.functional.cross_entropy((x1 @ w1.t()).float(), tg, ignore_index=-100, reduction="none")
+    want.sum().backward()
+    x2, w2 = x0.clone().requires_grad_(True), w0.clone().requires_grad_(True)
+    got = vocab_parallel_cross_entropy(x2, w2, tg, comm)
+    got.sum().backward()
+    tol = dict(atol=3e-2, rtol=3e-2) if cuda else dict(atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(got, want, **tol)
+    torch.testing.assert_close(x2.grad.float(), x1.grad.float(), **tol)
+    torch.testing.assert_close(w2.grad.float(), w1.grad.float(), **tol)
+    # all-reduce + residual + RMSNorm in one call
+    part = torch.randn(4, E, generator=g).to(dev, dtype) + rank
+    res = torch.randn(4, E, generator=g).to(dev, dtype)
+    nw = torch.rand(E, generator=g).to(dev, dtype)
+    buf = comm.out_buffer(4, E, dtype)
+    buf.copy_(part)
+    x, normed = comm.all_reduce_add_norm(buf, res, nw, 1e-5)
+    total = part.float().clone()
+    dist.all_reduce(total)
+    want_x = (total + res.float()).to(dtype)
+    wf = want_x.float()
+    want_n = (wf * torch.rsqrt(wf.pow(2).mean(-1, keepdim=True) + 1e-5) * nw.float()).to(dtype)
+    torch.testing.assert_close(x.float(), want_x.float(), **tol)
+    torch.testing.assert_close(normed.float(), want_n.float(), **tol)
+    comm.close()
+
+
 if __name__ == "__main__":
     main()

@@ -74,6 +74,16 @@ def test_dp_x_tp_training_step_on_gpus():
     _run("dp_tp_train", 4)
 
 
+def test_tp_vocab_parallel_loss_on_cpu_ranks():
+    _run("tp_vocab_ce", 3)
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tp_vocab_parallel_loss_and_fused_norm_on_gpus():
+    _run("tp_vocab_ce", 2)
+
+
 def test_tp_lora_gradients_on_cpu_ranks():
     _run("tp_lora_grads", 2)
 
