@@ -94,14 +94,20 @@ class DecodeGraph:
         self.graph = torch.cuda.CUDAGraph()
         torch.cuda.synchronize(dev)
         comm = getattr(model, "tp_comm", None)  # tensor-parallel shard: its all-reduce calls take their epochs from a device word
-        with cu.device_position(self.word):
-            with torch.cuda.graph(self.graph):
-                if comm is not None:
-                    comm.begin_capture()
-                self.logits = model(self.tokens)
-                self.word.add_(1)  # a scalar operand: nothing outside the graph's own memory is read here
-                if comm is not None:
-                    comm.end_capture()
+        try:
+            with cu.device_position(self.word):
+                with torch.cuda.graph(self.graph):
+                    if comm is not None:
+                        comm.begin_capture()
+                    self.logits = model(self.tokens)
+                    self.word.add_(1)  # a scalar operand: nothing outside the graph's own memory is read here
+                    if comm is not None:
+                        comm.end_capture()
+        except BaseException:
+            if comm is not None:
+                comm._capturing = False  # a failed capture must not leave later eager calls on the graph's sites
+            self.graph = None
+            raise
         # Capturing ran the host side of one step (the caches' counters moved on) without running
         # its kernels: the first replay is that step.
 
