@@ -76,9 +76,10 @@ def test_streamed_weights_give_the_same_gradients_on_cpu(full, lpc):
 def test_streamed_weights_give_the_same_gradients_on_gpu(full):
     dev = torch.device("cuda", 0)
     (l0, g0, v0, _, _), (l1, g1, v1, ws, mm) = _run(dev, torch.bfloat16, "tiny-qwen3", full, 1, T=1152, C=384, cs=128)
-    # same kernels, same inputs, same order of operations: the streamed pass reproduces the resident one
+    # same kernels, same inputs, same order of operations: the streamed pass reproduces the resident one; the weight
+    # gradients of the norms are sums over rows by atomic adds, whose last bit may differ from run to run
     assert l0 == l1 and torch.equal(v0, v1)
     for k in g0:
-        torch.testing.assert_close(g1[k], g0[k], atol=0, rtol=0, msg=lambda m_: f"{k}: {m_}")
+        torch.testing.assert_close(g1[k], g0[k], atol=1e-6, rtol=8e-3, msg=lambda m_: f"{k}: {m_}")
     assert all(p.device.type == "cpu" and p.is_pinned() for p in ws.trainable_parameters())
     assert ws.resident_bytes() < sum(h.numel() * h.element_size() for h in ws.host) or len(ws.host) <= 2
