@@ -23,6 +23,7 @@
 // (keys_values/attention/sdpa_op.py:31-251) and the library SDPA backward it otherwise uses.
 #include <cuda.h>
 #include <limits.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "kvb200.h"
@@ -89,8 +90,10 @@ __device__ __forceinline__ float bw_exp2(float x) {
 }
 
 // delta[b,h,t] = sum_d dO[b,t,h,d] * O[b,t,h,d]
+// With dOt the kernel also leaves a head-major copy dOt[b,h,t,:] of dO (which it reads anyway): the TMA boxes of the
+// two launches then read runs of consecutive positions of one head, as they do for Q.
 __global__ void att_delta_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O,
-                                 float* __restrict__ delta, int B, int T, int H) {
+                                 float* __restrict__ delta, __nv_bfloat16* __restrict__ dOt, int B, int T, int H) {
   const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= (long long)B * T * H) return;
   const int lane = threadIdx.x & 31;
@@ -105,13 +108,13 @@ __global__ void att_delta_kernel(const __nv_bfloat16* __restrict__ dO, const __n
     s += x.x * y.x + x.y * y.y;
   }
   s = warp_sum(s);
-  if (lane == 0) {
-    const int h = (int)(row % H);
-    const long long bt = row / H;
-    const int t = (int)(bt % T);
-    const int b = (int)(bt / T);
-    delta[((long long)b * H + h) * T + t] = s;
-  }
+  const int h = (int)(row % H);
+  const long long bt = row / H;
+  const int t = (int)(bt % T);
+  const int b = (int)(bt / T);
+  const long long hrow = ((long long)b * H + h) * T + t;
+  if (dOt) *reinterpret_cast<uint2*>(dOt + hrow * 128 + lane * 4) = a;
+  if (lane == 0) delta[hrow] = s;
 }
 
 // tmR1/tmR2: row operands (boxes of 128 rows); tmC1/tmC2: column operands (boxes of 64 rows).
@@ -657,10 +660,11 @@ extern "C" int kvb_sdpa_bwd_set_trace(void* buf, int cap, int mode) {
   return KVB_OK;
 }
 
-// scratch: tile_min | tile_max (B*G*nT int32 each) | delta (B*H*T fp32)
+static long long bw_round4(long long n) { return (n + 3) / 4 * 4; }
+// scratch: tile_min | tile_max (B*G*nT int32 each) | delta (B*H*T fp32) | head-major copy of dO (B*H*T*128 bf16)
 extern "C" long long kvb_sdpa_bwd_scratch_bytes(int B, int H, int G, int q_len, int kv_len) {
   const long long nT = (kv_len + 127) / 128;
-  return (2LL * B * G * nT + (long long)B * H * q_len) * 4;
+  return (bw_round4(2LL * B * G * nT) + bw_round4((long long)B * H * q_len)) * 4 + (long long)B * H * q_len * 128 * 2;
 }
 
 extern "C" int kvb_sdpa_bwd(const void* q, const void* k, const void* v, const int32_t* token_pos, const void* out,
@@ -692,7 +696,12 @@ extern "C" int kvb_sdpa_bwd(const void* q, const void* k, const void* v, const i
   int32_t* sc = reinterpret_cast<int32_t*>(scratch);
   int32_t* tmin = sc;
   int32_t* tmax = sc + (long long)B * G * p.nT;
-  float* delta = reinterpret_cast<float*>(sc + 2LL * B * G * p.nT);
+  float* delta = reinterpret_cast<float*>(sc + bw_round4(2LL * B * G * p.nT));
+  static const int dout_headmajor = [] {
+    const char* e = getenv("KVB200_BWD_DOUT_T");  // "0": read dO in place (diagnostics)
+    return (e && e[0] == '0') ? 0 : 1;
+  }();
+  __nv_bfloat16* dOt = dout_headmajor ? reinterpret_cast<__nv_bfloat16*>(delta + bw_round4((long long)B * H * q_len)) : nullptr;
   p.tile_min = tmin; p.tile_max = tmax; p.lse = lse; p.delta = delta;
   p.dq = (__nv_bfloat16*)dq; p.dk = dk; p.dv = dv;
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
@@ -707,8 +716,13 @@ extern "C" int kvb_sdpa_bwd(const void* q, const void* k, const void* v, const i
   if ((rc = bw_make_tmap_4d(&tmQ, q, 128, q_len, H, B, 128, qT * 128, HT * 128, 64, p.npos, gs))) return rc;
   if ((rc = bw_make_tmap_4d(&tmQh, q, 128, q_len, H, B, 128, qT * 128, HT * 128, 64, p.hnpos, p.u_heads))) return rc;
   // dO (B,T,H,D) viewed with dims (D,T,H,B): T stride H*D, H stride D
-  if ((rc = bw_make_tmap_4d(&tmdO, dout, 128, q_len, H, B, (uint64_t)H * 128, 128, HT * 128, 64, p.npos, gs))) return rc;
-  if ((rc = bw_make_tmap_4d(&tmdOh, dout, 128, q_len, H, B, (uint64_t)H * 128, 128, HT * 128, 64, p.hnpos, p.u_heads))) return rc;
+  if (dOt) {  // the head-major copy that the delta kernel leaves: same strides as Q
+    if ((rc = bw_make_tmap_4d(&tmdO, dOt, 128, q_len, H, B, 128, qT * 128, HT * 128, 64, p.npos, gs))) return rc;
+    if ((rc = bw_make_tmap_4d(&tmdOh, dOt, 128, q_len, H, B, 128, qT * 128, HT * 128, 64, p.hnpos, p.u_heads))) return rc;
+  } else {
+    if ((rc = bw_make_tmap_4d(&tmdO, dout, 128, q_len, H, B, (uint64_t)H * 128, 128, HT * 128, 64, p.npos, gs))) return rc;
+    if ((rc = bw_make_tmap_4d(&tmdOh, dout, 128, q_len, H, B, (uint64_t)H * 128, 128, HT * 128, 64, p.hnpos, p.u_heads))) return rc;
+  }
   if ((rc = bw_make_tmap_4d(&tmK, k, 128, kv_len, G, B, 128, k_sg, k_sb, 64, 128, 1))) return rc;
   if ((rc = bw_make_tmap_4d(&tmV, v, 128, kv_len, G, B, 128, k_sg, k_sb, 64, 128, 1))) return rc;
   if ((rc = bw_make_tmap_4d(&tmKh, k, 128, kv_len, G, B, 128, k_sg, k_sb, 64, 64, 1))) return rc;
@@ -716,7 +730,7 @@ extern "C" int kvb_sdpa_bwd(const void* q, const void* k, const void* v, const i
 
   if ((rc = kvb_att_tile_minmax(token_pos, tmin, tmax, B, G, kv_len, tp_sb, tp_sg, 128, stream))) return rc;
   const long long rows = (long long)B * q_len * H;
-  att_delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, delta, B, q_len, H);
+  att_delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, delta, dOt, B, q_len, H);
   static kvb::PerDeviceOnce attr_once;
   if (attr_once.first()) {
     cudaFuncSetAttribute(sdpa_bwd_kernel<MODE_DQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwSmem::TOTAL);
