@@ -199,6 +199,15 @@ configs: List[dict] = [
         n_head=8, n_query_groups=2, head_size=128, intermediate_size=512, norm_qk=True,
         norm_eps=1e-6, rope_base=1000000, **_llama_like,
     ),
+    dict(  # Gemma-2 style: every other layer with a sliding window, capped attention scores and logits
+        name="tiny-gemma2",
+        block_size=4096, vocab_size=1024, padded_vocab_size=1024, n_layer=2, n_embd=256,
+        n_head=8, n_query_groups=2, head_size=128, intermediate_size=512, norm_eps=1e-6,
+        rotary_percentage=1.0, parallel_residual=False, bias=False, norm_class_name="RMSNorm",
+        mlp_class_name="GemmaMLP", gelu_approximate="tanh", scale_embeddings=True,
+        post_attention_norm=True, post_mlp_norm=True, sliding_window_size=96, sliding_window_indices=[1, 0],
+        attention_logit_softcapping=4.0, final_logit_softcapping=30.0,
+    ),
     dict(
         name="pythia-14m",
         block_size=512, n_layer=6, n_embd=128, n_head=4, padding_multiple=128,

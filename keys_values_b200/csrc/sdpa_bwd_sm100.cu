@@ -68,6 +68,11 @@ struct BwParams {
   long long tp_sb, tp_sg, dk_sb, dk_sg;
   float scale, scale_log2;
   int input_pos;
+  // Sliding window (0: none): a slot is visible to a query at position q iff q - window < token <= q.
+  // Soft-capping (cap_pre = 0: none): s' = cap·tanh(scale·s / cap) with cap_pre = scale / cap, cap_l2 = cap·log2(e);
+  // then P = exp2(cap_l2·t − lse·log2(e)) and dS = P (dP − δ) scale (1 − t²) with t = tanh(cap_pre·s).
+  int window;
+  float cap_pre, cap_l2;
   int* status;
   long long* trace;     // optional timeline of CTA 0: per role trace_cap (tag, clock) pairs
   int trace_cap;
@@ -87,6 +92,12 @@ __device__ __forceinline__ float bw_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// hardware tanh, as in the forward kernels (P must be recomputed from the same capped scores)
+__device__ __forceinline__ float bw_tanh(float z) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(z));
+  return t;
 }
 
 // delta[b,h,t] = sum_d dO[b,t,h,d] * O[b,t,h,d]
@@ -119,7 +130,9 @@ __global__ void att_delta_kernel(const __nv_bfloat16* __restrict__ dO, const __n
 
 // tmR1/tmR2: row operands (boxes of 128 rows); tmC1/tmC2: column operands (boxes of 64 rows).
 //   MODE_DQ : R1 = Q, R2 = dO, C1 = K, C2 = V      MODE_DKV: R1 = K, R2 = V, C1 = Q, C2 = dO
-template <int MODE>
+// GEN: sliding window and / or soft-capping are in use (separate instantiations, so that the plain kernels keep their
+// register allocation)
+template <int MODE, bool GEN>
 __global__ void __launch_bounds__(BW_THREADS, 1)
 sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ CUtensorMap tmR2,
                 const __grid_constant__ CUtensorMap tmC1, const __grid_constant__ CUtensorMap tmC2, const BwParams p) {
@@ -153,11 +166,16 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
   // (kv tile t, query tile qt) is active iff some slot of t is visible to some query of qt
   auto qpos_min_of = [&](int qt) { return p.input_pos + qt * qtile_pos; };
   auto qpos_max_of = [&](int qt) { return p.input_pos + min((qt + 1) * qtile_pos, p.T) - 1; };
+  // with a window, a tile is also inactive when its newest token has left the window of the first query, and
+  // masked when its oldest token has left the window of the last query
+  const int win = GEN ? p.window : 0;
   auto active_g = [&](int ct) -> bool {
-    return MODE == MODE_DQ ? (tmin[ct] <= qpos_max_of(rt)) : (tmin[rt] <= qpos_max_of(ct));
+    const int kt = MODE == MODE_DQ ? ct : rt, qt = MODE == MODE_DQ ? rt : ct;
+    return tmin[kt] <= qpos_max_of(qt) && (win <= 0 || tmax[kt] > qpos_min_of(qt) - win);
   };
   auto masked_g = [&](int ct) -> bool {
-    return MODE == MODE_DQ ? (tmax[ct] > qpos_min_of(rt)) : (tmax[rt] > qpos_min_of(ct));
+    const int kt = MODE == MODE_DQ ? ct : rt, qt = MODE == MODE_DQ ? rt : ct;
+    return tmax[kt] > qpos_min_of(qt) || (win > 0 && tmin[kt] <= qpos_max_of(qt) - win);
   };
   // the flags of the column tiles are kept in shared memory so that no role reads global memory
   // inside its tile loop
@@ -490,7 +508,27 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
         BW_TRACE(2, 2200000 + 2 * s + h);
         // bit e of `hide`: column cc0 + e is not visible to this thread's row
         uint32_t hide = 0;
-        if (msk) {
+        if (msk && win > 0) {
+          // visible iff 0 <= position of the query − token < window
+          if (MODE == MODE_DQ) {
+            uint32_t nm = __ballot_sync(0xffffffffu, v_tp > qpos_min_of(rt) || v_tp <= qpos_max_of(rt) - win);
+            while (nm) {
+              const int e = __ffs(nm) - 1;
+              nm &= nm - 1;
+              const int d = row_pos - __shfl_sync(0xffffffffu, v_tp, e);
+              hide |= (uint32_t)((uint32_t)d >= (uint32_t)win) << e;
+            }
+          } else {
+            const int upos0 = cpos0 + h * p.u_dp;
+            int pp_ = (32 * hh) % p.hnpos;
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              const int d = upos0 + pp_ - row_tp;
+              hide |= (uint32_t)((uint32_t)d >= (uint32_t)win) << e;
+              pp_ = pp_ + 1 == p.hnpos ? 0 : pp_ + 1;
+            }
+          }
+        } else if (msk) {
           if (MODE == MODE_DQ) {
             // only columns beyond the first query of the CTA need the per-row comparison
             // (positions broadcast by shuffle)
@@ -517,6 +555,30 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
           }
         }
         uint32_t pk[16], dk_[16];
+        if (GEN && p.cap_pre != 0.f) {
+          // capped scores: the raw score goes through tanh, and dS takes the factor 1 − tanh² of the cap
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            float2 nl, nd;
+            if (MODE == MODE_DQ) {
+              nl = make_float2(row_nlse, row_nlse);
+              nd = make_float2(row_ndls, row_ndls);
+            } else {
+              nl = *reinterpret_cast<const float2*>(stat_nlse + sbuf * 128 + cc0 + e);
+              nd = *reinterpret_cast<const float2*>(stat_ndls + sbuf * 128 + cc0 + e);
+            }
+            const float2 th = make_float2(bw_tanh(__uint_as_float(xr[e]) * p.cap_pre), bw_tanh(__uint_as_float(xr[e + 1]) * p.cap_pre));
+            const float2 xx = ffma2(th, make_float2(p.cap_l2, p.cap_l2), nl);
+            float2 pp = make_float2(bw_exp2(xx.x), bw_exp2(xx.y));
+            if (hide & (1u << e)) pp.x = 0.f;
+            if (hide & (1u << (e + 1))) pp.y = 0.f;
+            float2 tt = ffma2(make_float2(__uint_as_float(yr[e]), __uint_as_float(yr[e + 1])), sc2, nd);
+            tt = fmul2(tt, make_float2(fmaf(-th.x, th.x, 1.f), fmaf(-th.y, th.y, 1.f)));
+            const float2 ds = fmul2(pp, tt);
+            pk[e >> 1] = pack_bf16x2(pp.x, pp.y);
+            dk_[e >> 1] = pack_bf16x2(ds.x, ds.y);
+          }
+        } else
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
           float2 nl, nd;
@@ -667,12 +729,29 @@ extern "C" long long kvb_sdpa_bwd_scratch_bytes(int B, int H, int G, int q_len, 
   return (bw_round4(2LL * B * G * nT) + bw_round4((long long)B * H * q_len)) * 4 + (long long)B * H * q_len * 128 * 2;
 }
 
+// window: sliding window in tokens (0: none); softcap: logit soft-capping threshold (0: none), as in the forward.
+extern "C" int kvb_sdpa_bwd_ex(const void* q, const void* k, const void* v, const int32_t* token_pos, const void* out,
+                               const void* dout, const float* lse, void* dq, float* dk, float* dv, void* scratch, int B, int H,
+                               int G, int q_len, int kv_len, long long k_sb, long long k_sg, long long tp_sb, long long tp_sg,
+                               long long dk_sb, long long dk_sg, float scale, int input_pos, int window, float softcap,
+                               int* status, void* stream);
+
 extern "C" int kvb_sdpa_bwd(const void* q, const void* k, const void* v, const int32_t* token_pos, const void* out,
                             const void* dout, const float* lse, void* dq, float* dk, float* dv, void* scratch, int B, int H,
                             int G, int q_len, int kv_len, long long k_sb, long long k_sg, long long tp_sb, long long tp_sg,
                             long long dk_sb, long long dk_sg, float scale, int input_pos, int* status, void* stream) {
+  return kvb_sdpa_bwd_ex(q, k, v, token_pos, out, dout, lse, dq, dk, dv, scratch, B, H, G, q_len, kv_len, k_sb, k_sg, tp_sb, tp_sg,
+                         dk_sb, dk_sg, scale, input_pos, 0, 0.f, status, stream);
+}
+
+extern "C" int kvb_sdpa_bwd_ex(const void* q, const void* k, const void* v, const int32_t* token_pos, const void* out,
+                               const void* dout, const float* lse, void* dq, float* dk, float* dv, void* scratch, int B, int H,
+                               int G, int q_len, int kv_len, long long k_sb, long long k_sg, long long tp_sb, long long tp_sg,
+                               long long dk_sb, long long dk_sg, float scale, int input_pos, int window, float softcap,
+                               int* status, void* stream) {
   using namespace kvb;
   if (B <= 0 || H <= 0 || G <= 0 || q_len <= 0 || kv_len <= 0 || H % G) return KVB_ERR_ARG;
+  if (window < 0 || softcap < 0.f || (softcap > 0.f && scale <= 0.f)) return KVB_ERR_ARG;
   const int gs = H / G;
   if (gs > 64) return KVB_ERR_UNSUPPORTED;  // a 64-column unit of the dK/dV launch holds all heads of a group
   if ((k_sb % 8) || (k_sg % 8) || (dk_sb % 4) || (dk_sg % 4)) return KVB_ERR_ALIGN;
@@ -706,6 +785,9 @@ extern "C" int kvb_sdpa_bwd(const void* q, const void* k, const void* v, const i
   p.dq = (__nv_bfloat16*)dq; p.dk = dk; p.dv = dv;
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
   p.input_pos = input_pos; p.status = status;
+  p.window = window;
+  p.cap_pre = softcap > 0.f ? scale / softcap : 0.f;
+  p.cap_l2 = softcap * 1.4426950408889634f;
 
   // row operands: boxes of npos positions x gs heads (dQ launch) or 128 slots (dK/dV launch); streamed units: boxes of
   // 64 slots (dQ launch) or hnpos positions x gs heads (dK/dV launch)
@@ -733,8 +815,10 @@ extern "C" int kvb_sdpa_bwd(const void* q, const void* k, const void* v, const i
   att_delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, delta, dOt, B, q_len, H);
   static kvb::PerDeviceOnce attr_once;
   if (attr_once.first()) {
-    cudaFuncSetAttribute(sdpa_bwd_kernel<MODE_DQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwSmem::TOTAL);
-    cudaFuncSetAttribute(sdpa_bwd_kernel<MODE_DKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwSmem::TOTAL);
+    cudaFuncSetAttribute(sdpa_bwd_kernel<MODE_DQ, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwSmem::TOTAL);
+    cudaFuncSetAttribute(sdpa_bwd_kernel<MODE_DKV, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwSmem::TOTAL);
+    cudaFuncSetAttribute(sdpa_bwd_kernel<MODE_DQ, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwSmem::TOTAL);
+    cudaFuncSetAttribute(sdpa_bwd_kernel<MODE_DKV, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwSmem::TOTAL);
   }
   // The two launches are independent (dQ | dK, dV). They run on two streams, forked from and joined
   // back into the caller's stream, so that the tail of one grid (256 CTAs of the dQ launch fill
@@ -754,8 +838,13 @@ extern "C" int kvb_sdpa_bwd(const void* q, const void* k, const void* v, const i
   pq.trace = g_bw_trace_mode == 0 ? g_bw_trace : nullptr; pq.trace_cap = g_bw_trace_cap;
   p.trace = g_bw_trace_mode == 1 ? g_bw_trace : nullptr; p.trace_cap = g_bw_trace_cap;
   // the launch with few long CTAs goes first: the short CTAs of the other one fill its second wave
-  sdpa_bwd_kernel<MODE_DQ><<<B * G * p.nQT, BW_THREADS, BwSmem::TOTAL, side[dev]>>>(tmQ, tmdO, tmKh, tmVh, pq);
-  sdpa_bwd_kernel<MODE_DKV><<<B * G * p.nT, BW_THREADS, BwSmem::TOTAL, s>>>(tmK, tmV, tmQh, tmdOh, p);
+  if (window > 0 || softcap > 0.f) {
+    sdpa_bwd_kernel<MODE_DQ, true><<<B * G * p.nQT, BW_THREADS, BwSmem::TOTAL, side[dev]>>>(tmQ, tmdO, tmKh, tmVh, pq);
+    sdpa_bwd_kernel<MODE_DKV, true><<<B * G * p.nT, BW_THREADS, BwSmem::TOTAL, s>>>(tmK, tmV, tmQh, tmdOh, p);
+  } else {
+    sdpa_bwd_kernel<MODE_DQ, false><<<B * G * p.nQT, BW_THREADS, BwSmem::TOTAL, side[dev]>>>(tmQ, tmdO, tmKh, tmVh, pq);
+    sdpa_bwd_kernel<MODE_DKV, false><<<B * G * p.nT, BW_THREADS, BwSmem::TOTAL, s>>>(tmK, tmV, tmQh, tmdOh, p);
+  }
   cudaEventRecord(ev_join[dev], side[dev]);
   cudaStreamWaitEvent(s, ev_join[dev], 0);
   return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;

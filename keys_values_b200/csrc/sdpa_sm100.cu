@@ -2,6 +2,7 @@
 // normalisers, and a column-owner kernel for the per-slot weight sums.
 //
 //   out[b, t, h, :]   = softmax_j(scale · q[b,h,t]·k[b,g,j] | token_pos[b,g,j] <= input_pos + t) · v[b,g,:]
+//                       (optionally: only tokens newer than input_pos + t − window; scores soft-capped by cap·tanh(·/cap))
 //   lse[b, h, t]      = natural-log normaliser of that softmax
 //   weights[b, g, j]  = (1 / (H/G)) · sum over t and over the H/G heads of group g of the softmax weight of slot j
 //
@@ -101,7 +102,24 @@ struct F2Params {
   int n_split, tiles_per_split;
   float* part_o;             // (n_split, B, H, T, D)
   float* part_lse2;          // (n_split, B, H, T), -inf for a split that saw no visible slot
+  // Sliding window (0: none): a slot is visible to a query at position q iff q - window < token <= q.
+  // Logit soft-capping (cap_pre = 0: none): the score scale·s becomes cap·tanh(scale·s / cap); the kernels rewrite the
+  // raw score s as cap_post·tanh(cap_pre·s) with cap_pre = scale / cap, cap_post = cap / scale and go on as without.
+  int window;
+  float cap_pre, cap_post;
 };
+
+// Hardware tanh (one special-function operation, relative error about 5e-4: below the rounding of bf16 scores). The
+// exponentials already bound the softmax warps, so a tanh built from ex2 and rcp would cost twice as much again.
+__device__ __forceinline__ float f2_tanh(float z) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(z));
+  return t;
+}
+// the capped raw score; −inf (a slot hidden by the bias step of the MMA) stays −inf
+__device__ __forceinline__ float f2_softcap(float s, float pre, float post) {
+  return s == -INFINITY ? s : post * f2_tanh(pre * s);
+}
 
 // Optional phase profile of CTA 0 (diagnostics): each role adds the cycles spent since its previous mark to one of
 // eight counters and writes them once at the end, so that the measurement costs a clock read per mark.
@@ -239,6 +257,9 @@ __device__ __forceinline__ void f2_zero_unused_rows(uint8_t* tile, int rows_used
   }
 }
 
+// GEN: sliding window and / or soft-capping are in use (a separate instantiation, so that the plain kernel keeps its
+// register allocation)
+template <bool GEN>
 __global__ void __launch_bounds__(F2_THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const F2Params p) {
@@ -275,13 +296,21 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int split = p.n_split > 1 ? (int)blockIdx.y : 0;
   const int t_lo = p.n_split > 1 ? split * p.tiles_per_split : 0;
   const int t_hi = p.n_split > 1 ? min(p.nT, t_lo + p.tiles_per_split) : p.nT;
-  for (int t = threadIdx.x; t < min(p.nT, F2_MAX_FLAG_TILES); t += F2_THREADS)
-    tflags[t] = (t >= t_lo && t < t_hi) ? (uint8_t)((tmin[t] <= qpos_max) | ((tmax[t] > qpos_min) << 1)) : (uint8_t)0;
-  auto tile_bits = [&](int t) -> uint32_t {
-    if (t >= F2_MAX_FLAG_TILES)
-      return (t >= t_lo && t < t_hi) ? ((uint32_t)(tmin[t] <= qpos_max) | ((uint32_t)(tmax[t] > qpos_min) << 1)) : 0u;
-    return tflags[t];
+  // With a window, tokens at or below lo_all are hidden from every row of the CTA, those at or below lo_some from some row.
+  const int f_window = GEN ? p.window : 0;
+  const int lo_all = f_window > 0 ? qpos_min - f_window : INT_MIN;
+  const int lo_some = f_window > 0 ? qpos_max - f_window : INT_MIN;
+  const bool soft = GEN && p.cap_pre != 0.f;
+  constexpr bool general = GEN;  // masked tiles are then always treated element by element
+  auto calc_bits = [&](int t) -> uint32_t {
+    if (t < t_lo || t >= t_hi) return 0u;
+    const int lo = tmin[t], hi = tmax[t];
+    const uint32_t act = (lo <= qpos_max) && (hi > lo_all);
+    const uint32_t msk = (hi > qpos_min) || (lo <= lo_some) || soft;  // soft-capping rewrites every tile
+    return act | (msk << 1);
   };
+  for (int t = threadIdx.x; t < min(p.nT, F2_MAX_FLAG_TILES); t += F2_THREADS) tflags[t] = (uint8_t)calc_bits(t);
+  auto tile_bits = [&](int t) -> uint32_t { return t >= F2_MAX_FLAG_TILES ? calc_bits(t) : (uint32_t)tflags[t]; };
   if (p.rows_used < F2_T) {
     f2_zero_unused_rows(smem + F2Smem::Q, p.rows_used, threadIdx.x, F2_THREADS);
     f2_zero_unused_rows(smem + F2Smem::Q + F2_TILE_BYTES, p.rows_used, threadIdx.x, F2_THREADS);
@@ -364,10 +393,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           if (!ok) break;
           if (kv == 0 && (tb & 2u)) {
             uint8_t* kx = smem + F2Smem::KX + st * F2_BIAS_TILE_BYTES;
-            *reinterpret_cast<uint16_t*>(kx + f2_bias_offset(4 * lane + 0)) = pv.x > qpos_max ? 0xFF80 : 0;  // bf16 -inf
-            *reinterpret_cast<uint16_t*>(kx + f2_bias_offset(4 * lane + 1)) = pv.y > qpos_max ? 0xFF80 : 0;
-            *reinterpret_cast<uint16_t*>(kx + f2_bias_offset(4 * lane + 2)) = pv.z > qpos_max ? 0xFF80 : 0;
-            *reinterpret_cast<uint16_t*>(kx + f2_bias_offset(4 * lane + 3)) = pv.w > qpos_max ? 0xFF80 : 0;
+            *reinterpret_cast<uint16_t*>(kx + f2_bias_offset(4 * lane + 0)) = (pv.x > qpos_max || pv.x <= lo_all) ? 0xFF80 : 0;  // bf16 -inf
+            *reinterpret_cast<uint16_t*>(kx + f2_bias_offset(4 * lane + 1)) = (pv.y > qpos_max || pv.y <= lo_all) ? 0xFF80 : 0;
+            *reinterpret_cast<uint16_t*>(kx + f2_bias_offset(4 * lane + 2)) = (pv.z > qpos_max || pv.z <= lo_all) ? 0xFF80 : 0;
+            *reinterpret_cast<uint16_t*>(kx + f2_bias_offset(4 * lane + 3)) = (pv.w > qpos_max || pv.w <= lo_all) ? 0xFF80 : 0;
             fence_proxy_async_smem();
             __syncwarp();
           }
@@ -481,6 +510,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int tq = qt * p.npos + pl;
     const bool row_valid = row < p.rows_used && tq < p.T;
     const int my_pos = p.input_pos + tq;
+    const int my_lo = f_window > 0 ? my_pos - f_window : INT_MIN;  // tokens at or below are outside this row's window
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     const uint32_t tmem_S = tmem_base + (uint32_t)(wg * F2_T) + lane_base;
     const uint32_t tmem_O = tmem_base + (uint32_t)(2 * F2_T + wg * F2_T) + lane_base;
@@ -536,6 +566,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           m_some[cc] = cand & ~m_all[cc];
           n_cand += __popc(cand);
         }
+        if (general) n_cand = F2_T;  // window edges and capped scores: every element of the tile is looked at
       }
       {
         const int tn = next_active(t);
@@ -548,6 +579,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       F2_MARK(0);
       tc_fence_after();
+      float a8[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) a8[u] = -INFINITY;
+      bool have_max = false;  // GEN: the element pass below also takes the maximum of the row
       if (n_cand > F2_PATCH_MAX_COLS) {
         // element by element: the masked tile goes back to TMEM, the two passes below read it from there
         const int4* pp = reinterpret_cast<const int4*>(pos_row + (long long)t * F2_T);
@@ -556,18 +591,30 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           uint32_t x[32];
           tmem_ld_32x32b_x32(tmem_S + (uint32_t)c0, x);
           tmem_ld_wait();
+          if (soft) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) x[e] = __float_as_uint(f2_softcap(__uint_as_float(x[e]), p.cap_pre, p.cap_post));
+          }
 #pragma unroll
           for (int e = 0; e < 32; e += 4) {
             const int4 v = __ldg(pp + ((c0 + e) >> 2));
-            if (v.x > my_pos) x[e] = 0xff800000u;
-            if (v.y > my_pos) x[e + 1] = 0xff800000u;
-            if (v.z > my_pos) x[e + 2] = 0xff800000u;
-            if (v.w > my_pos) x[e + 3] = 0xff800000u;
+            if (v.x > my_pos || v.x <= my_lo) x[e] = 0xff800000u;
+            if (v.y > my_pos || v.y <= my_lo) x[e + 1] = 0xff800000u;
+            if (v.z > my_pos || v.z <= my_lo) x[e + 2] = 0xff800000u;
+            if (v.w > my_pos || v.w <= my_lo) x[e + 3] = 0xff800000u;
+          }
+          if (GEN) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 16) {
+#pragma unroll
+              for (int u = 0; u < 8; ++u) a8[u] = fmax3(a8[u], __uint_as_float(x[e + 2 * u]), __uint_as_float(x[e + 2 * u + 1]));
+            }
           }
           tmem_st_32x32b_x16(tmem_S + (uint32_t)c0, x);
           tmem_st_32x32b_x16(tmem_S + (uint32_t)(c0 + 16), x + 16);
         }
         tmem_st_wait();
+        have_max = GEN;
       } else if (n_cand > 0) {
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
@@ -593,10 +640,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       F2_MARK(1);
       // pass 1: maximum of the row; the scores stay in TMEM, 32 of them are in registers at a time
-      float a8[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) a8[u] = -INFINITY;
-      {
+      if (!have_max) {
         uint32_t x[2][32];
         tmem_ld_32x32b_x32(tmem_S, x[0]);
 #pragma unroll
@@ -798,6 +842,7 @@ struct CsSmem {
   static constexpr int TOTAL = XCH + 512;
 };
 
+template <bool GEN>
 __global__ void __launch_bounds__(F2_THREADS, 1)
 colsum_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const F2Params p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -830,7 +875,14 @@ colsum_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     if (need > 0) qt_first = (int)min((long long)p.nQT, need / p.npos);
     if (tile_lo == INT_MAX) qt_first = p.nQT;
   }
-  const int n_q = p.nQT - qt_first;
+  int qt_end = p.nQT;  // with a window, query tiles whose first position lies beyond the newest slot's window see nothing
+  const int c_window = GEN ? p.window : 0;
+  if (c_window > 0 && tile_hi != INT_MAX) {
+    const long long last = (long long)tile_hi + c_window - 1 - p.input_pos;  // last position index that sees the newest slot
+    qt_end = last < 0 ? 0 : (int)min((long long)p.nQT, last / p.npos + 1);
+  }
+  const int n_q = max(qt_end - qt_first, 0);
+  const bool soft = GEN && p.cap_pre != 0.f;
 
   if (p.rows_used < F2_T) {
     for (int s = 0; s < CS_QSTAGES; ++s)
@@ -929,7 +981,10 @@ colsum_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       // row e of the query tile sits at position qt·npos + e / gs: the slot is visible from column thr on
       const long long first_vis = ((long long)pj - p.input_pos - (long long)qt * p.npos) * p.gs;
       const int thr = first_vis <= 0 ? 0 : (first_vis >= F2_T ? F2_T : (int)first_vis);
-      const bool masked = __any_sync(0xffffffffu, thr > 0);
+      // with a window the slot is visible up to (not including) column thr_hi
+      const long long end_vis = first_vis + (long long)c_window * p.gs;
+      const int thr_hi = c_window <= 0 ? F2_T : (end_vis <= 0 ? 0 : (end_vis >= F2_T ? F2_T : (int)end_vis));
+      const bool masked = __any_sync(0xffffffffu, thr > 0 || thr_hi < F2_T);
       const float4* lp = reinterpret_cast<const float4*>(lse_row(i));
       if (!mbar_wait_bounded(&s_full[sb], (i / CS_SBUF) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) {
         ok = false;
@@ -960,17 +1015,21 @@ colsum_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         for (int k = 0; k < 8; ++k) {
           const int e = 32 * u + 4 * k;
           const float4 lv = ls[u & 1][k];
-          const float2 x0 = ffma2(make_float2(__uint_as_float(x[u & 1][4 * k]), __uint_as_float(x[u & 1][4 * k + 1])), c2,
-                                  make_float2(-lv.x, -lv.y));
-          const float2 x1 = ffma2(make_float2(__uint_as_float(x[u & 1][4 * k + 2]), __uint_as_float(x[u & 1][4 * k + 3])), c2,
-                                  make_float2(-lv.z, -lv.w));
+          float2 r0 = make_float2(__uint_as_float(x[u & 1][4 * k]), __uint_as_float(x[u & 1][4 * k + 1]));
+          float2 r1 = make_float2(__uint_as_float(x[u & 1][4 * k + 2]), __uint_as_float(x[u & 1][4 * k + 3]));
+          if (soft) {
+            r0 = make_float2(f2_softcap(r0.x, p.cap_pre, p.cap_post), f2_softcap(r0.y, p.cap_pre, p.cap_post));
+            r1 = make_float2(f2_softcap(r1.x, p.cap_pre, p.cap_post), f2_softcap(r1.y, p.cap_pre, p.cap_post));
+          }
+          const float2 x0 = ffma2(r0, c2, make_float2(-lv.x, -lv.y));
+          const float2 x1 = ffma2(r1, c2, make_float2(-lv.z, -lv.w));
           float2 y0 = cs_pair_on_fma(2 * k) ? f2_exp2_poly2(x0) : make_float2(f2_exp2(x0.x), f2_exp2(x0.y));
           float2 y1 = cs_pair_on_fma(2 * k + 1) ? f2_exp2_poly2(x1) : make_float2(f2_exp2(x1.x), f2_exp2(x1.y));
           if (masked) {
-            if (e < thr) y0.x = 0.f;
-            if (e + 1 < thr) y0.y = 0.f;
-            if (e + 2 < thr) y1.x = 0.f;
-            if (e + 3 < thr) y1.y = 0.f;
+            if (e < thr || e >= thr_hi) y0.x = 0.f;
+            if (e + 1 < thr || e + 1 >= thr_hi) y0.y = 0.f;
+            if (e + 2 < thr || e + 2 >= thr_hi) y1.x = 0.f;
+            if (e + 3 < thr || e + 3 >= thr_hi) y1.y = 0.f;
           }
           acc0 = fadd2(acc0, y0);
           acc1 = fadd2(acc1, y1);
@@ -979,7 +1038,6 @@ colsum_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     }
     // the two warpgroups hold the even and the odd query tiles of the same slots: add them in a fixed order
     float* xch = reinterpret_cast<float*>(smem + CsSmem::XCH);
-    (void)tile_hi;
     const float mine = (acc0.x + acc0.y) + (acc1.x + acc1.y);
     if (wg == 1) xch[slot_in_tile] = mine;
     asm volatile("bar.sync 1, 256;" ::: "memory");
@@ -1076,11 +1134,26 @@ extern "C" long long kvb_sdpa_fwd_scratch_bytes(int B, int H, int G, int q_len, 
 // q (B,H,T,128) contiguous bf16; k, v (B,G,L,128) bf16 with batch / group strides k_sb, k_sg (elements);
 // token_pos (B,G,L) int32 with strides, or NULL (slot j holds token j); out (B,T,H,128) bf16;
 // lse (B,H,T) fp32 or NULL; weights (B,G,L) fp32 or NULL.
+// window: sliding window in tokens (0: none); softcap: logit soft-capping threshold (0: none).
+extern "C" int kvb_sdpa_fwd_ex(const void* q, const void* k, const void* v, const int32_t* token_pos, void* out, float* lse,
+                                float* weights, void* scratch, int B, int H, int G, int q_len, int kv_len, long long k_sb,
+                                long long k_sg, long long tp_sb, long long tp_sg, float scale, int input_pos, int window,
+                                float softcap, int* status, void* stream);
+
 extern "C" int kvb_sdpa_fwd(const void* q, const void* k, const void* v, const int32_t* token_pos, void* out, float* lse,
                              float* weights, void* scratch, int B, int H, int G, int q_len, int kv_len, long long k_sb,
                              long long k_sg, long long tp_sb, long long tp_sg, float scale, int input_pos, int* status,
                              void* stream) {
+  return kvb_sdpa_fwd_ex(q, k, v, token_pos, out, lse, weights, scratch, B, H, G, q_len, kv_len, k_sb, k_sg, tp_sb, tp_sg, scale,
+                         input_pos, 0, 0.f, status, stream);
+}
+
+extern "C" int kvb_sdpa_fwd_ex(const void* q, const void* k, const void* v, const int32_t* token_pos, void* out, float* lse,
+                                float* weights, void* scratch, int B, int H, int G, int q_len, int kv_len, long long k_sb,
+                                long long k_sg, long long tp_sb, long long tp_sg, float scale, int input_pos, int window,
+                                float softcap, int* status, void* stream) {
   using namespace kvb;
+  if (window < 0 || softcap < 0.f || (softcap > 0.f && scale <= 0.f)) return KVB_ERR_ARG;
   if (B <= 0 || H <= 0 || G <= 0 || q_len <= 0 || kv_len <= 0 || H % G) return KVB_ERR_ARG;
   const int gs = H / G;
   if (gs > 128) return KVB_ERR_UNSUPPORTED;
@@ -1106,6 +1179,9 @@ extern "C" int kvb_sdpa_fwd(const void* q, const void* k, const void* v, const i
   p.inv_gs = 1.f / gs;
   p.input_pos = input_pos; p.status = status;
   p.trace = g_f2_trace;
+  p.window = window;
+  p.cap_pre = softcap > 0.f ? scale / softcap : 0.f;
+  p.cap_post = softcap > 0.f ? softcap / scale : 0.f;
 
   CUtensorMap tmQ, tmK, tmV;
   int rc;
@@ -1119,19 +1195,24 @@ extern "C" int kvb_sdpa_fwd(const void* q, const void* k, const void* v, const i
   f2_prepare_kernel<<<B * G * p.nT, F2_T, 0, s>>>(token_pos, tmin, tmax, pos, G, kv_len, p.nT, tp_sb, tp_sg);
   static kvb::PerDeviceOnce attr_once;
   if (attr_once.first()) {
-    cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F2Smem::TOTAL);
-    cudaFuncSetAttribute(colsum_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, CsSmem::TOTAL);
+    cudaFuncSetAttribute(flash_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, F2Smem::TOTAL);
+    cudaFuncSetAttribute(flash_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, F2Smem::TOTAL);
+    cudaFuncSetAttribute(colsum_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, CsSmem::TOTAL);
+    cudaFuncSetAttribute(colsum_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, CsSmem::TOTAL);
   }
   const int nPair = (p.nQT + 1) / 2;
   p.n_split = f2_num_splits((long long)B * G * nPair, p.nT);
   p.tiles_per_split = (p.nT + p.n_split - 1) / p.n_split;
   p.part_lse2 = lse2 + (long long)B * G * p.nQT * 128;
   p.part_o = p.part_lse2 + f2_round4((long long)p.n_split * B * H * q_len);
-  flash_fwd_kernel<<<dim3(B * G * nPair, p.n_split), F2_THREADS, F2Smem::TOTAL, s>>>(tmQ, tmK, tmV, p);
+  const bool gen = window > 0 || softcap > 0.f;
+  if (gen) flash_fwd_kernel<true><<<dim3(B * G * nPair, p.n_split), F2_THREADS, F2Smem::TOTAL, s>>>(tmQ, tmK, tmV, p);
+  else flash_fwd_kernel<false><<<dim3(B * G * nPair, p.n_split), F2_THREADS, F2Smem::TOTAL, s>>>(tmQ, tmK, tmV, p);
   if (p.n_split > 1) {
     const long long rows = (long long)B * G * p.nQT * F2_T;
     flash_merge_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(p);
   }
-  if (weights) colsum_kernel<<<B * G * p.nT, F2_THREADS, CsSmem::TOTAL, s>>>(tmQ, tmK, p);
+  if (weights && gen) colsum_kernel<true><<<B * G * p.nT, F2_THREADS, CsSmem::TOTAL, s>>>(tmQ, tmK, p);
+  else if (weights) colsum_kernel<false><<<B * G * p.nT, F2_THREADS, CsSmem::TOTAL, s>>>(tmQ, tmK, p);
   return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
 }

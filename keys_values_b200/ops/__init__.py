@@ -210,7 +210,7 @@ def sdpa_fwd(
 ):
     """Returns ``(out (B,q,H·D), weights (B,G,kv) fp32 | None, lse (B,H,q) fp32)``."""
     if query.is_cuda and _NATIVE_ATTENTION and _cuda().sdpa_supported(query, key, sliding_window, softcap):
-        return _cuda().sdpa_fwd(query, key, value, scale, input_pos, token_pos, return_weights)
+        return _cuda().sdpa_fwd(query, key, value, scale, input_pos, token_pos, return_weights, sliding_window, softcap)
     if query.is_cuda and _NATIVE_ATTENTION:
         _restatement_on_gpu("sdpa_fwd", _sdpa_shape_text(query, sliding_window, softcap))
     return ref.sdpa(query, key, value, scale, input_pos, token_pos, return_weights, sliding_window, softcap, return_lse=True)
@@ -240,7 +240,8 @@ def sdpa_bwd(
     ``dk_accum/dv_accum`` (fp32, cache shaped) the K/V gradients are added into their
     first ``kv`` slots instead and ``None`` is returned for them."""
     if query.is_cuda and _NATIVE_ATTENTION and _cuda().sdpa_bwd_supported(query, key, sliding_window, softcap):
-        return _cuda().sdpa_bwd(grad_out, query, key, value, out, lse, scale, input_pos, token_pos, dk_accum, dv_accum)
+        return _cuda().sdpa_bwd(grad_out, query, key, value, out, lse, scale, input_pos, token_pos, dk_accum, dv_accum,
+                                sliding_window, softcap)
     if query.is_cuda and _NATIVE_ATTENTION:
         _restatement_on_gpu("sdpa_bwd", _sdpa_shape_text(query, sliding_window, softcap))
     dq, dk, dv = ref.sdpa_backward(grad_out, query, key, value, scale, input_pos, token_pos, sliding_window, softcap)

@@ -487,8 +487,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, a2=None, b2=None, residual=None, out=
 def sdpa_supported(query: torch.Tensor, key: torch.Tensor, sliding_window, softcap) -> bool:
     H, G = query.shape[1], key.shape[1]
     gs = H // G
-    return (query.dtype == torch.bfloat16 and query.shape[-1] == 128 and sliding_window is None and softcap is None
-            and gs <= 128 and query.shape[2] > 0)
+    return (query.dtype == torch.bfloat16 and query.shape[-1] == 128 and gs <= 128 and query.shape[2] > 0
+            and (sliding_window is None or sliding_window > 0) and (softcap is None or softcap > 0))
 
 
 def sdpa_bwd_supported(query: torch.Tensor, key: torch.Tensor, sliding_window, softcap) -> bool:
@@ -497,9 +497,11 @@ def sdpa_bwd_supported(query: torch.Tensor, key: torch.Tensor, sliding_window, s
     return sdpa_supported(query, key, sliding_window, softcap) and query.shape[1] // key.shape[1] <= 64
 
 
-def sdpa_fwd(query, key, value, scale, input_pos, token_pos=None, return_weights=False):
+def sdpa_fwd(query, key, value, scale, input_pos, token_pos=None, return_weights=False, sliding_window=None, softcap=None):
     """SDPA forward: flash sweep (P in TMEM, online softmax) + column-owner weight sums. Returns
-    ``(out (B,T,H·D) bf16, weights (B,G,L) fp32 | None, lse (B,H,T) fp32)``; any group size up to 128."""
+    ``(out (B,T,H·D) bf16, weights (B,G,L) fp32 | None, lse (B,H,T) fp32)``; any group size up to 128.
+    ``sliding_window``: a query at position ``p`` sees tokens in ``(p - window, p]`` only; ``softcap``: scores
+    become ``cap · tanh(score / cap)`` (both inside the kernels)."""
     B, H, T, D = query.shape
     G, L = key.shape[1], key.shape[2]
     query = query.contiguous()
@@ -516,11 +518,12 @@ def sdpa_fwd(query, key, value, scale, input_pos, token_pos=None, return_weights
         raise NativeError("sdpa_fwd: unsupported head / group configuration")
     scratch = torch.empty(nbytes // 4, dtype=torch.int32, device=dev)
     st = status_word(dev)
-    _check(lib().kvb_sdpa_fwd(_p(query), _p(key), _p(value), _p(token_pos), _p(out), _p(lse), _p(weights), _p(scratch), B, H, G, T, L,
-                               _ll(key.stride(0)), _ll(key.stride(1)),
-                               _ll(token_pos.stride(0) if token_pos is not None else 0),
-                               _ll(token_pos.stride(1) if token_pos is not None else 0),
-                               ctypes.c_float(scale), int(input_pos), _p(st), _stream(query)), "sdpa_fwd")
+    _check(lib().kvb_sdpa_fwd_ex(_p(query), _p(key), _p(value), _p(token_pos), _p(out), _p(lse), _p(weights), _p(scratch), B, H, G, T, L,
+                                  _ll(key.stride(0)), _ll(key.stride(1)),
+                                  _ll(token_pos.stride(0) if token_pos is not None else 0),
+                                  _ll(token_pos.stride(1) if token_pos is not None else 0),
+                                  ctypes.c_float(scale), int(input_pos), int(sliding_window or 0), ctypes.c_float(softcap or 0.0),
+                                  _p(st), _stream(query)), "sdpa_fwd")
     _count(3 if return_weights else 2)
     return out, weights, lse
 
@@ -537,7 +540,8 @@ def _norm_token_pos(token_pos, B, G, L):
     return token_pos
 
 
-def sdpa_bwd(grad_out, query, key, value, out, lse, scale, input_pos, token_pos=None, dk_accum=None, dv_accum=None):
+def sdpa_bwd(grad_out, query, key, value, out, lse, scale, input_pos, token_pos=None, dk_accum=None, dv_accum=None,
+             sliding_window=None, softcap=None):
     """Attention backward (tcgen05 kernels). Returns ``(dq, dk, dv)``: ``dq (B,H,T,D)`` in
     the dtype of ``query``; ``dk, dv`` fp32. If ``dk_accum/dv_accum`` (fp32, cache shaped,
     contiguous along the last two axes) are given, the gradients are *added* into their
@@ -562,12 +566,12 @@ def sdpa_bwd(grad_out, query, key, value, out, lse, scale, input_pos, token_pos=
     nbytes = lib().kvb_sdpa_bwd_scratch_bytes(B, H, G, T, L)
     scratch = torch.empty(nbytes // 4, dtype=torch.int32, device=dev)
     st = status_word(dev)
-    _check(lib().kvb_sdpa_bwd(_p(query), _p(key), _p(value), _p(token_pos), _p(out), _p(grad_out), _p(lse.contiguous()), _p(dq),
-                              _p(dk_accum), _p(dv_accum), _p(scratch), B, H, G, T, L, _ll(key.stride(0)), _ll(key.stride(1)),
-                              _ll(token_pos.stride(0) if token_pos is not None else 0),
-                              _ll(token_pos.stride(1) if token_pos is not None else 0),
-                              _ll(dk_accum.stride(0)), _ll(dk_accum.stride(1)), ctypes.c_float(scale), int(input_pos), _p(st),
-                              _stream(query)), "sdpa_bwd")
+    _check(lib().kvb_sdpa_bwd_ex(_p(query), _p(key), _p(value), _p(token_pos), _p(out), _p(grad_out), _p(lse.contiguous()), _p(dq),
+                                 _p(dk_accum), _p(dv_accum), _p(scratch), B, H, G, T, L, _ll(key.stride(0)), _ll(key.stride(1)),
+                                 _ll(token_pos.stride(0) if token_pos is not None else 0),
+                                 _ll(token_pos.stride(1) if token_pos is not None else 0),
+                                 _ll(dk_accum.stride(0)), _ll(dk_accum.stride(1)), ctypes.c_float(scale), int(input_pos),
+                                 int(sliding_window or 0), ctypes.c_float(softcap or 0.0), _p(st), _stream(query)), "sdpa_bwd")
     _count(4)
     if own:
         return dq, dk_accum, dv_accum

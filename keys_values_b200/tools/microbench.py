@@ -1,7 +1,7 @@
 """Kernel micro-benchmarks: CUDA-event timing after warm-up, with an L2 flush
 (a write larger than the 126 MB L2) between timed iterations.
 
-    python -m keys_values_b200.tools.microbench sdpa|sdpa_train|sdpa_bwd|gemm|elementwise|all [--out file.jsonl]
+    python -m keys_values_b200.tools.microbench sdpa|sdpa_train|sdpa_bwd|sdpa_variants|gemm|elementwise|all [--out file.jsonl]
 
 ``sdpa`` covers the SDPA-with-weights grid: bf16 GQA 32/8 heads, head size 128,
 batch 1 and 4, query length {1, 256, 2048}, KV length {4096, 16384, 32768}.
@@ -136,6 +136,31 @@ def bench_sdpa_train(out, peaks):
              "bwd_frac_of_measured_peak": 2.5 * flops / ms_b / 1e9 / peaks["bf16_tflops"]})
 
 
+def bench_sdpa_variants(out, peaks):
+    """Sliding window and logit soft-capping on the training chunk (plain prefix positions): forward with summed
+    weights and backward with accumulation."""
+    from keys_values_b200.ops import cuda as cu
+
+    dev = torch.device("cuda")
+    flush = _flush_buf(dev)
+    B, H, G, D, T, L = 1, 32, 8, 128, 1024, 16384
+    scale = 1 / math.sqrt(D)
+    q = torch.randn(B, H, T, D, device=dev, dtype=torch.bfloat16)
+    k = torch.randn(B, G, L, D, device=dev, dtype=torch.bfloat16)
+    v = torch.randn(B, G, L, D, device=dev, dtype=torch.bfloat16)
+    go = torch.randn(B, T, H * D, device=dev, dtype=torch.bfloat16)
+    dk = torch.zeros(B, G, L, D, device=dev)
+    dv = torch.zeros_like(dk)
+    ip = L - T
+    for window, softcap in ((None, None), (4096, None), (None, 50.0), (4096, 50.0)):
+        ms_f = time_fn(lambda: cu.sdpa_fwd(q, k, v, scale, ip, None, True, window, softcap), flush=flush)
+        o, _, lse = cu.sdpa_fwd(q, k, v, scale, ip, None, False, window, softcap)
+        ms_b = time_fn(lambda: cu.sdpa_bwd(go, q, k, v, o, lse, scale, ip, None, dk, dv, window, softcap), flush=flush)
+        cu.check_status(dev)
+        out({"bench": "sdpa_variants", "B": B, "q": T, "kv": L, "window": window, "softcap": softcap,
+             "fwd_with_weights_us": ms_f * 1e3, "bwd_us": ms_b * 1e3})
+
+
 def bench_gemm(out, peaks):
     from keys_values_b200.ops import cuda as cu
 
@@ -214,6 +239,8 @@ def main():
         bench_sdpa_train(out, peaks)
     if args.which in ("sdpa_bwd", "all"):
         bench_sdpa_bwd(out, peaks)
+    if args.which in ("sdpa_variants", "all"):
+        bench_sdpa_variants(out, peaks)
     if args.which in ("elementwise", "all"):
         bench_elementwise(out, peaks)
 

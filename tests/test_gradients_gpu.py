@@ -120,3 +120,41 @@ def test_gradients_through_eviction_match_oracle_on_gpu(cache_name):
     noise = rel(o16, o32)
     assert abs(float(loss.value) - float(o_loss32)) < 0.03
     assert rel(g1, o32) < max(3 * noise, 0.05), (rel(g1, o32), noise)
+
+
+def test_sliding_window_and_softcap_layers_run_on_the_native_kernels(monkeypatch):
+    """A Gemma-2 style model (a window layer, capped scores) through the chunked training pass: the tcgen05 attention
+    kernels serve it (no restatement: strict mode), and loss and gradients agree with the PyTorch restatement."""
+    from keys_values_b200 import ops
+    from keys_values_b200.config import Config
+    from keys_values_b200.models.model import GPT
+
+    monkeypatch.setenv("KVB200_STRICT_NATIVE", "1")
+    dev, dtype = torch.device("cuda", 0), torch.bfloat16
+    torch.manual_seed(0)
+    cfg = Config.from_name("tiny-gemma2")
+    m = GPT(cfg)
+    m.apply(m._init_weights)
+    m = m.to(device=dev, dtype=dtype)
+    head = CrossEntropyOnLogits(cfg)
+    T, C, cs = 512, 640, 128
+    ids = torch.randint(0, cfg.vocab_size, (1, T), device=dev)
+    tg = torch.randint(0, cfg.vocab_size, (1, 96), device=dev)
+    m.assign_kv_caches(KVCacheFactory.create(m, "h2o-default", 1, C, dtype=dtype, device=dev, cache_kwargs=dict(max_chunk_size=cs)))
+    gm = LongContextGradientModel(m, head, layers_per_cell=1, chunk_size=cs)
+    gm.train()
+    loss = gm(ids, tg)
+    loss.backward()
+    g1 = _grads(m)
+    monkeypatch.setenv("KVB200_STRICT_NATIVE", "0")
+    ops.set_native_attention(False)
+    try:
+        loss2 = gm(ids, tg)
+        loss2.backward()
+    finally:
+        ops.set_native_attention(True)
+    g2 = _grads(m)
+    assert abs(float(loss.value) - float(loss2.value)) < 0.02
+    num = sum(((g1[k] - g2[k]) ** 2).sum() for k in g1) ** 0.5
+    den = sum((g2[k] ** 2).sum() for k in g1) ** 0.5
+    assert len(g1) > 0 and float(num / den) < 0.05, float(num / den)

@@ -183,7 +183,7 @@ def test_gemm_lora_residual():
     torch.testing.assert_close(c.float(), cr, atol=1e-1, rtol=2e-2)
 
 
-def _sdpa_case(B, H, G, T, L, input_pos, mode, want_w=True):
+def _sdpa_case(B, H, G, T, L, input_pos, mode, want_w=True, window=None, softcap=None):
     D = 128
     q = torch.randn(B, H, T, D, device=DEV, dtype=torch.bfloat16)
     k = torch.randn(B, G, L, D, device=DEV, dtype=torch.bfloat16)
@@ -200,9 +200,9 @@ def _sdpa_case(B, H, G, T, L, input_pos, mode, want_w=True):
                 allp = torch.cat((old, new))
                 tp[b, g] = allp[torch.randperm(L, device=DEV)].to(torch.int32)
     scale = 1.0 / math.sqrt(D)
-    out, w, lse = _cuda().sdpa_fwd(q, k, v, scale, input_pos, tp, want_w)
+    out, w, lse = _cuda().sdpa_fwd(q, k, v, scale, input_pos, tp, want_w, window, softcap)
     _cuda().check_status(DEV)
-    out_r, w_r, lse_r = ref.sdpa(q, k, v, scale, input_pos, tp, want_w, return_lse=True)
+    out_r, w_r, lse_r = ref.sdpa(q, k, v, scale, input_pos, tp, want_w, window, softcap, return_lse=True)
     torch.testing.assert_close(lse, lse_r, atol=2e-2, rtol=1e-3)
     torch.testing.assert_close(out.float(), out_r.float(), atol=2e-2, rtol=2e-2)
     if want_w:
@@ -244,6 +244,23 @@ def test_sdpa_few_queries_split_over_the_cache(B, H, G, T, L, mode):
 def test_sdpa_plain_causal_with_weights():
     # square causal prefill with weights: diagonal tiles take the element-wise mask path
     _sdpa_case(2, 8, 2, 700, 700, 0, "arange")
+
+
+WINDOW_SOFTCAP_CASES = [
+    (1, 8, 2, 300, 1500, "arange", 256, None),    # window edge inside the chunk's diagonal and before it
+    (1, 8, 2, 300, 1500, "arange", None, 2.0),    # a cap that bends most scores
+    (2, 8, 2, 100, 1000, "perm", 2500, 50.0),     # evicted cache: part of the old tokens outside the window
+    (1, 10, 2, 77, 900, "arange", 100, 3.0),      # group size 5
+    (1, 32, 8, 1, 2048, "arange", 512, 50.0),     # one query: a decode step of such a layer
+    (1, 4, 1, 64, 8192, "arange", 1000, None),    # few queries: split over the KV axis, most tiles outside the window
+    (1, 8, 2, 700, 700, "arange", 128, None),     # square prefill: a band of diagonal tiles
+]
+
+
+@pytest.mark.parametrize("B,H,G,T,L,mode,window,softcap", WINDOW_SOFTCAP_CASES)
+def test_sdpa_sliding_window_and_softcap(B, H, G, T, L, mode, window, softcap):
+    """Sliding window and logit soft-capping inside the tcgen05 kernels (outputs, normalisers, summed weights)."""
+    _sdpa_case(B, H, G, T, L, 3 * L if mode == "perm" else L - T, mode, window=window, softcap=softcap)
 
 
 def test_sdpa_is_deterministic():
@@ -309,6 +326,32 @@ def test_sdpa_bwd(B, H, G, T, L, mode):
     assert _rel_err(dk_acc[:, :, :L] - dk0[:, :, :L], dk_r) < 3e-2
     assert _rel_err(dv_acc[:, :, :L] - dv0[:, :, :L], dv_r) < 3e-2
     assert torch.equal(dk_acc[:, :, L:], dk0[:, :, L:]) and torch.equal(dv_acc[:, :, L:], dv0[:, :, L:])
+
+
+@pytest.mark.parametrize("B,H,G,T,L,mode,window,softcap", WINDOW_SOFTCAP_CASES)
+def test_sdpa_bwd_sliding_window_and_softcap(B, H, G, T, L, mode, window, softcap):
+    D = 128
+    q = torch.randn(B, H, T, D, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(B, G, L, D, device=DEV, dtype=torch.bfloat16)
+    v = torch.randn(B, G, L, D, device=DEV, dtype=torch.bfloat16)
+    go = torch.randn(B, T, H * D, device=DEV, dtype=torch.bfloat16)
+    if mode == "perm":
+        input_pos = 3 * L
+        tp = torch.empty(B, G, L, device=DEV, dtype=torch.int32)
+        for b in range(B):
+            for g in range(G):
+                allp = torch.cat((torch.randperm(input_pos, device=DEV)[: L - T], torch.arange(input_pos, input_pos + T, device=DEV)))
+                tp[b, g] = allp[torch.randperm(L, device=DEV)].to(torch.int32)
+    else:
+        tp, input_pos = None, L - T
+    scale = 1.0 / math.sqrt(D)
+    out, _, lse = _cuda().sdpa_fwd(q, k, v, scale, input_pos, tp, False, window, softcap)
+    dq, dk, dv = _cuda().sdpa_bwd(go, q, k, v, out, lse, scale, input_pos, tp, sliding_window=window, softcap=softcap)
+    _cuda().check_status(DEV)
+    dq_r, dk_r, dv_r = ref.sdpa_backward(go, q, k, v, scale, input_pos, tp, window, softcap)
+    assert _rel_err(dq, dq_r) < 3e-2
+    assert _rel_err(dk, dk_r) < 3e-2
+    assert _rel_err(dv, dv_r) < 3e-2
 
 
 @pytest.mark.parametrize("bits", [16, 8, 4])
