@@ -48,9 +48,11 @@ def check_numerical_equivalence(tensor_a: torch.Tensor, tensor_b: torch.Tensor, 
 
 def verify_backend_equivalence(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, scale_factor: float,
                                return_attn_weights: bool = False, token_positions: Optional[torch.Tensor] = None, input_pos: int = 0,
-                               rtol: float = 2e-2, atol: float = 2e-2, log_results: bool = True) -> BackendEquivalenceResult:
+                               rtol: float = 2e-2, atol: float = 2e-2, log_results: bool = True,
+                               sliding_window_size: Optional[int] = None, softcap: Optional[float] = None) -> BackendEquivalenceResult:
     """``query (B,H,q,D)``, ``key / value (B,G,kv,D)`` on a GPU. A query of length 1 goes to the decode
-    kernel, longer ones to the tcgen05 forward; the weights compared are the per-slot sums the
+    kernel, longer ones (and layers with a sliding window or capped scores) to the tcgen05 forward (head size 128 or
+    64); the weights compared are the per-slot sums the
     cache policies consume (``(B,G,kv)``, summed over queries, averaged over the heads of a group)."""
     from keys_values_b200.ops import cuda as cu
 
@@ -58,14 +60,15 @@ def verify_backend_equivalence(query: torch.Tensor, key: torch.Tensor, value: to
         raise RuntimeError("the kernels run on a GPU; the tensors are on " + str(query.device))
     B, H, T, D = query.shape
     L = key.shape[2]
-    if T == 1 and token_positions is None and cu.decode_supported(query, key.shape[1]):
+    if T == 1 and token_positions is None and sliding_window_size is None and softcap is None and cu.decode_supported(query, key.shape[1]):
         out, w = cu.decode_attention(query, key.contiguous(), value.contiguous(), scale_factor, L, return_attn_weights)
-    elif cu.sdpa_supported(query, key, None, None):
-        out, w, _ = cu.sdpa_fwd(query, key, value, scale_factor, input_pos, token_positions, return_attn_weights)
+    elif cu.sdpa_supported(query, key, sliding_window_size, softcap):
+        out, w, _ = cu.sdpa_fwd(query, key, value, scale_factor, input_pos, token_positions, return_attn_weights,
+                                sliding_window_size, softcap)
     else:
         raise RuntimeError(f"no kernel for query {tuple(query.shape)} {query.dtype}, key {tuple(key.shape)}")
     cu.check_status(query.device)
-    res = ref.sdpa(query, key, value, scale_factor, input_pos, token_positions, return_attn_weights)
+    res = ref.sdpa(query, key, value, scale_factor, input_pos, token_positions, return_attn_weights, sliding_window_size, softcap)
     out_r, w_r = res[0], res[1]
     ok, omax, omean = check_numerical_equivalence(out, out_r.to(out.dtype), rtol, atol)
     wmax = wmean = None

@@ -199,6 +199,12 @@ configs: List[dict] = [
         n_head=8, n_query_groups=2, head_size=128, intermediate_size=512, norm_qk=True,
         norm_eps=1e-6, rope_base=1000000, **_llama_like,
     ),
+    dict(  # head size 64 (Llama-3.2-1B, Qwen2.5-0.5B shapes)
+        name="tiny-llama-d64",
+        block_size=4096, vocab_size=1024, padded_vocab_size=1024, n_layer=2, n_embd=256,
+        n_head=4, n_query_groups=2, head_size=64, intermediate_size=512,
+        norm_eps=1e-5, rope_base=500000, **_llama_like,
+    ),
     dict(  # Gemma-2 style: every other layer with a sliding window, capped attention scores and logits
         name="tiny-gemma2",
         block_size=4096, vocab_size=1024, padded_vocab_size=1024, n_layer=2, n_embd=256,

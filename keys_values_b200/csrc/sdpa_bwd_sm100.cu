@@ -103,18 +103,26 @@ __device__ __forceinline__ float bw_tanh(float z) {
 // delta[b,h,t] = sum_d dO[b,t,h,d] * O[b,t,h,d]
 // With dOt the kernel also leaves a head-major copy dOt[b,h,t,:] of dO (which it reads anyway): the TMA boxes of the
 // two launches then read runs of consecutive positions of one head, as they do for Q.
+template <int HD>
 __global__ void att_delta_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O,
                                  float* __restrict__ delta, __nv_bfloat16* __restrict__ dOt, int B, int T, int H) {
   const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= (long long)B * T * H) return;
   const int lane = threadIdx.x & 31;
-  const uint2 a = *reinterpret_cast<const uint2*>(dO + row * 128 + lane * 4);
-  const uint2 o = *reinterpret_cast<const uint2*>(O + row * 128 + lane * 4);
+  constexpr int PER = HD / 32;  // features per lane: 4 (one 8-byte access) or 2 (one 4-byte access)
+  uint2 a = make_uint2(0, 0), o = make_uint2(0, 0);
+  if (PER == 4) {
+    a = *reinterpret_cast<const uint2*>(dO + row * HD + lane * 4);
+    o = *reinterpret_cast<const uint2*>(O + row * HD + lane * 4);
+  } else {
+    a.x = *reinterpret_cast<const uint32_t*>(dO + row * HD + lane * 2);
+    o.x = *reinterpret_cast<const uint32_t*>(O + row * HD + lane * 2);
+  }
   const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&a);
   const __nv_bfloat162* op = reinterpret_cast<const __nv_bfloat162*>(&o);
   float s = 0.f;
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
+  for (int i = 0; i < PER / 2; ++i) {
     const float2 x = __bfloat1622float2(ap[i]), y = __bfloat1622float2(op[i]);
     s += x.x * y.x + x.y * y.y;
   }
@@ -124,7 +132,10 @@ __global__ void att_delta_kernel(const __nv_bfloat16* __restrict__ dO, const __n
   const int t = (int)(bt % T);
   const int b = (int)(bt / T);
   const long long hrow = ((long long)b * H + h) * T + t;
-  if (dOt) *reinterpret_cast<uint2*>(dOt + hrow * 128 + lane * 4) = a;
+  if (dOt) {
+    if (PER == 4) *reinterpret_cast<uint2*>(dOt + hrow * HD + lane * 4) = a;
+    else *reinterpret_cast<uint32_t*>(dOt + hrow * HD + lane * 2) = a.x;
+  }
   if (lane == 0) delta[hrow] = s;
 }
 
@@ -132,7 +143,9 @@ __global__ void att_delta_kernel(const __nv_bfloat16* __restrict__ dO, const __n
 //   MODE_DQ : R1 = Q, R2 = dO, C1 = K, C2 = V      MODE_DKV: R1 = K, R2 = V, C1 = Q, C2 = dO
 // GEN: sliding window and / or soft-capping are in use (separate instantiations, so that the plain kernels keep their
 // register allocation)
-template <int MODE, bool GEN>
+// HD: head size, 128 or 64 (row operands and units of one 64-feature chunk, half as many K steps for X / Y,
+// accumulators of 64 columns)
+template <int MODE, bool GEN, int HD>
 __global__ void __launch_bounds__(BW_THREADS, 1)
 sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ CUtensorMap tmR2,
                 const __grid_constant__ CUtensorMap tmC1, const __grid_constant__ CUtensorMap tmC2, const BwParams p) {
@@ -194,16 +207,19 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
   // enter MMAs as operand rows, and 0 · anything finite is 0 while stale shared memory could hold NaN patterns.
   if (MODE == MODE_DQ && p.rows_used < 128) {
     const int n16 = (128 - p.rows_used) * 8;  // 16-byte pieces per 64-feature chunk
-    for (int i = threadIdx.x; i < 4 * n16; i += BW_THREADS) {
-      uint8_t* chunk = smem + (i / n16 < 2 ? S::R1 : S::R2) + ((i / n16) & 1) * (BW_TILE_BYTES / 2);
+    constexpr int NCH = HD / 64;
+    for (int i = threadIdx.x; i < 2 * NCH * n16; i += BW_THREADS) {
+      uint8_t* chunk = smem + ((i / n16) / NCH == 0 ? S::R1 : S::R2) + ((i / n16) % NCH) * (BW_TILE_BYTES / 2);
       *reinterpret_cast<uint4*>(chunk + p.rows_used * 128 + (i % n16) * 16) = make_uint4(0, 0, 0, 0);
     }
     fence_proxy_async_smem();
   }
   if (MODE == MODE_DKV && p.cols_used < 64) {
     const int n16 = (64 - p.cols_used) * 8;
-    for (int i = threadIdx.x; i < BW_STAGES * 4 * n16; i += BW_THREADS) {
-      uint8_t* chunk = smem + S::C + (i / n16) * (BW_UNIT_BYTES / 2);  // stage-major: C1 lo | C1 hi | C2 lo | C2 hi
+    constexpr int NCH = HD / 64;
+    for (int i = threadIdx.x; i < BW_STAGES * 2 * NCH * n16; i += BW_THREADS) {
+      const int idx = i / n16;  // (stage, operand C1 | C2, 64-feature chunk)
+      uint8_t* chunk = smem + S::C + (idx / NCH) * BW_UNIT_BYTES + (idx % NCH) * (BW_UNIT_BYTES / 2);
       *reinterpret_cast<uint4*>(chunk + p.cols_used * 128 + (i % n16) * 16) = make_uint4(0, 0, 0, 0);
     }
     fence_proxy_async_smem();
@@ -250,14 +266,14 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
       tma_prefetch_desc(&tmR2);
       tma_prefetch_desc(&tmC1);
       tma_prefetch_desc(&tmC2);
-      mbar_expect_tx(r_full, MODE == MODE_DQ ? (uint32_t)(4 * p.rows_used * 128) : (uint32_t)(2 * BW_TILE_BYTES));
+      mbar_expect_tx(r_full, MODE == MODE_DQ ? (uint32_t)(4 * p.rows_used * HD) : (uint32_t)(2 * 128 * HD * 2));
       {
         const int c1 = MODE == MODE_DQ ? rt * p.npos : rt * 128;
         const int c2 = MODE == MODE_DQ ? g * p.gs : g;
         tma_load_4d(smem + S::R1, &tmR1, r_full, 0, c1, c2, b);
-        tma_load_4d(smem + S::R1 + BW_TILE_BYTES / 2, &tmR1, r_full, 64, c1, c2, b);
+        if (HD == 128) tma_load_4d(smem + S::R1 + BW_TILE_BYTES / 2, &tmR1, r_full, 64, c1, c2, b);
         tma_load_4d(smem + S::R2, &tmR2, r_full, 0, c1, c2, b);
-        tma_load_4d(smem + S::R2 + BW_TILE_BYTES / 2, &tmR2, r_full, 64, c1, c2, b);
+        if (HD == 128) tma_load_4d(smem + S::R2 + BW_TILE_BYTES / 2, &tmR2, r_full, 64, c1, c2, b);
       }
       uint32_t u = 0;
       bool ok = true;
@@ -276,11 +292,11 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
             x1 = ct * p.npos_col + h * p.u_dp;
             x2 = g * p.gs + h * p.u_dh;
           }
-          mbar_expect_tx(&c_full[st], MODE == MODE_DQ ? (uint32_t)(2 * BW_UNIT_BYTES) : (uint32_t)(4 * p.cols_used * 128));
+          mbar_expect_tx(&c_full[st], MODE == MODE_DQ ? (uint32_t)(2 * 64 * HD * 2) : (uint32_t)(4 * p.cols_used * HD));
           tma_load_4d(c1, &tmC1, &c_full[st], 0, x1, x2, b);
-          tma_load_4d(c1 + BW_UNIT_BYTES / 2, &tmC1, &c_full[st], 64, x1, x2, b);
+          if (HD == 128) tma_load_4d(c1 + BW_UNIT_BYTES / 2, &tmC1, &c_full[st], 64, x1, x2, b);
           tma_load_4d(c2, &tmC2, &c_full[st], 0, x1, x2, b);
-          tma_load_4d(c2 + BW_UNIT_BYTES / 2, &tmC2, &c_full[st], 64, x1, x2, b);
+          if (HD == 128) tma_load_4d(c2 + BW_UNIT_BYTES / 2, &tmC2, &c_full[st], 64, x1, x2, b);
         }
       }
       if (!ok) {  // let copies in flight land before the CTA's shared memory is released
@@ -300,7 +316,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
     if (lane == 0 && n_active > 0) {
       const uint32_t par = warp == 1 ? 0u : 1u;
       constexpr uint32_t idesc_xy = make_idesc_bf16(128, 64, 0, 0);     // both operands K-major
-      constexpr uint32_t idesc_acc = make_idesc_bf16(128, 128, 0, 1);   // A from TMEM, B MN-major
+      constexpr uint32_t idesc_acc = make_idesc_bf16(128, HD, 0, 1);    // A from TMEM, B MN-major
       const uint32_t r1 = smem_u32(smem + S::R1), r2 = smem_u32(smem + S::R2);
       const uint32_t cbase = smem_u32(smem + S::C);
       const uint32_t n_units = 2u * (uint32_t)n_active;
@@ -318,7 +334,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
         tc_fence_after();
         const uint32_t c1 = cbase + st * 2 * BW_UNIT_BYTES, c2 = c1 + BW_UNIT_BYTES;
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
+        for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t a_off = (uint32_t)((kk >> 2) * (BW_TILE_BYTES / 2) + (kk & 3) * 32);
           const uint32_t b_off = (uint32_t)((kk >> 2) * (BW_UNIT_BYTES / 2) + (kk & 3) * 32);
           if (MODE == MODE_DQ)
@@ -328,7 +344,7 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
                         idesc_xy, kk != 0);
         }
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
+        for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t a_off = (uint32_t)((kk >> 2) * (BW_TILE_BYTES / 2) + (kk & 3) * 32);
           const uint32_t b_off = (uint32_t)((kk >> 2) * (BW_UNIT_BYTES / 2) + (kk & 3) * 32);
           if (MODE == MODE_DQ)
@@ -445,14 +461,14 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
 #pragma unroll
       for (int i = 0; i < 16; ++i) z[i] = 0;
 #pragma unroll
-      for (int c = 0; c < 64; c += 16) {
-        if (MODE == MODE_DKV) tmem_st_32x32b_x16(tmem_A1 + lane_base + (uint32_t)(64 * hh + c), z);
-        tmem_st_32x32b_x16(tmem_A2 + lane_base + (uint32_t)(64 * hh + c), z);
+      for (int c = 0; c < HD / 2; c += 16) {
+        if (MODE == MODE_DKV) tmem_st_32x32b_x16(tmem_A1 + lane_base + (uint32_t)((HD / 2) * hh + c), z);
+        tmem_st_32x32b_x16(tmem_A2 + lane_base + (uint32_t)((HD / 2) * hh + c), z);
       }
       if (MODE == MODE_DQ) ok = mbar_wait_bounded(r_full, 0, abort_flag, p.status, STATUS_TIMEOUT_FULL);
       // MODE_DQ row operands: shared memory -> registers -> TMEM. This thread moves features
       // [64·hh, +64) of its row: one 128-byte swizzled row of chunk hh = 32 columns of bf16 pairs.
-      if (MODE == MODE_DQ && ok) {
+      if (MODE == MODE_DQ && ok && (HD == 128 || hh == 0)) {
 #pragma unroll
         for (int op = 0; op < 2; ++op) {
           const uint8_t* src = smem + (op == 0 ? S::R1 : S::R2) + hh * (BW_TILE_BYTES / 2);
@@ -508,8 +524,11 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
         BW_TRACE(2, 2200000 + 2 * s + h);
         // bit e of `hide`: column cc0 + e is not visible to this thread's row
         uint32_t hide = 0;
-        if (msk && win > 0) {
+        bool win_done = false;
+        if constexpr (GEN) {
+         if (msk && win > 0) {
           // visible iff 0 <= position of the query − token < window
+          win_done = true;
           if (MODE == MODE_DQ) {
             uint32_t nm = __ballot_sync(0xffffffffu, v_tp > qpos_min_of(rt) || v_tp <= qpos_max_of(rt) - win);
             while (nm) {
@@ -528,7 +547,9 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
               pp_ = pp_ + 1 == p.hnpos ? 0 : pp_ + 1;
             }
           }
-        } else if (msk) {
+         }
+        }
+        if (msk && !win_done) {
           if (MODE == MODE_DQ) {
             // only columns beyond the first query of the CTA need the per-row comparison
             // (positions broadcast by shuffle)
@@ -622,9 +643,9 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
     if (ok) {
       tc_fence_after();
       if (MODE == MODE_DQ) {
-        __nv_bfloat16* dst = p.dq + (((long long)b * p.H + g * p.gs + hq) * p.T + tq) * 128;
+        __nv_bfloat16* dst = p.dq + (((long long)b * p.H + g * p.gs + hq) * p.T + tq) * HD;
 #pragma unroll 1
-        for (int c0 = 64 * hh; c0 < 64 * hh + 64; c0 += 32) {
+        for (int c0 = (HD / 2) * hh; c0 < (HD / 2) * (hh + 1); c0 += 32) {
           uint32_t r[32];
           tmem_ld_32x32b_x32(tmem_A2 + lane_base + (uint32_t)c0, r);
           tmem_ld_wait();
@@ -641,9 +662,9 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
           }
         }
       } else {
-        const long long off = b * p.dk_sb + g * p.dk_sg + (long long)(rt * 128 + row) * 128;
+        const long long off = b * p.dk_sb + g * p.dk_sg + (long long)(rt * 128 + row) * HD;
 #pragma unroll 1
-        for (int c0 = 64 * hh; c0 < 64 * hh + 64; c0 += 32) {
+        for (int c0 = (HD / 2) * hh; c0 < (HD / 2) * (hh + 1); c0 += 32) {
           uint32_t r1v[32], r2v[32];
           tmem_ld_32x32b_x32(tmem_A1 + lane_base + (uint32_t)c0, r1v);
           tmem_ld_32x32b_x32(tmem_A2 + lane_base + (uint32_t)c0, r2v);
@@ -668,8 +689,8 @@ sdpa_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
         }
       }
     } else if (n_active == 0 && MODE == MODE_DQ && row_valid) {
-      __nv_bfloat16* dst = p.dq + (((long long)b * p.H + g * p.gs + hq) * p.T + tq) * 128;
-      for (int c = 64 * hh; c < 64 * hh + 64; c += 8) *reinterpret_cast<uint4*>(dst + c) = make_uint4(0, 0, 0, 0);
+      __nv_bfloat16* dst = p.dq + (((long long)b * p.H + g * p.gs + hq) * p.T + tq) * HD;
+      for (int c = (HD / 2) * hh; c < (HD / 2) * (hh + 1); c += 8) *reinterpret_cast<uint4*>(dst + c) = make_uint4(0, 0, 0, 0);
     }
   }
   tc_fence_before();
@@ -704,6 +725,20 @@ static int bw_make_tmap_4d(CUtensorMap* tm, const void* ptr, uint64_t d0, uint64
   return r == CUDA_SUCCESS ? KVB_OK : KVB_ERR_TMAP;
 }
 
+// the two launches of one backward call for one (GEN, head size) instantiation: dQ on the side stream, dK / dV on the caller's
+template <bool GEN, int HD>
+static void bw_launch(const CUtensorMap& tmQ, const CUtensorMap& tmdO, const CUtensorMap& tmKh, const CUtensorMap& tmVh,
+                      const BwParams& pq, const CUtensorMap& tmK, const CUtensorMap& tmV, const CUtensorMap& tmQh,
+                      const CUtensorMap& tmdOh, const BwParams& p, cudaStream_t side, cudaStream_t s) {
+  static kvb::PerDeviceOnce attr_once;
+  if (attr_once.first()) {
+    cudaFuncSetAttribute(sdpa_bwd_kernel<MODE_DQ, GEN, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwSmem::TOTAL);
+    cudaFuncSetAttribute(sdpa_bwd_kernel<MODE_DKV, GEN, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwSmem::TOTAL);
+  }
+  sdpa_bwd_kernel<MODE_DQ, GEN, HD><<<p.B * p.G * p.nQT, BW_THREADS, BwSmem::TOTAL, side>>>(tmQ, tmdO, tmKh, tmVh, pq);
+  sdpa_bwd_kernel<MODE_DKV, GEN, HD><<<p.B * p.G * p.nT, BW_THREADS, BwSmem::TOTAL, s>>>(tmK, tmV, tmQh, tmdOh, p);
+}
+
 }  // namespace kvb
 
 extern "C" int kvb_att_tile_minmax(const int32_t* token_pos, int32_t* tmin, int32_t* tmax, int B, int G, int L, long long tp_sb,
@@ -729,29 +764,31 @@ extern "C" long long kvb_sdpa_bwd_scratch_bytes(int B, int H, int G, int q_len, 
   return (bw_round4(2LL * B * G * nT) + bw_round4((long long)B * H * q_len)) * 4 + (long long)B * H * q_len * 128 * 2;
 }
 
-// window: sliding window in tokens (0: none); softcap: logit soft-capping threshold (0: none), as in the forward.
+// head_size: 128 or 64; window: sliding window in tokens (0: none); softcap: logit soft-capping threshold (0: none),
+// as in the forward.
 extern "C" int kvb_sdpa_bwd_ex(const void* q, const void* k, const void* v, const int32_t* token_pos, const void* out,
                                const void* dout, const float* lse, void* dq, float* dk, float* dv, void* scratch, int B, int H,
-                               int G, int q_len, int kv_len, long long k_sb, long long k_sg, long long tp_sb, long long tp_sg,
-                               long long dk_sb, long long dk_sg, float scale, int input_pos, int window, float softcap,
-                               int* status, void* stream);
+                               int G, int q_len, int kv_len, int head_size, long long k_sb, long long k_sg, long long tp_sb,
+                               long long tp_sg, long long dk_sb, long long dk_sg, float scale, int input_pos, int window,
+                               float softcap, int* status, void* stream);
 
 extern "C" int kvb_sdpa_bwd(const void* q, const void* k, const void* v, const int32_t* token_pos, const void* out,
                             const void* dout, const float* lse, void* dq, float* dk, float* dv, void* scratch, int B, int H,
                             int G, int q_len, int kv_len, long long k_sb, long long k_sg, long long tp_sb, long long tp_sg,
                             long long dk_sb, long long dk_sg, float scale, int input_pos, int* status, void* stream) {
-  return kvb_sdpa_bwd_ex(q, k, v, token_pos, out, dout, lse, dq, dk, dv, scratch, B, H, G, q_len, kv_len, k_sb, k_sg, tp_sb, tp_sg,
-                         dk_sb, dk_sg, scale, input_pos, 0, 0.f, status, stream);
+  return kvb_sdpa_bwd_ex(q, k, v, token_pos, out, dout, lse, dq, dk, dv, scratch, B, H, G, q_len, kv_len, 128, k_sb, k_sg, tp_sb,
+                         tp_sg, dk_sb, dk_sg, scale, input_pos, 0, 0.f, status, stream);
 }
 
 extern "C" int kvb_sdpa_bwd_ex(const void* q, const void* k, const void* v, const int32_t* token_pos, const void* out,
                                const void* dout, const float* lse, void* dq, float* dk, float* dv, void* scratch, int B, int H,
-                               int G, int q_len, int kv_len, long long k_sb, long long k_sg, long long tp_sb, long long tp_sg,
-                               long long dk_sb, long long dk_sg, float scale, int input_pos, int window, float softcap,
-                               int* status, void* stream) {
+                               int G, int q_len, int kv_len, int head_size, long long k_sb, long long k_sg, long long tp_sb,
+                               long long tp_sg, long long dk_sb, long long dk_sg, float scale, int input_pos, int window,
+                               float softcap, int* status, void* stream) {
   using namespace kvb;
   if (B <= 0 || H <= 0 || G <= 0 || q_len <= 0 || kv_len <= 0 || H % G) return KVB_ERR_ARG;
   if (window < 0 || softcap < 0.f || (softcap > 0.f && scale <= 0.f)) return KVB_ERR_ARG;
+  if (head_size != 128 && head_size != 64) return KVB_ERR_UNSUPPORTED;
   const int gs = H / G;
   if (gs > 64) return KVB_ERR_UNSUPPORTED;  // a 64-column unit of the dK/dV launch holds all heads of a group
   if ((k_sb % 8) || (k_sg % 8) || (dk_sb % 4) || (dk_sg % 4)) return KVB_ERR_ALIGN;
@@ -793,33 +830,29 @@ extern "C" int kvb_sdpa_bwd_ex(const void* q, const void* k, const void* v, cons
   // 64 slots (dQ launch) or hnpos positions x gs heads (dK/dV launch)
   CUtensorMap tmQ, tmdO, tmK, tmV, tmQh, tmdOh, tmKh, tmVh;
   int rc;
-  const uint64_t qT = (uint64_t)q_len, HT = (uint64_t)H * q_len;
+  const uint64_t qT = (uint64_t)q_len, HT = (uint64_t)H * q_len, hd = (uint64_t)head_size;
   // Q (B,H,T,D): dims (D,T,H,B)
-  if ((rc = bw_make_tmap_4d(&tmQ, q, 128, q_len, H, B, 128, qT * 128, HT * 128, 64, p.npos, gs))) return rc;
-  if ((rc = bw_make_tmap_4d(&tmQh, q, 128, q_len, H, B, 128, qT * 128, HT * 128, 64, p.hnpos, p.u_heads))) return rc;
+  if ((rc = bw_make_tmap_4d(&tmQ, q, hd, q_len, H, B, hd, qT * hd, HT * hd, 64, p.npos, gs))) return rc;
+  if ((rc = bw_make_tmap_4d(&tmQh, q, hd, q_len, H, B, hd, qT * hd, HT * hd, 64, p.hnpos, p.u_heads))) return rc;
   // dO (B,T,H,D) viewed with dims (D,T,H,B): T stride H*D, H stride D
   if (dOt) {  // the head-major copy that the delta kernel leaves: same strides as Q
-    if ((rc = bw_make_tmap_4d(&tmdO, dOt, 128, q_len, H, B, 128, qT * 128, HT * 128, 64, p.npos, gs))) return rc;
-    if ((rc = bw_make_tmap_4d(&tmdOh, dOt, 128, q_len, H, B, 128, qT * 128, HT * 128, 64, p.hnpos, p.u_heads))) return rc;
+    if ((rc = bw_make_tmap_4d(&tmdO, dOt, hd, q_len, H, B, hd, qT * hd, HT * hd, 64, p.npos, gs))) return rc;
+    if ((rc = bw_make_tmap_4d(&tmdOh, dOt, hd, q_len, H, B, hd, qT * hd, HT * hd, 64, p.hnpos, p.u_heads))) return rc;
   } else {
-    if ((rc = bw_make_tmap_4d(&tmdO, dout, 128, q_len, H, B, (uint64_t)H * 128, 128, HT * 128, 64, p.npos, gs))) return rc;
-    if ((rc = bw_make_tmap_4d(&tmdOh, dout, 128, q_len, H, B, (uint64_t)H * 128, 128, HT * 128, 64, p.hnpos, p.u_heads))) return rc;
+    if ((rc = bw_make_tmap_4d(&tmdO, dout, hd, q_len, H, B, (uint64_t)H * hd, hd, HT * hd, 64, p.npos, gs))) return rc;
+    if ((rc = bw_make_tmap_4d(&tmdOh, dout, hd, q_len, H, B, (uint64_t)H * hd, hd, HT * hd, 64, p.hnpos, p.u_heads))) return rc;
   }
-  if ((rc = bw_make_tmap_4d(&tmK, k, 128, kv_len, G, B, 128, k_sg, k_sb, 64, 128, 1))) return rc;
-  if ((rc = bw_make_tmap_4d(&tmV, v, 128, kv_len, G, B, 128, k_sg, k_sb, 64, 128, 1))) return rc;
-  if ((rc = bw_make_tmap_4d(&tmKh, k, 128, kv_len, G, B, 128, k_sg, k_sb, 64, 64, 1))) return rc;
-  if ((rc = bw_make_tmap_4d(&tmVh, v, 128, kv_len, G, B, 128, k_sg, k_sb, 64, 64, 1))) return rc;
+  if ((rc = bw_make_tmap_4d(&tmK, k, hd, kv_len, G, B, hd, k_sg, k_sb, 64, 128, 1))) return rc;
+  if ((rc = bw_make_tmap_4d(&tmV, v, hd, kv_len, G, B, hd, k_sg, k_sb, 64, 128, 1))) return rc;
+  if ((rc = bw_make_tmap_4d(&tmKh, k, hd, kv_len, G, B, hd, k_sg, k_sb, 64, 64, 1))) return rc;
+  if ((rc = bw_make_tmap_4d(&tmVh, v, hd, kv_len, G, B, hd, k_sg, k_sb, 64, 64, 1))) return rc;
 
   if ((rc = kvb_att_tile_minmax(token_pos, tmin, tmax, B, G, kv_len, tp_sb, tp_sg, 128, stream))) return rc;
   const long long rows = (long long)B * q_len * H;
-  att_delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, delta, dOt, B, q_len, H);
-  static kvb::PerDeviceOnce attr_once;
-  if (attr_once.first()) {
-    cudaFuncSetAttribute(sdpa_bwd_kernel<MODE_DQ, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwSmem::TOTAL);
-    cudaFuncSetAttribute(sdpa_bwd_kernel<MODE_DKV, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwSmem::TOTAL);
-    cudaFuncSetAttribute(sdpa_bwd_kernel<MODE_DQ, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwSmem::TOTAL);
-    cudaFuncSetAttribute(sdpa_bwd_kernel<MODE_DKV, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwSmem::TOTAL);
-  }
+  if (head_size == 128)
+    att_delta_kernel<128><<<(unsigned)((rows + 7) / 8), 256, 0, s>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, delta, dOt, B, q_len, H);
+  else
+    att_delta_kernel<64><<<(unsigned)((rows + 7) / 8), 256, 0, s>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, delta, dOt, B, q_len, H);
   // The two launches are independent (dQ | dK, dV). They run on two streams, forked from and joined
   // back into the caller's stream, so that the tail of one grid (256 CTAs of the dQ launch fill
   // 148 SMs 1.73 times) is filled with CTAs of the other.
@@ -838,12 +871,13 @@ extern "C" int kvb_sdpa_bwd_ex(const void* q, const void* k, const void* v, cons
   pq.trace = g_bw_trace_mode == 0 ? g_bw_trace : nullptr; pq.trace_cap = g_bw_trace_cap;
   p.trace = g_bw_trace_mode == 1 ? g_bw_trace : nullptr; p.trace_cap = g_bw_trace_cap;
   // the launch with few long CTAs goes first: the short CTAs of the other one fill its second wave
-  if (window > 0 || softcap > 0.f) {
-    sdpa_bwd_kernel<MODE_DQ, true><<<B * G * p.nQT, BW_THREADS, BwSmem::TOTAL, side[dev]>>>(tmQ, tmdO, tmKh, tmVh, pq);
-    sdpa_bwd_kernel<MODE_DKV, true><<<B * G * p.nT, BW_THREADS, BwSmem::TOTAL, s>>>(tmK, tmV, tmQh, tmdOh, p);
+  const bool gen = window > 0 || softcap > 0.f;
+  if (head_size == 128) {
+    if (gen) bw_launch<true, 128>(tmQ, tmdO, tmKh, tmVh, pq, tmK, tmV, tmQh, tmdOh, p, side[dev], s);
+    else bw_launch<false, 128>(tmQ, tmdO, tmKh, tmVh, pq, tmK, tmV, tmQh, tmdOh, p, side[dev], s);
   } else {
-    sdpa_bwd_kernel<MODE_DQ, false><<<B * G * p.nQT, BW_THREADS, BwSmem::TOTAL, side[dev]>>>(tmQ, tmdO, tmKh, tmVh, pq);
-    sdpa_bwd_kernel<MODE_DKV, false><<<B * G * p.nT, BW_THREADS, BwSmem::TOTAL, s>>>(tmK, tmV, tmQh, tmdOh, p);
+    if (gen) bw_launch<true, 64>(tmQ, tmdO, tmKh, tmVh, pq, tmK, tmV, tmQh, tmdOh, p, side[dev], s);
+    else bw_launch<false, 64>(tmQ, tmdO, tmKh, tmVh, pq, tmK, tmV, tmQh, tmdOh, p, side[dev], s);
   }
   cudaEventRecord(ev_join[dev], side[dev]);
   cudaStreamWaitEvent(s, ev_join[dev], 0);

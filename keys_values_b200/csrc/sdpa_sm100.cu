@@ -247,8 +247,8 @@ __device__ __forceinline__ constexpr bool cs_pair_on_fma(int pair) { return (pai
 
 // Rows of a query tile that TMA does not write (npos · gs < 128) are cleared once, so that their
 // scores are finite zeros.
-__device__ __forceinline__ void f2_zero_unused_rows(uint8_t* tile, int rows_used, int tid, int nthreads) {
-  const int n16 = (F2_T - rows_used) * 8 * 2;  // 16-byte units: rows x 8 units x 2 chunks
+__device__ __forceinline__ void f2_zero_unused_rows(uint8_t* tile, int rows_used, int tid, int nthreads, int nch) {
+  const int n16 = (F2_T - rows_used) * 8 * nch;  // 16-byte units: rows x 8 units x chunks of 64 features
   for (int u = tid; u < n16; u += nthreads) {
     const int chunk = u / ((F2_T - rows_used) * 8);
     const int rem = u % ((F2_T - rows_used) * 8);
@@ -259,7 +259,8 @@ __device__ __forceinline__ void f2_zero_unused_rows(uint8_t* tile, int rows_used
 
 // GEN: sliding window and / or soft-capping are in use (a separate instantiation, so that the plain kernel keeps its
 // register allocation)
-template <bool GEN>
+// HD: head size, 128 or 64 (one 64-feature chunk per tile, half as many K steps for S, O of 64 columns)
+template <bool GEN, int HD>
 __global__ void __launch_bounds__(F2_THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const F2Params p) {
@@ -312,8 +313,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   for (int t = threadIdx.x; t < min(p.nT, F2_MAX_FLAG_TILES); t += F2_THREADS) tflags[t] = (uint8_t)calc_bits(t);
   auto tile_bits = [&](int t) -> uint32_t { return t >= F2_MAX_FLAG_TILES ? calc_bits(t) : (uint32_t)tflags[t]; };
   if (p.rows_used < F2_T) {
-    f2_zero_unused_rows(smem + F2Smem::Q, p.rows_used, threadIdx.x, F2_THREADS);
-    f2_zero_unused_rows(smem + F2Smem::Q + F2_TILE_BYTES, p.rows_used, threadIdx.x, F2_THREADS);
+    f2_zero_unused_rows(smem + F2Smem::Q, p.rows_used, threadIdx.x, F2_THREADS, HD / 64);
+    f2_zero_unused_rows(smem + F2Smem::Q + F2_TILE_BYTES, p.rows_used, threadIdx.x, F2_THREADS, HD / 64);
     fence_proxy_async_smem();
   }
   // bias operands: zero everywhere, then ones in column 0 of the A tile (the producer fills column 0 of the B tiles)
@@ -356,12 +357,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tma_prefetch_desc(&tmQ);
         tma_prefetch_desc(&tmK);
         tma_prefetch_desc(&tmV);
-        const uint32_t q_bytes = (uint32_t)p.rows_used * 128u * 2u;
+        const uint32_t q_bytes = (uint32_t)p.rows_used * (uint32_t)HD * 2u;
         for (int w = 0; w < 2; ++w) {
           uint8_t* qd = smem + F2Smem::Q + w * F2_TILE_BYTES;
           mbar_expect_tx(&q_full[w], q_bytes);
           tma_load_4d(qd, &tmQ, &q_full[w], 0, g * p.gs, t0 + w * p.npos, b);
-          tma_load_4d(qd + F2_CHUNK_BYTES, &tmQ, &q_full[w], 64, g * p.gs, t0 + w * p.npos, b);
+          if (HD == 128) tma_load_4d(qd + F2_CHUNK_BYTES, &tmQ, &q_full[w], 64, g * p.gs, t0 + w * p.npos, b);
         }
       }
       const int32_t* pos_row = p.pos + bg * p.nT * F2_T;
@@ -403,9 +404,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           if (lane == 0) {
             uint8_t* d = smem + F2Smem::KV + st * F2_TILE_BYTES;
             const CUtensorMap* tm = kv == 0 ? &tmK : &tmV;
-            mbar_expect_tx(&kv_full[st], F2_TILE_BYTES);
+            mbar_expect_tx(&kv_full[st], F2_T * HD * 2);
             tma_load_4d(d, tm, &kv_full[st], 0, t * F2_T, g, b);
-            tma_load_4d(d + F2_CHUNK_BYTES, tm, &kv_full[st], 64, t * F2_T, g, b);
+            if (HD == 128) tma_load_4d(d + F2_CHUNK_BYTES, tm, &kv_full[st], 64, t * F2_T, g, b);
           }
           ++seq;
         }
@@ -421,7 +422,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // ------------------------------------------------------------- MMA issuer
     if (lane == 0 && n_active > 0) {
       constexpr uint32_t idesc_qk = make_idesc_bf16(F2_T, F2_T, 0, 0);  // Q, K both K-major
-      constexpr uint32_t idesc_pv = make_idesc_bf16(F2_T, F2_T, 0, 1);  // P K-major (TMEM), V MN-major
+      constexpr uint32_t idesc_pv = make_idesc_bf16(F2_T, HD, 0, 1);    // P K-major (TMEM), V MN-major
       bool ok = true;
       F2_TRACE_DECL(true);
       for (int w = 0; w < 2 && ok; ++w) ok = mbar_wait_bounded(&q_full[w], 0, abort_flag, p.status, STATUS_TIMEOUT_FULL);
@@ -435,7 +436,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t q_addr = smem_u32(smem + F2Smem::Q + w * F2_TILE_BYTES);
         const uint32_t k_addr = stage_addr(kseq);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
+        for (int kk = 0; kk < HD / 16; ++kk) {
           // 16 features per step: chunk kk/4, 32 bytes per step inside the swizzled 128-byte row
           const uint32_t off = (uint32_t)((kk >> 2) * F2_CHUNK_BYTES + (kk & 3) * 32);
           umma_f16_ss(tmem_base + (uint32_t)(w * F2_T), make_smem_desc_sw128(q_addr + off, 16, 1024),
@@ -665,7 +666,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const float f = raise ? f2_exp2(m_used - m_new) : 1.f;
         l *= f;
 #pragma unroll 1
-        for (int c0 = 0; c0 < F2_T; c0 += 32) {
+        for (int c0 = 0; c0 < HD; c0 += 32) {
           uint32_t o[32];
           tmem_ld_32x32b_x32(tmem_O + (uint32_t)c0, o);
           tmem_ld_wait();
@@ -726,9 +727,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (p.n_split > 1) {
         // partial result of this split: normalised fp32 rows and their log2 normaliser
         const long long prow = (((long long)split * p.B + b) * p.H + (g * p.gs + (row_valid ? hq : 0))) * p.T + (row_valid ? tq : 0);
-        float* pdst = p.part_o + prow * F2_T;
+        float* pdst = p.part_o + prow * HD;
 #pragma unroll 1
-        for (int c0 = 0; c0 < F2_T; c0 += 32) {
+        for (int c0 = 0; c0 < HD; c0 += 32) {
           uint32_t o[32];
           if (n_active > 0) {
             tmem_ld_32x32b_x32(tmem_O + (uint32_t)c0, o);
@@ -748,9 +749,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (row_valid) p.part_lse2[prow] = l > 0.f ? lse2 : -INFINITY;
       } else {
       // tcgen05.ld is warp-collective: rows without a query take part in the loads and skip the stores
-      __nv_bfloat16* dst = p.out + (((long long)b * p.T + (row_valid ? tq : 0)) * p.H + (g * p.gs + (row_valid ? hq : 0))) * F2_T;
+      __nv_bfloat16* dst = p.out + (((long long)b * p.T + (row_valid ? tq : 0)) * p.H + (g * p.gs + (row_valid ? hq : 0))) * HD;
 #pragma unroll 1
-      for (int c0 = 0; c0 < F2_T; c0 += 32) {
+      for (int c0 = 0; c0 < HD; c0 += 32) {
         uint32_t o[32];
         if (n_active > 0) {
           tmem_ld_32x32b_x32(tmem_O + (uint32_t)c0, o);
@@ -787,6 +788,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 // Combines the partial results of the splits of a query row: out = Σ_s w_s O_s / Σ_s w_s with w_s = 2^(lse2_s − max),
 // in a fixed order of the splits. One warp per packed query row (the rows of the lse2 layout, padding rows included,
 // which get +inf there as in the unsplit kernel); lane l holds features 4l .. 4l+3.
+template <int HD>
 __global__ void __launch_bounds__(256) flash_merge_kernel(const F2Params p) {
   const long long wrow = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);  // index into (B, G, nQT, 128)
   const int lane = threadIdx.x & 31;
@@ -807,23 +809,34 @@ __global__ void __launch_bounds__(256) flash_merge_kernel(const F2Params p) {
   const long long prow = ((long long)b * p.H + h) * p.T + tq;
   float mx = -INFINITY;
   for (int sidx = 0; sidx < p.n_split; ++sidx) mx = fmaxf(mx, p.part_lse2[sidx * stride + prow]);
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);  // HD = 64: x and y only (lane l holds features 2l, 2l+1)
   float total = 0.f;
   if (mx > -INFINITY) {
     for (int sidx = 0; sidx < p.n_split; ++sidx) {
       const float w = exp2f(p.part_lse2[sidx * stride + prow] - mx);
       if (w > 0.f) {
-        const float4 o = *reinterpret_cast<const float4*>(p.part_o + (sidx * stride + prow) * F2_T + 4 * lane);
-        acc.x += w * o.x; acc.y += w * o.y; acc.z += w * o.z; acc.w += w * o.w;
+        const float* src = p.part_o + (sidx * stride + prow) * HD;
+        if (HD == 128) {
+          const float4 o = *reinterpret_cast<const float4*>(src + 4 * lane);
+          acc.x += w * o.x; acc.y += w * o.y; acc.z += w * o.z; acc.w += w * o.w;
+        } else {
+          const float2 o = *reinterpret_cast<const float2*>(src + 2 * lane);
+          acc.x += w * o.x; acc.y += w * o.y;
+        }
         total += w;
       }
     }
   }
   const float inv = total > 0.f ? 1.f / total : 0.f;
-  uint2 v;
-  v.x = pack_bf16x2(acc.x * inv, acc.y * inv);
-  v.y = pack_bf16x2(acc.z * inv, acc.w * inv);
-  *reinterpret_cast<uint2*>(p.out + (((long long)b * p.T + tq) * p.H + h) * F2_T + 4 * lane) = v;
+  __nv_bfloat16* dst = p.out + (((long long)b * p.T + tq) * p.H + h) * HD;
+  if (HD == 128) {
+    uint2 v;
+    v.x = pack_bf16x2(acc.x * inv, acc.y * inv);
+    v.y = pack_bf16x2(acc.z * inv, acc.w * inv);
+    *reinterpret_cast<uint2*>(dst + 4 * lane) = v;
+  } else {
+    *reinterpret_cast<uint32_t*>(dst + 2 * lane) = pack_bf16x2(acc.x * inv, acc.y * inv);
+  }
   if (lane == 0) {
     const float lse2 = total > 0.f ? mx + log2f(total) : INFINITY;
     if (p.lse) p.lse[prow] = lse2 * 0.6931471805599453f;
@@ -842,7 +855,7 @@ struct CsSmem {
   static constexpr int TOTAL = XCH + 512;
 };
 
-template <bool GEN>
+template <bool GEN, int HD>
 __global__ void __launch_bounds__(F2_THREADS, 1)
 colsum_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const F2Params p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -886,7 +899,7 @@ colsum_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 
   if (p.rows_used < F2_T) {
     for (int s = 0; s < CS_QSTAGES; ++s)
-      f2_zero_unused_rows(smem + CsSmem::Q + s * F2_TILE_BYTES, p.rows_used, threadIdx.x, F2_THREADS);
+      f2_zero_unused_rows(smem + CsSmem::Q + s * F2_TILE_BYTES, p.rows_used, threadIdx.x, F2_THREADS, HD / 64);
     fence_proxy_async_smem();
   }
   if (threadIdx.x == 0) {
@@ -915,10 +928,10 @@ colsum_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     if (lane == 0 && n_q > 0) {
       tma_prefetch_desc(&tmQ);
       tma_prefetch_desc(&tmK);
-      mbar_expect_tx(k_full, F2_TILE_BYTES);
+      mbar_expect_tx(k_full, F2_T * HD * 2);
       tma_load_4d(smem + CsSmem::K, &tmK, k_full, 0, t * F2_T, g, b);
-      tma_load_4d(smem + CsSmem::K + F2_CHUNK_BYTES, &tmK, k_full, 64, t * F2_T, g, b);
-      const uint32_t q_bytes = (uint32_t)p.rows_used * 128u * 2u;
+      if (HD == 128) tma_load_4d(smem + CsSmem::K + F2_CHUNK_BYTES, &tmK, k_full, 64, t * F2_T, g, b);
+      const uint32_t q_bytes = (uint32_t)p.rows_used * (uint32_t)HD * 2u;
       bool ok = true;
       for (int i = 0; i < n_q && ok; ++i) {
         const int st = i % CS_QSTAGES;
@@ -929,7 +942,7 @@ colsum_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         uint8_t* qd = smem + CsSmem::Q + st * F2_TILE_BYTES;
         mbar_expect_tx(&q_full[st], q_bytes);
         tma_load_4d(qd, &tmQ, &q_full[st], 0, g * p.gs, (qt_first + i) * p.npos, b);
-        tma_load_4d(qd + F2_CHUNK_BYTES, &tmQ, &q_full[st], 64, g * p.gs, (qt_first + i) * p.npos, b);
+        if (HD == 128) tma_load_4d(qd + F2_CHUNK_BYTES, &tmQ, &q_full[st], 64, g * p.gs, (qt_first + i) * p.npos, b);
       }
       if (!ok) {
         long long c0 = clock64();
@@ -949,7 +962,7 @@ colsum_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         tc_fence_after();
         const uint32_t q_addr = smem_u32(smem + CsSmem::Q + st * F2_TILE_BYTES);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
+        for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (uint32_t)((kk >> 2) * F2_CHUNK_BYTES + (kk & 3) * 32);
           umma_f16_ss(tmem_base + (uint32_t)(sb * F2_T), make_smem_desc_sw128(k_addr + off, 16, 1024),
                       make_smem_desc_sw128(q_addr + off, 16, 1024), idesc, kk != 0);
@@ -1078,6 +1091,24 @@ static int f2_make_tmap(CUtensorMap* tm, const void* ptr, uint64_t d0, uint64_t 
 
 static inline long long f2_round4(long long x) { return (x + 3) / 4 * 4; }
 
+// the launches of one forward call for one (GEN, head size) instantiation
+template <bool GEN, int HD>
+static int f2_launch(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const F2Params& p, cudaStream_t s) {
+  static kvb::PerDeviceOnce attr_once;
+  if (attr_once.first()) {
+    cudaFuncSetAttribute(flash_fwd_kernel<GEN, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, F2Smem::TOTAL);
+    cudaFuncSetAttribute(colsum_kernel<GEN, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, CsSmem::TOTAL);
+  }
+  const int nPair = (p.nQT + 1) / 2;
+  flash_fwd_kernel<GEN, HD><<<dim3(p.B * p.G * nPair, p.n_split), F2_THREADS, F2Smem::TOTAL, s>>>(tmQ, tmK, tmV, p);
+  if (p.n_split > 1) {
+    const long long rows = (long long)p.B * p.G * p.nQT * F2_T;
+    flash_merge_kernel<HD><<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(p);
+  }
+  if (p.weights) colsum_kernel<GEN, HD><<<p.B * p.G * p.nT, F2_THREADS, CsSmem::TOTAL, s>>>(tmQ, tmK, p);
+  return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
+}
+
 }  // namespace kvb
 
 // Per-tile min/max of the token positions for tiles of `tile` slots (64 or 128): (B,G,nT) each.
@@ -1134,26 +1165,28 @@ extern "C" long long kvb_sdpa_fwd_scratch_bytes(int B, int H, int G, int q_len, 
 // q (B,H,T,128) contiguous bf16; k, v (B,G,L,128) bf16 with batch / group strides k_sb, k_sg (elements);
 // token_pos (B,G,L) int32 with strides, or NULL (slot j holds token j); out (B,T,H,128) bf16;
 // lse (B,H,T) fp32 or NULL; weights (B,G,L) fp32 or NULL.
-// window: sliding window in tokens (0: none); softcap: logit soft-capping threshold (0: none).
+// head_size: 128 or 64 (the last axis of q, k, v, out); window: sliding window in tokens (0: none); softcap: logit
+// soft-capping threshold (0: none).
 extern "C" int kvb_sdpa_fwd_ex(const void* q, const void* k, const void* v, const int32_t* token_pos, void* out, float* lse,
-                                float* weights, void* scratch, int B, int H, int G, int q_len, int kv_len, long long k_sb,
-                                long long k_sg, long long tp_sb, long long tp_sg, float scale, int input_pos, int window,
-                                float softcap, int* status, void* stream);
+                                float* weights, void* scratch, int B, int H, int G, int q_len, int kv_len, int head_size,
+                                long long k_sb, long long k_sg, long long tp_sb, long long tp_sg, float scale, int input_pos,
+                                int window, float softcap, int* status, void* stream);
 
 extern "C" int kvb_sdpa_fwd(const void* q, const void* k, const void* v, const int32_t* token_pos, void* out, float* lse,
                              float* weights, void* scratch, int B, int H, int G, int q_len, int kv_len, long long k_sb,
                              long long k_sg, long long tp_sb, long long tp_sg, float scale, int input_pos, int* status,
                              void* stream) {
-  return kvb_sdpa_fwd_ex(q, k, v, token_pos, out, lse, weights, scratch, B, H, G, q_len, kv_len, k_sb, k_sg, tp_sb, tp_sg, scale,
-                         input_pos, 0, 0.f, status, stream);
+  return kvb_sdpa_fwd_ex(q, k, v, token_pos, out, lse, weights, scratch, B, H, G, q_len, kv_len, 128, k_sb, k_sg, tp_sb, tp_sg,
+                         scale, input_pos, 0, 0.f, status, stream);
 }
 
 extern "C" int kvb_sdpa_fwd_ex(const void* q, const void* k, const void* v, const int32_t* token_pos, void* out, float* lse,
-                                float* weights, void* scratch, int B, int H, int G, int q_len, int kv_len, long long k_sb,
-                                long long k_sg, long long tp_sb, long long tp_sg, float scale, int input_pos, int window,
-                                float softcap, int* status, void* stream) {
+                                float* weights, void* scratch, int B, int H, int G, int q_len, int kv_len, int head_size,
+                                long long k_sb, long long k_sg, long long tp_sb, long long tp_sg, float scale, int input_pos,
+                                int window, float softcap, int* status, void* stream) {
   using namespace kvb;
   if (window < 0 || softcap < 0.f || (softcap > 0.f && scale <= 0.f)) return KVB_ERR_ARG;
+  if (head_size != 128 && head_size != 64) return KVB_ERR_UNSUPPORTED;
   if (B <= 0 || H <= 0 || G <= 0 || q_len <= 0 || kv_len <= 0 || H % G) return KVB_ERR_ARG;
   const int gs = H / G;
   if (gs > 128) return KVB_ERR_UNSUPPORTED;
@@ -1186,33 +1219,20 @@ extern "C" int kvb_sdpa_fwd_ex(const void* q, const void* k, const void* v, cons
   CUtensorMap tmQ, tmK, tmV;
   int rc;
   // Q (B,H,T,D) read position-major: dims (D, H, T, B) with strides (T·D, D, H·T·D); box = 64 x gs x npos
-  if ((rc = f2_make_tmap(&tmQ, q, F2_T, H, q_len, B, (uint64_t)q_len * F2_T, F2_T, (uint64_t)H * q_len * F2_T, 64, gs, p.npos)))
+  const uint64_t hd = (uint64_t)head_size;
+  if ((rc = f2_make_tmap(&tmQ, q, hd, H, q_len, B, (uint64_t)q_len * hd, hd, (uint64_t)H * q_len * hd, 64, gs, p.npos)))
     return rc;
   // K, V (B,G,L,D) with strides: dims (D, L, G, B); box = 64 x 128 x 1
-  if ((rc = f2_make_tmap(&tmK, k, F2_T, kv_len, G, B, F2_T, k_sg, k_sb, 64, F2_T, 1))) return rc;
-  if ((rc = f2_make_tmap(&tmV, v, F2_T, kv_len, G, B, F2_T, k_sg, k_sb, 64, F2_T, 1))) return rc;
+  if ((rc = f2_make_tmap(&tmK, k, hd, kv_len, G, B, hd, k_sg, k_sb, 64, F2_T, 1))) return rc;
+  if ((rc = f2_make_tmap(&tmV, v, hd, kv_len, G, B, hd, k_sg, k_sb, 64, F2_T, 1))) return rc;
 
   f2_prepare_kernel<<<B * G * p.nT, F2_T, 0, s>>>(token_pos, tmin, tmax, pos, G, kv_len, p.nT, tp_sb, tp_sg);
-  static kvb::PerDeviceOnce attr_once;
-  if (attr_once.first()) {
-    cudaFuncSetAttribute(flash_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, F2Smem::TOTAL);
-    cudaFuncSetAttribute(flash_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, F2Smem::TOTAL);
-    cudaFuncSetAttribute(colsum_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, CsSmem::TOTAL);
-    cudaFuncSetAttribute(colsum_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, CsSmem::TOTAL);
-  }
   const int nPair = (p.nQT + 1) / 2;
   p.n_split = f2_num_splits((long long)B * G * nPair, p.nT);
   p.tiles_per_split = (p.nT + p.n_split - 1) / p.n_split;
   p.part_lse2 = lse2 + (long long)B * G * p.nQT * 128;
   p.part_o = p.part_lse2 + f2_round4((long long)p.n_split * B * H * q_len);
   const bool gen = window > 0 || softcap > 0.f;
-  if (gen) flash_fwd_kernel<true><<<dim3(B * G * nPair, p.n_split), F2_THREADS, F2Smem::TOTAL, s>>>(tmQ, tmK, tmV, p);
-  else flash_fwd_kernel<false><<<dim3(B * G * nPair, p.n_split), F2_THREADS, F2Smem::TOTAL, s>>>(tmQ, tmK, tmV, p);
-  if (p.n_split > 1) {
-    const long long rows = (long long)B * G * p.nQT * F2_T;
-    flash_merge_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(p);
-  }
-  if (weights && gen) colsum_kernel<true><<<B * G * p.nT, F2_THREADS, CsSmem::TOTAL, s>>>(tmQ, tmK, p);
-  else if (weights) colsum_kernel<false><<<B * G * p.nT, F2_THREADS, CsSmem::TOTAL, s>>>(tmQ, tmK, p);
-  return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
+  if (head_size == 128) return gen ? f2_launch<true, 128>(tmQ, tmK, tmV, p, s) : f2_launch<false, 128>(tmQ, tmK, tmV, p, s);
+  return gen ? f2_launch<true, 64>(tmQ, tmK, tmV, p, s) : f2_launch<false, 64>(tmQ, tmK, tmV, p, s);
 }

@@ -487,7 +487,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, a2=None, b2=None, residual=None, out=
 def sdpa_supported(query: torch.Tensor, key: torch.Tensor, sliding_window, softcap) -> bool:
     H, G = query.shape[1], key.shape[1]
     gs = H // G
-    return (query.dtype == torch.bfloat16 and query.shape[-1] == 128 and gs <= 128 and query.shape[2] > 0
+    return (query.dtype == torch.bfloat16 and query.shape[-1] in (64, 128) and gs <= 128 and query.shape[2] > 0
             and (sliding_window is None or sliding_window > 0) and (softcap is None or softcap > 0))
 
 
@@ -499,7 +499,7 @@ def sdpa_bwd_supported(query: torch.Tensor, key: torch.Tensor, sliding_window, s
 
 def sdpa_fwd(query, key, value, scale, input_pos, token_pos=None, return_weights=False, sliding_window=None, softcap=None):
     """SDPA forward: flash sweep (P in TMEM, online softmax) + column-owner weight sums. Returns
-    ``(out (B,T,H·D) bf16, weights (B,G,L) fp32 | None, lse (B,H,T) fp32)``; any group size up to 128.
+    ``(out (B,T,H·D) bf16, weights (B,G,L) fp32 | None, lse (B,H,T) fp32)``; head size 128 or 64, any group size up to 128.
     ``sliding_window``: a query at position ``p`` sees tokens in ``(p - window, p]`` only; ``softcap``: scores
     become ``cap · tanh(score / cap)`` (both inside the kernels)."""
     B, H, T, D = query.shape
@@ -519,7 +519,7 @@ def sdpa_fwd(query, key, value, scale, input_pos, token_pos=None, return_weights
     scratch = torch.empty(nbytes // 4, dtype=torch.int32, device=dev)
     st = status_word(dev)
     _check(lib().kvb_sdpa_fwd_ex(_p(query), _p(key), _p(value), _p(token_pos), _p(out), _p(lse), _p(weights), _p(scratch), B, H, G, T, L,
-                                  _ll(key.stride(0)), _ll(key.stride(1)),
+                                  int(D), _ll(key.stride(0)), _ll(key.stride(1)),
                                   _ll(token_pos.stride(0) if token_pos is not None else 0),
                                   _ll(token_pos.stride(1) if token_pos is not None else 0),
                                   ctypes.c_float(scale), int(input_pos), int(sliding_window or 0), ctypes.c_float(softcap or 0.0),
@@ -567,7 +567,7 @@ def sdpa_bwd(grad_out, query, key, value, out, lse, scale, input_pos, token_pos=
     scratch = torch.empty(nbytes // 4, dtype=torch.int32, device=dev)
     st = status_word(dev)
     _check(lib().kvb_sdpa_bwd_ex(_p(query), _p(key), _p(value), _p(token_pos), _p(out), _p(grad_out), _p(lse.contiguous()), _p(dq),
-                                 _p(dk_accum), _p(dv_accum), _p(scratch), B, H, G, T, L, _ll(key.stride(0)), _ll(key.stride(1)),
+                                 _p(dk_accum), _p(dv_accum), _p(scratch), B, H, G, T, L, int(D), _ll(key.stride(0)), _ll(key.stride(1)),
                                  _ll(token_pos.stride(0) if token_pos is not None else 0),
                                  _ll(token_pos.stride(1) if token_pos is not None else 0),
                                  _ll(dk_accum.stride(0)), _ll(dk_accum.stride(1)), ctypes.c_float(scale), int(input_pos),

@@ -122,9 +122,11 @@ def test_gradients_through_eviction_match_oracle_on_gpu(cache_name):
     assert rel(g1, o32) < max(3 * noise, 0.05), (rel(g1, o32), noise)
 
 
-def test_sliding_window_and_softcap_layers_run_on_the_native_kernels(monkeypatch):
-    """A Gemma-2 style model (a window layer, capped scores) through the chunked training pass: the tcgen05 attention
-    kernels serve it (no restatement: strict mode), and loss and gradients agree with the PyTorch restatement."""
+@pytest.mark.parametrize("name", ["tiny-gemma2", "tiny-llama-d64"])
+def test_sliding_window_softcap_and_head_size_64_run_on_the_native_kernels(name, monkeypatch):
+    """A Gemma-2 style model (a window layer, capped scores) and a model with head size 64 through the chunked training
+    pass: the tcgen05 attention kernels serve them (no restatement: strict mode), and loss and gradients agree with
+    the PyTorch restatement."""
     from keys_values_b200 import ops
     from keys_values_b200.config import Config
     from keys_values_b200.models.model import GPT
@@ -132,7 +134,7 @@ def test_sliding_window_and_softcap_layers_run_on_the_native_kernels(monkeypatch
     monkeypatch.setenv("KVB200_STRICT_NATIVE", "1")
     dev, dtype = torch.device("cuda", 0), torch.bfloat16
     torch.manual_seed(0)
-    cfg = Config.from_name("tiny-gemma2")
+    cfg = Config.from_name(name)
     m = GPT(cfg)
     m.apply(m._init_weights)
     m = m.to(device=dev, dtype=dtype)

@@ -183,8 +183,7 @@ def test_gemm_lora_residual():
     torch.testing.assert_close(c.float(), cr, atol=1e-1, rtol=2e-2)
 
 
-def _sdpa_case(B, H, G, T, L, input_pos, mode, want_w=True, window=None, softcap=None):
-    D = 128
+def _sdpa_case(B, H, G, T, L, input_pos, mode, want_w=True, window=None, softcap=None, D=128):
     q = torch.randn(B, H, T, D, device=DEV, dtype=torch.bfloat16)
     k = torch.randn(B, G, L, D, device=DEV, dtype=torch.bfloat16)
     v = torch.randn(B, G, L, D, device=DEV, dtype=torch.bfloat16)
@@ -263,6 +262,15 @@ def test_sdpa_sliding_window_and_softcap(B, H, G, T, L, mode, window, softcap):
     _sdpa_case(B, H, G, T, L, 3 * L if mode == "perm" else L - T, mode, window=window, softcap=softcap)
 
 
+@pytest.mark.parametrize("B,H,G,T,L,mode,window,softcap", [
+    (1, 8, 2, 256, 2048, "perm", None, None), (2, 8, 2, 100, 1000, "perm", None, None), (1, 14, 2, 77, 900, "arange", None, None),
+    (1, 32, 8, 700, 700, "arange", None, None), (1, 4, 1, 64, 8192, "perm", None, None), (1, 8, 2, 300, 1500, "arange", 256, 3.0),
+    (1, 32, 8, 1, 2048, "arange", None, None)])
+def test_sdpa_head_size_64(B, H, G, T, L, mode, window, softcap):
+    """Head size 64 (Llama-3.2-1B, Qwen2.5-0.5B): tiles of one 64-feature chunk, O of 64 TMEM columns."""
+    _sdpa_case(B, H, G, T, L, 3 * L if mode == "perm" else L - T, mode, window=window, softcap=softcap, D=64)
+
+
 def test_sdpa_is_deterministic():
     """Outputs, normalisers and the summed weights (which drive the eviction decisions) are bit-identical run to run."""
     D, B, H, G, T, L = 128, 1, 32, 8, 512, 4096  # 64 CTAs: split over the KV axis, partials merged in a fixed order
@@ -328,9 +336,15 @@ def test_sdpa_bwd(B, H, G, T, L, mode):
     assert torch.equal(dk_acc[:, :, L:], dk0[:, :, L:]) and torch.equal(dv_acc[:, :, L:], dv0[:, :, L:])
 
 
+@pytest.mark.parametrize("B,H,G,T,L,mode,window,softcap", [
+    (1, 8, 2, 256, 2048, "perm", None, None), (2, 8, 2, 100, 1000, "perm", None, None), (1, 14, 2, 77, 900, "arange", None, None),
+    (1, 32, 8, 700, 700, "arange", None, None), (1, 3, 1, 50, 200, "perm", None, None), (1, 8, 2, 300, 1500, "arange", 256, 3.0)])
+def test_sdpa_bwd_head_size_64(B, H, G, T, L, mode, window, softcap):
+    test_sdpa_bwd_sliding_window_and_softcap(B, H, G, T, L, mode, window, softcap, D=64)
+
+
 @pytest.mark.parametrize("B,H,G,T,L,mode,window,softcap", WINDOW_SOFTCAP_CASES)
-def test_sdpa_bwd_sliding_window_and_softcap(B, H, G, T, L, mode, window, softcap):
-    D = 128
+def test_sdpa_bwd_sliding_window_and_softcap(B, H, G, T, L, mode, window, softcap, D=128):
     q = torch.randn(B, H, T, D, device=DEV, dtype=torch.bfloat16)
     k = torch.randn(B, G, L, D, device=DEV, dtype=torch.bfloat16)
     v = torch.randn(B, G, L, D, device=DEV, dtype=torch.bfloat16)
