@@ -1,0 +1,391 @@
+// Persistent bf16 GEMM for sm_100a on CTA pairs:  C[M,N] = A[M,K] · B[N,K]^T (+ A2[M,K2] · B2[N,K2]^T) (+ residual)
+//
+// A cluster of two CTAs (two SMs) works on one 256 x 256 tile with tcgen05.mma.cta_group::2 (M = 256, N = 256,
+// K = 16 per instruction):
+//   * CTA r of the pair loads rows [m0 + 128 r, +128) of A and rows [n0 + 128 r, +128) of B (its half of the N
+//     extent) into its own shared memory, by plain TMA loads (no multicast); the tensor core of each SM reads its own A
+//     rows and both halves of B. Per SM that is 8 KB of operand reads per instruction and 32 KB of TMA writes per
+//     k-block of 64, half of what a 128 x 256 tile per single CTA needs: the single-CTA kernel is bound by the
+//     shared-memory port at about 0.65 of the tensor pipe.
+//   * The first CTA of the pair (the leader) issues every MMA. The TMA loads of both CTAs complete on the leader's
+//     "full" barrier of the stage (the leader arms it with the bytes of both). When the MMAs of a stage are done the
+//     leader's tcgen05.commit arrives on the "empty" barrier of the stage in both CTAs, and when a tile is done on the
+//     "accumulator full" barrier of both.
+//   * Each CTA holds its 128 rows x 256 columns of the fp32 accumulator in its own TMEM, double-buffered (2 x 256
+//     columns), so the epilogue of tile i (tcgen05.ld -> bf16 -> shared memory -> global, 4 rows x 128 contiguous
+//     bytes per store instruction) overlaps the main loop of tile i + 1. The epilogue warps of both CTAs hand the
+//     buffer back on the leader's "accumulator empty" barrier (the follower's with a remote arrive).
+//   * warp roles per CTA: warp 0 = TMA producer, warp 1 = TMEM owner (and MMA issuer in the leader), warps 2..5 =
+//     epilogue.
+// Every wait is bounded; a CTA that gives up raises the status word and still takes part in the cluster barrier at the
+// end, so that neither CTA's shared memory is released while the other may still signal it.
+//
+// Replaces the cuBLAS calls behind nn.Linear in the reference (keys_values/model.py:596-610, lora_utils.py:159-172).
+#include <cuda.h>
+#include <string.h>
+
+#include "common.cuh"
+#include "kvb200.h"
+
+namespace kvb {
+
+int make_tmap_2d_bf16(CUtensorMap* tm, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                      uint32_t box_cols);
+
+constexpr int G2_BM = 128;      // rows of A per CTA (256 per pair)
+constexpr int G2_BNH = 128;     // rows of B per CTA (N = 256 per pair)
+constexpr int G2_BN = 256;
+constexpr int G2_BK = 64;
+constexpr int G2_STAGES = 6;
+constexpr int G2_THREADS = 192;
+
+struct G2Smem {
+  static constexpr int A_BYTES = G2_BM * G2_BK * 2;
+  static constexpr int B_BYTES = G2_BNH * G2_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;          // per CTA
+  static constexpr int EPI_OFFSET = G2_STAGES * STAGE_BYTES;     // per epilogue warp: 32 rows x 128 B staging
+  static constexpr int EPI_BYTES = 4 * 32 * 128;
+  static constexpr int BAR_OFFSET = EPI_OFFSET + EPI_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;          // barriers + alignment slack
+};
+static_assert(G2Smem::TOTAL <= 232448, "shared memory of the pair GEMM exceeds the limit of a CTA");
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of `local` (a shared::cta address of this CTA) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t local, uint32_t rank) {
+  uint32_t a;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(local), "r"(rank));
+  return a;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// arrive on a barrier that may live in the other CTA of the cluster (shared::cluster address)
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load of a CTA of a pair: the destination is this CTA's shared memory, the barrier (shared::cluster address) may be
+// the other CTA's
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const void* tmap, uint32_t bar_cluster_addr, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(tmap), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// D[tmem of both CTAs] (+)= A[256 x 16: 128 rows per CTA] · B[256 x 16: 128 rows per CTA]^T; issued by ONE thread of the leader
+__device__ __forceinline__ void umma_f16_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive, in both CTAs of the pair, on the barrier at this shared-memory offset once all MMAs issued so far are done.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                   smem_u32(bar)),
+               "h"(mask)
+               : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
+gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
+                  __nv_bfloat16* __restrict__ C, const __nv_bfloat16* __restrict__ residual, int M, int N, int K, int K2,
+                  long long ldc, int* status) {
+  using S = G2Smem;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;  // the same offsets in both CTAs: the leader's descriptors address both
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + G2_STAGES;
+  uint64_t* tmem_full = empty_bar + G2_STAGES;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0: leader
+  const int pair = (int)blockIdx.x >> 1;
+  const int n_pairs = (int)gridDim.x >> 1;
+  const int num_m = (M + 2 * G2_BM - 1) / (2 * G2_BM);
+  const int num_n = (N + G2_BN - 1) / G2_BN;
+  const int num_tiles = num_m * num_n;
+  const int kb1 = (K + G2_BK - 1) / G2_BK;
+  const int kb2 = (K2 + G2_BK - 1) / G2_BK;
+  const int num_kb = kb1 + kb2;
+  const bool aligned_ok = (smem_u32(smem) & 1023u) == 0;  // swizzled tiles need a 1024-byte aligned window
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < G2_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);    // the leader's producer arms it with the bytes of both CTAs
+      mbar_init(&empty_bar[s], 1);   // the leader's commit, in both CTAs
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);   // the leader's commit, in both CTAs
+      mbar_init(&tmem_empty[a], 8);  // one arrive per epilogue warp of both CTAs (used in the leader)
+    }
+    *abort_flag = aligned_ok ? 0 : 1;
+    if (!aligned_ok && status) atomicCAS(status, 0, STATUS_TIMEOUT_MISC);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_base_slot, 2 * G2_BN);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // barriers of both CTAs are initialised before either signals the other
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0 && !*abort_flag) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
+        const int m0 = (tile % num_m) * (2 * G2_BM) + (int)rank * G2_BM;
+        const int n0 = (tile / num_m) * G2_BN + (int)rank * G2_BNH;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag, status, STATUS_TIMEOUT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * S::STAGE_BYTES;
+          uint8_t* sb = sa + S::A_BYTES;
+          if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * S::STAGE_BYTES);
+          const uint32_t bar = mapa_u32(smem_u32(&full_bar[stage]), 0);  // the leader's barrier
+          if (kb < kb1) {
+            tma_load_2d_pair(sa, &tmA, bar, kb * G2_BK, m0);
+            tma_load_2d_pair(sb, &tmB, bar, kb * G2_BK, n0);
+          } else {
+            tma_load_2d_pair(sa, &tmA2, bar, (kb - kb1) * G2_BK, m0);
+            tma_load_2d_pair(sb, &tmB2, bar, (kb - kb1) * G2_BK, n0);
+          }
+          if (++stage == G2_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) {
+        // unwinding: give the copies that are still in flight a bounded time to land
+        long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issuer (leader only)
+    if (lane == 0 && rank == 0 && !*abort_flag) {
+      constexpr uint32_t idesc = make_idesc_bf16(2 * G2_BM, G2_BN, 0, 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
+        if (!mbar_wait_bounded(&tmem_empty[acc], acc_phase ^ 1, abort_flag, status, STATUS_TIMEOUT_TMEM_EMPTY)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * G2_BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, status, STATUS_TIMEOUT_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * S::STAGE_BYTES);
+          const uint32_t sb = sa + S::A_BYTES;
+          const uint64_t da = make_smem_desc_sw128(sa, 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(sb, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < G2_BK / 16; ++k) {
+            // advance 16 elements (32 B) along K inside the 128B swizzle row: +2 in 16 B units
+            umma_f16_ss_pair(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(&empty_bar[stage]);
+          if (++stage == G2_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit_pair(&tmem_full[acc]);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // --------------------------------------------------------------- epilogue (both CTAs)
+    const int quarter = warp & 3;  // TMEM sub-partition of this warp
+    const int row_in_tile = quarter * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const uint32_t empty_remote = mapa_u32(smem_u32(&tmem_empty[0]), 0);  // the leader's "accumulator empty" barriers
+    for (int tile = pair; tile < num_tiles; tile += n_pairs) {
+      const int m0 = (tile % num_m) * (2 * G2_BM) + (int)rank * G2_BM;
+      const int n0 = (tile / num_m) * G2_BN;
+      if (!mbar_wait_bounded(&tmem_full[acc], acc_phase, abort_flag, status, STATUS_TIMEOUT_TMEM_FULL)) break;
+      tc_fence_after();
+      const int m = m0 + row_in_tile;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * G2_BN);
+      // 64 columns at a time: thread = row converts its 128 bytes, the warp exchanges them through shared memory
+      // (16-byte units XOR-swizzled by row, conflict-free both ways) and stores 4 rows x 128 contiguous bytes per
+      // instruction.
+      uint8_t* stg = smem + S::EPI_OFFSET + quarter * (32 * 128);
+      const int m_warp0 = m0 + quarter * 32;  // first row of this warp
+#pragma unroll 1
+      for (int c0 = 0; c0 < G2_BN; c0 += 64) {
+        const int n = n0 + c0;
+        if (n >= N) break;  // warp-uniform
+        uint32_t r[64];
+        tmem_ld_32x32b_x32(taddr + (uint32_t)c0, r);
+        tmem_ld_32x32b_x32(taddr + (uint32_t)(c0 + 32), r + 32);
+        tmem_ld_wait();
+        if (n + 64 <= N) {
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(r[8 * v]), __uint_as_float(r[8 * v + 1]));
+            o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+            o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+            o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+            *reinterpret_cast<uint4*>(stg + lane * 128 + ((v ^ (lane & 7)) << 4)) = o;
+          }
+          __syncwarp();
+          const int u = lane & 7;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int rr = 4 * j + (lane >> 3);  // row of the warp's 32
+            uint4 o = *reinterpret_cast<const uint4*>(stg + rr * 128 + ((u ^ (rr & 7)) << 4));
+            if (m_warp0 + rr < M) {
+              if (residual) {
+                const uint4 rv = *reinterpret_cast<const uint4*>(residual + (long long)(m_warp0 + rr) * ldc + n + u * 8);
+                const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv);
+                __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const float2 a = __bfloat1622float2(op[i]), t = __bfloat1622float2(rp[i]);
+                  op[i] = __floats2bfloat162_rn(a.x + t.x, a.y + t.y);
+                }
+              }
+              *reinterpret_cast<uint4*>(C + (long long)(m_warp0 + rr) * ldc + n + u * 8) = o;
+            }
+          }
+          __syncwarp();
+        } else if (m < M) {
+          // ragged right edge: element by element
+          __nv_bfloat16* dst = C + (long long)m * ldc + n;
+          const __nv_bfloat16* res = residual ? residual + (long long)m * ldc + n : nullptr;
+          for (int i = 0; i < 64 && n + i < N; ++i) {
+            float f = __uint_as_float(r[i]);
+            if (res) f += __bfloat162float(res[i]);
+            dst[i] = __float2bfloat16_rn(f);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(empty_remote + (uint32_t)(acc * 8));
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // nothing of either CTA is released while the other one may still signal it
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 2 * G2_BN);
+  }
+}
+
+static int g2_max_pairs() {
+  static int n[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (!n[dev]) {
+    cudaFuncSetAttribute(gemm2_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G2Smem::TOTAL);
+    int sms = 0;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    // how many clusters of two can be resident at once (clusters do not span GPCs)
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)(sms / 2 * 2));
+    cfg.blockDim = dim3(G2_THREADS);
+    cfg.dynamicSmemBytes = G2Smem::TOTAL;
+    cudaLaunchAttribute at;
+    at.id = cudaLaunchAttributeClusterDimension;
+    at.val.clusterDim.x = 2;
+    at.val.clusterDim.y = 1;
+    at.val.clusterDim.z = 1;
+    cfg.attrs = &at;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, gemm2_bf16_kernel, &cfg) != cudaSuccess || clusters <= 0) {
+      cudaGetLastError();
+      clusters = sms / 2 - 2;  // a conservative count
+    }
+    if (clusters > sms / 2) clusters = sms / 2;
+    n[dev] = clusters > 0 ? clusters : 1;
+  }
+  return n[dev];
+}
+
+}  // namespace kvb
+
+// C[M,N] = A[M,K] · B[N,K]^T (+ A2 · B2^T) (+ residual), bf16 with fp32 accumulation, on CTA pairs (cta_group::2).
+// max_pairs > 0 limits the number of CTA pairs.
+extern "C" int kvb_gemm2_bf16(const void* A, const void* B, const void* A2, const void* B2, void* C, const void* residual,
+                              int M, int N, int K, int K2, long long lda, long long ldb, long long lda2, long long ldb2,
+                              long long ldc, int* status, int max_pairs, void* stream) {
+  using namespace kvb;
+  if (M <= 0 || N <= 0 || K <= 0) return KVB_ERR_ARG;
+  if ((K % 8) || (lda % 8) || (ldb % 8) || (ldc % 8) || (N % 8)) return KVB_ERR_ALIGN;
+  if (K2 > 0 && ((K2 % 8) || (lda2 % 8) || (ldb2 % 8))) return KVB_ERR_ALIGN;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) return KVB_ERR_ALIGN;
+  CUtensorMap tmA, tmB, tmA2, tmB2;
+  int rc;
+  if ((rc = make_tmap_2d_bf16(&tmA, A, M, K, lda, G2_BM, G2_BK))) return rc;
+  if ((rc = make_tmap_2d_bf16(&tmB, B, N, K, ldb, G2_BNH, G2_BK))) return rc;
+  if (K2 > 0) {
+    if ((rc = make_tmap_2d_bf16(&tmA2, A2, M, K2, lda2, G2_BM, G2_BK))) return rc;
+    if ((rc = make_tmap_2d_bf16(&tmB2, B2, N, K2, ldb2, G2_BNH, G2_BK))) return rc;
+  } else {
+    tmA2 = tmA;
+    tmB2 = tmB;
+  }
+  int pairs = g2_max_pairs();
+  if (pairs <= 0) return KVB_ERR_CUDA;
+  if (max_pairs > 0 && max_pairs < pairs) pairs = max_pairs;
+  const int num_tiles = ((M + 2 * G2_BM - 1) / (2 * G2_BM)) * ((N + G2_BN - 1) / G2_BN);
+  if (num_tiles < pairs) pairs = num_tiles;
+  gemm2_bf16_kernel<<<2 * pairs, G2_THREADS, G2Smem::TOTAL, reinterpret_cast<cudaStream_t>(stream)>>>(
+      tmA, tmB, tmA2, tmB2, (__nv_bfloat16*)C, (const __nv_bfloat16*)residual, M, N, K, K2, ldc, status);
+  return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
+}

@@ -80,6 +80,11 @@ int kvb_gemm_bf16(const void* A, const void* B, const void* A2, const void* B2, 
                   int K, int K2, long long lda, long long ldb, long long lda2, long long ldb2, long long ldc, int* status,
                   int max_ctas, void* stream);
 
+// ---- gemm2_sm100.cu: the same product on CTA pairs (tcgen05.mma.cta_group::2, 256 x 256 tiles)
+int kvb_gemm2_bf16(const void* A, const void* B, const void* A2, const void* B2, void* C, const void* residual, int M, int N,
+                   int K, int K2, long long lda, long long ldb, long long lda2, long long ldb2, long long ldc, int* status,
+                   int max_pairs, void* stream);
+
 // ---- sdpa_sm100.cu
 // Diagnostics: per-phase cycle counters of CTA 0 of later kvb_sdpa_fwd launches (4 roles x 8 int64, see sdpa_sm100.cu).
 int kvb_sdpa_fwd_set_trace(void* buf);

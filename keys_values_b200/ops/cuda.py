@@ -483,6 +483,22 @@ def gemm(a: torch.Tensor, b: torch.Tensor, a2=None, b2=None, residual=None, out=
     return out
 
 
+def gemm_pair(a: torch.Tensor, b: torch.Tensor, a2=None, b2=None, residual=None, out=None, max_pairs: int = 0) -> torch.Tensor:
+    """The same product as :func:`gemm` on CTA pairs (``tcgen05.mma.cta_group::2``, 256 x 256 tiles): each SM of a pair
+    loads half of the B tile, which halves the shared-memory traffic per flop."""
+    M, K = a.shape
+    N = b.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    K2 = 0 if a2 is None else a2.shape[1]
+    st = status_word(a.device)
+    _check(lib().kvb_gemm2_bf16(_p(a), _p(b), _p(a2), _p(b2), _p(out), _p(residual), M, N, K, K2, _ll(a.stride(0)), _ll(b.stride(0)),
+                                _ll(a2.stride(0) if a2 is not None else 0), _ll(b2.stride(0) if b2 is not None else 0),
+                                _ll(out.stride(0)), _p(st), int(max_pairs), _stream(a)), "gemm2_bf16")
+    _count()
+    return out
+
+
 # ---------------------------------------------------------------- attention
 def sdpa_supported(query: torch.Tensor, key: torch.Tensor, sliding_window, softcap) -> bool:
     H, G = query.shape[1], key.shape[1]

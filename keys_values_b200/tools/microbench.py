@@ -173,11 +173,15 @@ def bench_gemm(out, peaks):
         b = torch.randn(N, K, device=dev, dtype=torch.bfloat16)
         ms = time_fn(lambda: cu.gemm(a, b), flush=flush)
         cu.check_status(dev)
+        ms_pair = time_fn(lambda: cu.gemm_pair(a, b), flush=flush)
+        cu.check_status(dev)
         ms_ref = time_fn(lambda: torch.matmul(a, b.t()), flush=flush)
         fl = 2.0 * M * N * K
         out({"bench": "gemm_bf16", "M": M, "N": N, "K": K, "us": ms * 1e3, "tflops": fl / ms / 1e9,
+             "pair_us": ms_pair * 1e3, "pair_tflops": fl / ms_pair / 1e9,
              "cublas_us": ms_ref * 1e3, "cublas_tflops": fl / ms_ref / 1e9,
-             "frac_of_measured_peak": fl / ms / 1e9 / peaks["bf16_tflops"]})
+             "frac_of_measured_peak": fl / ms / 1e9 / peaks["bf16_tflops"],
+             "pair_frac_of_measured_peak": fl / ms_pair / 1e9 / peaks["bf16_tflops"], "pair_over_cublas": ms_ref / ms_pair})
 
 
 def bench_elementwise(out, peaks):

@@ -170,6 +170,30 @@ def test_gemm(M, N, K):
     torch.testing.assert_close(c.float(), cr, atol=3e-2 * math.sqrt(K / 64), rtol=2e-2)
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 512, 512), (1024, 6144, 2560), (200, 264, 136), (130, 520, 72), (4096, 2560, 9728)])
+def test_gemm_on_cta_pairs(M, N, K):
+    """The cta_group::2 kernel (256 x 256 tiles over two SMs), ragged edges included."""
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.05
+    c = _cuda().gemm_pair(a, b)
+    _cuda().check_status(DEV)
+    cr = a.float() @ b.float().t()
+    torch.testing.assert_close(c.float(), cr, atol=3e-2 * math.sqrt(K / 64), rtol=2e-2)
+
+
+def test_gemm_on_cta_pairs_lora_residual():
+    M, N, K, R = 512, 1024, 512, 64
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.05
+    a2 = torch.randn(M, R, device=DEV, dtype=torch.bfloat16)
+    b2 = torch.randn(N, R, device=DEV, dtype=torch.bfloat16) * 0.05
+    res = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    c = _cuda().gemm_pair(a, b, a2, b2, residual=res)
+    _cuda().check_status(DEV)
+    cr = a.float() @ b.float().t() + a2.float() @ b2.float().t() + res.float()
+    torch.testing.assert_close(c.float(), cr, atol=1e-1, rtol=2e-2)
+
+
 def test_gemm_lora_residual():
     M, N, K, R = 512, 1024, 512, 64
     a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
