@@ -25,6 +25,7 @@
 #include <string.h>
 
 #include "common.cuh"
+#include "gemm_extra.cuh"
 #include "kvb200.h"
 
 namespace kvb {
@@ -109,10 +110,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
                   __nv_bfloat16* __restrict__ C, const __nv_bfloat16* __restrict__ residual, int M, int N, int K, int K2,
-                  long long ldc, int* status) {
+                  long long ldc, int* status, const GemmExtra ex) {
   using S = G2Smem;
-  extern __shared__ __align__(1024) uint8_t smem_raw[];
-  uint8_t* smem = smem_raw;  // the same offsets in both CTAs: the leader's descriptors address both
+  extern __shared__ uint8_t smem_raw[];
+  // ---- all-gather copy CTAs (whole pairs: copy_span CTAs, the last one idle when ag_copy_ctas is odd). They take no
+  // part in any cluster barrier, MMA or TMEM allocation.
+  const int copy_span = (ex.ag_copy_ctas + 1) & ~1;
+  if ((int)blockIdx.x < copy_span) {
+    if ((int)blockIdx.x < ex.ag_copy_ctas) gemm_ag_copy_role(ex, K, status, smem_raw);
+    return;
+  }
+  // the same offsets in both CTAs (the window starts at the same shared-memory address in every CTA of the kernel): the
+  // leader's descriptors address both
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::BAR_OFFSET);
   uint64_t* empty_bar = full_bar + G2_STAGES;
   uint64_t* tmem_full = empty_bar + G2_STAGES;
@@ -123,8 +133,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();  // 0: leader
-  const int pair = (int)blockIdx.x >> 1;
-  const int n_pairs = (int)gridDim.x >> 1;
+  const int pair = ((int)blockIdx.x - copy_span) >> 1;
+  const int n_pairs = ((int)gridDim.x - copy_span) >> 1;
   const int num_m = (M + 2 * G2_BM - 1) / (2 * G2_BM);
   const int num_n = (N + G2_BN - 1) / G2_BN;
   const int num_tiles = num_m * num_n;
@@ -132,6 +142,22 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const int kb2 = (K2 + G2_BK - 1) / G2_BK;
   const int num_kb = kb1 + kb2;
   const bool aligned_ok = (smem_u32(smem) & 1023u) == 0;  // swizzled tiles need a 1024-byte aligned window
+  // tile -> (first row of the pair's 256 rows, first column). With a fused collective the order is row-block major and
+  // the row blocks are rotated so that the blocks this rank already holds (all-gather) come first, or the rows this
+  // rank owns (reduce-scatter) last.
+  const bool comm = ex.a_flags != nullptr || ex.rs_world > 1;
+  int m_rot = 0;
+  if (ex.a_flags) m_rot = (ex.ag_rank * ex.rows_per_chunk) / (2 * G2_BM);
+  if (ex.rs_world > 1) m_rot = (((ex.rs_rank + 1) * ex.rows_per_rank + 2 * G2_BM - 1) / (2 * G2_BM)) % num_m;
+  auto tile_coords = [&](int tile, int& m0, int& n0) {
+    if (comm) {
+      m0 = ((tile / num_n + m_rot) % num_m) * (2 * G2_BM);
+      n0 = (tile % num_n) * G2_BN;
+    } else {
+      m0 = (tile % num_m) * (2 * G2_BM);
+      n0 = (tile / num_m) * G2_BN;
+    }
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < G2_STAGES; ++s) {
@@ -165,8 +191,27 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
-        const int m0 = (tile % num_m) * (2 * G2_BM) + (int)rank * G2_BM;
-        const int n0 = (tile / num_m) * G2_BN + (int)rank * G2_BNH;
+        int m0, n0;
+        tile_coords(tile, m0, n0);
+        m0 += (int)rank * G2_BM;
+        n0 += (int)rank * G2_BNH;
+        if (ex.a_flags && m0 < M) {
+          // rows of A come from an all-gather: wait until the chunk that holds this CTA's rows is local
+          const int chunk = m0 / ex.rows_per_chunk;
+          if (chunk != ex.ag_rank) {
+            long long t0 = clock64();
+            while ((int32_t)(ld_acquire_gpu_u32(ex.a_flags + chunk) - ex.a_target) < 0) {
+              if (*abort_flag || clock64() - t0 > ex.wait_limit) {
+                if (status) atomicCAS(status, 0, STATUS_TIMEOUT_PEER_FLAG);
+                *abort_flag = 1;
+                ok = false;
+                break;
+              }
+            }
+            if (!ok) break;
+            asm volatile("fence.proxy.async;" ::: "memory");  // generic-proxy writes -> visible to the TMA reads
+          }
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag, status, STATUS_TIMEOUT_EMPTY)) {
             ok = false;
@@ -246,11 +291,22 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     uint32_t acc_phase = 0;
     const uint32_t empty_remote = mapa_u32(smem_u32(&tmem_empty[0]), 0);  // the leader's "accumulator empty" barriers
     for (int tile = pair; tile < num_tiles; tile += n_pairs) {
-      const int m0 = (tile % num_m) * (2 * G2_BM) + (int)rank * G2_BM;
-      const int n0 = (tile / num_m) * G2_BN;
+      int m0, n0;
+      tile_coords(tile, m0, n0);
+      m0 += (int)rank * G2_BM;
       if (!mbar_wait_bounded(&tmem_full[acc], acc_phase, abort_flag, status, STATUS_TIMEOUT_TMEM_FULL)) break;
       tc_fence_after();
       const int m = m0 + row_in_tile;
+      // reduce-scatter epilogue: this CTA's 128 rows go to the receive buffer of the rank that owns them
+      __nv_bfloat16* out_base = C;
+      long long out_row = m;
+      int dest = -1;
+      if (ex.rs_world > 1 && m0 < M) {
+        dest = m0 / ex.rows_per_rank;
+        out_base = ex.rs_dst[dest];
+        out_row = (long long)ex.rs_rank * ex.rows_per_rank + (m - dest * ex.rows_per_rank);
+      }
+      const long long out_row0 = out_row - lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * G2_BN);
       // 64 columns at a time: thread = row converts its 128 bytes, the warp exchanges them through shared memory
       // (16-byte units XOR-swizzled by row, conflict-free both ways) and stores 4 rows x 128 contiguous bytes per
@@ -292,13 +348,13 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                   op[i] = __floats2bfloat162_rn(a.x + t.x, a.y + t.y);
                 }
               }
-              *reinterpret_cast<uint4*>(C + (long long)(m_warp0 + rr) * ldc + n + u * 8) = o;
+              *reinterpret_cast<uint4*>(out_base + (out_row0 + rr) * ldc + n + u * 8) = o;
             }
           }
           __syncwarp();
         } else if (m < M) {
           // ragged right edge: element by element
-          __nv_bfloat16* dst = C + (long long)m * ldc + n;
+          __nv_bfloat16* dst = out_base + out_row * ldc + n;
           const __nv_bfloat16* res = residual ? residual + (long long)m * ldc + n : nullptr;
           for (int i = 0; i < 64 && n + i < N; ++i) {
             float f = __uint_as_float(r[i]);
@@ -310,6 +366,12 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(empty_remote + (uint32_t)(acc * 8));
+      if (dest >= 0) {
+        // make this warp's peer stores visible system-wide, then count a quarter of a 128 x 256 block at the owner
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) red_release_sys_add(ex.rs_flag[dest] + ex.rs_rank, ex.rs_tile_inc);
+      }
       if (++acc == 2) {
         acc = 0;
         acc_phase ^= 1;
@@ -357,18 +419,11 @@ static int g2_max_pairs() {
   return n[dev];
 }
 
-}  // namespace kvb
-
-// C[M,N] = A[M,K] · B[N,K]^T (+ A2 · B2^T) (+ residual), bf16 with fp32 accumulation, on CTA pairs (cta_group::2).
-// max_pairs > 0 limits the number of CTA pairs.
-extern "C" int kvb_gemm2_bf16(const void* A, const void* B, const void* A2, const void* B2, void* C, const void* residual,
-                              int M, int N, int K, int K2, long long lda, long long ldb, long long lda2, long long ldb2,
-                              long long ldc, int* status, int max_pairs, void* stream) {
-  using namespace kvb;
-  if (M <= 0 || N <= 0 || K <= 0) return KVB_ERR_ARG;
-  if ((K % 8) || (lda % 8) || (ldb % 8) || (ldc % 8) || (N % 8)) return KVB_ERR_ALIGN;
-  if (K2 > 0 && ((K2 % 8) || (lda2 % 8) || (ldb2 % 8))) return KVB_ERR_ALIGN;
-  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) return KVB_ERR_ALIGN;
+// Launch on CTA pairs; `extra` (may be NULL) selects a fused collective as in the single-CTA kernel. max_pairs > 0 limits
+// the number of compute pairs.
+int launch_gemm_pair(const void* A, const void* B, const void* A2, const void* B2, void* C, const void* residual, int M, int N,
+                     int K, int K2, long long lda, long long ldb, long long lda2, long long ldb2, long long ldc, int* status,
+                     int max_pairs, cudaStream_t stream, const GemmExtra* extra) {
   CUtensorMap tmA, tmB, tmA2, tmB2;
   int rc;
   if ((rc = make_tmap_2d_bf16(&tmA, A, M, K, lda, G2_BM, G2_BK))) return rc;
@@ -380,12 +435,33 @@ extern "C" int kvb_gemm2_bf16(const void* A, const void* B, const void* A2, cons
     tmA2 = tmA;
     tmB2 = tmB;
   }
+  GemmExtra ex;
+  memset(&ex, 0, sizeof(ex));
+  if (extra) ex = *extra;
   int pairs = g2_max_pairs();
   if (pairs <= 0) return KVB_ERR_CUDA;
+  const int copy_pairs = (ex.ag_copy_ctas + 1) / 2;
+  pairs -= copy_pairs;  // copy CTAs and compute CTAs wait on one another: all of them must be resident at once
+  if (pairs < 1) return KVB_ERR_ARG;
   if (max_pairs > 0 && max_pairs < pairs) pairs = max_pairs;
   const int num_tiles = ((M + 2 * G2_BM - 1) / (2 * G2_BM)) * ((N + G2_BN - 1) / G2_BN);
   if (num_tiles < pairs) pairs = num_tiles;
-  gemm2_bf16_kernel<<<2 * pairs, G2_THREADS, G2Smem::TOTAL, reinterpret_cast<cudaStream_t>(stream)>>>(
-      tmA, tmB, tmA2, tmB2, (__nv_bfloat16*)C, (const __nv_bfloat16*)residual, M, N, K, K2, ldc, status);
+  gemm2_bf16_kernel<<<2 * (pairs + copy_pairs), G2_THREADS, G2Smem::TOTAL, stream>>>(
+      tmA, tmB, tmA2, tmB2, (__nv_bfloat16*)C, (const __nv_bfloat16*)residual, M, N, K, K2, ldc, status, ex);
   return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
+}
+
+}  // namespace kvb
+
+// C[M,N] = A[M,K] · B[N,K]^T (+ A2 · B2^T) (+ residual), bf16 with fp32 accumulation, on CTA pairs (cta_group::2).
+// max_pairs > 0 limits the number of CTA pairs.
+extern "C" int kvb_gemm2_bf16(const void* A, const void* B, const void* A2, const void* B2, void* C, const void* residual,
+                              int M, int N, int K, int K2, long long lda, long long ldb, long long lda2, long long ldb2,
+                              long long ldc, int* status, int max_pairs, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return KVB_ERR_ARG;
+  if ((K % 8) || (lda % 8) || (ldb % 8) || (ldc % 8) || (N % 8)) return KVB_ERR_ALIGN;
+  if (K2 > 0 && ((K2 % 8) || (lda2 % 8) || (ldb2 % 8))) return KVB_ERR_ALIGN;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) return KVB_ERR_ALIGN;
+  return kvb::launch_gemm_pair(A, B, A2, B2, C, residual, M, N, K, K2, lda, ldb, lda2, ldb2, ldc, status, max_pairs,
+                               reinterpret_cast<cudaStream_t>(stream), nullptr);
 }

@@ -1,7 +1,7 @@
 """Runs ONE small case of one kernel family, for use under ``ncu`` (a few launches, a few
 hundred MB on the device). Inputs are larger than the 126 MB L2 only where stated.
 
-    python -m keys_values_b200.tools.profile_case sdpa_fwd|sdpa_bwd|gemm|decode|allreduce [--iters N]
+    python -m keys_values_b200.tools.profile_case sdpa_fwd|sdpa_bwd|gemm|gemm_pair|decode|allreduce [--iters N]
 """
 import argparse
 import math
@@ -52,6 +52,11 @@ def main():
         b = torch.randn(6144, 2560, device=dev, dtype=torch.bfloat16)
         for _ in range(args.iters):
             cu.gemm(a, b)
+    elif args.which == "gemm_pair":
+        a = torch.randn(12288, 2560, device=dev, dtype=torch.bfloat16)
+        b = torch.randn(6144, 2560, device=dev, dtype=torch.bfloat16)
+        for _ in range(args.iters):
+            cu.gemm_pair(a, b)
     elif args.which == "decode":
         Bd = max(args.batch, 4)
         q = torch.randn(Bd, H, 1, D, device=dev, dtype=torch.bfloat16)
