@@ -22,6 +22,7 @@
 //
 // Replaces the cuBLAS calls behind nn.Linear in the reference (keys_values/model.py:596-610, lora_utils.py:159-172).
 #include <cuda.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -110,7 +111,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
                   __nv_bfloat16* __restrict__ C, const __nv_bfloat16* __restrict__ residual, int M, int N, int K, int K2,
-                  long long ldc, int* status, const GemmExtra ex) {
+                  long long ldc, int* status, const GemmExtra ex, const int diag) {
   using S = G2Smem;
   extern __shared__ uint8_t smem_raw[];
   // ---- all-gather copy CTAs (whole pairs: copy_span CTAs, the last one idle when ag_copy_ctas is odd). They take no
@@ -213,14 +214,18 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           }
         }
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag, status, STATUS_TIMEOUT_EMPTY)) {
+          if (diag == 1 && (tile != pair || kb >= G2_STAGES)) continue;  // diagnostics: the ring is filled once, the MMAs re-read it
+          // diag 2: loads keep flowing at their own pace (a stage is refilled when its previous load has landed, on this
+          // CTA's own barrier), the MMAs never wait
+          if (!mbar_wait_bounded(diag == 2 ? &full_bar[stage] : &empty_bar[stage], phase ^ 1, abort_flag, status, STATUS_TIMEOUT_EMPTY)) {
             ok = false;
             break;
           }
           uint8_t* sa = smem + stage * S::STAGE_BYTES;
           uint8_t* sb = sa + S::A_BYTES;
-          if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * S::STAGE_BYTES);
-          const uint32_t bar = mapa_u32(smem_u32(&full_bar[stage]), 0);  // the leader's barrier
+          if (diag == 2) mbar_expect_tx(&full_bar[stage], S::STAGE_BYTES);
+          else if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * S::STAGE_BYTES);
+          const uint32_t bar = mapa_u32(smem_u32(&full_bar[stage]), diag == 2 ? rank : 0);  // the leader's barrier
           if (kb < kb1) {
             tma_load_2d_pair(sa, &tmA, bar, kb * G2_BK, m0);
             tma_load_2d_pair(sb, &tmB, bar, kb * G2_BK, n0);
@@ -255,7 +260,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * G2_BN);
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, status, STATUS_TIMEOUT_FULL)) {
+          const bool fed = !diag || (diag == 1 && tile == pair && kb < G2_STAGES);
+          if (fed && !mbar_wait_bounded(&full_bar[stage], phase, abort_flag, status, STATUS_TIMEOUT_FULL)) {
             ok = false;
             break;
           }
@@ -269,7 +275,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             // advance 16 elements (32 B) along K inside the 128B swizzle row: +2 in 16 B units
             umma_f16_ss_pair(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          umma_commit_pair(&empty_bar[stage]);
+          if (!diag) umma_commit_pair(&empty_bar[stage]);
           if (++stage == G2_STAGES) {
             stage = 0;
             phase ^= 1;
@@ -387,12 +393,308 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   }
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// The wide variant: one 256 x 512 tile per CTA pair. The operands of a 256 x 256 tile cross L2 -> shared memory at 64
+// bytes per clock and SM at full tensor rate, which is what the L2 delivers to 148 SMs at once (measured: the loads of
+// the 256 x 256 kernel alone, running at their own pace, take as long as the whole kernel). A 256 x 512 tile re-uses the
+// A rows for two B tiles: 25 % fewer operand bytes per flop. Both 256-column accumulators of an SM belong to the same
+// tile (acc 0: columns [n0, n0 + 256), acc 1: [n0 + 256, n0 + 512)), so there is no second buffer: eight epilogue warps
+// (two per TMEM lane quarter, 128 columns each) drain acc 0 and then acc 1 while the next tile's first MMAs wait for the
+// accumulator they need; the producer keeps prefetching.
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int G2W_STAGES = 4;
+constexpr int G2W_THREADS = 64 + 256;
+constexpr int G2W_BN = 512;
+
+struct G2WSmem {
+  static constexpr int A_BYTES = G2_BM * G2_BK * 2;
+  static constexpr int B_BYTES = G2_BNH * G2_BK * 2;             // one half (128 rows) of one 256-row B tile
+  static constexpr int STAGE_BYTES = A_BYTES + 2 * B_BYTES;      // per CTA: A | B of acc 0 | B of acc 1
+  static constexpr int EPI_OFFSET = G2W_STAGES * STAGE_BYTES;    // per epilogue warp: 32 rows x 128 B staging
+  static constexpr int EPI_BYTES = 8 * 32 * 128;
+  static constexpr int BAR_OFFSET = EPI_OFFSET + EPI_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;
+};
+static_assert(G2WSmem::TOTAL + 64 <= 232448, "shared memory of the wide pair GEMM exceeds the limit of a CTA");
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2W_THREADS, 1)
+gemm2w_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                   const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
+                   __nv_bfloat16* __restrict__ C, const __nv_bfloat16* __restrict__ residual, int M, int N, int K, int K2,
+                   long long ldc, int* status, const GemmExtra ex) {
+  using S = G2WSmem;
+  extern __shared__ uint8_t smem_raw[];
+  const int copy_span = (ex.ag_copy_ctas + 1) & ~1;
+  if ((int)blockIdx.x < copy_span) {
+    if ((int)blockIdx.x < ex.ag_copy_ctas) gemm_ag_copy_role(ex, K, status, smem_raw);
+    return;
+  }
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + G2W_STAGES;
+  uint64_t* tmem_full = empty_bar + G2W_STAGES;   // [2]: accumulator h of the current tile is complete
+  uint64_t* tmem_empty = tmem_full + 2;           // [2]: accumulator h has been drained (used in the leader)
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0: leader
+  const int pair = ((int)blockIdx.x - copy_span) >> 1;
+  const int n_pairs = ((int)gridDim.x - copy_span) >> 1;
+  const int num_m = (M + 2 * G2_BM - 1) / (2 * G2_BM);
+  const int num_n = (N + G2W_BN - 1) / G2W_BN;
+  const int num_tiles = num_m * num_n;
+  const int kb1 = (K + G2_BK - 1) / G2_BK;
+  const int kb2 = (K2 + G2_BK - 1) / G2_BK;
+  const int num_kb = kb1 + kb2;
+  const bool aligned_ok = (smem_u32(smem) & 1023u) == 0;
+  const bool comm = ex.a_flags != nullptr || ex.rs_world > 1;
+  int m_rot = 0;
+  if (ex.a_flags) m_rot = (ex.ag_rank * ex.rows_per_chunk) / (2 * G2_BM);
+  if (ex.rs_world > 1) m_rot = (((ex.rs_rank + 1) * ex.rows_per_rank + 2 * G2_BM - 1) / (2 * G2_BM)) % num_m;
+  auto tile_coords = [&](int tile, int& m0, int& n0) {
+    if (comm) {
+      m0 = ((tile / num_n + m_rot) % num_m) * (2 * G2_BM);
+      n0 = (tile % num_n) * G2W_BN;
+    } else {
+      m0 = (tile % num_m) * (2 * G2_BM);
+      n0 = (tile / num_m) * G2W_BN;
+    }
+  };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < G2W_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 16);  // one arrive per epilogue warp of both CTAs
+    }
+    *abort_flag = aligned_ok ? 0 : 1;
+    if (!aligned_ok && status) atomicCAS(status, 0, STATUS_TIMEOUT_MISC);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_base_slot, 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0 && !*abort_flag) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
+        int m0, n0;
+        tile_coords(tile, m0, n0);
+        m0 += (int)rank * G2_BM;
+        n0 += (int)rank * G2_BNH;  // this CTA's half of the B tile of acc 0; acc 1: 256 rows further
+        if (ex.a_flags && m0 < M) {
+          const int chunk = m0 / ex.rows_per_chunk;
+          if (chunk != ex.ag_rank) {
+            long long t0 = clock64();
+            while ((int32_t)(ld_acquire_gpu_u32(ex.a_flags + chunk) - ex.a_target) < 0) {
+              if (*abort_flag || clock64() - t0 > ex.wait_limit) {
+                if (status) atomicCAS(status, 0, STATUS_TIMEOUT_PEER_FLAG);
+                *abort_flag = 1;
+                ok = false;
+                break;
+              }
+            }
+            if (!ok) break;
+            asm volatile("fence.proxy.async;" ::: "memory");
+          }
+        }
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag, status, STATUS_TIMEOUT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * S::STAGE_BYTES;
+          uint8_t* sb0 = sa + S::A_BYTES;
+          uint8_t* sb1 = sb0 + S::B_BYTES;
+          if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * S::STAGE_BYTES);
+          const uint32_t bar = mapa_u32(smem_u32(&full_bar[stage]), 0);  // the leader's barrier
+          const CUtensorMap* ta = kb < kb1 ? &tmA : &tmA2;
+          const CUtensorMap* tb = kb < kb1 ? &tmB : &tmB2;
+          const int k0 = (kb < kb1 ? kb : kb - kb1) * G2_BK;
+          tma_load_2d_pair(sa, ta, bar, k0, m0);
+          tma_load_2d_pair(sb0, tb, bar, k0, n0);
+          tma_load_2d_pair(sb1, tb, bar, k0, n0 + G2_BN);  // rows beyond N are filled with zeros
+          if (++stage == G2W_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) {
+        long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issuer (leader only)
+    if (lane == 0 && rank == 0 && !*abort_flag) {
+      constexpr uint32_t idesc = make_idesc_bf16(2 * G2_BM, G2_BN, 0, 0);
+      int stage = 0;
+      uint32_t phase = 0, tile_phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
+        for (int kb = 0; kb < num_kb && ok; ++kb) {
+          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, status, STATUS_TIMEOUT_FULL)) {
+            ok = false;
+            break;
+          }
+          const uint32_t sa = smem_u32(smem + stage * S::STAGE_BYTES);
+          const uint64_t da = make_smem_desc_sw128(sa, 16, 1024);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            if (kb == 0 && !mbar_wait_bounded(&tmem_empty[h], tile_phase ^ 1, abort_flag, status, STATUS_TIMEOUT_TMEM_EMPTY)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint64_t db = make_smem_desc_sw128(sa + S::A_BYTES + h * S::B_BYTES, 16, 1024);
+            const uint32_t d_tmem = tmem_base + (uint32_t)(h * G2_BN);
+#pragma unroll
+            for (int k = 0; k < G2_BK / 16; ++k)
+              umma_f16_ss_pair(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
+            if (kb == num_kb - 1) umma_commit_pair(&tmem_full[h]);
+          }
+          if (!ok) break;
+          umma_commit_pair(&empty_bar[stage]);
+          if (++stage == G2W_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        tile_phase ^= 1;
+      }
+    }
+  } else {
+    // --------------------------------------------------------------- epilogue (both CTAs, 8 warps)
+    const int e = warp - 2;
+    const int quarter = warp & 3;   // TMEM sub-partition of this warp
+    const int colhalf = e >> 2;     // which 128 of the 256 columns of an accumulator
+    const int row_in_tile = quarter * 32 + lane;
+    uint32_t tile_phase = 0;
+    const uint32_t empty_remote = mapa_u32(smem_u32(&tmem_empty[0]), 0);
+    uint8_t* stg = smem + S::EPI_OFFSET + e * (32 * 128);
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
+      int m0, n0;
+      tile_coords(tile, m0, n0);
+      m0 += (int)rank * G2_BM;
+      const int m = m0 + row_in_tile;
+      __nv_bfloat16* out_base = C;
+      long long out_row = m;
+      int dest = -1;
+      if (ex.rs_world > 1 && m0 < M) {
+        dest = m0 / ex.rows_per_rank;
+        out_base = ex.rs_dst[dest];
+        out_row = (long long)ex.rs_rank * ex.rows_per_rank + (m - dest * ex.rows_per_rank);
+      }
+      const long long out_row0 = out_row - lane;
+      const int m_warp0 = m0 + quarter * 32;
+      for (int h = 0; h < 2; ++h) {
+        if (!mbar_wait_bounded(&tmem_full[h], tile_phase, abort_flag, status, STATUS_TIMEOUT_TMEM_FULL)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(h * G2_BN + colhalf * 128);
+        const int nh = n0 + h * G2_BN + colhalf * 128;  // first column of this warp's 128
+#pragma unroll 1
+        for (int c0 = 0; c0 < 128; c0 += 64) {
+          const int n = nh + c0;
+          if (n >= N) break;  // warp-uniform
+          uint32_t r[64];
+          tmem_ld_32x32b_x32(taddr + (uint32_t)c0, r);
+          tmem_ld_32x32b_x32(taddr + (uint32_t)(c0 + 32), r + 32);
+          tmem_ld_wait();
+          if (n + 64 <= N) {
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(r[8 * v]), __uint_as_float(r[8 * v + 1]));
+              o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+              o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+              o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+              *reinterpret_cast<uint4*>(stg + lane * 128 + ((v ^ (lane & 7)) << 4)) = o;
+            }
+            __syncwarp();
+            const int u = lane & 7;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int rr = 4 * j + (lane >> 3);
+              uint4 o = *reinterpret_cast<const uint4*>(stg + rr * 128 + ((u ^ (rr & 7)) << 4));
+              if (m_warp0 + rr < M) {
+                if (residual) {
+                  const uint4 rv = *reinterpret_cast<const uint4*>(residual + (long long)(m_warp0 + rr) * ldc + n + u * 8);
+                  const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv);
+                  __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    const float2 a = __bfloat1622float2(op[i]), t = __bfloat1622float2(rp[i]);
+                    op[i] = __floats2bfloat162_rn(a.x + t.x, a.y + t.y);
+                  }
+                }
+                *reinterpret_cast<uint4*>(out_base + (out_row0 + rr) * ldc + n + u * 8) = o;
+              }
+            }
+            __syncwarp();
+          } else if (m < M) {
+            __nv_bfloat16* dst = out_base + out_row * ldc + n;
+            const __nv_bfloat16* res = residual ? residual + (long long)m * ldc + n : nullptr;
+            for (int i = 0; i < 64 && n + i < N; ++i) {
+              float f = __uint_as_float(r[i]);
+              if (res) f += __bfloat162float(res[i]);
+              dst[i] = __float2bfloat16_rn(f);
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(empty_remote + (uint32_t)(h * 8));
+        if (dest >= 0 && n0 + h * G2_BN < N) {
+          // Both warps of this lane quarter have stored their halves of the 128 x 256 block: make the peer stores
+          // visible system-wide, then one of them counts a quarter of the block at the owner (the same count per
+          // 128 x 256 block as in the other kernels).
+          __threadfence_system();
+          asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+          if (colhalf == 0 && lane == 0) red_release_sys_add(ex.rs_flag[dest] + ex.rs_rank, ex.rs_tile_inc);
+        }
+      }
+      tile_phase ^= 1;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
+}
+
 static int g2_max_pairs() {
   static int n[64] = {0};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
   if (!n[dev]) {
     cudaFuncSetAttribute(gemm2_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G2Smem::TOTAL);
+    cudaFuncSetAttribute(gemm2w_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G2WSmem::TOTAL);
     int sms = 0;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     // how many clusters of two can be resident at once (clusters do not span GPCs)
@@ -417,6 +719,27 @@ static int g2_max_pairs() {
     n[dev] = clusters > 0 ? clusters : 1;
   }
   return n[dev];
+}
+
+// KVB200_GEMM2_DIAG=1 (diagnostics, wrong results): the operand ring is filled once per CTA and every later MMA re-reads
+// it without waiting, which shows the rate of the issue loop and of the tensor core's own shared-memory reads alone.
+// KVB200_GEMM2_DIAG=2 (wrong results too): all loads are issued, each CTA refills a stage as soon as its previous load
+// has landed, and the MMAs never wait: the two sides run at their own pace, without the barrier hand-shake.
+static int g2_diag() {
+  static const int v = [] {
+    const char* e = getenv("KVB200_GEMM2_DIAG");
+    return (e && e[0] == '1') ? 1 : ((e && e[0] == '2') ? 2 : 0);
+  }();
+  return v;
+}
+
+// KVB200_GEMM2_TILE=narrow: always 256 x 256 tiles; =wide: always 256 x 512; otherwise chosen by the number of tiles.
+static int g2_wide_mode() {
+  static const int v = [] {
+    const char* e = getenv("KVB200_GEMM2_TILE");
+    return (e && e[0] == 'n') ? 0 : ((e && e[0] == 'w') ? 2 : 1);
+  }();
+  return v;
 }
 
 // Launch on CTA pairs; `extra` (may be NULL) selects a fused collective as in the single-CTA kernel. max_pairs > 0 limits
@@ -444,10 +767,24 @@ int launch_gemm_pair(const void* A, const void* B, const void* A2, const void* B
   pairs -= copy_pairs;  // copy CTAs and compute CTAs wait on one another: all of them must be resident at once
   if (pairs < 1) return KVB_ERR_ARG;
   if (max_pairs > 0 && max_pairs < pairs) pairs = max_pairs;
-  const int num_tiles = ((M + 2 * G2_BM - 1) / (2 * G2_BM)) * ((N + G2_BN - 1) / G2_BN);
+  // 256 x 512 tiles (fewer operand bytes per flop) when there are enough of them to keep every pair busy
+  const int num_m = (M + 2 * G2_BM - 1) / (2 * G2_BM);
+  const int tiles_wide = num_m * ((N + G2W_BN - 1) / G2W_BN);
+  // (measured: the wide tile wins for long K loops, where its exposed epilogue is a small share, as long as its fewer
+  // tiles still fill the last wave of pairs: 8192^3 0.81 -> 0.92 of the library GEMM, 8192 x 14336 x 4096 0.84 -> 0.88;
+  // 8192 x 4096 x 2048 0.92 -> 0.79)
+  const int waves_wide = (tiles_wide + pairs - 1) / pairs;
+  const bool wide_pays = K + K2 >= 4096 && tiles_wide >= 3 * pairs && 10LL * tiles_wide >= 9LL * waves_wide * pairs;
+  if (g2_wide_mode() == 2 || (g2_wide_mode() == 1 && wide_pays && !g2_diag())) {
+    if (tiles_wide < pairs) pairs = tiles_wide;
+    gemm2w_bf16_kernel<<<2 * (pairs + copy_pairs), G2W_THREADS, G2WSmem::TOTAL, stream>>>(
+        tmA, tmB, tmA2, tmB2, (__nv_bfloat16*)C, (const __nv_bfloat16*)residual, M, N, K, K2, ldc, status, ex);
+    return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
+  }
+  const int num_tiles = num_m * ((N + G2_BN - 1) / G2_BN);
   if (num_tiles < pairs) pairs = num_tiles;
   gemm2_bf16_kernel<<<2 * (pairs + copy_pairs), G2_THREADS, G2Smem::TOTAL, stream>>>(
-      tmA, tmB, tmA2, tmB2, (__nv_bfloat16*)C, (const __nv_bfloat16*)residual, M, N, K, K2, ldc, status, ex);
+      tmA, tmB, tmA2, tmB2, (__nv_bfloat16*)C, (const __nv_bfloat16*)residual, M, N, K, K2, ldc, status, ex, g2_diag());
   return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
 }
 

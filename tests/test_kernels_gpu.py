@@ -181,6 +181,17 @@ def test_gemm_on_cta_pairs(M, N, K):
     torch.testing.assert_close(c.float(), cr, atol=3e-2 * math.sqrt(K / 64), rtol=2e-2)
 
 
+def test_gemm_on_cta_pairs_wide_tiles():
+    """Long K and many tiles: the launcher takes 256 x 512 tiles per pair (both accumulators of an SM in one tile)."""
+    M, N, K = 4096, 8192, 4096  # 16 x 16 wide tiles: at least three waves of 74 pairs
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.05
+    c = _cuda().gemm_pair(a, b)
+    _cuda().check_status(DEV)
+    cr = a.float() @ b.float().t()
+    torch.testing.assert_close(c.float(), cr, atol=3e-2 * math.sqrt(K / 64), rtol=2e-2)
+
+
 def test_gemm_on_cta_pairs_lora_residual():
     M, N, K, R = 512, 1024, 512, 64
     a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
