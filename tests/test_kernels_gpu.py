@@ -183,7 +183,7 @@ def test_gemm_on_cta_pairs(M, N, K):
 
 def test_gemm_on_cta_pairs_wide_tiles():
     """Long K and many tiles: the launcher takes 256 x 512 tiles per pair (both accumulators of an SM in one tile)."""
-    M, N, K = 4096, 8192, 4096  # 16 x 16 wide tiles: at least three waves of 74 pairs
+    M, N, K = 8192, 8192, 4096  # 32 x 16 wide tiles: seven nearly full waves of 74 pairs
     a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
     b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.05
     c = _cuda().gemm_pair(a, b)
