@@ -214,7 +214,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           }
         }
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (diag == 1 && (tile != pair || kb >= G2_STAGES)) continue;  // diagnostics: the ring is filled once, the MMAs re-read it
+          if ((diag == 1 || diag >= 3) && (tile != pair || kb >= G2_STAGES)) continue;  // diagnostics: the ring is filled once, the MMAs re-read it
           // diag 2: loads keep flowing at their own pace (a stage is refilled when its previous load has landed, on this
           // CTA's own barrier), the MMAs never wait
           if (!mbar_wait_bounded(diag == 2 ? &full_bar[stage] : &empty_bar[stage], phase ^ 1, abort_flag, status, STATUS_TIMEOUT_EMPTY)) {
@@ -249,7 +249,10 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer (leader only)
     if (lane == 0 && rank == 0 && !*abort_flag) {
-      constexpr uint32_t idesc = make_idesc_bf16(2 * G2_BM, G2_BN, 0, 0);
+      // diag 3 / 4 (as diag 1, no operand feed): MMAs of N = 64 / N = 128 instead of 256, to time small instructions
+      // diag 5: N = 64 MMAs that alternate between two accumulators (two independent chains of accumulation)
+      const uint32_t idesc = (diag == 3 || diag == 5) ? make_idesc_bf16(2 * G2_BM, 64, 0, 0)
+                                       : (diag == 4 ? make_idesc_bf16(2 * G2_BM, 128, 0, 0) : make_idesc_bf16(2 * G2_BM, G2_BN, 0, 0));
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -260,7 +263,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * G2_BN);
         for (int kb = 0; kb < num_kb; ++kb) {
-          const bool fed = !diag || (diag == 1 && tile == pair && kb < G2_STAGES);
+          const bool fed = !diag || ((diag == 1 || diag >= 3) && tile == pair && kb < G2_STAGES);
           if (fed && !mbar_wait_bounded(&full_bar[stage], phase, abort_flag, status, STATUS_TIMEOUT_FULL)) {
             ok = false;
             break;
@@ -273,7 +276,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 #pragma unroll
           for (int k = 0; k < G2_BK / 16; ++k) {
             // advance 16 elements (32 B) along K inside the 128B swizzle row: +2 in 16 B units
-            umma_f16_ss_pair(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16_ss_pair(diag == 5 ? d_tmem + (uint32_t)((k & 1) * 64) : d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
+                             (kb | k) != 0 ? 1u : 0u);
           }
           if (!diag) umma_commit_pair(&empty_bar[stage]);
           if (++stage == G2_STAGES) {
@@ -723,12 +727,14 @@ static int g2_max_pairs() {
 
 // KVB200_GEMM2_DIAG=1 (diagnostics, wrong results): the operand ring is filled once per CTA and every later MMA re-reads
 // it without waiting, which shows the rate of the issue loop and of the tensor core's own shared-memory reads alone.
+// KVB200_GEMM2_DIAG=3 / 4 / 5: as 1 with MMAs of N = 64 / N = 128 / N = 64 alternating between two accumulators (the
+// cost of small instructions).
 // KVB200_GEMM2_DIAG=2 (wrong results too): all loads are issued, each CTA refills a stage as soon as its previous load
 // has landed, and the MMAs never wait: the two sides run at their own pace, without the barrier hand-shake.
 static int g2_diag() {
   static const int v = [] {
     const char* e = getenv("KVB200_GEMM2_DIAG");
-    return (e && e[0] == '1') ? 1 : ((e && e[0] == '2') ? 2 : 0);
+    return (e && e[0] >= '1' && e[0] <= '5') ? e[0] - '0' : 0;
   }();
   return v;
 }
