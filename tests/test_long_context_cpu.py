@@ -107,6 +107,35 @@ def test_gradients_multi_cell_equal_single_cell(name, lpc):
     torch.testing.assert_close(gm(ids, tg).mean(), torch.tensor(res[0][0]), atol=1e-6, rtol=1e-6)
 
 
+@pytest.mark.parametrize("name", ["tiny-gemma2", "tiny-llama-d64"])
+def test_gradients_window_softcap_and_small_heads_chunked_equal_naive(name):
+    """A Gemma-2 style model (one layer with a sliding window, capped attention scores and logits, post norms) and a model
+    with head size 64: the chunked pass over a cache that holds the whole sequence equals whole-sequence autograd."""
+    from keys_values_b200.config import Config
+
+    torch.manual_seed(0)
+    cfg = Config.from_name(name)
+    m = GPT(cfg)
+    m.apply(m._init_weights)
+    head = CrossEntropyOnLogits(cfg)
+    T, C, cs = 320, 384, 64  # the window of the Gemma-style layer (96) is shorter than the sequence
+    ids = torch.randint(0, cfg.vocab_size, (1, T))
+    tg = torch.randint(0, cfg.vocab_size, (1, 64))
+    m.assign_kv_caches(KVCacheFactory.create(m, "h2o-default", 1, C, dtype=torch.float32, cache_kwargs=dict(max_chunk_size=cs)))
+    gm = LongContextGradientModel(m, head, layers_per_cell=1, chunk_size=cs)
+    gm.train()
+    loss = gm(ids, tg)
+    loss.backward()
+    g1 = _grads(m)
+    l2 = NaiveGPTAndHeadModel(m, head)(ids, tg)
+    l2.backward()
+    g2 = _grads(m)
+    assert abs(float(loss.value) - float(l2.detach())) < 1e-4
+    assert g1.keys() == g2.keys() and len(g1) > 0
+    for k in g1:
+        torch.testing.assert_close(g1[k], g2[k], atol=2e-5, rtol=1e-3)
+
+
 def test_gradients_quantized_cache_and_saved_attention():
     _, m = _lora_model()
     head = CrossEntropyOnLogits(m.config)
