@@ -49,6 +49,14 @@ struct DecParams {
   float* lse;                   // (B,H)
   int B, H, G, L, C, gs, nS, split;
   float scale;
+  // Logit soft-capping (0: none): scores become softcap · tanh(score / softcap). Sliding window (0: none): slots whose
+  // token is at or before query position − window are hidden; tok_pos (B,G,C) with strides gives the tokens of the slots,
+  // the query position is *pos_src when that pointer is set (captured decode steps), else query_pos.
+  float softcap;
+  int window, query_pos;
+  const int32_t* tok_pos;
+  long long tp_sb, tp_sg;
+  const int* pos_src;
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -384,6 +392,18 @@ decode_partial_kernel(const DecParams p) {
     }
     float s00 = p.scale * kslo * (d[0] - kzlo * qsum0), s01 = p.scale * kslo * (d[1] - kzlo * qsum1);
     float s10 = p.scale * kshi * (d[2] - kzhi * qsum0), s11 = p.scale * kshi * (d[3] - kzhi * qsum1);
+    if (p.softcap > 0.f) {
+      const float inv = 1.f / p.softcap;
+      s00 = p.softcap * tanhf(s00 * inv); s01 = p.softcap * tanhf(s01 * inv);
+      s10 = p.softcap * tanhf(s10 * inv); s11 = p.softcap * tanhf(s11 * inv);
+    }
+    if (p.window > 0) {
+      // hidden slots keep the mark of "no slot" (their weight and their share of the output are zero)
+      const int oldest = (p.pos_src ? *p.pos_src : p.query_pos) - p.window;
+      const int32_t* tp = p.tok_pos + b * p.tp_sb + g * p.tp_sg + j0;
+      if (jlo < n && tp[jlo] <= oldest) s00 = s01 = -FLT_MAX;
+      if (jhi < n && tp[jhi] <= oldest) s10 = s11 = -FLT_MAX;
+    }
     float mx0 = -FLT_MAX, mx1 = -FLT_MAX;
     if (jlo < n) {
       if (ha < nh) p.logits[(head0 + ha) * p.L + j0 + jlo] = s00;
@@ -602,12 +622,27 @@ extern "C" long long kvb_decode_scratch_bytes(int B, int H, int L) {
   return ((long long)B * H * L + 2LL * B * H * nS + (long long)B * H * nS * kvb::DEC_D + (long long)B * H) * 4;
 }
 
+extern "C" const int* kvb_position_source();
+
 extern "C" int kvb_decode_attn(const void* q, const void* kq, const void* vq, const float* ks, const int32_t* kz, const float* vs,
                                const int32_t* vz, const void* k_new, const void* v_new, const int32_t* new_slot, void* out,
                                float* weights, void* scratch, int B, int H, int G, int L, int C, int bits, float scale,
                                void* stream) {
+  return kvb_decode_attn_ex(q, kq, vq, ks, kz, vs, vz, k_new, v_new, new_slot, out, weights, scratch, B, H, G, L, C, bits, scale,
+                            0.f, 0, nullptr, 0, 0, 0, stream);
+}
+
+// softcap: logit soft-capping threshold (0: none). window: sliding window in tokens (0: none) with token_pos (B,G,C) int32
+// (strides tp_sb, tp_sg in elements) and the position of the query token (read from the device-resident position word
+// when one is set, so that a captured step serves every later position).
+extern "C" int kvb_decode_attn_ex(const void* q, const void* kq, const void* vq, const float* ks, const int32_t* kz,
+                                  const float* vs, const int32_t* vz, const void* k_new, const void* v_new,
+                                  const int32_t* new_slot, void* out, float* weights, void* scratch, int B, int H, int G, int L,
+                                  int C, int bits, float scale, float softcap, int window, const int32_t* token_pos,
+                                  long long tp_sb, long long tp_sg, int query_pos, void* stream) {
   using namespace kvb;
   if (B <= 0 || H <= 0 || G <= 0 || L <= 0 || C < L || H % G) return KVB_ERR_ARG;
+  if (softcap < 0.f || window < 0 || (window > 0 && !token_pos)) return KVB_ERR_ARG;
   const int gs = H / G;
   if (gs > DEC_MAX_GS) return KVB_ERR_UNSUPPORTED;
   if (bits != 16 && bits != 8 && bits != 4) return KVB_ERR_ARG;
@@ -620,6 +655,8 @@ extern "C" int kvb_decode_attn(const void* q, const void* kq, const void* vq, co
   p.k_new = (const __nv_bfloat16*)k_new; p.v_new = (const __nv_bfloat16*)v_new; p.new_slot = k_new ? new_slot : nullptr;
   p.out = (__nv_bfloat16*)out; p.weights = weights;
   p.B = B; p.H = H; p.G = G; p.L = L; p.C = C; p.gs = gs; p.scale = scale;
+  p.softcap = softcap; p.window = window; p.query_pos = query_pos; p.tok_pos = token_pos; p.tp_sb = tp_sb; p.tp_sg = tp_sg;
+  p.pos_src = window > 0 ? kvb_position_source() : nullptr;
   // Slots per CTA: longer splits spend less on the per-CTA prologue and merge, as long as there are
   // CTAs for a few waves over the SMs. The scratch is laid out for the shortest split.
   const int zb = (gs + DEC_HB - 1) / DEC_HB;

@@ -116,6 +116,12 @@ long long kvb_decode_scratch_bytes(int B, int H, int L);
 int kvb_decode_attn(const void* q, const void* kq, const void* vq, const float* ks, const int32_t* kz, const float* vs,
                     const int32_t* vz, const void* k_new, const void* v_new, const int32_t* new_slot, void* out, float* weights,
                     void* scratch, int B, int H, int G, int L, int C, int bits, float scale, void* stream);
+// the same with logit soft-capping (0: none) and a sliding window (0: none; token_pos (B,G,C) int32 with strides, query_pos =
+// position of the query token, taken from the device-resident position word when one is set)
+int kvb_decode_attn_ex(const void* q, const void* kq, const void* vq, const float* ks, const int32_t* kz, const float* vs,
+                       const int32_t* vz, const void* k_new, const void* v_new, const int32_t* new_slot, void* out, float* weights,
+                       void* scratch, int B, int H, int G, int L, int C, int bits, float scale, float softcap, int window,
+                       const int32_t* token_pos, long long tp_sb, long long tp_sg, int query_pos, void* stream);
 
 
 // ---- comm.cu: symmetric memory over CUDA IPC and the fused all-reduce

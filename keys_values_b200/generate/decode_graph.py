@@ -69,8 +69,6 @@ class DecodeGraph:
                 return "only last-recent caches and the plain H2O family with max_chunk_size choose their slots on the device"
             if cache._do_replay_log or cache.attn_recorder is not None:
                 return "replay logging or recording is switched on"
-            if cache.mha.sliding_window(cache.block_idx) is not None or cache.config.attention_logit_softcapping is not None:
-                return "sliding windows and logit soft-capping are not served by the decode kernel"
             if not cache.kv_buffers.supports_direct_decode() or getattr(cache.kv_buffers, "before_access", None) is not None:
                 return "the cache buffers are not read in place by the decode kernel"
         c = model.config

@@ -69,9 +69,7 @@ class KVCacheWithBuffers(DefaultKVCache):
 
     # -- single-token decode straight from the storage
     def _can_decode_direct(self, query: torch.Tensor) -> bool:
-        if not query.is_cuda or self.mha.sliding_window(self.block_idx) is not None:
-            return False
-        if self.config.attention_logit_softcapping is not None or torch.is_grad_enabled() and query.requires_grad:
+        if not query.is_cuda or (torch.is_grad_enabled() and query.requires_grad):
             return False
         from keys_values_b200.ops import cuda as _cu
 
@@ -83,7 +81,12 @@ class KVCacheWithBuffers(DefaultKVCache):
             self._forward(key, value, token_idx)
         finally:
             self.kv_buffers.decode_mode = False
-        return self.kv_buffers.decode_attention(query, self.mha.pos_encoding.sdpa_scale_factor(), need_weights)
+        # a layer with a sliding window hides the slots whose token has left it; capped scores go through tanh in the kernel
+        window = self.mha.sliding_window(self.block_idx)
+        variant = dict(softcap=self.config.attention_logit_softcapping)
+        if window is not None:
+            variant.update(sliding_window=window, token_pos=self.token_pos, query_pos=self.input_pos)
+        return self.kv_buffers.decode_attention(query, self.mha.pos_encoding.sdpa_scale_factor(), need_weights, **variant)
 
     def deallocate_buffers(self) -> None:
         self.kv_buffers.deallocate()

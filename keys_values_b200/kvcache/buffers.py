@@ -160,10 +160,11 @@ class DefaultKVCacheBuffers(KVCacheBuffers):
     def supports_direct_decode(self) -> bool:
         return self.k is not None and self.k.is_cuda and self.k.dtype == torch.bfloat16 and self.head_size == 128
 
-    def decode_attention(self, query, scale, need_weights):
+    def decode_attention(self, query, scale, need_weights, **variant):
+        """``variant``: ``softcap``, ``sliding_window``, ``token_pos``, ``query_pos`` of :func:`ops.cuda.decode_attention`."""
         from keys_values_b200.ops import cuda as _cu
 
-        return _cu.decode_attention(query, self.k, self.v, scale, self.current_length, need_weights)
+        return _cu.decode_attention(query, self.k, self.v, scale, self.current_length, need_weights, **variant)
 
     def size_estimate(self):
         p = self.params

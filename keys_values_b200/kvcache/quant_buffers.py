@@ -152,7 +152,7 @@ class QuantizedKVCacheBuffers(KVCacheBuffers):
         return (self._fusable() and qk.buffers_are_allocated and qk.quant_buffer.is_cuda and self.head_size == 128
                 and self.cache_length % 4 == 0)
 
-    def decode_attention(self, query, scale, need_weights):
+    def decode_attention(self, query, scale, need_weights, **variant):
         """Attention of one new token straight from the quantized storage; the row
         written by the preceding :meth:`write` is taken in full precision."""
         from keys_values_b200.ops import cuda as _cu
@@ -163,6 +163,7 @@ class QuantizedKVCacheBuffers(KVCacheBuffers):
         return _cu.decode_attention(
             query, qk.quant_buffer, qv.quant_buffer, scale, self.current_length, need_weights,
             quant=(qk.quant_scales, qk.quant_zero_points, qv.quant_scales, qv.quant_zero_points, self.num_bits), new_kv=new_kv,
+            **variant,
         )
 
     def write(self, slots, key, value, token_pos, input_pos) -> None:

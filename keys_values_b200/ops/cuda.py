@@ -601,10 +601,14 @@ def decode_supported(query: torch.Tensor, n_query_groups: int) -> bool:
             and H % n_query_groups == 0 and H // n_query_groups <= 16)
 
 
-def decode_attention(query, key, value, scale, kv_len, return_weights=False, quant=None, new_kv=None):
+def decode_attention(query, key, value, scale, kv_len, return_weights=False, quant=None, new_kv=None, softcap=None,
+                     sliding_window=None, token_pos=None, query_pos: int = 0):
     """One-token attention. ``key/value``: bf16 ``(Bmax,G,C,D)`` buffers (``quant is None``) or
     uint8 code buffers with ``quant = (k_scale, k_zp, v_scale, v_zp, bits)``. ``new_kv =
     (k_new (B,G,D), v_new (B,G,D), slot (B,G) int32)`` substitutes one row in full precision.
+    ``softcap``: scores become ``cap · tanh(score / cap)``. ``sliding_window`` with ``token_pos (Bmax,G,C)`` int32 and
+    ``query_pos`` (the position of the query token; inside :class:`device_position` the kernel reads the device word
+    instead): slots whose token is at or before ``query_pos - sliding_window`` are hidden.
     Returns ``(out (B,1,H·D), weights (B,G,kv_len) | None)``."""
     B, H, _, D = query.shape
     G, C = key.shape[1], key.shape[2]
@@ -625,8 +629,15 @@ def decode_attention(query, key, value, scale, kv_len, return_weights=False, qua
         kn, vn, sl = new_kv
         kn, vn = kn.contiguous(), vn.contiguous()
         sl = sl.to(torch.int32).contiguous()
-    _check(lib().kvb_decode_attn(_p(query.contiguous()), _p(key), _p(value), _p(ks), _p(kz), _p(vs), _p(vz), _p(kn), _p(vn), _p(sl),
-                                 _p(out), _p(weights), _p(scratch), B, H, G, int(kv_len), C, int(bits), ctypes.c_float(scale),
-                                 _stream(query)), "decode_attn")
+    tp = None
+    if sliding_window:
+        if token_pos is None or token_pos.dtype != torch.int32 or token_pos.stride(2) != 1:
+            raise NativeError("decode_attention: a sliding window needs int32 token positions (B, G, C) with unit stride")
+        tp = token_pos
+    _check(lib().kvb_decode_attn_ex(_p(query.contiguous()), _p(key), _p(value), _p(ks), _p(kz), _p(vs), _p(vz), _p(kn), _p(vn), _p(sl),
+                                    _p(out), _p(weights), _p(scratch), B, H, G, int(kv_len), C, int(bits), ctypes.c_float(scale),
+                                    ctypes.c_float(softcap or 0.0), int(sliding_window or 0), _p(tp),
+                                    _ll(tp.stride(0) if tp is not None else 0), _ll(tp.stride(1) if tp is not None else 0),
+                                    int(query_pos), _stream(query)), "decode_attn")
     _count(3 if return_weights else 2)
     return out, weights

@@ -14,10 +14,10 @@ from keys_values_b200.models.model import GPT
 pytestmark = pytest.mark.gpu
 
 
-def _setup(cache_name, B, C, cache_kwargs=None):
+def _setup(cache_name, B, C, cache_kwargs=None, model="tiny-qwen3"):
     dev, dtype = torch.device("cuda", 0), torch.bfloat16
     torch.manual_seed(0)
-    cfg = Config.from_name("tiny-qwen3")
+    cfg = Config.from_name(model)
     m = GPT(cfg)
     m.apply(m._init_weights)
     m = m.to(device=dev, dtype=dtype).eval()
@@ -65,6 +65,45 @@ def test_graph_decode_equals_eager(cache_name, cache_kwargs):
     assert torch.allclose(l0, l1, atol=2e-2, rtol=2e-2)
     for a, b in zip(tp0, tp1):  # the slots chosen and the positions written there agree
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("cache_name", ["h2o-default", "h2o-torch-quantized8", "lastrec-default"])
+def test_graph_decode_with_sliding_window_and_softcap(cache_name, monkeypatch):
+    """A Gemma-2 style model (a layer with a window shorter than the cache, capped scores): the decode kernel serves it
+    (strict mode: no restatement), captured steps give the tokens of eager steps, and the first step agrees with the
+    PyTorch restatement of the same attention."""
+    from keys_values_b200 import ops
+
+    monkeypatch.setenv("KVB200_STRICT_NATIVE", "1")
+    B, C, T, steps = 2, 256, 600, 16
+    cfg, m, dev = _setup(cache_name, B, C, model="tiny-gemma2")
+    prompts = torch.randint(0, cfg.vocab_size, (B, T), device=dev)
+    results = {}
+    with torch.inference_mode():
+        for use_graph in (False, True):
+            logits = _prefill(m, prompts, T + steps + 1)
+            tok = logits.argmax(-1).view(B, 1)
+            dec = Decoder(m, B, use_graph=use_graph)
+            toks, lgs = [], []
+            for _ in range(steps):
+                lg = dec(tok)
+                tok = lg[:, -1].argmax(-1, keepdim=True)
+                toks.append(tok.clone())
+                lgs.append(lg.float().clone())
+            if use_graph:
+                assert dec.graph is not None, dec.reason
+            results[use_graph] = (torch.cat(toks, 1), torch.stack(lgs))
+        assert torch.equal(results[False][0], results[True][0])
+        assert torch.allclose(results[False][1], results[True][1], atol=2e-2, rtol=2e-2)
+        # the same first step through the restatement
+        monkeypatch.setenv("KVB200_STRICT_NATIVE", "0")
+        ops.set_native_attention(False)
+        try:
+            logits = _prefill(m, prompts, T + steps + 1)
+            lg = m(logits.argmax(-1).view(B, 1))
+        finally:
+            ops.set_native_attention(True)
+        assert torch.allclose(lg.float(), results[False][1][0], atol=8e-2, rtol=5e-2)
 
 
 def test_graph_decode_conditions_and_generate_api():

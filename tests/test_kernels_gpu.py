@@ -432,6 +432,46 @@ def test_decode_attention(bits, B, H, G, L, C):
     torch.testing.assert_close(w, w_r, atol=1e-3, rtol=2e-2)
 
 
+@pytest.mark.parametrize("bits", [16, 8, 4])
+@pytest.mark.parametrize("B,H,G,L,C,window,softcap", [(1, 32, 8, 4096, 4096, 1000, None), (2, 8, 2, 1500, 2048, None, 2.0),
+                                                      (2, 14, 2, 777, 1024, 300, 3.0)])
+def test_decode_attention_sliding_window_and_softcap(bits, B, H, G, L, C, window, softcap):
+    """The decode kernel with capped scores and with slots hidden by a sliding window (an evicted cache: the tokens
+    of the slots are a random subset of the positions before the query)."""
+    D = 128
+    scale = 1.0 / math.sqrt(D)
+    q = torch.randn(B, H, 1, D, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(B, G, C, D, device=DEV, dtype=torch.bfloat16)
+    v = torch.randn(B, G, C, D, device=DEV, dtype=torch.bfloat16)
+    query_pos = 3 * L
+    tp = torch.zeros(B, G, C, device=DEV, dtype=torch.int32)
+    for b in range(B):
+        for g in range(G):
+            tp[b, g, :L] = torch.randperm(query_pos, device=DEV)[:L].to(torch.int32)
+    slot = torch.randint(0, L, (B, G), device=DEV, dtype=torch.int32)
+    tp.scatter_(2, slot.long().unsqueeze(-1), torch.full((B, G, 1), query_pos, device=DEV, dtype=torch.int32))  # the query's own token
+    kw = dict(softcap=softcap, sliding_window=window, token_pos=tp, query_pos=query_pos)
+    if bits == 16:
+        out, w = _cuda().decode_attention(q, k, v, scale, L, True, **kw)
+        k_eff, v_eff = k[:, :, :L], v[:, :, :L]
+    else:
+        qk, sk, zk = ref.quantize_rows(k, bits)
+        qv, sv, zv = ref.quantize_rows(v, bits)
+        k_new = torch.randn(B, G, D, device=DEV, dtype=torch.bfloat16)
+        v_new = torch.randn(B, G, D, device=DEV, dtype=torch.bfloat16)
+        out, w = _cuda().decode_attention(q, qk, qv, scale, L, True, quant=(sk, zk, sv, zv, bits), new_kv=(k_new, v_new, slot), **kw)
+        k_eff = ref.dequantize_rows(qk, sk, zk, bits, torch.bfloat16)[:, :, :L].clone()
+        v_eff = ref.dequantize_rows(qv, sv, zv, bits, torch.bfloat16)[:, :, :L].clone()
+        idx = slot.long().view(B, G, 1, 1).expand(B, G, 1, D)
+        k_eff.scatter_(2, idx, k_new.unsqueeze(2))
+        v_eff.scatter_(2, idx, v_new.unsqueeze(2))
+    out_r, w_r = ref.sdpa(q, k_eff, v_eff, scale, query_pos, tp[:, :, :L], True, window, softcap)
+    torch.testing.assert_close(out.float(), out_r.float(), atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(w, w_r, atol=1e-3, rtol=2e-2)
+    if window is not None:
+        assert bool((w[tp[:, :, :L] <= query_pos - window] == 0).all())
+
+
 @pytest.mark.parametrize("dim,rows", [(1024, 777), (2560, 777), (3072, 777), (4096, 4), (2560, 1), (5120, 64)])
 def test_add_rmsnorm_fused(dim, rows):
     """s = x + res; y = rmsnorm(s): one kernel forward, one kernel backward (with the gradient of
