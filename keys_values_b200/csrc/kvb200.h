@@ -94,11 +94,12 @@ long long kvb_sdpa_fwd_scratch_bytes(int B, int H, int G, int q_len, int kv_len)
 int kvb_sdpa_fwd(const void* q, const void* k, const void* v, const int32_t* token_pos, void* out, float* lse, float* weights,
                  void* scratch, int B, int H, int G, int q_len, int kv_len, long long k_sb, long long k_sg, long long tp_sb,
                  long long tp_sg, float scale, int input_pos, int* status, void* stream);
-// the same for head size 128 or 64, with a sliding window in tokens (0: none) and a logit soft-capping threshold (0: none)
+// the same for head size 128 or 64, q with batch / head strides q_sb, q_sh (elements; 0, 0: contiguous), with a sliding
+// window in tokens (0: none) and a logit soft-capping threshold (0: none)
 int kvb_sdpa_fwd_ex(const void* q, const void* k, const void* v, const int32_t* token_pos, void* out, float* lse, float* weights,
-                    void* scratch, int B, int H, int G, int q_len, int kv_len, int head_size, long long k_sb, long long k_sg,
-                    long long tp_sb, long long tp_sg, float scale, int input_pos, int window, float softcap, int* status,
-                    void* stream);
+                    void* scratch, int B, int H, int G, int q_len, int kv_len, int head_size, long long q_sb, long long q_sh,
+                    long long k_sb, long long k_sg, long long tp_sb, long long tp_sg, float scale, int input_pos, int window,
+                    float softcap, int* status, void* stream);
 
 // ---- sdpa_bwd_sm100.cu: dq (B,H,T,D) bf16 is written, dk/dv (B,G,C,D) fp32 are accumulated into
 long long kvb_sdpa_bwd_scratch_bytes(int B, int H, int G, int q_len, int kv_len);
@@ -108,8 +109,9 @@ int kvb_sdpa_bwd(const void* q, const void* k, const void* v, const int32_t* tok
                  int input_pos, int* status, void* stream);
 int kvb_sdpa_bwd_ex(const void* q, const void* k, const void* v, const int32_t* token_pos, const void* out, const void* dout,
                     const float* lse, void* dq, float* dk, float* dv, void* scratch, int B, int H, int G, int q_len, int kv_len,
-                    int head_size, long long k_sb, long long k_sg, long long tp_sb, long long tp_sg, long long dk_sb,
-                    long long dk_sg, float scale, int input_pos, int window, float softcap, int* status, void* stream);
+                    int head_size, long long q_sb, long long q_sh, long long k_sb, long long k_sg, long long tp_sb,
+                    long long tp_sg, long long dk_sb, long long dk_sg, float scale, int input_pos, int window, float softcap,
+                    int* status, void* stream);
 
 // ---- decode.cu: q (B,H,D) bf16; K/V either bf16 (bits = 16) or int8/int4 codes with scale / zero point
 long long kvb_decode_scratch_bytes(int B, int H, int L);

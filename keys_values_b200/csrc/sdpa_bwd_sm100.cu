@@ -764,31 +764,34 @@ extern "C" long long kvb_sdpa_bwd_scratch_bytes(int B, int H, int G, int q_len, 
   return (bw_round4(2LL * B * G * nT) + bw_round4((long long)B * H * q_len)) * 4 + (long long)B * H * q_len * 128 * 2;
 }
 
-// head_size: 128 or 64; window: sliding window in tokens (0: none); softcap: logit soft-capping threshold (0: none),
-// as in the forward.
+// head_size: 128 or 64; q_sb, q_sh: batch and head strides of q in elements (0, 0: contiguous (B,H,T,D)); window: sliding
+// window in tokens (0: none); softcap: logit soft-capping threshold (0: none), as in the forward.
 extern "C" int kvb_sdpa_bwd_ex(const void* q, const void* k, const void* v, const int32_t* token_pos, const void* out,
                                const void* dout, const float* lse, void* dq, float* dk, float* dv, void* scratch, int B, int H,
-                               int G, int q_len, int kv_len, int head_size, long long k_sb, long long k_sg, long long tp_sb,
-                               long long tp_sg, long long dk_sb, long long dk_sg, float scale, int input_pos, int window,
-                               float softcap, int* status, void* stream);
+                               int G, int q_len, int kv_len, int head_size, long long q_sb, long long q_sh, long long k_sb,
+                               long long k_sg, long long tp_sb, long long tp_sg, long long dk_sb, long long dk_sg, float scale,
+                               int input_pos, int window, float softcap, int* status, void* stream);
 
 extern "C" int kvb_sdpa_bwd(const void* q, const void* k, const void* v, const int32_t* token_pos, const void* out,
                             const void* dout, const float* lse, void* dq, float* dk, float* dv, void* scratch, int B, int H,
                             int G, int q_len, int kv_len, long long k_sb, long long k_sg, long long tp_sb, long long tp_sg,
                             long long dk_sb, long long dk_sg, float scale, int input_pos, int* status, void* stream) {
-  return kvb_sdpa_bwd_ex(q, k, v, token_pos, out, dout, lse, dq, dk, dv, scratch, B, H, G, q_len, kv_len, 128, k_sb, k_sg, tp_sb,
-                         tp_sg, dk_sb, dk_sg, scale, input_pos, 0, 0.f, status, stream);
+  return kvb_sdpa_bwd_ex(q, k, v, token_pos, out, dout, lse, dq, dk, dv, scratch, B, H, G, q_len, kv_len, 128, 0, 0, k_sb, k_sg,
+                         tp_sb, tp_sg, dk_sb, dk_sg, scale, input_pos, 0, 0.f, status, stream);
 }
 
 extern "C" int kvb_sdpa_bwd_ex(const void* q, const void* k, const void* v, const int32_t* token_pos, const void* out,
                                const void* dout, const float* lse, void* dq, float* dk, float* dv, void* scratch, int B, int H,
-                               int G, int q_len, int kv_len, int head_size, long long k_sb, long long k_sg, long long tp_sb,
-                               long long tp_sg, long long dk_sb, long long dk_sg, float scale, int input_pos, int window,
-                               float softcap, int* status, void* stream) {
+                               int G, int q_len, int kv_len, int head_size, long long q_sb, long long q_sh, long long k_sb,
+                               long long k_sg, long long tp_sb, long long tp_sg, long long dk_sb, long long dk_sg, float scale,
+                               int input_pos, int window, float softcap, int* status, void* stream) {
   using namespace kvb;
   if (B <= 0 || H <= 0 || G <= 0 || q_len <= 0 || kv_len <= 0 || H % G) return KVB_ERR_ARG;
   if (window < 0 || softcap < 0.f || (softcap > 0.f && scale <= 0.f)) return KVB_ERR_ARG;
   if (head_size != 128 && head_size != 64) return KVB_ERR_UNSUPPORTED;
+  if (q_sh == 0) q_sh = (long long)q_len * head_size;
+  if (q_sb == 0) q_sb = (long long)H * q_sh;
+  if ((q_sb % 8) || (q_sh % 8) || q_sh < (long long)q_len * head_size) return KVB_ERR_ALIGN;
   const int gs = H / G;
   if (gs > 64) return KVB_ERR_UNSUPPORTED;  // a 64-column unit of the dK/dV launch holds all heads of a group
   if ((k_sb % 8) || (k_sg % 8) || (dk_sb % 4) || (dk_sg % 4)) return KVB_ERR_ALIGN;
@@ -832,8 +835,8 @@ extern "C" int kvb_sdpa_bwd_ex(const void* q, const void* k, const void* v, cons
   int rc;
   const uint64_t qT = (uint64_t)q_len, HT = (uint64_t)H * q_len, hd = (uint64_t)head_size;
   // Q (B,H,T,D): dims (D,T,H,B)
-  if ((rc = bw_make_tmap_4d(&tmQ, q, hd, q_len, H, B, hd, qT * hd, HT * hd, 64, p.npos, gs))) return rc;
-  if ((rc = bw_make_tmap_4d(&tmQh, q, hd, q_len, H, B, hd, qT * hd, HT * hd, 64, p.hnpos, p.u_heads))) return rc;
+  if ((rc = bw_make_tmap_4d(&tmQ, q, hd, q_len, H, B, hd, (uint64_t)q_sh, (uint64_t)q_sb, 64, p.npos, gs))) return rc;
+  if ((rc = bw_make_tmap_4d(&tmQh, q, hd, q_len, H, B, hd, (uint64_t)q_sh, (uint64_t)q_sb, 64, p.hnpos, p.u_heads))) return rc;
   // dO (B,T,H,D) viewed with dims (D,T,H,B): T stride H*D, H stride D
   if (dOt) {  // the head-major copy that the delta kernel leaves: same strides as Q
     if ((rc = bw_make_tmap_4d(&tmdO, dOt, hd, q_len, H, B, hd, qT * hd, HT * hd, 64, p.npos, gs))) return rc;

@@ -1165,28 +1165,33 @@ extern "C" long long kvb_sdpa_fwd_scratch_bytes(int B, int H, int G, int q_len, 
 // q (B,H,T,128) contiguous bf16; k, v (B,G,L,128) bf16 with batch / group strides k_sb, k_sg (elements);
 // token_pos (B,G,L) int32 with strides, or NULL (slot j holds token j); out (B,T,H,128) bf16;
 // lse (B,H,T) fp32 or NULL; weights (B,G,L) fp32 or NULL.
-// head_size: 128 or 64 (the last axis of q, k, v, out); window: sliding window in tokens (0: none); softcap: logit
-// soft-capping threshold (0: none).
+// head_size: 128 or 64 (the last axis of q, k, v, out); q_sb, q_sh: batch and head strides of q in elements (0, 0:
+// contiguous (B,H,T,D); rows of one head are always head_size apart), so that a slice of positions of a longer
+// (B,H,T',D) tensor is read in place; window: sliding window in tokens (0: none); softcap: logit soft-capping
+// threshold (0: none).
 extern "C" int kvb_sdpa_fwd_ex(const void* q, const void* k, const void* v, const int32_t* token_pos, void* out, float* lse,
                                 float* weights, void* scratch, int B, int H, int G, int q_len, int kv_len, int head_size,
-                                long long k_sb, long long k_sg, long long tp_sb, long long tp_sg, float scale, int input_pos,
-                                int window, float softcap, int* status, void* stream);
+                                long long q_sb, long long q_sh, long long k_sb, long long k_sg, long long tp_sb, long long tp_sg,
+                                float scale, int input_pos, int window, float softcap, int* status, void* stream);
 
 extern "C" int kvb_sdpa_fwd(const void* q, const void* k, const void* v, const int32_t* token_pos, void* out, float* lse,
                              float* weights, void* scratch, int B, int H, int G, int q_len, int kv_len, long long k_sb,
                              long long k_sg, long long tp_sb, long long tp_sg, float scale, int input_pos, int* status,
                              void* stream) {
-  return kvb_sdpa_fwd_ex(q, k, v, token_pos, out, lse, weights, scratch, B, H, G, q_len, kv_len, 128, k_sb, k_sg, tp_sb, tp_sg,
-                         scale, input_pos, 0, 0.f, status, stream);
+  return kvb_sdpa_fwd_ex(q, k, v, token_pos, out, lse, weights, scratch, B, H, G, q_len, kv_len, 128, 0, 0, k_sb, k_sg, tp_sb,
+                         tp_sg, scale, input_pos, 0, 0.f, status, stream);
 }
 
 extern "C" int kvb_sdpa_fwd_ex(const void* q, const void* k, const void* v, const int32_t* token_pos, void* out, float* lse,
                                 float* weights, void* scratch, int B, int H, int G, int q_len, int kv_len, int head_size,
-                                long long k_sb, long long k_sg, long long tp_sb, long long tp_sg, float scale, int input_pos,
-                                int window, float softcap, int* status, void* stream) {
+                                long long q_sb, long long q_sh, long long k_sb, long long k_sg, long long tp_sb, long long tp_sg,
+                                float scale, int input_pos, int window, float softcap, int* status, void* stream) {
   using namespace kvb;
   if (window < 0 || softcap < 0.f || (softcap > 0.f && scale <= 0.f)) return KVB_ERR_ARG;
   if (head_size != 128 && head_size != 64) return KVB_ERR_UNSUPPORTED;
+  if (q_sh == 0) q_sh = (long long)q_len * head_size;
+  if (q_sb == 0) q_sb = (long long)H * q_sh;
+  if ((q_sb % 8) || (q_sh % 8) || q_sh < (long long)q_len * head_size) return KVB_ERR_ALIGN;
   if (B <= 0 || H <= 0 || G <= 0 || q_len <= 0 || kv_len <= 0 || H % G) return KVB_ERR_ARG;
   const int gs = H / G;
   if (gs > 128) return KVB_ERR_UNSUPPORTED;
@@ -1220,8 +1225,7 @@ extern "C" int kvb_sdpa_fwd_ex(const void* q, const void* k, const void* v, cons
   int rc;
   // Q (B,H,T,D) read position-major: dims (D, H, T, B) with strides (T·D, D, H·T·D); box = 64 x gs x npos
   const uint64_t hd = (uint64_t)head_size;
-  if ((rc = f2_make_tmap(&tmQ, q, hd, H, q_len, B, (uint64_t)q_len * hd, hd, (uint64_t)H * q_len * hd, 64, gs, p.npos)))
-    return rc;
+  if ((rc = f2_make_tmap(&tmQ, q, hd, H, q_len, B, (uint64_t)q_sh, hd, (uint64_t)q_sb, 64, gs, p.npos))) return rc;
   // K, V (B,G,L,D) with strides: dims (D, L, G, B); box = 64 x 128 x 1
   if ((rc = f2_make_tmap(&tmK, k, hd, kv_len, G, B, hd, k_sg, k_sb, 64, F2_T, 1))) return rc;
   if ((rc = f2_make_tmap(&tmV, v, hd, kv_len, G, B, hd, k_sg, k_sb, 64, F2_T, 1))) return rc;

@@ -100,10 +100,22 @@ class LoRALinear(nn.Module):
         pretrained = self.linear(x)
         if self.r == 0 or self.merged:
             return pretrained
-        lora = self._lora_branch(x)
-        if self.rms_norm is not None:
-            lora = self.rms_norm(lora)
-        return pretrained + lora
+        if self.rms_norm is None:
+            # pretrained + scaling · (x A^T) B^T as the epilogue of the second small product: one pass over the output
+            # instead of three (product, scaling, sum)
+            return _add_low_rank(pretrained, F.linear(self.lora_dropout(x), self.lora_A), self.lora_B, self.scaling)
+        return pretrained + self.rms_norm(self._lora_branch(x))
+
+
+def _add_low_rank(pretrained: torch.Tensor, after_a: torch.Tensor, b: torch.Tensor, scaling: float) -> torch.Tensor:
+    """``pretrained + scaling · after_a @ b^T`` with the sum and the scaling in the epilogue of the product, written over
+    ``pretrained`` (the fresh output of the frozen linear, which nothing else holds and whose backward does not need it;
+    out of place the library would first copy it)."""
+    if not pretrained.is_contiguous():
+        return torch.addmm(pretrained.reshape(-1, pretrained.shape[-1]), after_a.reshape(-1, after_a.shape[-1]), b.t(),
+                           alpha=scaling).view(pretrained.shape)
+    pretrained.view(-1, pretrained.shape[-1]).addmm_(after_a.reshape(-1, after_a.shape[-1]), b.t(), alpha=scaling)
+    return pretrained
 
 
 class LoRAQKVLinear(LoRALinear):
@@ -166,14 +178,24 @@ class LoRAQKVLinear(LoRALinear):
         pieces = [F.linear(after_a[..., a_rows], self.lora_B[b_rows]) for _, _, a_rows, b_rows in self._parts()]
         return self.zero_pad(torch.cat(pieces, dim=-1)) * self.scaling
 
+    def _b_blocks(self) -> torch.Tensor:
+        """``(out_features, r · n_enabled)``: B of every enabled part on its output rows and its rank columns, zeros
+        elsewhere, so that one product serves all parts (and leaves the outputs of disabled parts alone)."""
+        parts = list(self._parts())
+        if len(parts) == 1 and parts[0][1] == self.linear.out_features:
+            return self.lora_B
+        blocks = self.lora_B.new_zeros(self.linear.out_features, self.lora_A.shape[0])
+        for out_off, size, a_rows, b_rows in parts:
+            blocks[out_off : out_off + size, a_rows] = self.lora_B[b_rows]
+        return blocks
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         pretrained = self.linear(x)
         if self.r == 0 or not any(self.enable_lora) or self.merged:
             return pretrained
-        lora = self._lora_branch(x)
-        if self.rms_norm is not None:
-            lora = self.rms_norm(lora)
-        return pretrained + lora
+        if self.rms_norm is None:
+            return _add_low_rank(pretrained, F.linear(self.lora_dropout(x), self.lora_A), self._b_blocks(), self.scaling)
+        return pretrained + self.rms_norm(self._lora_branch(x))
 
 
 # ---------------------------------------------------------------------- DoRA

@@ -520,7 +520,7 @@ def sdpa_fwd(query, key, value, scale, input_pos, token_pos=None, return_weights
     become ``cap · tanh(score / cap)`` (both inside the kernels)."""
     B, H, T, D = query.shape
     G, L = key.shape[1], key.shape[2]
-    query = query.contiguous()
+    query = _rows_in_place(query)
     if key.stride(3) != 1 or key.stride(2) != D or key.stride() != value.stride():
         key, value = key.contiguous(), value.contiguous()
     token_pos = _norm_token_pos(token_pos, B, G, L)
@@ -535,13 +535,24 @@ def sdpa_fwd(query, key, value, scale, input_pos, token_pos=None, return_weights
     scratch = torch.empty(nbytes // 4, dtype=torch.int32, device=dev)
     st = status_word(dev)
     _check(lib().kvb_sdpa_fwd_ex(_p(query), _p(key), _p(value), _p(token_pos), _p(out), _p(lse), _p(weights), _p(scratch), B, H, G, T, L,
-                                  int(D), _ll(key.stride(0)), _ll(key.stride(1)),
+                                  int(D), _ll(query.stride(0)), _ll(query.stride(1)), _ll(key.stride(0)), _ll(key.stride(1)),
                                   _ll(token_pos.stride(0) if token_pos is not None else 0),
                                   _ll(token_pos.stride(1) if token_pos is not None else 0),
                                   ctypes.c_float(scale), int(input_pos), int(sliding_window or 0), ctypes.c_float(softcap or 0.0),
                                   _p(st), _stream(query)), "sdpa_fwd")
     _count(3 if return_weights else 2)
     return out, weights, lse
+
+
+def _rows_in_place(query: torch.Tensor) -> torch.Tensor:
+    """``query (B,H,T,D)`` as the attention kernels read it: rows of a head ``D`` apart, head and batch strides free
+    (multiples of 8 elements), so that a slice of positions of a longer tensor is not copied; anything else is made
+    contiguous."""
+    D = query.shape[3]
+    if (query.stride(3) == 1 and query.stride(2) == D and query.stride(1) % 8 == 0 and query.stride(0) % 8 == 0
+            and query.stride(1) >= query.shape[2] * D and query.data_ptr() % 16 == 0):
+        return query
+    return query.contiguous()
 
 
 def _norm_token_pos(token_pos, B, G, L):
@@ -566,7 +577,7 @@ def sdpa_bwd(grad_out, query, key, value, out, lse, scale, input_pos, token_pos=
     G, L = key.shape[1], key.shape[2]
     dev = query.device
     lib().kvb_sdpa_bwd_scratch_bytes.restype = ctypes.c_longlong
-    query = query.contiguous()
+    query = _rows_in_place(query)
     grad_out = grad_out.contiguous()
     out = out.contiguous()
     if key.stride(3) != 1 or key.stride(2) != D or key.stride() != value.stride():
@@ -583,7 +594,8 @@ def sdpa_bwd(grad_out, query, key, value, out, lse, scale, input_pos, token_pos=
     scratch = torch.empty(nbytes // 4, dtype=torch.int32, device=dev)
     st = status_word(dev)
     _check(lib().kvb_sdpa_bwd_ex(_p(query), _p(key), _p(value), _p(token_pos), _p(out), _p(grad_out), _p(lse.contiguous()), _p(dq),
-                                 _p(dk_accum), _p(dv_accum), _p(scratch), B, H, G, T, L, int(D), _ll(key.stride(0)), _ll(key.stride(1)),
+                                 _p(dk_accum), _p(dv_accum), _p(scratch), B, H, G, T, L, int(D), _ll(query.stride(0)), _ll(query.stride(1)),
+                                 _ll(key.stride(0)), _ll(key.stride(1)),
                                  _ll(token_pos.stride(0) if token_pos is not None else 0),
                                  _ll(token_pos.stride(1) if token_pos is not None else 0),
                                  _ll(dk_accum.stride(0)), _ll(dk_accum.stride(1)), ctypes.c_float(scale), int(input_pos),

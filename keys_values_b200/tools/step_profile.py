@@ -22,6 +22,7 @@ def main():
     ap.add_argument("--cache-length", type=int, default=16384)
     ap.add_argument("--chunk-size", type=int, default=1024)
     ap.add_argument("--top", type=int, default=30)
+    ap.add_argument("--ops", action="store_true", help="a second table: device time per framework operator (aten::* and the native ops)")
     args = ap.parse_args()
     from torch.profiler import ProfilerActivity, profile
 
@@ -55,6 +56,16 @@ def main():
         print(f"{100 * t / total:6.1f}% {c:7d}  {k[:120]}")
     rest = sum(r[0] for r in rows[args.top:])
     print(f"{100 * rest / total:6.1f}% {sum(r[1] for r in rows[args.top:]):7d}  ({len(rows) - args.top} more kernels)")
+    if args.ops:
+        # which framework operators launch the small kernels: one more step with the host side recorded as well
+        with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA], record_shapes=True) as prof:
+            training_step(setup, ids, tg)
+            torch.cuda.synchronize(dev)
+        ops = sorted(((e.self_device_time_total, e.count, e.key, str(e.input_shapes)[:90]) for e in prof.key_averages(group_by_input_shape=True)
+                      if e.self_device_time_total > 0 and e.key.startswith("aten::")), reverse=True)
+        print(f"{'share':>7} {'calls':>7}  operator (input shapes)")
+        for t, c, k, shp in ops[: args.top]:
+            print(f"{100 * t / total:6.1f}% {c:7d}  {k} {shp}")
 
 
 if __name__ == "__main__":

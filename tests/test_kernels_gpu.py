@@ -306,6 +306,30 @@ def test_sdpa_head_size_64(B, H, G, T, L, mode, window, softcap):
     _sdpa_case(B, H, G, T, L, 3 * L if mode == "perm" else L - T, mode, window=window, softcap=softcap, D=64)
 
 
+@pytest.mark.parametrize("D", [128, 64])
+def test_sdpa_reads_a_slice_of_positions_in_place(D):
+    """The queries of a chunk are a slice of the cell's (B,H,T',D) tensor: forward and backward read it through the
+    head and batch strides (no copy) and give what the contiguous copy gives, bit for bit."""
+    B, H, G, T, L, T_cell = 2, 8, 2, 200, 1000, 700
+    q_cell = torch.randn(B, H, T_cell, D, device=DEV, dtype=torch.bfloat16)
+    q = q_cell[:, :, 300:300 + T]
+    assert not q.is_contiguous()
+    k = torch.randn(B, G, L, D, device=DEV, dtype=torch.bfloat16)
+    v = torch.randn(B, G, L, D, device=DEV, dtype=torch.bfloat16)
+    go = torch.randn(B, T, H * D, device=DEV, dtype=torch.bfloat16)
+    scale, ip = 1.0 / math.sqrt(D), L - T
+    res = []
+    for qq in (q, q.contiguous()):
+        out, w, lse = _cuda().sdpa_fwd(qq, k, v, scale, ip, None, True)
+        dq, dk, dv = _cuda().sdpa_bwd(go, qq, k, v, out, lse, scale, ip, None)
+        res.append((out, w, lse, dq, dk, dv))
+    _cuda().check_status(DEV)
+    for a, b in zip(*res):
+        assert torch.equal(a, b)
+    out_r, w_r, _ = ref.sdpa(q, k, v, scale, ip, None, True, return_lse=True)
+    torch.testing.assert_close(res[0][0].float(), out_r.float(), atol=2e-2, rtol=2e-2)
+
+
 def test_sdpa_is_deterministic():
     """Outputs, normalisers and the summed weights (which drive the eviction decisions) are bit-identical run to run."""
     D, B, H, G, T, L = 128, 1, 32, 8, 512, 4096  # 64 CTAs: split over the KV axis, partials merged in a fixed order
