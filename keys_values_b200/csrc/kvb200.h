@@ -60,6 +60,11 @@ int kvb_dequantize_rows(const uint8_t* q, const float* scale, const int32_t* zp,
 int kvb_cache_write(void* k_buf, void* v_buf, int32_t* token_pos, const int32_t* slots, const void* key, const void* value,
                     uint8_t* qk, float* sk, int32_t* zk, uint8_t* qv, float* sv, int32_t* zv, int B, int G, int n, int D, int C,
                     long long slot_sb, long long slot_sg, int input_pos, int bits, int dtype, int* status, void* stream);
+// the same with batch and group strides of key / value in elements (rows D apart)
+int kvb_cache_write_strided(void* k_buf, void* v_buf, int32_t* token_pos, const int32_t* slots, const void* key, const void* value,
+                            uint8_t* qk, float* sk, int32_t* zk, uint8_t* qv, float* sv, int32_t* zv, int B, int G, int n, int D,
+                            int C, long long slot_sb, long long slot_sg, long long kv_sb, long long kv_sg, int input_pos, int bits,
+                            int dtype, int* status, void* stream);
 
 // Device word that overrides the host ``input_pos`` of kvb_cache_write / kvb_h2o_update while set
 // (NULL clears it): lets a captured decode step be replayed at later positions.

@@ -143,8 +143,8 @@ cache_write128_kernel(__nv_bfloat16* __restrict__ k_buf, __nv_bfloat16* __restri
                       const int32_t* __restrict__ slots, const __nv_bfloat16* __restrict__ key,
                       const __nv_bfloat16* __restrict__ value, uint8_t* __restrict__ qk, float* __restrict__ sk,
                       int32_t* __restrict__ zk, uint8_t* __restrict__ qv, float* __restrict__ sv, int32_t* __restrict__ zv, int B,
-                      int G, int n, int C, long long slot_sb, long long slot_sg, int input_pos, const int* __restrict__ pos_ptr, int bits,
-                      int* status) {
+                      int G, int n, int C, long long slot_sb, long long slot_sg, long long kv_sb, long long kv_sg, int input_pos,
+                      const int* __restrict__ pos_ptr, int bits, int* status) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long row = (long long)blockIdx.x * Q_WARPS + warp;
   if (row >= (long long)B * G * n) return;
@@ -161,8 +161,9 @@ cache_write128_kernel(__nv_bfloat16* __restrict__ k_buf, __nv_bfloat16* __restri
   const int Dq = bits == 8 ? 128 : 64;
   float kx[4], vx[4];
   uint2 kraw, vraw;
-  q128_load(key + row * 128, lane, kx, kraw);
-  q128_load(value + row * 128, lane, vx, vraw);
+  const long long src = b * kv_sb + g * kv_sg + (long long)i * 128;  // key / value (B,G,n,128) with batch and group strides
+  q128_load(key + src, lane, kx, kraw);
+  q128_load(value + src, lane, vx, vraw);
   if (lane == 0) token_pos[dst_row] = input_pos + i;
   if (k_buf) *reinterpret_cast<uint2*>(k_buf + dst_row * 128 + 4 * lane) = kraw;
   if (v_buf) *reinterpret_cast<uint2*>(v_buf + dst_row * 128 + 4 * lane) = vraw;
@@ -290,8 +291,8 @@ __global__ void cache_write_kernel(T* __restrict__ k_buf, T* __restrict__ v_buf,
                                    const int32_t* __restrict__ slots, const T* __restrict__ key, const T* __restrict__ value,
                                    uint8_t* __restrict__ qk, float* __restrict__ sk, int32_t* __restrict__ zk,
                                    uint8_t* __restrict__ qv, float* __restrict__ sv, int32_t* __restrict__ zv, int B, int G, int n,
-                                   int D, int C, long long slot_sb, long long slot_sg, int input_pos, const int* __restrict__ pos_ptr,
-                                   int bits, int* status) {
+                                   int D, int C, long long slot_sb, long long slot_sg, long long kv_sb, long long kv_sg, int input_pos,
+                                   const int* __restrict__ pos_ptr, int bits, int* status) {
   extern __shared__ float sm[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float* xs = sm + warp * D;
@@ -308,8 +309,8 @@ __global__ void cache_write_kernel(T* __restrict__ k_buf, T* __restrict__ v_buf,
   }
   const long long bg = (long long)b * G + g;
   const long long dst_row = bg * C + slot;
-  const T* kr = key + row * D;
-  const T* vr = value + row * D;
+  const T* kr = key + b * kv_sb + g * kv_sg + (long long)i * D;
+  const T* vr = value + b * kv_sb + g * kv_sg + (long long)i * D;
   if (lane == 0) token_pos[dst_row] = input_pos + i;
   const int Dq = bits == 8 ? D : D / 2;
   // keys
@@ -386,21 +387,32 @@ extern "C" int kvb_cache_write(void* k_buf, void* v_buf, int32_t* token_pos, con
                                const void* value, uint8_t* qk, float* sk, int32_t* zk, uint8_t* qv, float* sv, int32_t* zv, int B,
                                int G, int n, int D, int C, long long slot_sb, long long slot_sg, int input_pos, int bits,
                                int dtype, int* status, void* stream) {
+  return kvb_cache_write_strided(k_buf, v_buf, token_pos, slots, key, value, qk, sk, zk, qv, sv, zv, B, G, n, D, C, slot_sb, slot_sg,
+                                 (long long)G * n * D, (long long)n * D, input_pos, bits, dtype, status, stream);
+}
+
+// key / value (B,G,n,D) with batch and group strides kv_sb, kv_sg in elements (rows D apart): a slice of positions of a
+// longer (B,G,T,D) tensor is written without a copy.
+extern "C" int kvb_cache_write_strided(void* k_buf, void* v_buf, int32_t* token_pos, const int32_t* slots, const void* key,
+                                       const void* value, uint8_t* qk, float* sk, int32_t* zk, uint8_t* qv, float* sv, int32_t* zv,
+                                       int B, int G, int n, int D, int C, long long slot_sb, long long slot_sg, long long kv_sb,
+                                       long long kv_sg, int input_pos, int bits, int dtype, int* status, void* stream) {
   if (B <= 0 || G <= 0 || n <= 0 || D <= 0 || C <= 0) return KVB_ERR_ARG;
   if (qk && bits != 4 && bits != 8) return KVB_ERR_ARG;
   if ((size_t)Q_WARPS * D * 4 > 48 * 1024) return KVB_ERR_TOO_LARGE;
   const long long rows = (long long)B * G * n;
   const unsigned grid = (unsigned)((rows + Q_WARPS - 1) / Q_WARPS);
   auto al = [](const void* p, uintptr_t m) { return (reinterpret_cast<uintptr_t>(p) & m) == 0; };
-  if (dtype == 1 && D == 128 && al(key, 7) && al(value, 7) && al(k_buf, 7) && al(v_buf, 7) && al(qk, 3) && al(qv, 3)) {
+  if (dtype == 1 && D == 128 && al(key, 7) && al(value, 7) && al(k_buf, 7) && al(v_buf, 7) && al(qk, 3) && al(qv, 3) &&
+      kv_sb % 4 == 0 && kv_sg % 4 == 0) {
     cache_write128_kernel<<<grid, Q_WARPS * 32, 0, (cudaStream_t)stream>>>(
         (__nv_bfloat16*)k_buf, (__nv_bfloat16*)v_buf, token_pos, slots, (const __nv_bfloat16*)key, (const __nv_bfloat16*)value, qk,
-        sk, zk, qv, sv, zv, B, G, n, C, slot_sb, slot_sg, input_pos, g_position_source, bits ? bits : 8, status);
+        sk, zk, qv, sv, zv, B, G, n, C, slot_sb, slot_sg, kv_sb, kv_sg, input_pos, g_position_source, bits ? bits : 8, status);
     return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
   }
   KVB_DISPATCH_DTYPE(dtype, (cache_write_kernel<T><<<grid, Q_WARPS * 32, (size_t)Q_WARPS * D * 4, (cudaStream_t)stream>>>(
                                 (T*)k_buf, (T*)v_buf, token_pos, slots, (const T*)key, (const T*)value, qk, sk, zk, qv, sv, zv, B,
-                                G, n, D, C, slot_sb, slot_sg, input_pos, g_position_source, bits ? bits : 8, status)));
+                                G, n, D, C, slot_sb, slot_sg, kv_sb, kv_sg, input_pos, g_position_source, bits ? bits : 8, status)));
   return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
 }
 

@@ -327,15 +327,19 @@ def _cache_write(k_buf, v_buf, token_pos, slots, key, value, input_pos, qk, sk, 
             raise NativeError("cache_write: cache buffers must be contiguous")
     if k_buf is not None and k_buf.dtype != key.dtype:
         key, value = key.to(k_buf.dtype), value.to(k_buf.dtype)
-    key, value = key.contiguous(), value.contiguous()
+    # rows of a (batch, group) D apart, the other strides free: a slice of positions of a longer tensor is read in place
+    if not (key.stride(3) == 1 and key.stride(2) == D and key.stride() == value.stride()
+            and key.stride(0) % 8 == 0 and key.stride(1) % 8 == 0):
+        key, value = key.contiguous(), value.contiguous()
     if slots.dtype != torch.int32:
         slots = slots.to(torch.int32)
     if slots.stride(2) != 1:
         slots = slots.contiguous()
     st = status_word(key.device)
-    _check(lib().kvb_cache_write(_p(k_buf), _p(v_buf), _p(token_pos), _p(slots), _p(key), _p(value), _p(qk), _p(sk), _p(zk),
-                                 _p(qv), _p(sv), _p(zv), B, G, n, D, C, _ll(slots.stride(0)), _ll(slots.stride(1)),
-                                 int(input_pos), int(bits), _code(key.dtype), _p(st), _stream(key)), "cache_write")
+    _check(lib().kvb_cache_write_strided(_p(k_buf), _p(v_buf), _p(token_pos), _p(slots), _p(key), _p(value), _p(qk), _p(sk), _p(zk),
+                                         _p(qv), _p(sv), _p(zv), B, G, n, D, C, _ll(slots.stride(0)), _ll(slots.stride(1)),
+                                         _ll(key.stride(0)), _ll(key.stride(1)), int(input_pos), int(bits), _code(key.dtype), _p(st),
+                                         _stream(key)), "cache_write")
     _count()
 
 

@@ -105,8 +105,9 @@ def test_quantize_roundtrip(bits, dtype):
     assert buf[:, :, 50:].abs().max().item() == 0
 
 
+@pytest.mark.parametrize("sliced", [False, True])
 @pytest.mark.parametrize("bits", [0, 8, 4])
-def test_cache_write(bits):
+def test_cache_write(bits, sliced):
     B, G, C, D, n = 2, 3, 40, 128, 7
     dt = torch.bfloat16
     kb = torch.randn(B, G, C, D, device=DEV, dtype=dt)
@@ -114,6 +115,10 @@ def test_cache_write(bits):
     tp = torch.zeros(B, G, C, device=DEV, dtype=torch.int32)
     slots = torch.stack([torch.stack([torch.randperm(C, device=DEV)[:n] for _ in range(G)]) for _ in range(B)]).to(torch.int32)
     key, val = torch.randn(B, G, n, D, device=DEV, dtype=dt), torch.randn(B, G, n, D, device=DEV, dtype=dt)
+    if sliced:  # the rows of a chunk inside the cell's longer tensor: read through the batch and group strides, no copy
+        key = torch.randn(B, G, 3 * n, D, device=DEV, dtype=dt)[:, :, n:2 * n]
+        val = torch.randn(B, G, 3 * n, D, device=DEV, dtype=dt)[:, :, n:2 * n]
+        assert not key.is_contiguous()
     kb_r, vb_r, tp_r = kb.clone(), vb.clone(), tp.clone()
     ref.cache_write(kb_r, vb_r, tp_r, slots, key, val, 100)
     if bits == 0:
