@@ -254,7 +254,8 @@ __device__ __forceinline__ void decb_frag(const uint32_t (&wa)[DecRaw<BITS>::WB]
 // exponentials (handed from the score layout to the P^T operand layout through a warp-private patch
 // of shared memory) and the product with V follow without a block-wide barrier; the four warps
 // merge their (max, sum, O) once at the end.
-template <int BITS>
+// VAR: capped scores and / or a sliding window (a separate instantiation: the plain kernel keeps its registers)
+template <int BITS, bool VAR>
 __global__ void __launch_bounds__(DEC_THREADS)
 decode_partial_kernel(const DecParams p) {
   using ST = DecStage<BITS>;
@@ -392,12 +393,12 @@ decode_partial_kernel(const DecParams p) {
     }
     float s00 = p.scale * kslo * (d[0] - kzlo * qsum0), s01 = p.scale * kslo * (d[1] - kzlo * qsum1);
     float s10 = p.scale * kshi * (d[2] - kzhi * qsum0), s11 = p.scale * kshi * (d[3] - kzhi * qsum1);
-    if (p.softcap > 0.f) {
+    if (VAR && p.softcap > 0.f) {
       const float inv = 1.f / p.softcap;
       s00 = p.softcap * tanhf(s00 * inv); s01 = p.softcap * tanhf(s01 * inv);
       s10 = p.softcap * tanhf(s10 * inv); s11 = p.softcap * tanhf(s11 * inv);
     }
-    if (p.window > 0) {
+    if (VAR && p.window > 0) {
       // hidden slots keep the mark of "no slot" (their weight and their share of the output are zero)
       const int oldest = (p.pos_src ? *p.pos_src : p.query_pos) - p.window;
       const int32_t* tp = p.tok_pos + b * p.tp_sb + g * p.tp_sg + j0;
@@ -675,14 +676,23 @@ extern "C" int kvb_decode_attn_ex(const void* q, const void* kq, const void* vq,
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return KVB_ERR_CUDA;
   if (!attr_set[dev]) {
-    cudaFuncSetAttribute(decode_partial_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, dec_dyn_smem<16>());
-    cudaFuncSetAttribute(decode_partial_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, dec_dyn_smem<8>());
-    cudaFuncSetAttribute(decode_partial_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, dec_dyn_smem<4>());
+    cudaFuncSetAttribute(decode_partial_kernel<16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, dec_dyn_smem<16>());
+    cudaFuncSetAttribute(decode_partial_kernel<8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, dec_dyn_smem<8>());
+    cudaFuncSetAttribute(decode_partial_kernel<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, dec_dyn_smem<4>());
+    cudaFuncSetAttribute(decode_partial_kernel<16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, dec_dyn_smem<16>());
+    cudaFuncSetAttribute(decode_partial_kernel<8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, dec_dyn_smem<8>());
+    cudaFuncSetAttribute(decode_partial_kernel<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, dec_dyn_smem<4>());
     attr_set[dev] = true;
   }
-  if (bits == 16) decode_partial_kernel<16><<<grid, DEC_THREADS, dec_dyn_smem<16>(), s>>>(p);
-  else if (bits == 8) decode_partial_kernel<8><<<grid, DEC_THREADS, dec_dyn_smem<8>(), s>>>(p);
-  else decode_partial_kernel<4><<<grid, DEC_THREADS, dec_dyn_smem<4>(), s>>>(p);
+  if (softcap > 0.f || window > 0) {
+    if (bits == 16) decode_partial_kernel<16, true><<<grid, DEC_THREADS, dec_dyn_smem<16>(), s>>>(p);
+    else if (bits == 8) decode_partial_kernel<8, true><<<grid, DEC_THREADS, dec_dyn_smem<8>(), s>>>(p);
+    else decode_partial_kernel<4, true><<<grid, DEC_THREADS, dec_dyn_smem<4>(), s>>>(p);
+  } else {
+    if (bits == 16) decode_partial_kernel<16, false><<<grid, DEC_THREADS, dec_dyn_smem<16>(), s>>>(p);
+    else if (bits == 8) decode_partial_kernel<8, false><<<grid, DEC_THREADS, dec_dyn_smem<8>(), s>>>(p);
+    else decode_partial_kernel<4, false><<<grid, DEC_THREADS, dec_dyn_smem<4>(), s>>>(p);
+  }
   decode_merge_kernel<<<B * H, DEC_D, 0, s>>>(p);
   if (weights) {
     dim3 g2((L + 255) / 256, B * G);
