@@ -97,25 +97,24 @@ class LoRALinear(nn.Module):
         return F.linear(F.linear(self.lora_dropout(x), self.lora_A), self.lora_B) * self.scaling
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        pretrained = self.linear(x)
         if self.r == 0 or self.merged:
-            return pretrained
+            return self.linear(x)
         if self.rms_norm is None:
             # pretrained + scaling · (x A^T) B^T as the epilogue of the second small product: one pass over the output
             # instead of three (product, scaling, sum)
-            return _add_low_rank(pretrained, F.linear(self.lora_dropout(x), self.lora_A), self.lora_B, self.scaling)
-        return pretrained + self.rms_norm(self._lora_branch(x))
+            return _linear_plus_low_rank(self.linear, x, self.lora_dropout, self.lora_A, self.lora_B, self.scaling)
+        return self.linear(x) + self.rms_norm(self._lora_branch(x))
 
 
-def _add_low_rank(pretrained: torch.Tensor, after_a: torch.Tensor, b: torch.Tensor, scaling: float) -> torch.Tensor:
-    """``pretrained + scaling · after_a @ b^T`` with the sum and the scaling in the epilogue of the product, written over
-    ``pretrained`` (the fresh output of the frozen linear, which nothing else holds and whose backward does not need it;
-    out of place the library would first copy it)."""
-    if not pretrained.is_contiguous():
-        return torch.addmm(pretrained.reshape(-1, pretrained.shape[-1]), after_a.reshape(-1, after_a.shape[-1]), b.t(),
-                           alpha=scaling).view(pretrained.shape)
-    pretrained.view(-1, pretrained.shape[-1]).addmm_(after_a.reshape(-1, after_a.shape[-1]), b.t(), alpha=scaling)
-    return pretrained
+def _linear_plus_low_rank(linear: nn.Linear, x: torch.Tensor, dropout, a: torch.Tensor, b: torch.Tensor, scaling: float) -> torch.Tensor:
+    """``linear(x) + scaling · (dropout(x) a^T) b^T`` with the sum and the scaling in the epilogue of the second small
+    product, written over the fresh output of the frozen linear (which nothing else holds and whose backward does not
+    need it). Everything runs on the rows as a 2-d matrix and the result is viewed back: an in-place update through a
+    view of a 3-d output would cost three copies of the output in the backward pass."""
+    rows = x.reshape(-1, x.shape[-1])
+    out = linear(rows)
+    out.addmm_(F.linear(dropout(rows), a), b.t(), alpha=scaling)
+    return out.view(*x.shape[:-1], out.shape[-1])
 
 
 class LoRAQKVLinear(LoRALinear):
@@ -190,12 +189,11 @@ class LoRAQKVLinear(LoRALinear):
         return blocks
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        pretrained = self.linear(x)
         if self.r == 0 or not any(self.enable_lora) or self.merged:
-            return pretrained
+            return self.linear(x)
         if self.rms_norm is None:
-            return _add_low_rank(pretrained, F.linear(self.lora_dropout(x), self.lora_A), self._b_blocks(), self.scaling)
-        return pretrained + self.rms_norm(self._lora_branch(x))
+            return _linear_plus_low_rank(self.linear, x, self.lora_dropout, self.lora_A, self._b_blocks(), self.scaling)
+        return self.linear(x) + self.rms_norm(self._lora_branch(x))
 
 
 # ---------------------------------------------------------------------- DoRA
