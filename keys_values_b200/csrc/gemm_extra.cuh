@@ -18,7 +18,7 @@ namespace kvb {
 //     that copies remote shards into LOCAL staging memory); the TMA producer waits for the
 //     chunk's flag before it loads a tile of that chunk. The copy runs in the first
 //     `ag_copy_ctas` CTAs of the same grid, which pull the peers' shards with plain loads.
-// No TMA load ever targets peer memory and nothing uses cluster multicast.
+// No TMA load ever targets peer memory and no load uses cluster multicast.
 struct GemmExtra {
   // reduce-scatter epilogue
   int rs_world, rs_rank, rows_per_rank;
