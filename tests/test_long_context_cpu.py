@@ -224,6 +224,32 @@ def test_lora_merge_and_state_dict_compat():
     torch.testing.assert_close(before, after, atol=1e-5, rtol=1e-4)
 
 
+@pytest.mark.parametrize("enable", [(True, False, True), (False, True, False), (True, True, True)])
+def test_lora_qkv_parts_forward_and_gradients_match_the_definition(enable):
+    """The fused form (sum and scaling in the epilogue of the low-rank product, one block matrix for the enabled parts)
+    against the definition: linear(x) + scaling · x (B A)^T with the update of disabled parts zero; gradients too."""
+    torch.manual_seed(0)
+    lin = lora_mod.LoRAQKVLinear(48, head_size=8, n_head=4, n_query_groups=2, r=4, lora_alpha=8, enable_lora=enable, bias=True)
+    torch.nn.init.normal_(lin.lora_B, std=0.2)
+    x = torch.randn(2, 7, 48, requires_grad=True)
+    y = lin(x)
+    y.square().sum().backward()
+    got = (y.detach().clone(), x.grad.clone(), lin.lora_A.grad.clone(), lin.lora_B.grad.clone())
+    x.grad = lin.lora_A.grad = lin.lora_B.grad = None
+    y_def = torch.nn.functional.linear(x, lin.linear.weight + lin.get_lora_AB(), lin.linear.bias)
+    y_def.square().sum().backward()
+    want = (y_def.detach(), x.grad, lin.lora_A.grad, lin.lora_B.grad)
+    for a, b in zip(got, want):
+        torch.testing.assert_close(a, b, atol=1e-4, rtol=1e-4)
+    # the outputs of a disabled part are those of the frozen linear alone
+    base = torch.nn.functional.linear(x, lin.linear.weight, lin.linear.bias)
+    off = 0
+    for size, on in zip((32, 16, 16), enable):
+        if not on:
+            torch.testing.assert_close(y[..., off:off + size], base[..., off:off + size])
+        off += size
+
+
 def test_dora_forward_matches_definition():
     torch.manual_seed(0)
     lin = lora_mod.DoRALinear(16, 12, r=4, lora_alpha=8)
