@@ -809,34 +809,30 @@ __global__ void __launch_bounds__(256) flash_merge_kernel(const F2Params p) {
   const long long prow = ((long long)b * p.H + h) * p.T + tq;
   float mx = -INFINITY;
   for (int sidx = 0; sidx < p.n_split; ++sidx) mx = fmaxf(mx, p.part_lse2[sidx * stride + prow]);
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);  // HD = 64: x and y only (lane l holds features 2l, 2l+1)
+  constexpr int PER = HD / 32;  // features per lane: lane l holds features PER·l .. PER·l + PER − 1
+  float acc[PER];
+#pragma unroll
+  for (int e = 0; e < PER; ++e) acc[e] = 0.f;
   float total = 0.f;
   if (mx > -INFINITY) {
     for (int sidx = 0; sidx < p.n_split; ++sidx) {
       const float w = exp2f(p.part_lse2[sidx * stride + prow] - mx);
       if (w > 0.f) {
-        const float* src = p.part_o + (sidx * stride + prow) * HD;
-        if (HD == 128) {
-          const float4 o = *reinterpret_cast<const float4*>(src + 4 * lane);
-          acc.x += w * o.x; acc.y += w * o.y; acc.z += w * o.z; acc.w += w * o.w;
-        } else {
-          const float2 o = *reinterpret_cast<const float2*>(src + 2 * lane);
-          acc.x += w * o.x; acc.y += w * o.y;
+        const float2* src = reinterpret_cast<const float2*>(p.part_o + (sidx * stride + prow) * HD + PER * lane);
+#pragma unroll
+        for (int e = 0; e < PER / 2; ++e) {
+          const float2 o = src[e];
+          acc[2 * e] += w * o.x;
+          acc[2 * e + 1] += w * o.y;
         }
         total += w;
       }
     }
   }
   const float inv = total > 0.f ? 1.f / total : 0.f;
-  __nv_bfloat16* dst = p.out + (((long long)b * p.T + tq) * p.H + h) * HD;
-  if (HD == 128) {
-    uint2 v;
-    v.x = pack_bf16x2(acc.x * inv, acc.y * inv);
-    v.y = pack_bf16x2(acc.z * inv, acc.w * inv);
-    *reinterpret_cast<uint2*>(dst + 4 * lane) = v;
-  } else {
-    *reinterpret_cast<uint32_t*>(dst + 2 * lane) = pack_bf16x2(acc.x * inv, acc.y * inv);
-  }
+  uint32_t* dst = reinterpret_cast<uint32_t*>(p.out + (((long long)b * p.T + tq) * p.H + h) * HD + PER * lane);
+#pragma unroll
+  for (int e = 0; e < PER / 2; ++e) dst[e] = pack_bf16x2(acc[2 * e] * inv, acc[2 * e + 1] * inv);
   if (lane == 0) {
     const float lse2 = total > 0.f ? mx + log2f(total) : INFINITY;
     if (p.lse) p.lse[prow] = lse2 * 0.6931471805599453f;
@@ -844,20 +840,391 @@ __global__ void __launch_bounds__(256) flash_merge_kernel(const F2Params p) {
   }
 }
 
+// ------------------------------------------------------------------ head size 256
+// The flash sweep for head size 256 (Gemma-2 2b / 9b, Gemma-3 shapes). A query tile of 128 rows x 256 features and one
+// K and one V tile of 128 slots x 256 features are 64 KB each, and O is 256 TMEM columns, so a CTA has ONE query tile:
+//   shared memory: Q | K stage | V stage (64 KB each, four 64-feature chunks of [128 rows x 128 B]);
+//   TMEM: S0 [0,128) | S1 [128,256) | O [256,512). S is double buffered over the KV tiles of the same query tile: the
+//   QK MMAs of tile i + 1 (16 K-steps) run while the softmax warpgroup works on tile i; P aliases the first 64 columns
+//   of its S buffer and is the A operand of the PV MMAs (N = 256) from TMEM.
+// MMA order: QK(0), then per tile i: QK(i + 1), PV(i). O may still be accumulating PV(i - 1) when S(i) is complete, so a
+// softmax warp that has to rescale O first waits for that PV (the barrier that also frees the V stage).
+// Masks are taken element by element in every tile that needs one (no bias step); soft-capping rewrites every tile.
+constexpr int F3_HD = 256;
+constexpr int F3_TILE_BYTES = F2_T * F3_HD * 2;
+constexpr int F3_THREADS = 64 + 128;  // TMA warp, MMA warp, one softmax warpgroup
+struct F3Smem {
+  static constexpr int Q = 0;
+  static constexpr int K = Q + F3_TILE_BYTES;
+  static constexpr int V = K + F3_TILE_BYTES;
+  static constexpr int TF = V + F3_TILE_BYTES;
+  static constexpr int BAR = TF + F2_MAX_FLAG_TILES;
+  static constexpr int TOTAL = BAR + 256;
+};
+static_assert(F3Smem::TOTAL <= 232448, "shared memory of the head-size-256 flash kernel exceeds the limit of a CTA");
+
+__global__ void __launch_bounds__(F3_THREADS, 1)
+flash256_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const F2Params p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if (smem_u32(smem) & 1023u) {
+    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, STATUS_TIMEOUT_MISC);
+    return;
+  }
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + F3Smem::BAR);
+  uint64_t* q_full = bars + 0;
+  uint64_t* k_full = bars + 1;
+  uint64_t* v_full = bars + 2;
+  uint64_t* k_empty = bars + 3;
+  uint64_t* v_empty = bars + 4;   // PV of a tile is complete: the V stage is free and O is quiet
+  uint64_t* s_full = bars + 5;    // [2]
+  uint64_t* p_full = bars + 7;    // [2]
+  uint64_t* o_full = bars + 9;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint8_t* tflags = smem + F3Smem::TF;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = blockIdx.x % p.nQT;
+  const int g = (blockIdx.x / p.nQT) % p.G;
+  const int b = blockIdx.x / (p.nQT * p.G);
+  const int t0 = qt * p.npos;
+  const int qpos_min = p.input_pos + t0;
+  const int qpos_max = p.input_pos + min(t0 + p.npos, p.T) - 1;
+  const long long bg = (long long)b * p.G + g;
+  const int32_t* tmin = p.tile_min + bg * p.nT;
+  const int32_t* tmax = p.tile_max + bg * p.nT;
+  const int split = p.n_split > 1 ? (int)blockIdx.y : 0;
+  const int t_lo = p.n_split > 1 ? split * p.tiles_per_split : 0;
+  const int t_hi = p.n_split > 1 ? min(p.nT, t_lo + p.tiles_per_split) : p.nT;
+  const int lo_all = p.window > 0 ? qpos_min - p.window : INT_MIN;   // tokens at or below: outside every row's window
+  const int lo_some = p.window > 0 ? qpos_max - p.window : INT_MIN;  // ... outside some row's window
+  const bool soft = p.cap_pre != 0.f;
+  auto calc_bits = [&](int t) -> uint32_t {
+    if (t < t_lo || t >= t_hi) return 0u;
+    const int lo = tmin[t], hi = tmax[t];
+    const uint32_t act = (lo <= qpos_max) && (hi > lo_all);
+    const uint32_t msk = (hi > qpos_min) || (lo <= lo_some) || soft;
+    return act | (msk << 1);
+  };
+  for (int t = threadIdx.x; t < min(p.nT, F2_MAX_FLAG_TILES); t += F3_THREADS) tflags[t] = (uint8_t)calc_bits(t);
+  auto tile_bits = [&](int t) -> uint32_t { return t >= F2_MAX_FLAG_TILES ? calc_bits(t) : (uint32_t)tflags[t]; };
+  if (p.rows_used < F2_T) {
+    f2_zero_unused_rows(smem + F3Smem::Q, p.rows_used, threadIdx.x, F3_THREADS, F3_HD / 64);
+    fence_proxy_async_smem();
+  }
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    mbar_init(k_full, 1);
+    mbar_init(v_full, 1);
+    mbar_init(k_empty, 1);
+    mbar_init(v_empty, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], 4);
+    }
+    mbar_init(o_full, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  int n_active = 0;
+  for (int t = 0; t < p.nT; ++t) n_active += (int)(tile_bits(t) & 1u);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0 && n_active > 0) {
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      mbar_expect_tx(q_full, (uint32_t)p.rows_used * F3_HD * 2u);
+      for (int c = 0; c < 4; ++c) tma_load_4d(smem + F3Smem::Q + c * F2_CHUNK_BYTES, &tmQ, q_full, 64 * c, g * p.gs, t0, b);
+      bool ok = true;
+      int i = 0;
+      for (int t = 0; t < p.nT && ok; ++t) {
+        if (!(tile_bits(t) & 1u)) continue;
+        if (!(ok = mbar_wait_bounded(k_empty, (i & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_EMPTY))) break;
+        mbar_expect_tx(k_full, F3_TILE_BYTES);
+        for (int c = 0; c < 4; ++c) tma_load_4d(smem + F3Smem::K + c * F2_CHUNK_BYTES, &tmK, k_full, 64 * c, t * F2_T, g, b);
+        if (!(ok = mbar_wait_bounded(v_empty, (i & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_EMPTY))) break;
+        mbar_expect_tx(v_full, F3_TILE_BYTES);
+        for (int c = 0; c < 4; ++c) tma_load_4d(smem + F3Smem::V + c * F2_CHUNK_BYTES, &tmV, v_full, 64 * c, t * F2_T, g, b);
+        ++i;
+      }
+      if (!ok) {  // let copies in flight land before the CTA's shared memory is released
+        long long c0 = clock64();
+        while (clock64() - c0 < 2000000LL) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issuer
+    if (lane == 0 && n_active > 0) {
+      constexpr uint32_t idesc_qk = make_idesc_bf16(F2_T, F2_T, 0, 0);    // Q, K both K-major
+      constexpr uint32_t idesc_pv = make_idesc_bf16(F2_T, F3_HD, 0, 1);   // P K-major (TMEM), V MN-major, N = 256
+      const uint32_t q_addr = smem_u32(smem + F3Smem::Q), k_addr = smem_u32(smem + F3Smem::K), v_addr = smem_u32(smem + F3Smem::V);
+      auto issue_qk = [&](int buf) {
+#pragma unroll
+        for (int kk = 0; kk < F3_HD / 16; ++kk) {
+          const uint32_t off = (uint32_t)((kk >> 2) * F2_CHUNK_BYTES + (kk & 3) * 32);
+          umma_f16_ss(tmem_base + (uint32_t)(buf * F2_T), make_smem_desc_sw128(q_addr + off, 16, 1024),
+                      make_smem_desc_sw128(k_addr + off, 16, 1024), idesc_qk, kk != 0);
+        }
+        umma_commit(k_empty);
+        umma_commit(&s_full[buf]);
+      };
+      bool ok = mbar_wait_bounded(q_full, 0, abort_flag, p.status, STATUS_TIMEOUT_FULL);
+      if (ok) ok = mbar_wait_bounded(k_full, 0, abort_flag, p.status, STATUS_TIMEOUT_FULL);
+      if (ok) {
+        tc_fence_after();
+        issue_qk(0);
+      }
+      for (int i = 0; i < n_active && ok; ++i) {
+        if (i + 1 < n_active) {
+          if (!(ok = mbar_wait_bounded(k_full, (i + 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL))) break;
+          tc_fence_after();
+          issue_qk((i + 1) & 1);  // its buffer held P of tile i - 1, whose PV MMAs were issued before
+        }
+        if (!(ok = mbar_wait_bounded(v_full, i & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL))) break;
+        if (!(ok = mbar_wait_bounded(&p_full[i & 1], (i >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL))) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          // A = P from TMEM: 16 slots = 8 columns of packed bf16 pairs per step; B = V, MN-major: 16 slot rows per step
+          // (2048 B), the four 64-wide feature chunks LBO apart
+          umma_f16_ts(tmem_base + 256u, tmem_base + (uint32_t)((i & 1) * F2_T + 8 * kk),
+                      make_smem_desc_sw128(v_addr + (uint32_t)(kk * 16 * 128), F2_CHUNK_BYTES, 1024), idesc_pv,
+                      (i == 0 && kk == 0) ? 0u : 1u);
+        }
+        umma_commit(v_empty);
+      }
+      if (ok) umma_commit(o_full);
+    }
+  } else {
+    // ------------------------------------------------- softmax + epilogue warps (one warpgroup)
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const int pl = row / p.gs, hq = row % p.gs;
+    const int tq = t0 + pl;
+    const bool row_valid = row < p.rows_used && tq < p.T;
+    const int my_pos = p.input_pos + tq;
+    const int my_lo = p.window > 0 ? my_pos - p.window : INT_MIN;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tmem_O = tmem_base + 256u + lane_base;
+    const float c = p.scale_log2;
+    const float2 c2 = make_float2(c, c);
+    const int32_t* pos_row = p.pos + bg * p.nT * F2_T;
+    bool ok = n_active > 0;
+    float m_used = -1e30f, l = 0.f;
+    int i = 0;
+    for (int t = 0; t < p.nT && ok; ++t) {
+      const uint32_t tb = tile_bits(t);
+      if (!(tb & 1u)) continue;
+      const uint32_t tmem_S = tmem_base + (uint32_t)((i & 1) * F2_T) + lane_base;
+      if (!mbar_wait_bounded(&s_full[i & 1], (i >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      float a8[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) a8[u] = -INFINITY;
+      if (tb & 2u) {
+        // element by element: capped scores, causal and window masks; the row maximum in the same pass
+        const int4* pp = reinterpret_cast<const int4*>(pos_row + (long long)t * F2_T);
+#pragma unroll 1
+        for (int c0 = 0; c0 < F2_T; c0 += 32) {
+          uint32_t x[32];
+          tmem_ld_32x32b_x32(tmem_S + (uint32_t)c0, x);
+          tmem_ld_wait();
+          if (soft) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) x[e] = __float_as_uint(f2_softcap(__uint_as_float(x[e]), p.cap_pre, p.cap_post));
+          }
+#pragma unroll
+          for (int e = 0; e < 32; e += 4) {
+            const int4 v = __ldg(pp + ((c0 + e) >> 2));
+            if (v.x > my_pos || v.x <= my_lo) x[e] = 0xff800000u;
+            if (v.y > my_pos || v.y <= my_lo) x[e + 1] = 0xff800000u;
+            if (v.z > my_pos || v.z <= my_lo) x[e + 2] = 0xff800000u;
+            if (v.w > my_pos || v.w <= my_lo) x[e + 3] = 0xff800000u;
+          }
+#pragma unroll
+          for (int e = 0; e < 32; e += 16) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) a8[u] = fmax3(a8[u], __uint_as_float(x[e + 2 * u]), __uint_as_float(x[e + 2 * u + 1]));
+          }
+          tmem_st_32x32b_x16(tmem_S + (uint32_t)c0, x);
+          tmem_st_32x32b_x16(tmem_S + (uint32_t)(c0 + 16), x + 16);
+        }
+        tmem_st_wait();
+      } else {
+        uint32_t x[2][32];
+        tmem_ld_32x32b_x32(tmem_S, x[0]);
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          tmem_ld_wait();
+          if (w < 3) tmem_ld_32x32b_x32(tmem_S + (uint32_t)(32 * (w + 1)), x[(w + 1) & 1]);
+#pragma unroll
+          for (int e = 0; e < 32; e += 16) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              a8[u] = fmax3(a8[u], __uint_as_float(x[w & 1][e + 2 * u]), __uint_as_float(x[w & 1][e + 2 * u + 1]));
+          }
+        }
+      }
+      const float m_tile = fmax3(fmax3(a8[0], a8[1], a8[2]), fmax3(a8[3], a8[4], a8[5]), fmaxf(a8[6], a8[7])) * c;
+      const bool raise = m_tile > m_used + F2_RESCALE_STEP;
+      const float m_new = raise ? m_tile : m_used;
+      if (i > 0 && __any_sync(0xffffffffu, raise)) {
+        // O may still be accumulating the PV MMAs of the previous tile: wait for them, then rescale the rows
+        if (!mbar_wait_bounded(v_empty, (i - 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const float f = raise ? f2_exp2(m_used - m_new) : 1.f;
+        l *= f;
+#pragma unroll 1
+        for (int c0 = 0; c0 < F3_HD; c0 += 32) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(tmem_O + (uint32_t)c0, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * f);
+          tmem_st_32x32b_x16(tmem_O + (uint32_t)c0, o);
+          tmem_st_32x32b_x16(tmem_O + (uint32_t)(c0 + 16), o + 16);
+        }
+      }
+      m_used = m_new;
+      const float2 neg_m2 = make_float2(-m_used, -m_used);
+      float2 s0 = make_float2(0.f, 0.f), s1 = s0;
+      {
+        uint32_t x[2][32];
+        tmem_ld_32x32b_x32(tmem_S, x[0]);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          tmem_ld_wait();
+          if (u < 3) tmem_ld_32x32b_x32(tmem_S + (uint32_t)(32 * (u + 1)), x[(u + 1) & 1]);
+          uint32_t pk[16];
+#pragma unroll
+          for (int e = 0; e < 32; e += 4) {
+            const float2 x0 = ffma2(make_float2(__uint_as_float(x[u & 1][e]), __uint_as_float(x[u & 1][e + 1])), c2, neg_m2);
+            const float2 x1 = ffma2(make_float2(__uint_as_float(x[u & 1][e + 2]), __uint_as_float(x[u & 1][e + 3])), c2, neg_m2);
+            const float2 y0 = make_float2(f2_exp2(x0.x), f2_exp2(x0.y));
+            const float2 y1 = make_float2(f2_exp2(x1.x), f2_exp2(x1.y));
+            s0 = fadd2(s0, y0);
+            s1 = fadd2(s1, y1);
+            pk[e >> 1] = pack_bf16x2(y0.x, y0.y);
+            pk[(e >> 1) + 1] = pack_bf16x2(y1.x, y1.y);
+          }
+          tmem_st_32x32b_x16(tmem_S + (uint32_t)(16 * u), pk);
+        }
+      }
+      s0 = fadd2(s0, s1);
+      l += s0.x + s0.y;
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[i & 1]);
+      ++i;
+    }
+    // ---- epilogue
+    if (ok) ok = mbar_wait_bounded(o_full, 0, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL);
+    if (ok || n_active == 0) {
+      tc_fence_after();
+      const float inv_l = l > 0.f ? 1.f / l : 0.f;
+      const float lse2 = l > 0.f ? m_used + log2f(l) : INFINITY;
+      const int h = g * p.gs + (row_valid ? hq : 0);
+      const int tqv = row_valid ? tq : 0;
+      if (p.n_split > 1) {
+        const long long prow = (((long long)split * p.B + b) * p.H + h) * p.T + tqv;
+        float* pdst = p.part_o + prow * F3_HD;
+#pragma unroll 1
+        for (int c0 = 0; c0 < F3_HD; c0 += 32) {
+          uint32_t o[32];
+          if (n_active > 0) {
+            tmem_ld_32x32b_x32(tmem_O + (uint32_t)c0, o);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) o[e] = 0;
+          }
+          if (row_valid) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              *reinterpret_cast<float4*>(pdst + c0 + 4 * u) =
+                  make_float4(__uint_as_float(o[4 * u]) * inv_l, __uint_as_float(o[4 * u + 1]) * inv_l,
+                              __uint_as_float(o[4 * u + 2]) * inv_l, __uint_as_float(o[4 * u + 3]) * inv_l);
+          }
+        }
+        if (row_valid) p.part_lse2[prow] = l > 0.f ? lse2 : -INFINITY;
+      } else {
+        __nv_bfloat16* dst = p.out + (((long long)b * p.T + tqv) * p.H + h) * F3_HD;
+#pragma unroll 1
+        for (int c0 = 0; c0 < F3_HD; c0 += 32) {
+          uint32_t o[32];
+          if (n_active > 0) {
+            tmem_ld_32x32b_x32(tmem_O + (uint32_t)c0, o);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) o[e] = 0;
+          }
+          if (row_valid) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(o[8 * u + 0]) * inv_l, __uint_as_float(o[8 * u + 1]) * inv_l);
+              v.y = pack_bf16x2(__uint_as_float(o[8 * u + 2]) * inv_l, __uint_as_float(o[8 * u + 3]) * inv_l);
+              v.z = pack_bf16x2(__uint_as_float(o[8 * u + 4]) * inv_l, __uint_as_float(o[8 * u + 5]) * inv_l);
+              v.w = pack_bf16x2(__uint_as_float(o[8 * u + 6]) * inv_l, __uint_as_float(o[8 * u + 7]) * inv_l);
+              *reinterpret_cast<uint4*>(dst + c0 + 8 * u) = v;
+            }
+          }
+        }
+        if (row_valid && p.lse) p.lse[((long long)b * p.H + h) * p.T + tq] = lse2 * 0.6931471805599453f;
+        if (p.lse2) p.lse2[(bg * p.nQT + qt) * F2_T + row] = row_valid ? lse2 : INFINITY;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
 // ------------------------------------------------------------------ column sums
-constexpr int CS_QSTAGES = 4;
 constexpr int CS_SBUF = 4;
-struct CsSmem {
+// K tile | ring of query tiles (four, or two of the 64 KB tiles of head size 256) | barriers | exchange
+template <int HD>
+struct CsSmemT {
+  static constexpr int TILE = F2_T * (HD < 128 ? 128 : HD) * 2;  // head size 64 keeps the 32 KB slots of 128
+  static constexpr int QSTAGES = HD == 256 ? 2 : 4;
   static constexpr int K = 0;
-  static constexpr int Q = K + F2_TILE_BYTES;
-  static constexpr int BAR = Q + CS_QSTAGES * F2_TILE_BYTES;
+  static constexpr int Q = K + TILE;
+  static constexpr int BAR = Q + QSTAGES * TILE;
   static constexpr int XCH = BAR + 256;   // 128 floats: sums of the second warpgroup
   static constexpr int TOTAL = XCH + 512;
 };
+static_assert(CsSmemT<256>::TOTAL <= 232448, "shared memory of the column-sum kernel exceeds the limit of a CTA");
 
 template <bool GEN, int HD>
 __global__ void __launch_bounds__(F2_THREADS, 1)
 colsum_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const F2Params p) {
+  using CsSmem = CsSmemT<HD>;
+  constexpr int CS_QSTAGES = CsSmem::QSTAGES;
+  constexpr int CS_TILE = CsSmem::TILE;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   if (smem_u32(smem) & 1023u) {
@@ -899,7 +1266,7 @@ colsum_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 
   if (p.rows_used < F2_T) {
     for (int s = 0; s < CS_QSTAGES; ++s)
-      f2_zero_unused_rows(smem + CsSmem::Q + s * F2_TILE_BYTES, p.rows_used, threadIdx.x, F2_THREADS, HD / 64);
+      f2_zero_unused_rows(smem + CsSmem::Q + s * CS_TILE, p.rows_used, threadIdx.x, F2_THREADS, HD / 64);
     fence_proxy_async_smem();
   }
   if (threadIdx.x == 0) {
@@ -929,8 +1296,9 @@ colsum_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       tma_prefetch_desc(&tmQ);
       tma_prefetch_desc(&tmK);
       mbar_expect_tx(k_full, F2_T * HD * 2);
-      tma_load_4d(smem + CsSmem::K, &tmK, k_full, 0, t * F2_T, g, b);
-      if (HD == 128) tma_load_4d(smem + CsSmem::K + F2_CHUNK_BYTES, &tmK, k_full, 64, t * F2_T, g, b);
+#pragma unroll
+      for (int cch = 0; cch < HD / 64; ++cch)
+        tma_load_4d(smem + CsSmem::K + cch * F2_CHUNK_BYTES, &tmK, k_full, 64 * cch, t * F2_T, g, b);
       const uint32_t q_bytes = (uint32_t)p.rows_used * (uint32_t)HD * 2u;
       bool ok = true;
       for (int i = 0; i < n_q && ok; ++i) {
@@ -939,10 +1307,11 @@ colsum_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           ok = false;
           break;
         }
-        uint8_t* qd = smem + CsSmem::Q + st * F2_TILE_BYTES;
+        uint8_t* qd = smem + CsSmem::Q + st * CS_TILE;
         mbar_expect_tx(&q_full[st], q_bytes);
-        tma_load_4d(qd, &tmQ, &q_full[st], 0, g * p.gs, (qt_first + i) * p.npos, b);
-        if (HD == 128) tma_load_4d(qd + F2_CHUNK_BYTES, &tmQ, &q_full[st], 64, g * p.gs, (qt_first + i) * p.npos, b);
+#pragma unroll
+        for (int cch = 0; cch < HD / 64; ++cch)
+          tma_load_4d(qd + cch * F2_CHUNK_BYTES, &tmQ, &q_full[st], 64 * cch, g * p.gs, (qt_first + i) * p.npos, b);
       }
       if (!ok) {
         long long c0 = clock64();
@@ -960,7 +1329,7 @@ colsum_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         if (!(ok = mbar_wait_bounded(&q_full[st], (i / CS_QSTAGES) & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL))) break;
         if (!(ok = mbar_wait_bounded(&s_empty[sb], ((i / CS_SBUF) & 1) ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY))) break;
         tc_fence_after();
-        const uint32_t q_addr = smem_u32(smem + CsSmem::Q + st * F2_TILE_BYTES);
+        const uint32_t q_addr = smem_u32(smem + CsSmem::Q + st * CS_TILE);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (uint32_t)((kk >> 2) * F2_CHUNK_BYTES + (kk & 3) * 32);
@@ -1097,7 +1466,7 @@ static int f2_launch(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUten
   static kvb::PerDeviceOnce attr_once;
   if (attr_once.first()) {
     cudaFuncSetAttribute(flash_fwd_kernel<GEN, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, F2Smem::TOTAL);
-    cudaFuncSetAttribute(colsum_kernel<GEN, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, CsSmem::TOTAL);
+    cudaFuncSetAttribute(colsum_kernel<GEN, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, CsSmemT<HD>::TOTAL);
   }
   const int nPair = (p.nQT + 1) / 2;
   flash_fwd_kernel<GEN, HD><<<dim3(p.B * p.G * nPair, p.n_split), F2_THREADS, F2Smem::TOTAL, s>>>(tmQ, tmK, tmV, p);
@@ -1105,7 +1474,28 @@ static int f2_launch(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUten
     const long long rows = (long long)p.B * p.G * p.nQT * F2_T;
     flash_merge_kernel<HD><<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(p);
   }
-  if (p.weights) colsum_kernel<GEN, HD><<<p.B * p.G * p.nT, F2_THREADS, CsSmem::TOTAL, s>>>(tmQ, tmK, p);
+  if (p.weights) colsum_kernel<GEN, HD><<<p.B * p.G * p.nT, F2_THREADS, CsSmemT<HD>::TOTAL, s>>>(tmQ, tmK, p);
+  return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
+}
+
+// the launches of one forward call for head size 256
+static int f3_launch(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const F2Params& p, bool gen,
+                     cudaStream_t s) {
+  static kvb::PerDeviceOnce attr_once;
+  if (attr_once.first()) {
+    cudaFuncSetAttribute(flash256_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F3Smem::TOTAL);
+    cudaFuncSetAttribute(colsum_kernel<false, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, CsSmemT<256>::TOTAL);
+    cudaFuncSetAttribute(colsum_kernel<true, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, CsSmemT<256>::TOTAL);
+  }
+  flash256_fwd_kernel<<<dim3(p.B * p.G * p.nQT, p.n_split), F3_THREADS, F3Smem::TOTAL, s>>>(tmQ, tmK, tmV, p);
+  if (p.n_split > 1) {
+    const long long rows = (long long)p.B * p.G * p.nQT * F2_T;
+    flash_merge_kernel<256><<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(p);
+  }
+  if (p.weights) {
+    if (gen) colsum_kernel<true, 256><<<p.B * p.G * p.nT, F2_THREADS, CsSmemT<256>::TOTAL, s>>>(tmQ, tmK, p);
+    else colsum_kernel<false, 256><<<p.B * p.G * p.nT, F2_THREADS, CsSmemT<256>::TOTAL, s>>>(tmQ, tmK, p);
+  }
   return cudaGetLastError() == cudaSuccess ? KVB_OK : KVB_ERR_LAUNCH;
 }
 
@@ -1158,7 +1548,8 @@ extern "C" long long kvb_sdpa_fwd_scratch_bytes(int B, int H, int G, int q_len, 
   const long long bgt = kvb::f2_round4((long long)B * G * nT);
   long long words = 2 * bgt + (long long)B * G * nT * 128 + (long long)B * G * nQT * 128;
   const int n_split = f2_num_splits((long long)B * G * ((nQT + 1) / 2), nT);
-  if (n_split > 1) words += kvb::f2_round4((long long)n_split * B * H * q_len) + (long long)n_split * B * H * q_len * 128;
+  // partial outputs sized for the largest head size (256); the number of splits of a launch never exceeds this one's
+  if (n_split > 1) words += kvb::f2_round4((long long)n_split * B * H * q_len) + (long long)n_split * B * H * q_len * 256;
   return words * 4;
 }
 
@@ -1188,7 +1579,7 @@ extern "C" int kvb_sdpa_fwd_ex(const void* q, const void* k, const void* v, cons
                                 float scale, int input_pos, int window, float softcap, int* status, void* stream) {
   using namespace kvb;
   if (window < 0 || softcap < 0.f || (softcap > 0.f && scale <= 0.f)) return KVB_ERR_ARG;
-  if (head_size != 128 && head_size != 64) return KVB_ERR_UNSUPPORTED;
+  if (head_size != 128 && head_size != 64 && head_size != 256) return KVB_ERR_UNSUPPORTED;
   if (q_sh == 0) q_sh = (long long)q_len * head_size;
   if (q_sb == 0) q_sb = (long long)H * q_sh;
   if ((q_sb % 8) || (q_sh % 8) || q_sh < (long long)q_len * head_size) return KVB_ERR_ALIGN;
@@ -1231,12 +1622,13 @@ extern "C" int kvb_sdpa_fwd_ex(const void* q, const void* k, const void* v, cons
   if ((rc = f2_make_tmap(&tmV, v, hd, kv_len, G, B, hd, k_sg, k_sb, 64, F2_T, 1))) return rc;
 
   f2_prepare_kernel<<<B * G * p.nT, F2_T, 0, s>>>(token_pos, tmin, tmax, pos, G, kv_len, p.nT, tp_sb, tp_sg);
-  const int nPair = (p.nQT + 1) / 2;
+  const int nPair = head_size == 256 ? p.nQT : (p.nQT + 1) / 2;  // head size 256: one query tile per CTA
   p.n_split = f2_num_splits((long long)B * G * nPair, p.nT);
   p.tiles_per_split = (p.nT + p.n_split - 1) / p.n_split;
   p.part_lse2 = lse2 + (long long)B * G * p.nQT * 128;
   p.part_o = p.part_lse2 + f2_round4((long long)p.n_split * B * H * q_len);
   const bool gen = window > 0 || softcap > 0.f;
+  if (head_size == 256) return f3_launch(tmQ, tmK, tmV, p, gen, s);
   if (head_size == 128) return gen ? f2_launch<true, 128>(tmQ, tmK, tmV, p, s) : f2_launch<false, 128>(tmQ, tmK, tmV, p, s);
   return gen ? f2_launch<true, 64>(tmQ, tmK, tmV, p, s) : f2_launch<false, 64>(tmQ, tmK, tmV, p, s);
 }

@@ -507,19 +507,21 @@ def gemm_pair(a: torch.Tensor, b: torch.Tensor, a2=None, b2=None, residual=None,
 def sdpa_supported(query: torch.Tensor, key: torch.Tensor, sliding_window, softcap) -> bool:
     H, G = query.shape[1], key.shape[1]
     gs = H // G
-    return (query.dtype == torch.bfloat16 and query.shape[-1] in (64, 128) and gs <= 128 and query.shape[2] > 0
+    return (query.dtype == torch.bfloat16 and query.shape[-1] in (64, 128, 256) and gs <= 128 and query.shape[2] > 0
             and (sliding_window is None or sliding_window > 0) and (softcap is None or softcap > 0))
 
 
 def sdpa_bwd_supported(query: torch.Tensor, key: torch.Tensor, sliding_window, softcap) -> bool:
     """Same shapes as the forward, with at most 64 query heads per KV head (a 64-column unit of the dK/dV launch
     holds all heads of a group). Any group size: 5 (Qwen3-14B) packs 25 positions x 5 heads into the 128-row tile."""
-    return sdpa_supported(query, key, sliding_window, softcap) and query.shape[1] // key.shape[1] <= 64
+    return (sdpa_supported(query, key, sliding_window, softcap) and query.shape[-1] in (64, 128)
+            and query.shape[1] // key.shape[1] <= 64)
 
 
 def sdpa_fwd(query, key, value, scale, input_pos, token_pos=None, return_weights=False, sliding_window=None, softcap=None):
     """SDPA forward: flash sweep (P in TMEM, online softmax) + column-owner weight sums. Returns
-    ``(out (B,T,H·D) bf16, weights (B,G,L) fp32 | None, lse (B,H,T) fp32)``; head size 128 or 64, any group size up to 128.
+    ``(out (B,T,H·D) bf16, weights (B,G,L) fp32 | None, lse (B,H,T) fp32)``; head size 128, 64 or 256 (256: forward
+    only, one query tile per CTA), any group size up to 128.
     ``sliding_window``: a query at position ``p`` sees tokens in ``(p - window, p]`` only; ``softcap``: scores
     become ``cap · tanh(score / cap)`` (both inside the kernels)."""
     B, H, T, D = query.shape

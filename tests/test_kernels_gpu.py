@@ -335,6 +335,16 @@ def test_sdpa_reads_a_slice_of_positions_in_place(D):
     torch.testing.assert_close(res[0][0].float(), out_r.float(), atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("B,H,G,T,L,mode,window,softcap", [
+    (1, 8, 4, 256, 2048, "perm", None, None), (2, 8, 4, 100, 1000, "perm", None, None), (1, 16, 8, 700, 700, "arange", None, None),
+    (1, 8, 4, 300, 1500, "arange", 256, 50.0), (1, 4, 1, 64, 8192, "perm", None, None), (1, 8, 4, 1, 2048, "arange", 512, 50.0),
+    (1, 6, 2, 77, 900, "arange", None, None)])
+def test_sdpa_head_size_256(B, H, G, T, L, mode, window, softcap):
+    """Head size 256 (Gemma-2 2b / 9b, Gemma-3 shapes), forward: one query tile per CTA, S double buffered over the KV
+    tiles, O of 256 TMEM columns; outputs, normalisers and summed weights."""
+    _sdpa_case(B, H, G, T, L, 3 * L if mode == "perm" else L - T, mode, window=window, softcap=softcap, D=256)
+
+
 def test_sdpa_is_deterministic():
     """Outputs, normalisers and the summed weights (which drive the eviction decisions) are bit-identical run to run."""
     D, B, H, G, T, L = 128, 1, 32, 8, 512, 4096  # 64 CTAs: split over the KV axis, partials merged in a fixed order
