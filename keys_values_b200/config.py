@@ -205,6 +205,15 @@ configs: List[dict] = [
         n_head=4, n_query_groups=2, head_size=64, intermediate_size=512,
         norm_eps=1e-5, rope_base=500000, **_llama_like,
     ),
+    dict(  # head size 256 with a window layer and capped scores (Gemma-2 2b / 9b shapes): forward kernels only
+        name="tiny-gemma2-d256",
+        block_size=4096, vocab_size=1024, padded_vocab_size=1024, n_layer=2, n_embd=256,
+        n_head=4, n_query_groups=2, head_size=256, intermediate_size=512, norm_eps=1e-6,
+        rotary_percentage=1.0, parallel_residual=False, bias=False, norm_class_name="RMSNorm",
+        mlp_class_name="GemmaMLP", gelu_approximate="tanh", scale_embeddings=True,
+        post_attention_norm=True, post_mlp_norm=True, sliding_window_size=96, sliding_window_indices=[1, 0],
+        attention_logit_softcapping=4.0, final_logit_softcapping=30.0,
+    ),
     dict(  # Gemma-2 style: every other layer with a sliding window, capped attention scores and logits
         name="tiny-gemma2",
         block_size=4096, vocab_size=1024, padded_vocab_size=1024, n_layer=2, n_embd=256,

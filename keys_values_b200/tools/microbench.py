@@ -1,7 +1,7 @@
 """Kernel micro-benchmarks: CUDA-event timing after warm-up, with an L2 flush
 (a write larger than the 126 MB L2) between timed iterations.
 
-    python -m keys_values_b200.tools.microbench sdpa|sdpa_train|sdpa_bwd|sdpa_variants|gemm|elementwise|all [--out file.jsonl]
+    python -m keys_values_b200.tools.microbench sdpa|sdpa_train|sdpa_bwd|sdpa_variants|sdpa_head_sizes|gemm|elementwise|all [--out file.jsonl]
 
 ``sdpa`` covers the SDPA-with-weights grid: bf16 GQA 32/8 heads, head size 128,
 batch 1 and 4, query length {1, 256, 2048}, KV length {4096, 16384, 32768}.
@@ -161,6 +161,26 @@ def bench_sdpa_variants(out, peaks):
              "fwd_with_weights_us": ms_f * 1e3, "bwd_us": ms_b * 1e3})
 
 
+def bench_sdpa_head_sizes(out, peaks):
+    """Forward with summed weights on the training chunk for the head sizes the kernels cover (256: forward only)."""
+    from keys_values_b200.ops import cuda as cu
+
+    dev = torch.device("cuda")
+    flush = _flush_buf(dev)
+    B, T, L = 1, 1024, 16384
+    for D, H, G in ((64, 32, 8), (128, 32, 8), (256, 16, 8)):
+        scale = 1 / math.sqrt(D)
+        q = torch.randn(B, H, T, D, device=dev, dtype=torch.bfloat16)
+        k = torch.randn(B, G, L, D, device=dev, dtype=torch.bfloat16)
+        v = torch.randn(B, G, L, D, device=dev, dtype=torch.bfloat16)
+        ms_w = time_fn(lambda: cu.sdpa_fwd(q, k, v, scale, L - T, None, True), flush=flush)
+        ms = time_fn(lambda: cu.sdpa_fwd(q, k, v, scale, L - T, None, False), flush=flush)
+        cu.check_status(dev)
+        flops = 4.0 * B * H * T * L * D
+        out({"bench": "sdpa_head_size", "D": D, "H": H, "G": G, "q": T, "kv": L, "fwd_with_weights_us": ms_w * 1e3, "fwd_us": ms * 1e3,
+             "fwd_tflops": flops / ms / 1e9, "fwd_frac_of_measured_peak": flops / ms / 1e9 / peaks["bf16_tflops"]})
+
+
 def bench_gemm(out, peaks):
     from keys_values_b200.ops import cuda as cu
 
@@ -245,6 +265,8 @@ def main():
         bench_sdpa_bwd(out, peaks)
     if args.which in ("sdpa_variants", "all"):
         bench_sdpa_variants(out, peaks)
+    if args.which in ("sdpa_head_sizes", "all"):
+        bench_sdpa_head_sizes(out, peaks)
     if args.which in ("elementwise", "all"):
         bench_elementwise(out, peaks)
 

@@ -106,6 +106,36 @@ def test_graph_decode_with_sliding_window_and_softcap(cache_name, monkeypatch):
         assert torch.allclose(lg.float(), results[False][1][0], atol=8e-2, rtol=5e-2)
 
 
+def test_inference_with_head_size_256_runs_on_the_native_forward(monkeypatch):
+    """Head size 256 with a window layer and capped scores: chunked prefill and single-token steps are served by the
+    head-size-256 forward kernels (strict mode: no restatement), and agree with the PyTorch restatement step by step."""
+    from keys_values_b200 import ops
+
+    monkeypatch.setenv("KVB200_STRICT_NATIVE", "1")
+    B, C, T, steps = 2, 256, 600, 6
+    cfg, m, dev = _setup("h2o-default", B, C, model="tiny-gemma2-d256")
+    prompts = torch.randint(0, cfg.vocab_size, (B, T), device=dev)
+    with torch.inference_mode():
+        logits = _prefill(m, prompts, T + steps + 1)
+        tok = logits.argmax(-1).view(B, 1)
+        toks, lgs = [tok.clone()], []
+        for _ in range(steps):
+            lg = m(tok)
+            tok = lg[:, -1].argmax(-1, keepdim=True)
+            toks.append(tok.clone())
+            lgs.append(lg.float().clone())
+        monkeypatch.setenv("KVB200_STRICT_NATIVE", "0")
+        ops.set_native_attention(False)
+        try:
+            logits_r = _prefill(m, prompts, T + steps + 1)
+            lgs_r = [m(t).float().clone() for t in toks[:steps]]  # the same tokens fed to the restatement
+        finally:
+            ops.set_native_attention(True)
+    assert torch.allclose(logits.float(), logits_r.float(), atol=8e-2, rtol=5e-2)
+    for a, b in zip(lgs, lgs_r):
+        assert torch.allclose(a, b, atol=8e-2, rtol=5e-2)
+
+
 def test_graph_decode_conditions_and_generate_api():
     B, C, T = 2, 256, 100
     cfg, m, dev = _setup("h2o-default", B, C)
