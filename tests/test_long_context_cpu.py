@@ -107,7 +107,7 @@ def test_gradients_multi_cell_equal_single_cell(name, lpc):
     torch.testing.assert_close(gm(ids, tg).mean(), torch.tensor(res[0][0]), atol=1e-6, rtol=1e-6)
 
 
-@pytest.mark.parametrize("name", ["tiny-gemma2", "tiny-llama-d64"])
+@pytest.mark.parametrize("name", ["tiny-gemma2", "tiny-llama-d64", "tiny-gemma2-d256"])
 def test_gradients_window_softcap_and_small_heads_chunked_equal_naive(name):
     """A Gemma-2 style model (one layer with a sliding window, capped attention scores and logits, post norms) and a model
     with head size 64: the chunked pass over a cache that holds the whole sequence equals whole-sequence autograd."""
