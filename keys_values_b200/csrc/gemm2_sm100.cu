@@ -780,8 +780,7 @@ int launch_gemm_pair(const void* A, const void* B, const void* A2, const void* B
   // tiles still fill the last wave of pairs: 8192^3 0.81 -> 0.92 of the library GEMM, 8192 x 14336 x 4096 0.84 -> 0.88;
   // 8192 x 4096 x 2048 0.92 -> 0.79)
   const int waves_wide = (tiles_wide + pairs - 1) / pairs;
-  // (the reduce-scatter epilogue stays on the narrow tile, the configuration that the multi-GPU tests cover)
-  const bool wide_pays = K + K2 >= 4096 && tiles_wide >= 3 * pairs && 10LL * tiles_wide >= 9LL * waves_wide * pairs && ex.rs_world <= 1;
+  const bool wide_pays = K + K2 >= 4096 && tiles_wide >= 3 * pairs && 10LL * tiles_wide >= 9LL * waves_wide * pairs;
   if (g2_wide_mode() == 2 || (g2_wide_mode() == 1 && wide_pays && !g2_diag())) {
     if (tiles_wide < pairs) pairs = tiles_wide;
     gemm2w_bf16_kernel<<<2 * (pairs + copy_pairs), G2W_THREADS, G2WSmem::TOTAL, stream>>>(

@@ -132,6 +132,15 @@ def test_fused_tp_gemm_collectives_match_nccl():
 
 @pytest.mark.gpu
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_tp_gemm_collectives_on_wide_pair_tiles(monkeypatch):
+    """The same collectives with the CTA-pair GEMM forced onto its 256 x 512 tiles (all-gather gating and the
+    reduce-scatter epilogue of eight epilogue warps)."""
+    monkeypatch.setenv("KVB200_GEMM2_TILE", "wide")
+    _run("tp_ops", 2)
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_tp_model_matches_single_gpu():
     _run("tp_model", 2)
 
