@@ -17,11 +17,15 @@ def main():
     ap.add_argument("--kv", type=int, default=16384)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--bits", type=int, default=8, help="decode: 16 (bf16 cache), 8 or 4")
+    ap.add_argument("--head-size", type=int, default=128, help="sdpa_fwd: 128, 64 or 256 (256: 16 heads over 8 groups)")
     args = ap.parse_args()
     from keys_values_b200.ops import cuda as cu
 
     dev = torch.device("cuda")
     H, G, D = 32, 8, 128
+    if args.which == "sdpa_fwd" and args.head_size != 128:
+        D = args.head_size
+        H = 16 if D == 256 else 32
     scale = 1 / math.sqrt(D)
     B, T, L = args.batch, args.q, args.kv
     torch.manual_seed(0)
