@@ -35,6 +35,11 @@
 //   memory, no atomics, no partial buffers, a fixed order (run-to-run identical eviction decisions).
 //   Position-major query rows turn the causal mask of a slot into one threshold on the column index.
 //
+// Variants: head size 64 and 128 are template parameters of these kernels (HD), sliding window and logit soft-capping a
+// separate instantiation (GEN); head size 256 has its own flash kernel further down (flash256_fwd_kernel) and shares the
+// column-sum and merge kernels. Launches with few query tiles are split over the KV axis (fp32 partials, merged in a
+// fixed order by flash_merge_kernel).
+//
 // Replaces FlashInfer prefill + Triton score-sum + K/V reordering + query padding of the reference
 // (keys_values/attention/flashinfer_wrapper.py:51-273, :367-510, csrc/kernels/sdpa_prefill.cu,
 // attention/sdpa_wrapper.py:66-432).
