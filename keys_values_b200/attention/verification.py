@@ -51,8 +51,8 @@ def verify_backend_equivalence(query: torch.Tensor, key: torch.Tensor, value: to
                                rtol: float = 2e-2, atol: float = 2e-2, log_results: bool = True,
                                sliding_window_size: Optional[int] = None, softcap: Optional[float] = None) -> BackendEquivalenceResult:
     """``query (B,H,q,D)``, ``key / value (B,G,kv,D)`` on a GPU. A query of length 1 goes to the decode
-    kernel, longer ones (and layers with a sliding window or capped scores) to the tcgen05 forward (head size 128 or
-    64); the weights compared are the per-slot sums the
+    kernel, longer ones (and layers with a sliding window or capped scores) to the tcgen05 forward (head size 128,
+    64 or 256); the weights compared are the per-slot sums the
     cache policies consume (``(B,G,kv)``, summed over queries, averaged over the heads of a group)."""
     from keys_values_b200.ops import cuda as cu
 
